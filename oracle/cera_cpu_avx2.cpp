@@ -32,8 +32,10 @@ namespace {
 class RowPool {
   public:
     static RowPool &get() {
-        static RowPool p;
-        return p;
+        // Leaked on purpose: parked workers still wait on the condition variable
+        // at process exit, and destroying it under them would block.
+        static RowPool *p = new RowPool();
+        return *p;
     }
     // Runs f(lo, hi) over [0, m) split into `parts` contiguous ranges.
     void run(size_t m, int parts, const std::function<void(size_t, size_t)> &f) {

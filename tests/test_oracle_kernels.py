@@ -1,0 +1,285 @@
+"""Pins the oracle's int8 kernels, quantizer and glue with the reference's tests.
+
+Restates cera/src/backend/simd.rs:6584-6743 (integer reference, GEMV and GEMM),
+7017-7103 (GEMV == GEMM at n=1), 7113-7213 (K-quant and Q4_1 against a
+dequantize-then-dot f64 reference), 7872-7946 (quantizer corner blocks),
+cera/src/backend/cpu.rs:6074-6189 (rmsnorm / softmax / expf), and
+cera/src/model/lfm2.rs:3619-3720 (routing).
+"""
+import math
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+import ref_fixtures as R
+
+SHAPES = [(9, 7), (8, 8), (3, 2), (16, 5)]
+
+
+@pytest.mark.parametrize("avx2", [False, True])
+def test_gemm_matches_integer_reference(avx2):
+    if avx2 and not O.has_avx2():
+        pytest.skip("host has no AVX2")
+    k = 128
+    for m, n in SHAPES:
+        rng = R.Lcg(0x77AA33CC)
+        q4 = R.q4_0_rows(m, k, rng)
+        q8 = R.q8_0_rows_with_extremes(m, k, rng)
+        bs, bq = R.activations(n, k, rng)
+        for t, w, is4 in ((O.Q4_0, q4, True), (O.Q8_0, q8, False)):
+            got = O.gemm_preq(t, w, bs, bq, m, n, k, avx2=avx2)
+            want = R.ref_gemm(w, bs, bq, m, n, k, is4)
+            assert np.abs(got).max() > 0
+            assert np.all(np.abs(got - want) <= 1e-5 * np.maximum(np.abs(want), 1.0)), (m, n, t)
+
+
+@pytest.mark.parametrize("avx2", [False, True])
+def test_gemv_matches_integer_reference(avx2):
+    if avx2 and not O.has_avx2():
+        pytest.skip("host has no AVX2")
+    k = 128
+    for m in (1, 3, 8, 9, 16):
+        rng = R.Lcg(0x22446688)
+        q4 = R.q4_0_rows(m, k, rng)
+        q8 = R.q8_0_rows_with_extremes(m, k, rng)
+        xs, xq = R.activations(1, k, rng)
+        for t, w, is4 in ((O.Q4_0, q4, True), (O.Q8_0, q8, False)):
+            got = O.gemm_preq(t, w, xs, xq, m, 1, k, avx2=avx2)
+            want = R.ref_gemm(w, xs, xq, m, 1, k, is4)
+            assert np.all(np.abs(got - want) <= 1e-5 * np.maximum(np.abs(want), 1.0))
+
+
+def _dequant_reference(t, w, bs, bq, m, n, k):
+    rb = O.row_bytes(t, k)
+    out = np.zeros((m, n), dtype=np.float64)
+    for i in range(m):
+        wf = O.dequantize(t, w[i * rb:(i + 1) * rb], k)
+        for j in range(n):
+            xa = np.repeat(bs[j * (k // 32):(j + 1) * (k // 32)], 32) * bq[j * k:(j + 1) * k].astype(np.float32)
+            out[i, j] = (wf * xa.astype(np.float32)).astype(np.float64).sum()
+    return out
+
+
+@pytest.mark.parametrize("avx2", [False, True])
+def test_k_quant_gemm_matches_dequant_reference(avx2):
+    if avx2 and not O.has_avx2():
+        pytest.skip("host has no AVX2")
+    m, k = 3, 512
+    rng = R.Lcg(0x9F1E2D3C)
+    q4k, q6k = R.k_quant_rows(m, k // 256, rng)
+    for n in (5, 1):
+        bs, bq = R.activations(n, k, rng)
+        for t, w in ((O.Q4_K, q4k), (O.Q6_K, q6k)):
+            got = O.gemm_preq(t, w, bs, bq, m, n, k, avx2=avx2).astype(np.float64)
+            want = _dequant_reference(t, w, bs, bq, m, n, k)
+            assert np.all(np.abs(got - want) <= 1e-5 * (1.0 + np.abs(want))), (t, n)
+
+
+@pytest.mark.parametrize("avx2", [False, True])
+def test_gemm_q4_1_matches_dequant_reference(avx2):
+    if avx2 and not O.has_avx2():
+        pytest.skip("host has no AVX2")
+    m, n, k = 3, 11, 512
+    rng = R.Lcg(0x04517B3D)
+    w = R.q4_1_rows(m, k, rng)
+    bs, bq = R.activations(n, k, rng)
+    got = O.gemm_preq(O.Q4_1, w, bs, bq, m, n, k, avx2=avx2).astype(np.float64)
+    want = _dequant_reference(O.Q4_1, w, bs, bq, m, n, k)
+    assert np.all(np.abs(got - want) <= 1e-5 * (1.0 + np.abs(want)))
+
+
+def test_q5_k_extension_matches_dequant_reference():
+    # No reference kernel exists for Q5_K x Q8_0: this is the only pin it has.
+    import test_oracle_formats as F
+    m, n, k = 3, 5, 512
+    rng = np.random.default_rng(5)
+    w = F._rand_block_bytes(O.Q5_K, m, k, rng)
+    lcg = R.Lcg(0x5555)
+    bs, bq = R.activations(n, k, lcg)
+    got = O.gemm_preq(O.Q5_K, w, bs, bq, m, n, k).astype(np.float64)
+    want = _dequant_reference(O.Q5_K, w, bs, bq, m, n, k)
+    assert np.all(np.abs(got - want) <= 1e-5 * (1.0 + np.abs(want)))
+
+
+def test_avx2_build_is_bit_identical_to_scalar_restatement():
+    if not O.has_avx2():
+        pytest.skip("host has no AVX2")
+    import test_oracle_formats as F
+    rng = np.random.default_rng(11)
+    for t in (O.Q4_0, O.Q8_0, O.Q4_1, O.Q4_K, O.Q6_K):
+        for (m, n) in ((9, 7), (3, 1), (70, 5), (130, 1)):
+            k = 512
+            w = F._rand_block_bytes(t, m, k, rng)
+            lcg = R.Lcg(0xABCDEF + t)
+            bs, bq = R.activations(n, k, lcg)
+            a = O.gemm_preq(t, w, bs, bq, m, n, k, avx2=False)
+            b = O.gemm_preq(t, w, bs, bq, m, n, k, avx2=True, threads=4)
+            assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), (t, m, n)
+
+
+# simd.rs:7017-7103: the GEMV entry is the GEMM at n == 1, bit for bit.
+def test_gemv_is_gemm_at_n1():
+    import test_oracle_formats as F
+    rng = np.random.default_rng(3)
+    k, m = 512, 7
+    x = rng.standard_normal(k).astype(np.float32)
+    xs, xq = O.quantize_q8_0(x)
+    for t in (O.Q4_0, O.Q8_0, O.Q4_1, O.Q4_K, O.Q6_K):
+        w = F._rand_block_bytes(t, m, k, rng)
+        a = O.gemv(t, w, x, m, k)
+        b = O.gemm_preq(t, w, xs, xq, m, 1, k).ravel()
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+        assert np.abs(a).max() > 0
+
+
+# ---- Q8_0 activation quantizer -------------------------------------------
+
+def test_quantizer_zero_block():
+    s, q = O.quantize_q8_0(np.zeros(64, dtype=np.float32))
+    assert np.all(s == 0) and np.all(q == 0)
+
+
+def test_quantizer_corner_blocks():
+    for amax in (1e-30, 1e-38, 1e-40, 1e-44, float("nan")):
+        x = np.zeros(32, dtype=np.float32)
+        x[0], x[1], x[2] = amax, -amax, np.float32(amax) / np.float32(2)
+        s, q = O.quantize_q8_0(x)
+        assert np.all(q != -128) or s[0] == 0.0
+        assert not np.isnan(s[0])
+    x = np.full(32, 0.25, dtype=np.float32)
+    x[0], x[1] = np.nan, -1.0
+    s, q = O.quantize_q8_0(x)
+    assert q[0] == 0 and q[1] == -127 and q[2] == 32
+    x[0] = np.inf
+    s, q = O.quantize_q8_0(x)
+    assert np.isinf(s[0]) and np.all(q == 0)
+
+
+def test_quantizer_matches_formula():
+    rng = np.random.default_rng(0)
+    x = (rng.standard_normal(4096) * 3).astype(np.float32)
+    s, q = O.quantize_q8_0(x)
+    xb = x.reshape(-1, 32)
+    amax = np.abs(xb).max(axis=1)
+    d = (amax / np.float32(127.0)).astype(np.float32)
+    assert np.array_equal(s, d.astype(np.float16).astype(np.float32))
+    idv = (np.float32(1.0) / d).astype(np.float32)
+    want = np.clip(np.rint(xb * idv[:, None]), -128, 127).astype(np.int8)
+    assert np.array_equal(q.reshape(-1, 32), want)
+
+
+def test_quantize_columns_is_per_column_quantize():
+    rng = np.random.default_rng(1)
+    dim, n = 128, 5
+    mat = rng.standard_normal((dim, n)).astype(np.float32)
+    s, q = O.quantize_columns(mat, dim, n)
+    for j in range(n):
+        sj, qj = O.quantize_q8_0(mat[:, j].copy())
+        assert np.array_equal(s[j * (dim // 32):(j + 1) * (dim // 32)], sj)
+        assert np.array_equal(q[j * dim:(j + 1) * dim], qj)
+
+
+# ---- weight quantizers: round trip error bounds ---------------------------
+
+@pytest.mark.parametrize("t,tol", [(O.Q8_0, 0.006), (O.Q4_0, 0.13), (O.Q4_1, 0.07), (O.Q4_K, 0.09),
+                                   (O.Q5_K, 0.05), (O.Q6_K, 0.05)])
+def test_weight_quantizer_round_trip(t, tol):
+    w = O.synth_normal(8 * 1024, seed=42, sigma=0.02)
+    raw = O.quantize_weights(t, w)
+    back = O.dequantize(t, raw, w.size)
+    err = np.abs(back - w).max()
+    assert err <= tol * np.abs(w).max(), err
+    assert np.isfinite(back).all()
+
+
+def test_synth_normal_moments():
+    x = O.synth_normal(1 << 18, seed=1, sigma=1.0)
+    assert abs(float(x.mean())) < 0.01 and abs(float(x.std()) - 1.0) < 0.01
+    y = O.synth_normal(1000, seed=1, sigma=1.0, offset=1000)
+    assert np.array_equal(x[1000:2000], y)
+
+
+# ---- glue -----------------------------------------------------------------
+
+def test_expf_tracks_libm():
+    for v in np.linspace(-80, 80, 4001):
+        got = O.expf(float(np.float32(v)))
+        want = math.exp(float(np.float32(v)))
+        assert abs(got - want) <= 3e-7 * want + 1e-38
+    assert O.expf(-200.0) == 0.0 and math.isinf(O.expf(200.0))
+
+
+def test_rmsnorm_and_softmax():
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal(256).astype(np.float32)
+    w = rng.standard_normal(256).astype(np.float32)
+    got = O.rmsnorm(x, w, 1e-5)
+    inv = np.float32(1.0 / math.sqrt(float((x.astype(np.float64) ** 2).mean()) + float(np.float32(1e-5))))
+    assert np.array_equal(got, (x * inv) * w)
+    p = O.softmax(x)
+    assert abs(float(p.sum()) - 1.0) < 1e-5 and p.argmax() == x.argmax()
+
+
+def test_rope_norm_rotates_adjacent_pairs():
+    hd = 8
+    q = np.arange(hd, dtype=np.float32) + 1
+    k = q.copy()
+    q0, _ = O.rope(q, k, 0, 1, 1, hd, 10000.0)
+    assert np.array_equal(q0, q)  # pos 0 is the identity
+    q1, k1 = O.rope(q, k, 3, 1, 1, hd, 10000.0)
+    ts = np.float32(10000.0) ** np.float32(-2.0 / hd)
+    theta = np.float32(3.0)
+    for i in range(hd // 2):
+        c, s = math.cos(float(theta)), math.sin(float(theta))
+        assert abs(q1[2 * i] - (q[2 * i] * c - q[2 * i + 1] * s)) < 1e-5
+        assert abs(q1[2 * i + 1] - (q[2 * i] * s + q[2 * i + 1] * c)) < 1e-5
+        theta = np.float32(theta * ts)
+    assert np.array_equal(q1, k1)
+    qn, _ = O.rope(q, k, 3, 1, 1, hd, 10000.0, rope_type=1)
+    assert abs(qn[0] - (q[0] * math.cos(3.0) - q[hd // 2] * math.sin(3.0))) < 1e-5
+
+
+def test_flash_prefill_matches_naive_decode_attention():
+    rng = np.random.default_rng(4)
+    nh, nkv, hd, n, start = 4, 2, 16, 37, 5
+    total = start + n
+    kc = rng.standard_normal((total, nkv * hd)).astype(np.float32)
+    vc = rng.standard_normal((total, nkv * hd)).astype(np.float32)
+    qm = rng.standard_normal((nh * hd, n)).astype(np.float32)
+    out = O.flash_attention_gqa(qm, kc, vc, nh, nkv, hd, n, start, 0.25)
+    for j in (0, 17, n - 1):
+        ref = O.decode_attention(qm[:, j].copy(), kc, vc, nh, nkv, hd, start + j + 1, 0.25).reshape(nh, hd)
+        assert np.allclose(out[:, j, :], ref, rtol=1e-4, atol=1e-5)
+
+
+def test_argmax_first_strict_max():
+    assert O.argmax(np.array([1.0, 5.0, 5.0, 2.0], dtype=np.float32)) == 1
+    assert O.argmax(np.array([np.nan, np.nan], dtype=np.float32)) == 0
+
+
+# ---- routing (lfm2.rs:3619-3720) -------------------------------------------
+
+def test_bias_ranks_experts_but_does_not_weight_them():
+    ids, w = O.select_experts([0.40, 0.30, 0.05, 0.01], [0.0, 0.5, 0.0, 0.0], 2)
+    assert list(ids) == [1, 0]
+    assert abs(w[0] - 0.30 / 0.70) < 1e-6 and abs(w[1] - 0.40 / 0.70) < 1e-6 and w[0] < w[1]
+
+
+def test_matches_llama_cpp_non_monotonic_token():
+    probs = np.zeros(32, dtype=np.float32)
+    bias = np.zeros(32, dtype=np.float32)
+    probs[21], probs[17], probs[6], probs[12] = 0.3474, 0.3556, 0.1866, 0.1103
+    bias[21] = 0.10
+    ids, w = O.select_experts(probs, bias, 4)
+    assert list(ids) == [21, 17, 6, 12]
+    assert np.all(np.abs(w - np.array([0.3474, 0.3556, 0.1866, 0.1103])) < 1e-3)
+
+
+def test_routing_ties_zero_gate_and_saturation():
+    ids, _ = O.select_experts([0.25] * 4, [0.0] * 4, 2)
+    assert list(ids) == [0, 1]
+    _, w = O.select_experts([0.0] * 4, [0.0] * 4, 2)
+    assert np.isfinite(w).all()
+    ids, w = O.select_experts([0.5, 0.3], [0.0, 0.0], 8)
+    assert list(ids) == [0, 1] and len(w) == 2
