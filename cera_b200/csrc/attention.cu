@@ -1,0 +1,316 @@
+// Flash-decode GQA attention: split-KV partial pass + merge pass.
+//
+// HBM-bound on the KV stream.  Grid = (n_kv_heads, n_splits): one CTA owns one
+// KV head and one contiguous range of cached positions and serves all G = n_heads /
+// n_kv_heads query heads of that KV head, so every K and V row is read from
+// HBM exactly once.  Inside a CTA each warp walks tiles of P = 32/G positions:
+//   * lane L holds head_dim/32 consecutive dims of every row (coalesced 128-bit loads),
+//   * the P*G partial dot products are reduced with a 31-shuffle butterfly transpose,
+//     leaving score (position L/G, head L%G) on lane L,
+//   * running max / sum per head are kept online (one exp per lane per tile),
+//   * probabilities are broadcast back by shuffle for the P x V accumulation.
+// Warps merge through shared memory, splits merge in a second kernel that also
+// emits the Q8_0 form of the output for the o-projection.
+//
+// Arithmetic contract: cera/src/model/transformer.rs:1166-1305 with
+// cera/src/backend/cpu.rs:3222-3363 (scores = q.K * scale, softmax with the
+// polynomial expf, weighted V sum); the online form agrees within f32 rounding.
+#include "ops.h"
+
+namespace cera {
+
+namespace {
+
+constexpr int ATT_WARPS = 8;
+constexpr int MAX_SPLITS = 64;
+
+template <int VEC, bool F16>
+__device__ __forceinline__ void load_row(const void *base, size_t elem_off, float (&v)[VEC]) {
+    if (F16) {
+        const __half *p = reinterpret_cast<const __half *>(base) + elem_off;
+        if (VEC == 4) {
+            const uint2 u = *reinterpret_cast<const uint2 *>(p);
+            const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
+            const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+            v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+        } else {
+#pragma unroll
+            for (int i = 0; i < VEC; i += 2) {
+                const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(p + i));
+                v[i] = a.x;
+                v[i + 1] = a.y;
+            }
+        }
+    } else {
+        const float *p = reinterpret_cast<const float *>(base) + elem_off;
+        if (VEC % 4 == 0) {
+#pragma unroll
+            for (int i = 0; i < VEC; i += 4) {
+                const float4 a = *reinterpret_cast<const float4 *>(p + i);
+                v[i] = a.x; v[i + 1] = a.y; v[i + 2] = a.z; v[i + 3] = a.w;
+            }
+        } else {
+            const float2 a = *reinterpret_cast<const float2 *>(p);
+            v[0] = a.x;
+            v[1] = a.y;
+        }
+    }
+}
+
+// Workspace record per (query head, split): out[head_dim], max, sum.
+template <int VEC, int G, bool F16>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_split_kernel(const float *__restrict__ q, const void *__restrict__ kc, const void *__restrict__ vc,
+                  uint32_t seq_len_imm, const uint32_t *__restrict__ seq_len_dev, uint32_t n_kv_heads, float scale,
+                  float *__restrict__ ws) {
+    constexpr int HD = VEC * 32;
+    constexpr int P = 32 / G;  // positions per warp tile
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t kvh = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
+    const uint32_t seq_len = seq_len_dev ? *seq_len_dev : seq_len_imm;
+    const size_t kv_dim = (size_t)n_kv_heads * HD;
+
+    uint32_t chunk = (seq_len + n_splits - 1) / n_splits;
+    chunk = (chunk + P - 1) / P * P;
+    const uint32_t t_begin = min(seq_len, split * chunk), t_end = min(seq_len, t_begin + chunk);
+
+    // q slices of the G heads this CTA serves
+    float qv[G][VEC];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) qv[g][v] = q[(size_t)(kvh * G + g) * HD + lane * VEC + v];
+
+    float acc[G][VEC];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[g][v] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;  // state of head (lane % G), replicated over its P lanes
+
+    const size_t head_off = (size_t)kvh * HD + lane * VEC;
+    for (uint32_t t0 = t_begin + warp * P; t0 < t_end; t0 += ATT_WARPS * P) {
+        float kr[P][VEC], vr[P][VEC];
+#pragma unroll
+        for (int i = 0; i < P; ++i) {
+            const uint32_t t = t0 + i;
+            if (t < t_end) {
+                load_row<VEC, F16>(kc, t * kv_dim + head_off, kr[i]);
+                load_row<VEC, F16>(vc, t * kv_dim + head_off, vr[i]);
+            } else {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) kr[i][v] = vr[i][v] = 0.0f;
+            }
+        }
+        float val[32];
+#pragma unroll
+        for (int i = 0; i < P; ++i)
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float s = 0.0f;
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) s = fmaf(qv[g][v], kr[i][v], s);
+                val[i * G + g] = s;
+            }
+        // butterfly transpose-reduce: afterwards lane L holds the full sum of val[L]
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+            const bool up = (lane & o) != 0;
+#pragma unroll
+            for (int j = 0; j < o; ++j) {
+                const float send = up ? val[j] : val[j + o];
+                const float keep = up ? val[j + o] : val[j];
+                val[j] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+            }
+        }
+        const uint32_t my_t = t0 + lane / G;
+        const float s = my_t < t_end ? __fmul_rn(val[0], scale) : -INFINITY;
+        float tmax = s;
+#pragma unroll
+        for (int o = G; o < 32; o <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+        const float m_new = fmaxf(m_run, tmax);  // finite: the tile holds at least one valid position
+        const float p = my_t < t_end ? ggml_expf(__fsub_rn(s, m_new)) : 0.0f;
+        const float corr = m_run == -INFINITY ? 0.0f : ggml_expf(__fsub_rn(m_run, m_new));
+        float psum = p;
+#pragma unroll
+        for (int o = G; o < 32; o <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+        l_run = fmaf(l_run, corr, psum);
+        m_run = m_new;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float cg = __shfl_sync(0xffffffffu, corr, g);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[g][v] *= cg;
+        }
+#pragma unroll
+        for (int i = 0; i < P; ++i)
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float pg = __shfl_sync(0xffffffffu, p, i * G + g);
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) acc[g][v] = fmaf(pg, vr[i][v], acc[g][v]);
+            }
+    }
+
+    // merge the warps of this CTA
+    __shared__ float s_acc[ATT_WARPS][G][HD];
+    __shared__ float s_m[ATT_WARPS][G], s_l[ATT_WARPS][G];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) s_acc[warp][g][lane * VEC + v] = acc[g][v];
+    if (lane < G) {
+        s_m[warp][lane] = m_run;
+        s_l[warp][lane] = l_run;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+        const int g = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, s_m[w][g]);
+        float L = 0.0f, O = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) {
+            const float f = s_m[w][g] == -INFINITY ? 0.0f : ggml_expf(s_m[w][g] - M);
+            L = fmaf(s_l[w][g], f, L);
+            O = fmaf(s_acc[w][g][d], f, O);
+        }
+        float *rec = ws + ((size_t)(kvh * G + g) * n_splits + split) * (HD + 2);
+        rec[d] = O;
+        if (d == 0) {
+            rec[HD] = M;
+            rec[HD + 1] = L;
+        }
+    }
+}
+
+// One CTA per query head, one thread per output dim.
+__global__ void attn_merge_kernel(const float *__restrict__ ws, uint32_t n_splits, uint32_t hd, float *__restrict__ out,
+                                  float *scales, int8_t *quants, int16_t *sums) {
+    const uint32_t h = blockIdx.x, d = threadIdx.x;
+    const float *base = ws + (size_t)h * n_splits * (hd + 2);
+    float M = -INFINITY;
+    for (uint32_t s = 0; s < n_splits; ++s) M = fmaxf(M, base[s * (hd + 2) + hd]);
+    double L = 0.0;
+    float O = 0.0f;
+    for (uint32_t s = 0; s < n_splits; ++s) {
+        const float *rec = base + s * (hd + 2);
+        const float m = rec[hd];
+        const float f = m == -INFINITY ? 0.0f : ggml_expf(m - M);
+        L += (double)(rec[hd + 1] * f);
+        O = fmaf(rec[d], f, O);
+    }
+    const float v = O * (float)(1.0 / L);
+    const size_t o = (size_t)h * hd + d;
+    out[o] = v;
+    if (quants) {
+        float scale;
+        int hs;
+        const int qv = quantize_lane(v, scale, hs);
+        quants[o] = (int8_t)qv;
+        if ((d & 31) == 0) scales[o / 32] = scale;
+        if ((d & 15) == 0) sums[o / 16] = (int16_t)hs;
+    }
+}
+
+template <int VEC, int G>
+int32_t launch_split(bool f16, dim3 grid, cudaStream_t st, const float *q, const void *kc, const void *vc,
+                     uint32_t seq_len, const uint32_t *seq_dev, uint32_t n_kv, float scale, float *ws) {
+    if (f16)
+        attn_split_kernel<VEC, G, true><<<grid, ATT_WARPS * 32, 0, st>>>(q, kc, vc, seq_len, seq_dev, n_kv, scale, ws);
+    else
+        attn_split_kernel<VEC, G, false><<<grid, ATT_WARPS * 32, 0, st>>>(q, kc, vc, seq_len, seq_dev, n_kv, scale, ws);
+    return CERA_CUDA_OK;
+}
+
+}  // namespace
+
+size_t attn_workspace_bytes(size_t n_heads, size_t head_dim, size_t) {
+    return n_heads * MAX_SPLITS * (head_dim + 2) * sizeof(float);
+}
+
+uint32_t attn_pick_splits(size_t n_kv_heads, size_t seq_len_hint) {
+    // Fill the machine about twice over, but never give a split fewer than 64 positions.
+    size_t want = (size_t)(2 * sm_count() + n_kv_heads - 1) / n_kv_heads;
+    const size_t by_len = (seq_len_hint + 63) / 64;
+    if (want > by_len) want = by_len;
+    if (want < 1) want = 1;
+    if (want > MAX_SPLITS) want = MAX_SPLITS;
+    return (uint32_t)want;
+}
+
+int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
+                                   size_t n_kv_heads, size_t head_dim, size_t seq_len, const uint32_t *seq_len_dev,
+                                   uint32_t n_splits, float scale, float *out, void *workspace, size_t workspace_bytes,
+                                   float *scales, int8_t *quants, int16_t *sums, cudaStream_t st) {
+    if (!q || !kc || !vc || !out || !workspace) return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: null argument");
+    if (n_kv_heads == 0 || n_heads % n_kv_heads)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: n_heads (%zu) must be a positive multiple of n_kv_heads (%zu)",
+                    n_heads, n_kv_heads);
+    const size_t G = n_heads / n_kv_heads;
+    if (seq_len == 0 && !seq_len_dev) return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: empty KV cache");
+    if (workspace_bytes < attn_workspace_bytes(n_heads, head_dim, seq_len))
+        return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: workspace of %zu bytes is too small", workspace_bytes);
+    if (n_splits < 1 || n_splits > MAX_SPLITS) return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: %u splits", n_splits);
+    const dim3 grid((unsigned)n_kv_heads, n_splits);
+    float *ws = (float *)workspace;
+    const bool f16 = kv_f16 != 0;
+    const uint32_t sl = (uint32_t)seq_len, nkv = (uint32_t)n_kv_heads;
+#define CERA_ATT(VEC, GG) launch_split<VEC, GG>(f16, grid, st, q, kc, vc, sl, seq_len_dev, nkv, scale, ws)
+    bool ok = true;
+    if (head_dim == 128) {
+        switch (G) {
+            case 4: CERA_ATT(4, 4); break;
+            case 8: CERA_ATT(4, 8); break;
+            default: ok = false;
+        }
+    } else if (head_dim == 64) {
+        switch (G) {
+            case 4: CERA_ATT(2, 4); break;
+            case 8: CERA_ATT(2, 8); break;
+            default: ok = false;
+        }
+    } else {
+        ok = false;
+    }
+#undef CERA_ATT
+    if (!ok)
+        return fail(CERA_CUDA_ERR_UNSUPPORTED, "decode_attention: head_dim %zu with group size %zu has no kernel "
+                    "(head_dim 64 or 128, group 4 or 8)", head_dim, G);
+    count_launch();
+    CERA_CUDA_TRY(cudaGetLastError());
+    attn_merge_kernel<<<(unsigned)n_heads, (unsigned)head_dim, 0, st>>>(ws, n_splits, (uint32_t)head_dim, out, scales,
+                                                                       quants, sums);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "attention merge launch");
+}
+
+int32_t launch_decode_attention(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
+                                size_t n_kv_heads, size_t head_dim, size_t seq_len, float scale, float *out,
+                                void *workspace, size_t workspace_bytes, float *scales, int8_t *quants, int16_t *sums,
+                                cudaStream_t st) {
+    return launch_decode_attention_ex(q, kc, vc, kv_f16, n_heads, n_kv_heads, head_dim, seq_len, nullptr,
+                                      attn_pick_splits(n_kv_heads, seq_len), scale, out, workspace, workspace_bytes,
+                                      scales, quants, sums, st);
+}
+
+}  // namespace cera
+
+using namespace cera;
+
+extern "C" {
+
+size_t cera_cuda_decode_attention_workspace_bytes(size_t n_heads, size_t head_dim, size_t seq_len) {
+    return attn_workspace_bytes(n_heads, head_dim, seq_len);
+}
+
+int32_t cera_cuda_decode_attention(const float *q_dev, const void *k_cache_dev, const void *v_cache_dev, int32_t kv_f16,
+                                   size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t seq_len, float scale,
+                                   float *out_dev, void *workspace_dev, size_t workspace_bytes, void *stream) {
+    return launch_decode_attention(q_dev, k_cache_dev, v_cache_dev, kv_f16, n_heads, n_kv_heads, head_dim, seq_len,
+                                   scale, out_dev, workspace_dev, workspace_bytes, nullptr, nullptr, nullptr,
+                                   (cudaStream_t)stream);
+}
+
+}  // extern "C"

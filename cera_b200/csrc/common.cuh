@@ -1,0 +1,111 @@
+// Shared declarations for the sm_100a kernels: status plumbing, the device
+// layout of a quantized weight, and the per-format decode helpers every kernel
+// (GEMV, GEMM, dequantize, block-sum probe) goes through.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/cera_cuda.h"
+
+namespace cera {
+
+// ---- status ---------------------------------------------------------------
+int32_t fail(int32_t code, const char *fmt, ...);
+int32_t check_cuda(cudaError_t e, const char *what);
+void count_launch(int n = 1);      // bumps the library-wide kernel launch counter
+uint64_t launches_so_far();
+
+#define CERA_CUDA_TRY(expr)                                          \
+    do {                                                             \
+        int32_t _st = ::cera::check_cuda((expr), #expr);             \
+        if (_st != CERA_CUDA_OK) return _st;                         \
+    } while (0)
+#define CERA_TRY(expr)                                               \
+    do {                                                             \
+        int32_t _st = (expr);                                        \
+        if (_st != CERA_CUDA_OK) return _st;                         \
+    } while (0)
+
+// ---- device layout of a weight matrix --------------------------------------
+// GGUF stores a row as packed blocks (18/20/34/144/176/210 bytes) whose fields
+// are at best 2-byte aligned.  On load each tensor is split into planes whose
+// per-row extents are multiples of 16 bytes, so a warp streams a row with
+// 128-bit loads; the byte total is unchanged.  `nb` counts the format's blocks
+// per row (32-element blocks, or 256-element super-blocks for K-quants).
+//
+//   Q4_0 : q[m][nb][16]                     d[m][nb] (half)
+//   Q4_1 : q[m][nb][16]                     dm[m][nb] (half2: d, m)
+//   Q8_0 : q[m][nb][32]                     d[m][nb] (half)
+//   Q4_K : q[m][nb][128]                    hdr[m][nb][16] (d, dmin, scales[12])
+//   Q5_K : q[m][nb][128]  qh[m][nb][32]     hdr[m][nb][16]
+//   Q6_K : q[m][nb][128]  qh[m][nb][64]     sc[m][nb][16]   d[m][nb] (half)
+struct WeightView {
+    int32_t type;
+    uint32_t m, k, nb;
+    const uint8_t *q;    // low quant plane
+    const uint8_t *qh;   // high-bit plane (Q5_K, Q6_K)
+    const uint8_t *hdr;  // scale plane (see table)
+    const uint8_t *d;    // Q6_K super-scale plane
+};
+
+struct TypeInfo {
+    int elems, bytes;    // GGUF block
+    int q_b, qh_b, hdr_b, d_b;  // plane bytes per block
+};
+
+__host__ __device__ inline TypeInfo type_info(int t) {
+    switch (t) {
+        case CERA_TYPE_Q4_0: return {32, 18, 16, 0, 2, 0};
+        case CERA_TYPE_Q4_1: return {32, 20, 16, 0, 4, 0};
+        case CERA_TYPE_Q8_0: return {32, 34, 32, 0, 2, 0};
+        case CERA_TYPE_Q4_K: return {256, 144, 128, 0, 16, 0};
+        case CERA_TYPE_Q5_K: return {256, 176, 128, 32, 16, 0};
+        case CERA_TYPE_Q6_K: return {256, 210, 128, 64, 16, 2};
+        case CERA_TYPE_F32: return {1, 4, 4, 0, 0, 0};
+        case CERA_TYPE_F16: return {1, 2, 2, 0, 0, 0};
+        case CERA_TYPE_BF16: return {1, 2, 2, 0, 0, 0};
+        default: return {0, 0, 0, 0, 0, 0};
+    }
+}
+
+inline bool is_block_type(int t) {
+    return t == CERA_TYPE_Q4_0 || t == CERA_TYPE_Q4_1 || t == CERA_TYPE_Q8_0 || t == CERA_TYPE_Q4_K ||
+           t == CERA_TYPE_Q5_K || t == CERA_TYPE_Q6_K;
+}
+
+// ---- small device helpers ---------------------------------------------------
+__device__ __forceinline__ float h2f(uint16_t bits) { return __half2float(__ushort_as_half(bits)); }
+
+// 6-bit scale / min of sub-block s from the 12 packed bytes
+// (cera/src/quant.rs:591-605).
+__device__ __forceinline__ void kscale(const uint8_t *s12, int s, int &sc, int &mn) {
+    if (s < 4) {
+        sc = s12[s] & 63;
+        mn = s12[s + 4] & 63;
+    } else {
+        sc = (s12[s + 4] & 0x0F) | ((s12[s - 4] >> 6) << 4);
+        mn = (s12[s + 4] >> 4) | ((s12[s] >> 6) << 4);
+    }
+}
+
+// 128-bit streaming load that does not allocate in L1 (weights are read once).
+__device__ __forceinline__ uint4 ld_stream(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ---- launch geometry ----------------------------------------------------------
+int sm_count();  // SMs of the current device (148 on B200), cached
+
+}  // namespace cera

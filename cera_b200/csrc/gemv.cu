@@ -1,0 +1,260 @@
+// Decode GEMV / small-batch GEMM: quantized weights x Q8_0 activations.
+//
+// HBM-bound.  One warp owns one weight row at a time (grid-stride over rows);
+// each lane streams 16-byte items of the low-quant plane with L1-bypassing
+// 128-bit loads, unpacks nibbles / high bits in registers, forms exact int32
+// half-block sums with dp4a against the Q8_0 activation quants (read through
+// L1, they are shared by every row), scales them in f32 and the warp reduces
+// with shuffles.  NC activation columns reuse the unpacked weights.
+//
+// Arithmetic contract: cera/src/backend/simd.rs:4593-4637 (Q4_0/Q8_0),
+// 5693-5878 (Q4_K), 5893-5976 (Q4_1), 5988-6195 (Q6_K).  Integer sums are
+// exact; the f32 combination order is this kernel's own (per-lane sequential
+// fma over the lane's items, then an xor-shuffle tree), within the path's f32
+// tolerance of any of the reference's three orders.
+#include "formats.cuh"
+#include "ops.h"
+#include "weight.h"
+
+namespace cera {
+
+namespace {
+
+constexpr int MAX_SEGS = 3;
+constexpr int WARPS = 8;
+
+struct GemvParams {
+    WeightView w[MAX_SEGS];
+    float *y[MAX_SEGS];
+    uint32_t row_end[MAX_SEGS];  // cumulative row counts
+    int n_segs;
+    uint32_t total_rows;
+    ActView x;
+    uint32_t k;
+    uint32_t ldy;  // row stride of y in floats
+    int epilogue;
+};
+
+template <int T, int NC>
+__device__ __forceinline__ void accumulate_item(const typename Fmt<T>::Raw &raw, int item, const ActView &x, uint32_t k,
+                                                float (&acc)[NC]) {
+    using F = Fmt<T>;
+    int lo[4], hi[4];
+    HalfRef h0, h1;
+    F::decode(raw, item, lo, hi, h0, h1);
+    const uint32_t nb32 = k >> 5, nb16 = k >> 4;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+        const int8_t *q = x.quants + (size_t)c * k;
+        const int u0 = dot16(lo, q + h0.off), u1 = dot16(hi, q + h1.off);
+        if (F::WHOLE_BLOCK) {
+            const float xs = __ldg(x.scales + (size_t)c * nb32 + (h0.off >> 5));
+            int a0 = 0, a1 = 0;
+            if (T != CERA_TYPE_Q8_0) {
+                const int s2 = __ldg(reinterpret_cast<const int *>(x.sums + (size_t)c * nb16 + (h0.off >> 4)));
+                a0 = (int)(int16_t)(s2 & 0xFFFF);
+                a1 = s2 >> 16;
+            }
+            const int U = F::view(u0, a0) + F::view(u1, a1);
+            acc[c] = fmaf((float)U, __fmul_rn(h0.scale, xs), acc[c]);
+            if (F::SIGN != 0) acc[c] = fmaf(__fmul_rn(xs, h0.mscale), (float)(F::SIGN * (a0 + a1)), acc[c]);
+        } else {
+            const float xs0 = __ldg(x.scales + (size_t)c * nb32 + (h0.off >> 5));
+            const float xs1 = __ldg(x.scales + (size_t)c * nb32 + (h1.off >> 5));
+            const int a0 = __ldg(x.sums + (size_t)c * nb16 + (h0.off >> 4));
+            const int a1 = __ldg(x.sums + (size_t)c * nb16 + (h1.off >> 4));
+            acc[c] = fmaf((float)u0, __fmul_rn(h0.scale, xs0), acc[c]);
+            acc[c] = fmaf((float)u1, __fmul_rn(h1.scale, xs1), acc[c]);
+            acc[c] = fmaf(__fmul_rn(xs0, h0.mscale), (float)(F::SIGN * a0), acc[c]);
+            acc[c] = fmaf(__fmul_rn(xs1, h1.mscale), (float)(F::SIGN * a1), acc[c]);
+        }
+    }
+}
+
+template <int T, int NC, int UNROLL>
+__global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
+    using F = Fmt<T>;
+    const int lane = threadIdx.x & 31;
+    const uint32_t warp = blockIdx.x * WARPS + (threadIdx.x >> 5);
+    const uint32_t n_warps = gridDim.x * WARPS;
+    const int items = p.k >> 5;
+
+    for (uint32_t row = warp; row < p.total_rows; row += n_warps) {
+        int s = 0;
+        while (s + 1 < p.n_segs && row >= p.row_end[s]) ++s;
+        const uint32_t local = row - (s ? p.row_end[s - 1] : 0);
+        const WeightView &w = p.w[s];
+
+        float acc[NC];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[c] = 0.0f;
+
+        for (int base = 0; base < items; base += 32 * UNROLL) {
+            typename F::Raw raw[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int item = base + u * 32 + lane;
+                if (item < items) raw[u] = F::load(w, local, item);
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int item = base + u * 32 + lane;
+                if (item < items) accumulate_item<T, NC>(raw[u], item, p.x, p.k, acc);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[c] = warp_sum(acc[c]);
+        if (lane == 0) {
+            float *y = p.y[s] + (size_t)local * p.ldy;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) y[c] = p.epilogue == EPI_ADD ? __fadd_rn(y[c], acc[c]) : acc[c];
+        }
+    }
+}
+
+// Q5_K against f32 activations (cera/src/quant.rs:892-937, cpu.rs:1830-1854):
+// per 64-element pair d*(sc1*S1 + sc2*S2) - dmin*(mn1*Y1 + mn2*Y2).  One warp per row;
+// each lane owns whole items so the element sums inside an item stay sequential.
+__global__ void __launch_bounds__(WARPS * 32) gemv_q5k_f32_kernel(const WeightView w, const float *__restrict__ x,
+                                                                float *__restrict__ y) {
+    using F = Fmt<CERA_TYPE_Q5_K>;
+    const int lane = threadIdx.x & 31;
+    const uint32_t warp = blockIdx.x * WARPS + (threadIdx.x >> 5);
+    const uint32_t n_warps = gridDim.x * WARPS;
+    const int items = w.k >> 5;
+    for (uint32_t row = warp; row < w.m; row += n_warps) {
+        float acc = 0.0f;
+        for (int item = lane; item < items; item += 32) {
+            const F::Raw raw = F::load(w, row, item);
+            int lo[4], hi[4];
+            HalfRef h0, h1;
+            F::decode(raw, item, lo, hi, h0, h1);
+            float s0 = 0.0f, s1 = 0.0f, y0 = 0.0f, y1 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const float xa = __ldg(x + h0.off + 4 * i + t), xb = __ldg(x + h1.off + 4 * i + t);
+                    s0 = fmaf((float)((lo[i] >> (8 * t)) & 0xFF), xa, s0);
+                    s1 = fmaf((float)((hi[i] >> (8 * t)) & 0xFF), xb, s1);
+                    y0 += xa;
+                    y1 += xb;
+                }
+            acc += h0.scale * s0 + h1.scale * s1 - (h0.mscale * y0 + h1.mscale * y1);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) y[row] = acc;
+    }
+}
+
+template <int T, int NC>
+int32_t launch_typed(const GemvParams &p, cudaStream_t st) {
+    const uint32_t ctas_needed = (p.total_rows + WARPS - 1) / WARPS;
+    const uint32_t cap = (uint32_t)sm_count() * 8;
+    const uint32_t grid = ctas_needed < cap ? ctas_needed : cap;
+    if (p.k >= 4096)
+        gemv_kernel<T, NC, 4><<<grid, WARPS * 32, 0, st>>>(p);
+    else
+        gemv_kernel<T, NC, 1><<<grid, WARPS * 32, 0, st>>>(p);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "gemv launch");
+}
+
+template <int T>
+int32_t launch_cols(const GemvParams &p, size_t n_cols, cudaStream_t st) {
+    switch (n_cols) {
+        case 1: return launch_typed<T, 1>(p, st);
+        case 2: return launch_typed<T, 2>(p, st);
+        case 4: return launch_typed<T, 4>(p, st);
+        case 8: return launch_typed<T, 8>(p, st);
+        default: return fail(CERA_CUDA_ERR_BAD_ARG, "gemv: column tile %zu not instantiated", n_cols);
+    }
+}
+
+}  // namespace
+
+// All segments must share the type and k.  n_cols in {1,2,4,8}.
+int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_cols, size_t ldy, int epilogue,
+                    cudaStream_t st) {
+    if (n_segs < 1 || n_segs > MAX_SEGS) return fail(CERA_CUDA_ERR_BAD_ARG, "gemv: %d segments", n_segs);
+    GemvParams p{};
+    uint32_t rows = 0;
+    for (int i = 0; i < n_segs; ++i) {
+        if (segs[i].w.type != segs[0].w.type || segs[i].w.k != segs[0].w.k)
+            return fail(CERA_CUDA_ERR_BAD_ARG, "gemv: fused segments must share type and k");
+        p.w[i] = segs[i].w;
+        p.y[i] = segs[i].y;
+        rows += segs[i].w.m;
+        p.row_end[i] = rows;
+    }
+    p.n_segs = n_segs;
+    p.total_rows = rows;
+    p.x = x;
+    p.k = segs[0].w.k;
+    p.epilogue = epilogue;
+    p.ldy = (uint32_t)ldy;
+    if ((uintptr_t)x.quants % 16 || (uintptr_t)x.sums % 4 || (p.k % 32))
+        return fail(CERA_CUDA_ERR_BAD_ARG, "gemv: activation quants must be 16-byte aligned and k a multiple of 32");
+    CERA_DISPATCH_BLOCK_TYPE(segs[0].w.type, return (launch_cols<TT>(p, n_cols, st)));
+    return CERA_CUDA_OK;
+}
+
+// Any n: column tiles of 8/4/2/1 through the multi-column GEMV.  Weights are
+// re-streamed once per tile, so this is the small-batch path; large batches
+// belong to the tensor-core GEMM.
+int32_t launch_gemm(const WeightView &w, const ActView &x, size_t n, float *out, cudaStream_t st) {
+    const size_t k = w.k;
+    size_t j = 0;
+    while (j < n) {
+        const size_t left = n - j;
+        const size_t nc = left >= 8 ? 8 : left >= 4 ? 4 : left >= 2 ? 2 : 1;
+        GemvSeg seg{w, out + j};
+        ActView xv{x.scales + j * (k / 32), x.quants + j * k, x.sums + j * (k / 16)};
+        CERA_TRY(launch_gemv(&seg, 1, xv, nc, n, EPI_STORE, st));
+        j += nc;
+    }
+    return CERA_CUDA_OK;
+}
+
+int32_t launch_gemv_q5k_f32(const WeightView &w, const float *x, float *y, cudaStream_t st) {
+    const uint32_t ctas_needed = (w.m + WARPS - 1) / WARPS, cap = (uint32_t)sm_count() * 8;
+    gemv_q5k_f32_kernel<<<ctas_needed < cap ? ctas_needed : cap, WARPS * 32, 0, st>>>(w, x, y);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "gemv_q5k_f32 launch");
+}
+
+}  // namespace cera
+
+using namespace cera;
+
+extern "C" {
+
+int32_t cera_cuda_gemv(const cera_cuda_weight *w, const float *x_dev, float *y_dev, void *stream) {
+    if (!w || !x_dev || !y_dev) return fail(CERA_CUDA_ERR_BAD_ARG, "gemv: null argument");
+    if (!w->xq) return fail(CERA_CUDA_ERR_STATE, "gemv: weight was created without activation scratch");
+    cudaStream_t st = (cudaStream_t)stream;
+    CERA_TRY(launch_quantize(x_dev, w->v.k, 1, false, w->xs, w->xq, w->xsum, st));
+    GemvSeg seg{w->v, y_dev};
+    ActView x{w->xs, w->xq, w->xsum};
+    return launch_gemv(&seg, 1, x, 1, 1, EPI_STORE, st);
+}
+
+int32_t cera_cuda_gemv_q5k_f32(const cera_cuda_weight *w, const float *x_dev, float *y_dev, void *stream) {
+    if (!w || !x_dev || !y_dev) return fail(CERA_CUDA_ERR_BAD_ARG, "gemv_q5k_f32: null argument");
+    if (w->v.type != CERA_TYPE_Q5_K) return fail(CERA_CUDA_ERR_UNSUPPORTED, "gemv_q5k_f32: weight is ggml type %d", w->v.type);
+    return launch_gemv_q5k_f32(w->v, x_dev, y_dev, (cudaStream_t)stream);
+}
+
+int32_t cera_cuda_gemm_preq(const cera_cuda_weight *w, const float *scales_dev, const int8_t *quants_dev,
+                            const int16_t *sums_dev, float *out_dev, size_t m, size_t n, size_t k, void *stream) {
+    if (!w || !scales_dev || !quants_dev || !sums_dev || !out_dev)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "gemm_preq: null argument");
+    // A declined GEMM must be loud: callers reuse output buffers (cera/src/model/transformer.rs:790-820).
+    if (m != w->v.m || k != w->v.k)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "gemm_preq: shape [%zu x %zu] does not match the weight [%u x %u]", m, k,
+                    w->v.m, w->v.k);
+    if (n == 0) return CERA_CUDA_OK;
+    return launch_gemm(w->v, ActView{scales_dev, quants_dev, sums_dev}, n, out_dev, (cudaStream_t)stream);
+}
+
+}  // extern "C"

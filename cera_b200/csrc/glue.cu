@@ -1,0 +1,181 @@
+// Small kernels around the matmuls on the decode path: RoPE (+KV append),
+// embedding row lookup, argmax.
+#include "formats.cuh"
+#include "ops.h"
+
+namespace cera {
+
+namespace {
+
+// One thread per rotation pair.  theta_i = pos * ts^i built by repeated f32
+// multiplication exactly as the CPU loop does (cera/src/backend/cpu.rs:5161-5180,
+// 5041-5054), so the angle fed to sincos is bit-identical; sincosf itself is
+// CUDA's full-range implementation (last-ulp differences from libm are inside
+// the path's f32 tolerance).
+__global__ void rope_kernel(float *q, float *k, const float *__restrict__ v, uint32_t pos_imm,
+                            const uint32_t *__restrict__ pos_dev, uint32_t n_heads, uint32_t n_kv_heads, uint32_t hd,
+                            float ts, const float *__restrict__ ff, int neox, void *k_cache, void *v_cache, int kv_f16) {
+    const uint32_t half = hd / 2;
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t total = (n_heads + n_kv_heads) * half;
+    const uint32_t pos = pos_dev ? *pos_dev : pos_imm;
+    const size_t kv_dim = (size_t)n_kv_heads * hd;
+    if (idx < total) {
+        const uint32_t h = idx / half, i = idx % half;
+        float theta = (float)pos;
+        for (uint32_t s = 0; s < i; ++s) theta = __fmul_rn(theta, ts);
+        if (!neox && ff) theta = __fdiv_rn(theta, ff[i]);
+        float sn, cs;
+        sincosf(theta, &sn, &cs);
+        float *head = h < n_heads ? q + (size_t)h * hd : k + (size_t)(h - n_heads) * hd;
+        const uint32_t i0 = neox ? i : 2 * i, i1 = neox ? i + half : 2 * i + 1;
+        const float x0 = head[i0], x1 = head[i1];
+        const float r0 = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+        const float r1 = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
+        head[i0] = r0;
+        head[i1] = r1;
+        if (k_cache && h >= n_heads) {
+            const size_t o = (size_t)pos * kv_dim + (size_t)(h - n_heads) * hd;
+            if (kv_f16) {
+                __half *kc = (__half *)k_cache;
+                kc[o + i0] = __float2half_rn(r0);
+                kc[o + i1] = __float2half_rn(r1);
+            } else {
+                float *kc = (float *)k_cache;
+                kc[o + i0] = r0;
+                kc[o + i1] = r1;
+            }
+        }
+    }
+    // v rows ride along: threads beyond the rotation pairs are not needed, reuse the same grid
+    if (v_cache) {
+        for (size_t e = idx; e < kv_dim; e += (size_t)gridDim.x * blockDim.x) {
+            const size_t o = (size_t)pos * kv_dim + e;
+            if (kv_f16) ((__half *)v_cache)[o] = __float2half_rn(v[e]);
+            else ((float *)v_cache)[o] = v[e];
+        }
+    }
+}
+
+template <int T>
+__global__ void embed_kernel(WeightView w, uint32_t token_imm, const uint32_t *__restrict__ token_dev, float *out) {
+    const uint32_t token = token_dev ? *token_dev : token_imm;
+    const int items = w.k / 32;
+    const int item = blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= items || token >= w.m) return;
+    const typename Fmt<T>::Raw raw = Fmt<T>::load(w, token, item);
+    int lo[4], hi[4];
+    HalfRef h0, h1;
+    Fmt<T>::decode(raw, item, lo, hi, h0, h1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            int q0 = (lo[i] >> (8 * t)) & 0xFF, q1 = (hi[i] >> (8 * t)) & 0xFF;
+            if (T == CERA_TYPE_Q8_0) {
+                q0 = (int8_t)q0;
+                q1 = (int8_t)q1;
+            }
+            out[h0.off + 4 * i + t] = Fmt<T>::deq(q0, h0);
+            out[h1.off + 4 * i + t] = Fmt<T>::deq(q1, h1);
+        }
+}
+
+constexpr int ARGMAX_BLOCKS = 128, ARGMAX_THREADS = 256;
+
+// Order: greater value wins; on equal values the lower index wins, which is
+// what a left-to-right strict `>` scan returns.
+__device__ __forceinline__ void amax_merge(float &bv, uint32_t &bi, float v, uint32_t i) {
+    if (v > bv || (v == bv && i < bi)) {
+        bv = v;
+        bi = i;
+    }
+}
+
+__global__ void argmax_stage1(const float *__restrict__ x, uint32_t n, uint32_t *scratch) {
+    float bv = -INFINITY;
+    uint32_t bi = 0xFFFFFFFFu;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float v = x[i];
+        if (v > bv) {  // ascending i within a thread: strict > keeps the first
+            bv = v;
+            bi = i;
+        }
+    }
+    __shared__ float sv[ARGMAX_THREADS];
+    __shared__ uint32_t si[ARGMAX_THREADS];
+    sv[threadIdx.x] = bv;
+    si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+        if ((int)threadIdx.x < s) amax_merge(sv[threadIdx.x], si[threadIdx.x], sv[threadIdx.x + s], si[threadIdx.x + s]);
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        scratch[2 * blockIdx.x] = __float_as_uint(sv[0]);
+        scratch[2 * blockIdx.x + 1] = si[0];
+    }
+}
+
+__global__ void argmax_stage2(const uint32_t *__restrict__ scratch, int blocks, uint32_t *out) {
+    float bv = -INFINITY;
+    uint32_t bi = 0xFFFFFFFFu;
+    for (int b = threadIdx.x; b < blocks; b += 32) amax_merge(bv, bi, __uint_as_float(scratch[2 * b]), scratch[2 * b + 1]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        amax_merge(bv, bi, ov, oi);
+    }
+    // no finite / non-NaN winner -> index 0, as the reference returns
+    if (threadIdx.x == 0) *out = bi == 0xFFFFFFFFu ? 0u : bi;
+}
+
+}  // namespace
+
+int32_t launch_rope(float *q, float *k, const float *v, size_t pos, const uint32_t *pos_dev, size_t n_heads,
+                    size_t n_kv_heads, size_t head_dim, float theta_scale, const float *freq_factors, int rope_type,
+                    void *k_cache, void *v_cache, int kv_f16, cudaStream_t st) {
+    if (!q || !k) return fail(CERA_CUDA_ERR_BAD_ARG, "rope: null argument");
+    if (head_dim == 0 || head_dim % 2) return fail(CERA_CUDA_ERR_BAD_ARG, "rope: head_dim %zu must be even", head_dim);
+    if (v_cache && !v) return fail(CERA_CUDA_ERR_BAD_ARG, "rope: v_cache without v");
+    const uint32_t total = (uint32_t)((n_heads + n_kv_heads) * (head_dim / 2));
+    const int threads = 128;
+    rope_kernel<<<(total + threads - 1) / threads, threads, 0, st>>>(
+        q, k, v, (uint32_t)pos, pos_dev, (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)head_dim, theta_scale,
+        freq_factors, rope_type == 1, k_cache, v_cache, kv_f16);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "rope launch");
+}
+
+int32_t launch_embed(const WeightView &w, uint32_t token, const uint32_t *token_dev, float *out, cudaStream_t st) {
+    const int items = w.k / 32, threads = 128;
+    CERA_DISPATCH_BLOCK_TYPE(w.type, (embed_kernel<TT><<<(items + threads - 1) / threads, threads, 0, st>>>(w, token, token_dev, out)));
+    count_launch();
+    return check_cuda(cudaGetLastError(), "embed launch");
+}
+
+size_t argmax_scratch_words() { return 2 * ARGMAX_BLOCKS; }
+
+int32_t launch_argmax(const float *x, size_t n, uint32_t *out, uint32_t *scratch, cudaStream_t st) {
+    if (!x || !out || !scratch) return fail(CERA_CUDA_ERR_BAD_ARG, "argmax: null argument");
+    argmax_stage1<<<ARGMAX_BLOCKS, ARGMAX_THREADS, 0, st>>>(x, (uint32_t)n, scratch);
+    argmax_stage2<<<1, 32, 0, st>>>(scratch, ARGMAX_BLOCKS, out);
+    count_launch(2);
+    return check_cuda(cudaGetLastError(), "argmax launch");
+}
+
+}  // namespace cera
+
+using namespace cera;
+
+extern "C" {
+
+int32_t cera_cuda_rope(float *q_dev, float *k_dev, size_t pos, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                       float freq_base, const float *freq_factors_dev, int32_t rope_type, void *stream) {
+    const float ts = powf(freq_base, -2.0f / (float)head_dim);
+    return launch_rope(q_dev, k_dev, nullptr, pos, nullptr, n_heads, n_kv_heads, head_dim, ts, freq_factors_dev,
+                       rope_type, nullptr, nullptr, 0, (cudaStream_t)stream);
+}
+
+}  // extern "C"

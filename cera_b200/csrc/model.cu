@@ -1,0 +1,404 @@
+// Dense llama-architecture model on one B200: the object a `--device cuda`
+// backend hands to cera's Session as its `Box<dyn Model>`.
+//
+// Weights, KV cache, scratch and the sequence-length counter live on the
+// device side of the boundary (cera's wgpu / Metal models do the same:
+// cera/src/model/mod.rs:184-199); every entry point takes one internal mutex.
+// A decode token is one CUDA-graph launch: embedding row -> per layer
+// [RMSNorm+Q8_0 -> q/k/v GEMV -> RoPE + KV append -> split-KV attention (+Q8_0)
+// -> o-proj GEMV (+residual) -> RMSNorm+Q8_0 -> gate/up GEMV -> SiLU*mul+Q8_0 ->
+// down GEMV (+residual)] -> final RMSNorm+Q8_0 -> LM-head GEMV [-> argmax].
+// The token id and position are read from device memory so the graph is
+// recorded once per attention split count and replayed.
+// Layer wiring: cera/src/model/llama.rs:468-597, 1585-1605 and
+// cera/src/model/transformer.rs:1313-1652.
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "ops.h"
+#include "weight.h"
+
+using namespace cera;
+
+namespace {
+
+struct ActBuf {
+    float *scales = nullptr;
+    int8_t *quants = nullptr;
+    int16_t *sums = nullptr;
+    ActView view() const { return ActView{scales, quants, sums}; }
+};
+
+struct Layer {
+    float *attn_norm = nullptr, *ffn_norm = nullptr;
+    cera_cuda_weight *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *gate = nullptr, *up = nullptr,
+                     *down = nullptr;
+    void *kc = nullptr, *vc = nullptr;
+};
+
+enum GraphKind { G_BODY = 0, G_LOGITS = 1, G_GREEDY = 2 };
+
+}  // namespace
+
+struct cera_cuda_model {
+    cera_cuda_config cfg{};
+    std::mutex mu;
+    bool finalized = false;
+    cera_cuda_weight *embd = nullptr, *output = nullptr;
+    float *out_norm = nullptr, *rope_freqs = nullptr;
+    std::vector<Layer> layers;
+    std::vector<void *> owned;  // plain device allocations to free
+    size_t mem_bytes = 0;
+    // scratch
+    float *hidden = nullptr, *final_hidden = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr,
+          *g = nullptr, *u = nullptr, *logits = nullptr;
+    ActBuf act_hs, act_q, act_ff;
+    void *attn_ws = nullptr;
+    size_t attn_ws_bytes = 0;
+    uint32_t *argmax_scratch = nullptr;
+    uint32_t *dyn = nullptr;      // device: [0]=token [1]=pos [2]=seq_len(pos+1)
+    uint32_t *tok_out = nullptr;  // device
+    uint32_t *h_dyn = nullptr;    // pinned host mirror of dyn + returned token
+    float *h_logits = nullptr;    // pinned host staging for logits
+    float theta_scale = 0.0f;
+    cudaStream_t stream = nullptr;
+    std::map<uint32_t, cudaGraphExec_t> graphs;  // key = kind | n_splits << 8
+    size_t seq_len = 0;
+    uint64_t launches = 0;         // kernels launched by decode steps
+    uint32_t nodes_per_step[3] = {0, 0, 0};
+};
+
+namespace {
+
+int32_t dev_alloc(cera_cuda_model *m, void **p, size_t bytes) {
+    CERA_CUDA_TRY(cudaMalloc(p, bytes));
+    m->owned.push_back(*p);
+    m->mem_bytes += bytes;
+    return CERA_CUDA_OK;
+}
+
+int32_t alloc_act(cera_cuda_model *m, ActBuf &a, size_t k) {
+    CERA_TRY(dev_alloc(m, (void **)&a.scales, k / 32 * 4));
+    CERA_TRY(dev_alloc(m, (void **)&a.quants, k));
+    CERA_TRY(dev_alloc(m, (void **)&a.sums, k / 16 * 2));
+    return CERA_CUDA_OK;
+}
+
+// Enqueue one decode step on m->stream; token / position come from m->dyn.
+int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
+    const auto &c = m->cfg;
+    cudaStream_t st = m->stream;
+    const size_t hs = c.hidden_size;
+    const float scale = 1.0f / sqrtf((float)c.head_dim);
+    CERA_TRY(launch_embed(m->embd->v, 0, m->dyn, m->hidden, st));
+    for (auto &L : m->layers) {
+        CERA_TRY(launch_rmsnorm(m->hidden, L.attn_norm, hs, 1, c.rms_norm_eps, nullptr, m->act_hs.scales,
+                                m->act_hs.quants, m->act_hs.sums, st));
+        if (L.wq->v.type == L.wk->v.type && L.wq->v.type == L.wv->v.type) {
+            GemvSeg segs[3] = {{L.wq->v, m->q}, {L.wk->v, m->k}, {L.wv->v, m->v}};
+            CERA_TRY(launch_gemv(segs, 3, m->act_hs.view(), 1, 1, EPI_STORE, st));
+        } else {
+            GemvSeg sq{L.wq->v, m->q}, sk{L.wk->v, m->k}, sv{L.wv->v, m->v};
+            CERA_TRY(launch_gemv(&sq, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
+            CERA_TRY(launch_gemv(&sk, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
+            CERA_TRY(launch_gemv(&sv, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
+        }
+        CERA_TRY(launch_rope(m->q, m->k, m->v, 0, m->dyn + 1, c.n_heads, c.n_kv_heads, c.head_dim, m->theta_scale,
+                             m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st));
+        CERA_TRY(launch_decode_attention_ex(m->q, L.kc, L.vc, c.kv_f16, c.n_heads, c.n_kv_heads, c.head_dim, 0,
+                                            m->dyn + 2, n_splits, scale, m->attn, m->attn_ws, m->attn_ws_bytes,
+                                            m->act_q.scales, m->act_q.quants, m->act_q.sums, st));
+        GemvSeg so{L.wo->v, m->hidden};
+        CERA_TRY(launch_gemv(&so, 1, m->act_q.view(), 1, 1, EPI_ADD, st));
+        CERA_TRY(launch_rmsnorm(m->hidden, L.ffn_norm, hs, 1, c.rms_norm_eps, nullptr, m->act_hs.scales,
+                                m->act_hs.quants, m->act_hs.sums, st));
+        if (L.gate->v.type == L.up->v.type) {
+            GemvSeg segs[2] = {{L.gate->v, m->g}, {L.up->v, m->u}};
+            CERA_TRY(launch_gemv(segs, 2, m->act_hs.view(), 1, 1, EPI_STORE, st));
+        } else {
+            GemvSeg sg{L.gate->v, m->g}, su{L.up->v, m->u};
+            CERA_TRY(launch_gemv(&sg, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
+            CERA_TRY(launch_gemv(&su, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
+        }
+        CERA_TRY(launch_silu_mul(m->g, m->u, c.intermediate_size, 1, m->act_ff.scales, m->act_ff.quants,
+                                 m->act_ff.sums, st));
+        GemvSeg sd{L.down->v, m->hidden};
+        CERA_TRY(launch_gemv(&sd, 1, m->act_ff.view(), 1, 1, EPI_ADD, st));
+    }
+    if (kind == G_BODY) return CERA_CUDA_OK;
+    CERA_TRY(launch_rmsnorm(m->hidden, m->out_norm, hs, 1, c.rms_norm_eps, m->final_hidden, m->act_hs.scales,
+                            m->act_hs.quants, m->act_hs.sums, st));
+    const cera_cuda_weight *ow = m->output ? m->output : m->embd;
+    GemvSeg sl{ow->v, m->logits};
+    CERA_TRY(launch_gemv(&sl, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
+    if (kind == G_GREEDY) CERA_TRY(launch_argmax(m->logits, c.vocab_size, m->tok_out, m->argmax_scratch, st));
+    return CERA_CUDA_OK;
+}
+
+int32_t get_graph(cera_cuda_model *m, int kind, uint32_t n_splits, cudaGraphExec_t *out) {
+    const uint32_t key = (uint32_t)kind | (n_splits << 8);
+    auto it = m->graphs.find(key);
+    if (it != m->graphs.end()) {
+        *out = it->second;
+        return CERA_CUDA_OK;
+    }
+    const uint64_t before = launches_so_far();
+    CERA_CUDA_TRY(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+    int32_t st = enqueue_step(m, kind, n_splits);
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(m->stream, &graph);
+    if (st != CERA_CUDA_OK) {
+        if (graph) cudaGraphDestroy(graph);
+        return st;
+    }
+    CERA_CUDA_TRY(e);
+    m->nodes_per_step[kind] = (uint32_t)(launches_so_far() - before);
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    CERA_CUDA_TRY(e);
+    m->graphs[key] = exec;
+    *out = exec;
+    return CERA_CUDA_OK;
+}
+
+// Runs one token; leaves results in device buffers (logits / tok_out).
+int32_t run_token(cera_cuda_model *m, uint32_t token, size_t pos, int kind) {
+    const auto &c = m->cfg;
+    if (!m->finalized) return fail(CERA_CUDA_ERR_STATE, "forward: model_finalize has not been called");
+    if (token >= c.vocab_size) return fail(CERA_CUDA_ERR_BAD_ARG, "forward: token %u out of range (vocab %u)", token, c.vocab_size);
+    if (pos != m->seq_len) return fail(CERA_CUDA_ERR_STATE, "forward: pos %zu != seq_len %zu", pos, m->seq_len);
+    if (pos >= c.max_seq_len) return fail(CERA_CUDA_ERR_BAD_ARG, "forward: pos %zu exceeds max_seq_len %u", pos, c.max_seq_len);
+    const uint32_t n_splits = attn_pick_splits(c.n_kv_heads, pos + 1);
+    cudaGraphExec_t g = nullptr;
+    CERA_TRY(get_graph(m, kind, n_splits, &g));
+    m->h_dyn[0] = token;
+    m->h_dyn[1] = (uint32_t)pos;
+    m->h_dyn[2] = (uint32_t)pos + 1;
+    CERA_CUDA_TRY(cudaMemcpyAsync(m->dyn, m->h_dyn, 3 * sizeof(uint32_t), cudaMemcpyHostToDevice, m->stream));
+    CERA_CUDA_TRY(cudaGraphLaunch(g, m->stream));
+    m->launches += m->nodes_per_step[kind];
+    m->seq_len = pos + 1;
+    return CERA_CUDA_OK;
+}
+
+struct DeviceGuard {
+    int prev = 0;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        cudaSetDevice(dev);
+    }
+    ~DeviceGuard() { cudaSetDevice(prev); }
+};
+
+}  // namespace
+
+extern "C" {
+
+int32_t cera_cuda_model_create(const cera_cuda_config *cfg, cera_cuda_model **out) {
+    if (!cfg || !out) return fail(CERA_CUDA_ERR_BAD_ARG, "model_create: null argument");
+    const auto &c = *cfg;
+    if (!c.n_layers || !c.hidden_size || !c.intermediate_size || !c.n_heads || !c.n_kv_heads || !c.head_dim ||
+        !c.vocab_size || !c.max_seq_len)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "model_create: zero dimension in config");
+    if (c.n_heads % c.n_kv_heads) return fail(CERA_CUDA_ERR_BAD_ARG, "model_create: n_heads %% n_kv_heads != 0");
+    if (c.hidden_size % 32 || c.intermediate_size % 32 || (c.n_heads * c.head_dim) % 32)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "model_create: hidden, intermediate and q dims must be multiples of 32");
+    int n_dev = 0;
+    CERA_CUDA_TRY(cudaGetDeviceCount(&n_dev));
+    if (c.device < 0 || c.device >= n_dev) return fail(CERA_CUDA_ERR_BAD_ARG, "model_create: device %d of %d", c.device, n_dev);
+    auto *m = new (std::nothrow) cera_cuda_model();
+    if (!m) return fail(CERA_CUDA_ERR_OOM, "model_create: host allocation failed");
+    m->cfg = c;
+    m->layers.resize(c.n_layers);
+    m->theta_scale = powf(c.rope_theta, -2.0f / (float)c.head_dim);
+    *out = m;
+    return CERA_CUDA_OK;
+}
+
+int32_t cera_cuda_model_add_tensor(cera_cuda_model *m, int32_t role, int32_t layer, int32_t type, size_t rows,
+                                   size_t cols, const void *bytes, size_t nbytes) {
+    if (!m || !bytes) return fail(CERA_CUDA_ERR_BAD_ARG, "add_tensor: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    if (m->finalized) return fail(CERA_CUDA_ERR_STATE, "add_tensor: model already finalized");
+    const auto &c = m->cfg;
+    const size_t qd = (size_t)c.n_heads * c.head_dim, kvd = (size_t)c.n_kv_heads * c.head_dim;
+    const bool per_layer = role >= CERA_ROLE_ATTN_NORM && role <= CERA_ROLE_FFN_DOWN;
+    if (per_layer && (layer < 0 || (uint32_t)layer >= c.n_layers))
+        return fail(CERA_CUDA_ERR_BAD_ARG, "add_tensor: layer %d out of range", layer);
+
+    auto f32_vector = [&](float **slot, size_t n) -> int32_t {
+        if (type != CERA_TYPE_F32) return fail(CERA_CUDA_ERR_UNSUPPORTED, "add_tensor: role %d must be F32, got ggml type %d", role, type);
+        if (rows * cols != n || nbytes != n * 4) return fail(CERA_CUDA_ERR_BAD_ARG, "add_tensor: role %d expects %zu floats", role, n);
+        if (*slot) return fail(CERA_CUDA_ERR_STATE, "add_tensor: role %d layer %d given twice", role, layer);
+        CERA_TRY(dev_alloc(m, (void **)slot, nbytes));
+        return check_cuda(cudaMemcpy(*slot, bytes, nbytes, cudaMemcpyDefault), "cudaMemcpy(norm weights)");
+    };
+    auto matrix = [&](cera_cuda_weight **slot, size_t want_m, size_t want_k) -> int32_t {
+        if (rows != want_m || cols != want_k)
+            return fail(CERA_CUDA_ERR_BAD_ARG, "add_tensor: role %d expects [%zu x %zu], got [%zu x %zu]", role, want_m, want_k, rows, cols);
+        if (*slot) return fail(CERA_CUDA_ERR_STATE, "add_tensor: role %d layer %d given twice", role, layer);
+        CERA_TRY(weight_upload(type, rows, cols, bytes, nbytes, false, slot));
+        m->mem_bytes += (*slot)->bytes;
+        return CERA_CUDA_OK;
+    };
+    Layer *L = per_layer ? &m->layers[layer] : nullptr;
+    switch (role) {
+        case CERA_ROLE_TOKEN_EMBD: return matrix(&m->embd, c.vocab_size, c.hidden_size);
+        case CERA_ROLE_OUTPUT: return matrix(&m->output, c.vocab_size, c.hidden_size);
+        case CERA_ROLE_OUTPUT_NORM: return f32_vector(&m->out_norm, c.hidden_size);
+        case CERA_ROLE_ROPE_FREQS: return f32_vector(&m->rope_freqs, c.head_dim / 2);
+        case CERA_ROLE_ATTN_NORM: return f32_vector(&L->attn_norm, c.hidden_size);
+        case CERA_ROLE_FFN_NORM: return f32_vector(&L->ffn_norm, c.hidden_size);
+        case CERA_ROLE_ATTN_Q: return matrix(&L->wq, qd, c.hidden_size);
+        case CERA_ROLE_ATTN_K: return matrix(&L->wk, kvd, c.hidden_size);
+        case CERA_ROLE_ATTN_V: return matrix(&L->wv, kvd, c.hidden_size);
+        case CERA_ROLE_ATTN_OUTPUT: return matrix(&L->wo, c.hidden_size, qd);
+        case CERA_ROLE_FFN_GATE: return matrix(&L->gate, c.intermediate_size, c.hidden_size);
+        case CERA_ROLE_FFN_UP: return matrix(&L->up, c.intermediate_size, c.hidden_size);
+        case CERA_ROLE_FFN_DOWN: return matrix(&L->down, c.hidden_size, c.intermediate_size);
+        default: return fail(CERA_CUDA_ERR_BAD_ARG, "add_tensor: unknown role %d", role);
+    }
+}
+
+int32_t cera_cuda_model_finalize(cera_cuda_model *m) {
+    if (!m) return fail(CERA_CUDA_ERR_BAD_ARG, "finalize: null model");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    if (m->finalized) return CERA_CUDA_OK;
+    const auto &c = m->cfg;
+    if (!m->embd || !m->out_norm) return fail(CERA_CUDA_ERR_STATE, "finalize: token_embd / output_norm missing");
+    for (uint32_t l = 0; l < c.n_layers; ++l) {
+        const Layer &L = m->layers[l];
+        if (!L.attn_norm || !L.ffn_norm || !L.wq || !L.wk || !L.wv || !L.wo || !L.gate || !L.up || !L.down)
+            return fail(CERA_CUDA_ERR_STATE, "finalize: layer %u is missing a tensor", l);
+    }
+    const size_t hs = c.hidden_size, qd = (size_t)c.n_heads * c.head_dim, kvd = (size_t)c.n_kv_heads * c.head_dim,
+                 ff = c.intermediate_size;
+    const size_t esz = c.kv_f16 ? 2 : 4;
+    for (auto &L : m->layers) {
+        CERA_TRY(dev_alloc(m, &L.kc, (size_t)c.max_seq_len * kvd * esz));
+        CERA_TRY(dev_alloc(m, &L.vc, (size_t)c.max_seq_len * kvd * esz));
+    }
+    CERA_TRY(dev_alloc(m, (void **)&m->hidden, hs * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->final_hidden, hs * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->q, qd * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->k, kvd * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->v, kvd * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->attn, qd * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->g, ff * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->u, ff * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->logits, (size_t)c.vocab_size * 4));
+    CERA_TRY(alloc_act(m, m->act_hs, hs));
+    CERA_TRY(alloc_act(m, m->act_q, qd));
+    CERA_TRY(alloc_act(m, m->act_ff, ff));
+    m->attn_ws_bytes = attn_workspace_bytes(c.n_heads, c.head_dim, c.max_seq_len);
+    CERA_TRY(dev_alloc(m, &m->attn_ws, m->attn_ws_bytes));
+    CERA_TRY(dev_alloc(m, (void **)&m->argmax_scratch, argmax_scratch_words() * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->dyn, 4 * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->tok_out, 4));
+    CERA_CUDA_TRY(cudaMallocHost((void **)&m->h_dyn, 8 * 4));
+    CERA_CUDA_TRY(cudaMallocHost((void **)&m->h_logits, (size_t)c.vocab_size * 4));
+    CERA_CUDA_TRY(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+    CERA_CUDA_TRY(cudaDeviceSynchronize());
+    m->finalized = true;
+    return CERA_CUDA_OK;
+}
+
+int32_t cera_cuda_forward(cera_cuda_model *m, uint32_t token, size_t pos, float *logits_out) {
+    if (!m || !logits_out) return fail(CERA_CUDA_ERR_BAD_ARG, "forward: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    CERA_TRY(run_token(m, token, pos, G_LOGITS));
+    const size_t bytes = (size_t)m->cfg.vocab_size * 4;
+    CERA_CUDA_TRY(cudaMemcpyAsync(m->h_logits, m->logits, bytes, cudaMemcpyDeviceToHost, m->stream));
+    CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    memcpy(logits_out, m->h_logits, bytes);
+    return CERA_CUDA_OK;
+}
+
+int32_t cera_cuda_forward_greedy(cera_cuda_model *m, uint32_t token, size_t pos, uint32_t *token_out) {
+    if (!m || !token_out) return fail(CERA_CUDA_ERR_BAD_ARG, "forward_greedy: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    CERA_TRY(run_token(m, token, pos, G_GREEDY));
+    CERA_CUDA_TRY(cudaMemcpyAsync(m->h_dyn + 4, m->tok_out, 4, cudaMemcpyDeviceToHost, m->stream));
+    CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    *token_out = m->h_dyn[4];
+    return CERA_CUDA_OK;
+}
+
+int32_t cera_cuda_forward_prefill(cera_cuda_model *m, const uint32_t *tokens, size_t n, size_t start_pos,
+                                  float *logits_out) {
+    if (!m || (!tokens && n)) return fail(CERA_CUDA_ERR_BAD_ARG, "forward_prefill: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    if (start_pos != m->seq_len) return fail(CERA_CUDA_ERR_STATE, "forward_prefill: start_pos %zu != seq_len %zu", start_pos, m->seq_len);
+    if (n == 0) return CERA_CUDA_OK;
+    // Per-token arithmetic for every prompt position: identical to decode, which is the
+    // reference's canonical stream (its batched kernels are held to the same per-cell
+    // arithmetic).  The host buffer h_dyn is rewritten per token, so wait for the copy
+    // of the previous one before touching it again.
+    for (size_t i = 0; i < n; ++i) {
+        const bool last = i + 1 == n;
+        CERA_TRY(run_token(m, tokens[i], start_pos + i, last && logits_out ? G_LOGITS : G_BODY));
+        CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    }
+    if (logits_out) {
+        const size_t bytes = (size_t)m->cfg.vocab_size * 4;
+        CERA_CUDA_TRY(cudaMemcpyAsync(m->h_logits, m->logits, bytes, cudaMemcpyDeviceToHost, m->stream));
+        CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+        memcpy(logits_out, m->h_logits, bytes);
+    }
+    return CERA_CUDA_OK;
+}
+
+int32_t cera_cuda_truncate_kv(cera_cuda_model *m, size_t len) {
+    if (!m) return fail(CERA_CUDA_ERR_BAD_ARG, "truncate_kv: null model");
+    std::lock_guard<std::mutex> lock(m->mu);
+    if (len < m->seq_len) m->seq_len = len;  // rows beyond seq_len are simply overwritten later
+    return CERA_CUDA_OK;
+}
+
+size_t cera_cuda_seq_len(const cera_cuda_model *m) { return m ? m->seq_len : 0; }
+size_t cera_cuda_memory_bytes(const cera_cuda_model *m) { return m ? m->mem_bytes : 0; }
+uint64_t cera_cuda_launch_count(const cera_cuda_model *m) { return m ? m->launches : 0; }
+
+int32_t cera_cuda_last_hidden(cera_cuda_model *m, float *out) {
+    if (!m || !out) return fail(CERA_CUDA_ERR_BAD_ARG, "last_hidden: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    if (!m->finalized) return fail(CERA_CUDA_ERR_STATE, "last_hidden: model not finalized");
+    CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return check_cuda(cudaMemcpy(out, m->final_hidden, (size_t)m->cfg.hidden_size * 4, cudaMemcpyDeviceToHost),
+                      "cudaMemcpy(last_hidden)");
+}
+
+void cera_cuda_model_free(cera_cuda_model *m) {
+    if (!m) return;
+    {
+        DeviceGuard dg(m->cfg.device);
+        if (m->stream) cudaStreamSynchronize(m->stream);
+        for (auto &kv : m->graphs) cudaGraphExecDestroy(kv.second);
+        for (void *p : m->owned) cudaFree(p);
+        auto fw = [](cera_cuda_weight *w) {
+            if (w) cera_cuda_weight_free(w);
+        };
+        fw(m->embd);
+        fw(m->output);
+        for (auto &L : m->layers) {
+            fw(L.wq); fw(L.wk); fw(L.wv); fw(L.wo); fw(L.gate); fw(L.up); fw(L.down);
+        }
+        if (m->h_dyn) cudaFreeHost(m->h_dyn);
+        if (m->h_logits) cudaFreeHost(m->h_logits);
+        if (m->stream) cudaStreamDestroy(m->stream);
+    }
+    delete m;
+}
+
+}  // extern "C"

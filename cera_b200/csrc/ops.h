@@ -1,0 +1,55 @@
+// Internal launch helpers shared between the C entry points and the model.
+#pragma once
+
+#include "act.cuh"
+#include "common.cuh"
+
+namespace cera {
+
+int32_t launch_quantize(const float *x, size_t k, size_t n, bool strided, float *scales, int8_t *quants,
+                        int16_t *sums, cudaStream_t st);
+// out_f32 and the quantized outputs are each optional (null = skip).
+int32_t launch_rmsnorm(const float *x, const float *weight, size_t n_elem, size_t n_cols, float eps, float *out_f32,
+                       float *scales, int8_t *quants, int16_t *sums, cudaStream_t st);
+int32_t launch_silu_mul(float *gate, const float *up, size_t n_elem, size_t n_cols, float *scales, int8_t *quants,
+                        int16_t *sums, cudaStream_t st);
+
+// Up to three weight matrices of one type sharing the same activations
+// (q/k/v, gate/up), handled by one launch.
+struct GemvSeg {
+    WeightView w;
+    float *y;  // [m x n] row-major
+};
+enum { EPI_STORE = 0, EPI_ADD = 1 };
+int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_cols, size_t ldy, int epilogue,
+                    cudaStream_t st);
+int32_t launch_gemm(const WeightView &w, const ActView &x, size_t n, float *out, cudaStream_t st);
+int32_t launch_gemv_q5k_f32(const WeightView &w, const float *x, float *y, cudaStream_t st);
+
+// Rotates q and k in place at position pos (or *pos_dev when non-null).  When k_cache is
+// non-null the rotated k and the untouched v are also appended as cache row `pos`
+// (f32, or f16 through the round-to-nearest-even narrow of cera/src/quant.rs:117-164).
+int32_t launch_rope(float *q, float *k, const float *v, size_t pos, const uint32_t *pos_dev, size_t n_heads,
+                    size_t n_kv_heads, size_t head_dim, float theta_scale, const float *freq_factors, int rope_type,
+                    void *k_cache, void *v_cache, int kv_f16, cudaStream_t st);
+
+size_t attn_workspace_bytes(size_t n_heads, size_t head_dim, size_t seq_len);
+// q8 outputs optional: the merge pass can emit the Q8_0 form of `out` for the next GEMV.
+int32_t launch_decode_attention(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
+                                size_t n_kv_heads, size_t head_dim, size_t seq_len, float scale, float *out,
+                                void *workspace, size_t workspace_bytes, float *scales, int8_t *quants, int16_t *sums,
+                                cudaStream_t st);
+
+uint32_t attn_pick_splits(size_t n_kv_heads, size_t seq_len_hint);
+// seq_len_dev != null: the kernel reads the length from device memory (graph replay).
+int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
+                                   size_t n_kv_heads, size_t head_dim, size_t seq_len, const uint32_t *seq_len_dev,
+                                   uint32_t n_splits, float scale, float *out, void *workspace, size_t workspace_bytes,
+                                   float *scales, int8_t *quants, int16_t *sums, cudaStream_t st);
+
+int32_t launch_embed(const WeightView &w, uint32_t token, const uint32_t *token_dev, float *out, cudaStream_t st);
+// First strict maximum (cera/src/sampler.rs:20-30).  scratch: 2*blocks words, see argmax_scratch_words().
+size_t argmax_scratch_words();
+int32_t launch_argmax(const float *x, size_t n, uint32_t *out, uint32_t *scratch, cudaStream_t st);
+
+}  // namespace cera

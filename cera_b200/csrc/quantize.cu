@@ -1,0 +1,152 @@
+// Q8_0 activation quantizer kernels, alone and fused behind RMSNorm / SiLU*mul.
+#include "act.cuh"
+#include "ops.h"
+
+namespace cera {
+
+namespace {
+
+// One warp per (column, block).  strided != 0: x is [k x n] with row stride n.
+__global__ void quantize_kernel(const float *__restrict__ x, size_t k, size_t n, int strided, float *scales,
+                                int8_t *quants, int16_t *sums) {
+    const size_t nb = k / 32;
+    const size_t wid = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= nb * n) return;
+    const size_t j = wid / nb, b = wid % nb;
+    const size_t e = b * 32 + lane;
+    const float v = strided ? x[e * n + j] : x[j * k + e];
+    float scale;
+    int hs;
+    const int q = quantize_lane(v, scale, hs);
+    quants[j * k + e] = (int8_t)q;
+    if (lane == 0) scales[j * nb + b] = scale;
+    if (sums && (lane & 15) == 0) sums[j * (k / 16) + b * 2 + (lane >> 4)] = (int16_t)hs;
+}
+
+// RMSNorm of one column per CTA (cera/src/backend/cpu.rs:2479-2496: f64 sum of
+// squares, inv = (float)(1/sqrt(mean+eps)), x*inv*w left to right), then
+// optionally the Q8_0 quantizer on the normed values.
+__global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ weight, size_t n_elem, float eps,
+                               float *out_f32, float *scales, int8_t *quants, int16_t *sums) {
+    __shared__ double red[32];
+    __shared__ float inv_s;
+    const size_t col = blockIdx.x;
+    const float *xc = x + col * n_elem;
+    double ss = 0.0;
+    for (size_t i = threadIdx.x; i < n_elem; i += blockDim.x) {
+        const double v = (double)xc[i];
+        ss += v * v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        double t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (threadIdx.x == 0) inv_s = (float)(1.0 / sqrt(t / (double)n_elem + (double)eps));
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    // n_elem is a multiple of 32 whenever quantization is requested, so whole warps stay converged.
+    for (size_t i = threadIdx.x; i < n_elem; i += blockDim.x) {
+        const float v = __fmul_rn(__fmul_rn(xc[i], inv), weight[i]);
+        if (out_f32) out_f32[col * n_elem + i] = v;
+        if (quants) {
+            float scale;
+            int hs;
+            const int q = quantize_lane(v, scale, hs);
+            const int lane = threadIdx.x & 31;
+            quants[col * n_elem + i] = (int8_t)q;
+            if (lane == 0) scales[col * (n_elem / 32) + i / 32] = scale;
+            if ((lane & 15) == 0) sums[col * (n_elem / 16) + i / 16] = (int16_t)hs;
+        }
+    }
+}
+
+__global__ void silu_mul_kernel(float *gate, const float *__restrict__ up, size_t n_elem, size_t n_cols,
+                                float *scales, int8_t *quants, int16_t *sums) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_elem * n_cols) return;
+    const float v = silu_mul(gate[i], up[i]);
+    gate[i] = v;
+    if (quants) {
+        float scale;
+        int hs;
+        const int q = quantize_lane(v, scale, hs);
+        const int lane = threadIdx.x & 31;
+        quants[i] = (int8_t)q;
+        if (lane == 0) scales[i / 32] = scale;
+        if ((lane & 15) == 0) sums[i / 16] = (int16_t)hs;
+    }
+}
+
+}  // namespace
+
+int32_t launch_quantize(const float *x, size_t k, size_t n, bool strided, float *scales, int8_t *quants,
+                        int16_t *sums, cudaStream_t st) {
+    if (!x || !scales || !quants) return fail(CERA_CUDA_ERR_BAD_ARG, "quantize_q8_0: null argument");
+    if (k == 0 || k % 32) return fail(CERA_CUDA_ERR_BAD_ARG, "quantize_q8_0: k=%zu must be a positive multiple of 32", k);
+    if (n == 0) return CERA_CUDA_OK;
+    const size_t warps = (k / 32) * n;
+    const int threads = 256;
+    const size_t grid = (warps * 32 + threads - 1) / threads;
+    quantize_kernel<<<(unsigned)grid, threads, 0, st>>>(x, k, n, strided ? 1 : 0, scales, quants, sums);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "quantize launch");
+}
+
+int32_t launch_rmsnorm(const float *x, const float *weight, size_t n_elem, size_t n_cols, float eps, float *out_f32,
+                       float *scales, int8_t *quants, int16_t *sums, cudaStream_t st) {
+    if (!x || !weight) return fail(CERA_CUDA_ERR_BAD_ARG, "rmsnorm: null argument");
+    if (quants && (n_elem % 32 || !scales || !sums))
+        return fail(CERA_CUDA_ERR_BAD_ARG, "rmsnorm+quantize: n=%zu must be a multiple of 32", n_elem);
+    if (n_elem == 0 || n_cols == 0) return CERA_CUDA_OK;
+    const int threads = n_elem >= 1024 ? 1024 : (int)((n_elem + 31) / 32 * 32);
+    rmsnorm_kernel<<<(unsigned)n_cols, threads, 0, st>>>(x, weight, n_elem, eps, out_f32, scales, quants, sums);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "rmsnorm launch");
+}
+
+int32_t launch_silu_mul(float *gate, const float *up, size_t n_elem, size_t n_cols, float *scales, int8_t *quants,
+                        int16_t *sums, cudaStream_t st) {
+    if (!gate || !up) return fail(CERA_CUDA_ERR_BAD_ARG, "silu_mul: null argument");
+    if (quants && n_elem % 32) return fail(CERA_CUDA_ERR_BAD_ARG, "silu_mul+quantize: n=%zu must be a multiple of 32", n_elem);
+    const size_t total = n_elem * n_cols;
+    if (total == 0) return CERA_CUDA_OK;
+    const int threads = 256;
+    silu_mul_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, st>>>(gate, up, n_elem, n_cols, scales,
+                                                                                   quants, sums);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "silu_mul launch");
+}
+
+}  // namespace cera
+
+using namespace cera;
+
+extern "C" {
+
+int32_t cera_cuda_quantize_q8_0(const float *x_dev, size_t k, size_t n, float *scales_dev, int8_t *quants_dev,
+                                int16_t *sums_dev, void *stream) {
+    return launch_quantize(x_dev, k, n, false, scales_dev, quants_dev, sums_dev, (cudaStream_t)stream);
+}
+
+int32_t cera_cuda_quantize_columns(const float *mat_dev, size_t dim, size_t n, float *scales_dev, int8_t *quants_dev,
+                                   int16_t *sums_dev, void *stream) {
+    return launch_quantize(mat_dev, dim, n, true, scales_dev, quants_dev, sums_dev, (cudaStream_t)stream);
+}
+
+int32_t cera_cuda_rmsnorm(const float *x_dev, const float *weight_dev, size_t n, float eps, float *out_dev,
+                          void *stream) {
+    if (!out_dev) return fail(CERA_CUDA_ERR_BAD_ARG, "rmsnorm: null output");
+    return launch_rmsnorm(x_dev, weight_dev, n, 1, eps, out_dev, nullptr, nullptr, nullptr, (cudaStream_t)stream);
+}
+
+int32_t cera_cuda_silu_mul(float *gate_dev, const float *up_dev, size_t n, void *stream) {
+    return launch_silu_mul(gate_dev, up_dev, n, 1, nullptr, nullptr, nullptr, (cudaStream_t)stream);
+}
+
+}  // extern "C"

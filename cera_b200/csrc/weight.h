@@ -1,0 +1,21 @@
+// Host-side handle of a device-resident quantized matrix.
+#pragma once
+
+#include "common.cuh"
+
+struct cera_cuda_weight {
+    cera::WeightView v{};
+    void *base = nullptr;   // one allocation holding every plane
+    size_t bytes = 0;       // size of that allocation
+    // Q8_0 activation scratch for one column of length k, used by cera_cuda_gemv.
+    float *xs = nullptr;
+    int8_t *xq = nullptr;
+    int16_t *xsum = nullptr;
+    int device = 0;
+};
+
+namespace cera {
+// Allocates planes and re-lays `bytes` (host or device, raw GGUF blocks) into them.
+int32_t weight_upload(int32_t type, size_t m, size_t k, const void *bytes, size_t nbytes, bool with_scratch,
+                      cera_cuda_weight **out);
+}  // namespace cera

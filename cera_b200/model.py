@@ -1,0 +1,98 @@
+"""Host-side mirror of `trait Model` (cera/src/model/mod.rs:200-606) over the
+C ABI: forward, forward_greedy, forward_prefill, truncate_kv, gpu_memory_bytes."""
+import ctypes as C
+import enum
+
+import numpy as np
+
+from ._lib import Config, check, lib
+
+
+class Role(enum.IntEnum):
+    TOKEN_EMBD = 0
+    OUTPUT_NORM = 1
+    OUTPUT = 2
+    ATTN_NORM = 3
+    ATTN_Q = 4
+    ATTN_K = 5
+    ATTN_V = 6
+    ATTN_OUTPUT = 7
+    FFN_NORM = 8
+    FFN_GATE = 9
+    FFN_UP = 10
+    FFN_DOWN = 11
+    ROPE_FREQS = 12
+
+
+ModelConfig = Config
+
+
+class CudaModel:
+    def __init__(self, **cfg):
+        cfg.setdefault("device", 0)
+        cfg.setdefault("rope_type", 0)
+        cfg.setdefault("kv_f16", 0)
+        self.cfg = Config(**cfg)
+        self.handle = C.c_void_p()
+        check(lib.cera_cuda_model_create(C.byref(self.cfg), C.byref(self.handle)))
+
+    def config(self):
+        return self.cfg
+
+    def add_tensor(self, role, layer, ggml_type, rows, cols, data):
+        """data: numpy array / bytes (host) or a torch CUDA tensor (device) of raw GGUF bytes."""
+        if isinstance(data, (bytes, bytearray)):
+            data = np.frombuffer(data, dtype=np.uint8)
+        if isinstance(data, np.ndarray):
+            data = np.ascontiguousarray(data)
+            ptr, nbytes = data.ctypes.data, data.nbytes
+        else:
+            data = data.contiguous()
+            ptr, nbytes = data.data_ptr(), data.numel() * data.element_size()
+        check(lib.cera_cuda_model_add_tensor(self.handle, int(role), layer, ggml_type, rows, cols, C.c_void_p(ptr),
+                                             nbytes))
+
+    def finalize(self):
+        check(lib.cera_cuda_model_finalize(self.handle))
+
+    def forward(self, token, pos):
+        logits = np.empty(self.cfg.vocab_size, dtype=np.float32)
+        check(lib.cera_cuda_forward(self.handle, token, pos, logits.ctypes.data_as(C.c_void_p)))
+        return logits
+
+    def forward_greedy(self, token, pos):
+        out = C.c_uint32()
+        check(lib.cera_cuda_forward_greedy(self.handle, token, pos, C.byref(out)))
+        return out.value
+
+    def forward_prefill(self, tokens, start_pos, want_logits=True):
+        tokens = np.ascontiguousarray(tokens, dtype=np.uint32)
+        logits = np.empty(self.cfg.vocab_size, dtype=np.float32) if want_logits else None
+        check(lib.cera_cuda_forward_prefill(self.handle, tokens.ctypes.data_as(C.c_void_p), tokens.size, start_pos,
+                                            logits.ctypes.data_as(C.c_void_p) if want_logits else None))
+        return logits
+
+    def truncate_kv(self, n):
+        check(lib.cera_cuda_truncate_kv(self.handle, n))
+
+    @property
+    def seq_len(self):
+        return lib.cera_cuda_seq_len(self.handle)
+
+    def gpu_memory_bytes(self):
+        return lib.cera_cuda_memory_bytes(self.handle)
+
+    def launch_count(self):
+        return lib.cera_cuda_launch_count(self.handle)
+
+    def last_hidden(self):
+        out = np.empty(self.cfg.hidden_size, dtype=np.float32)
+        check(lib.cera_cuda_last_hidden(self.handle, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def close(self):
+        if getattr(self, "handle", None):
+            lib.cera_cuda_model_free(self.handle)
+            self.handle = None
+
+    __del__ = close

@@ -1,0 +1,181 @@
+"""Operator-level interface, named after the reference's own functions
+(cera/src/model/transformer.rs: gemv 450-453, gemm_preq 710-788,
+quantize_columns 865-946, decode_attention 1249-1305).
+
+Tensors are torch CUDA tensors used purely as device memory; every function
+hands raw device pointers to the C ABI and launches on torch's current stream.
+"""
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+from .types import BLOCK, row_bytes
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _dev(t, dtype):
+    if not (isinstance(t, torch.Tensor) and t.is_cuda):
+        raise TypeError("expected a CUDA tensor: this path has no CPU fallback")
+    if t.dtype != dtype or not t.is_contiguous():
+        raise TypeError(f"expected a contiguous {dtype} tensor, got {t.dtype}")
+    return t
+
+
+class QuantWeight:
+    """A device-resident quantized [m x k] matrix (the device form of a WeightRef,
+    cera/src/model/transformer.rs:127-231).  `raw` holds GGUF block bytes: a
+    uint8 torch tensor (CPU or CUDA), a numpy uint8 array or bytes."""
+
+    def __init__(self, ggml_type, m, k, raw):
+        import numpy as np
+        if isinstance(raw, (bytes, bytearray)):
+            raw = np.frombuffer(raw, dtype=np.uint8)
+        if isinstance(raw, np.ndarray):
+            raw = np.ascontiguousarray(raw, dtype=np.uint8)
+            ptr, nbytes, keep = raw.ctypes.data, raw.size, raw
+        else:
+            raw = raw.contiguous()
+            ptr, nbytes, keep = raw.data_ptr(), raw.numel() * raw.element_size(), raw
+        h = C.c_void_p()
+        check(lib.cera_cuda_weight_create(ggml_type, m, k, C.c_void_p(ptr), nbytes, C.byref(h)))
+        del keep
+        self.handle, self.type, self.m, self.k = h, ggml_type, m, k
+
+    def close(self):
+        if getattr(self, "handle", None):
+            lib.cera_cuda_weight_free(self.handle)
+            self.handle = None
+
+    __del__ = close
+
+
+class Q8Activations:
+    """Q8_0 activation columns in the reference's SoA layout
+    (cera/src/model/transformer.rs:857-860) plus the 16-wide quant sums."""
+
+    def __init__(self, k, n, device="cuda"):
+        self.k, self.n = k, n
+        self.scales = torch.empty(n * (k // 32), dtype=torch.float32, device=device)
+        self.quants = torch.empty(n * k, dtype=torch.int8, device=device)
+        self.sums = torch.empty(n * (k // 16), dtype=torch.int16, device=device)
+
+
+def quantize_q8_0(x, k=None, n=1):
+    """x: n contiguous columns of length k (f32).  -> Q8Activations."""
+    x = _dev(x, torch.float32)
+    k = k or x.numel() // n
+    a = Q8Activations(k, n, x.device)
+    check(lib.cera_cuda_quantize_q8_0(_ptr(x), k, n, _ptr(a.scales), _ptr(a.quants), _ptr(a.sums), _stream()))
+    return a
+
+
+def quantize_columns(mat, dim, n):
+    """mat: [dim x n] row stride n (token j = column j)."""
+    mat = _dev(mat, torch.float32)
+    a = Q8Activations(dim, n, mat.device)
+    check(lib.cera_cuda_quantize_columns(_ptr(mat), dim, n, _ptr(a.scales), _ptr(a.quants), _ptr(a.sums), _stream()))
+    return a
+
+
+def gemv(w: QuantWeight, x, y=None):
+    x = _dev(x, torch.float32)
+    if x.numel() != w.k:
+        raise ValueError(f"gemv: x has {x.numel()} elements, weight k is {w.k}")
+    y = y if y is not None else torch.empty(w.m, dtype=torch.float32, device=x.device)
+    check(lib.cera_cuda_gemv(w.handle, _ptr(x), _ptr(_dev(y, torch.float32)), _stream()))
+    return y
+
+
+def gemv_q5k_f32(w: QuantWeight, x, y=None):
+    x = _dev(x, torch.float32)
+    y = y if y is not None else torch.empty(w.m, dtype=torch.float32, device=x.device)
+    check(lib.cera_cuda_gemv_q5k_f32(w.handle, _ptr(x), _ptr(y), _stream()))
+    return y
+
+
+def gemm_preq(w: QuantWeight, acts: Q8Activations, out=None):
+    """out[m x n] = W * X for pre-quantized columns."""
+    out = out if out is not None else torch.empty(w.m, acts.n, dtype=torch.float32, device=acts.quants.device)
+    check(lib.cera_cuda_gemm_preq(w.handle, _ptr(acts.scales), _ptr(acts.quants), _ptr(acts.sums), _ptr(out), w.m,
+                                  acts.n, acts.k, _stream()))
+    return out
+
+
+def block_sums(w: QuantWeight, row, quants):
+    quants = _dev(quants, torch.int8)
+    u = torch.empty(w.k // 16, dtype=torch.int32, device=quants.device)
+    a = torch.empty(w.k // 16, dtype=torch.int32, device=quants.device)
+    check(lib.cera_cuda_block_sums(w.handle, row, _ptr(quants), _ptr(u), _ptr(a), _stream()))
+    return u, a
+
+
+def dequantize_rows(w: QuantWeight, row0=0, nrows=None):
+    nrows = w.m - row0 if nrows is None else nrows
+    out = torch.empty(nrows, w.k, dtype=torch.float32, device="cuda")
+    check(lib.cera_cuda_dequantize_rows(w.handle, row0, nrows, _ptr(out), _stream()))
+    return out
+
+
+def rmsnorm(x, weight, eps):
+    x = _dev(x, torch.float32)
+    out = torch.empty_like(x)
+    check(lib.cera_cuda_rmsnorm(_ptr(x), _ptr(_dev(weight, torch.float32)), x.numel(), eps, _ptr(out), _stream()))
+    return out
+
+
+def silu_mul(gate, up):
+    gate = _dev(gate, torch.float32).clone()
+    check(lib.cera_cuda_silu_mul(_ptr(gate), _ptr(_dev(up, torch.float32)), gate.numel(), _stream()))
+    return gate
+
+
+def rope(q, k, pos, n_heads, n_kv_heads, head_dim, freq_base, freq_factors=None, rope_type=0):
+    q = _dev(q, torch.float32).clone()
+    k = _dev(k, torch.float32).clone()
+    check(lib.cera_cuda_rope(_ptr(q), _ptr(k), pos, n_heads, n_kv_heads, head_dim, freq_base, _ptr(freq_factors),
+                             rope_type, _stream()))
+    return q, k
+
+
+def decode_attention(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim, seq_len, scale, workspace=None):
+    """k_cache / v_cache: time-major rows of n_kv_heads*head_dim, float32 or float16."""
+    q = _dev(q, torch.float32)
+    f16 = k_cache.dtype == torch.float16
+    if v_cache.dtype != k_cache.dtype or k_cache.dtype not in (torch.float16, torch.float32):
+        raise TypeError("KV caches must both be float32 or both float16")
+    need = lib.cera_cuda_decode_attention_workspace_bytes(n_heads, head_dim, seq_len)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    out = torch.empty(n_heads * head_dim, dtype=torch.float32, device=q.device)
+    check(lib.cera_cuda_decode_attention(_ptr(q), _ptr(k_cache), _ptr(v_cache), int(f16), n_heads, n_kv_heads,
+                                         head_dim, seq_len, scale, _ptr(out), _ptr(workspace), workspace.numel(),
+                                         _stream()))
+    return out
+
+
+def synth_normal(n, seed, sigma, offset=0, device="cuda"):
+    out = torch.empty(n, dtype=torch.float32, device=device)
+    check(lib.cera_cuda_synth_normal(_ptr(out), n, seed, offset, sigma, _stream()))
+    return out
+
+
+def quantize_weights(ggml_type, w):
+    """f32 device tensor -> uint8 device tensor of GGUF blocks."""
+    w = _dev(w, torch.float32)
+    elems, nbytes = BLOCK[ggml_type]
+    out = torch.empty(w.numel() // elems * nbytes, dtype=torch.uint8, device=w.device)
+    check(lib.cera_cuda_quantize_weights(ggml_type, _ptr(w), w.numel(), _ptr(out), _stream()))
+    return out
+
+
+__all__ = [n for n in dir() if not n.startswith("_")]
+_ = (_lib, row_bytes)

@@ -1,0 +1,238 @@
+/* cera_cuda.h - C ABI of the B200 (sm_100a) CUDA device for cera's quantized
+ * decode hot path: GGML-block quantized matmul against Q8_0 activations and
+ * split-KV flash-decode GQA attention, plus the dense llama-architecture model
+ * wired from them.
+ *
+ * This is the boundary a `--device cuda` backend of cera binds: plain pointers
+ * and sizes, no C++ or torch types.  Every entry point returns an int32 status
+ * (CERA_CUDA_OK == 0); cera_cuda_last_error() gives the text for the calling
+ * thread.  Nothing here falls back to the CPU: with no usable CUDA device every
+ * call fails with CERA_CUDA_ERR_CUDA.
+ *
+ * Conventions (cera's own, cera/src/backend/cpu.rs:1423): a weight matrix is
+ * W[m x k], m = out-features (rows), k = in-features; a batch is n activation
+ * columns (tokens); out is [m x n] row-major.  Pointers named *_dev are device
+ * pointers on the current device; `stream` is a cudaStream_t passed as void*
+ * (NULL = the legacy default stream).  Operator-level calls are asynchronous
+ * on `stream`; model-level calls take host buffers and return when the result
+ * is on the host.
+ */
+#ifndef CERA_CUDA_H
+#define CERA_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define CERA_API __declspec(dllexport)
+#else
+#define CERA_API __attribute__((visibility("default")))
+#endif
+
+enum {
+    CERA_CUDA_OK = 0,
+    CERA_CUDA_ERR_BAD_ARG = 1,     /* extent / alignment / null contract violated   */
+    CERA_CUDA_ERR_UNSUPPORTED = 2, /* (dtype, role) pair with no kernel: loud, never
+                                      a silent fallback (cera/src/model/transformer.rs:607-633) */
+    CERA_CUDA_ERR_OOM = 3,
+    CERA_CUDA_ERR_CUDA = 4, /* driver / runtime error, text in last_error */
+    CERA_CUDA_ERR_NCCL = 5,
+    CERA_CUDA_ERR_TIMEOUT = 6, /* a bounded device-side wait ran out */
+    CERA_CUDA_ERR_STATE = 7    /* call order violated (e.g. pos != seq_len) */
+};
+
+/* GGML tensor type ids as stored in GGUF (cera/src/convert/writer.rs:23-37). */
+enum {
+    CERA_TYPE_F32 = 0,
+    CERA_TYPE_F16 = 1,
+    CERA_TYPE_Q4_0 = 2,
+    CERA_TYPE_Q4_1 = 3,
+    CERA_TYPE_Q8_0 = 8,
+    CERA_TYPE_Q4_K = 12,
+    CERA_TYPE_Q5_K = 13,
+    CERA_TYPE_Q6_K = 14,
+    CERA_TYPE_BF16 = 30
+};
+
+CERA_API const char *cera_cuda_last_error(void);
+CERA_API int32_t cera_cuda_device_count(int32_t *count);
+
+/* ------------------------------------------------------------------------ */
+/* Weights.  Replaces the (WeightRef, mmap bytes) pair a CPU GEMV receives   */
+/* (cera/src/model/transformer.rs:127-231, gpu_weight_source.rs:40-118).     */
+/* `bytes` is the raw GGUF block data of an [m x k] tensor, host or device    */
+/* memory; it is copied (and re-laid out into 16-byte aligned planes) before  */
+/* the call returns.                                                          */
+typedef struct cera_cuda_weight cera_cuda_weight;
+
+CERA_API int32_t cera_cuda_weight_create(int32_t ggml_type, size_t m, size_t k, const void *bytes,
+                                         size_t nbytes, cera_cuda_weight **out);
+CERA_API void cera_cuda_weight_free(cera_cuda_weight *w);
+CERA_API int32_t cera_cuda_weight_info(const cera_cuda_weight *w, int32_t *ggml_type, size_t *m,
+                                       size_t *k, size_t *device_bytes);
+
+/* cera/src/quant.rs:321-356 dequantize_*_matrix, rows [row0, row0+nrows):
+ * out_dev[nrows x k] f32, bit-identical to the reference's dequantizers. */
+CERA_API int32_t cera_cuda_dequantize_rows(const cera_cuda_weight *w, size_t row0, size_t nrows,
+                                           float *out_dev, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Q8_0 activation quantizer (cera/src/backend/cpu.rs:942-1041).              */
+/* x_dev: n columns, column j at x_dev + j*k (contiguous).  Outputs are the   */
+/* reference's SoA layout (cera/src/model/transformer.rs:857-860):            */
+/* scales_dev[n][k/32] f32, quants_dev[n][k] i8.  sums_dev (optional, may be  */
+/* NULL) receives int16 sums of each 16 consecutive quants, [n][k/16]: the    */
+/* kernels' form of cera/src/backend/simd.rs:5651-5684.                       */
+CERA_API int32_t cera_cuda_quantize_q8_0(const float *x_dev, size_t k, size_t n, float *scales_dev,
+                                         int8_t *quants_dev, int16_t *sums_dev, void *stream);
+/* cera/src/model/transformer.rs:865-946: mat_dev is [dim x n] with row stride
+ * n (token j = column j). */
+CERA_API int32_t cera_cuda_quantize_columns(const float *mat_dev, size_t dim, size_t n,
+                                            float *scales_dev, int8_t *quants_dev,
+                                            int16_t *sums_dev, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Matmul.                                                                    */
+/* cera/src/model/transformer.rs:450-453 gemv -> cera/src/backend/cpu.rs:2360- */
+/* 2474 gemv_dispatch: y[m] = W * x with x quantized to Q8_0 on the way in.    */
+/* Uses the weight's own activation scratch: calls on one weight serialise on  */
+/* the stream they are given.  Q5_K runs the Q8_0-activation extension unless  */
+/* cera_cuda_gemv_q5k_f32 is used.                                             */
+CERA_API int32_t cera_cuda_gemv(const cera_cuda_weight *w, const float *x_dev, float *y_dev,
+                                void *stream);
+/* cera/src/backend/cpu.rs:1830-1854: Q5_K against f32 activations, the only
+ * Q5_K GEMV the reference has. */
+CERA_API int32_t cera_cuda_gemv_q5k_f32(const cera_cuda_weight *w, const float *x_dev, float *y_dev,
+                                        void *stream);
+/* cera/src/model/transformer.rs:710-788 gemm_preq -> cpu.rs:1437-1557:
+ * out_dev[m x n] = W * X for pre-quantized columns.  sums_dev as produced by
+ * cera_cuda_quantize_q8_0 (required). */
+CERA_API int32_t cera_cuda_gemm_preq(const cera_cuda_weight *w, const float *scales_dev,
+                                     const int8_t *quants_dev, const int16_t *sums_dev,
+                                     float *out_dev, size_t m, size_t n, size_t k, void *stream);
+/* Parity probe: the integer sums the GEMV kernels form for one weight row and
+ * one activation column, per 16-element half block: u_dev[k/16] = sum q*a (q as
+ * the kernel sees it), a_dev[k/16] = sum a.  Exact, compared bit for bit. */
+CERA_API int32_t cera_cuda_block_sums(const cera_cuda_weight *w, size_t row, const int8_t *quants_dev,
+                                      int32_t *u_dev, int32_t *a_dev, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Glue on the decode path.                                                   */
+/* cera/src/backend/cpu.rs:2479-2496. out_dev may alias x_dev. */
+CERA_API int32_t cera_cuda_rmsnorm(const float *x_dev, const float *weight_dev, size_t n, float eps,
+                                   float *out_dev, void *stream);
+/* cera/src/backend/cpu.rs:2570-2575: gate = silu(gate) * up. */
+CERA_API int32_t cera_cuda_silu_mul(float *gate_dev, const float *up_dev, size_t n, void *stream);
+/* cera/src/backend/cpu.rs:5009-5180.  rope_type 0 = NORM (adjacent pairs,
+ * optional freq_factors_dev[head_dim/2]), 1 = NEOX. */
+CERA_API int32_t cera_cuda_rope(float *q_dev, float *k_dev, size_t pos, size_t n_heads,
+                                size_t n_kv_heads, size_t head_dim, float freq_base,
+                                const float *freq_factors_dev, int32_t rope_type, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Flash-decode GQA attention (cera/src/model/transformer.rs:1249-1305).      */
+/* Caches are time-major rows of n_kv_heads*head_dim, f32 (kv_f16 = 0) or raw  */
+/* IEEE half bits (kv_f16 = 1), as cera/src/kv_cache.rs:201-221 keeps them.    */
+/* One query token attends to rows [0, seq_len).  workspace_dev must hold      */
+/* cera_cuda_decode_attention_workspace_bytes(...) bytes.                      */
+CERA_API size_t cera_cuda_decode_attention_workspace_bytes(size_t n_heads, size_t head_dim,
+                                                          size_t seq_len);
+CERA_API int32_t cera_cuda_decode_attention(const float *q_dev, const void *k_cache_dev,
+                                            const void *v_cache_dev, int32_t kv_f16, size_t n_heads,
+                                            size_t n_kv_heads, size_t head_dim, size_t seq_len,
+                                            float scale, float *out_dev, void *workspace_dev,
+                                            size_t workspace_bytes, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Synthetic inputs for benchmarks and tests (the reference's counterpart is   */
+/* its converter, cera/src/convert/quantize.rs:254-343 quantize_tensor_data).  */
+/* out_dev[i] = sigma * IH12(seed, offset+i): twelve 16-bit uniforms from three */
+/* splitmix64 draws, centred and scaled in integer arithmetic.                  */
+CERA_API int32_t cera_cuda_synth_normal(float *out_dev, size_t n, uint64_t seed, uint64_t offset,
+                                        float sigma, void *stream);
+/* f32 -> GGML blocks with the reference's quantizer rules
+ * (cera/src/convert/quantize.rs:344-387, 523-570, 719-1094). */
+CERA_API int32_t cera_cuda_quantize_weights(int32_t ggml_type, const float *in_dev, size_t n,
+                                            void *out_dev, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Model: the object behind `Box<dyn Model>` for --device cuda                 */
+/* (cera/src/model/mod.rs:200-606; config mirrors ModelConfig, mod.rs:117-145). */
+typedef struct cera_cuda_model cera_cuda_model;
+
+typedef struct {
+    uint32_t n_layers;
+    uint32_t hidden_size;
+    uint32_t intermediate_size;
+    uint32_t n_heads;
+    uint32_t n_kv_heads;
+    uint32_t head_dim;
+    uint32_t vocab_size;
+    uint32_t max_seq_len;
+    float rope_theta;
+    float rms_norm_eps;
+    int32_t rope_type; /* 0 NORM (llama), 1 NEOX */
+    int32_t kv_f16;    /* 0: f32 KV (the CPU default), 1: f16 KV (KvCompression::F16) */
+    int32_t device;    /* CUDA ordinal */
+    int32_t reserved;
+} cera_cuda_config;
+
+/* Tensor roles: the GGUF names a llama-architecture loader resolves
+ * (cera/src/model/llama.rs:158-450). */
+enum {
+    CERA_ROLE_TOKEN_EMBD = 0,  /* token_embd.weight            */
+    CERA_ROLE_OUTPUT_NORM = 1, /* output_norm.weight (F32)      */
+    CERA_ROLE_OUTPUT = 2,      /* output.weight (optional: tied) */
+    CERA_ROLE_ATTN_NORM = 3,   /* blk.N.attn_norm.weight (F32)   */
+    CERA_ROLE_ATTN_Q = 4,
+    CERA_ROLE_ATTN_K = 5,
+    CERA_ROLE_ATTN_V = 6,
+    CERA_ROLE_ATTN_OUTPUT = 7,
+    CERA_ROLE_FFN_NORM = 8, /* blk.N.ffn_norm.weight (F32) */
+    CERA_ROLE_FFN_GATE = 9,
+    CERA_ROLE_FFN_UP = 10,
+    CERA_ROLE_FFN_DOWN = 11,
+    CERA_ROLE_ROPE_FREQS = 12 /* rope_freqs.weight (F32, optional) */
+};
+
+CERA_API int32_t cera_cuda_model_create(const cera_cuda_config *cfg, cera_cuda_model **out);
+/* GpuWeightSource::weight_bytes (cera/src/model/gpu_weight_source.rs:40-118):
+ * bytes are borrowed for the call only (host or device memory). */
+CERA_API int32_t cera_cuda_model_add_tensor(cera_cuda_model *m, int32_t role, int32_t layer,
+                                            int32_t ggml_type, size_t rows, size_t cols,
+                                            const void *bytes, size_t nbytes);
+/* Checks every required tensor is present, allocates KV and scratch, and
+ * records the decode step.  Must precede the first forward. */
+CERA_API int32_t cera_cuda_model_finalize(cera_cuda_model *m);
+/* Model::forward (mod.rs:202): one token at pos == seq_len; logits_out[vocab]
+ * on the host. */
+CERA_API int32_t cera_cuda_forward(cera_cuda_model *m, uint32_t token, size_t pos,
+                                   float *logits_out);
+/* Model::forward_greedy (mod.rs:494-497): argmax on the device, first maximum
+ * wins (cera/src/sampler.rs:20-30); 4 bytes come back. */
+CERA_API int32_t cera_cuda_forward_greedy(cera_cuda_model *m, uint32_t token, size_t pos,
+                                          uint32_t *token_out);
+/* Model::forward_prefill (cera/src/model/llama.rs:1607-1649): start_pos must
+ * equal seq_len; logits of the last token (may be NULL). */
+CERA_API int32_t cera_cuda_forward_prefill(cera_cuda_model *m, const uint32_t *tokens, size_t n,
+                                           size_t start_pos, float *logits_out);
+/* Model::truncate_kv (mod.rs:251-283). */
+CERA_API int32_t cera_cuda_truncate_kv(cera_cuda_model *m, size_t len);
+CERA_API size_t cera_cuda_seq_len(const cera_cuda_model *m);
+/* Model::gpu_memory_bytes (mod.rs:500). */
+CERA_API size_t cera_cuda_memory_bytes(const cera_cuda_model *m);
+/* Final normed hidden state of the last forward, hidden_size floats on the
+ * host (Model::hidden_states precedent; used for drift diagnosis). */
+CERA_API int32_t cera_cuda_last_hidden(cera_cuda_model *m, float *out);
+/* Kernels launched by this library on behalf of the model since creation. */
+CERA_API uint64_t cera_cuda_launch_count(const cera_cuda_model *m);
+CERA_API void cera_cuda_model_free(cera_cuda_model *m);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CERA_CUDA_H */

@@ -1,0 +1,106 @@
+"""CUDA glue kernels and flash-decode attention against the oracle."""
+import math
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+from gpu_util import assert_bits, assert_close, need_gpu
+
+pytestmark = pytest.mark.gpu
+
+
+def _cuda(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def test_rmsnorm_and_silu_mul():
+    torch = need_gpu()
+    import cera_b200 as cb
+    rng = np.random.default_rng(0)
+    for n in (32, 4096, 14336):
+        x = rng.standard_normal(n).astype(np.float32) * 3
+        w = rng.standard_normal(n).astype(np.float32)
+        got = cb.rmsnorm(_cuda(torch, x), _cuda(torch, w), 1e-5).cpu().numpy()
+        want = O.rmsnorm(x, w, 1e-5)
+        # f64 partial sums are combined in a different order: equal or one ulp of `inv` apart
+        assert np.allclose(got, want, rtol=2e-7, atol=0)
+        g = rng.standard_normal(n).astype(np.float32) * 4
+        u = rng.standard_normal(n).astype(np.float32)
+        assert_bits(cb.silu_mul(_cuda(torch, g), _cuda(torch, u)).cpu().numpy(), O.silu_mul(g, u), "silu_mul")
+
+
+@pytest.mark.parametrize("rope_type", [0, 1])
+@pytest.mark.parametrize("pos", [0, 1, 511, 32767])
+def test_rope(rope_type, pos):
+    torch = need_gpu()
+    import cera_b200 as cb
+    rng = np.random.default_rng(pos)
+    nh, nkv, hd = 32, 8, 128
+    q = rng.standard_normal(nh * hd).astype(np.float32)
+    k = rng.standard_normal(nkv * hd).astype(np.float32)
+    gq, gk = cb.rope(_cuda(torch, q), _cuda(torch, k), pos, nh, nkv, hd, 500000.0, rope_type=rope_type)
+    wq, wk = O.rope(q, k, pos, nh, nkv, hd, 500000.0, rope_type=rope_type)
+    assert_close(gq.cpu().numpy(), wq, "q")
+    assert_close(gk.cpu().numpy(), wk, "k")
+
+
+def test_rope_freq_factors():
+    torch = need_gpu()
+    import cera_b200 as cb
+    rng = np.random.default_rng(3)
+    nh, nkv, hd = 4, 2, 64
+    q = rng.standard_normal(nh * hd).astype(np.float32)
+    k = rng.standard_normal(nkv * hd).astype(np.float32)
+    ff = (1.0 + rng.random(hd // 2) * 7).astype(np.float32)
+    gq, gk = cb.rope(_cuda(torch, q), _cuda(torch, k), 77, nh, nkv, hd, 10000.0, _cuda(torch, ff))
+    wq, wk = O.rope(q, k, 77, nh, nkv, hd, 10000.0, ff)
+    assert_close(gq.cpu().numpy(), wq)
+    assert_close(gk.cpu().numpy(), wk)
+
+
+def _attn_case(torch, cb, nh, nkv, hd, seq, f16, seed):
+    kv_dim = nkv * hd
+    kc = cb.synth_normal(seq * kv_dim, seed=seed, sigma=1.0).reshape(seq, kv_dim)
+    vc = cb.synth_normal(seq * kv_dim, seed=seed + 1, sigma=1.0).reshape(seq, kv_dim)
+    q = cb.synth_normal(nh * hd, seed=seed + 2, sigma=1.0)
+    scale = 1.0 / math.sqrt(hd)
+    if f16:
+        kc, vc = kc.half(), vc.half()
+        kh, vh = kc.cpu().numpy().view(np.uint16), vc.cpu().numpy().view(np.uint16)
+    else:
+        kh, vh = kc.cpu().numpy(), vc.cpu().numpy()
+    got = cb.decode_attention(q, kc, vc, nh, nkv, hd, seq, scale).cpu().numpy()
+    want = O.decode_attention(q.cpu().numpy(), kh, vh, nh, nkv, hd, seq, scale)
+    assert_close(got, want, f"seq={seq} f16={f16}")
+
+
+@pytest.mark.parametrize("f16", [False, True])
+@pytest.mark.parametrize("seq", [1, 7, 8, 63, 65, 512, 1000, 4096])
+def test_decode_attention_llama_shape(seq, f16):
+    torch = need_gpu()
+    import cera_b200 as cb
+    _attn_case(torch, cb, 32, 8, 128, seq, f16, seed=100 + seq)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (16, 2, 128), (8, 1, 64)])
+def test_decode_attention_other_groupings(nh, nkv, hd):
+    torch = need_gpu()
+    import cera_b200 as cb
+    _attn_case(torch, cb, nh, nkv, hd, 300, False, seed=7)
+
+
+def test_decode_attention_16k():
+    torch = need_gpu()
+    import cera_b200 as cb
+    _attn_case(torch, cb, 32, 8, 128, 16384, False, seed=5)
+
+
+def test_decode_attention_rejects_unsupported_shapes():
+    torch = need_gpu()
+    import cera_b200 as cb
+    q = torch.zeros(6 * 64, device="cuda")
+    kc = torch.zeros(4, 2 * 64, device="cuda")
+    with pytest.raises(cb.CeraCudaError) as e:
+        cb.decode_attention(q, kc, kc, 6, 2, 64, 4, 0.125)
+    assert e.value.code == 2

@@ -1,0 +1,167 @@
+"""CUDA quantizer / GEMV / GEMM against the oracle.
+
+Bit-exact: Q8_0 activation bytes and scales, per-half-block int32 sums.
+Toleranced (1e-3 rel / 1e-4 abs): every f32 output.
+"""
+import numpy as np
+import pytest
+
+import oracle_lib as O
+import ref_fixtures as R
+from gpu_util import assert_bits, assert_close, need_gpu
+from test_oracle_formats import _rand_block_bytes
+
+pytestmark = pytest.mark.gpu
+
+
+def _cuda(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def test_quantizer_bit_exact_incl_corner_blocks():
+    torch = need_gpu()
+    import cera_b200 as cb
+    rng = np.random.default_rng(0)
+    x = (rng.standard_normal(4096) * 3).astype(np.float32)
+    # corner blocks from cera/src/backend/simd.rs:7872-7946
+    x[0:32] = 0.0
+    for b, amax in enumerate((1e-30, 1e-38, 1e-40, 1e-44), start=1):
+        x[32 * b:32 * b + 32] = 0.0
+        x[32 * b], x[32 * b + 1], x[32 * b + 2] = amax, -amax, np.float32(amax) / np.float32(2)
+    x[160:192] = 0.25
+    x[160], x[161] = np.nan, -1.0
+    x[192:224] = 0.25
+    x[192], x[193] = np.inf, -1.0
+    a = cb.quantize_q8_0(_cuda(torch, x))
+    ws, wq = O.quantize_q8_0(x)
+    assert_bits(a.quants.cpu().numpy(), wq, "quants")
+    assert_bits(a.scales.cpu().numpy(), ws, "scales")
+    sums = wq.astype(np.int32).reshape(-1, 16).sum(axis=1).astype(np.int16)
+    assert_bits(a.sums.cpu().numpy(), sums, "sums")
+
+
+def test_quantize_columns_matches_oracle():
+    torch = need_gpu()
+    import cera_b200 as cb
+    rng = np.random.default_rng(1)
+    dim, n = 256, 9
+    mat = rng.standard_normal((dim, n)).astype(np.float32)
+    a = cb.quantize_columns(_cuda(torch, mat), dim, n)
+    ws, wq = O.quantize_columns(mat, dim, n)
+    assert_bits(a.quants.cpu().numpy(), wq)
+    assert_bits(a.scales.cpu().numpy(), ws)
+
+
+@pytest.mark.parametrize("t", O.QUANT_TYPES)
+def test_block_sums_bit_exact(t):
+    torch = need_gpu()
+    import cera_b200 as cb
+    rng = np.random.default_rng(40 + t)
+    m, k = 3, 1024
+    raw = _rand_block_bytes(t, m, k, rng)
+    if t == O.Q8_0:  # force the -128 weight extreme of the reference's fixtures
+        raw.reshape(-1, 34)[:, 2:4] = 0x80
+    aq = rng.integers(-127, 128, size=k, dtype=np.int8)
+    aq[0:4] = (127, 127, -127, -127)
+    w = cb.QuantWeight(t, m, k, raw)
+    rb = O.row_bytes(t, k)
+    for row in range(m):
+        u, a = cb.block_sums(w, row, _cuda(torch, aq))
+        wu, wa = O.block_sums(t, raw[row * rb:(row + 1) * rb], k, aq)
+        assert_bits(u.cpu().numpy(), wu, f"{O.NAMES[t]} u row {row}")
+        assert_bits(a.cpu().numpy(), wa, f"{O.NAMES[t]} a row {row}")
+
+
+@pytest.mark.parametrize("t", O.QUANT_TYPES)
+@pytest.mark.parametrize("m,k", [(7, 512), (1, 256), (33, 4096), (130, 1024)])
+def test_gemv_matches_oracle(t, m, k):
+    torch = need_gpu()
+    import cera_b200 as cb
+    rng = np.random.default_rng(1000 * t + m)
+    w32 = O.synth_normal(m * k, seed=t * 7 + m, sigma=0.02)
+    raw = O.quantize_weights(t, w32)
+    x = rng.standard_normal(k).astype(np.float32)
+    w = cb.QuantWeight(t, m, k, raw)
+    got = cb.gemv(w, _cuda(torch, x)).cpu().numpy()
+    if t == O.Q5_K:
+        # the Q8_0-activation Q5_K kernel is an extension: oracle = restated integer form
+        xs, xq = O.quantize_q8_0(x)
+        want = O.gemm_preq(t, raw, xs, xq, m, 1, k).ravel()
+    else:
+        want = O.gemv(t, raw, x, m, k)
+    assert_close(got, want, f"{O.NAMES[t]} {m}x{k}")
+
+
+def test_gemv_q5k_f32_matches_reference_semantics():
+    torch = need_gpu()
+    import cera_b200 as cb
+    m, k = 19, 1024
+    raw = O.quantize_weights(O.Q5_K, O.synth_normal(m * k, seed=5, sigma=0.02))
+    x = np.random.default_rng(5).standard_normal(k).astype(np.float32)
+    w = cb.QuantWeight(O.Q5_K, m, k, raw)
+    got = cb.gemv_q5k_f32(w, _cuda(torch, x)).cpu().numpy()
+    assert_close(got, O.gemv(O.Q5_K, raw, x, m, k), "q5_k f32 activations")
+    # and the Q8_0 extension agrees with it up to activation-quantisation noise
+    ext = cb.gemv(w, _cuda(torch, x)).cpu().numpy()
+    assert np.abs(ext - got).max() < 0.02 * np.abs(got).max()
+
+
+def test_config1_q4_0_gemv_4096():
+    """BASELINE config 1: W 4096x4096 N(0,0.02) seed 0 -> Q4_0, x N(0,1) seed 1."""
+    torch = need_gpu()
+    import cera_b200 as cb
+    m = k = 4096
+    w32 = cb.synth_normal(m * k, seed=0, sigma=0.02)
+    raw = cb.quantize_weights(O.Q4_0, w32)
+    x = cb.synth_normal(k, seed=1, sigma=1.0)
+    w = cb.QuantWeight(O.Q4_0, m, k, raw)
+    got = cb.gemv(w, x).cpu().numpy()
+    want = O.gemv(O.Q4_0, raw.cpu().numpy(), x.cpu().numpy(), m, k, avx2=O.has_avx2(), threads=4)
+    assert_close(got, want, "config 1")
+
+
+@pytest.mark.parametrize("t", O.QUANT_TYPES)
+@pytest.mark.parametrize("n", [1, 2, 3, 5, 8, 9, 17])
+def test_gemm_preq_matches_oracle(t, n):
+    torch = need_gpu()
+    import cera_b200 as cb
+    m, k = 21, 512
+    raw = O.quantize_weights(t, O.synth_normal(m * k, seed=t + 100 * n, sigma=0.02))
+    X = np.random.default_rng(n).standard_normal((n, k)).astype(np.float32)
+    acts = cb.quantize_q8_0(_cuda(torch, X), k=k, n=n)
+    w = cb.QuantWeight(t, m, k, raw)
+    out = torch.full((m, n), float("nan"), device="cuda")  # poison: unwritten cells must show
+    got = cb.gemm_preq(w, acts, out).cpu().numpy()
+    bs, bq = O.quantize_columns(X.T.copy(), k, n)
+    want = O.gemm_preq(t, raw, bs, bq, m, n, k)
+    assert_close(got, want, f"{O.NAMES[t]} n={n}")
+
+
+def test_gemm_on_reference_fixtures():
+    """The reference's own extreme fixtures (-128 weights, +/-127 activations)."""
+    torch = need_gpu()
+    import cera_b200 as cb
+    k = 128
+    for m, n in [(9, 7), (8, 8), (3, 2), (16, 5)]:
+        rng = R.Lcg(0x77AA33CC)
+        q4 = R.q4_0_rows(m, k, rng)
+        q8 = R.q8_0_rows_with_extremes(m, k, rng)
+        bs, bq = R.activations(n, k, rng)
+        acts = cb.Q8Activations(k, n)
+        acts.scales.copy_(_cuda(torch, bs))
+        acts.quants.copy_(_cuda(torch, bq))
+        acts.sums.copy_(_cuda(torch, bq.astype(np.int32).reshape(-1, 16).sum(axis=1).astype(np.int16)))
+        for t, raw, is4 in ((O.Q4_0, q4, True), (O.Q8_0, q8, False)):
+            got = cb.gemm_preq(cb.QuantWeight(t, m, k, raw), acts).cpu().numpy()
+            want = R.ref_gemm(raw, bs, bq, m, n, k, is4)
+            assert np.all(np.abs(got - want) <= 1e-5 * np.maximum(np.abs(want), 1.0)), (t, m, n)
+
+
+def test_gemm_preq_declines_loudly():
+    torch = need_gpu()
+    import cera_b200 as cb
+    raw = O.quantize_weights(O.Q4_0, O.synth_normal(4 * 64, seed=1, sigma=0.02))
+    w = cb.QuantWeight(O.Q4_0, 4, 64, raw)
+    acts = cb.quantize_q8_0(torch.zeros(128, device="cuda"), k=128, n=1)
+    with pytest.raises(cb.CeraCudaError):
+        cb.gemm_preq(w, acts)

@@ -1,0 +1,105 @@
+"""Whole-model decode on the CUDA device against the oracle's llama forward."""
+import numpy as np
+import pytest
+
+import oracle_lib as O
+from gpu_util import assert_close, need_gpu
+
+pytestmark = pytest.mark.gpu
+
+SMALL = dict(n_layers=2, hidden_size=256, intermediate_size=512, n_heads=4, n_kv_heads=1, head_dim=64, vocab_size=512,
+             rope_theta=500000.0, rms_norm_eps=1e-5, rope_type=0)
+
+
+def _pair(cfg, seed, kv_f16=0, max_seq_len=64, types=None, threads=2):
+    from cera_b200 import synth
+    oracle = O.OracleModel(**{k: cfg[k] for k in ("n_layers", "hidden_size", "intermediate_size", "n_heads",
+                                                   "n_kv_heads", "head_dim", "vocab_size", "rope_theta",
+                                                   "rms_norm_eps", "rope_type")},
+                           max_seq_len=max_seq_len, kv_f16=kv_f16, n_threads=threads)
+
+    def sink(role, layer, t, rows, cols, data):
+        oracle.set_tensor(int(role), layer, t, rows, cols, data)
+
+    gpu = synth.build_llama(cfg, seed=seed, sink=sink, types=types, max_seq_len=max_seq_len, kv_f16=kv_f16)
+    return gpu, oracle
+
+
+@pytest.mark.parametrize("kv_f16", [0, 1])
+def test_small_llama_logits_and_greedy_stream(kv_f16):
+    need_gpu()
+    from cera_b200 import synth
+    gpu, oracle = _pair(SMALL, seed=3, kv_f16=kv_f16)
+    prompt = synth.prompt_tokens(8, SMALL["vocab_size"], seed=1)
+    tok_g = tok_o = None
+    for pos, t in enumerate(prompt):
+        lg = gpu.forward(int(t), pos)
+        lo = oracle.forward(int(t), pos)
+        assert_close(lg, lo, f"logits at pos {pos}")
+        assert_close(gpu.last_hidden(), oracle.last_hidden(), f"hidden at pos {pos}")
+    tok_g, tok_o = int(O.argmax(lg)), int(O.argmax(lo))
+    stream_g, stream_o = [], []
+    pos = len(prompt)
+    for _ in range(24):
+        assert tok_g == tok_o, (stream_g, stream_o)
+        ng = gpu.forward_greedy(tok_g, pos)
+        lo = oracle.forward(tok_o, pos)
+        no = int(O.argmax(lo))
+        stream_g.append(ng)
+        stream_o.append(no)
+        tok_g, tok_o, pos = ng, no, pos + 1
+    assert stream_g == stream_o
+    assert gpu.seq_len == oracle.seq_len == pos
+    assert gpu.launch_count() > 0 and gpu.gpu_memory_bytes() > 0
+
+
+def test_prefill_equals_per_token_forward_and_truncate():
+    need_gpu()
+    from cera_b200 import synth
+    gpu, oracle = _pair(SMALL, seed=5)
+    prompt = synth.prompt_tokens(12, SMALL["vocab_size"], seed=2)
+    lp = gpu.forward_prefill(prompt, 0)
+    for pos, t in enumerate(prompt):
+        lo = oracle.forward(int(t), pos)
+    assert_close(lp, lo, "prefill last logits")
+    # rewind and replay: same logits again (truncate_kv moves the device counter)
+    gpu.truncate_kv(6)
+    assert gpu.seq_len == 6
+    again = gpu.forward_prefill(prompt[6:], 6)
+    assert np.array_equal(again, lp)
+
+
+def test_model_contract_errors():
+    need_gpu()
+    import cera_b200 as cb
+    from cera_b200 import synth
+    gpu, _ = _pair(SMALL, seed=7, max_seq_len=4)
+    with pytest.raises(cb.CeraCudaError) as e:
+        gpu.forward(1, 3)  # pos != seq_len
+    assert e.value.code == 7
+    with pytest.raises(cb.CeraCudaError):
+        gpu.forward(SMALL["vocab_size"], 0)
+    for p in range(4):
+        gpu.forward(1, p)
+    with pytest.raises(cb.CeraCudaError):
+        gpu.forward(1, 4)  # beyond max_seq_len
+    m = cb.CudaModel(**SMALL, max_seq_len=8)
+    with pytest.raises(cb.CeraCudaError):
+        m.finalize()  # tensors missing
+    with pytest.raises(cb.CeraCudaError) as e:
+        m.add_tensor(cb.Role.ATTN_NORM, 0, cb.Q4_0, 1, 256, np.zeros(144, dtype=np.uint8))
+    assert e.value.code == 2
+
+
+def test_mixed_type_layers():
+    """Q4_0 / Q8_0 / Q4_1 / Q5_K tensors in one model take the unfused launch paths."""
+    need_gpu()
+    import cera_b200 as cb
+    from cera_b200 import synth
+    types = {cb.Role.ATTN_Q: cb.Q4_0, cb.Role.ATTN_K: cb.Q8_0, cb.Role.ATTN_V: cb.Q6_K, cb.Role.ATTN_OUTPUT: cb.Q4_1,
+             cb.Role.FFN_GATE: cb.Q4_K, cb.Role.FFN_UP: cb.Q4_0, cb.Role.FFN_DOWN: cb.Q8_0, cb.Role.TOKEN_EMBD: cb.Q8_0,
+             cb.Role.OUTPUT: cb.Q4_K}
+    gpu, oracle = _pair(SMALL, seed=11, types=types)
+    prompt = synth.prompt_tokens(5, SMALL["vocab_size"], seed=4)
+    for pos, t in enumerate(prompt):
+        assert_close(gpu.forward(int(t), pos), oracle.forward(int(t), pos), f"pos {pos}")
