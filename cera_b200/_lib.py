@@ -14,7 +14,7 @@ class CeraCudaError(RuntimeError):
 
 if not os.path.exists(_PATH):
     raise ImportError(
-        f"{_PATH} is missing: build it with `python -m cera_b200.build` (needs nvcc). "
+        f"{_PATH} is missing: build it with `python cera_b200/build.py` (needs nvcc). "
         "cera_b200 has no CPU fallback.")
 
 lib = C.CDLL(_PATH)
@@ -55,6 +55,7 @@ SIGNATURES = {
     "cera_cuda_model_finalize": (_i32, [_p]),
     "cera_cuda_forward": (_i32, [_p, _u32, _sz, _p]),
     "cera_cuda_forward_greedy": (_i32, [_p, _u32, _sz, C.POINTER(_u32)]),
+    "cera_cuda_generate_greedy": (_i32, [_p, _u32, _sz, _sz, _p, C.POINTER(_f)]),
     "cera_cuda_forward_prefill": (_i32, [_p, _p, _sz, _sz, _p]),
     "cera_cuda_truncate_kv": (_i32, [_p, _sz]),
     "cera_cuda_seq_len": (_sz, [_p]),
@@ -65,7 +66,10 @@ SIGNATURES = {
 }
 
 for _name, (_res, _args) in SIGNATURES.items():
-    _fn = getattr(lib, _name)  # AttributeError here = the library does not export a declared symbol
+    try:
+        _fn = getattr(lib, _name)
+    except AttributeError as e:  # the library does not export a declared symbol: stale build
+        raise ImportError(f"{_PATH} does not export {_name}: rebuild it with `python cera_b200/build.py`") from e
     _fn.restype = _res
     _fn.argtypes = _args
 

@@ -1,7 +1,8 @@
 """Build libcera_cuda.so (sm_100a) from cera_b200/csrc with nvcc.
 
 The library is built in-tree so that it travels with the source tree; nothing
-is JIT-compiled at import time.  `python -m cera_b200.build [--force] [-v]`.
+is JIT-compiled at import time.  Run it by path, `python cera_b200/build.py [--force] [-v]`:
+importing the package itself requires the library to exist already.
 """
 import concurrent.futures
 import os

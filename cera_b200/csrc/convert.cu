@@ -39,10 +39,8 @@ __device__ __forceinline__ float sclamp(float v, float lo, float hi) {
     if (v > hi) return hi;
     return v;
 }
-__device__ __forceinline__ void put16(uint8_t *p, uint16_t v) {
-    p[0] = (uint8_t)(v & 0xFF);
-    p[1] = (uint8_t)(v >> 8);
-}
+// Every block size and every f16 field offset is even, so the field is 2-byte aligned.
+__device__ __forceinline__ void put16(uint8_t *p, uint16_t v) { *reinterpret_cast<uint16_t *>(p) = v; }
 
 __device__ void wq_q8_0(const float *in, uint8_t *out) {
     float amax = 0.0f;

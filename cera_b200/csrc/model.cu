@@ -40,7 +40,7 @@ struct Layer {
     void *kc = nullptr, *vc = nullptr;
 };
 
-enum GraphKind { G_BODY = 0, G_LOGITS = 1, G_GREEDY = 2 };
+enum GraphKind { G_BODY = 0, G_LOGITS = 1, G_GREEDY = 2, G_CHAIN = 3 };
 
 }  // namespace
 
@@ -69,7 +69,9 @@ struct cera_cuda_model {
     std::map<uint32_t, cudaGraphExec_t> graphs;  // key = kind | n_splits << 8
     size_t seq_len = 0;
     uint64_t launches = 0;         // kernels launched by decode steps
-    uint32_t nodes_per_step[3] = {0, 0, 0};
+    uint32_t nodes_per_step[4] = {0, 0, 0, 0};
+    uint32_t *tok_hist = nullptr;  // device ring of generated tokens (chained greedy decode)
+    uint32_t tok_hist_cap = 0;
 };
 
 namespace {
@@ -86,6 +88,17 @@ int32_t alloc_act(cera_cuda_model *m, ActBuf &a, size_t k) {
     CERA_TRY(dev_alloc(m, (void **)&a.quants, k));
     CERA_TRY(dev_alloc(m, (void **)&a.sums, k / 16 * 2));
     return CERA_CUDA_OK;
+}
+
+// After the argmax of a chained step: record the token, make it the next input, advance
+// the position.  dyn = {token, pos, seq_len, step}.
+__global__ void advance_kernel(uint32_t *dyn, const uint32_t *tok_out, uint32_t *hist, uint32_t cap) {
+    const uint32_t t = *tok_out, step = dyn[3];
+    if (step < cap) hist[step] = t;
+    dyn[0] = t;
+    dyn[1] += 1;
+    dyn[2] += 1;
+    dyn[3] = step + 1;
 }
 
 // Enqueue one decode step on m->stream; token / position come from m->dyn.
@@ -135,7 +148,13 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
     const cera_cuda_weight *ow = m->output ? m->output : m->embd;
     GemvSeg sl{ow->v, m->logits};
     CERA_TRY(launch_gemv(&sl, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
-    if (kind == G_GREEDY) CERA_TRY(launch_argmax(m->logits, c.vocab_size, m->tok_out, m->argmax_scratch, st));
+    if (kind == G_GREEDY || kind == G_CHAIN)
+        CERA_TRY(launch_argmax(m->logits, c.vocab_size, m->tok_out, m->argmax_scratch, st));
+    if (kind == G_CHAIN) {
+        advance_kernel<<<1, 1, 0, st>>>(m->dyn, m->tok_out, m->tok_hist, m->tok_hist_cap);
+        count_launch();
+        CERA_CUDA_TRY(cudaGetLastError());
+    }
     return CERA_CUDA_OK;
 }
 
@@ -302,6 +321,8 @@ int32_t cera_cuda_model_finalize(cera_cuda_model *m) {
     CERA_TRY(dev_alloc(m, (void **)&m->argmax_scratch, argmax_scratch_words() * 4));
     CERA_TRY(dev_alloc(m, (void **)&m->dyn, 4 * 4));
     CERA_TRY(dev_alloc(m, (void **)&m->tok_out, 4));
+    m->tok_hist_cap = c.max_seq_len;
+    CERA_TRY(dev_alloc(m, (void **)&m->tok_hist, (size_t)m->tok_hist_cap * 4));
     CERA_CUDA_TRY(cudaMallocHost((void **)&m->h_dyn, 8 * 4));
     CERA_CUDA_TRY(cudaMallocHost((void **)&m->h_logits, (size_t)c.vocab_size * 4));
     CERA_CUDA_TRY(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
@@ -355,6 +376,49 @@ int32_t cera_cuda_forward_prefill(cera_cuda_model *m, const uint32_t *tokens, si
         CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
         memcpy(logits_out, m->h_logits, bytes);
     }
+    return CERA_CUDA_OK;
+}
+
+int32_t cera_cuda_generate_greedy(cera_cuda_model *m, uint32_t first_token, size_t start_pos, size_t n,
+                                  uint32_t *tokens_out, float *device_ms) {
+    if (!m || !tokens_out) return fail(CERA_CUDA_ERR_BAD_ARG, "generate_greedy: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    const auto &c = m->cfg;
+    if (!m->finalized) return fail(CERA_CUDA_ERR_STATE, "generate_greedy: model_finalize has not been called");
+    if (first_token >= c.vocab_size) return fail(CERA_CUDA_ERR_BAD_ARG, "generate_greedy: token out of range");
+    if (start_pos != m->seq_len) return fail(CERA_CUDA_ERR_STATE, "generate_greedy: start_pos %zu != seq_len %zu", start_pos, m->seq_len);
+    if (start_pos + n > c.max_seq_len) return fail(CERA_CUDA_ERR_BAD_ARG, "generate_greedy: %zu tokens from %zu exceed max_seq_len %u", n, start_pos, c.max_seq_len);
+    if (n == 0) return CERA_CUDA_OK;
+    m->h_dyn[0] = first_token;
+    m->h_dyn[1] = (uint32_t)start_pos;
+    m->h_dyn[2] = (uint32_t)start_pos + 1;
+    m->h_dyn[3] = 0;
+    CERA_CUDA_TRY(cudaMemcpyAsync(m->dyn, m->h_dyn, 4 * sizeof(uint32_t), cudaMemcpyHostToDevice, m->stream));
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    CERA_CUDA_TRY(cudaEventCreate(&e0));
+    CERA_CUDA_TRY(cudaEventCreate(&e1));
+    // instantiate every graph the run needs before the timed region
+    for (size_t i = 0; i < n; ++i) {
+        cudaGraphExec_t g = nullptr;
+        CERA_TRY(get_graph(m, G_CHAIN, attn_pick_splits(c.n_kv_heads, start_pos + i + 1), &g));
+    }
+    CERA_CUDA_TRY(cudaEventRecord(e0, m->stream));
+    for (size_t i = 0; i < n; ++i) {
+        cudaGraphExec_t g = nullptr;
+        CERA_TRY(get_graph(m, G_CHAIN, attn_pick_splits(c.n_kv_heads, start_pos + i + 1), &g));
+        CERA_CUDA_TRY(cudaGraphLaunch(g, m->stream));
+    }
+    CERA_CUDA_TRY(cudaEventRecord(e1, m->stream));
+    m->launches += (uint64_t)m->nodes_per_step[G_CHAIN] * n;
+    m->seq_len = start_pos + n;
+    CERA_CUDA_TRY(cudaMemcpyAsync(tokens_out, m->tok_hist, n * 4, cudaMemcpyDeviceToHost, m->stream));
+    CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    float ms = 0.0f;
+    CERA_CUDA_TRY(cudaEventElapsedTime(&ms, e0, e1));
+    if (device_ms) *device_ms = ms;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
     return CERA_CUDA_OK;
 }
 

@@ -65,6 +65,14 @@ class CudaModel:
         check(lib.cera_cuda_forward_greedy(self.handle, token, pos, C.byref(out)))
         return out.value
 
+    def generate_greedy(self, first_token, start_pos, n):
+        """n greedy tokens decoded on the device back to back -> (tokens, device milliseconds)."""
+        out = np.empty(n, dtype=np.uint32)
+        ms = C.c_float()
+        check(lib.cera_cuda_generate_greedy(self.handle, first_token, start_pos, n, out.ctypes.data_as(C.c_void_p),
+                                            C.byref(ms)))
+        return out, ms.value
+
     def forward_prefill(self, tokens, start_pos, want_logits=True):
         tokens = np.ascontiguousarray(tokens, dtype=np.uint32)
         logits = np.empty(self.cfg.vocab_size, dtype=np.float32) if want_logits else None

@@ -26,7 +26,7 @@ def tensor_seed(seed, role, layer):
 def build_llama(cfg, seed=0, sigma=0.02, types=None, sink=None, **model_kw):
     """Create, fill and finalize a CudaModel.  sink(role, layer, ggml_type, rows, cols, host_bytes)
     receives a host copy of every tensor (tests hand these to the CPU oracle)."""
-    types = dict(DEFAULT_TYPES, **(types or {}))
+    types = {**DEFAULT_TYPES, **(types or {})}
     m = CudaModel(**cfg, **model_kw)
     hs, ff = cfg["hidden_size"], cfg["intermediate_size"]
     qd, kvd = cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"]
@@ -67,10 +67,12 @@ def build_llama(cfg, seed=0, sigma=0.02, types=None, sink=None, **model_kw):
 
 def prompt_tokens(n, vocab, seed):
     """Uniform-random token ids, reproducible without numpy's generator state."""
-    x = np.arange(n, dtype=np.uint64) + np.uint64(seed) * np.uint64(0x9E3779B97F4A7C15)
-    x ^= x >> np.uint64(30)
-    x *= np.uint64(0xBF58476D1CE4E5B9)
-    x ^= x >> np.uint64(27)
-    x *= np.uint64(0x94D049BB133111EB)
-    x ^= x >> np.uint64(31)
-    return (x % np.uint64(vocab)).astype(np.uint32)
+    mask = (1 << 64) - 1
+    out = np.empty(n, dtype=np.uint32)
+    for i in range(n):
+        x = (i + seed * 0x9E3779B97F4A7C15 + 0x9E3779B97F4A7C15) & mask
+        x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & mask
+        x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & mask
+        x ^= x >> 31
+        out[i] = x % vocab
+    return out

@@ -216,6 +216,12 @@ CERA_API int32_t cera_cuda_forward(cera_cuda_model *m, uint32_t token, size_t po
  * wins (cera/src/sampler.rs:20-30); 4 bytes come back. */
 CERA_API int32_t cera_cuda_forward_greedy(cera_cuda_model *m, uint32_t token, size_t pos,
                                           uint32_t *token_out);
+/* The greedy loop of Session::generate (cera/src/session.rs:1788-2310, which calls
+ * forward_greedy once per token at 2233) kept on the device: n tokens are decoded
+ * back to back, each argmax feeding the next step without a host round trip.
+ * tokens_out[n] on the host; device_ms (optional) = CUDA-event time of the n steps. */
+CERA_API int32_t cera_cuda_generate_greedy(cera_cuda_model *m, uint32_t first_token, size_t start_pos,
+                                           size_t n, uint32_t *tokens_out, float *device_ms);
 /* Model::forward_prefill (cera/src/model/llama.rs:1607-1649): start_pos must
  * equal seq_len; logits of the last token (may be NULL). */
 CERA_API int32_t cera_cuda_forward_prefill(cera_cuda_model *m, const uint32_t *tokens, size_t n,
