@@ -283,7 +283,7 @@ def cuda_arm(args, rank, world):
     out = None
     if rank == 0:
         hbm, which = measured_peaks()
-        algo, us, roof_launches = roofline_q4k_gemv(torch, cb, iters=200)
+        algo, us, roof_launches = roofline_q4k_gemv(torch, cb, iters=args.iters)
         achieved = algo / (us * 1e-6) / 1e9
         step_gbs = TOKEN_WEIGHT_BYTES / (dev_ms / K * 1e-3) / 1e9
         value = world * K / (dev_ms * 1e-3)
@@ -331,10 +331,21 @@ def main():
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--only", default=None, choices=["roofline"],
+                    help="run just the dominant-kernel microbench (the case ncu captures are taken on)")
+    ap.add_argument("--iters", type=int, default=200, help="timed launches of the kernel microbench")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    if args.impl == "reference":
+    if args.only == "roofline":
+        import torch
+        import cera_b200 as cb
+        algo, us, n = roofline_q4k_gemv(torch, cb, args.iters)
+        hbm, which = measured_peaks()
+        print(json.dumps({"kernel": "gemv_kernel<Q4_K, 1 column> 14336x4096", "us_per_launch": us,
+                          "achieved_gbs": algo / us / 1e3, "frac": algo / us / 1e3 / hbm, "peak_source": which,
+                          "launches": n}))
+    elif args.impl == "reference":
         reference_arm(args, rank)
     else:
         cuda_arm(args, rank, world)
