@@ -41,9 +41,15 @@ uint64_t launches_so_far();
 //   Q4_K : q[m][nb][128]                    hdr[m][nb][16] (d, dmin, scales[12])
 //   Q5_K : q[m][nb][128]  qh[m][nb][32]     hdr[m][nb][16]
 //   Q6_K : q[m][nb][128]  qh[m][nb][64]     sc[m][nb][16]   d[m][nb] (half)
+//
+// Inside a row the low-quant plane is stored PIECE-MAJOR when k is a multiple of 128
+// (t128 = k/128 != 0): the row is cut into 128-weight lane tasks of NP 16-byte pieces
+// (NP = 4, or 8 for Q8_0), and piece c of task t sits at 16*(c*t128 + t).  A warp whose
+// lane t fetches piece c of its own task then reads 512 contiguous bytes per load.
 struct WeightView {
     int32_t type;
     uint32_t m, k, nb;
+    uint32_t t128;       // lane tasks per row, 0 = pieces in GGUF order
     const uint8_t *q;    // low quant plane
     const uint8_t *qh;   // high-bit plane (Q5_K, Q6_K)
     const uint8_t *hdr;  // scale plane (see table)
@@ -68,6 +74,13 @@ __host__ __device__ inline TypeInfo type_info(int t) {
         case CERA_TYPE_BF16: return {1, 2, 2, 0, 0, 0};
         default: return {0, 0, 0, 0, 0, 0};
     }
+}
+
+// Byte offset inside a row's low-quant plane of its i-th 16-byte piece (GGUF order).
+__host__ __device__ inline size_t q_piece_off(uint32_t t128, uint32_t np, uint32_t i) {
+    if (!t128) return (size_t)i * 16;
+    const uint32_t t = i / np, c = i - t * np;
+    return ((size_t)c * t128 + t) * 16;
 }
 
 inline bool is_block_type(int t) {

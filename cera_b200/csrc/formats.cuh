@@ -48,7 +48,7 @@ struct Fmt<CERA_TYPE_Q4_0> {
     __device__ static Raw load(const WeightView &w, size_t row, int item) {
         const size_t b = row * w.nb + item;
         Raw r;
-        r.q = ld_stream(w.q + b * 16);
+        r.q = ld_stream(w.q + row * ((size_t)w.nb * 16) + q_piece_off(w.t128, 4, (uint32_t)item));
         r.d = __ldg(reinterpret_cast<const uint16_t *>(w.hdr) + b);
         return r;
     }
@@ -81,7 +81,7 @@ struct Fmt<CERA_TYPE_Q4_1> {
     __device__ static Raw load(const WeightView &w, size_t row, int item) {
         const size_t b = row * w.nb + item;
         Raw r;
-        r.q = ld_stream(w.q + b * 16);
+        r.q = ld_stream(w.q + row * ((size_t)w.nb * 16) + q_piece_off(w.t128, 4, (uint32_t)item));
         r.dm = __ldg(reinterpret_cast<const uint32_t *>(w.hdr) + b);
         return r;
     }
@@ -115,8 +115,9 @@ struct Fmt<CERA_TYPE_Q8_0> {
     __device__ static Raw load(const WeightView &w, size_t row, int item) {
         const size_t b = row * w.nb + item;
         Raw r;
-        r.q0 = ld_stream(w.q + b * 32);
-        r.q1 = ld_stream(w.q + b * 32 + 16);
+        const uint8_t *rq = w.q + row * ((size_t)w.nb * 32);
+        r.q0 = ld_stream(rq + q_piece_off(w.t128, 8, 2u * item));
+        r.q1 = ld_stream(rq + q_piece_off(w.t128, 8, 2u * item + 1));
         r.d = __ldg(reinterpret_cast<const uint16_t *>(w.hdr) + b);
         return r;
     }
@@ -162,7 +163,7 @@ struct Fmt<CERA_TYPE_Q4_K> {
     __device__ static Raw load(const WeightView &w, size_t row, int item) {
         const size_t sb = row * w.nb + (item >> 3);
         Raw r;
-        r.q = ld_stream(w.q + sb * 128 + (item & 7) * 16);
+        r.q = ld_stream(w.q + row * ((size_t)w.nb * 128) + q_piece_off(w.t128, 4, (uint32_t)item));
         r.h = __ldg(reinterpret_cast<const uint4 *>(w.hdr) + sb);
         return r;
     }
@@ -199,7 +200,7 @@ struct Fmt<CERA_TYPE_Q5_K> {
     __device__ static Raw load(const WeightView &w, size_t row, int item) {
         const size_t sb = row * w.nb + (item >> 3);
         Raw r;
-        r.q = ld_stream(w.q + sb * 128 + (item & 7) * 16);
+        r.q = ld_stream(w.q + row * ((size_t)w.nb * 128) + q_piece_off(w.t128, 4, (uint32_t)item));
         r.qh = __ldg(reinterpret_cast<const uint4 *>(w.qh + sb * 32 + (item & 1) * 16));
         r.h = __ldg(reinterpret_cast<const uint4 *>(w.hdr) + sb);
         return r;
@@ -240,7 +241,7 @@ struct Fmt<CERA_TYPE_Q6_K> {
         const size_t sb = row * w.nb + (item >> 3);
         const int c = item & 7;
         Raw r;
-        r.q = ld_stream(w.q + sb * 128 + c * 16);
+        r.q = ld_stream(w.q + row * ((size_t)w.nb * 128) + q_piece_off(w.t128, 4, (uint32_t)item));
         r.qh = __ldg(reinterpret_cast<const uint4 *>(w.qh + sb * 64 + (c >> 2) * 32 + (c & 1) * 16));
         r.sc = __ldg(reinterpret_cast<const uint4 *>(w.hdr) + sb);
         r.d = __ldg(reinterpret_cast<const uint16_t *>(w.d) + sb);

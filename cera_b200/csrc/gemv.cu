@@ -12,6 +12,9 @@
 // exact; the f32 combination order is this kernel's own (per-lane sequential
 // fma over the lane's items, then an xor-shuffle tree), within the path's f32
 // tolerance of any of the reference's three orders.
+#include <cstdlib>
+#include <cstring>
+
 #include "formats.cuh"
 #include "ops.h"
 #include "weight.h"
@@ -173,10 +176,24 @@ int32_t launch_cols(const GemvParams &p, size_t n_cols, cudaStream_t st) {
 
 }  // namespace
 
+// CERA_CUDA_GEMV=direct keeps every GEMV on the item-wise kernel (A/B runs); read once.
+static bool force_direct() {
+    static const bool v = [] {
+        const char *e = getenv("CERA_CUDA_GEMV");
+        return e && strcmp(e, "direct") == 0;
+    }();
+    return v;
+}
+
 // All segments must share the type and k.  n_cols in {1,2,4,8}.
 int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_cols, size_t ldy, int epilogue,
                     cudaStream_t st) {
     if (n_segs < 1 || n_segs > MAX_SEGS) return fail(CERA_CUDA_ERR_BAD_ARG, "gemv: %d segments", n_segs);
+    if (n_cols == 1 && ldy == 1 && !force_direct()) {
+        bool taken = false;
+        CERA_TRY(launch_gemv_rows(segs, n_segs, x, epilogue, st, &taken));
+        if (taken) return CERA_CUDA_OK;
+    }
     GemvParams p{};
     uint32_t rows = 0;
     for (int i = 0; i < n_segs; ++i) {

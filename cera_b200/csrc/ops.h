@@ -23,6 +23,9 @@ struct GemvSeg {
 enum { EPI_STORE = 0, EPI_ADD = 1 };
 int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_cols, size_t ldy, int epilogue,
                     cudaStream_t st);
+// Register-resident-activation single-column GEMV.  *taken = false: shape outside its rules,
+// nothing was launched and the caller uses the item-wise kernel.
+int32_t launch_gemv_rows(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, cudaStream_t st, bool *taken);
 int32_t launch_gemm(const WeightView &w, const ActView &x, size_t n, float *out, cudaStream_t st);
 int32_t launch_gemv_q5k_f32(const WeightView &w, const float *x, float *y, cudaStream_t st);
 

@@ -12,8 +12,8 @@ namespace {
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // One thread per GGUF block: scatter its fields into the planes.
-__global__ void repack_kernel(int type, const uint8_t *__restrict__ raw, size_t n_blocks, uint8_t *q, uint8_t *qh,
-                              uint8_t *hdr, uint8_t *d) {
+__global__ void repack_kernel(int type, const uint8_t *__restrict__ raw, size_t n_blocks, uint32_t nb, uint32_t t128,
+                              uint8_t *q, uint8_t *qh, uint8_t *hdr, uint8_t *d) {
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n_blocks) return;
     const TypeInfo ti = type_info(type);
@@ -21,30 +21,38 @@ __global__ void repack_kernel(int type, const uint8_t *__restrict__ raw, size_t 
     auto cp = [](uint8_t *dst, const uint8_t *s, int n) {
         for (int i = 0; i < n; ++i) dst[i] = s[i];
     };
+    // low-quant plane: the block's 16-byte pieces go to their (possibly piece-major) slots in the row
+    const size_t row = b / nb;
+    const uint32_t blk = (uint32_t)(b - row * nb);
+    const uint32_t ppb = ti.q_b / 16, np = type == CERA_TYPE_Q8_0 ? 8u : 4u;
+    uint8_t *qrow = q + row * ((size_t)nb * ti.q_b);
+    auto cpq = [&](const uint8_t *s) {
+        for (uint32_t j = 0; j < ppb; ++j) cp(qrow + q_piece_off(t128, np, blk * ppb + j), s + 16 * j, 16);
+    };
     switch (type) {
         case CERA_TYPE_Q4_0:  // d(2) qs(16)
             cp(hdr + b * 2, src, 2);
-            cp(q + b * 16, src + 2, 16);
+            cpq(src + 2);
             break;
         case CERA_TYPE_Q4_1:  // d(2) m(2) qs(16)
             cp(hdr + b * 4, src, 4);
-            cp(q + b * 16, src + 4, 16);
+            cpq(src + 4);
             break;
         case CERA_TYPE_Q8_0:  // d(2) qs(32)
             cp(hdr + b * 2, src, 2);
-            cp(q + b * 32, src + 2, 32);
+            cpq(src + 2);
             break;
         case CERA_TYPE_Q4_K:  // d(2) dmin(2) scales(12) qs(128)
             cp(hdr + b * 16, src, 16);
-            cp(q + b * 128, src + 16, 128);
+            cpq(src + 16);
             break;
         case CERA_TYPE_Q5_K:  // d(2) dmin(2) scales(12) qh(32) qs(128)
             cp(hdr + b * 16, src, 16);
             cp(qh + b * 32, src + 16, 32);
-            cp(q + b * 128, src + 48, 128);
+            cpq(src + 48);
             break;
         case CERA_TYPE_Q6_K:  // ql(128) qh(64) scales(16) d(2)
-            cp(q + b * 128, src, 128);
+            cpq(src);
             cp(qh + b * 64, src + 128, 64);
             cp(hdr + b * 16, src + 192, 16);
             cp(d + b * 2, src + 208, 2);
@@ -137,7 +145,8 @@ int32_t weight_upload(int32_t type, size_t m, size_t k, const void *bytes, size_
         w->xq = (int8_t *)((uint8_t *)w->xs + xs_sz);
         w->xsum = (int16_t *)((uint8_t *)w->xq + xq_sz);
     }
-    w->v = WeightView{type, (uint32_t)m, (uint32_t)k, (uint32_t)nb, q, ti.qh_b ? qh : nullptr, hdr,
+    const uint32_t t128 = k % 128 == 0 ? (uint32_t)(k / 128) : 0u;
+    w->v = WeightView{type, (uint32_t)m, (uint32_t)k, (uint32_t)nb, t128, q, ti.qh_b ? qh : nullptr, hdr,
                       ti.d_b ? d : nullptr};
 
     // Stage the raw blocks on the device, scatter, release the staging copy.
@@ -147,7 +156,7 @@ int32_t weight_upload(int32_t type, size_t m, size_t k, const void *bytes, size_
     if (st == CERA_CUDA_OK) {
         const int threads = 128;
         const size_t grid = (n_blocks + threads - 1) / threads;
-        repack_kernel<<<(unsigned)grid, threads>>>(type, (const uint8_t *)raw, n_blocks, q, qh, hdr, d);
+        repack_kernel<<<(unsigned)grid, threads>>>(type, (const uint8_t *)raw, n_blocks, (uint32_t)nb, t128, q, qh, hdr, d);
         count_launch();
         st = check_cuda(cudaGetLastError(), "repack launch");
         if (st == CERA_CUDA_OK) st = check_cuda(cudaDeviceSynchronize(), "repack");

@@ -92,6 +92,29 @@ def test_gemv_matches_oracle(t, m, k):
     assert_close(got, want, f"{O.NAMES[t]} {m}x{k}")
 
 
+@pytest.mark.parametrize("t", O.QUANT_TYPES)
+@pytest.mark.parametrize("m,k", [(64, 4096), (24, 14336), (128, 1024), (8, 2048), (5, 384), (37, 4096), (40, 11008 // 256 * 256)])
+def test_gemv_rows_kernel_shapes(t, m, k):
+    """Shapes that take the register-resident-activation kernel (k a multiple of 128), ragged m included,
+    and rows shared by several warps (k = 14336)."""
+    torch = need_gpu()
+    import cera_b200 as cb
+    if k % O.BLOCK[t][0]:
+        pytest.skip("k is not a whole number of super-blocks for this format")
+    w32 = cb.synth_normal(m * k, seed=31 * t + m, sigma=0.02)
+    raw = cb.quantize_weights(t, w32).cpu().numpy()
+    x = cb.synth_normal(k, seed=m + k, sigma=1.0)
+    w = cb.QuantWeight(t, m, k, raw)
+    got = cb.gemv(w, x).cpu().numpy()
+    xh = x.cpu().numpy()
+    if t == O.Q5_K:
+        xs, xq = O.quantize_q8_0(xh)
+        want = O.gemm_preq(t, raw, xs, xq, m, 1, k).ravel()
+    else:
+        want = O.gemv(t, raw, xh, m, k, avx2=O.has_avx2(), threads=4)
+    assert_close(got, want, f"{O.NAMES[t]} {m}x{k}")
+
+
 def test_gemv_q5k_f32_matches_reference_semantics():
     torch = need_gpu()
     import cera_b200 as cb

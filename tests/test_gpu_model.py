@@ -11,6 +11,11 @@ SMALL = dict(n_layers=2, hidden_size=256, intermediate_size=512, n_heads=4, n_kv
              rope_theta=500000.0, rms_norm_eps=1e-5, rope_type=0)
 
 
+# wide enough (k >= 1024) for every projection to take the lane-task GEMV kernel, fused segments included
+WIDE = dict(n_layers=2, hidden_size=1024, intermediate_size=2048, n_heads=8, n_kv_heads=2, head_dim=128,
+            vocab_size=1024, rope_theta=500000.0, rms_norm_eps=1e-5, rope_type=0)
+
+
 def _pair(cfg, seed, kv_f16=0, max_seq_len=64, types=None, threads=2):
     from cera_b200 import synth
     oracle = O.OracleModel(**{k: cfg[k] for k in ("n_layers", "hidden_size", "intermediate_size", "n_heads",
@@ -75,6 +80,30 @@ def test_prefill_equals_per_token_forward_and_truncate():
     assert gpu.seq_len == 6
     again = gpu.forward_prefill(prompt[6:], 6)
     assert np.array_equal(again, lp)
+
+
+def test_wide_llama_matches_oracle():
+    need_gpu()
+    from cera_b200 import synth
+    gpu, oracle = _pair(WIDE, seed=21, threads=4)
+    prompt = synth.prompt_tokens(6, WIDE["vocab_size"], seed=3)
+    for pos, t in enumerate(prompt):
+        lg, lo = gpu.forward(int(t), pos), oracle.forward(int(t), pos)
+        assert_model_logits(lg, lo, f"pos {pos}")
+        if pos == 0:
+            assert np.abs(lg - lo).max() <= 5e-3 * np.abs(lo).max()
+    tok = int(O.argmax(lo))
+    stream_o, logits_o, stream_g = [], [], []
+    t_o = t_g = tok
+    for i in range(12):
+        lo = oracle.forward(t_o, len(prompt) + i)
+        logits_o.append(lo)
+        t_o = int(O.argmax(lo))
+        stream_o.append(t_o)
+    for i in range(12):
+        t_g = gpu.forward_greedy(t_g, len(prompt) + i)
+        stream_g.append(t_g)
+    assert compare_greedy_streams(stream_g, stream_o, lambda i: logits_o[i]) >= 4
 
 
 def test_generate_greedy_equals_stepwise_greedy():
