@@ -65,6 +65,8 @@ attn_split_kernel(const float *__restrict__ q, const void *__restrict__ kc, cons
                   float *__restrict__ ws) {
     constexpr int HD = VEC * 32;
     constexpr int P = 32 / G;  // positions per warp tile
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t kvh = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
     const uint32_t seq_len = seq_len_dev ? *seq_len_dev : seq_len_imm;
@@ -188,6 +190,8 @@ attn_split_kernel(const float *__restrict__ q, const void *__restrict__ kc, cons
 // One CTA per query head, one thread per output dim.
 __global__ void attn_merge_kernel(const float *__restrict__ ws, uint32_t n_splits, uint32_t hd, float *__restrict__ out,
                                   float *scales, int8_t *quants, int16_t *sums) {
+    pdl_trigger();
+    pdl_wait();
     const uint32_t h = blockIdx.x, d = threadIdx.x;
     const float *base = ws + (size_t)h * n_splits * (hd + 2);
     float M = -INFINITY;
@@ -218,10 +222,10 @@ template <int VEC, int G>
 int32_t launch_split(bool f16, dim3 grid, cudaStream_t st, const float *q, const void *kc, const void *vc,
                      uint32_t seq_len, const uint32_t *seq_dev, uint32_t n_kv, float scale, float *ws) {
     if (f16)
-        attn_split_kernel<VEC, G, true><<<grid, ATT_WARPS * 32, 0, st>>>(q, kc, vc, seq_len, seq_dev, n_kv, scale, ws);
-    else
-        attn_split_kernel<VEC, G, false><<<grid, ATT_WARPS * 32, 0, st>>>(q, kc, vc, seq_len, seq_dev, n_kv, scale, ws);
-    return CERA_CUDA_OK;
+        return check_cuda(launch_k(attn_split_kernel<VEC, G, true>, grid, dim3(ATT_WARPS * 32), 0, st, q, kc, vc, seq_len,
+                                   seq_dev, n_kv, scale, ws), "attention launch");
+    return check_cuda(launch_k(attn_split_kernel<VEC, G, false>, grid, dim3(ATT_WARPS * 32), 0, st, q, kc, vc, seq_len,
+                               seq_dev, n_kv, scale, ws), "attention launch");
 }
 
 }  // namespace
@@ -257,8 +261,9 @@ int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *v
     float *ws = (float *)workspace;
     const bool f16 = kv_f16 != 0;
     const uint32_t sl = (uint32_t)seq_len, nkv = (uint32_t)n_kv_heads;
-#define CERA_ATT(VEC, GG) launch_split<VEC, GG>(f16, grid, st, q, kc, vc, sl, seq_len_dev, nkv, scale, ws)
+#define CERA_ATT(VEC, GG) att_status = launch_split<VEC, GG>(f16, grid, st, q, kc, vc, sl, seq_len_dev, nkv, scale, ws)
     bool ok = true;
+    int32_t att_status = CERA_CUDA_OK;
     if (head_dim == 128) {
         switch (G) {
             case 4: CERA_ATT(4, 4); break;
@@ -279,11 +284,11 @@ int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *v
         return fail(CERA_CUDA_ERR_UNSUPPORTED, "decode_attention: head_dim %zu with group size %zu has no kernel "
                     "(head_dim 64 or 128, group 4 or 8)", head_dim, G);
     count_launch();
-    CERA_CUDA_TRY(cudaGetLastError());
-    attn_merge_kernel<<<(unsigned)n_heads, (unsigned)head_dim, 0, st>>>(ws, n_splits, (uint32_t)head_dim, out, scales,
-                                                                       quants, sums);
+    CERA_TRY(att_status);
     count_launch();
-    return check_cuda(cudaGetLastError(), "attention merge launch");
+    return check_cuda(launch_k(attn_merge_kernel, dim3((unsigned)n_heads), dim3((unsigned)head_dim), 0, st,
+                               (const float *)ws, n_splits, (uint32_t)head_dim, out, scales, quants, sums),
+                      "attention merge launch");
 }
 
 int32_t launch_decode_attention(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,

@@ -118,6 +118,32 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// ---- programmatic dependent launch ----------------------------------------------
+// Every kernel of the decode step begins with pdl_trigger() (the next kernel in the stream may be
+// scheduled and run the part of its code that precedes its own pdl_wait()) and calls pdl_wait()
+// before it first touches anything an earlier kernel wrote, and before its own first write.  Weight
+// bytes are immutable, so a GEMV prefetches its first rows ahead of the wait.  Both are no-ops when
+// the kernel was launched without the attribute.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool pdl_enabled();  // CERA_CUDA_PDL=0 turns the launch attribute off (read once)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- launch geometry ----------------------------------------------------------
 int sm_count();  // SMs of the current device (148 on B200), cached
 

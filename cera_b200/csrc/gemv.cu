@@ -77,6 +77,8 @@ __device__ __forceinline__ void accumulate_item(const typename Fmt<T>::Raw &raw,
 template <int T, int NC, int UNROLL>
 __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
     using F = Fmt<T>;
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const uint32_t warp = blockIdx.x * WARPS + (threadIdx.x >> 5);
     const uint32_t n_warps = gridDim.x * WARPS;
@@ -155,12 +157,9 @@ int32_t launch_typed(const GemvParams &p, cudaStream_t st) {
     const uint32_t ctas_needed = (p.total_rows + WARPS - 1) / WARPS;
     const uint32_t cap = (uint32_t)sm_count() * 8;
     const uint32_t grid = ctas_needed < cap ? ctas_needed : cap;
-    if (p.k >= 4096)
-        gemv_kernel<T, NC, 4><<<grid, WARPS * 32, 0, st>>>(p);
-    else
-        gemv_kernel<T, NC, 1><<<grid, WARPS * 32, 0, st>>>(p);
     count_launch();
-    return check_cuda(cudaGetLastError(), "gemv launch");
+    if (p.k >= 4096) return check_cuda(launch_k(gemv_kernel<T, NC, 4>, dim3(grid), dim3(WARPS * 32), 0, st, p), "gemv launch");
+    return check_cuda(launch_k(gemv_kernel<T, NC, 1>, dim3(grid), dim3(WARPS * 32), 0, st, p), "gemv launch");
 }
 
 template <int T>
@@ -191,7 +190,7 @@ int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_
     if (n_segs < 1 || n_segs > MAX_SEGS) return fail(CERA_CUDA_ERR_BAD_ARG, "gemv: %d segments", n_segs);
     if (n_cols == 1 && ldy == 1 && !force_direct()) {
         bool taken = false;
-        CERA_TRY(launch_gemv_rows(segs, n_segs, x, epilogue, st, &taken));
+        CERA_TRY(launch_gemv_rows(segs, n_segs, x, epilogue, nullptr, st, &taken));
         if (taken) return CERA_CUDA_OK;
     }
     GemvParams p{};

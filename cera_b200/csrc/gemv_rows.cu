@@ -40,6 +40,7 @@ struct RowsParams {
     uint32_t k, t128;
     int wpr;  // warps sharing one row: 1, 2, 4 or 8
     int epilogue;
+    GemvFusion f;
 };
 
 // signed x signed and unsigned x signed byte dot products
@@ -83,10 +84,10 @@ template <int T>
 __device__ __forceinline__ void load_act(const ActView &x, uint32_t tau, ActRegs<T> &r) {
     const int4 *q = reinterpret_cast<const int4 *>(x.quants + (size_t)tau * 128);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) r.a[i] = __ldg(q + i);
-    const float4 s = __ldg(reinterpret_cast<const float4 *>(x.scales + (size_t)tau * 4));
+    for (int i = 0; i < 8; ++i) r.a[i] = q[i];
+    const float4 s = *reinterpret_cast<const float4 *>(x.scales + (size_t)tau * 4);
     r.xs[0] = s.x; r.xs[1] = s.y; r.xs[2] = s.z; r.xs[3] = s.w;
-    const int4 sm = __ldg(reinterpret_cast<const int4 *>(x.sums + (size_t)tau * 8));  // 8 int16 half sums
+    const int4 sm = *reinterpret_cast<const int4 *>(x.sums + (size_t)tau * 8);  // 8 int16 half sums
     const int h[8] = {(int16_t)(sm.x & 0xFFFF), sm.x >> 16, (int16_t)(sm.y & 0xFFFF), sm.y >> 16,
                       (int16_t)(sm.z & 0xFFFF), sm.z >> 16, (int16_t)(sm.w & 0xFFFF), sm.w >> 16};
     if (T == CERA_TYPE_Q6_K) {
@@ -251,6 +252,11 @@ __device__ __forceinline__ float task_dot(const Raw<T> &r, const ActRegs<T> &x, 
     }
 }
 
+__device__ __forceinline__ void store_kv(void *cache, int f16, size_t idx, float v) {
+    if (f16) reinterpret_cast<__half *>(cache)[idx] = __float2half_rn(v);
+    else reinterpret_cast<float *>(cache)[idx] = v;
+}
+
 template <int T, int UNR>
 __global__ void __launch_bounds__(RW_THREADS) gemv_rows_kernel(const RowsParams p) {
     __shared__ float partial[RW_WARPS][UNR];
@@ -261,7 +267,7 @@ __global__ void __launch_bounds__(RW_THREADS) gemv_rows_kernel(const RowsParams 
     const bool active = tau < p.t128;
 
     ActRegs<T> act;
-    if (active) load_act<T>(p.x, tau, act);
+    bool first = true;
 
     for (uint32_t base = blockIdx.x * rows_per_pass; base < p.total_rows; base += gridDim.x * rows_per_pass) {
         Raw<T> raw[UNR];
@@ -278,6 +284,13 @@ __global__ void __launch_bounds__(RW_THREADS) gemv_rows_kernel(const RowsParams 
             local[u] = row - (s ? p.row_end[s - 1] : 0);
             if (valid[u] && active) load_raw<T>(p.w[s], local[u], tau, raw[u]);
         }
+        if (first) {
+            // the first rows' weight loads are in flight; only now wait for the producer of the activations
+            pdl_trigger();
+            pdl_wait();
+            if (active) load_act<T>(p.x, tau, act);
+            first = false;
+        }
         float acc[UNR];
 #pragma unroll
         for (int u = 0; u < UNR; ++u) {
@@ -286,12 +299,35 @@ __global__ void __launch_bounds__(RW_THREADS) gemv_rows_kernel(const RowsParams 
         }
         if (wpr == 1) {
             if (lane == 0) {
-#pragma unroll
-                for (int u = 0; u < UNR; ++u)
-                    if (valid[u]) {
-                        float *y = p.y[seg[u]] + local[u];
-                        *y = p.epilogue == EPI_ADD ? __fadd_rn(*y, acc[u]) : acc[u];
+                if (p.epilogue == EPI_ROPE_KV && UNR == 2) {
+                    // rows (2i, 2i+1) of one head: a NORM rotation pair (cera/src/backend/cpu.rs:5161-5180)
+                    if (valid[0]) {
+                        const uint32_t pos = *p.f.pos_dev, l0 = local[0];
+                        if (seg[0] == 2) {
+                            store_kv(p.f.v_cache, p.f.kv_f16, (size_t)pos * p.f.kv_dim + l0, acc[0]);
+                            store_kv(p.f.v_cache, p.f.kv_f16, (size_t)pos * p.f.kv_dim + l0 + 1, acc[1]);
+                        } else {
+                            const uint32_t pi = (l0 % p.f.head_dim) >> 1;
+                            const float cs = p.f.rope_cs[2 * pi], sn = p.f.rope_cs[2 * pi + 1];
+                            const float r0 = __fsub_rn(__fmul_rn(acc[0], cs), __fmul_rn(acc[1], sn));
+                            const float r1 = __fadd_rn(__fmul_rn(acc[0], sn), __fmul_rn(acc[1], cs));
+                            if (seg[0] == 0) {
+                                p.y[0][l0] = r0;
+                                p.y[0][l0 + 1] = r1;
+                            } else {
+                                store_kv(p.f.k_cache, p.f.kv_f16, (size_t)pos * p.f.kv_dim + l0, r0);
+                                store_kv(p.f.k_cache, p.f.kv_f16, (size_t)pos * p.f.kv_dim + l0 + 1, r1);
+                            }
+                        }
                     }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u)
+                        if (valid[u]) {
+                            float *y = p.y[seg[u]] + local[u];
+                            *y = p.epilogue == EPI_ADD ? __fadd_rn(*y, acc[u]) : acc[u];
+                        }
+                }
             }
         } else {
             if (lane == 0) {
@@ -323,30 +359,47 @@ __global__ void __launch_bounds__(RW_THREADS) gemv_rows_kernel(const RowsParams 
     }
 }
 
+__global__ void rope_table_kernel(const uint32_t *__restrict__ pos_dev, uint32_t half, float ts, const float *__restrict__ ff,
+                                  float *__restrict__ table) {
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= half) return;
+    float theta = (float)*pos_dev;
+    for (uint32_t s = 0; s < i; ++s) theta = __fmul_rn(theta, ts);
+    if (ff) theta = __fdiv_rn(theta, ff[i]);
+    float sn, cs;
+    sincosf(theta, &sn, &cs);
+    table[2 * i] = cs;
+    table[2 * i + 1] = sn;
+}
+
 template <int T>
 int32_t launch_rows_typed(const RowsParams &p, cudaStream_t st) {
     constexpr int UNR = 2;
+    const uint32_t cap = (uint32_t)sm_count() * 2;
     const uint32_t rows_per_pass = (RW_WARPS / p.wpr) * UNR;
     const uint32_t passes = (p.total_rows + rows_per_pass - 1) / rows_per_pass;
-    const uint32_t cap = (uint32_t)sm_count() * 2;
-    gemv_rows_kernel<T, UNR><<<passes < cap ? passes : cap, RW_THREADS, 0, st>>>(p);
     count_launch();
-    return check_cuda(cudaGetLastError(), "gemv launch");
+    return check_cuda(launch_k(gemv_rows_kernel<T, UNR>, dim3(passes < cap ? passes : cap), dim3(RW_THREADS), 0, st, p),
+                      "gemv launch");
 }
 
 }  // namespace
 
 // Single-column GEMV over up to three same-typed weight matrices.  *taken = false: the shape is
-// outside this kernel's rules (k not a multiple of 128, or wider than 8 warps of lane tasks); nothing
-// was launched and the caller falls back to the item-wise kernel.
-int32_t launch_gemv_rows(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, cudaStream_t st, bool *taken) {
+// outside this kernel's rules (k not a multiple of 128, wider than 8 warps of lane tasks, or a
+// fused epilogue whose alignment rules do not hold); nothing was launched and the caller falls back.
+int32_t launch_gemv_rows(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
+                         cudaStream_t st, bool *taken) {
     *taken = false;
     if (n_segs < 1 || n_segs > RW_MAX_SEGS) return CERA_CUDA_OK;
     const int type = segs[0].w.type;
     const uint32_t k = segs[0].w.k, t128 = segs[0].w.t128;
     if (!is_block_type(type) || t128 == 0 || t128 > 32 * RW_WARPS) return CERA_CUDA_OK;
-    if ((uintptr_t)x.quants % 16 || (uintptr_t)x.scales % 16 || (uintptr_t)x.sums % 16) return CERA_CUDA_OK;
     RowsParams p{};
+    if (fusion) p.f = *fusion;
+    if ((uintptr_t)x.quants % 16 || (uintptr_t)x.scales % 16 || (uintptr_t)x.sums % 16) return CERA_CUDA_OK;
     uint32_t rows = 0;
     for (int i = 0; i < n_segs; ++i) {
         if (segs[i].w.type != type || segs[i].w.k != k) return CERA_CUDA_OK;
@@ -355,18 +408,32 @@ int32_t launch_gemv_rows(const GemvSeg *segs, int n_segs, const ActView &x, int 
         rows += segs[i].w.m;
         p.row_end[i] = rows;
     }
+    int wpr = 1;
+    while (wpr * 32u < t128) wpr <<= 1;
+    if (epilogue == EPI_ROPE_KV) {
+        if (n_segs != 3 || wpr != 1 || !p.f.rope_cs || !p.f.pos_dev || !p.f.k_cache || !p.f.v_cache || p.f.head_dim % 2 ||
+            segs[0].w.m % 2 || segs[1].w.m % 2 || segs[2].w.m % 2)
+            return CERA_CUDA_OK;
+    }
     p.n_segs = n_segs;
     p.total_rows = rows;
     p.x = x;
     p.k = k;
     p.t128 = t128;
-    int wpr = 1;
-    while (wpr * 32u < t128) wpr <<= 1;
     p.wpr = wpr;
     p.epilogue = epilogue;
     *taken = true;
     CERA_DISPATCH_BLOCK_TYPE(type, return (launch_rows_typed<TT>(p, st)));
     return CERA_CUDA_OK;
+}
+
+int32_t launch_rope_table(const uint32_t *pos_dev, size_t head_dim, float theta_scale, const float *freq_factors,
+                          float *table, cudaStream_t st) {
+    const uint32_t half = (uint32_t)(head_dim / 2);
+    count_launch();
+    return check_cuda(launch_k(rope_table_kernel, dim3((half + 63) / 64), dim3(64), 0, st, pos_dev, half, theta_scale,
+                               freq_factors, table),
+                      "rope table launch");
 }
 
 }  // namespace cera

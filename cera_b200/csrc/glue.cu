@@ -15,6 +15,8 @@ namespace {
 __global__ void rope_kernel(float *q, float *k, const float *__restrict__ v, uint32_t pos_imm,
                             const uint32_t *__restrict__ pos_dev, uint32_t n_heads, uint32_t n_kv_heads, uint32_t hd,
                             float ts, const float *__restrict__ ff, int neox, void *k_cache, void *v_cache, int kv_f16) {
+    pdl_trigger();
+    pdl_wait();
     const uint32_t half = hd / 2;
     const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
     const uint32_t total = (n_heads + n_kv_heads) * half;
@@ -59,6 +61,8 @@ __global__ void rope_kernel(float *q, float *k, const float *__restrict__ v, uin
 
 template <int T>
 __global__ void embed_kernel(WeightView w, uint32_t token_imm, const uint32_t *__restrict__ token_dev, float *out) {
+    pdl_trigger();
+    pdl_wait();
     const uint32_t token = token_dev ? *token_dev : token_imm;
     const int items = w.k / 32;
     const int item = blockIdx.x * blockDim.x + threadIdx.x;
@@ -93,6 +97,8 @@ __device__ __forceinline__ void amax_merge(float &bv, uint32_t &bi, float v, uin
 }
 
 __global__ void argmax_stage1(const float *__restrict__ x, uint32_t n, uint32_t *scratch) {
+    pdl_trigger();
+    pdl_wait();
     float bv = -INFINITY;
     uint32_t bi = 0xFFFFFFFFu;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
@@ -118,6 +124,8 @@ __global__ void argmax_stage1(const float *__restrict__ x, uint32_t n, uint32_t 
 }
 
 __global__ void argmax_stage2(const uint32_t *__restrict__ scratch, int blocks, uint32_t *out) {
+    pdl_trigger();
+    pdl_wait();
     float bv = -INFINITY;
     uint32_t bi = 0xFFFFFFFFu;
     for (int b = threadIdx.x; b < blocks; b += 32) amax_merge(bv, bi, __uint_as_float(scratch[2 * b]), scratch[2 * b + 1]);
@@ -141,28 +149,29 @@ int32_t launch_rope(float *q, float *k, const float *v, size_t pos, const uint32
     if (v_cache && !v) return fail(CERA_CUDA_ERR_BAD_ARG, "rope: v_cache without v");
     const uint32_t total = (uint32_t)((n_heads + n_kv_heads) * (head_dim / 2));
     const int threads = 128;
-    rope_kernel<<<(total + threads - 1) / threads, threads, 0, st>>>(
-        q, k, v, (uint32_t)pos, pos_dev, (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)head_dim, theta_scale,
-        freq_factors, rope_type == 1, k_cache, v_cache, kv_f16);
     count_launch();
-    return check_cuda(cudaGetLastError(), "rope launch");
+    return check_cuda(launch_k(rope_kernel, dim3((total + threads - 1) / threads), dim3(threads), 0, st, q, k, v, (uint32_t)pos,
+                               pos_dev, (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)head_dim, theta_scale, freq_factors,
+                               rope_type == 1 ? 1 : 0, k_cache, v_cache, kv_f16),
+                      "rope launch");
 }
 
 int32_t launch_embed(const WeightView &w, uint32_t token, const uint32_t *token_dev, float *out, cudaStream_t st) {
     const int items = w.k / 32, threads = 128;
-    CERA_DISPATCH_BLOCK_TYPE(w.type, (embed_kernel<TT><<<(items + threads - 1) / threads, threads, 0, st>>>(w, token, token_dev, out)));
     count_launch();
-    return check_cuda(cudaGetLastError(), "embed launch");
+    CERA_DISPATCH_BLOCK_TYPE(w.type, return check_cuda(launch_k(embed_kernel<TT>, dim3((items + threads - 1) / threads), dim3(threads),
+                                                                0, st, w, token, token_dev, out), "embed launch"));
+    return CERA_CUDA_OK;
 }
 
 size_t argmax_scratch_words() { return 2 * ARGMAX_BLOCKS; }
 
 int32_t launch_argmax(const float *x, size_t n, uint32_t *out, uint32_t *scratch, cudaStream_t st) {
     if (!x || !out || !scratch) return fail(CERA_CUDA_ERR_BAD_ARG, "argmax: null argument");
-    argmax_stage1<<<ARGMAX_BLOCKS, ARGMAX_THREADS, 0, st>>>(x, (uint32_t)n, scratch);
-    argmax_stage2<<<1, 32, 0, st>>>(scratch, ARGMAX_BLOCKS, out);
     count_launch(2);
-    return check_cuda(cudaGetLastError(), "argmax launch");
+    CERA_CUDA_TRY(launch_k(argmax_stage1, dim3(ARGMAX_BLOCKS), dim3(ARGMAX_THREADS), 0, st, x, (uint32_t)n, scratch));
+    return check_cuda(launch_k(argmax_stage2, dim3(1), dim3(32), 0, st, (const uint32_t *)scratch, (int)ARGMAX_BLOCKS, out),
+                      "argmax launch");
 }
 
 }  // namespace cera

@@ -65,6 +65,7 @@ struct cera_cuda_model {
     uint32_t *h_dyn = nullptr;    // pinned host mirror of dyn + returned token
     float *h_logits = nullptr;    // pinned host staging for logits
     float theta_scale = 0.0f;
+    float *rope_cs = nullptr;  // [head_dim/2][2] cos/sin at the current position
     cudaStream_t stream = nullptr;
     std::map<uint32_t, cudaGraphExec_t> graphs;  // key = kind | n_splits << 8
     size_t seq_len = 0;
@@ -93,6 +94,8 @@ int32_t alloc_act(cera_cuda_model *m, ActBuf &a, size_t k) {
 // After the argmax of a chained step: record the token, make it the next input, advance
 // the position.  dyn = {token, pos, seq_len, step}.
 __global__ void advance_kernel(uint32_t *dyn, const uint32_t *tok_out, uint32_t *hist, uint32_t cap) {
+    pdl_trigger();
+    pdl_wait();
     const uint32_t t = *tok_out, step = dyn[3];
     if (step < cap) hist[step] = t;
     dyn[0] = t;
@@ -108,10 +111,27 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
     const size_t hs = c.hidden_size;
     const float scale = 1.0f / sqrtf((float)c.head_dim);
     CERA_TRY(launch_embed(m->embd->v, 0, m->dyn, m->hidden, st));
+    const bool norm_rope = c.rope_type == 0;
+    if (norm_rope) CERA_TRY(launch_rope_table(m->dyn + 1, c.head_dim, m->theta_scale, m->rope_freqs, m->rope_cs, st));
     for (auto &L : m->layers) {
         CERA_TRY(launch_rmsnorm(m->hidden, L.attn_norm, hs, 1, c.rms_norm_eps, nullptr, m->act_hs.scales,
                                 m->act_hs.quants, m->act_hs.sums, st));
-        if (L.wq->v.type == L.wk->v.type && L.wq->v.type == L.wv->v.type) {
+        bool fused_qkv = false;
+        if (norm_rope && L.wq->v.type == L.wk->v.type && L.wq->v.type == L.wv->v.type) {
+            // q/k/v GEMV with RoPE and the KV-cache append as its epilogue
+            GemvSeg segs[3] = {{L.wq->v, m->q}, {L.wk->v, m->k}, {L.wv->v, m->v}};
+            GemvFusion f;
+            f.rope_cs = m->rope_cs;
+            f.pos_dev = m->dyn + 1;
+            f.k_cache = L.kc;
+            f.v_cache = L.vc;
+            f.kv_f16 = c.kv_f16;
+            f.head_dim = c.head_dim;
+            f.kv_dim = c.n_kv_heads * c.head_dim;
+            CERA_TRY(launch_gemv_rows(segs, 3, m->act_hs.view(), EPI_ROPE_KV, &f, st, &fused_qkv));
+        }
+        if (fused_qkv) {
+        } else if (L.wq->v.type == L.wk->v.type && L.wq->v.type == L.wv->v.type) {
             GemvSeg segs[3] = {{L.wq->v, m->q}, {L.wk->v, m->k}, {L.wv->v, m->v}};
             CERA_TRY(launch_gemv(segs, 3, m->act_hs.view(), 1, 1, EPI_STORE, st));
         } else {
@@ -120,8 +140,9 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
             CERA_TRY(launch_gemv(&sk, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
             CERA_TRY(launch_gemv(&sv, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
         }
-        CERA_TRY(launch_rope(m->q, m->k, m->v, 0, m->dyn + 1, c.n_heads, c.n_kv_heads, c.head_dim, m->theta_scale,
-                             m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st));
+        if (!fused_qkv)
+            CERA_TRY(launch_rope(m->q, m->k, m->v, 0, m->dyn + 1, c.n_heads, c.n_kv_heads, c.head_dim, m->theta_scale,
+                                 m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st));
         CERA_TRY(launch_decode_attention_ex(m->q, L.kc, L.vc, c.kv_f16, c.n_heads, c.n_kv_heads, c.head_dim, 0,
                                             m->dyn + 2, n_splits, scale, m->attn, m->attn_ws, m->attn_ws_bytes,
                                             m->act_q.scales, m->act_q.quants, m->act_q.sums, st));
@@ -151,9 +172,9 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
     if (kind == G_GREEDY || kind == G_CHAIN)
         CERA_TRY(launch_argmax(m->logits, c.vocab_size, m->tok_out, m->argmax_scratch, st));
     if (kind == G_CHAIN) {
-        advance_kernel<<<1, 1, 0, st>>>(m->dyn, m->tok_out, m->tok_hist, m->tok_hist_cap);
         count_launch();
-        CERA_CUDA_TRY(cudaGetLastError());
+        CERA_CUDA_TRY(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, m->dyn, (const uint32_t *)m->tok_out, m->tok_hist,
+                               m->tok_hist_cap));
     }
     return CERA_CUDA_OK;
 }
@@ -321,6 +342,7 @@ int32_t cera_cuda_model_finalize(cera_cuda_model *m) {
     CERA_TRY(dev_alloc(m, (void **)&m->argmax_scratch, argmax_scratch_words() * 4));
     CERA_TRY(dev_alloc(m, (void **)&m->dyn, 4 * 4));
     CERA_TRY(dev_alloc(m, (void **)&m->tok_out, 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->rope_cs, (size_t)c.head_dim * 4));
     m->tok_hist_cap = c.max_seq_len;
     CERA_TRY(dev_alloc(m, (void **)&m->tok_hist, (size_t)m->tok_hist_cap * 4));
     CERA_CUDA_TRY(cudaMallocHost((void **)&m->h_dyn, 8 * 4));

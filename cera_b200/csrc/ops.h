@@ -20,12 +20,27 @@ struct GemvSeg {
     WeightView w;
     float *y;  // [m x n] row-major
 };
-enum { EPI_STORE = 0, EPI_ADD = 1 };
+// EPI_STORE: y = Wx.  EPI_ADD: y += Wx (residual).  EPI_ROPE_KV: segments are q, k, v; q and k rows are
+// rotated (NORM pairs) with the per-token cos/sin table, k and v go straight into the KV cache row.
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_ROPE_KV = 2 };
+
+// Work fused behind the single-column GEMV (EPI_ROPE_KV).
+struct GemvFusion {
+    const float *rope_cs = nullptr;       // [head_dim/2][2] cos, sin at the current position
+    const uint32_t *pos_dev = nullptr;
+    void *k_cache = nullptr, *v_cache = nullptr;
+    int kv_f16 = 0;
+    uint32_t head_dim = 0, kv_dim = 0;
+};
 int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_cols, size_t ldy, int epilogue,
                     cudaStream_t st);
 // Register-resident-activation single-column GEMV.  *taken = false: shape outside its rules,
 // nothing was launched and the caller uses the item-wise kernel.
-int32_t launch_gemv_rows(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, cudaStream_t st, bool *taken);
+int32_t launch_gemv_rows(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
+                         cudaStream_t st, bool *taken);
+// cos/sin of every rotation pair at position *pos_dev, same arithmetic as launch_rope.
+int32_t launch_rope_table(const uint32_t *pos_dev, size_t head_dim, float theta_scale, const float *freq_factors,
+                          float *table, cudaStream_t st);
 int32_t launch_gemm(const WeightView &w, const ActView &x, size_t n, float *out, cudaStream_t st);
 int32_t launch_gemv_q5k_f32(const WeightView &w, const float *x, float *y, cudaStream_t st);
 

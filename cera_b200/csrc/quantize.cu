@@ -9,6 +9,8 @@ namespace {
 // One warp per (column, block).  strided != 0: x is [k x n] with row stride n.
 __global__ void quantize_kernel(const float *__restrict__ x, size_t k, size_t n, int strided, float *scales,
                                 int8_t *quants, int16_t *sums) {
+    pdl_trigger();
+    pdl_wait();
     const size_t nb = k / 32;
     const size_t wid = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -31,6 +33,8 @@ __global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restr
                                float *out_f32, float *scales, int8_t *quants, int16_t *sums) {
     __shared__ double red[32];
     __shared__ float inv_s;
+    pdl_trigger();
+    pdl_wait();
     const size_t col = blockIdx.x;
     const float *xc = x + col * n_elem;
     double ss = 0.0;
@@ -68,6 +72,8 @@ __global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restr
 
 __global__ void silu_mul_kernel(float *gate, const float *__restrict__ up, size_t n_elem, size_t n_cols,
                                 float *scales, int8_t *quants, int16_t *sums) {
+    pdl_trigger();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_elem * n_cols) return;
     const float v = silu_mul(gate[i], up[i]);
@@ -93,7 +99,7 @@ int32_t launch_quantize(const float *x, size_t k, size_t n, bool strided, float 
     const size_t warps = (k / 32) * n;
     const int threads = 256;
     const size_t grid = (warps * 32 + threads - 1) / threads;
-    quantize_kernel<<<(unsigned)grid, threads, 0, st>>>(x, k, n, strided ? 1 : 0, scales, quants, sums);
+    CERA_CUDA_TRY(launch_k(quantize_kernel, dim3((unsigned)grid), dim3(threads), 0, st, x, k, n, strided ? 1 : 0, scales, quants, sums));
     count_launch();
     return check_cuda(cudaGetLastError(), "quantize launch");
 }
@@ -105,7 +111,7 @@ int32_t launch_rmsnorm(const float *x, const float *weight, size_t n_elem, size_
         return fail(CERA_CUDA_ERR_BAD_ARG, "rmsnorm+quantize: n=%zu must be a multiple of 32", n_elem);
     if (n_elem == 0 || n_cols == 0) return CERA_CUDA_OK;
     const int threads = n_elem >= 1024 ? 1024 : (int)((n_elem + 31) / 32 * 32);
-    rmsnorm_kernel<<<(unsigned)n_cols, threads, 0, st>>>(x, weight, n_elem, eps, out_f32, scales, quants, sums);
+    CERA_CUDA_TRY(launch_k(rmsnorm_kernel, dim3((unsigned)n_cols), dim3(threads), 0, st, x, weight, n_elem, eps, out_f32, scales, quants, sums));
     count_launch();
     return check_cuda(cudaGetLastError(), "rmsnorm launch");
 }
@@ -117,8 +123,8 @@ int32_t launch_silu_mul(float *gate, const float *up, size_t n_elem, size_t n_co
     const size_t total = n_elem * n_cols;
     if (total == 0) return CERA_CUDA_OK;
     const int threads = 256;
-    silu_mul_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, st>>>(gate, up, n_elem, n_cols, scales,
-                                                                                   quants, sums);
+    CERA_CUDA_TRY(launch_k(silu_mul_kernel, dim3((unsigned)((total + threads - 1) / threads)), dim3(threads), 0, st, gate, up,
+                           n_elem, n_cols, scales, quants, sums));
     count_launch();
     return check_cuda(cudaGetLastError(), "silu_mul launch");
 }

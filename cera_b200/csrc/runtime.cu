@@ -3,6 +3,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -27,6 +28,14 @@ int32_t check_cuda(cudaError_t e, const char *what) {
 
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 uint64_t launches_so_far() { return g_launches.load(std::memory_order_relaxed); }
+
+bool pdl_enabled() {
+    static const bool v = [] {
+        const char *e = getenv("CERA_CUDA_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return v;
+}
 
 int sm_count() {
     static thread_local int cached_dev = -1, cached = 0;

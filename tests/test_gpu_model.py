@@ -82,10 +82,12 @@ def test_prefill_equals_per_token_forward_and_truncate():
     assert np.array_equal(again, lp)
 
 
-def test_wide_llama_matches_oracle():
+@pytest.mark.parametrize("kv_f16", [0, 1])
+def test_wide_llama_matches_oracle(kv_f16):
+    """Takes the fused launches: norm + quantize prologue, RoPE + KV-append and SiLU*mul + quantize epilogues."""
     need_gpu()
     from cera_b200 import synth
-    gpu, oracle = _pair(WIDE, seed=21, threads=4)
+    gpu, oracle = _pair(WIDE, seed=21, threads=4, kv_f16=kv_f16)
     prompt = synth.prompt_tokens(6, WIDE["vocab_size"], seed=3)
     for pos, t in enumerate(prompt):
         lg, lo = gpu.forward(int(t), pos), oracle.forward(int(t), pos)
