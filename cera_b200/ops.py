@@ -162,6 +162,21 @@ def decode_attention(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim, seq_len
     return out
 
 
+def decode_attention_noalloc(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim, seq_len, scale, out=None):
+    """decode_attention for callers that may not allocate device memory: the split-KV workspace is the
+    library's built-in array (n_heads <= 64, head_dim <= 128).  Pass `out` to make the call allocation-free
+    on the Python side too.  Calls on different streams must not overlap: they share the array."""
+    q = _dev(q, torch.float32)
+    f16 = k_cache.dtype == torch.float16
+    if v_cache.dtype != k_cache.dtype or k_cache.dtype not in (torch.float16, torch.float32):
+        raise TypeError("KV caches must both be float32 or both float16")
+    if out is None:
+        out = torch.empty(n_heads * head_dim, dtype=torch.float32, device=q.device)
+    check(lib.cera_cuda_decode_attention_noalloc(_ptr(q), _ptr(k_cache), _ptr(v_cache), int(f16), n_heads, n_kv_heads,
+                                                 head_dim, seq_len, scale, _ptr(_dev(out, torch.float32)), _stream()))
+    return out
+
+
 def synth_normal(n, seed, sigma, offset=0, device="cuda"):
     out = torch.empty(n, dtype=torch.float32, device=device)
     check(lib.cera_cuda_synth_normal(_ptr(out), n, seed, offset, sigma, _stream()))

@@ -147,6 +147,20 @@ CERA_API int32_t cera_cuda_decode_attention(const float *q_dev, const void *k_ca
                                             float scale, float *out_dev, void *workspace_dev,
                                             size_t workspace_bytes, void *stream);
 
+/* No counterpart in the reference.  The same attention for callers that cannot allocate device
+ * memory (an embedding engine that owns the device heap, a thread on which allocation is forbidden,
+ * a process with a frozen memory budget): the split-KV workspace is a fixed 2.1 MB array inside the
+ * library, held by every GPU that loads it.  Limits: n_heads <= 64, head_dim <= 128; larger shapes
+ * are rejected with CERA_CUDA_ERR_BAD_ARG.  The call allocates nothing.  The first call on each
+ * device looks up the array's device address (cudaGetSymbolAddress, with that device current), so
+ * make that first call before starting any stream capture.  All calls on a device share the array:
+ * two calls that overlap on the GPU (different streams) race on it; calls on one stream do not. */
+CERA_API int32_t cera_cuda_decode_attention_noalloc(const float *q_dev, const void *k_cache_dev,
+                                                    const void *v_cache_dev, int32_t kv_f16,
+                                                    size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                                                    size_t seq_len, float scale, float *out_dev,
+                                                    void *stream);
+
 /* ------------------------------------------------------------------------ */
 /* Synthetic inputs for benchmarks and tests (the reference's counterpart is   */
 /* its converter, cera/src/convert/quantize.rs:254-343 quantize_tensor_data).  */
