@@ -190,23 +190,27 @@ def reference_arm(args, rank):
 
 
 # --------------------------------------------------------------------------- CUDA arm
-def roofline_q4k_gemv(torch, cb, iters):
-    """The gate/up-shape Q4_K GEMV alone: 16 distinct weight copies (528 MB > 126 MB L2) visited
-    round-robin, CUDA events on the launching (current) stream."""
-    from cera_b200.types import Q4_K
-    m, k, copies = 14336, 4096, 16
+BLOCKS = {"q4_0": (2, 32, 18), "q4_1": (3, 32, 20), "q8_0": (8, 32, 34), "q4_k": (12, 256, 144), "q5_k": (13, 256, 176),
+          "q6_k": (14, 256, 210)}
+
+
+def gemv_microbench(torch, cb, tname, m, k, iters):
+    """One GEMV shape alone: distinct weight copies totalling more than 4x L2 visited round-robin, the launches
+    recorded into a CUDA graph (a Python launch loop costs more per call than the kernel runs), CUDA events on
+    the launching stream.  Returns (algorithmic bytes per launch, microseconds per launch, launches)."""
+    t, blk, bb = BLOCKS[tname]
+    wbytes = m * (k // blk) * bb
+    copies = max(2, min(16, -(-(512 << 20) // wbytes)))
     ws = []
     for i in range(copies):
         w = cb.synth_normal(m * k, seed=500 + i, sigma=0.02)
-        ws.append(cb.QuantWeight(Q4_K, m, k, cb.quantize_weights(Q4_K, w)))
+        ws.append(cb.QuantWeight(t, m, k, cb.quantize_weights(t, w)))
         del w
     acts = cb.quantize_q8_0(cb.synth_normal(k, seed=77, sigma=1.0), k=k, n=1)
     out = torch.empty(m, 1, device="cuda")
     for i in range(copies):
         cb.gemm_preq(ws[i], acts, out)
     torch.cuda.synchronize()
-    # Record the launches into a CUDA graph so the timed region holds kernels only
-    # (a Python launch loop costs more per call than the kernel runs).
     side = torch.cuda.Stream()
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(side):
@@ -221,10 +225,20 @@ def roofline_q4k_gemv(torch, cb, iters):
         e1.record(side)
         side.synchronize()
     us = e0.elapsed_time(e1) * 1000.0 / iters
-    algo = gemv_bytes(m, k, 256, 144)
+    algo = gemv_bytes(m, k, blk, bb)
     for w in ws:
         w.close()
     return algo, us, 2 * iters + copies
+
+
+def roofline_q4k_gemv(torch, cb, iters):
+    """The dominant kernel of the decode step: the Q4_K GEMV at the gate/up shape."""
+    return gemv_microbench(torch, cb, "q4_k", 14336, 4096, iters)
+
+
+DECODE_SHAPES = [("q4_k", 4096, 4096), ("q4_k", 14336, 4096), ("q6_k", 4096, 14336), ("q6_k", 128256, 4096),
+                 ("q5_k", 4096, 4096), ("q6_k", 4096, 4096), ("q4_0", 4096, 4096), ("q8_0", 4096, 4096),
+                 ("q4_1", 4096, 4096), ("q4_k", 4096, 14336)]
 
 
 def cuda_arm(args, rank, world):
@@ -343,7 +357,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
                     help="prompt tokens before the timed decode (512 is the benchmark; shorter only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--only", default=None, choices=["roofline"],
+    ap.add_argument("--only", default=None, choices=["roofline", "gemv-sweep"],
                     help="run just the dominant-kernel microbench (the case ncu captures are taken on)")
     ap.add_argument("--iters", type=int, default=200, help="timed launches of the kernel microbench")
     args = ap.parse_args()
@@ -357,6 +371,15 @@ def main():
         print(json.dumps({"kernel": "gemv_kernel<Q4_K, 1 column> 14336x4096", "us_per_launch": us,
                           "achieved_gbs": algo / us / 1e3, "frac": algo / us / 1e3 / hbm, "peak_source": which,
                           "launches": n}))
+    elif args.only == "gemv-sweep":
+        import torch
+        import cera_b200 as cb
+        hbm, which = measured_peaks()
+        for tname, m, k in DECODE_SHAPES:
+            algo, us, _ = gemv_microbench(torch, cb, tname, m, k, args.iters if m < 100000 else max(8, args.iters // 8))
+            print(json.dumps({"type": tname, "m": m, "k": k, "us": round(us, 3), "algorithmic_bytes": algo,
+                              "gbs": round(algo / us / 1e3, 1), "frac_of_measured": round(algo / us / 1e3 / hbm, 4),
+                              "frac_of_8000": round(algo / us / 1e3 / 8000.0, 4)}), flush=True)
     elif args.impl == "reference":
         reference_arm(args, rank)
     else:

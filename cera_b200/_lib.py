@@ -32,6 +32,7 @@ class Config(C.Structure):
 # name -> (restype, argtypes); every symbol include/cera_cuda.h declares.
 SIGNATURES = {
     "cera_cuda_last_error": (C.c_char_p, []),
+    "cera_cuda_kernel_status": (_i32, [C.POINTER(_u32)]),
     "cera_cuda_device_count": (_i32, [C.POINTER(_i32)]),
     "cera_cuda_weight_create": (_i32, [_i32, _sz, _sz, _p, _sz, C.POINTER(_p)]),
     "cera_cuda_weight_free": (None, [_p]),
@@ -86,3 +87,10 @@ def last_error():
 def check(code):
     if code != 0:
         raise CeraCudaError(code, last_error())
+
+
+def kernel_status():
+    """0 when no bounded device-side wait has run out on the current device."""
+    v = _u32()
+    lib.cera_cuda_kernel_status(C.byref(v))
+    return v.value

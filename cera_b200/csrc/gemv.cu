@@ -184,13 +184,20 @@ static bool force_direct() {
     return v;
 }
 
+int32_t launch_gemv_fused(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
+                          cudaStream_t st, bool *taken) {
+    CERA_TRY(launch_gemv_tma(segs, n_segs, x, epilogue, fusion, st, taken));
+    if (*taken) return CERA_CUDA_OK;
+    return launch_gemv_rows(segs, n_segs, x, epilogue, fusion, st, taken);
+}
+
 // All segments must share the type and k.  n_cols in {1,2,4,8}.
 int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_cols, size_t ldy, int epilogue,
                     cudaStream_t st) {
     if (n_segs < 1 || n_segs > MAX_SEGS) return fail(CERA_CUDA_ERR_BAD_ARG, "gemv: %d segments", n_segs);
     if (n_cols == 1 && ldy == 1 && !force_direct()) {
         bool taken = false;
-        CERA_TRY(launch_gemv_rows(segs, n_segs, x, epilogue, nullptr, st, &taken));
+        CERA_TRY(launch_gemv_fused(segs, n_segs, x, epilogue, nullptr, st, &taken));
         if (taken) return CERA_CUDA_OK;
     }
     GemvParams p{};

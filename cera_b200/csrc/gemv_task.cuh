@@ -74,35 +74,46 @@ struct Raw {
     uint4 hd;                               // header words (format specific, see load_raw)
 };
 
-template <int T>
+// Loads of weight bytes: GLOBAL = streaming / read-only global loads, otherwise plain loads (the
+// view then points at a shared-memory copy of the same planes).
+template <bool GLOBAL>
+__device__ __forceinline__ uint4 ldw16(const void *p) {
+    if (GLOBAL) return ld_stream(p);
+    return *reinterpret_cast<const uint4 *>(p);
+}
+template <bool GLOBAL, typename V>
+__device__ __forceinline__ V ldh(const void *p) {
+    if (GLOBAL) return __ldg(reinterpret_cast<const V *>(p));
+    return *reinterpret_cast<const V *>(p);
+}
+
+template <int T, bool GLOBAL = true>
 __device__ __forceinline__ void load_raw(const WeightView &w, size_t row, uint32_t tau, Raw<T> &r) {
     constexpr int NP = T == CERA_TYPE_Q8_0 ? 8 : 4;
     const TypeInfo ti = type_info(T);
     const uint8_t *q = w.q + row * ((size_t)w.nb * ti.q_b) + (size_t)tau * 16;
 #pragma unroll
-    for (int c = 0; c < NP; ++c) r.p[c] = ld_stream(q + (size_t)c * w.t128 * 16);
+    for (int c = 0; c < NP; ++c) r.p[c] = ldw16<GLOBAL>(q + (size_t)c * w.t128 * 16);
     if (T == CERA_TYPE_Q4_0 || T == CERA_TYPE_Q8_0) {  // 4 half scales
-        const uint2 d = __ldg(reinterpret_cast<const uint2 *>(w.hdr + (row * w.nb + 4 * (size_t)tau) * 2));
+        const uint2 d = ldh<GLOBAL, uint2>(w.hdr + (row * w.nb + 4 * (size_t)tau) * 2);
         r.hd = make_uint4(d.x, d.y, 0, 0);
     } else if (T == CERA_TYPE_Q4_1) {  // 4 x (d, m)
-        r.hd = __ldg(reinterpret_cast<const uint4 *>(w.hdr + (row * w.nb + 4 * (size_t)tau) * 4));
+        r.hd = ldh<GLOBAL, uint4>(w.hdr + (row * w.nb + 4 * (size_t)tau) * 4);
     } else if (T == CERA_TYPE_Q4_K || T == CERA_TYPE_Q5_K) {  // d, dmin, scales[12] of super-block tau/2
         const size_t sb = row * w.nb + (tau >> 1);
-        r.hd = __ldg(reinterpret_cast<const uint4 *>(w.hdr) + sb);
+        r.hd = ldh<GLOBAL, uint4>(w.hdr + sb * 16);
         if (T == CERA_TYPE_Q5_K) {
-            const uint4 *h = reinterpret_cast<const uint4 *>(w.qh + sb * 32);
-            r.hi[0] = __ldg(h);
-            r.hi[1] = __ldg(h + 1);
+            r.hi[0] = ldh<GLOBAL, uint4>(w.qh + sb * 32);
+            r.hi[1] = ldh<GLOBAL, uint4>(w.qh + sb * 32 + 16);
         }
     } else {  // Q6_K: 8 int8 scales of half nh, d in .z
         const size_t sb = row * w.nb + (tau >> 1);
         const uint32_t nh = tau & 1;
-        const uint2 sc = __ldg(reinterpret_cast<const uint2 *>(w.hdr + sb * 16 + nh * 8));
-        const uint16_t d = __ldg(reinterpret_cast<const uint16_t *>(w.d) + sb);
+        const uint2 sc = ldh<GLOBAL, uint2>(w.hdr + sb * 16 + nh * 8);
+        const uint16_t d = ldh<GLOBAL, uint16_t>(w.d + sb * 2);
         r.hd = make_uint4(sc.x, sc.y, d, 0);
-        const uint4 *h = reinterpret_cast<const uint4 *>(w.qh + sb * 64 + nh * 32);
-        r.hi[0] = __ldg(h);
-        r.hi[1] = __ldg(h + 1);
+        r.hi[0] = ldh<GLOBAL, uint4>(w.qh + sb * 64 + nh * 32);
+        r.hi[1] = ldh<GLOBAL, uint4>(w.qh + sb * 64 + nh * 32 + 16);
     }
 }
 

@@ -128,7 +128,7 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
             f.kv_f16 = c.kv_f16;
             f.head_dim = c.head_dim;
             f.kv_dim = c.n_kv_heads * c.head_dim;
-            CERA_TRY(launch_gemv_rows(segs, 3, m->act_hs.view(), EPI_ROPE_KV, &f, st, &fused_qkv));
+            CERA_TRY(launch_gemv_fused(segs, 3, m->act_hs.view(), EPI_ROPE_KV, &f, st, &fused_qkv));
         }
         if (fused_qkv) {
         } else if (L.wq->v.type == L.wk->v.type && L.wq->v.type == L.wv->v.type) {

@@ -38,6 +38,12 @@ int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_
 // nothing was launched and the caller uses the item-wise kernel.
 int32_t launch_gemv_rows(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
                          cudaStream_t st, bool *taken);
+// Same contract through the TMA-staged kernel (bulk asynchronous copies into a shared-memory ring).
+int32_t launch_gemv_tma(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
+                        cudaStream_t st, bool *taken);
+// Tries the TMA-staged kernel, then the register-streaming one.
+int32_t launch_gemv_fused(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
+                          cudaStream_t st, bool *taken);
 // cos/sin of every rotation pair at position *pos_dev, same arithmetic as launch_rope.
 int32_t launch_rope_table(const uint32_t *pos_dev, size_t head_dim, float theta_scale, const float *freq_factors,
                           float *table, cudaStream_t st);

@@ -28,44 +28,72 @@ __global__ void quantize_kernel(const float *__restrict__ x, size_t k, size_t n,
 
 // RMSNorm of one column per CTA (cera/src/backend/cpu.rs:2479-2496: f64 sum of
 // squares, inv = (float)(1/sqrt(mean+eps)), x*inv*w left to right), then
-// optionally the Q8_0 quantizer on the normed values.
-__global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ weight, size_t n_elem, float eps,
-                               float *out_f32, float *scales, int8_t *quants, int16_t *sums) {
-    __shared__ double red[32];
+// optionally the Q8_0 quantizer on the normed values.  Latency-bound: 256 threads, every
+// thread's x and w values fetched once with all loads issued before the reduction.
+constexpr int RN_THREADS = 256, RN_WARPS = 8, RN_CH = 16;
+
+__global__ void __launch_bounds__(RN_THREADS) rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ weight,
+                                                              size_t n_elem, float eps, float *out_f32, float *scales,
+                                                              int8_t *quants, int16_t *sums) {
+    __shared__ double red[RN_WARPS];
     __shared__ float inv_s;
     pdl_trigger();
-    pdl_wait();
     const size_t col = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t nblk = (uint32_t)((n_elem + 31) >> 5);
+    const bool single = nblk <= RN_WARPS * RN_CH;  // up to 4096 elements stay in registers
+    // lane `lane` of warp `warp` owns element `lane` of 32-blocks warp, warp+8, ...
+    float wv[RN_CH], xv[RN_CH];
+    if (single) {
+#pragma unroll
+        for (int j = 0; j < RN_CH; ++j) {
+            const size_t i = (size_t)(warp + RN_WARPS * j) * 32 + lane;
+            wv[j] = i < n_elem ? weight[i] : 0.0f;  // weights do not depend on the previous kernel
+        }
+    }
+    pdl_wait();
     const float *xc = x + col * n_elem;
     double ss = 0.0;
-    for (size_t i = threadIdx.x; i < n_elem; i += blockDim.x) {
-        const double v = (double)xc[i];
-        ss += v * v;
+    for (uint32_t c0 = 0; c0 < nblk; c0 += RN_WARPS * RN_CH) {
+#pragma unroll
+        for (int j = 0; j < RN_CH; ++j) {
+            const size_t i = (size_t)(c0 + warp + RN_WARPS * j) * 32 + lane;
+            xv[j] = i < n_elem ? xc[i] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < RN_CH; ++j) ss += (double)xv[j] * (double)xv[j];
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    if (lane == 0) red[warp] = ss;
     __syncthreads();
-    if (threadIdx.x < 32) {
-        double t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0;
+    if (threadIdx.x == 0) {
+        double t = 0.0;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-        if (threadIdx.x == 0) inv_s = (float)(1.0 / sqrt(t / (double)n_elem + (double)eps));
+        for (int w = 0; w < RN_WARPS; ++w) t += red[w];
+        inv_s = (float)(1.0 / sqrt(t / (double)n_elem + (double)eps));
     }
     __syncthreads();
     const float inv = inv_s;
-    // n_elem is a multiple of 32 whenever quantization is requested, so whole warps stay converged.
-    for (size_t i = threadIdx.x; i < n_elem; i += blockDim.x) {
-        const float v = __fmul_rn(__fmul_rn(xc[i], inv), weight[i]);
-        if (out_f32) out_f32[col * n_elem + i] = v;
-        if (quants) {
-            float scale;
-            int hs;
-            const int q = quantize_lane(v, scale, hs);
-            const int lane = threadIdx.x & 31;
-            quants[col * n_elem + i] = (int8_t)q;
-            if (lane == 0) scales[col * (n_elem / 32) + i / 32] = scale;
-            if ((lane & 15) == 0) sums[col * (n_elem / 16) + i / 16] = (int16_t)hs;
+    for (uint32_t c0 = 0; c0 < nblk; c0 += RN_WARPS * RN_CH) {
+#pragma unroll
+        for (int j = 0; j < RN_CH; ++j) {
+            const uint32_t b = c0 + warp + RN_WARPS * j;
+            if (b >= nblk) continue;  // warp-uniform
+            const size_t i = (size_t)b * 32 + lane;
+            const bool in = i < n_elem;  // only the f32-only path may see a ragged last block
+            const float xi = single ? xv[j] : (in ? xc[i] : 0.0f);
+            const float wi = single ? wv[j] : (in ? weight[i] : 0.0f);
+            const float v = __fmul_rn(__fmul_rn(xi, inv), wi);
+            if (out_f32 && in) out_f32[col * n_elem + i] = v;
+            if (quants) {
+                float scale;
+                int hs;
+                const int q = quantize_lane(v, scale, hs);
+                quants[col * n_elem + i] = (int8_t)q;
+                if (lane == 0) scales[col * (n_elem / 32) + b] = scale;
+                if ((lane & 15) == 0) sums[col * (n_elem / 16) + 2 * b + (lane >> 4)] = (int16_t)hs;
+            }
         }
     }
 }
@@ -110,7 +138,7 @@ int32_t launch_rmsnorm(const float *x, const float *weight, size_t n_elem, size_
     if (quants && (n_elem % 32 || !scales || !sums))
         return fail(CERA_CUDA_ERR_BAD_ARG, "rmsnorm+quantize: n=%zu must be a multiple of 32", n_elem);
     if (n_elem == 0 || n_cols == 0) return CERA_CUDA_OK;
-    const int threads = n_elem >= 1024 ? 1024 : (int)((n_elem + 31) / 32 * 32);
+    const int threads = RN_THREADS;
     CERA_CUDA_TRY(launch_k(rmsnorm_kernel, dim3((unsigned)n_cols), dim3(threads), 0, st, x, weight, n_elem, eps, out_f32, scales, quants, sums));
     count_launch();
     return check_cuda(cudaGetLastError(), "rmsnorm launch");

@@ -59,6 +59,11 @@ enum {
 };
 
 CERA_API const char *cera_cuda_last_error(void);
+/* Device-side health word of the current device: 0 when no bounded wait inside a kernel has ever
+ * run out (then the call returns CERA_CUDA_OK), else CERA_CUDA_ERR_TIMEOUT with the bits in
+ * *status_out.  The counterpart of the reference's "a declined kernel must be loud" rule
+ * (cera/src/model/transformer.rs:790-820) for kernels that wait on hardware barriers. */
+CERA_API int32_t cera_cuda_kernel_status(uint32_t *status_out);
 CERA_API int32_t cera_cuda_device_count(int32_t *count);
 
 /* ------------------------------------------------------------------------ */

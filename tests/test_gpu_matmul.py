@@ -188,3 +188,31 @@ def test_gemm_preq_declines_loudly():
     acts = cb.quantize_q8_0(torch.zeros(128, device="cuda"), k=128, n=1)
     with pytest.raises(cb.CeraCudaError):
         cb.gemm_preq(w, acts)
+
+
+def test_tma_staged_gemv_in_its_own_process():
+    """The opt-in TMA-staged GEMV (CERA_CUDA_GEMV=tma is read once per process) against the oracle,
+    and its bounded waits must not have run out."""
+    need_gpu()
+    import os
+    import subprocess
+    import sys
+    code = r"""
+import sys, numpy as np
+sys.path.insert(0, 'tests')
+import oracle_lib as O, cera_b200 as cb
+from cera_b200 import _lib
+for t, m, k in ((O.Q4_K, 64, 4096), (O.Q6_K, 24, 14336), (O.Q4_0, 128, 1024), (O.Q8_0, 32, 2048), (O.Q5_K, 48, 4096), (O.Q4_1, 16, 4096)):
+    raw = cb.quantize_weights(t, cb.synth_normal(m * k, 3 * t + m, 0.02)).cpu().numpy()
+    x = cb.synth_normal(k, m + k, 1.0)
+    got = cb.gemv(cb.QuantWeight(t, m, k, raw), x).cpu().numpy()
+    xs, xq = O.quantize_q8_0(x.cpu().numpy())
+    want = O.gemm_preq(t, raw, xs, xq, m, 1, k).ravel()
+    assert np.all(np.abs(got - want) <= 1e-4 + 1e-3 * np.abs(want)), (t, m, k, np.abs(got - want).max())
+assert _lib.kernel_status() == 0
+print('tma ok')
+"""
+    env = dict(os.environ, CERA_CUDA_GEMV="tma")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "tma ok" in r.stdout, r.stdout + r.stderr
