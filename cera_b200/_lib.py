@@ -49,6 +49,7 @@ SIGNATURES = {
     "cera_cuda_rope": (_i32, [_p, _p, _sz, _sz, _sz, _sz, _f, _p, _i32, _p]),
     "cera_cuda_decode_attention_workspace_bytes": (_sz, [_sz, _sz, _sz]),
     "cera_cuda_decode_attention": (_i32, [_p, _p, _p, _i32, _sz, _sz, _sz, _sz, _f, _p, _p, _sz, _p]),
+    "cera_cuda_prefill_attention": (_i32, [_p, _p, _p, _i32, _sz, _sz, _sz, _sz, _sz, _f, _p, _p]),
     "cera_cuda_decode_attention_noalloc": (_i32, [_p, _p, _p, _i32, _sz, _sz, _sz, _sz, _f, _p, _p]),
     "cera_cuda_synth_normal": (_i32, [_p, _sz, _u64, _u64, _f, _p]),
     "cera_cuda_quantize_weights": (_i32, [_i32, _p, _sz, _p, _p]),

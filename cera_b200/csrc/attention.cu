@@ -218,6 +218,71 @@ __global__ void attn_merge_kernel(const float *__restrict__ ws, uint32_t n_split
     }
 }
 
+// Causal attention for a batch of prompt tokens: one warp per (query head, query token), online softmax
+// over cache rows [0, start_pos + j] with the polynomial expf (cera/src/backend/cpu.rs:4146-4241; the tile
+// width there is 32, here 1, which only changes f32 rounding).  q / out are token-major.
+template <int VEC, bool F16>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_prefill_kernel(const float *__restrict__ q, const void *__restrict__ kc, const void *__restrict__ vc, uint32_t n_heads,
+                    uint32_t n_kv_heads, uint32_t n, uint32_t start_pos, float scale, float *__restrict__ out) {
+    constexpr int HD = VEC * 32;
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t h = blockIdx.x, j = blockIdx.y * ATT_WARPS + warp;
+    if (j >= n) return;
+    const uint32_t kvh = h / (n_heads / n_kv_heads);
+    const size_t kv_dim = (size_t)n_kv_heads * HD, q_dim = (size_t)n_heads * HD;
+    const size_t head_off = (size_t)kvh * HD + lane * VEC;
+    float qv[VEC], acc[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+        qv[v] = q[j * q_dim + (size_t)h * HD + lane * VEC + v];
+        acc[v] = 0.0f;
+    }
+    float m_run = -INFINITY, l_run = 0.0f;
+    const uint32_t max_kv = start_pos + j + 1;
+    for (uint32_t t0 = 0; t0 < max_kv; t0 += 4) {
+        float kr[4][VEC], vr[4][VEC], sc[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (t0 + i < max_kv) {
+                load_row<VEC, F16>(kc, (t0 + i) * kv_dim + head_off, kr[i]);
+                load_row<VEC, F16>(vc, (t0 + i) * kv_dim + head_off, vr[i]);
+            } else {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) kr[i][v] = vr[i][v] = 0.0f;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float s = 0.0f;
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) s = fmaf(qv[v], kr[i][v], s);
+            sc[i] = s;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sc[i] += __shfl_xor_sync(0xffffffffu, sc[i], o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (t0 + i >= max_kv) break;
+            const float s = __fmul_rn(sc[i], scale);
+            const float m_new = fmaxf(m_run, s);
+            const float corr = m_run == -INFINITY ? 0.0f : ggml_expf(__fsub_rn(m_run, m_new));
+            const float pexp = ggml_expf(__fsub_rn(s, m_new));
+            l_run = fmaf(l_run, corr, pexp);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[v] = fmaf(pexp, vr[i][v], acc[v] * corr);
+            m_run = m_new;
+        }
+    }
+    const float inv = 1.0f / l_run;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) out[j * q_dim + (size_t)h * HD + lane * VEC + v] = acc[v] * inv;
+}
+
 template <int VEC, int G>
 int32_t launch_split(bool f16, dim3 grid, cudaStream_t st, const float *q, const void *kc, const void *vc,
                      uint32_t seq_len, const uint32_t *seq_dev, uint32_t n_kv, float scale, float *ws) {
@@ -291,6 +356,27 @@ int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *v
                       "attention merge launch");
 }
 
+int32_t launch_prefill_attention(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
+                                 size_t n_kv_heads, size_t head_dim, size_t n, size_t start_pos, float scale, float *out,
+                                 cudaStream_t st) {
+    if (!q || !kc || !vc || !out) return fail(CERA_CUDA_ERR_BAD_ARG, "prefill_attention: null argument");
+    if (n_kv_heads == 0 || n_heads % n_kv_heads) return fail(CERA_CUDA_ERR_BAD_ARG, "prefill_attention: bad head counts");
+    if (n == 0) return CERA_CUDA_OK;
+    const dim3 grid((unsigned)n_heads, (unsigned)((n + ATT_WARPS - 1) / ATT_WARPS));
+    const dim3 block(ATT_WARPS * 32);
+    const uint32_t nh = (uint32_t)n_heads, nkv = (uint32_t)n_kv_heads, nn = (uint32_t)n, sp = (uint32_t)start_pos;
+    count_launch();
+    if (head_dim == 128) {
+        if (kv_f16) return check_cuda(launch_k(attn_prefill_kernel<4, true>, grid, block, 0, st, q, kc, vc, nh, nkv, nn, sp, scale, out), "prefill attention launch");
+        return check_cuda(launch_k(attn_prefill_kernel<4, false>, grid, block, 0, st, q, kc, vc, nh, nkv, nn, sp, scale, out), "prefill attention launch");
+    }
+    if (head_dim == 64) {
+        if (kv_f16) return check_cuda(launch_k(attn_prefill_kernel<2, true>, grid, block, 0, st, q, kc, vc, nh, nkv, nn, sp, scale, out), "prefill attention launch");
+        return check_cuda(launch_k(attn_prefill_kernel<2, false>, grid, block, 0, st, q, kc, vc, nh, nkv, nn, sp, scale, out), "prefill attention launch");
+    }
+    return fail(CERA_CUDA_ERR_UNSUPPORTED, "prefill_attention: head_dim %zu has no kernel (64 or 128)", head_dim);
+}
+
 int32_t launch_decode_attention(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
                                 size_t n_kv_heads, size_t head_dim, size_t seq_len, float scale, float *out,
                                 void *workspace, size_t workspace_bytes, float *scales, int8_t *quants, int16_t *sums,
@@ -305,6 +391,13 @@ int32_t launch_decode_attention(const float *q, const void *kc, const void *vc, 
 using namespace cera;
 
 extern "C" {
+
+int32_t cera_cuda_prefill_attention(const float *q_dev, const void *k_cache_dev, const void *v_cache_dev, int32_t kv_f16,
+                                    size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t n, size_t start_pos,
+                                    float scale, float *out_dev, void *stream) {
+    return launch_prefill_attention(q_dev, k_cache_dev, v_cache_dev, kv_f16, n_heads, n_kv_heads, head_dim, n, start_pos,
+                                    scale, out_dev, (cudaStream_t)stream);
+}
 
 size_t cera_cuda_decode_attention_workspace_bytes(size_t n_heads, size_t head_dim, size_t seq_len) {
     return attn_workspace_bytes(n_heads, head_dim, seq_len);

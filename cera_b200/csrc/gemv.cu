@@ -35,6 +35,7 @@ struct GemvParams {
     ActView x;
     uint32_t k;
     uint32_t ldy;  // row stride of y in floats
+    uint32_t ldc;  // column stride of y in floats
     int epilogue;
 };
 
@@ -112,7 +113,10 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
         if (lane == 0) {
             float *y = p.y[s] + (size_t)local * p.ldy;
 #pragma unroll
-            for (int c = 0; c < NC; ++c) y[c] = p.epilogue == EPI_ADD ? __fadd_rn(y[c], acc[c]) : acc[c];
+            for (int c = 0; c < NC; ++c) {
+                float *yc = y + (size_t)c * p.ldc;
+                *yc = p.epilogue == EPI_ADD ? __fadd_rn(*yc, acc[c]) : acc[c];
+            }
         }
     }
 }
@@ -193,9 +197,9 @@ int32_t launch_gemv_fused(const GemvSeg *segs, int n_segs, const ActView &x, int
 
 // All segments must share the type and k.  n_cols in {1,2,4,8}.
 int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_cols, size_t ldy, int epilogue,
-                    cudaStream_t st) {
+                    cudaStream_t st, size_t ldc, bool batch_tile) {
     if (n_segs < 1 || n_segs > MAX_SEGS) return fail(CERA_CUDA_ERR_BAD_ARG, "gemv: %d segments", n_segs);
-    if (n_cols == 1 && ldy == 1 && !force_direct()) {
+    if (n_cols == 1 && ldy == 1 && !batch_tile && !force_direct()) {
         bool taken = false;
         CERA_TRY(launch_gemv_fused(segs, n_segs, x, epilogue, nullptr, st, &taken));
         if (taken) return CERA_CUDA_OK;
@@ -216,6 +220,7 @@ int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_
     p.k = segs[0].w.k;
     p.epilogue = epilogue;
     p.ldy = (uint32_t)ldy;
+    p.ldc = (uint32_t)ldc;
     if ((uintptr_t)x.quants % 16 || (uintptr_t)x.sums % 4 || (p.k % 32))
         return fail(CERA_CUDA_ERR_BAD_ARG, "gemv: activation quants must be 16-byte aligned and k a multiple of 32");
     CERA_DISPATCH_BLOCK_TYPE(segs[0].w.type, return (launch_cols<TT>(p, n_cols, st)));
@@ -224,19 +229,27 @@ int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_
 
 // Any n: column tiles of 8/4/2/1 through the multi-column GEMV.  Weights are
 // re-streamed once per tile, so this is the small-batch path; large batches
-// belong to the tensor-core GEMM.
-int32_t launch_gemm(const WeightView &w, const ActView &x, size_t n, float *out, cudaStream_t st) {
+// belong to the tensor-core GEMM.  Cell (row i, column j) goes to out[i*ldy + j*ldc]:
+// (ldy, ldc) = (n, 1) is the reference's row-major [m x n]; (1, m) is token-major.
+int32_t launch_gemm_ex(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
+                       cudaStream_t st) {
     const size_t k = w.k;
     size_t j = 0;
     while (j < n) {
         const size_t left = n - j;
         const size_t nc = left >= 8 ? 8 : left >= 4 ? 4 : left >= 2 ? 2 : 1;
-        GemvSeg seg{w, out + j};
+        GemvSeg seg{w, out + j * ldc};
         ActView xv{x.scales + j * (k / 32), x.quants + j * k, x.sums + j * (k / 16)};
-        CERA_TRY(launch_gemv(&seg, 1, xv, nc, n, EPI_STORE, st));
+        // Every tile of a batch runs the item-wise kernel, so a cell's arithmetic does not depend on how the
+        // columns were tiled; only the reference-layout single column (n == 1) takes the decode kernel.
+        CERA_TRY(launch_gemv(&seg, 1, xv, nc, ldy, epilogue, st, ldc, /*batch_tile=*/n > 1));
         j += nc;
     }
     return CERA_CUDA_OK;
+}
+
+int32_t launch_gemm(const WeightView &w, const ActView &x, size_t n, float *out, cudaStream_t st) {
+    return launch_gemm_ex(w, x, n, out, n, 1, EPI_STORE, st);
 }
 
 int32_t launch_gemv_q5k_f32(const WeightView &w, const float *x, float *y, cudaStream_t st) {

@@ -20,8 +20,12 @@ __global__ void rope_kernel(float *q, float *k, const float *__restrict__ v, uin
     const uint32_t half = hd / 2;
     const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
     const uint32_t total = (n_heads + n_kv_heads) * half;
-    const uint32_t pos = pos_dev ? *pos_dev : pos_imm;
+    // blockIdx.y walks a batch of tokens at consecutive positions (token-major q / k / v)
+    const uint32_t pos = (pos_dev ? *pos_dev : pos_imm) + blockIdx.y;
     const size_t kv_dim = (size_t)n_kv_heads * hd;
+    q += (size_t)blockIdx.y * n_heads * hd;
+    k += (size_t)blockIdx.y * kv_dim;
+    if (v) v += (size_t)blockIdx.y * kv_dim;
     if (idx < total) {
         const uint32_t h = idx / half, i = idx % half;
         float theta = (float)pos;
@@ -51,7 +55,7 @@ __global__ void rope_kernel(float *q, float *k, const float *__restrict__ v, uin
     }
     // v rows ride along: threads beyond the rotation pairs are not needed, reuse the same grid
     if (v_cache) {
-        for (size_t e = idx; e < kv_dim; e += (size_t)gridDim.x * blockDim.x) {
+        for (size_t e = idx; e < kv_dim; e += (size_t)gridDim.x * blockDim.x) {  // gridDim.x spans one token
             const size_t o = (size_t)pos * kv_dim + e;
             if (kv_f16) ((__half *)v_cache)[o] = __float2half_rn(v[e]);
             else ((float *)v_cache)[o] = v[e];
@@ -63,7 +67,8 @@ template <int T>
 __global__ void embed_kernel(WeightView w, uint32_t token_imm, const uint32_t *__restrict__ token_dev, float *out) {
     pdl_trigger();
     pdl_wait();
-    const uint32_t token = token_dev ? *token_dev : token_imm;
+    const uint32_t token = token_dev ? token_dev[blockIdx.y] : token_imm;  // blockIdx.y walks a batch of tokens
+    out += (size_t)blockIdx.y * w.k;
     const int items = w.k / 32;
     const int item = blockIdx.x * blockDim.x + threadIdx.x;
     if (item >= items || token >= w.m) return;
@@ -161,6 +166,30 @@ int32_t launch_embed(const WeightView &w, uint32_t token, const uint32_t *token_
     count_launch();
     CERA_DISPATCH_BLOCK_TYPE(w.type, return check_cuda(launch_k(embed_kernel<TT>, dim3((items + threads - 1) / threads), dim3(threads),
                                                                 0, st, w, token, token_dev, out), "embed launch"));
+    return CERA_CUDA_OK;
+}
+
+int32_t launch_rope_batch(float *q, float *k, const float *v, size_t start_pos, size_t n, size_t n_heads, size_t n_kv_heads,
+                          size_t head_dim, float theta_scale, const float *freq_factors, int rope_type, void *k_cache,
+                          void *v_cache, int kv_f16, cudaStream_t st) {
+    if (!q || !k) return fail(CERA_CUDA_ERR_BAD_ARG, "rope: null argument");
+    if (head_dim == 0 || head_dim % 2) return fail(CERA_CUDA_ERR_BAD_ARG, "rope: head_dim %zu must be even", head_dim);
+    if (n == 0) return CERA_CUDA_OK;
+    const uint32_t total = (uint32_t)((n_heads + n_kv_heads) * (head_dim / 2));
+    const int threads = 128;
+    count_launch();
+    return check_cuda(launch_k(rope_kernel, dim3((total + threads - 1) / threads, (unsigned)n), dim3(threads), 0, st, q, k, v,
+                               (uint32_t)start_pos, (const uint32_t *)nullptr, (uint32_t)n_heads, (uint32_t)n_kv_heads,
+                               (uint32_t)head_dim, theta_scale, freq_factors, rope_type == 1 ? 1 : 0, k_cache, v_cache, kv_f16),
+                      "rope launch");
+}
+
+int32_t launch_embed_batch(const WeightView &w, const uint32_t *tokens_dev, size_t n, float *out, cudaStream_t st) {
+    if (n == 0) return CERA_CUDA_OK;
+    const int items = w.k / 32, threads = 128;
+    count_launch();
+    CERA_DISPATCH_BLOCK_TYPE(w.type, return check_cuda(launch_k(embed_kernel<TT>, dim3((items + threads - 1) / threads, (unsigned)n),
+                                                                dim3(threads), 0, st, w, 0u, tokens_dev, out), "embed launch"));
     return CERA_CUDA_OK;
 }
 

@@ -40,6 +40,8 @@ struct Layer {
     void *kc = nullptr, *vc = nullptr;
 };
 
+constexpr size_t PREFILL_CHUNK = 256;
+
 enum GraphKind { G_BODY = 0, G_LOGITS = 1, G_GREEDY = 2, G_CHAIN = 3 };
 
 }  // namespace
@@ -71,6 +73,11 @@ struct cera_cuda_model {
     size_t seq_len = 0;
     uint64_t launches = 0;         // kernels launched by decode steps
     uint32_t nodes_per_step[4] = {0, 0, 0, 0};
+    // batched prefill (chunks of PREFILL_CHUNK tokens, token-major buffers)
+    uint32_t *pf_tokens = nullptr;
+    float *pf_hidden = nullptr, *pf_q = nullptr, *pf_k = nullptr, *pf_v = nullptr, *pf_attn = nullptr, *pf_g = nullptr,
+          *pf_u = nullptr;
+    ActBuf pf_act_hs, pf_act_q, pf_act_ff;
     uint32_t *tok_hist = nullptr;  // device ring of generated tokens (chained greedy decode)
     uint32_t tok_hist_cap = 0;
 };
@@ -226,6 +233,54 @@ int32_t run_token(cera_cuda_model *m, uint32_t token, size_t pos, int kind) {
     return CERA_CUDA_OK;
 }
 
+// One chunk (n <= PREFILL_CHUNK) of prompt tokens through every layer with batched kernels: column
+// RMSNorm + Q8_0, multi-column GEMMs (token-major outputs), batched RoPE + KV append, causal attention,
+// SiLU*mul + Q8_0 (cera/src/model/llama.rs:738-1523).  Leaves the hidden state of the chunk's last token
+// in m->hidden so the ordinary LM-head path can finish.
+int32_t prefill_chunk(cera_cuda_model *m, const uint32_t *tokens, size_t n, size_t start_pos) {
+    const auto &c = m->cfg;
+    cudaStream_t st = m->stream;
+    const size_t hs = c.hidden_size, qd = (size_t)c.n_heads * c.head_dim, kvd = (size_t)c.n_kv_heads * c.head_dim,
+                 ff = c.intermediate_size;
+    const float scale = 1.0f / sqrtf((float)c.head_dim);
+    CERA_CUDA_TRY(cudaMemcpyAsync(m->pf_tokens, tokens, n * 4, cudaMemcpyHostToDevice, st));
+    CERA_TRY(launch_embed_batch(m->embd->v, m->pf_tokens, n, m->pf_hidden, st));
+    const uint64_t before = launches_so_far();
+    for (auto &L : m->layers) {
+        CERA_TRY(launch_rmsnorm(m->pf_hidden, L.attn_norm, hs, n, c.rms_norm_eps, nullptr, m->pf_act_hs.scales,
+                                m->pf_act_hs.quants, m->pf_act_hs.sums, st));
+        CERA_TRY(launch_gemm_ex(L.wq->v, m->pf_act_hs.view(), n, m->pf_q, 1, qd, EPI_STORE, st));
+        CERA_TRY(launch_gemm_ex(L.wk->v, m->pf_act_hs.view(), n, m->pf_k, 1, kvd, EPI_STORE, st));
+        CERA_TRY(launch_gemm_ex(L.wv->v, m->pf_act_hs.view(), n, m->pf_v, 1, kvd, EPI_STORE, st));
+        CERA_TRY(launch_rope_batch(m->pf_q, m->pf_k, m->pf_v, start_pos, n, c.n_heads, c.n_kv_heads, c.head_dim,
+                                   m->theta_scale, m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st));
+        CERA_TRY(launch_prefill_attention(m->pf_q, L.kc, L.vc, c.kv_f16, c.n_heads, c.n_kv_heads, c.head_dim, n, start_pos,
+                                          scale, m->pf_attn, st));
+        CERA_TRY(launch_quantize(m->pf_attn, qd, n, false, m->pf_act_q.scales, m->pf_act_q.quants, m->pf_act_q.sums, st));
+        CERA_TRY(launch_gemm_ex(L.wo->v, m->pf_act_q.view(), n, m->pf_hidden, 1, hs, EPI_ADD, st));
+        CERA_TRY(launch_rmsnorm(m->pf_hidden, L.ffn_norm, hs, n, c.rms_norm_eps, nullptr, m->pf_act_hs.scales,
+                                m->pf_act_hs.quants, m->pf_act_hs.sums, st));
+        CERA_TRY(launch_gemm_ex(L.gate->v, m->pf_act_hs.view(), n, m->pf_g, 1, ff, EPI_STORE, st));
+        CERA_TRY(launch_gemm_ex(L.up->v, m->pf_act_hs.view(), n, m->pf_u, 1, ff, EPI_STORE, st));
+        CERA_TRY(launch_silu_mul(m->pf_g, m->pf_u, ff, n, m->pf_act_ff.scales, m->pf_act_ff.quants, m->pf_act_ff.sums, st));
+        CERA_TRY(launch_gemm_ex(L.down->v, m->pf_act_ff.view(), n, m->pf_hidden, 1, hs, EPI_ADD, st));
+    }
+    CERA_CUDA_TRY(cudaMemcpyAsync(m->hidden, m->pf_hidden + (n - 1) * hs, hs * 4, cudaMemcpyDeviceToDevice, st));
+    m->launches += launches_so_far() - before + 1;
+    return CERA_CUDA_OK;
+}
+
+// Final RMSNorm + LM head on m->hidden (eager launches on the model's stream).
+int32_t logits_from_hidden(cera_cuda_model *m) {
+    const auto &c = m->cfg;
+    CERA_TRY(launch_rmsnorm(m->hidden, m->out_norm, c.hidden_size, 1, c.rms_norm_eps, m->final_hidden, m->act_hs.scales,
+                            m->act_hs.quants, m->act_hs.sums, m->stream));
+    const cera_cuda_weight *ow = m->output ? m->output : m->embd;
+    GemvSeg sl{ow->v, m->logits};
+    m->launches += 2;
+    return launch_gemv(&sl, 1, m->act_hs.view(), 1, 1, EPI_STORE, m->stream);
+}
+
 struct DeviceGuard {
     int prev = 0;
     explicit DeviceGuard(int dev) {
@@ -337,6 +392,20 @@ int32_t cera_cuda_model_finalize(cera_cuda_model *m) {
     CERA_TRY(alloc_act(m, m->act_hs, hs));
     CERA_TRY(alloc_act(m, m->act_q, qd));
     CERA_TRY(alloc_act(m, m->act_ff, ff));
+    {
+        const size_t C = PREFILL_CHUNK;
+        CERA_TRY(dev_alloc(m, (void **)&m->pf_tokens, C * 4));
+        CERA_TRY(dev_alloc(m, (void **)&m->pf_hidden, C * hs * 4));
+        CERA_TRY(dev_alloc(m, (void **)&m->pf_q, C * qd * 4));
+        CERA_TRY(dev_alloc(m, (void **)&m->pf_k, C * kvd * 4));
+        CERA_TRY(dev_alloc(m, (void **)&m->pf_v, C * kvd * 4));
+        CERA_TRY(dev_alloc(m, (void **)&m->pf_attn, C * qd * 4));
+        CERA_TRY(dev_alloc(m, (void **)&m->pf_g, C * ff * 4));
+        CERA_TRY(dev_alloc(m, (void **)&m->pf_u, C * ff * 4));
+        CERA_TRY(alloc_act(m, m->pf_act_hs, C * hs));
+        CERA_TRY(alloc_act(m, m->pf_act_q, C * qd));
+        CERA_TRY(alloc_act(m, m->pf_act_ff, C * ff));
+    }
     m->attn_ws_bytes = attn_workspace_bytes(c.n_heads, c.head_dim, c.max_seq_len);
     CERA_TRY(dev_alloc(m, &m->attn_ws, m->attn_ws_bytes));
     CERA_TRY(dev_alloc(m, (void **)&m->argmax_scratch, argmax_scratch_words() * 4));
@@ -383,14 +452,33 @@ int32_t cera_cuda_forward_prefill(cera_cuda_model *m, const uint32_t *tokens, si
     DeviceGuard dg(m->cfg.device);
     if (start_pos != m->seq_len) return fail(CERA_CUDA_ERR_STATE, "forward_prefill: start_pos %zu != seq_len %zu", start_pos, m->seq_len);
     if (n == 0) return CERA_CUDA_OK;
-    // Per-token arithmetic for every prompt position: identical to decode, which is the
-    // reference's canonical stream (its batched kernels are held to the same per-cell
-    // arithmetic).  The host buffer h_dyn is rewritten per token, so wait for the copy
-    // of the previous one before touching it again.
-    for (size_t i = 0; i < n; ++i) {
-        const bool last = i + 1 == n;
-        CERA_TRY(run_token(m, tokens[i], start_pos + i, last && logits_out ? G_LOGITS : G_BODY));
-        CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    const auto &c = m->cfg;
+    if (!m->finalized) return fail(CERA_CUDA_ERR_STATE, "forward_prefill: model_finalize has not been called");
+    if (start_pos + n > c.max_seq_len)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "forward_prefill: %zu tokens from %zu exceed max_seq_len %u", n, start_pos, c.max_seq_len);
+    for (size_t i = 0; i < n; ++i)
+        if (tokens[i] >= c.vocab_size) return fail(CERA_CUDA_ERR_BAD_ARG, "forward_prefill: token %u out of range", tokens[i]);
+    static const bool per_token = [] {
+        const char *e = getenv("CERA_CUDA_PREFILL");
+        return e && strcmp(e, "per_token") == 0;
+    }();
+    if (per_token || n < 2) {
+        // Decode arithmetic for every prompt position (one graph launch per token).  h_dyn is rewritten per
+        // token, so wait for the copy of the previous one before touching it again.
+        for (size_t i = 0; i < n; ++i) {
+            const bool last = i + 1 == n;
+            CERA_TRY(run_token(m, tokens[i], start_pos + i, last && logits_out ? G_LOGITS : G_BODY));
+            CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+        }
+    } else {
+        // Batched kernels, PREFILL_CHUNK tokens at a time (the reference's ubatch loop, cera/src/model/mod.rs:303-332).
+        for (size_t done = 0; done < n; done += PREFILL_CHUNK) {
+            const size_t cn = n - done < PREFILL_CHUNK ? n - done : PREFILL_CHUNK;
+            CERA_TRY(prefill_chunk(m, tokens + done, cn, start_pos + done));
+            CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));  // the host token slice may go away after the call
+        }
+        m->seq_len = start_pos + n;
+        if (logits_out) CERA_TRY(logits_from_hidden(m));
     }
     if (logits_out) {
         const size_t bytes = (size_t)m->cfg.vocab_size * 4;

@@ -33,7 +33,9 @@ struct GemvFusion {
     uint32_t head_dim = 0, kv_dim = 0;
 };
 int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_cols, size_t ldy, int epilogue,
-                    cudaStream_t st);
+                    cudaStream_t st, size_t ldc = 1, bool batch_tile = false);
+int32_t launch_gemm_ex(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
+                       cudaStream_t st);
 // Register-resident-activation single-column GEMV.  *taken = false: shape outside its rules,
 // nothing was launched and the caller uses the item-wise kernel.
 int32_t launch_gemv_rows(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
@@ -72,6 +74,18 @@ int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *v
                                    float *scales, int8_t *quants, int16_t *sums, cudaStream_t st);
 
 int32_t launch_embed(const WeightView &w, uint32_t token, const uint32_t *token_dev, float *out, cudaStream_t st);
+// n rows: out[j][k] = row tokens_dev[j] of the table.
+int32_t launch_embed_batch(const WeightView &w, const uint32_t *tokens_dev, size_t n, float *out, cudaStream_t st);
+// n tokens at positions start_pos + j: q is [n][n_heads*head_dim], k and v are [n][n_kv_heads*head_dim]
+// (token-major); rotated k and v rows are appended to the caches.
+int32_t launch_rope_batch(float *q, float *k, const float *v, size_t start_pos, size_t n, size_t n_heads, size_t n_kv_heads,
+                          size_t head_dim, float theta_scale, const float *freq_factors, int rope_type, void *k_cache,
+                          void *v_cache, int kv_f16, cudaStream_t st);
+// Causal attention of n query tokens (positions start_pos + j) over cache rows [0, start_pos + j]
+// (cera/src/backend/cpu.rs:4028-4241); q and out are token-major [n][n_heads*head_dim].
+int32_t launch_prefill_attention(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
+                                 size_t n_kv_heads, size_t head_dim, size_t n, size_t start_pos, float scale, float *out,
+                                 cudaStream_t st);
 // First strict maximum (cera/src/sampler.rs:20-30).  scratch: 2*blocks words, see argmax_scratch_words().
 size_t argmax_scratch_words();
 int32_t launch_argmax(const float *x, size_t n, uint32_t *out, uint32_t *scratch, cudaStream_t st);

@@ -162,6 +162,17 @@ def decode_attention(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim, seq_len
     return out
 
 
+def prefill_attention(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim, n, start_pos, scale):
+    """Causal attention of n prompt tokens; q is token-major [n][n_heads*head_dim]
+    (cera/src/backend/cpu.rs:4028-4241 flash_attention_gqa_cpu)."""
+    q = _dev(q, torch.float32)
+    f16 = k_cache.dtype == torch.float16
+    out = torch.empty(n * n_heads * head_dim, dtype=torch.float32, device=q.device)
+    check(lib.cera_cuda_prefill_attention(_ptr(q), _ptr(k_cache), _ptr(v_cache), int(f16), n_heads, n_kv_heads, head_dim, n,
+                                          start_pos, scale, _ptr(out), _stream()))
+    return out.reshape(n, n_heads * head_dim)
+
+
 def decode_attention_noalloc(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim, seq_len, scale, out=None):
     """decode_attention for callers that may not allocate device memory: the split-KV workspace is the
     library's built-in array (n_heads <= 64, head_dim <= 128).  Pass `out` to make the call allocation-free

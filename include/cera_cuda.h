@@ -152,6 +152,14 @@ CERA_API int32_t cera_cuda_decode_attention(const float *q_dev, const void *k_ca
                                             float scale, float *out_dev, void *workspace_dev,
                                             size_t workspace_bytes, void *stream);
 
+/* Causal attention of n prompt tokens (cera/src/backend/cpu.rs:4028-4241 flash_attention_gqa_cpu):
+ * query j sits at position start_pos + j and attends to cache rows [0, start_pos + j].  q_dev and
+ * out_dev are token-major [n][n_heads*head_dim]; the caches already hold rows up to start_pos + n. */
+CERA_API int32_t cera_cuda_prefill_attention(const float *q_dev, const void *k_cache_dev,
+                                             const void *v_cache_dev, int32_t kv_f16, size_t n_heads,
+                                             size_t n_kv_heads, size_t head_dim, size_t n,
+                                             size_t start_pos, float scale, float *out_dev, void *stream);
+
 /* No counterpart in the reference.  The same attention for callers that cannot allocate device
  * memory (an embedding engine that owns the device heap, a thread on which allocation is forbidden,
  * a process with a frozen memory budget): the split-KV workspace is a fixed 2.1 MB array inside the

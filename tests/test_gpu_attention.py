@@ -104,3 +104,22 @@ def test_decode_attention_rejects_unsupported_shapes():
     with pytest.raises(cb.CeraCudaError) as e:
         cb.decode_attention(q, kc, kc, 6, 2, 64, 4, 0.125)
     assert e.value.code == 2
+
+
+@pytest.mark.parametrize("f16", [False, True])
+def test_prefill_attention_matches_flash_oracle(f16):
+    torch = need_gpu()
+    import cera_b200 as cb
+    nh, nkv, hd, n, start = 8, 2, 128, 70, 37   # the reference's own flash test uses n=70, start_pos 37
+    total = start + n
+    kc = cb.synth_normal(total * nkv * hd, seed=1, sigma=1.0).reshape(total, nkv * hd)
+    vc = cb.synth_normal(total * nkv * hd, seed=2, sigma=1.0).reshape(total, nkv * hd)
+    q = cb.synth_normal(n * nh * hd, seed=3, sigma=1.0).reshape(n, nh * hd)
+    scale = 1.0 / math.sqrt(hd)
+    kk, vv = (kc.half(), vc.half()) if f16 else (kc, vc)
+    got = cb.prefill_attention(q, kk, vv, nh, nkv, hd, n, start, scale).cpu().numpy()  # [n][nh*hd]
+    kf, vf = kk.float().cpu().numpy(), vv.float().cpu().numpy()
+    qm = np.ascontiguousarray(q.cpu().numpy().T)  # oracle layout: [q_dim x n]
+    want = O.flash_attention_gqa(qm, kf, vf, nh, nkv, hd, n, start, scale)  # [nh][n][hd]
+    want = np.ascontiguousarray(want.transpose(1, 0, 2)).reshape(n, nh * hd)
+    assert_close(got, want, f"prefill attention f16={f16}")

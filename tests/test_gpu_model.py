@@ -108,6 +108,33 @@ def test_wide_llama_matches_oracle(kv_f16):
     assert compare_greedy_streams(stream_g, stream_o, lambda i: logits_o[i]) >= 4
 
 
+def test_batched_prefill_matches_oracle_and_crosses_a_chunk_boundary():
+    """300 prompt tokens = one full 256-token chunk + a ragged one, through the batched kernels; the last-token logits
+    against the oracle's per-token forward, then decode continues from the batched KV cache."""
+    need_gpu()
+    from cera_b200 import synth
+    gpu, oracle = _pair(SMALL, seed=13, max_seq_len=320, threads=4)
+    prompt = synth.prompt_tokens(300, SMALL["vocab_size"], seed=6)
+    lp = gpu.forward_prefill(prompt, 0)
+    for pos, t in enumerate(prompt):
+        lo = oracle.forward(int(t), pos)
+    assert_model_logits(lp, lo, "batched prefill, 300 tokens")
+    tok = int(O.argmax(lo))
+    assert_model_logits(gpu.forward(tok, 300), oracle.forward(tok, 300), "decode after batched prefill")
+
+
+def test_batched_prefill_wide_model_and_f16_kv():
+    need_gpu()
+    from cera_b200 import synth
+    for kv_f16 in (0, 1):
+        gpu, oracle = _pair(WIDE, seed=17, threads=4, kv_f16=kv_f16)
+        prompt = synth.prompt_tokens(21, WIDE["vocab_size"], seed=8)
+        lp = gpu.forward_prefill(prompt, 0)
+        for pos, t in enumerate(prompt):
+            lo = oracle.forward(int(t), pos)
+        assert_model_logits(lp, lo, f"batched prefill kv_f16={kv_f16}")
+
+
 def test_generate_greedy_equals_stepwise_greedy():
     need_gpu()
     gpu, _ = _pair(SMALL, seed=9)
