@@ -231,6 +231,32 @@ def gemv_microbench(torch, cb, tname, m, k, iters):
     return algo, us, 2 * iters + copies
 
 
+def gemm_microbench(torch, cb, tname, m, k, n, iters):
+    """Prefill GEMM out[m x n] = W x X for pre-quantized columns: CUDA events over a graph of `iters` launches."""
+    t, blk, bb = BLOCKS[tname]
+    w = cb.QuantWeight(t, m, k, cb.quantize_weights(t, cb.synth_normal(m * k, seed=3, sigma=0.02)))
+    acts = cb.quantize_q8_0(cb.synth_normal(n * k, seed=5, sigma=1.0), k=k, n=n)
+    out = torch.empty(m, n, device="cuda")
+    cb.gemm_preq(w, acts, out)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(iters):
+                cb.gemm_preq(w, acts, out)
+        graph.replay()
+        side.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(side)
+        graph.replay()
+        e1.record(side)
+        side.synchronize()
+    us = e0.elapsed_time(e1) * 1000.0 / iters
+    w.close()
+    return 2.0 * m * n * k, us
+
+
 def roofline_q4k_gemv(torch, cb, iters):
     """The dominant kernel of the decode step: the Q4_K GEMV at the gate/up shape."""
     return gemv_microbench(torch, cb, "q4_k", 14336, 4096, iters)
@@ -357,7 +383,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
                     help="prompt tokens before the timed decode (512 is the benchmark; shorter only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--only", default=None, choices=["roofline", "gemv-sweep"],
+    ap.add_argument("--only", default=None, choices=["roofline", "gemv-sweep", "gemm-sweep"],
                     help="run just the dominant-kernel microbench (the case ncu captures are taken on)")
     ap.add_argument("--iters", type=int, default=200, help="timed launches of the kernel microbench")
     args = ap.parse_args()
@@ -380,6 +406,15 @@ def main():
             print(json.dumps({"type": tname, "m": m, "k": k, "us": round(us, 3), "algorithmic_bytes": algo,
                               "gbs": round(algo / us / 1e3, 1), "frac_of_measured": round(algo / us / 1e3 / hbm, 4),
                               "frac_of_8000": round(algo / us / 1e3 / 8000.0, 4)}), flush=True)
+    elif args.only == "gemm-sweep":
+        import torch
+        import cera_b200 as cb
+        for tname, m, k in [("q4_k", 4096, 4096), ("q4_k", 14336, 4096), ("q6_k", 4096, 14336), ("q5_k", 4096, 4096)]:
+            for n in (8, 64, 512):
+                ops, us = gemm_microbench(torch, cb, tname, m, k, n, max(3, args.iters // (4 if n > 64 else 1)))
+                print(json.dumps({"type": tname, "m": m, "k": k, "n": n, "us": round(us, 2),
+                                  "tops": round(ops / us / 1e6, 2), "frac_of_int8_nominal_4500": round(ops / us / 1e6 / 4500, 4)}),
+                      flush=True)
     elif args.impl == "reference":
         reference_arm(args, rank)
     else:

@@ -1,0 +1,276 @@
+// Prefill GEMM on the integer tensor-core path: out[m x n] = W (Q4_K or Q6_K) x X (Q8_0 columns), n >= 16.
+//
+// A CTA owns a 64-row x 128-column output tile and walks k one 256-element super-block at a time:
+// weights of the 64 rows and the Q8_0 quants of the 128 columns are staged in shared memory with
+// cp.async, the six-bit / int8 sub-block scales are expanded to f32 once per chunk, and every warp
+// (16 rows x 64 columns) issues mma.sync int8 instructions whose int32 results are EXACT per-block sums:
+//   Q4_K : m16n8k32 (u8 x s8) per 32-element sub-block,  out += (d*sc) * xs * U - (dmin*mn) * (xs*A32)
+//   Q6_K : m16n8k16 (u8 x s8) per 16-element scale group, out += (d*sc) * (xs*U - 32*xs*A16)
+// Each int32 tile is scaled and folded into f32 accumulators on the CUDA cores right after its mma:
+// with one scale pair per (row, block, column) that per-block rescale, not the tensor pipe, bounds the
+// throughput of an exact kernel (about 20 CUDA-core instructions per 4096 multiply-adds).
+// This is the warp-level (mma.sync) form; the same tiling moved onto tcgen05 with TMEM accumulators
+// would free the issue slots the mma instructions take here, but keeps the same rescale bound.
+//
+// Arithmetic contract: cera/src/backend/simd.rs:5693-5878 (Q4_K) and 5988-6195 (Q6_K), per cell; the
+// f32 order is this kernel's own (blocks in k order per thread).
+#include <cstdlib>
+#include <cstring>
+
+#include "act.cuh"
+#include "ops.h"
+
+namespace cera {
+
+namespace {
+
+constexpr int GM_BM = 64, GM_BN = 128, GM_THREADS = 256;
+constexpr int GM_WQ_STRIDE = 144;   // 128 quant bytes per row, padded so 8 rows x 4 words hit 32 banks
+constexpr int GM_WH_STRIDE = 80;    // Q6_K high-bit plane: 64 bytes per row, padded likewise
+constexpr int GM_AQ_STRIDE = 272;   // 256 activation quants per column, padded likewise
+
+struct GemmParams {
+    WeightView w;
+    ActView x;
+    float *out;
+    uint32_t m, n, k;
+    uint32_t ldy, ldc;
+    int epilogue;
+};
+
+__device__ __forceinline__ void cpa16(void *smem, const void *gmem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cpa_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// D(16x8, s32) = A(16x32, u8, row) * B(32x8, s8, col)
+__device__ __forceinline__ void mma_u8s8_k32(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+// D(16x8, s32) = A(16x16, u8, row) * B(16x8, s8, col)
+__device__ __forceinline__ void mma_u8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+
+template <int T>
+__global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    // shared-memory carve-up
+    uint8_t *wq = smem;                                            // [64][144]
+    uint8_t *wqh = wq + GM_BM * GM_WQ_STRIDE;                      // [64][80]   (Q6_K)
+    uint8_t *whd = wqh + GM_BM * GM_WH_STRIDE;                     // [64][16]   raw header / int8 scales
+    float *wsc = reinterpret_cast<float *>(whd + GM_BM * 16);      // [64][16]   d*sc per sub-block (Q4_K uses 8)
+    float *wmn = wsc + GM_BM * 16;                                 // [64][8]    dmin*mn (Q4_K)
+    uint8_t *aq = reinterpret_cast<uint8_t *>(wmn + GM_BM * 8);    // [128][272]
+    float *axs = reinterpret_cast<float *>(aq + GM_BN * GM_AQ_STRIDE);  // [8][128]  block scales
+    float *axb = axs + 8 * GM_BN;                                  // [16][128] xs*A32 (Q4_K, 8 used) or -32*xs*A16 (Q6_K)
+
+    pdl_trigger();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int wrow = (warp & 3) * 16, wcol = (warp >> 2) * 64;  // this warp's 16 x 64 patch of the tile
+    const uint32_t row0 = blockIdx.x * GM_BM, col0 = blockIdx.y * GM_BN;
+    const uint32_t nb = p.w.nb, nb32 = p.k >> 5, nb16 = p.k >> 4;
+    const TypeInfo ti = type_info(T);
+
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
+
+    for (uint32_t bi = 0; bi < nb; ++bi) {
+        // ---- stage the chunk: weights of 64 rows, activations of 128 columns (rows / columns past the
+        // edge are clamped to the last valid one; their results are never stored)
+        for (int i = tid; i < GM_BM * 8; i += GM_THREADS) {
+            const int r = i >> 3, pc = i & 7;
+            const uint32_t row = min(row0 + r, p.m - 1);
+            const uint8_t *src = p.w.q + (size_t)row * nb * ti.q_b + q_piece_off(p.w.t128, 4, bi * 8 + pc);
+            cpa16(wq + r * GM_WQ_STRIDE + pc * 16, src);
+        }
+        if (T == CERA_TYPE_Q6_K) {
+            for (int i = tid; i < GM_BM * 4; i += GM_THREADS) {
+                const int r = i >> 2, pc = i & 3;
+                const uint32_t row = min(row0 + r, p.m - 1);
+                cpa16(wqh + r * GM_WH_STRIDE + pc * 16, p.w.qh + ((size_t)row * nb + bi) * 64 + pc * 16);
+            }
+        }
+        for (int r = tid; r < GM_BM; r += GM_THREADS) {
+            const uint32_t row = min(row0 + r, p.m - 1);
+            cpa16(whd + r * 16, p.w.hdr + ((size_t)row * nb + bi) * 16);
+        }
+        for (int i = tid; i < GM_BN * 16; i += GM_THREADS) {
+            const int c = i >> 4, pc = i & 15;
+            const uint32_t col = min(col0 + c, p.n - 1);
+            cpa16(aq + c * GM_AQ_STRIDE + pc * 16, p.x.quants + (size_t)col * p.k + (size_t)bi * 256 + pc * 16);
+        }
+        for (int i = tid; i < GM_BN * 8; i += GM_THREADS) {
+            const int c = i & (GM_BN - 1), s = i >> 7;
+            const uint32_t col = min(col0 + c, p.n - 1);
+            const float xs = p.x.scales[(size_t)col * nb32 + bi * 8 + s];
+            const int16_t *sm = p.x.sums + (size_t)col * nb16 + (bi * 8 + s) * 2;
+            axs[s * GM_BN + c] = xs;
+            if (T == CERA_TYPE_Q4_K) {
+                axb[s * GM_BN + c] = xs * (float)((int)sm[0] + (int)sm[1]);
+            } else {
+                axb[(2 * s) * GM_BN + c] = -32.0f * (xs * (float)sm[0]);
+                axb[(2 * s + 1) * GM_BN + c] = -32.0f * (xs * (float)sm[1]);
+            }
+        }
+        cpa_wait_all();
+        __syncthreads();
+        // ---- expand the sub-block scales of the 64 rows to f32
+        if (T == CERA_TYPE_Q4_K) {
+            for (int i = tid; i < GM_BM * 8; i += GM_THREADS) {
+                const int r = i >> 3, s = i & 7;
+                const uint8_t *h = whd + r * 16;
+                int sc, mn;
+                kscale(h + 4, s, sc, mn);
+                const float d = h2f((uint16_t)(h[0] | (h[1] << 8))), dmin = h2f((uint16_t)(h[2] | (h[3] << 8)));
+                wsc[r * 16 + s] = d * (float)sc;
+                wmn[r * 8 + s] = dmin * (float)mn;
+            }
+        } else {
+            for (int i = tid; i < GM_BM * 16; i += GM_THREADS) {
+                const int r = i >> 4, e = i & 15;
+                const uint32_t row = min(row0 + r, p.m - 1);
+                const float d = h2f(reinterpret_cast<const uint16_t *>(p.w.d)[(size_t)row * nb + bi]);
+                wsc[r * 16 + e] = d * (float)(int8_t)whd[r * 16 + e];
+            }
+        }
+        __syncthreads();
+
+        // ---- tensor-core work of this chunk
+        const uint8_t *qa = wq + (wrow + gid) * GM_WQ_STRIDE, *qb = qa + 8 * GM_WQ_STRIDE;
+        if (T == CERA_TYPE_Q4_K) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                // 32-byte group g: low nibbles = sub-block 2g, high nibbles = sub-block 2g+1; byte l = element l
+                const uint32_t wa0 = *reinterpret_cast<const uint32_t *>(qa + 32 * g + 4 * tig);
+                const uint32_t wa1 = *reinterpret_cast<const uint32_t *>(qa + 32 * g + 16 + 4 * tig);
+                const uint32_t wb0 = *reinterpret_cast<const uint32_t *>(qb + 32 * g + 4 * tig);
+                const uint32_t wb1 = *reinterpret_cast<const uint32_t *>(qb + 32 * g + 16 + 4 * tig);
+#pragma unroll
+                for (int hi = 0; hi < 2; ++hi) {
+                    const int s = 2 * g + hi, sh = 4 * hi;
+                    const uint32_t a[4] = {(wa0 >> sh) & 0x0F0F0F0Fu, (wb0 >> sh) & 0x0F0F0F0Fu, (wa1 >> sh) & 0x0F0F0F0Fu,
+                                           (wb1 >> sh) & 0x0F0F0F0Fu};
+                    const float sca = wsc[(wrow + gid) * 16 + s], scb = wsc[(wrow + gid + 8) * 16 + s];
+                    const float mna = wmn[(wrow + gid) * 8 + s], mnb = wmn[(wrow + gid + 8) * 8 + s];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int cb = wcol + 8 * j;  // this n-tile's first column inside the CTA tile
+                        const uint8_t *bp = aq + (cb + gid) * GM_AQ_STRIDE + 32 * s + 4 * tig;
+                        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp);
+                        const uint32_t b1 = *reinterpret_cast<const uint32_t *>(bp + 16);
+                        int c[4];
+                        mma_u8s8_k32(c, a, b0, b1);
+                        const float2 xs = *reinterpret_cast<const float2 *>(axs + s * GM_BN + cb + 2 * tig);
+                        const float2 xb = *reinterpret_cast<const float2 *>(axb + s * GM_BN + cb + 2 * tig);
+                        acc[j][0] = fmaf(sca * xs.x, (float)c[0], fmaf(-mna, xb.x, acc[j][0]));
+                        acc[j][1] = fmaf(sca * xs.y, (float)c[1], fmaf(-mna, xb.y, acc[j][1]));
+                        acc[j][2] = fmaf(scb * xs.x, (float)c[2], fmaf(-mnb, xb.x, acc[j][2]));
+                        acc[j][3] = fmaf(scb * xs.y, (float)c[3], fmaf(-mnb, xb.y, acc[j][3]));
+                    }
+                }
+            }
+        } else {
+            const uint8_t *ha = wqh + (wrow + gid) * GM_WH_STRIDE, *hb = ha + 8 * GM_WH_STRIDE;
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                // scale group e = 8*nh + 2*g + half: elements [16e, 16e+16) of the super-block
+                const int nh = e >> 3, g = (e >> 1) & 3, half = e & 1;
+                const int qo = 64 * nh + 32 * (g & 1) + 16 * half + 4 * tig, ho = 32 * nh + 16 * half + 4 * tig;
+                const int nsh = g >= 2 ? 4 : 0;
+                const uint32_t la = *reinterpret_cast<const uint32_t *>(qa + qo), lb = *reinterpret_cast<const uint32_t *>(qb + qo);
+                const uint32_t hha = *reinterpret_cast<const uint32_t *>(ha + ho), hhb = *reinterpret_cast<const uint32_t *>(hb + ho);
+                const uint32_t a0 = ((la >> nsh) & 0x0F0F0F0Fu) | (((hha >> (2 * g)) & 0x03030303u) << 4);
+                const uint32_t a1 = ((lb >> nsh) & 0x0F0F0F0Fu) | (((hhb >> (2 * g)) & 0x03030303u) << 4);
+                const float sca = wsc[(wrow + gid) * 16 + e], scb = wsc[(wrow + gid + 8) * 16 + e];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int cb = wcol + 8 * j;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t *>(aq + (cb + gid) * GM_AQ_STRIDE + 16 * e + 4 * tig);
+                    int c[4];
+                    mma_u8s8_k16(c, a0, a1, b0);
+                    const float2 xs = *reinterpret_cast<const float2 *>(axs + (e >> 1) * GM_BN + cb + 2 * tig);
+                    const float2 xb = *reinterpret_cast<const float2 *>(axb + e * GM_BN + cb + 2 * tig);
+                    acc[j][0] = fmaf(sca, fmaf(xs.x, (float)c[0], xb.x), acc[j][0]);
+                    acc[j][1] = fmaf(sca, fmaf(xs.y, (float)c[1], xb.y), acc[j][1]);
+                    acc[j][2] = fmaf(scb, fmaf(xs.x, (float)c[2], xb.x), acc[j][2]);
+                    acc[j][3] = fmaf(scb, fmaf(xs.y, (float)c[3], xb.y), acc[j][3]);
+                }
+            }
+        }
+        __syncthreads();  // the staging buffers are rewritten by the next chunk
+    }
+
+    // ---- store: cell (row, col) at out[row*ldy + col*ldc]
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t row = row0 + wrow + gid + (i >= 2 ? 8 : 0);
+            const uint32_t col = col0 + wcol + 8 * j + 2 * tig + (i & 1);
+            if (row < p.m && col < p.n) {
+                float *y = p.out + (size_t)row * p.ldy + (size_t)col * p.ldc;
+                *y = p.epilogue == EPI_ADD ? __fadd_rn(*y, acc[j][i]) : acc[j][i];
+            }
+        }
+}
+
+constexpr size_t GM_SMEM = GM_BM * GM_WQ_STRIDE + GM_BM * GM_WH_STRIDE + GM_BM * 16 + GM_BM * 16 * 4 + GM_BM * 8 * 4 +
+                           GM_BN * GM_AQ_STRIDE + 8 * GM_BN * 4 + 16 * GM_BN * 4;
+
+template <int T>
+int32_t launch_mma_typed(const GemmParams &p, cudaStream_t st) {
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        CERA_CUDA_TRY(cudaFuncSetAttribute(gemm_mma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM));
+        configured_dev = dev;
+    }
+    const dim3 grid((p.m + GM_BM - 1) / GM_BM, (p.n + GM_BN - 1) / GM_BN);
+    count_launch();
+    return check_cuda(launch_k(gemm_mma_kernel<T>, grid, dim3(GM_THREADS), GM_SMEM, st, p), "gemm (mma) launch");
+}
+
+}  // namespace
+
+// Tensor-core GEMM for Q4_K / Q6_K weights and n >= 16 columns.  *taken = false: not this kernel's case.
+int32_t launch_gemm_mma(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
+                        cudaStream_t st, bool *taken) {
+    *taken = false;
+    static const bool off = [] {
+        const char *e = getenv("CERA_CUDA_GEMM");
+        return e && strcmp(e, "columns") == 0;
+    }();
+    if (off || n < 16 || (w.type != CERA_TYPE_Q4_K && w.type != CERA_TYPE_Q6_K) || w.k % 256) return CERA_CUDA_OK;
+    if ((uintptr_t)x.quants % 16 || w.k % 16) return CERA_CUDA_OK;
+    GemmParams p{};
+    p.w = w;
+    p.x = x;
+    p.out = out;
+    p.m = w.m;
+    p.n = (uint32_t)n;
+    p.k = w.k;
+    p.ldy = (uint32_t)ldy;
+    p.ldc = (uint32_t)ldc;
+    p.epilogue = epilogue;
+    *taken = true;
+    if (w.type == CERA_TYPE_Q4_K) return launch_mma_typed<CERA_TYPE_Q4_K>(p, st);
+    return launch_mma_typed<CERA_TYPE_Q6_K>(p, st);
+}
+
+}  // namespace cera

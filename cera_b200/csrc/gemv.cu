@@ -234,6 +234,11 @@ int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_
 int32_t launch_gemm_ex(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
                        cudaStream_t st) {
     const size_t k = w.k;
+    {
+        bool taken = false;
+        CERA_TRY(launch_gemm_mma(w, x, n, out, ldy, ldc, epilogue, st, &taken));
+        if (taken) return CERA_CUDA_OK;
+    }
     size_t j = 0;
     while (j < n) {
         const size_t left = n - j;

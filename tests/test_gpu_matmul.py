@@ -160,6 +160,22 @@ def test_gemm_preq_matches_oracle(t, n):
     assert_close(got, want, f"{O.NAMES[t]} n={n}")
 
 
+@pytest.mark.parametrize("t", [O.Q4_K, O.Q6_K, O.Q5_K])
+@pytest.mark.parametrize("m,n,k", [(70, 130, 1024), (64, 128, 512), (200, 16, 768), (3, 64, 4096)])
+def test_gemm_tensor_core_shapes(t, m, n, k):
+    """n >= 16: Q4_K / Q6_K take the mma.sync int8 kernel (ragged tiles included), Q5_K the column-tile path."""
+    torch = need_gpu()
+    import cera_b200 as cb
+    raw = cb.quantize_weights(t, cb.synth_normal(m * k, seed=9 * t + m + n, sigma=0.02)).cpu().numpy()
+    X = cb.synth_normal(n * k, seed=n + k, sigma=1.0)
+    acts = cb.quantize_q8_0(X, k=k, n=n)
+    w = cb.QuantWeight(t, m, k, raw)
+    out = torch.full((m, n), float("nan"), device="cuda")
+    got = cb.gemm_preq(w, acts, out).cpu().numpy()
+    want = O.gemm_preq(t, raw, acts.scales.cpu().numpy(), acts.quants.cpu().numpy(), m, n, k, avx2=t != O.Q5_K, threads=4)
+    assert_close(got, want, f"{O.NAMES[t]} {m}x{n}x{k}")
+
+
 def test_gemm_on_reference_fixtures():
     """The reference's own extreme fixtures (-128 weights, +/-127 activations)."""
     torch = need_gpu()
