@@ -56,6 +56,10 @@ SIGNATURES = {
     "cera_cuda_model_create": (_i32, [C.POINTER(Config), C.POINTER(_p)]),
     "cera_cuda_model_add_tensor": (_i32, [_p, _i32, _i32, _i32, _sz, _sz, _p, _sz]),
     "cera_cuda_model_finalize": (_i32, [_p]),
+    "cera_cuda_model_set_tp": (_i32, [_p, _u32, _u32]),
+    "cera_cuda_model_tp_handle": (_i32, [_p, _p, _sz]),
+    "cera_cuda_model_tp_connect": (_i32, [_p, _p, _sz]),
+    "cera_cuda_tp_wait_selftest": (_i32, [_u32, C.POINTER(_u32), C.POINTER(C.c_float)]),
     "cera_cuda_forward": (_i32, [_p, _u32, _sz, _p]),
     "cera_cuda_forward_greedy": (_i32, [_p, _u32, _sz, C.POINTER(_u32)]),
     "cera_cuda_generate_greedy": (_i32, [_p, _u32, _sz, _sz, _p, C.POINTER(_f)]),

@@ -9,7 +9,7 @@
 // mbarrier and do the dp4a work from registers.  Up to STAGES-1 tiles (100-190 KB per SM) stay in flight
 // with no register cost, so the HBM stream no longer stalls on the consumers' arithmetic.
 //
-// No copy is multicast and no cluster is used.  Every mbarrier wait is bounded: a wait that runs out
+// Every copy targets the issuing CTA alone; no thread-block cluster is used.  Every mbarrier wait is bounded: a wait that runs out
 // raises a flag in device memory (cera_cuda_kernel_status reports it), makes the CTA's other waits give
 // up at once, and the kernel returns after a bounded drain of the copies it still has in flight.
 #include <cstdlib>
@@ -78,7 +78,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     atomicOr(&g_tma_status, who);
     return false;
 }
-// One contiguous global range -> shared memory, completion counted on `bar` (no multicast).
+// One contiguous global range -> shared memory, completion counted on `bar`.
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))

@@ -12,7 +12,16 @@
 // recorded once per attention split count and replayed.
 // Layer wiring: cera/src/model/llama.rs:468-597, 1585-1605 and
 // cera/src/model/transformer.rs:1313-1652.
+//
+// Tensor-parallel mode (cera_cuda_model_set_tp, one process per GPU): every matrix is split by
+// output rows, rank r keeping rows [r*m/G, (r+1)*m/G) of the tensor it is handed in full; q/k/v
+// rows are whole heads, so the KV cache and attention of a head live on one rank.  The vectors
+// every rank needs in full (Q8_0 attention output, residual stream, Q8_0 SwiGLU activations,
+// logits) sit in an exchange region whose slices the ranks push to each other (tp.cu) after the
+// kernel that produced them: four exchanges per layer plus one for the logits or the greedy pick.
+// RMSNorm, the embedding row and the RoPE table are recomputed on every rank.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -51,6 +60,8 @@ struct cera_cuda_model {
     std::mutex mu;
     bool finalized = false;
     cera_cuda_weight *embd = nullptr, *output = nullptr;
+    cera_cuda_weight *embd_rows = nullptr;  // tensor parallel: this rank's rows of a tied embedding, as LM head
+    cera_cuda_weight *embd_head = nullptr;  // LM head when output.weight is absent (embd or embd_rows)
     float *out_norm = nullptr, *rope_freqs = nullptr;
     std::vector<Layer> layers;
     std::vector<void *> owned;  // plain device allocations to free
@@ -80,6 +91,19 @@ struct cera_cuda_model {
     ActBuf pf_act_hs, pf_act_q, pf_act_ff;
     uint32_t *tok_hist = nullptr;  // device ring of generated tokens (chained greedy decode)
     uint32_t tok_hist_cap = 0;
+    // tensor parallelism (tp_size == 1: a single device, no exchange)
+    uint32_t tp_rank = 0, tp_size = 1;
+    bool tp_connected = false;
+    char *region = nullptr;  // exchange region: hidden, act_q, act_ff, logits, pairs, flags
+    size_t region_bytes = 0;
+    TpCtx tp{};
+    void *tp_opened[TP_MAX_RANKS] = {};  // peer mappings to close
+    uint32_t *tp_words = nullptr;        // device: [0] = step sequence, [16] = status, [32] = local greedy pick
+    uint32_t tp_slots = 0;
+    uint32_t *h_status = nullptr;  // pinned
+    // per-rank extents
+    uint32_t l_heads = 0, l_kv_heads = 0;
+    size_t l_qd = 0, l_kvd = 0, l_ff = 0, l_hs = 0, l_vocab = 0;
 };
 
 namespace {
@@ -116,7 +140,31 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
     const auto &c = m->cfg;
     cudaStream_t st = m->stream;
     const size_t hs = c.hidden_size;
+    const uint32_t r = m->tp_rank;
+    const bool tp = m->tp_size > 1;
     const float scale = 1.0f / sqrtf((float)c.head_dim);
+    uint32_t slot = 0;
+    // push this rank's slice of up to three arrays of the exchange region to every peer
+    auto exchange = [&](const void *a, size_t an, const void *b, size_t bn, const void *d, size_t dn) -> int32_t {
+        if (!tp) return CERA_CUDA_OK;
+        TpRange rg[3] = {{(uint32_t)((const char *)a - m->region), (uint32_t)an}, {0, 0}, {0, 0}};
+        int n = 1;
+        if (b) rg[n++] = {(uint32_t)((const char *)b - m->region), (uint32_t)bn};
+        if (d) rg[n++] = {(uint32_t)((const char *)d - m->region), (uint32_t)dn};
+        if (slot >= m->tp_slots) return fail(CERA_CUDA_ERR_STATE, "decode step: exchange slot %u of %u", slot, m->tp_slots);
+        return launch_tp_exchange(m->tp, rg, n, slot++, st);
+    };
+    // this rank's part of a Q8_0 activation buffer that holds `l` of its elements per rank
+    auto act_slice = [&](const ActBuf &a, size_t l) {
+        return ActBuf{a.scales + r * (l / 32), a.quants + r * l, a.sums + r * (l / 16)};
+    };
+    auto exchange_act = [&](const ActBuf &a, size_t l) {
+        const ActBuf s = act_slice(a, l);
+        return exchange(s.scales, l / 32 * 4, s.quants, l, s.sums, l / 16 * 2);
+    };
+    float *hidden_slice = m->hidden + r * m->l_hs;
+
+    if (tp) CERA_TRY(launch_tp_tick(m->tp_words, st));
     CERA_TRY(launch_embed(m->embd->v, 0, m->dyn, m->hidden, st));
     const bool norm_rope = c.rope_type == 0;
     if (norm_rope) CERA_TRY(launch_rope_table(m->dyn + 1, c.head_dim, m->theta_scale, m->rope_freqs, m->rope_cs, st));
@@ -134,7 +182,7 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
             f.v_cache = L.vc;
             f.kv_f16 = c.kv_f16;
             f.head_dim = c.head_dim;
-            f.kv_dim = c.n_kv_heads * c.head_dim;
+            f.kv_dim = (uint32_t)m->l_kvd;
             CERA_TRY(launch_gemv_fused(segs, 3, m->act_hs.view(), EPI_ROPE_KV, &f, st, &fused_qkv));
         }
         if (fused_qkv) {
@@ -148,13 +196,16 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
             CERA_TRY(launch_gemv(&sv, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
         }
         if (!fused_qkv)
-            CERA_TRY(launch_rope(m->q, m->k, m->v, 0, m->dyn + 1, c.n_heads, c.n_kv_heads, c.head_dim, m->theta_scale,
+            CERA_TRY(launch_rope(m->q, m->k, m->v, 0, m->dyn + 1, m->l_heads, m->l_kv_heads, c.head_dim, m->theta_scale,
                                  m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st));
-        CERA_TRY(launch_decode_attention_ex(m->q, L.kc, L.vc, c.kv_f16, c.n_heads, c.n_kv_heads, c.head_dim, 0,
+        const ActBuf aq = act_slice(m->act_q, m->l_qd);
+        CERA_TRY(launch_decode_attention_ex(m->q, L.kc, L.vc, c.kv_f16, m->l_heads, m->l_kv_heads, c.head_dim, 0,
                                             m->dyn + 2, n_splits, scale, m->attn, m->attn_ws, m->attn_ws_bytes,
-                                            m->act_q.scales, m->act_q.quants, m->act_q.sums, st));
-        GemvSeg so{L.wo->v, m->hidden};
+                                            aq.scales, aq.quants, aq.sums, st));
+        CERA_TRY(exchange_act(m->act_q, m->l_qd));
+        GemvSeg so{L.wo->v, hidden_slice};
         CERA_TRY(launch_gemv(&so, 1, m->act_q.view(), 1, 1, EPI_ADD, st));
+        CERA_TRY(exchange(hidden_slice, m->l_hs * 4, nullptr, 0, nullptr, 0));
         CERA_TRY(launch_rmsnorm(m->hidden, L.ffn_norm, hs, 1, c.rms_norm_eps, nullptr, m->act_hs.scales,
                                 m->act_hs.quants, m->act_hs.sums, st));
         if (L.gate->v.type == L.up->v.type) {
@@ -165,19 +216,30 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
             CERA_TRY(launch_gemv(&sg, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
             CERA_TRY(launch_gemv(&su, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
         }
-        CERA_TRY(launch_silu_mul(m->g, m->u, c.intermediate_size, 1, m->act_ff.scales, m->act_ff.quants,
-                                 m->act_ff.sums, st));
-        GemvSeg sd{L.down->v, m->hidden};
+        const ActBuf af = act_slice(m->act_ff, m->l_ff);
+        CERA_TRY(launch_silu_mul(m->g, m->u, m->l_ff, 1, af.scales, af.quants, af.sums, st));
+        CERA_TRY(exchange_act(m->act_ff, m->l_ff));
+        GemvSeg sd{L.down->v, hidden_slice};
         CERA_TRY(launch_gemv(&sd, 1, m->act_ff.view(), 1, 1, EPI_ADD, st));
+        CERA_TRY(exchange(hidden_slice, m->l_hs * 4, nullptr, 0, nullptr, 0));
     }
     if (kind == G_BODY) return CERA_CUDA_OK;
     CERA_TRY(launch_rmsnorm(m->hidden, m->out_norm, hs, 1, c.rms_norm_eps, m->final_hidden, m->act_hs.scales,
                             m->act_hs.quants, m->act_hs.sums, st));
-    const cera_cuda_weight *ow = m->output ? m->output : m->embd;
-    GemvSeg sl{ow->v, m->logits};
+    const cera_cuda_weight *ow = m->output ? m->output : m->embd_head;
+    float *logits_slice = m->logits + r * m->l_vocab;
+    GemvSeg sl{ow->v, logits_slice};
     CERA_TRY(launch_gemv(&sl, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
-    if (kind == G_GREEDY || kind == G_CHAIN)
-        CERA_TRY(launch_argmax(m->logits, c.vocab_size, m->tok_out, m->argmax_scratch, st));
+    if (kind == G_LOGITS) CERA_TRY(exchange(logits_slice, m->l_vocab * 4, nullptr, 0, nullptr, 0));
+    if (kind == G_GREEDY || kind == G_CHAIN) {
+        if (!tp) {
+            CERA_TRY(launch_argmax(m->logits, c.vocab_size, m->tok_out, m->argmax_scratch, st));
+        } else {
+            CERA_TRY(launch_argmax(logits_slice, m->l_vocab, m->tp_words + 32, m->argmax_scratch, st));
+            if (slot >= m->tp_slots) return fail(CERA_CUDA_ERR_STATE, "decode step: exchange slot %u of %u", slot, m->tp_slots);
+            CERA_TRY(launch_tp_argmax(m->tp, logits_slice, (uint32_t)m->l_vocab, m->tp_words + 32, m->tok_out, slot++, st));
+        }
+    }
     if (kind == G_CHAIN) {
         count_launch();
         CERA_CUDA_TRY(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, m->dyn, (const uint32_t *)m->tok_out, m->tok_hist,
@@ -220,7 +282,8 @@ int32_t run_token(cera_cuda_model *m, uint32_t token, size_t pos, int kind) {
     if (token >= c.vocab_size) return fail(CERA_CUDA_ERR_BAD_ARG, "forward: token %u out of range (vocab %u)", token, c.vocab_size);
     if (pos != m->seq_len) return fail(CERA_CUDA_ERR_STATE, "forward: pos %zu != seq_len %zu", pos, m->seq_len);
     if (pos >= c.max_seq_len) return fail(CERA_CUDA_ERR_BAD_ARG, "forward: pos %zu exceeds max_seq_len %u", pos, c.max_seq_len);
-    const uint32_t n_splits = attn_pick_splits(c.n_kv_heads, pos + 1);
+    if (m->tp_size > 1 && !m->tp_connected) return fail(CERA_CUDA_ERR_STATE, "forward: tensor-parallel model is not connected to its peers");
+    const uint32_t n_splits = attn_pick_splits(m->l_kv_heads, pos + 1);
     cudaGraphExec_t g = nullptr;
     CERA_TRY(get_graph(m, kind, n_splits, &g));
     m->h_dyn[0] = token;
@@ -281,6 +344,29 @@ int32_t logits_from_hidden(cera_cuda_model *m) {
     return launch_gemv(&sl, 1, m->act_hs.view(), 1, 1, EPI_STORE, m->stream);
 }
 
+void set_extents(cera_cuda_model *m) {
+    const auto &c = m->cfg;
+    const uint32_t G = m->tp_size;
+    m->l_heads = c.n_heads / G;
+    m->l_kv_heads = c.n_kv_heads / G;
+    m->l_qd = (size_t)m->l_heads * c.head_dim;
+    m->l_kvd = (size_t)m->l_kv_heads * c.head_dim;
+    m->l_ff = c.intermediate_size / G;
+    m->l_hs = c.hidden_size / G;
+    m->l_vocab = c.vocab_size / G;
+}
+
+// Reads the exchange status word after a synchronisation; a set word is a wait that ran out.
+int32_t tp_check(cera_cuda_model *m) {
+    if (m->tp_size < 2) return CERA_CUDA_OK;
+    CERA_CUDA_TRY(cudaMemcpyAsync(m->h_status, m->tp_words + 16, 4, cudaMemcpyDeviceToHost, m->stream));
+    CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    const uint32_t w = *m->h_status;
+    if (w == 0) return CERA_CUDA_OK;
+    return fail(CERA_CUDA_ERR_TIMEOUT, "tensor-parallel exchange %u: rank %u waited for rank %u longer than %llu ms", (w & 0xFFFFFFu) - 1,
+                m->tp_rank, (w >> 24) & 0x7Fu, (unsigned long long)(m->tp.timeout_ns / 1000000ull));
+}
+
 struct DeviceGuard {
     int prev = 0;
     explicit DeviceGuard(int dev) {
@@ -311,7 +397,31 @@ int32_t cera_cuda_model_create(const cera_cuda_config *cfg, cera_cuda_model **ou
     m->cfg = c;
     m->layers.resize(c.n_layers);
     m->theta_scale = powf(c.rope_theta, -2.0f / (float)c.head_dim);
+    set_extents(m);
     *out = m;
+    return CERA_CUDA_OK;
+}
+
+int32_t cera_cuda_model_set_tp(cera_cuda_model *m, uint32_t rank, uint32_t size) {
+    if (!m) return fail(CERA_CUDA_ERR_BAD_ARG, "set_tp: null model");
+    std::lock_guard<std::mutex> lock(m->mu);
+    const auto &c = m->cfg;
+    if (m->finalized || m->embd || m->out_norm || m->output)
+        return fail(CERA_CUDA_ERR_STATE, "set_tp: must precede the first add_tensor");
+    for (const auto &L : m->layers)
+        if (L.wq || L.wk || L.wv || L.wo || L.gate || L.up || L.down || L.attn_norm || L.ffn_norm)
+            return fail(CERA_CUDA_ERR_STATE, "set_tp: must precede the first add_tensor");
+    if (size == 0 || size > TP_MAX_RANKS || rank >= size)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "set_tp: rank %u of %u (at most %u ranks)", rank, size, TP_MAX_RANKS);
+    if (c.n_kv_heads % size) return fail(CERA_CUDA_ERR_BAD_ARG, "set_tp: %u KV heads do not split over %u ranks", c.n_kv_heads, size);
+    if (c.intermediate_size % (32 * size))
+        return fail(CERA_CUDA_ERR_BAD_ARG, "set_tp: intermediate size %u must be a multiple of 32 x %u ranks", c.intermediate_size, size);
+    if (c.hidden_size % size || c.vocab_size % size)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "set_tp: hidden size %u and vocabulary %u must be multiples of %u ranks", c.hidden_size,
+                    c.vocab_size, size);
+    m->tp_rank = rank;
+    m->tp_size = size;
+    set_extents(m);
     return CERA_CUDA_OK;
 }
 
@@ -334,17 +444,27 @@ int32_t cera_cuda_model_add_tensor(cera_cuda_model *m, int32_t role, int32_t lay
         CERA_TRY(dev_alloc(m, (void **)slot, nbytes));
         return check_cuda(cudaMemcpy(*slot, bytes, nbytes, cudaMemcpyDefault), "cudaMemcpy(norm weights)");
     };
-    auto matrix = [&](cera_cuda_weight **slot, size_t want_m, size_t want_k) -> int32_t {
+    // The caller always hands over the whole tensor; `split` keeps this rank's rows of it.
+    auto matrix = [&](cera_cuda_weight **slot, size_t want_m, size_t want_k, bool split = true) -> int32_t {
         if (rows != want_m || cols != want_k)
             return fail(CERA_CUDA_ERR_BAD_ARG, "add_tensor: role %d expects [%zu x %zu], got [%zu x %zu]", role, want_m, want_k, rows, cols);
         if (*slot) return fail(CERA_CUDA_ERR_STATE, "add_tensor: role %d layer %d given twice", role, layer);
-        CERA_TRY(weight_upload(type, rows, cols, bytes, nbytes, false, slot));
+        const TypeInfo ti = type_info(type);
+        if (!is_block_type(type) || cols % ti.elems || nbytes != rows * (cols / ti.elems) * ti.bytes || !split || m->tp_size == 1) {
+            CERA_TRY(weight_upload(type, rows, cols, bytes, nbytes, false, slot));  // also reports the malformed cases
+        } else {
+            const size_t l_rows = rows / m->tp_size, row_bytes = (cols / ti.elems) * ti.bytes;
+            CERA_TRY(weight_upload(type, l_rows, cols, (const char *)bytes + m->tp_rank * l_rows * row_bytes, l_rows * row_bytes, false, slot));
+        }
         m->mem_bytes += (*slot)->bytes;
         return CERA_CUDA_OK;
     };
     Layer *L = per_layer ? &m->layers[layer] : nullptr;
     switch (role) {
-        case CERA_ROLE_TOKEN_EMBD: return matrix(&m->embd, c.vocab_size, c.hidden_size);
+        case CERA_ROLE_TOKEN_EMBD:
+            CERA_TRY(matrix(&m->embd, c.vocab_size, c.hidden_size, false));
+            if (m->tp_size > 1) CERA_TRY(matrix(&m->embd_rows, c.vocab_size, c.hidden_size));  // dropped if output.weight arrives
+            return CERA_CUDA_OK;
         case CERA_ROLE_OUTPUT: return matrix(&m->output, c.vocab_size, c.hidden_size);
         case CERA_ROLE_OUTPUT_NORM: return f32_vector(&m->out_norm, c.hidden_size);
         case CERA_ROLE_ROPE_FREQS: return f32_vector(&m->rope_freqs, c.head_dim / 2);
@@ -377,22 +497,60 @@ int32_t cera_cuda_model_finalize(cera_cuda_model *m) {
                  ff = c.intermediate_size;
     const size_t esz = c.kv_f16 ? 2 : 4;
     for (auto &L : m->layers) {
-        CERA_TRY(dev_alloc(m, &L.kc, (size_t)c.max_seq_len * kvd * esz));
-        CERA_TRY(dev_alloc(m, &L.vc, (size_t)c.max_seq_len * kvd * esz));
+        CERA_TRY(dev_alloc(m, &L.kc, (size_t)c.max_seq_len * m->l_kvd * esz));
+        CERA_TRY(dev_alloc(m, &L.vc, (size_t)c.max_seq_len * m->l_kvd * esz));
     }
-    CERA_TRY(dev_alloc(m, (void **)&m->hidden, hs * 4));
-    CERA_TRY(dev_alloc(m, (void **)&m->final_hidden, hs * 4));
-    CERA_TRY(dev_alloc(m, (void **)&m->q, qd * 4));
-    CERA_TRY(dev_alloc(m, (void **)&m->k, kvd * 4));
-    CERA_TRY(dev_alloc(m, (void **)&m->v, kvd * 4));
-    CERA_TRY(dev_alloc(m, (void **)&m->attn, qd * 4));
-    CERA_TRY(dev_alloc(m, (void **)&m->g, ff * 4));
-    CERA_TRY(dev_alloc(m, (void **)&m->u, ff * 4));
-    CERA_TRY(dev_alloc(m, (void **)&m->logits, (size_t)c.vocab_size * 4));
-    CERA_TRY(alloc_act(m, m->act_hs, hs));
-    CERA_TRY(alloc_act(m, m->act_q, qd));
-    CERA_TRY(alloc_act(m, m->act_ff, ff));
     {
+        // Exchange region: the vectors every rank holds in full, at the same offsets on every rank.
+        size_t off = 0;
+        auto take = [&](size_t bytes) {
+            const size_t at = off;
+            off += (bytes + 255) & ~(size_t)255;
+            return at;
+        };
+        const size_t o_hidden = take(hs * 4), o_qs = take(qd / 32 * 4), o_qq = take(qd), o_qsum = take(qd / 16 * 2),
+                     o_fs = take(ff / 32 * 4), o_fq = take(ff), o_fsum = take(ff / 16 * 2),
+                     o_logits = take((size_t)c.vocab_size * 4), o_pairs = take(TP_MAX_RANKS * 8);
+        m->tp_slots = 4 * c.n_layers + 2;
+        const size_t o_flags = take((size_t)m->tp_slots * TP_MAX_RANKS * 4);
+        m->region_bytes = (off + ((size_t)2 << 20) - 1) & ~(((size_t)2 << 20) - 1);  // an allocation of its own to export
+        if (m->region_bytes > 0xFFFFFFFFull) return fail(CERA_CUDA_ERR_UNSUPPORTED, "finalize: exchange region of %zu bytes", m->region_bytes);
+        CERA_TRY(dev_alloc(m, (void **)&m->region, m->region_bytes));
+        CERA_CUDA_TRY(cudaMemset(m->region, 0, m->region_bytes));
+        char *b = m->region;
+        m->hidden = (float *)(b + o_hidden);
+        m->act_q = ActBuf{(float *)(b + o_qs), (int8_t *)(b + o_qq), (int16_t *)(b + o_qsum)};
+        m->act_ff = ActBuf{(float *)(b + o_fs), (int8_t *)(b + o_fq), (int16_t *)(b + o_fsum)};
+        m->logits = (float *)(b + o_logits);
+        CERA_TRY(dev_alloc(m, (void **)&m->tp_words, 64 * 4));
+        CERA_CUDA_TRY(cudaMemset(m->tp_words, 0, 64 * 4));
+        m->tp.rank = m->tp_rank;
+        m->tp.size = m->tp_size;
+        m->tp.peer[m->tp_rank] = m->region;
+        m->tp.flags_off = (uint32_t)o_flags;
+        m->tp.pairs_off = (uint32_t)o_pairs;
+        m->tp.seq = m->tp_words;
+        m->tp.status = m->tp_words + 16;
+        const char *e = getenv("CERA_CUDA_TP_TIMEOUT_MS");
+        const long ms = e ? atol(e) : 5000;
+        m->tp.timeout_ns = (uint64_t)(ms > 0 ? ms : 5000) * 1000000ull;
+    }
+    if (m->output && m->embd_rows) {
+        m->mem_bytes -= m->embd_rows->bytes;
+        cera_cuda_weight_free(m->embd_rows);
+        m->embd_rows = nullptr;
+    }
+    m->embd_head = m->embd_rows ? m->embd_rows : m->embd;
+    // per-rank buffers
+    CERA_TRY(dev_alloc(m, (void **)&m->final_hidden, hs * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->q, m->l_qd * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->k, m->l_kvd * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->v, m->l_kvd * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->attn, m->l_qd * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->g, m->l_ff * 4));
+    CERA_TRY(dev_alloc(m, (void **)&m->u, m->l_ff * 4));
+    CERA_TRY(alloc_act(m, m->act_hs, hs));
+    if (m->tp_size == 1) {
         const size_t C = PREFILL_CHUNK;
         CERA_TRY(dev_alloc(m, (void **)&m->pf_tokens, C * 4));
         CERA_TRY(dev_alloc(m, (void **)&m->pf_hidden, C * hs * 4));
@@ -406,7 +564,7 @@ int32_t cera_cuda_model_finalize(cera_cuda_model *m) {
         CERA_TRY(alloc_act(m, m->pf_act_q, C * qd));
         CERA_TRY(alloc_act(m, m->pf_act_ff, C * ff));
     }
-    m->attn_ws_bytes = attn_workspace_bytes(c.n_heads, c.head_dim, c.max_seq_len);
+    m->attn_ws_bytes = attn_workspace_bytes(m->l_heads, c.head_dim, c.max_seq_len);
     CERA_TRY(dev_alloc(m, &m->attn_ws, m->attn_ws_bytes));
     CERA_TRY(dev_alloc(m, (void **)&m->argmax_scratch, argmax_scratch_words() * 4));
     CERA_TRY(dev_alloc(m, (void **)&m->dyn, 4 * 4));
@@ -415,6 +573,7 @@ int32_t cera_cuda_model_finalize(cera_cuda_model *m) {
     m->tok_hist_cap = c.max_seq_len;
     CERA_TRY(dev_alloc(m, (void **)&m->tok_hist, (size_t)m->tok_hist_cap * 4));
     CERA_CUDA_TRY(cudaMallocHost((void **)&m->h_dyn, 8 * 4));
+    CERA_CUDA_TRY(cudaMallocHost((void **)&m->h_status, 4));
     CERA_CUDA_TRY(cudaMallocHost((void **)&m->h_logits, (size_t)c.vocab_size * 4));
     CERA_CUDA_TRY(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
     CERA_CUDA_TRY(cudaDeviceSynchronize());
@@ -430,6 +589,7 @@ int32_t cera_cuda_forward(cera_cuda_model *m, uint32_t token, size_t pos, float 
     const size_t bytes = (size_t)m->cfg.vocab_size * 4;
     CERA_CUDA_TRY(cudaMemcpyAsync(m->h_logits, m->logits, bytes, cudaMemcpyDeviceToHost, m->stream));
     CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    CERA_TRY(tp_check(m));
     memcpy(logits_out, m->h_logits, bytes);
     return CERA_CUDA_OK;
 }
@@ -441,6 +601,7 @@ int32_t cera_cuda_forward_greedy(cera_cuda_model *m, uint32_t token, size_t pos,
     CERA_TRY(run_token(m, token, pos, G_GREEDY));
     CERA_CUDA_TRY(cudaMemcpyAsync(m->h_dyn + 4, m->tok_out, 4, cudaMemcpyDeviceToHost, m->stream));
     CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    CERA_TRY(tp_check(m));
     *token_out = m->h_dyn[4];
     return CERA_CUDA_OK;
 }
@@ -462,7 +623,8 @@ int32_t cera_cuda_forward_prefill(cera_cuda_model *m, const uint32_t *tokens, si
         const char *e = getenv("CERA_CUDA_PREFILL");
         return e && strcmp(e, "per_token") == 0;
     }();
-    if (per_token || n < 2) {
+    if (m->tp_size > 1 && !m->tp_connected) return fail(CERA_CUDA_ERR_STATE, "forward_prefill: tensor-parallel model is not connected to its peers");
+    if (per_token || n < 2 || m->tp_size > 1) {
         // Decode arithmetic for every prompt position (one graph launch per token).  h_dyn is rewritten per
         // token, so wait for the copy of the previous one before touching it again.
         for (size_t i = 0; i < n; ++i) {
@@ -470,6 +632,7 @@ int32_t cera_cuda_forward_prefill(cera_cuda_model *m, const uint32_t *tokens, si
             CERA_TRY(run_token(m, tokens[i], start_pos + i, last && logits_out ? G_LOGITS : G_BODY));
             CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
         }
+        CERA_TRY(tp_check(m));
     } else {
         // Batched kernels, PREFILL_CHUNK tokens at a time (the reference's ubatch loop, cera/src/model/mod.rs:303-332).
         for (size_t done = 0; done < n; done += PREFILL_CHUNK) {
@@ -499,6 +662,7 @@ int32_t cera_cuda_generate_greedy(cera_cuda_model *m, uint32_t first_token, size
     if (first_token >= c.vocab_size) return fail(CERA_CUDA_ERR_BAD_ARG, "generate_greedy: token out of range");
     if (start_pos != m->seq_len) return fail(CERA_CUDA_ERR_STATE, "generate_greedy: start_pos %zu != seq_len %zu", start_pos, m->seq_len);
     if (start_pos + n > c.max_seq_len) return fail(CERA_CUDA_ERR_BAD_ARG, "generate_greedy: %zu tokens from %zu exceed max_seq_len %u", n, start_pos, c.max_seq_len);
+    if (m->tp_size > 1 && !m->tp_connected) return fail(CERA_CUDA_ERR_STATE, "generate_greedy: tensor-parallel model is not connected to its peers");
     if (n == 0) return CERA_CUDA_OK;
     m->h_dyn[0] = first_token;
     m->h_dyn[1] = (uint32_t)start_pos;
@@ -511,12 +675,12 @@ int32_t cera_cuda_generate_greedy(cera_cuda_model *m, uint32_t first_token, size
     // instantiate every graph the run needs before the timed region
     for (size_t i = 0; i < n; ++i) {
         cudaGraphExec_t g = nullptr;
-        CERA_TRY(get_graph(m, G_CHAIN, attn_pick_splits(c.n_kv_heads, start_pos + i + 1), &g));
+        CERA_TRY(get_graph(m, G_CHAIN, attn_pick_splits(m->l_kv_heads, start_pos + i + 1), &g));
     }
     CERA_CUDA_TRY(cudaEventRecord(e0, m->stream));
     for (size_t i = 0; i < n; ++i) {
         cudaGraphExec_t g = nullptr;
-        CERA_TRY(get_graph(m, G_CHAIN, attn_pick_splits(c.n_kv_heads, start_pos + i + 1), &g));
+        CERA_TRY(get_graph(m, G_CHAIN, attn_pick_splits(m->l_kv_heads, start_pos + i + 1), &g));
         CERA_CUDA_TRY(cudaGraphLaunch(g, m->stream));
     }
     CERA_CUDA_TRY(cudaEventRecord(e1, m->stream));
@@ -529,6 +693,38 @@ int32_t cera_cuda_generate_greedy(cera_cuda_model *m, uint32_t first_token, size
     if (device_ms) *device_ms = ms;
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
+    return tp_check(m);
+}
+
+int32_t cera_cuda_model_tp_handle(cera_cuda_model *m, void *handle_out, size_t handle_bytes) {
+    if (!m || !handle_out) return fail(CERA_CUDA_ERR_BAD_ARG, "tp_handle: null argument");
+    if (handle_bytes != sizeof(cudaIpcMemHandle_t)) return fail(CERA_CUDA_ERR_BAD_ARG, "tp_handle: handle is %zu bytes", sizeof(cudaIpcMemHandle_t));
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    if (!m->finalized) return fail(CERA_CUDA_ERR_STATE, "tp_handle: model_finalize has not been called");
+    cudaIpcMemHandle_t h;
+    CERA_CUDA_TRY(cudaIpcGetMemHandle(&h, m->region));
+    memcpy(handle_out, &h, sizeof(h));
+    return CERA_CUDA_OK;
+}
+
+int32_t cera_cuda_model_tp_connect(cera_cuda_model *m, const void *handles, size_t n_handles) {
+    if (!m || !handles) return fail(CERA_CUDA_ERR_BAD_ARG, "tp_connect: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    if (!m->finalized) return fail(CERA_CUDA_ERR_STATE, "tp_connect: model_finalize has not been called");
+    if (n_handles != m->tp_size) return fail(CERA_CUDA_ERR_BAD_ARG, "tp_connect: %zu handles for %u ranks", n_handles, m->tp_size);
+    if (m->tp_connected) return fail(CERA_CUDA_ERR_STATE, "tp_connect: already connected");
+    for (uint32_t p = 0; p < m->tp_size; ++p) {
+        if (p == m->tp_rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char *)handles + (size_t)p * sizeof(h), sizeof(h));
+        void *ptr = nullptr;
+        CERA_CUDA_TRY(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        m->tp_opened[p] = ptr;
+        m->tp.peer[p] = (char *)ptr;
+    }
+    m->tp_connected = true;
     return CERA_CUDA_OK;
 }
 
@@ -568,6 +764,10 @@ void cera_cuda_model_free(cera_cuda_model *m) {
         for (auto &L : m->layers) {
             fw(L.wq); fw(L.wk); fw(L.wv); fw(L.wo); fw(L.gate); fw(L.up); fw(L.down);
         }
+        for (void *p : m->tp_opened)
+            if (p) cudaIpcCloseMemHandle(p);
+        fw(m->embd_rows);
+        if (m->h_status) cudaFreeHost(m->h_status);
         if (m->h_dyn) cudaFreeHost(m->h_dyn);
         if (m->h_logits) cudaFreeHost(m->h_logits);
         if (m->stream) cudaStreamDestroy(m->stream);

@@ -93,4 +93,25 @@ int32_t launch_prefill_attention(const float *q, const void *kc, const void *vc,
 size_t argmax_scratch_words();
 int32_t launch_argmax(const float *x, size_t n, uint32_t *out, uint32_t *scratch, cudaStream_t st);
 
+// ---- tensor-parallel exchange (tp.cu) -------------------------------------------
+constexpr uint32_t TP_MAX_RANKS = 8;
+struct TpCtx {
+    char *peer[TP_MAX_RANKS];  // every rank's exchange region as mapped on this device; peer[rank] is its own
+    uint32_t rank, size;
+    uint32_t flags_off;        // byte offset of flags[n_slots][TP_MAX_RANKS] (u32) inside a region
+    uint32_t pairs_off;        // byte offset of the greedy pairs[TP_MAX_RANKS] {f32 bits, index}
+    const uint32_t *seq;       // device: sequence number of the running step
+    uint32_t *status;          // device: 0, or 0x80000000 | peer << 24 | slot + 1 after a wait ran out
+    uint64_t timeout_ns;
+};
+struct TpRange {
+    uint32_t off, bytes;  // inside the exchange region
+};
+int32_t launch_tp_tick(uint32_t *seq, cudaStream_t st);
+// Pushes the ranges to the same offsets of every peer, then waits for every peer's push of this slot.
+int32_t launch_tp_exchange(const TpCtx &ctx, const TpRange *ranges, int n_ranges, uint32_t slot, cudaStream_t st);
+// logits_local[local_n] are this rank's rows, *local_idx its local first maximum; *tok_out = global pick.
+int32_t launch_tp_argmax(const TpCtx &ctx, const float *logits_local, uint32_t local_n, const uint32_t *local_idx,
+                         uint32_t *tok_out, uint32_t slot, cudaStream_t st);
+
 }  // namespace cera

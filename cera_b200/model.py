@@ -28,13 +28,28 @@ ModelConfig = Config
 
 
 class CudaModel:
-    def __init__(self, **cfg):
+    def __init__(self, tp=None, **cfg):
+        """tp = (rank, size): this process holds rank `rank` of a `size`-way row split (see tp.py)."""
         cfg.setdefault("device", 0)
         cfg.setdefault("rope_type", 0)
         cfg.setdefault("kv_f16", 0)
         self.cfg = Config(**cfg)
         self.handle = C.c_void_p()
         check(lib.cera_cuda_model_create(C.byref(self.cfg), C.byref(self.handle)))
+        self.tp = tuple(tp) if tp else (0, 1)
+        if self.tp[1] > 1:
+            check(lib.cera_cuda_model_set_tp(self.handle, self.tp[0], self.tp[1]))
+
+    def tp_handle(self):
+        """64-byte handle of this rank's exchange region (after finalize)."""
+        buf = (C.c_uint8 * 64)()
+        check(lib.cera_cuda_model_tp_handle(self.handle, buf, 64))
+        return bytes(buf)
+
+    def tp_connect(self, handles):
+        """handles: the tp_handle() of every rank, in rank order."""
+        blob = b"".join(handles)
+        check(lib.cera_cuda_model_tp_connect(self.handle, blob, len(handles)))
 
     def config(self):
         return self.cfg

@@ -227,6 +227,14 @@ enum {
 };
 
 CERA_API int32_t cera_cuda_model_create(const cera_cuda_config *cfg, cera_cuda_model **out);
+/* Tensor parallelism over the output rows of every matrix, the axis the reference itself
+ * parallelises (cera/src/backend/cpu.rs:380-391, RowPool): this model becomes rank `rank` of
+ * `size` (<= 8) cooperating models, one process and one GPU each.  Call before the first
+ * add_tensor; add_tensor still receives every tensor in full (each rank's loader has the same
+ * mmap, cera/src/model/gpu_weight_source.rs:40-118) and keeps rows [rank*m/size, (rank+1)*m/size).
+ * Needs n_kv_heads, hidden_size, vocab_size divisible by size and intermediate_size by 32*size.
+ * Per-row arithmetic is unchanged, so logits and greedy streams do not depend on size. */
+CERA_API int32_t cera_cuda_model_set_tp(cera_cuda_model *m, uint32_t rank, uint32_t size);
 /* GpuWeightSource::weight_bytes (cera/src/model/gpu_weight_source.rs:40-118):
  * bytes are borrowed for the call only (host or device memory). */
 CERA_API int32_t cera_cuda_model_add_tensor(cera_cuda_model *m, int32_t role, int32_t layer,
@@ -235,6 +243,19 @@ CERA_API int32_t cera_cuda_model_add_tensor(cera_cuda_model *m, int32_t role, in
 /* Checks every required tensor is present, allocates KV and scratch, and
  * records the decode step.  Must precede the first forward. */
 CERA_API int32_t cera_cuda_model_finalize(cera_cuda_model *m);
+/* After finalize on a tensor-parallel model: a 64-byte handle (CUDA IPC) of this rank's
+ * exchange region.  The host gathers the handles of all ranks in rank order (any transport:
+ * the Python mirror uses torch.distributed) and gives every rank the whole list; the entry of
+ * the rank itself is ignored.  Every forward call must then be made by all ranks with the same
+ * arguments; a rank whose peers do not arrive within CERA_CUDA_TP_TIMEOUT_MS (default 5000)
+ * returns CERA_CUDA_ERR_TIMEOUT from that call.  No counterpart in the reference, whose
+ * backends are single-device. */
+CERA_API int32_t cera_cuda_model_tp_handle(cera_cuda_model *m, void *handle_out, size_t handle_bytes);
+CERA_API int32_t cera_cuda_model_tp_connect(cera_cuda_model *m, const void *handles, size_t n_handles);
+/* One exchange on the current device against a peer buffer that nothing signals, with a wait
+ * budget of timeout_ms (1..2000): *status_out receives the word the kernel leaves
+ * (0x80000000 | peer << 24 | slot + 1; slot 3, peer 1 here), elapsed_ms the kernel time. */
+CERA_API int32_t cera_cuda_tp_wait_selftest(uint32_t timeout_ms, uint32_t *status_out, float *elapsed_ms);
 /* Model::forward (mod.rs:202): one token at pos == seq_len; logits_out[vocab]
  * on the host. */
 CERA_API int32_t cera_cuda_forward(cera_cuda_model *m, uint32_t token, size_t pos,
