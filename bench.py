@@ -22,8 +22,12 @@ token ids.  One JSON line goes to stdout.
           this box's host cores, on a bounded sample of the same token.
 
 With --impl reference only that CPU implementation is timed.  With N > 1
-(launched by torchrun, one rank per GPU) every rank decodes its own sequence on
-its own full copy of the model: replicas, no collective on the data path.
+(launched by torchrun, one rank per GPU) the ranks decode ONE sequence together:
+every matrix is split by output rows over the N GPUs (whole heads for q/k/v, so
+each head's KV cache lives on one GPU) and the ranks push their slices of the
+gathered vectors into each other's memory over NVLink inside the decode step.
+Total work is fixed as N grows ("scaling": "strong"); the token stream is the
+single-GPU one by construction.
 """
 import argparse
 import json
@@ -257,6 +261,34 @@ def gemm_microbench(torch, cb, tname, m, k, n, iters):
     return 2.0 * m * n * k, us
 
 
+def moe_microbench(torch, cb, iters, n_tokens=512, softmax_gate=False):
+    """Routed FFN of the lfm2moe shape: 32 experts x (2 x 1792x2048 + 2048x1792) Q4_0, top-4, 512 tokens of N(0,1)."""
+    E, used, hs, ff = 32, 4, 2048, 1792
+    q = lambda n, seed: cb.quantize_weights(cb.Q4_0, cb.synth_normal(n, seed=seed, sigma=0.02))
+    gate, up, down = q(E * ff * hs, 1), q(E * ff * hs, 2), q(E * hs * ff, 3)
+    router = cb.synth_normal(E * hs, seed=4, sigma=0.05)
+    moe = cb.MoeFfn(E, used, hs, ff, cb.Q4_0, gate, up, down, router, max_tokens=n_tokens)
+    x = cb.synth_normal(n_tokens * hs, seed=5, sigma=1.0).view(n_tokens, hs)
+    out, ids, _ = moe(x, softmax_gate=softmax_gate, want_routing=True)
+    torch.cuda.synchronize()
+    counts = torch.bincount(ids.flatten().long(), minlength=E)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        moe(x, softmax_gate=softmax_gate)
+    e0.record()
+    for _ in range(iters):
+        moe(x, softmax_gate=softmax_gate)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    ops = 2.0 * n_tokens * used * 3 * ff * hs
+    wbytes = 3 * int((counts > 0).sum()) * ff * hs // 32 * 18  # experts that received a token
+    moe.close()
+    return {"tokens": n_tokens, "ms": ms, "tok_s": n_tokens / ms * 1e3, "tops": ops / ms / 1e9, "weight_bytes": wbytes,
+            "weight_gbs_single_pass": wbytes / ms / 1e6, "gate": "softmax" if softmax_gate else "sigmoid",
+            "tokens_per_expert_min_max": [int(counts.min()), int(counts.max())]}
+
+
 def roofline_q4k_gemv(torch, cb, iters):
     """The dominant kernel of the decode step: the Q4_K GEMV at the gate/up shape."""
     return gemv_microbench(torch, cb, "q4_k", 14336, 4096, iters)
@@ -286,9 +318,13 @@ def cuda_arm(args, rank, world):
     prompt_len = args.prompt_len
     max_seq = prompt_len + 2 * (K + W) + 16
     t_build = time.perf_counter()
-    model = synth.build_llama(cfg, seed=args.seed + rank, max_seq_len=max_seq, device=local)
+    model = synth.build_llama(cfg, seed=args.seed, max_seq_len=max_seq, device=local,
+                              tp=(rank, world) if world > 1 else None)
+    if world > 1:
+        from cera_b200 import tp
+        tp.connect(model, dist.new_group(backend="gloo"))
     t_build = time.perf_counter() - t_build
-    prompt = synth.prompt_tokens(prompt_len, cfg["vocab_size"], seed=7 + rank)
+    prompt = synth.prompt_tokens(prompt_len, cfg["vocab_size"], seed=7)
     t_pre = time.perf_counter()
     logits = model.forward_prefill(prompt, 0)
     t_pre = time.perf_counter() - t_pre
@@ -336,18 +372,22 @@ def cuda_arm(args, rank, world):
         algo, us, roof_launches = roofline_q4k_gemv(torch, cb, iters=args.iters)
         achieved = algo / (us * 1e-6) / 1e9
         step_gbs = TOKEN_WEIGHT_BYTES / (dev_ms / K * 1e-3) / 1e9
-        value = world * K / (dev_ms * 1e-3)
+        value = K / (dev_ms * 1e-3)
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+            "vs_baseline": None,
             "dtype": "int8 x int8 -> int32 dot, f32 scales and accumulation", "data": "synthetic",
             "config": {"workload": "Llama-3-8B-shape random-init model (32 layers, 4096/14336, 32/8 heads, vocab 128256; "
                                    "Q4_K attn/gate/up/embd, Q6_K down/output), 512-token prompt then greedy decode",
-                       "prompt_len": prompt_len, "kv_dtype": "f32", "parallelism": f"replicas x{world}",
+                       "prompt_len": prompt_len, "kv_dtype": "f32", "parallelism": (f"tensor-parallel x{world}: rows of every matrix split over the GPUs, slices pushed "
+                                       "into peer memory over NVLink inside the step (4 exchanges per layer)")
+                       if world > 1 else "1 GPU",
+                       "stream_head": [int(t) for t in stream[:8]],
                        "l2": "each token streams 4.84 GB of weights (>> 126 MB L2); the kernel microbench rotates "
                              "16 weight copies (528 MB)",
                        "build_s": round(t_build, 2), "prefill_s": round(t_pre, 2)},
-            "e2e": {"value": world * K / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 4},
+            "e2e": {"value": K / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 4},
             "gpu_launches": int(model_launches + roof_launches),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "gemv_kernel<Q4_K, 1 column> 14336x4096", "achieved": achieved,
@@ -355,8 +395,8 @@ def cuda_arm(args, rank, world):
                          "frac_of_nominal_8000": achieved / 8000.0, "us_per_launch": us, "algorithmic_bytes": algo,
                          "traffic": None},
             "step_roofline": {"bound": "hbm", "weight_bytes_per_token": TOKEN_WEIGHT_BYTES, "achieved": step_gbs,
-                              "peak": hbm, "unit": "GB/s", "frac": step_gbs / hbm,
-                              "roofline_tok_s_at_peak": hbm * 1e9 / TOKEN_WEIGHT_BYTES},
+                              "peak": hbm * world, "unit": "GB/s", "frac": step_gbs / (hbm * world),
+                              "roofline_tok_s_at_peak": hbm * world * 1e9 / TOKEN_WEIGHT_BYTES},
         }
     model.close()
     if rank == 0:
@@ -383,7 +423,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
                     help="prompt tokens before the timed decode (512 is the benchmark; shorter only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--only", default=None, choices=["roofline", "gemv-sweep", "gemm-sweep"],
+    ap.add_argument("--only", default=None, choices=["roofline", "gemv-sweep", "gemm-sweep", "moe"],
                     help="run just the dominant-kernel microbench (the case ncu captures are taken on)")
     ap.add_argument("--iters", type=int, default=200, help="timed launches of the kernel microbench")
     args = ap.parse_args()
@@ -406,6 +446,12 @@ def main():
             print(json.dumps({"type": tname, "m": m, "k": k, "us": round(us, 3), "algorithmic_bytes": algo,
                               "gbs": round(algo / us / 1e3, 1), "frac_of_measured": round(algo / us / 1e3 / hbm, 4),
                               "frac_of_8000": round(algo / us / 1e3 / 8000.0, 4)}), flush=True)
+    elif args.only == "moe":
+        import torch
+        import cera_b200 as cb
+        for n in (1, 64, 512):
+            print(json.dumps(moe_microbench(torch, cb, max(5, args.iters // 5), n_tokens=n)), flush=True)
+        print(json.dumps(moe_microbench(torch, cb, max(5, args.iters // 5), softmax_gate=True)), flush=True)
     elif args.only == "gemm-sweep":
         import torch
         import cera_b200 as cb

@@ -1,0 +1,371 @@
+// Routed feed-forward of an lfm2moe layer for a batch of tokens, grouped by expert.
+//
+// Reference (per token, unbatched on every backend): cera/src/model/lfm2.rs:177-226
+// (select_experts), 673-715 (route_experts), 735-901 (forward_moe_ffn), 914-937 (prefill_moe_ffn).
+//   probs = sigmoid(router . x)                         F32 router, std exp
+//   pick n_used experts by probs + exp_probs_b, ties to the lower index
+//   weights = unbiased probs of the picked, divided by max(their sum, 2^-14)
+//   out = sum over the picks in pick order of weight * down_e(silu(gate_e x) * up_e x)
+// with every expert projection an int8 GEMV against Q8_0-quantized input, like the dense FFN.
+//
+// Here the (token, pick) pairs of the whole batch are bucketed by expert (counting sort on the
+// device), the Q8_0 columns are gathered into bucket order, and one launch per projection walks a
+// device-built list of (expert, column tile) work items: each expert's weights are streamed once per
+// eight of its tokens instead of once per token.  The stacked expert tensors
+// (blk.N.ffn_{gate,up,down}_exps.weight, [n_expert][m][k] with expert stride m rows,
+// cera/src/model/gpu_weight_source.rs:179-257) are one weight matrix of n_expert*m rows here.
+#include <new>
+
+#include "gemv_item.cuh"
+#include "ops.h"
+#include "weight.h"
+
+using namespace cera;
+
+namespace {
+
+constexpr int MOE_MAX_EXPERTS = 256;  // the reference's stack buffer (lfm2.rs:180)
+constexpr int MOE_MAX_USED = 16;
+constexpr int MOE_NC = 8;             // token columns per work item
+constexpr int MOE_WARPS = 8;
+
+struct MoeTile {
+    uint32_t expert, first, count;  // entries [first, first + count) of the bucket order, count <= MOE_NC
+};
+
+// ---- routing -------------------------------------------------------------------------------------
+// One CTA per token.  Warps take experts round-robin; lane-strided f32 dot, shuffle tree.
+__global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict__ x, const float *__restrict__ router,
+                                                        const float *__restrict__ bias, uint32_t hidden, uint32_t n_expert,
+                                                        uint32_t n_used, int softmax_gate, uint32_t *ids, float *weights,
+                                                        uint32_t *counts) {
+    __shared__ float probs[MOE_MAX_EXPERTS];
+    const uint32_t j = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float *xj = x + (size_t)j * hidden;
+    for (uint32_t e = warp; e < n_expert; e += blockDim.x >> 5) {
+        const float *r = router + (size_t)e * hidden;
+        float acc = 0.0f;
+        for (uint32_t i = lane; i < hidden; i += 32) acc = fmaf(r[i], xj[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) probs[e] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    if (softmax_gate) {
+        float mx = probs[0];
+        for (uint32_t e = 1; e < n_expert; ++e) mx = fmaxf(mx, probs[e]);
+        float sum = 0.0f;
+        for (uint32_t e = 0; e < n_expert; ++e) {
+            probs[e] = expf(probs[e] - mx);
+            sum += probs[e];
+        }
+        for (uint32_t e = 0; e < n_expert; ++e) probs[e] = probs[e] / sum;
+    } else {
+        for (uint32_t e = 0; e < n_expert; ++e) probs[e] = 1.0f / (1.0f + expf(-probs[e]));
+    }
+    uint32_t picked[MOE_MAX_USED];
+    float w[MOE_MAX_USED];
+    float denom = 0.0f;
+    for (uint32_t s = 0; s < n_used; ++s) {
+        int best = -1;
+        float best_v = 0.0f;
+        for (uint32_t e = 0; e < n_expert; ++e) {
+            bool taken = false;
+            for (uint32_t t = 0; t < s; ++t) taken |= picked[t] == e;
+            if (taken) continue;
+            const float v = probs[e] + (bias ? bias[e] : 0.0f);
+            // total order on finite values; strict > keeps the lower index on ties
+            if (best < 0 || v > best_v) {
+                best = (int)e;
+                best_v = v;
+            }
+        }
+        picked[s] = (uint32_t)best;
+        w[s] = probs[best];
+        denom += w[s];
+    }
+    denom = fmaxf(denom, 1.0f / 16384.0f);
+    for (uint32_t s = 0; s < n_used; ++s) {
+        ids[(size_t)j * n_used + s] = picked[s];
+        weights[(size_t)j * n_used + s] = w[s] / denom;
+        atomicAdd(counts + picked[s], 1u);
+    }
+}
+
+// One CTA: bucket offsets, cursors, and the work list.  counts is zeroed again for the next call.
+__global__ void moe_plan_kernel(uint32_t *counts, uint32_t n_expert, uint32_t nc, uint32_t *cursor, MoeTile *tiles,
+                                uint32_t *n_tiles) {
+    if (threadIdx.x != 0) return;
+    uint32_t off = 0, t = 0;
+    for (uint32_t e = 0; e < n_expert; ++e) {
+        const uint32_t c = counts[e];
+        cursor[e] = off;
+        for (uint32_t f = 0; f < c; f += nc) tiles[t++] = MoeTile{e, off + f, c - f < nc ? c - f : nc};
+        off += c;
+        counts[e] = 0;
+    }
+    *n_tiles = t;
+}
+
+// One CTA per (token, pick): take the next place in the expert's bucket and copy the token's Q8_0 column there.
+__global__ void __launch_bounds__(128) moe_scatter_kernel(const uint32_t *__restrict__ ids, uint32_t n_used, uint32_t hidden,
+                                                          ActView x, uint32_t *cursor, uint32_t *entry_of, float *g_scales,
+                                                          int8_t *g_quants, int16_t *g_sums) {
+    __shared__ uint32_t pos_s;
+    const uint32_t pair = blockIdx.x, j = pair / n_used;
+    if (threadIdx.x == 0) {
+        pos_s = atomicAdd(cursor + ids[pair], 1u);
+        entry_of[pair] = pos_s;
+    }
+    __syncthreads();
+    const size_t pos = pos_s;
+    const uint32_t *sq = (const uint32_t *)(x.quants + (size_t)j * hidden);
+    uint32_t *dq = (uint32_t *)(g_quants + pos * hidden);
+    for (uint32_t i = threadIdx.x; i < hidden / 4; i += blockDim.x) dq[i] = sq[i];
+    for (uint32_t i = threadIdx.x; i < hidden / 32; i += blockDim.x)
+        g_scales[pos * (hidden / 32) + i] = x.scales[(size_t)j * (hidden / 32) + i];
+    for (uint32_t i = threadIdx.x; i < hidden / 16; i += blockDim.x)
+        g_sums[pos * (hidden / 16) + i] = x.sums[(size_t)j * (hidden / 16) + i];
+}
+
+// ---- grouped GEMM ----------------------------------------------------------------------------------
+// blockIdx.y walks the work list; inside an item the CTA's warps take rows of the expert's matrices
+// (up to two segments sharing the activations: gate and up).  Cell (row i, entry c) -> y[c*ldc + i].
+struct MoeGemmParams {
+    WeightView w[2];
+    float *y[2];
+    int n_segs;
+    uint32_t m;  // rows per expert and segment
+    uint32_t k;
+    ActView x;   // columns in bucket order
+    uint32_t ldc;
+    const MoeTile *tiles;
+    const uint32_t *n_tiles;
+};
+
+template <int T, int NC>
+__global__ void __launch_bounds__(MOE_WARPS * 32) moe_gemm_kernel(const MoeGemmParams p) {
+    using F = Fmt<T>;
+    if (blockIdx.y >= *p.n_tiles) return;
+    const MoeTile tile = p.tiles[blockIdx.y];
+    const int lane = threadIdx.x & 31;
+    const uint32_t warp = blockIdx.x * MOE_WARPS + (threadIdx.x >> 5), n_warps = gridDim.x * MOE_WARPS;
+    const int items = p.k >> 5;
+    const ActView x{p.x.scales + (size_t)tile.first * (p.k / 32), p.x.quants + (size_t)tile.first * p.k,
+                    p.x.sums + (size_t)tile.first * (p.k / 16)};
+    const uint32_t total = p.m * p.n_segs;
+    for (uint32_t row = warp; row < total; row += n_warps) {
+        const int s = row >= p.m ? 1 : 0;
+        const uint32_t local = row - s * p.m;
+        const WeightView &w = p.w[s];
+        const size_t wrow = (size_t)tile.expert * p.m + local;
+        float acc[NC];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[c] = 0.0f;
+        for (int item = lane; item < items; item += 32) {
+            const typename F::Raw raw = F::load(w, wrow, item);
+            accumulate_item<T, NC>(raw, item, x, p.k, acc);
+        }
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[c] = warp_sum(acc[c]);
+        if (lane == 0) {
+#pragma unroll
+            for (int c = 0; c < NC; ++c)
+                if ((uint32_t)c < tile.count) p.y[s][(size_t)(tile.first + c) * p.ldc + local] = acc[c];
+        }
+    }
+}
+
+// out[j][i] = sum over picks in pick order of weight * expert_out[entry][i]; multiply and add rounded
+// separately, as the reference's `*acc += weight * v` is (lfm2.rs:891-897).
+__global__ void moe_combine_kernel(const float *__restrict__ expert_out, const uint32_t *__restrict__ entry_of,
+                                   const float *__restrict__ weights, uint32_t n_used, uint32_t hidden, size_t n, float *out) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n * hidden) return;
+    const size_t j = idx / hidden, i = idx - j * hidden;
+    float acc = 0.0f;
+    for (uint32_t s = 0; s < n_used; ++s) {
+        const size_t e = entry_of[j * n_used + s];
+        acc = __fadd_rn(acc, __fmul_rn(weights[j * n_used + s], expert_out[e * hidden + i]));
+    }
+    out[idx] = acc;
+}
+
+template <int T>
+int32_t launch_moe_gemm(const MoeGemmParams &p, uint32_t max_tiles, bool single, cudaStream_t st) {
+    const uint32_t rows = p.m * p.n_segs;
+    uint32_t gx = (rows + MOE_WARPS - 1) / MOE_WARPS;
+    const uint32_t want = (uint32_t)sm_count() * 8 / (max_tiles ? max_tiles : 1) + 1;  // a few waves over all items
+    if (gx > want) gx = want;
+    if (gx < 1) gx = 1;
+    if (single)
+        moe_gemm_kernel<T, 1><<<dim3(gx, max_tiles), MOE_WARPS * 32, 0, st>>>(p);
+    else
+        moe_gemm_kernel<T, MOE_NC><<<dim3(gx, max_tiles), MOE_WARPS * 32, 0, st>>>(p);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "moe grouped gemm launch");
+}
+
+}  // namespace
+
+struct cera_cuda_moe {
+    uint32_t n_expert = 0, n_used = 0, hidden = 0, ff = 0;
+    size_t max_tokens = 0;
+    int device = 0;
+    cera_cuda_weight *gate = nullptr, *up = nullptr, *down = nullptr;
+    char *base = nullptr;  // one allocation: router, bias and every scratch array
+    size_t bytes = 0;
+    float *router = nullptr, *bias = nullptr;
+    // scratch
+    float *xs = nullptr, *g_scales = nullptr, *f_scales = nullptr, *weights = nullptr, *g = nullptr, *u = nullptr,
+          *expert_out = nullptr;
+    int8_t *xq = nullptr, *g_quants = nullptr, *f_quants = nullptr;
+    int16_t *xsum = nullptr, *g_sums = nullptr, *f_sums = nullptr;
+    uint32_t *ids = nullptr, *counts = nullptr, *cursor = nullptr, *entry_of = nullptr, *n_tiles = nullptr;
+    MoeTile *tiles = nullptr;
+};
+
+extern "C" {
+
+int32_t cera_cuda_moe_create(uint32_t n_expert, uint32_t n_used, uint32_t hidden, uint32_t ff, int32_t ggml_type,
+                             const void *gate_exps, const void *up_exps, const void *down_exps, size_t gate_up_bytes,
+                             size_t down_bytes, const float *router, const float *exp_probs_b, size_t max_tokens,
+                             cera_cuda_moe **out) {
+    if (!gate_exps || !up_exps || !down_exps || !router || !out) return fail(CERA_CUDA_ERR_BAD_ARG, "moe_create: null argument");
+    if (n_expert == 0 || n_expert > MOE_MAX_EXPERTS || n_used == 0 || n_used > MOE_MAX_USED || n_used > n_expert)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "moe_create: %u experts, %u used (limits %d, %d)", n_expert, n_used, MOE_MAX_EXPERTS, MOE_MAX_USED);
+    if (hidden % 32 || ff % 32 || hidden == 0 || ff == 0 || max_tokens == 0)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "moe_create: hidden %u and expert width %u must be positive multiples of 32", hidden, ff);
+    auto *h = new (std::nothrow) cera_cuda_moe();
+    if (!h) return fail(CERA_CUDA_ERR_OOM, "moe_create: host allocation failed");
+    h->n_expert = n_expert;
+    h->n_used = n_used;
+    h->hidden = hidden;
+    h->ff = ff;
+    h->max_tokens = max_tokens;
+    cudaGetDevice(&h->device);
+    int32_t st = weight_upload(ggml_type, (size_t)n_expert * ff, hidden, gate_exps, gate_up_bytes, false, &h->gate);
+    if (st == CERA_CUDA_OK) st = weight_upload(ggml_type, (size_t)n_expert * ff, hidden, up_exps, gate_up_bytes, false, &h->up);
+    if (st == CERA_CUDA_OK) st = weight_upload(ggml_type, (size_t)n_expert * hidden, ff, down_exps, down_bytes, false, &h->down);
+    const size_t entries = max_tokens * n_used, pad = MOE_NC;  // a ragged tile still reads MOE_NC columns
+    size_t off = 0;
+    auto take = [&](size_t b) {
+        const size_t at = off;
+        off += (b + 255) & ~(size_t)255;
+        return at;
+    };
+    const size_t o_router = take((size_t)n_expert * hidden * 4), o_bias = take((size_t)n_expert * 4),
+                 o_xs = take(max_tokens * (hidden / 32) * 4), o_xq = take(max_tokens * hidden), o_xsum = take(max_tokens * (hidden / 16) * 2),
+                 o_gs = take((entries + pad) * (hidden / 32) * 4), o_gq = take((entries + pad) * hidden),
+                 o_gsum = take((entries + pad) * (hidden / 16) * 2), o_fs = take((entries + pad) * (ff / 32) * 4),
+                 o_fq = take((entries + pad) * ff), o_fsum = take((entries + pad) * (ff / 16) * 2), o_w = take(entries * 4),
+                 o_g = take(entries * ff * 4), o_u = take(entries * ff * 4), o_eo = take(entries * hidden * 4),
+                 o_ids = take(entries * 4), o_counts = take((size_t)n_expert * 4), o_cursor = take((size_t)n_expert * 4),
+                 o_entry = take(entries * 4), o_nt = take(4), o_tiles = take((entries / 1 + n_expert) * sizeof(MoeTile));
+    h->bytes = off;
+    if (st == CERA_CUDA_OK) st = check_cuda(cudaMalloc((void **)&h->base, off), "cudaMalloc(moe scratch)");
+    if (st == CERA_CUDA_OK) st = check_cuda(cudaMemset(h->base, 0, off), "cudaMemset(moe scratch)");
+    if (st == CERA_CUDA_OK) {
+        char *b = h->base;
+        h->router = (float *)(b + o_router);
+        h->bias = exp_probs_b ? (float *)(b + o_bias) : nullptr;
+        h->xs = (float *)(b + o_xs);
+        h->xq = (int8_t *)(b + o_xq);
+        h->xsum = (int16_t *)(b + o_xsum);
+        h->g_scales = (float *)(b + o_gs);
+        h->g_quants = (int8_t *)(b + o_gq);
+        h->g_sums = (int16_t *)(b + o_gsum);
+        h->f_scales = (float *)(b + o_fs);
+        h->f_quants = (int8_t *)(b + o_fq);
+        h->f_sums = (int16_t *)(b + o_fsum);
+        h->weights = (float *)(b + o_w);
+        h->g = (float *)(b + o_g);
+        h->u = (float *)(b + o_u);
+        h->expert_out = (float *)(b + o_eo);
+        h->ids = (uint32_t *)(b + o_ids);
+        h->counts = (uint32_t *)(b + o_counts);
+        h->cursor = (uint32_t *)(b + o_cursor);
+        h->entry_of = (uint32_t *)(b + o_entry);
+        h->n_tiles = (uint32_t *)(b + o_nt);
+        h->tiles = (MoeTile *)(b + o_tiles);
+        st = check_cuda(cudaMemcpy(h->router, router, (size_t)n_expert * hidden * 4, cudaMemcpyDefault), "cudaMemcpy(router)");
+        if (st == CERA_CUDA_OK && exp_probs_b)
+            st = check_cuda(cudaMemcpy(h->bias, exp_probs_b, (size_t)n_expert * 4, cudaMemcpyDefault), "cudaMemcpy(exp_probs_b)");
+    }
+    if (st != CERA_CUDA_OK) {
+        cera_cuda_moe_free(h);
+        return st;
+    }
+    *out = h;
+    return CERA_CUDA_OK;
+}
+
+int32_t cera_cuda_moe_ffn(cera_cuda_moe *h, const float *x_dev, size_t n, int32_t softmax_gate, float *out_dev,
+                          uint32_t *ids_out_dev, float *weights_out_dev, void *stream) {
+    if (!h || !x_dev || !out_dev) return fail(CERA_CUDA_ERR_BAD_ARG, "moe_ffn: null argument");
+    if (n > h->max_tokens) return fail(CERA_CUDA_ERR_BAD_ARG, "moe_ffn: %zu tokens, created for at most %zu", n, h->max_tokens);
+    if (n == 0) return CERA_CUDA_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint32_t hs = h->hidden, ff = h->ff, ku = h->n_used;
+    const size_t entries = n * ku;
+    const bool single = n == 1;
+    const uint32_t nc = single ? 1 : MOE_NC;
+    const uint32_t max_tiles = (uint32_t)(entries / nc + (single ? 0 : h->n_expert));
+    CERA_TRY(launch_quantize(x_dev, hs, n, false, h->xs, h->xq, h->xsum, st));
+    moe_route_kernel<<<(unsigned)n, 256, 0, st>>>(x_dev, h->router, h->bias, hs, h->n_expert, ku, softmax_gate, h->ids, h->weights,
+                                                  h->counts);
+    moe_plan_kernel<<<1, 32, 0, st>>>(h->counts, h->n_expert, nc, h->cursor, h->tiles, h->n_tiles);
+    moe_scatter_kernel<<<(unsigned)entries, 128, 0, st>>>(h->ids, ku, hs, ActView{h->xs, h->xq, h->xsum}, h->cursor, h->entry_of,
+                                                          h->g_scales, h->g_quants, h->g_sums);
+    count_launch(3);
+    CERA_CUDA_TRY(cudaGetLastError());
+    MoeGemmParams p{};
+    p.w[0] = h->gate->v;
+    p.w[1] = h->up->v;
+    p.y[0] = h->g;
+    p.y[1] = h->u;
+    p.n_segs = 2;
+    p.m = ff;
+    p.k = hs;
+    p.x = ActView{h->g_scales, h->g_quants, h->g_sums};
+    p.ldc = ff;
+    p.tiles = h->tiles;
+    p.n_tiles = h->n_tiles;
+    CERA_DISPATCH_BLOCK_TYPE(h->gate->v.type, CERA_TRY(launch_moe_gemm<TT>(p, max_tiles, single, st)));
+    CERA_TRY(launch_silu_mul(h->g, h->u, ff, entries, h->f_scales, h->f_quants, h->f_sums, st));
+    MoeGemmParams d{};
+    d.w[0] = h->down->v;
+    d.y[0] = h->expert_out;
+    d.n_segs = 1;
+    d.m = hs;
+    d.k = ff;
+    d.x = ActView{h->f_scales, h->f_quants, h->f_sums};
+    d.ldc = hs;
+    d.tiles = h->tiles;
+    d.n_tiles = h->n_tiles;
+    CERA_DISPATCH_BLOCK_TYPE(h->down->v.type, CERA_TRY(launch_moe_gemm<TT>(d, max_tiles, single, st)));
+    const size_t total = n * hs;
+    moe_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(h->expert_out, h->entry_of, h->weights, ku, hs, n, out_dev);
+    count_launch();
+    CERA_CUDA_TRY(cudaGetLastError());
+    if (ids_out_dev) CERA_CUDA_TRY(cudaMemcpyAsync(ids_out_dev, h->ids, entries * 4, cudaMemcpyDeviceToDevice, st));
+    if (weights_out_dev) CERA_CUDA_TRY(cudaMemcpyAsync(weights_out_dev, h->weights, entries * 4, cudaMemcpyDeviceToDevice, st));
+    return CERA_CUDA_OK;
+}
+
+size_t cera_cuda_moe_memory_bytes(const cera_cuda_moe *h) {
+    if (!h) return 0;
+    return h->bytes + (h->gate ? h->gate->bytes : 0) + (h->up ? h->up->bytes : 0) + (h->down ? h->down->bytes : 0);
+}
+
+void cera_cuda_moe_free(cera_cuda_moe *h) {
+    if (!h) return;
+    if (h->gate) cera_cuda_weight_free(h->gate);
+    if (h->up) cera_cuda_weight_free(h->up);
+    if (h->down) cera_cuda_weight_free(h->down);
+    if (h->base) cudaFree(h->base);
+    delete h;
+}
+
+}  // extern "C"

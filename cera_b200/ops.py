@@ -7,6 +7,7 @@ hands raw device pointers to the C ABI and launches on torch's current stream.
 """
 import ctypes as C
 
+import numpy as np
 import torch
 
 from . import _lib
@@ -205,3 +206,46 @@ def quantize_weights(ggml_type, w):
 
 __all__ = [n for n in dir() if not n.startswith("_")]
 _ = (_lib, row_bytes)
+
+
+class MoeFfn:
+    """Routed feed-forward of one lfm2moe layer (cera/src/model/lfm2.rs:735-901 forward_moe_ffn):
+    stacked expert tensors, F32 router, optional selection bias.  Byte tensors are raw GGUF blocks
+    (CUDA uint8 tensors or numpy arrays)."""
+
+    def __init__(self, n_expert, n_used, hidden, ff, ggml_type, gate_exps, up_exps, down_exps, router, exp_probs_b=None,
+                 max_tokens=512):
+        def raw(a):
+            if isinstance(a, torch.Tensor):
+                a = a.contiguous()
+                return a, C.c_void_p(a.data_ptr()), a.numel() * a.element_size()
+            a = np.ascontiguousarray(a)
+            return a, C.c_void_p(a.ctypes.data), a.nbytes
+        keep = [raw(gate_exps), raw(up_exps), raw(down_exps), raw(router)]
+        if keep[0][2] != keep[1][2]:
+            raise ValueError("gate and up expert tensors differ in size")
+        bias = raw(exp_probs_b) if exp_probs_b is not None else (None, None, 0)
+        self.handle = C.c_void_p()
+        self.n_expert, self.n_used, self.hidden, self.ff = n_expert, n_used, hidden, ff
+        check(lib.cera_cuda_moe_create(n_expert, n_used, hidden, ff, ggml_type, keep[0][1], keep[1][1], keep[2][1], keep[0][2],
+                                       keep[2][2], keep[3][1], bias[1], max_tokens, C.byref(self.handle)))
+
+    def __call__(self, x, softmax_gate=False, want_routing=False):
+        """x: CUDA f32 [n, hidden] -> out [n, hidden] (and ids [n, n_used], weights [n, n_used])."""
+        x = _dev(x, torch.float32).contiguous().view(-1, self.hidden)
+        n = x.shape[0]
+        out = torch.empty_like(x)
+        ids = torch.empty(n, self.n_used, dtype=torch.int32, device=x.device) if want_routing else None
+        wts = torch.empty(n, self.n_used, dtype=torch.float32, device=x.device) if want_routing else None
+        check(lib.cera_cuda_moe_ffn(self.handle, _ptr(x), n, 1 if softmax_gate else 0, _ptr(out), _ptr(ids), _ptr(wts), _stream()))
+        return (out, ids, wts) if want_routing else out
+
+    def memory_bytes(self):
+        return lib.cera_cuda_moe_memory_bytes(self.handle)
+
+    def close(self):
+        if getattr(self, "handle", None):
+            lib.cera_cuda_moe_free(self.handle)
+            self.handle = None
+
+    __del__ = close

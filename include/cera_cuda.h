@@ -286,6 +286,34 @@ CERA_API int32_t cera_cuda_last_hidden(cera_cuda_model *m, float *out);
 CERA_API uint64_t cera_cuda_launch_count(const cera_cuda_model *m);
 CERA_API void cera_cuda_model_free(cera_cuda_model *m);
 
+/* ------------------------------------------------------------------------ */
+/* Routed feed-forward of an lfm2moe layer (cera/src/model/lfm2.rs:177-226 select_experts,
+ * 673-715 route_experts, 735-901 forward_moe_ffn, 914-937 prefill_moe_ffn).
+ *
+ * gate_exps / up_exps are the stacked tensors blk.N.ffn_{gate,up}_exps.weight,
+ * [n_expert][ff][hidden] raw GGUF blocks with expert stride ff rows; down_exps is
+ * [n_expert][hidden][ff] (cera/src/model/gpu_weight_source.rs:179-257).  router is
+ * blk.N.ffn_gate_inp.weight, F32 [n_expert][hidden]; exp_probs_b is blk.N.exp_probs_b.bias,
+ * F32 [n_expert], or NULL for zero bias.  Pointers may be host or device; all are copied. */
+typedef struct cera_cuda_moe cera_cuda_moe;
+CERA_API int32_t cera_cuda_moe_create(uint32_t n_expert, uint32_t n_used, uint32_t hidden, uint32_t ff,
+                                      int32_t ggml_type, const void *gate_exps, const void *up_exps,
+                                      const void *down_exps, size_t gate_up_bytes, size_t down_bytes,
+                                      const float *router, const float *exp_probs_b, size_t max_tokens,
+                                      cera_cuda_moe **out);
+/* x_dev and out_dev are token-major [n][hidden] f32 (the reference's prefill layout is the
+ * transpose, hidden x n; its decode layout is n == 1).  softmax_gate == 0 is the reference's rule:
+ * sigmoid probabilities, selection by probability + bias with ties to the lower index, weights =
+ * unbiased probabilities of the selected experts over max(their sum, 2^-14).  softmax_gate != 0
+ * replaces the sigmoid by a softmax over all experts and keeps the rest.  out = sum in selection
+ * order of weight * expert FFN output; every expert projection is the int8 product against the
+ * Q8_0 form of its input.  ids_out_dev / weights_out_dev (optional, [n][n_used]) receive the routing. */
+CERA_API int32_t cera_cuda_moe_ffn(cera_cuda_moe *moe, const float *x_dev, size_t n, int32_t softmax_gate,
+                                   float *out_dev, uint32_t *ids_out_dev, float *weights_out_dev,
+                                   void *stream);
+CERA_API size_t cera_cuda_moe_memory_bytes(const cera_cuda_moe *moe);
+CERA_API void cera_cuda_moe_free(cera_cuda_moe *moe);
+
 #ifdef __cplusplus
 }
 #endif
