@@ -73,3 +73,4 @@ def test_ranks_reproduce_single_gpu():
     assert report["world"] == world and len(report["cases"]) == 4
     for case in report["cases"]:
         assert case["stream_equal"], case
+        assert case["bit_identical"], case  # a row's dot product is the same arithmetic on any number of ranks
