@@ -235,6 +235,44 @@ def gemv_microbench(torch, cb, tname, m, k, iters):
     return algo, us, 2 * iters + copies
 
 
+def attention_microbench(torch, cb, ctx, f16, iters):
+    """Flash-decode attention at the Llama-3-8B head shape (32 query / 8 KV heads of 128) over `ctx` cached
+    positions: distinct KV copies (more than 2x L2 in total) visited round-robin inside a CUDA graph."""
+    import math
+    nh, nkv, hd = 32, 8, 128
+    kv_dim = nkv * hd
+    esz = 2 if f16 else 4
+    kv_bytes = 2 * ctx * kv_dim * esz
+    copies = max(2, min(64, -(-(256 << 20) // kv_bytes)))
+    caches = []
+    for i in range(copies):
+        kc = cb.synth_normal(ctx * kv_dim, seed=900 + 2 * i, sigma=1.0).view(ctx, kv_dim)
+        vc = cb.synth_normal(ctx * kv_dim, seed=901 + 2 * i, sigma=1.0).view(ctx, kv_dim)
+        caches.append((kc.half(), vc.half()) if f16 else (kc, vc))
+    q = cb.synth_normal(nh * hd, seed=3, sigma=1.0)
+    ws = torch.empty(cb._lib.lib.cera_cuda_decode_attention_workspace_bytes(nh, hd, ctx), dtype=torch.uint8, device="cuda")
+    scale = 1.0 / math.sqrt(hd)
+    for kc, vc in caches:
+        cb.decode_attention(q, kc, vc, nh, nkv, hd, ctx, scale, workspace=ws)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(iters):
+                kc, vc = caches[i % copies]
+                cb.decode_attention(q, kc, vc, nh, nkv, hd, ctx, scale, workspace=ws)
+        graph.replay()
+        side.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(side)
+        graph.replay()
+        e1.record(side)
+        side.synchronize()
+    us = e0.elapsed_time(e1) * 1000.0 / iters
+    return kv_bytes + 2 * nh * hd * 4, us
+
+
 def gemm_microbench(torch, cb, tname, m, k, n, iters):
     """Prefill GEMM out[m x n] = W x X for pre-quantized columns: CUDA events over a graph of `iters` launches."""
     t, blk, bb = BLOCKS[tname]
@@ -423,7 +461,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
                     help="prompt tokens before the timed decode (512 is the benchmark; shorter only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--only", default=None, choices=["roofline", "gemv-sweep", "gemm-sweep", "moe"],
+    ap.add_argument("--only", default=None, choices=["roofline", "gemv-sweep", "gemm-sweep", "moe", "attn-sweep"],
                     help="run just the dominant-kernel microbench (the case ncu captures are taken on)")
     ap.add_argument("--iters", type=int, default=200, help="timed launches of the kernel microbench")
     args = ap.parse_args()
@@ -446,6 +484,17 @@ def main():
             print(json.dumps({"type": tname, "m": m, "k": k, "us": round(us, 3), "algorithmic_bytes": algo,
                               "gbs": round(algo / us / 1e3, 1), "frac_of_measured": round(algo / us / 1e3 / hbm, 4),
                               "frac_of_8000": round(algo / us / 1e3 / 8000.0, 4)}), flush=True)
+    elif args.only == "attn-sweep":
+        import torch
+        import cera_b200 as cb
+        hbm, which = measured_peaks()
+        for f16 in (False, True):
+            for ctx in (512, 4096, 16384, 32768):
+                algo, us = attention_microbench(torch, cb, ctx, f16, args.iters)
+                gbs = algo / us / 1e3
+                print(json.dumps({"kernel": "flash-decode attention 32/8 heads x 128", "ctx": ctx, "kv_dtype": "f16" if f16 else "f32",
+                                  "algorithmic_bytes": algo, "us": round(us, 2), "achieved_gbs": round(gbs, 1),
+                                  "frac": round(gbs / hbm, 3), "peak_source": which}), flush=True)
     elif args.only == "moe":
         import torch
         import cera_b200 as cb

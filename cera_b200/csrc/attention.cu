@@ -189,7 +189,7 @@ attn_split_kernel(const float *__restrict__ q, const void *__restrict__ kc, cons
 
 // One CTA per query head, one thread per output dim.
 __global__ void attn_merge_kernel(const float *__restrict__ ws, uint32_t n_splits, uint32_t hd, float *__restrict__ out,
-                                  float *scales, int8_t *quants, int16_t *sums) {
+                                  float *scales, int8_t *quants, int16_t *sums, const TpHook tp) {
     pdl_trigger();
     pdl_wait();
     const uint32_t h = blockIdx.x, d = threadIdx.x;
@@ -215,6 +215,11 @@ __global__ void attn_merge_kernel(const float *__restrict__ ws, uint32_t n_split
         quants[o] = (int8_t)qv;
         if ((d & 31) == 0) scales[o / 32] = scale;
         if ((d & 15) == 0) sums[o / 16] = (int16_t)hs;
+        if (tp.push) {
+            tp_push(tp.ctx, quants + o, (int8_t)qv);
+            if ((d & 31) == 0) tp_push(tp.ctx, scales + o / 32, scale);
+            if ((d & 15) == 0) tp_push(tp.ctx, sums + o / 16, (int16_t)hs);
+        }
     }
 }
 
@@ -312,7 +317,7 @@ uint32_t attn_pick_splits(size_t n_kv_heads, size_t seq_len_hint) {
 int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
                                    size_t n_kv_heads, size_t head_dim, size_t seq_len, const uint32_t *seq_len_dev,
                                    uint32_t n_splits, float scale, float *out, void *workspace, size_t workspace_bytes,
-                                   float *scales, int8_t *quants, int16_t *sums, cudaStream_t st) {
+                                   float *scales, int8_t *quants, int16_t *sums, cudaStream_t st, const TpHook *tp) {
     if (!q || !kc || !vc || !out || !workspace) return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: null argument");
     if (n_kv_heads == 0 || n_heads % n_kv_heads)
         return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: n_heads (%zu) must be a positive multiple of n_kv_heads (%zu)",
@@ -352,7 +357,8 @@ int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *v
     CERA_TRY(att_status);
     count_launch();
     return check_cuda(launch_k(attn_merge_kernel, dim3((unsigned)n_heads), dim3((unsigned)head_dim), 0, st,
-                               (const float *)ws, n_splits, (uint32_t)head_dim, out, scales, quants, sums),
+                               (const float *)ws, n_splits, (uint32_t)head_dim, out, scales, quants, sums,
+                               tp ? *tp : TpHook{}),
                       "attention merge launch");
 }
 

@@ -38,6 +38,7 @@ struct GemvParams {
     uint32_t ldy;  // row stride of y in floats
     uint32_t ldc;  // column stride of y in floats
     int epilogue;
+    TpHook tp;
 };
 
 template <int T, int NC, int UNROLL>
@@ -45,6 +46,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
     using F = Fmt<T>;
     pdl_trigger();
     pdl_wait();
+    tp_arrive_wait(p.tp.ctx, p.tp.wait_slot);
     const int lane = threadIdx.x & 31;
     const uint32_t warp = blockIdx.x * WARPS + (threadIdx.x >> 5);
     const uint32_t n_warps = gridDim.x * WARPS;
@@ -80,7 +82,9 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
                 float *yc = y + (size_t)c * p.ldc;
-                *yc = p.epilogue == EPI_ADD ? __fadd_rn(*yc, acc[c]) : acc[c];
+                const float r = p.epilogue == EPI_ADD ? __fadd_rn(*yc, acc[c]) : acc[c];
+                *yc = r;
+                if (p.tp.push) tp_push(p.tp.ctx, yc, r);
             }
         }
     }
@@ -154,19 +158,22 @@ static bool force_direct() {
 }
 
 int32_t launch_gemv_fused(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
-                          cudaStream_t st, bool *taken) {
-    CERA_TRY(launch_gemv_tma(segs, n_segs, x, epilogue, fusion, st, taken));
-    if (*taken) return CERA_CUDA_OK;
-    return launch_gemv_rows(segs, n_segs, x, epilogue, fusion, st, taken);
+                          cudaStream_t st, bool *taken, const TpHook *tp) {
+    const bool hooked = tp && (tp->push || tp->wait_slot != TP_NO_SLOT);  // the TMA-staged variant carries no exchange hooks
+    if (!hooked) {
+        CERA_TRY(launch_gemv_tma(segs, n_segs, x, epilogue, fusion, st, taken));
+        if (*taken) return CERA_CUDA_OK;
+    }
+    return launch_gemv_rows(segs, n_segs, x, epilogue, fusion, st, taken, tp);
 }
 
 // All segments must share the type and k.  n_cols in {1,2,4,8}.
 int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_cols, size_t ldy, int epilogue,
-                    cudaStream_t st, size_t ldc, bool batch_tile) {
+                    cudaStream_t st, size_t ldc, bool batch_tile, const TpHook *tp) {
     if (n_segs < 1 || n_segs > MAX_SEGS) return fail(CERA_CUDA_ERR_BAD_ARG, "gemv: %d segments", n_segs);
     if (n_cols == 1 && ldy == 1 && !batch_tile && !force_direct()) {
         bool taken = false;
-        CERA_TRY(launch_gemv_fused(segs, n_segs, x, epilogue, nullptr, st, &taken));
+        CERA_TRY(launch_gemv_fused(segs, n_segs, x, epilogue, nullptr, st, &taken, tp));
         if (taken) return CERA_CUDA_OK;
     }
     GemvParams p{};
@@ -186,6 +193,7 @@ int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_
     p.epilogue = epilogue;
     p.ldy = (uint32_t)ldy;
     p.ldc = (uint32_t)ldc;
+    if (tp) p.tp = *tp;
     if ((uintptr_t)x.quants % 16 || (uintptr_t)x.sums % 4 || (p.k % 32))
         return fail(CERA_CUDA_ERR_BAD_ARG, "gemv: activation quants must be 16-byte aligned and k a multiple of 32");
     CERA_DISPATCH_BLOCK_TYPE(segs[0].w.type, return (launch_cols<TT>(p, n_cols, st)));

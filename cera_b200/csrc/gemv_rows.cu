@@ -40,6 +40,7 @@ struct RowsParams {
     int wpr;  // warps sharing one row: 1, 2, 4 or 8
     int epilogue;
     GemvFusion f;
+    TpHook tp;
 };
 
 template <int T, int UNR>
@@ -73,6 +74,7 @@ __global__ void __launch_bounds__(RW_THREADS) gemv_rows_kernel(const RowsParams 
             // the first rows' weight loads are in flight; only now wait for the producer of the activations
             pdl_trigger();
             pdl_wait();
+            tp_arrive_wait(p.tp.ctx, p.tp.wait_slot);
             if (active) load_act<T>(p.x, tau, act);
             first = false;
         }
@@ -110,7 +112,9 @@ __global__ void __launch_bounds__(RW_THREADS) gemv_rows_kernel(const RowsParams 
                     for (int u = 0; u < UNR; ++u)
                         if (valid[u]) {
                             float *y = p.y[seg[u]] + local[u];
-                            *y = p.epilogue == EPI_ADD ? __fadd_rn(*y, acc[u]) : acc[u];
+                            const float r = p.epilogue == EPI_ADD ? __fadd_rn(*y, acc[u]) : acc[u];
+                            *y = r;
+                            if (p.tp.push) tp_push(p.tp.ctx, y, r);
                         }
                 }
             }
@@ -136,7 +140,9 @@ __global__ void __launch_bounds__(RW_THREADS) gemv_rows_kernel(const RowsParams 
                     }
                 if (ok) {
                     float *y = p.y[sg] + loc;
-                    *y = p.epilogue == EPI_ADD ? __fadd_rn(*y, v) : v;
+                    const float r = p.epilogue == EPI_ADD ? __fadd_rn(*y, v) : v;
+                    *y = r;
+                    if (p.tp.push) tp_push(p.tp.ctx, y, r);
                 }
             }
             __syncthreads();
@@ -176,7 +182,7 @@ int32_t launch_rows_typed(const RowsParams &p, cudaStream_t st) {
 // outside this kernel's rules (k not a multiple of 128, wider than 8 warps of lane tasks, or a
 // fused epilogue whose alignment rules do not hold); nothing was launched and the caller falls back.
 int32_t launch_gemv_rows(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
-                         cudaStream_t st, bool *taken) {
+                         cudaStream_t st, bool *taken, const TpHook *tp) {
     *taken = false;
     if (n_segs < 1 || n_segs > RW_MAX_SEGS) return CERA_CUDA_OK;
     const int type = segs[0].w.type;
@@ -184,6 +190,7 @@ int32_t launch_gemv_rows(const GemvSeg *segs, int n_segs, const ActView &x, int 
     if (!is_block_type(type) || t128 == 0 || t128 > 32 * RW_WARPS) return CERA_CUDA_OK;
     RowsParams p{};
     if (fusion) p.f = *fusion;
+    if (tp) p.tp = *tp;
     if ((uintptr_t)x.quants % 16 || (uintptr_t)x.scales % 16 || (uintptr_t)x.sums % 16) return CERA_CUDA_OK;
     uint32_t rows = 0;
     for (int i = 0; i < n_segs; ++i) {

@@ -143,24 +143,22 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
     const uint32_t r = m->tp_rank;
     const bool tp = m->tp_size > 1;
     const float scale = 1.0f / sqrtf((float)c.head_dim);
-    uint32_t slot = 0;
-    // push this rank's slice of up to three arrays of the exchange region to every peer
-    auto exchange = [&](const void *a, size_t an, const void *b, size_t bn, const void *d, size_t dn) -> int32_t {
-        if (!tp) return CERA_CUDA_OK;
-        TpRange rg[3] = {{(uint32_t)((const char *)a - m->region), (uint32_t)an}, {0, 0}, {0, 0}};
-        int n = 1;
-        if (b) rg[n++] = {(uint32_t)((const char *)b - m->region), (uint32_t)bn};
-        if (d) rg[n++] = {(uint32_t)((const char *)d - m->region), (uint32_t)dn};
-        if (slot >= m->tp_slots) return fail(CERA_CUDA_ERR_STATE, "decode step: exchange slot %u of %u", slot, m->tp_slots);
-        return launch_tp_exchange(m->tp, rg, n, slot++, st);
+    // Exchange slots of layer l: 4l = Q8_0 attention output, 4l+1 = residual after o-proj, 4l+2 = Q8_0 SwiGLU
+    // activations, 4l+3 = residual after down-proj; then 4L = logits, 4L+1 = greedy pairs.  The producing kernel
+    // mirrors its stores into the peers' regions; the consuming kernel signals and waits in its prologue.
+    const uint32_t n_layers = (uint32_t)m->layers.size();
+    auto hook = [&](uint32_t wait_slot, bool push) {
+        TpHook h;
+        if (tp) {
+            h.ctx = m->tp;
+            h.wait_slot = wait_slot;
+            h.push = push ? 1 : 0;
+        }
+        return h;
     };
     // this rank's part of a Q8_0 activation buffer that holds `l` of its elements per rank
     auto act_slice = [&](const ActBuf &a, size_t l) {
         return ActBuf{a.scales + r * (l / 32), a.quants + r * l, a.sums + r * (l / 16)};
-    };
-    auto exchange_act = [&](const ActBuf &a, size_t l) {
-        const ActBuf s = act_slice(a, l);
-        return exchange(s.scales, l / 32 * 4, s.quants, l, s.sums, l / 16 * 2);
     };
     float *hidden_slice = m->hidden + r * m->l_hs;
 
@@ -168,9 +166,13 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
     CERA_TRY(launch_embed(m->embd->v, 0, m->dyn, m->hidden, st));
     const bool norm_rope = c.rope_type == 0;
     if (norm_rope) CERA_TRY(launch_rope_table(m->dyn + 1, c.head_dim, m->theta_scale, m->rope_freqs, m->rope_cs, st));
-    for (auto &L : m->layers) {
+    for (uint32_t li = 0; li < n_layers; ++li) {
+        Layer &L = m->layers[li];
+        const uint32_t s0 = 4 * li;
+        const TpHook h_norm1 = hook(li ? s0 - 1 : TP_NO_SLOT, false), h_merge = hook(TP_NO_SLOT, true), h_wo = hook(s0, true),
+                     h_norm2 = hook(s0 + 1, false), h_silu = hook(TP_NO_SLOT, true), h_down = hook(s0 + 2, true);
         CERA_TRY(launch_rmsnorm(m->hidden, L.attn_norm, hs, 1, c.rms_norm_eps, nullptr, m->act_hs.scales,
-                                m->act_hs.quants, m->act_hs.sums, st));
+                                m->act_hs.quants, m->act_hs.sums, st, &h_norm1));
         bool fused_qkv = false;
         if (norm_rope && L.wq->v.type == L.wk->v.type && L.wq->v.type == L.wv->v.type) {
             // q/k/v GEMV with RoPE and the KV-cache append as its epilogue
@@ -201,13 +203,11 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
         const ActBuf aq = act_slice(m->act_q, m->l_qd);
         CERA_TRY(launch_decode_attention_ex(m->q, L.kc, L.vc, c.kv_f16, m->l_heads, m->l_kv_heads, c.head_dim, 0,
                                             m->dyn + 2, n_splits, scale, m->attn, m->attn_ws, m->attn_ws_bytes,
-                                            aq.scales, aq.quants, aq.sums, st));
-        CERA_TRY(exchange_act(m->act_q, m->l_qd));
+                                            aq.scales, aq.quants, aq.sums, st, &h_merge));
         GemvSeg so{L.wo->v, hidden_slice};
-        CERA_TRY(launch_gemv(&so, 1, m->act_q.view(), 1, 1, EPI_ADD, st));
-        CERA_TRY(exchange(hidden_slice, m->l_hs * 4, nullptr, 0, nullptr, 0));
+        CERA_TRY(launch_gemv(&so, 1, m->act_q.view(), 1, 1, EPI_ADD, st, 1, false, &h_wo));
         CERA_TRY(launch_rmsnorm(m->hidden, L.ffn_norm, hs, 1, c.rms_norm_eps, nullptr, m->act_hs.scales,
-                                m->act_hs.quants, m->act_hs.sums, st));
+                                m->act_hs.quants, m->act_hs.sums, st, &h_norm2));
         if (L.gate->v.type == L.up->v.type) {
             GemvSeg segs[2] = {{L.gate->v, m->g}, {L.up->v, m->u}};
             CERA_TRY(launch_gemv(segs, 2, m->act_hs.view(), 1, 1, EPI_STORE, st));
@@ -217,27 +217,34 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
             CERA_TRY(launch_gemv(&su, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
         }
         const ActBuf af = act_slice(m->act_ff, m->l_ff);
-        CERA_TRY(launch_silu_mul(m->g, m->u, m->l_ff, 1, af.scales, af.quants, af.sums, st));
-        CERA_TRY(exchange_act(m->act_ff, m->l_ff));
+        CERA_TRY(launch_silu_mul(m->g, m->u, m->l_ff, 1, af.scales, af.quants, af.sums, st, &h_silu));
         GemvSeg sd{L.down->v, hidden_slice};
-        CERA_TRY(launch_gemv(&sd, 1, m->act_ff.view(), 1, 1, EPI_ADD, st));
-        CERA_TRY(exchange(hidden_slice, m->l_hs * 4, nullptr, 0, nullptr, 0));
+        CERA_TRY(launch_gemv(&sd, 1, m->act_ff.view(), 1, 1, EPI_ADD, st, 1, false, &h_down));
     }
-    if (kind == G_BODY) return CERA_CUDA_OK;
+    const uint32_t s_last = 4 * n_layers - 1, s_logits = 4 * n_layers, s_pick = 4 * n_layers + 1;
+    if (kind == G_BODY) {
+        // nothing in this graph consumes the last residual exchange; the next step's embedding row overwrites the
+        // buffer the peers are still writing, so wait for their slices here
+        if (tp) CERA_TRY(launch_tp_exchange(m->tp, nullptr, 0, s_last, st));
+        return CERA_CUDA_OK;
+    }
+    const TpHook h_final = hook(s_last, false);
     CERA_TRY(launch_rmsnorm(m->hidden, m->out_norm, hs, 1, c.rms_norm_eps, m->final_hidden, m->act_hs.scales,
-                            m->act_hs.quants, m->act_hs.sums, st));
+                            m->act_hs.quants, m->act_hs.sums, st, &h_final));
     const cera_cuda_weight *ow = m->output ? m->output : m->embd_head;
     float *logits_slice = m->logits + r * m->l_vocab;
     GemvSeg sl{ow->v, logits_slice};
     CERA_TRY(launch_gemv(&sl, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
-    if (kind == G_LOGITS) CERA_TRY(exchange(logits_slice, m->l_vocab * 4, nullptr, 0, nullptr, 0));
+    if (kind == G_LOGITS && tp) {
+        const TpRange rg{(uint32_t)((const char *)logits_slice - m->region), (uint32_t)(m->l_vocab * 4)};
+        CERA_TRY(launch_tp_exchange(m->tp, &rg, 1, s_logits, st));
+    }
     if (kind == G_GREEDY || kind == G_CHAIN) {
         if (!tp) {
             CERA_TRY(launch_argmax(m->logits, c.vocab_size, m->tok_out, m->argmax_scratch, st));
         } else {
             CERA_TRY(launch_argmax(logits_slice, m->l_vocab, m->tp_words + 32, m->argmax_scratch, st));
-            if (slot >= m->tp_slots) return fail(CERA_CUDA_ERR_STATE, "decode step: exchange slot %u of %u", slot, m->tp_slots);
-            CERA_TRY(launch_tp_argmax(m->tp, logits_slice, (uint32_t)m->l_vocab, m->tp_words + 32, m->tok_out, slot++, st));
+            CERA_TRY(launch_tp_argmax(m->tp, logits_slice, (uint32_t)m->l_vocab, m->tp_words + 32, m->tok_out, s_pick, st));
         }
     }
     if (kind == G_CHAIN) {

@@ -3,16 +3,19 @@
 
 #include "act.cuh"
 #include "common.cuh"
+#include "tp.cuh"
 
 namespace cera {
 
 int32_t launch_quantize(const float *x, size_t k, size_t n, bool strided, float *scales, int8_t *quants,
                         int16_t *sums, cudaStream_t st);
 // out_f32 and the quantized outputs are each optional (null = skip).
+// tp (optional, tensor-parallel decode step): rmsnorm waits for the exchange that completes x; silu_mul mirrors its
+// quantized output into the peers' regions.
 int32_t launch_rmsnorm(const float *x, const float *weight, size_t n_elem, size_t n_cols, float eps, float *out_f32,
-                       float *scales, int8_t *quants, int16_t *sums, cudaStream_t st);
+                       float *scales, int8_t *quants, int16_t *sums, cudaStream_t st, const TpHook *tp = nullptr);
 int32_t launch_silu_mul(float *gate, const float *up, size_t n_elem, size_t n_cols, float *scales, int8_t *quants,
-                        int16_t *sums, cudaStream_t st);
+                        int16_t *sums, cudaStream_t st, const TpHook *tp = nullptr);
 
 // Up to three weight matrices of one type sharing the same activations
 // (q/k/v, gate/up), handled by one launch.
@@ -32,20 +35,22 @@ struct GemvFusion {
     int kv_f16 = 0;
     uint32_t head_dim = 0, kv_dim = 0;
 };
+// tp (optional): wait for the exchange that completes x before reading it and / or mirror the output stores
+// (EPI_STORE / EPI_ADD, single column) into the peers' regions.
 int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_cols, size_t ldy, int epilogue,
-                    cudaStream_t st, size_t ldc = 1, bool batch_tile = false);
+                    cudaStream_t st, size_t ldc = 1, bool batch_tile = false, const TpHook *tp = nullptr);
 int32_t launch_gemm_ex(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
                        cudaStream_t st);
 // Register-resident-activation single-column GEMV.  *taken = false: shape outside its rules,
 // nothing was launched and the caller uses the item-wise kernel.
 int32_t launch_gemv_rows(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
-                         cudaStream_t st, bool *taken);
+                         cudaStream_t st, bool *taken, const TpHook *tp = nullptr);
 // Same contract through the TMA-staged kernel (bulk asynchronous copies into a shared-memory ring).
 int32_t launch_gemv_tma(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
                         cudaStream_t st, bool *taken);
 // Tries the TMA-staged kernel, then the register-streaming one.
 int32_t launch_gemv_fused(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
-                          cudaStream_t st, bool *taken);
+                          cudaStream_t st, bool *taken, const TpHook *tp = nullptr);
 // cos/sin of every rotation pair at position *pos_dev, same arithmetic as launch_rope.
 int32_t launch_rope_table(const uint32_t *pos_dev, size_t head_dim, float theta_scale, const float *freq_factors,
                           float *table, cudaStream_t st);
@@ -74,7 +79,8 @@ uint32_t attn_pick_splits(size_t n_kv_heads, size_t seq_len_hint);
 int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
                                    size_t n_kv_heads, size_t head_dim, size_t seq_len, const uint32_t *seq_len_dev,
                                    uint32_t n_splits, float scale, float *out, void *workspace, size_t workspace_bytes,
-                                   float *scales, int8_t *quants, int16_t *sums, cudaStream_t st);
+                                   float *scales, int8_t *quants, int16_t *sums, cudaStream_t st,
+                                   const TpHook *tp = nullptr);  // tp: mirror the Q8_0 output into the peers' regions
 
 int32_t launch_embed(const WeightView &w, uint32_t token, const uint32_t *token_dev, float *out, cudaStream_t st);
 // n rows: out[j][k] = row tokens_dev[j] of the table.
@@ -94,21 +100,11 @@ size_t argmax_scratch_words();
 int32_t launch_argmax(const float *x, size_t n, uint32_t *out, uint32_t *scratch, cudaStream_t st);
 
 // ---- tensor-parallel exchange (tp.cu) -------------------------------------------
-constexpr uint32_t TP_MAX_RANKS = 8;
-struct TpCtx {
-    char *peer[TP_MAX_RANKS];  // every rank's exchange region as mapped on this device; peer[rank] is its own
-    uint32_t rank, size;
-    uint32_t flags_off;        // byte offset of flags[n_slots][TP_MAX_RANKS] (u32) inside a region
-    uint32_t pairs_off;        // byte offset of the greedy pairs[TP_MAX_RANKS] {f32 bits, index}
-    const uint32_t *seq;       // device: sequence number of the running step
-    uint32_t *status;          // device: 0, or 0x80000000 | peer << 24 | slot + 1 after a wait ran out
-    uint64_t timeout_ns;
-};
 struct TpRange {
     uint32_t off, bytes;  // inside the exchange region
 };
 int32_t launch_tp_tick(uint32_t *seq, cudaStream_t st);
-// Pushes the ranges to the same offsets of every peer, then waits for every peer's push of this slot.
+// Pushes the ranges (0 to 3) to the same offsets of every peer, then waits for every peer's push of this slot.
 int32_t launch_tp_exchange(const TpCtx &ctx, const TpRange *ranges, int n_ranges, uint32_t slot, cudaStream_t st);
 // logits_local[local_n] are this rank's rows, *local_idx its local first maximum; *tok_out = global pick.
 int32_t launch_tp_argmax(const TpCtx &ctx, const float *logits_local, uint32_t local_n, const uint32_t *local_idx,

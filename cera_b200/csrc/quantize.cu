@@ -34,7 +34,7 @@ constexpr int RN_THREADS = 256, RN_WARPS = 8, RN_CH = 16;
 
 __global__ void __launch_bounds__(RN_THREADS) rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ weight,
                                                               size_t n_elem, float eps, float *out_f32, float *scales,
-                                                              int8_t *quants, int16_t *sums) {
+                                                              int8_t *quants, int16_t *sums, const TpHook tp) {
     __shared__ double red[RN_WARPS];
     __shared__ float inv_s;
     pdl_trigger();
@@ -52,6 +52,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_kernel(const float *__rest
         }
     }
     pdl_wait();
+    tp_arrive_wait(tp.ctx, tp.wait_slot);
     const float *xc = x + col * n_elem;
     double ss = 0.0;
     for (uint32_t c0 = 0; c0 < nblk; c0 += RN_WARPS * RN_CH) {
@@ -99,7 +100,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_kernel(const float *__rest
 }
 
 __global__ void silu_mul_kernel(float *gate, const float *__restrict__ up, size_t n_elem, size_t n_cols,
-                                float *scales, int8_t *quants, int16_t *sums) {
+                                float *scales, int8_t *quants, int16_t *sums, const TpHook tp) {
     pdl_trigger();
     pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -114,6 +115,11 @@ __global__ void silu_mul_kernel(float *gate, const float *__restrict__ up, size_
         quants[i] = (int8_t)q;
         if (lane == 0) scales[i / 32] = scale;
         if ((lane & 15) == 0) sums[i / 16] = (int16_t)hs;
+        if (tp.push) {
+            tp_push(tp.ctx, quants + i, (int8_t)q);
+            if (lane == 0) tp_push(tp.ctx, scales + i / 32, scale);
+            if ((lane & 15) == 0) tp_push(tp.ctx, sums + i / 16, (int16_t)hs);
+        }
     }
 }
 
@@ -133,26 +139,27 @@ int32_t launch_quantize(const float *x, size_t k, size_t n, bool strided, float 
 }
 
 int32_t launch_rmsnorm(const float *x, const float *weight, size_t n_elem, size_t n_cols, float eps, float *out_f32,
-                       float *scales, int8_t *quants, int16_t *sums, cudaStream_t st) {
+                       float *scales, int8_t *quants, int16_t *sums, cudaStream_t st, const TpHook *tp) {
     if (!x || !weight) return fail(CERA_CUDA_ERR_BAD_ARG, "rmsnorm: null argument");
     if (quants && (n_elem % 32 || !scales || !sums))
         return fail(CERA_CUDA_ERR_BAD_ARG, "rmsnorm+quantize: n=%zu must be a multiple of 32", n_elem);
     if (n_elem == 0 || n_cols == 0) return CERA_CUDA_OK;
     const int threads = RN_THREADS;
-    CERA_CUDA_TRY(launch_k(rmsnorm_kernel, dim3((unsigned)n_cols), dim3(threads), 0, st, x, weight, n_elem, eps, out_f32, scales, quants, sums));
+    CERA_CUDA_TRY(launch_k(rmsnorm_kernel, dim3((unsigned)n_cols), dim3(threads), 0, st, x, weight, n_elem, eps, out_f32, scales, quants, sums,
+                           tp ? *tp : TpHook{}));
     count_launch();
     return check_cuda(cudaGetLastError(), "rmsnorm launch");
 }
 
 int32_t launch_silu_mul(float *gate, const float *up, size_t n_elem, size_t n_cols, float *scales, int8_t *quants,
-                        int16_t *sums, cudaStream_t st) {
+                        int16_t *sums, cudaStream_t st, const TpHook *tp) {
     if (!gate || !up) return fail(CERA_CUDA_ERR_BAD_ARG, "silu_mul: null argument");
     if (quants && n_elem % 32) return fail(CERA_CUDA_ERR_BAD_ARG, "silu_mul+quantize: n=%zu must be a multiple of 32", n_elem);
     const size_t total = n_elem * n_cols;
     if (total == 0) return CERA_CUDA_OK;
     const int threads = 256;
     CERA_CUDA_TRY(launch_k(silu_mul_kernel, dim3((unsigned)((total + threads - 1) / threads)), dim3(threads), 0, st, gate, up,
-                           n_elem, n_cols, scales, quants, sums));
+                           n_elem, n_cols, scales, quants, sums, tp ? *tp : TpHook{}));
     count_launch();
     return check_cuda(cudaGetLastError(), "silu_mul launch");
 }

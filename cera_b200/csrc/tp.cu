@@ -24,38 +24,6 @@ namespace cera {
 
 namespace {
 
-__device__ __forceinline__ uint64_t global_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-// True once *flag has reached seq (wrap-safe); false when the budget ran out first.
-__device__ bool wait_flag(const uint32_t *flag, uint32_t seq, uint64_t timeout_ns) {
-    const uint64_t t0 = global_ns();
-    for (uint32_t it = 0;; ++it) {
-        if ((int32_t)(ld_acquire_sys(flag) - seq) >= 0) return true;
-        if ((it & 15) == 15) {
-            if (global_ns() - t0 > timeout_ns) return false;
-            if (it > 4096) __nanosleep(200);
-        }
-    }
-}
-
-__device__ __forceinline__ void record_timeout(uint32_t *status, uint32_t slot, uint32_t peer) {
-    atomicCAS(status, 0u, 0x80000000u | (peer << 24) | ((slot + 1) & 0xFFFFFFu));
-}
-
 __device__ void push_range(char *dst, const char *src, TpRange r) {
     if (((r.off | r.bytes) & 15) == 0) {
         const uint4 *s = (const uint4 *)(src + r.off);
@@ -83,10 +51,10 @@ __global__ void __launch_bounds__(512) tp_exchange_kernel(TpCtx c, TpRange r0, T
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
-        st_release_sys((uint32_t *)(dst + c.flags_off) + (size_t)slot * TP_MAX_RANKS + c.rank, seq);
+        tp_st_release_sys((uint32_t *)(dst + c.flags_off) + (size_t)slot * TP_MAX_RANKS + c.rank, seq);
         if (*(volatile uint32_t *)c.status == 0) {
             const uint32_t *mine = (const uint32_t *)(src + c.flags_off) + (size_t)slot * TP_MAX_RANKS + p;
-            if (!wait_flag(mine, seq, c.timeout_ns)) record_timeout(c.status, slot, p);
+            if (!tp_wait_flag(mine, seq, c.timeout_ns)) tp_record_timeout(c.status, slot, p);
         }
     }
 }
@@ -109,10 +77,10 @@ __global__ void __launch_bounds__(32) tp_argmax_kernel(TpCtx c, const float *log
         *((volatile unsigned long long *)(c.peer[t] + c.pairs_off) + c.rank) = pair;
         if (t != c.rank) {
             __threadfence_system();
-            st_release_sys((uint32_t *)(c.peer[t] + c.flags_off) + (size_t)slot * TP_MAX_RANKS + c.rank, seq);
+            tp_st_release_sys((uint32_t *)(c.peer[t] + c.flags_off) + (size_t)slot * TP_MAX_RANKS + c.rank, seq);
             if (*(volatile uint32_t *)c.status == 0) {
                 const uint32_t *mine = (const uint32_t *)(own + c.flags_off) + (size_t)slot * TP_MAX_RANKS + t;
-                if (!wait_flag(mine, seq, c.timeout_ns)) record_timeout(c.status, slot, t);
+                if (!tp_wait_flag(mine, seq, c.timeout_ns)) tp_record_timeout(c.status, slot, t);
             }
         }
     }
@@ -150,10 +118,10 @@ int32_t launch_tp_tick(uint32_t *seq, cudaStream_t st) {
 
 int32_t launch_tp_exchange(const TpCtx &ctx, const TpRange *ranges, int n_ranges, uint32_t slot, cudaStream_t st) {
     if (ctx.size < 2) return CERA_CUDA_OK;
-    if (n_ranges < 1 || n_ranges > 3) return fail(CERA_CUDA_ERR_BAD_ARG, "tp_exchange: 1..3 ranges, got %d", n_ranges);
+    if (n_ranges < 0 || n_ranges > 3) return fail(CERA_CUDA_ERR_BAD_ARG, "tp_exchange: 0..3 ranges, got %d", n_ranges);
     TpRange r[3] = {{0, 0}, {0, 0}, {0, 0}};
     uint32_t most = 0;
-    for (int i = 0; i < n_ranges; ++i) {
+    for (int i = 0; i < n_ranges && ranges; ++i) {
         if ((ranges[i].off | ranges[i].bytes) & 3)
             return fail(CERA_CUDA_ERR_BAD_ARG, "tp_exchange: range %d (offset %u, %u bytes) is not 4-byte aligned", i,
                         ranges[i].off, ranges[i].bytes);

@@ -90,10 +90,11 @@ def test_decode_attention_other_groupings(nh, nkv, hd):
     _attn_case(torch, cb, nh, nkv, hd, 300, False, seed=7)
 
 
-def test_decode_attention_16k():
+@pytest.mark.parametrize("seq,f16", [(16384, False), (32768, False), (32768, True)])
+def test_decode_attention_long_context(seq, f16):
     torch = need_gpu()
     import cera_b200 as cb
-    _attn_case(torch, cb, 32, 8, 128, 16384, False, seed=5)
+    _attn_case(torch, cb, 32, 8, 128, seq, f16, seed=5)
 
 
 def test_decode_attention_rejects_unsupported_shapes():
