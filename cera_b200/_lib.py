@@ -45,6 +45,7 @@ SIGNATURES = {
     "cera_cuda_gemm_preq": (_i32, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _p]),
     "cera_cuda_block_sums": (_i32, [_p, _sz, _p, _p, _p, _p]),
     "cera_cuda_rmsnorm": (_i32, [_p, _p, _sz, _f, _p, _p]),
+    "cera_cuda_rmsnorm_q8_0": (_i32, [_p, _p, _sz, _f, _p, _p, _p, _p, _p]),
     "cera_cuda_silu_mul": (_i32, [_p, _p, _sz, _p]),
     "cera_cuda_rope": (_i32, [_p, _p, _sz, _sz, _sz, _sz, _f, _p, _i32, _p]),
     "cera_cuda_decode_attention_workspace_bytes": (_sz, [_sz, _sz, _sz]),

@@ -15,7 +15,14 @@
 // Arithmetic contract: cera/src/model/transformer.rs:1166-1305 with
 // cera/src/backend/cpu.rs:3222-3363 (scores = q.K * scale, softmax with the
 // polynomial expf, weighted V sum); the online form agrees within f32 rounding.
+#include <cooperative_groups.h>
+
+#include <cstdlib>
+#include <cstring>
+
 #include "ops.h"
+
+namespace cg = cooperative_groups;
 
 namespace cera {
 
@@ -23,6 +30,8 @@ namespace {
 
 constexpr int ATT_WARPS = 8;
 constexpr int MAX_SPLITS = 64;
+constexpr uint32_t ATT_CLUSTER_FLAG = 0x80;
+constexpr size_t ATT_CLUSTER_MAX_SEQ = 4096;
 
 template <int VEC, bool F16>
 __device__ __forceinline__ void load_row(const void *base, size_t elem_off, float (&v)[VEC]) {
@@ -57,25 +66,16 @@ __device__ __forceinline__ void load_row(const void *base, size_t elem_off, floa
     }
 }
 
-// Workspace record per (query head, split): out[head_dim], max, sum.
+// The scan of one CTA over cached positions [t_begin, t_end) of KV head kvh for its G query heads: on return
+// acc / m_run / l_run hold this warp's unnormalised output, running maximum and running sum (the state of head
+// lane % G, replicated over its P lanes).
 template <int VEC, int G, bool F16>
-__global__ void __launch_bounds__(ATT_WARPS * 32)
-attn_split_kernel(const float *__restrict__ q, const void *__restrict__ kc, const void *__restrict__ vc,
-                  uint32_t seq_len_imm, const uint32_t *__restrict__ seq_len_dev, uint32_t n_kv_heads, float scale,
-                  float *__restrict__ ws) {
+__device__ __forceinline__ void attn_scan(const float *__restrict__ q, const void *__restrict__ kc, const void *__restrict__ vc,
+                                          uint32_t kvh, uint32_t t_begin, uint32_t t_end, size_t kv_dim, float scale,
+                                          float (&acc)[G][VEC], float &m_run, float &l_run) {
     constexpr int HD = VEC * 32;
     constexpr int P = 32 / G;  // positions per warp tile
-    pdl_trigger();
-    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t kvh = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
-    const uint32_t seq_len = seq_len_dev ? *seq_len_dev : seq_len_imm;
-    const size_t kv_dim = (size_t)n_kv_heads * HD;
-
-    uint32_t chunk = (seq_len + n_splits - 1) / n_splits;
-    chunk = (chunk + P - 1) / P * P;
-    const uint32_t t_begin = min(seq_len, split * chunk), t_end = min(seq_len, t_begin + chunk);
-
     // q slices of the G heads this CTA serves
     float qv[G][VEC];
 #pragma unroll
@@ -83,12 +83,12 @@ attn_split_kernel(const float *__restrict__ q, const void *__restrict__ kc, cons
 #pragma unroll
         for (int v = 0; v < VEC; ++v) qv[g][v] = q[(size_t)(kvh * G + g) * HD + lane * VEC + v];
 
-    float acc[G][VEC];
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
         for (int v = 0; v < VEC; ++v) acc[g][v] = 0.0f;
-    float m_run = -INFINITY, l_run = 0.0f;  // state of head (lane % G), replicated over its P lanes
+    m_run = -INFINITY;
+    l_run = 0.0f;
 
     const size_t head_off = (size_t)kvh * HD + lane * VEC;
     for (uint32_t t0 = t_begin + warp * P; t0 < t_end; t0 += ATT_WARPS * P) {
@@ -153,6 +153,30 @@ attn_split_kernel(const float *__restrict__ q, const void *__restrict__ kc, cons
                 for (int v = 0; v < VEC; ++v) acc[g][v] = fmaf(pg, vr[i][v], acc[g][v]);
             }
     }
+}
+
+// Workspace record per (query head, split): out[head_dim], max, sum.
+template <int VEC, int G, bool F16>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_split_kernel(const float *__restrict__ q, const void *__restrict__ kc, const void *__restrict__ vc,
+                  uint32_t seq_len_imm, const uint32_t *__restrict__ seq_len_dev, uint32_t n_kv_heads, float scale,
+                  float *__restrict__ ws) {
+    constexpr int HD = VEC * 32;
+    constexpr int P = 32 / G;  // positions per warp tile
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t kvh = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
+    const uint32_t seq_len = seq_len_dev ? *seq_len_dev : seq_len_imm;
+    const size_t kv_dim = (size_t)n_kv_heads * HD;
+
+    uint32_t chunk = (seq_len + n_splits - 1) / n_splits;
+    chunk = (chunk + P - 1) / P * P;
+    const uint32_t t_begin = min(seq_len, split * chunk), t_end = min(seq_len, t_begin + chunk);
+
+    float acc[G][VEC];
+    float m_run, l_run;
+    attn_scan<VEC, G, F16>(q, kc, vc, kvh, t_begin, t_end, kv_dim, scale, acc, m_run, l_run);
 
     // merge the warps of this CTA
     __shared__ float s_acc[ATT_WARPS][G][HD];
@@ -221,6 +245,102 @@ __global__ void attn_merge_kernel(const float *__restrict__ ws, uint32_t n_split
             if ((d & 15) == 0) tp_push(tp.ctx, sums + o / 16, (int16_t)hs);
         }
     }
+}
+
+// Short contexts (up to ATT_CLUSTER_MAX_SEQ positions): the splits of one KV head form a thread-block
+// cluster and merge through distributed shared memory, so one launch does what the split and merge
+// kernels do and the partial results never leave the SMs.  Grid = n_kv_heads * CL CTAs in clusters of
+// CL; CTA r of a cluster scans the r-th share of the positions, leaves its (out, max, sum) per query
+// head in its own shared memory, and after a cluster barrier combines G*HD/CL of the outputs from all
+// CL shares (same arithmetic as attn_merge_kernel), emitting f32 and Q8_0.
+template <int VEC, int G, bool F16>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_cluster_kernel(const float *__restrict__ q, const void *__restrict__ kc, const void *__restrict__ vc,
+                    uint32_t seq_len_imm, const uint32_t *__restrict__ seq_len_dev, uint32_t n_kv_heads, float scale,
+                    float *__restrict__ out, float *scales, int8_t *quants, int16_t *sums, const TpHook tp) {
+    constexpr int HD = VEC * 32;
+    constexpr int P = 32 / G;
+    __shared__ float s_acc[ATT_WARPS][G][HD];
+    __shared__ float s_m[ATT_WARPS][G], s_l[ATT_WARPS][G];
+    __shared__ float part[G][HD];      // this CTA's share, read by the whole cluster
+    __shared__ float part_m[G], part_l[G];
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t CL = cluster.num_blocks(), split = cluster.block_rank();
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t kvh = blockIdx.x / CL;
+    const uint32_t seq_len = seq_len_dev ? *seq_len_dev : seq_len_imm;
+    const size_t kv_dim = (size_t)n_kv_heads * HD;
+    uint32_t chunk = (seq_len + CL - 1) / CL;
+    chunk = (chunk + P - 1) / P * P;
+    const uint32_t t_begin = min(seq_len, split * chunk), t_end = min(seq_len, t_begin + chunk);
+
+    float acc[G][VEC];
+    float m_run, l_run;
+    attn_scan<VEC, G, F16>(q, kc, vc, kvh, t_begin, t_end, kv_dim, scale, acc, m_run, l_run);
+
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) s_acc[warp][g][lane * VEC + v] = acc[g][v];
+    if (lane < G) {
+        s_m[warp][lane] = m_run;
+        s_l[warp][lane] = l_run;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+        const int g = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, s_m[w][g]);
+        float L = 0.0f, O = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) {
+            const float f = s_m[w][g] == -INFINITY ? 0.0f : ggml_expf(s_m[w][g] - M);
+            L = fmaf(s_l[w][g], f, L);
+            O = fmaf(s_acc[w][g][d], f, O);
+        }
+        part[g][d] = O;
+        if (d == 0) {
+            part_m[g] = M;
+            part_l[g] = L;
+        }
+    }
+    cluster.sync();
+    // outputs [split * per, (split + 1) * per) of this KV head's G*HD; per is a multiple of 32, so every warp
+    // that enters the loop is whole and quantizes one Q8_0 block
+    const int per = G * HD / (int)CL;
+    for (int i = threadIdx.x; i < per; i += blockDim.x) {
+        const int idx = (int)split * per + i, g = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+        for (uint32_t r = 0; r < CL; ++r) M = fmaxf(M, cluster.map_shared_rank(&part_m[0], r)[g]);
+        double L = 0.0;
+        float O = 0.0f;
+        for (uint32_t r = 0; r < CL; ++r) {
+            const float m = cluster.map_shared_rank(&part_m[0], r)[g];
+            const float f = m == -INFINITY ? 0.0f : ggml_expf(m - M);
+            L += (double)(cluster.map_shared_rank(&part_l[0], r)[g] * f);
+            O = fmaf(cluster.map_shared_rank(&part[0][0], r)[g * HD + d], f, O);
+        }
+        const float v = O * (float)(1.0 / L);
+        const size_t o = (size_t)(kvh * G + g) * HD + d;
+        out[o] = v;
+        if (quants) {
+            float qs;
+            int hs;
+            const int qv = quantize_lane(v, qs, hs);
+            quants[o] = (int8_t)qv;
+            if ((d & 31) == 0) scales[o / 32] = qs;
+            if ((d & 15) == 0) sums[o / 16] = (int16_t)hs;
+            if (tp.push) {
+                tp_push(tp.ctx, quants + o, (int8_t)qv);
+                if ((d & 31) == 0) tp_push(tp.ctx, scales + o / 32, qs);
+                if ((d & 15) == 0) tp_push(tp.ctx, sums + o / 16, (int16_t)hs);
+            }
+        }
+    }
+    cluster.sync();  // peers may still be reading this CTA's share
 }
 
 // Causal attention for a batch of prompt tokens: one warp per (query head, query token), online softmax
@@ -298,13 +418,60 @@ int32_t launch_split(bool f16, dim3 grid, cudaStream_t st, const float *q, const
                                seq_dev, n_kv, scale, ws), "attention launch");
 }
 
+template <int VEC, int G>
+int32_t launch_cluster(bool f16, uint32_t cl, cudaStream_t st, const float *q, const void *kc, const void *vc, uint32_t seq_len,
+                       const uint32_t *seq_dev, uint32_t n_kv, float scale, float *out, float *scales, int8_t *quants,
+                       int16_t *sums, const TpHook &tp) {
+    if (cl > 8) {
+        static thread_local int configured_dev = -1;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (configured_dev != dev) {
+            CERA_CUDA_TRY(cudaFuncSetAttribute(attn_cluster_kernel<VEC, G, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+            CERA_CUDA_TRY(cudaFuncSetAttribute(attn_cluster_kernel<VEC, G, false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+            configured_dev = dev;
+        }
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_kv * cl);
+    cfg.blockDim = dim3(ATT_WARPS * 32);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cl;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    if (f16)
+        return check_cuda(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<VEC, G, true>, q, kc, vc, seq_len, seq_dev, n_kv, scale, out,
+                                             scales, quants, sums, tp), "attention (cluster) launch");
+    return check_cuda(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<VEC, G, false>, q, kc, vc, seq_len, seq_dev, n_kv, scale, out,
+                                         scales, quants, sums, tp), "attention (cluster) launch");
+}
+
 }  // namespace
 
 size_t attn_workspace_bytes(size_t n_heads, size_t head_dim, size_t) {
     return n_heads * MAX_SPLITS * (head_dim + 2) * sizeof(float);
 }
 
+// Plan for a decode attention over seq_len_hint positions.  Up to ATT_CLUSTER_MAX_SEQ positions: the one-launch
+// cluster kernel, returned as ATT_CLUSTER_FLAG | cluster size (1, 2, 4, 8 or 16; about 64 positions per CTA, more
+// once the cluster is full).  Beyond: the number of splits of the two-kernel path.
+// CERA_CUDA_ATTN=split keeps every length on the two-kernel path.
 uint32_t attn_pick_splits(size_t n_kv_heads, size_t seq_len_hint) {
+    static const bool no_cluster = [] {
+        const char *e = getenv("CERA_CUDA_ATTN");
+        return e && strcmp(e, "split") == 0;
+    }();
+    if (!no_cluster && seq_len_hint <= ATT_CLUSTER_MAX_SEQ) {
+        uint32_t cl = 1;
+        while (cl < 16 && (size_t)cl * 64 < seq_len_hint) cl <<= 1;  // 16 CTAs per cluster: beyond the portable 8, opted into
+        return ATT_CLUSTER_FLAG | cl;
+    }
     // Fill the machine about twice over, but never give a split fewer than 64 positions.
     size_t want = (size_t)(2 * sm_count() + n_kv_heads - 1) / n_kv_heads;
     const size_t by_len = (seq_len_hint + 63) / 64;
@@ -326,12 +493,21 @@ int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *v
     if (seq_len == 0 && !seq_len_dev) return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: empty KV cache");
     if (workspace_bytes < attn_workspace_bytes(n_heads, head_dim, seq_len))
         return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: workspace of %zu bytes is too small", workspace_bytes);
-    if (n_splits < 1 || n_splits > MAX_SPLITS) return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: %u splits", n_splits);
-    const dim3 grid((unsigned)n_kv_heads, n_splits);
+    const bool clustered = (n_splits & ATT_CLUSTER_FLAG) != 0;
+    uint32_t cl = n_splits & ~ATT_CLUSTER_FLAG;
+    if (clustered ? (cl != 1 && cl != 2 && cl != 4 && cl != 8 && cl != 16) : (n_splits < 1 || n_splits > MAX_SPLITS))
+        return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: split plan 0x%x", n_splits);
+    // every CTA of a cluster finishes whole 32-wide Q8_0 blocks of the G*head_dim outputs of its KV head
+    while (clustered && cl > 1 && (G * head_dim / cl) % 32) cl >>= 1;
+    const dim3 grid((unsigned)n_kv_heads, clustered ? 1 : n_splits);
     float *ws = (float *)workspace;
     const bool f16 = kv_f16 != 0;
     const uint32_t sl = (uint32_t)seq_len, nkv = (uint32_t)n_kv_heads;
-#define CERA_ATT(VEC, GG) att_status = launch_split<VEC, GG>(f16, grid, st, q, kc, vc, sl, seq_len_dev, nkv, scale, ws)
+    const TpHook hook = tp ? *tp : TpHook{};
+#define CERA_ATT(VEC, GG)                                                                                                  \
+    att_status = clustered ? launch_cluster<VEC, GG>(f16, cl, st, q, kc, vc, sl, seq_len_dev, nkv, scale, out, scales, quants, \
+                                                     sums, hook)                                                            \
+                           : launch_split<VEC, GG>(f16, grid, st, q, kc, vc, sl, seq_len_dev, nkv, scale, ws)
     bool ok = true;
     int32_t att_status = CERA_CUDA_OK;
     if (head_dim == 128) {
@@ -355,6 +531,7 @@ int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *v
                     "(head_dim 64 or 128, group 4 or 8)", head_dim, G);
     count_launch();
     CERA_TRY(att_status);
+    if (clustered) return CERA_CUDA_OK;
     count_launch();
     return check_cuda(launch_k(attn_merge_kernel, dim3((unsigned)n_heads), dim3((unsigned)head_dim), 0, st,
                                (const float *)ws, n_splits, (uint32_t)head_dim, out, scales, quants, sums,

@@ -28,13 +28,15 @@ __global__ void quantize_kernel(const float *__restrict__ x, size_t k, size_t n,
 
 // RMSNorm of one column per CTA (cera/src/backend/cpu.rs:2479-2496: f64 sum of
 // squares, inv = (float)(1/sqrt(mean+eps)), x*inv*w left to right), then
-// optionally the Q8_0 quantizer on the normed values.  Latency-bound: 256 threads, every
-// thread's x and w values fetched once with all loads issued before the reduction.
-constexpr int RN_THREADS = 256, RN_WARPS = 8, RN_CH = 16;
+// optionally the Q8_0 quantizer on the normed values.  Latency-bound and on the critical path of
+// every projection: 32 warps, every thread's x and w values fetched once with all loads issued
+// before the reduction, and at most four 32-element blocks quantized per warp one after another
+// (up to 4096 elements; longer columns loop).
+constexpr int RN_WARPS = 32, RN_THREADS = RN_WARPS * 32, RN_CH = 4;
 
 __global__ void __launch_bounds__(RN_THREADS) rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ weight,
-                                                              size_t n_elem, float eps, float *out_f32, float *scales,
-                                                              int8_t *quants, int16_t *sums, const TpHook tp) {
+                                                              size_t n_elem, double inv_n, float eps, float *out_f32,
+                                                              float *scales, int8_t *quants, int16_t *sums, const TpHook tp) {
     __shared__ double red[RN_WARPS];
     __shared__ float inv_s;
     pdl_trigger();
@@ -42,7 +44,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_kernel(const float *__rest
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t nblk = (uint32_t)((n_elem + 31) >> 5);
     const bool single = nblk <= RN_WARPS * RN_CH;  // up to 4096 elements stay in registers
-    // lane `lane` of warp `warp` owns element `lane` of 32-blocks warp, warp+8, ...
+    // lane `lane` of warp `warp` owns element `lane` of 32-blocks warp, warp+32, ...
     float wv[RN_CH], xv[RN_CH];
     if (single) {
 #pragma unroll
@@ -68,11 +70,13 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_kernel(const float *__rest
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (lane == 0) red[warp] = ss;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        double t = 0.0;
+    if (warp == 0) {
+        double t = red[lane];
 #pragma unroll
-        for (int w = 0; w < RN_WARPS; ++w) t += red[w];
-        inv_s = (float)(1.0 / sqrt(t / (double)n_elem + (double)eps));
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        // 1/sqrt(mean + eps) in f64, narrowed once: the reciprocal square root and the multiplication by 1/n are each
+        // within an f64 ulp of the reference's sqrt and divisions, far below the f32 rounding that follows
+        if (lane == 0) inv_s = (float)rsqrt(t * inv_n + (double)eps);
     }
     __syncthreads();
     const float inv = inv_s;
@@ -145,8 +149,8 @@ int32_t launch_rmsnorm(const float *x, const float *weight, size_t n_elem, size_
         return fail(CERA_CUDA_ERR_BAD_ARG, "rmsnorm+quantize: n=%zu must be a multiple of 32", n_elem);
     if (n_elem == 0 || n_cols == 0) return CERA_CUDA_OK;
     const int threads = RN_THREADS;
-    CERA_CUDA_TRY(launch_k(rmsnorm_kernel, dim3((unsigned)n_cols), dim3(threads), 0, st, x, weight, n_elem, eps, out_f32, scales, quants, sums,
-                           tp ? *tp : TpHook{}));
+    CERA_CUDA_TRY(launch_k(rmsnorm_kernel, dim3((unsigned)n_cols), dim3(threads), 0, st, x, weight, n_elem, 1.0 / (double)n_elem, eps, out_f32, scales,
+                           quants, sums, tp ? *tp : TpHook{}));
     count_launch();
     return check_cuda(cudaGetLastError(), "rmsnorm launch");
 }
@@ -184,6 +188,12 @@ int32_t cera_cuda_rmsnorm(const float *x_dev, const float *weight_dev, size_t n,
                           void *stream) {
     if (!out_dev) return fail(CERA_CUDA_ERR_BAD_ARG, "rmsnorm: null output");
     return launch_rmsnorm(x_dev, weight_dev, n, 1, eps, out_dev, nullptr, nullptr, nullptr, (cudaStream_t)stream);
+}
+
+int32_t cera_cuda_rmsnorm_q8_0(const float *x_dev, const float *weight_dev, size_t n, float eps, float *out_dev,
+                               float *scales_dev, int8_t *quants_dev, int16_t *sums_dev, void *stream) {
+    if (!scales_dev || !quants_dev || !sums_dev) return fail(CERA_CUDA_ERR_BAD_ARG, "rmsnorm_q8_0: null output");
+    return launch_rmsnorm(x_dev, weight_dev, n, 1, eps, out_dev, scales_dev, quants_dev, sums_dev, (cudaStream_t)stream);
 }
 
 int32_t cera_cuda_silu_mul(float *gate_dev, const float *up_dev, size_t n, void *stream) {

@@ -133,6 +133,16 @@ def rmsnorm(x, weight, eps):
     return out
 
 
+def rmsnorm_q8_0(x, weight, eps):
+    """RMSNorm and the Q8_0 quantizer in one launch -> (normed f32, Q8Activations)."""
+    x = _dev(x, torch.float32)
+    out = torch.empty_like(x)
+    acts = Q8Activations(x.numel(), 1, device=x.device)
+    check(lib.cera_cuda_rmsnorm_q8_0(_ptr(x), _ptr(_dev(weight, torch.float32)), x.numel(), eps, _ptr(out),
+                                     _ptr(acts.scales), _ptr(acts.quants), _ptr(acts.sums), _stream()))
+    return out, acts
+
+
 def silu_mul(gate, up):
     gate = _dev(gate, torch.float32).clone()
     check(lib.cera_cuda_silu_mul(_ptr(gate), _ptr(_dev(up, torch.float32)), gate.numel(), _stream()))

@@ -131,6 +131,13 @@ CERA_API int32_t cera_cuda_block_sums(const cera_cuda_weight *w, size_t row, con
 CERA_API int32_t cera_cuda_rmsnorm(const float *x_dev, const float *weight_dev, size_t n, float eps,
                                    float *out_dev, void *stream);
 /* cera/src/backend/cpu.rs:2570-2575: gate = silu(gate) * up. */
+/* RMSNorm followed by the Q8_0 activation quantizer in one launch, as the decode step uses it before
+ * every projection (cera/src/model/transformer.rs:1313-1345 runs cpu::rmsnorm then the quantizer of
+ * cera/src/backend/cpu.rs:969-1041).  out_dev (f32, optional) receives the normed vector; scales /
+ * quants / sums its Q8_0 form (n a multiple of 32). */
+CERA_API int32_t cera_cuda_rmsnorm_q8_0(const float *x_dev, const float *weight_dev, size_t n, float eps,
+                                        float *out_dev, float *scales_dev, int8_t *quants_dev,
+                                        int16_t *sums_dev, void *stream);
 CERA_API int32_t cera_cuda_silu_mul(float *gate_dev, const float *up_dev, size_t n, void *stream);
 /* cera/src/backend/cpu.rs:5009-5180.  rope_type 0 = NORM (adjacent pairs,
  * optional freq_factors_dev[head_dim/2]), 1 = NEOX. */

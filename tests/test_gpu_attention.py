@@ -30,6 +30,23 @@ def test_rmsnorm_and_silu_mul():
         assert_bits(cb.silu_mul(_cuda(torch, g), _cuda(torch, u)).cpu().numpy(), O.silu_mul(g, u), "silu_mul")
 
 
+@pytest.mark.parametrize("n", [32, 1024, 4096, 8192, 14336])
+def test_rmsnorm_with_fused_quantizer(n):
+    """The normed vector and its Q8_0 form from one launch: the quantizer bytes are those of the
+    stand-alone quantizer applied to the same f32 values."""
+    torch = need_gpu()
+    import cera_b200 as cb
+    x = O.synth_normal(n, 31, 2.0)
+    w = O.synth_normal(n, 32, 1.0)
+    out, acts = cb.rmsnorm_q8_0(_cuda(torch, x), _cuda(torch, w), 1e-5)
+    want = O.rmsnorm(x, w, 1e-5)
+    assert np.allclose(out.cpu().numpy(), want, rtol=2e-7, atol=0)
+    s, q = O.quantize_q8_0(out.cpu().numpy())
+    assert_bits(acts.scales.cpu().numpy(), s, "scales")
+    assert np.array_equal(acts.quants.cpu().numpy(), q)
+    assert np.array_equal(acts.sums.cpu().numpy().astype(np.int32), q.astype(np.int32).reshape(-1, 16).sum(axis=1))
+
+
 @pytest.mark.parametrize("rope_type", [0, 1])
 @pytest.mark.parametrize("pos", [0, 1, 511, 32767])
 def test_rope(rope_type, pos):
