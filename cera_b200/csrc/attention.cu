@@ -468,8 +468,11 @@ uint32_t attn_pick_splits(size_t n_kv_heads, size_t seq_len_hint) {
         return e && strcmp(e, "split") == 0;
     }();
     if (!no_cluster && seq_len_hint <= ATT_CLUSTER_MAX_SEQ) {
+        // about 64 positions per CTA up to the portable cluster of 8 (measured faster than 16 up to 1024 positions);
+        // longer contexts take 16 CTAs per cluster, which the kernel opts into
         uint32_t cl = 1;
-        while (cl < 16 && (size_t)cl * 64 < seq_len_hint) cl <<= 1;  // 16 CTAs per cluster: beyond the portable 8, opted into
+        while (cl < 8 && (size_t)cl * 64 < seq_len_hint) cl <<= 1;
+        if (seq_len_hint > 1024) cl = 16;
         return ATT_CLUSTER_FLAG | cl;
     }
     // Fill the machine about twice over, but never give a split fewer than 64 positions.
