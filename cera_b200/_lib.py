@@ -72,6 +72,11 @@ SIGNATURES = {
     "cera_cuda_launch_count": (_u64, [_p]),
     "cera_cuda_model_free": (None, [_p]),
     "cera_cuda_moe_create": (_i32, [_u32, _u32, _u32, _u32, _i32, _p, _p, _p, _sz, _sz, _p, _p, _sz, C.POINTER(_p)]),
+    "cera_cuda_moe_create_ep": (_i32, [_u32, _u32, _u32, _u32, _i32, _p, _p, _p, _sz, _sz, _p, _p, _sz, _u32, _u32, _sz,
+                                       C.POINTER(_p)]),
+    "cera_cuda_moe_ep_handle": (_i32, [_p, _p, _sz]),
+    "cera_cuda_moe_ep_connect": (_i32, [_p, _p, _sz]),
+    "cera_cuda_moe_ep_status": (_i32, [_p, C.POINTER(_u32)]),
     "cera_cuda_moe_ffn": (_i32, [_p, _p, _sz, _i32, _p, _p, _p, _p]),
     "cera_cuda_moe_memory_bytes": (_sz, [_p]),
     "cera_cuda_moe_free": (None, [_p]),

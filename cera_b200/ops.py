@@ -224,7 +224,9 @@ class MoeFfn:
     (CUDA uint8 tensors or numpy arrays)."""
 
     def __init__(self, n_expert, n_used, hidden, ff, ggml_type, gate_exps, up_exps, down_exps, router, exp_probs_b=None,
-                 max_tokens=512):
+                 max_tokens=512, ep=None, max_total_tokens=None):
+        """ep = (rank, size): expert-parallel rank of a group of processes, one GPU each; connect with
+        cera_b200.tp.connect(moe) before the first call, then every call is collective."""
         def raw(a):
             if isinstance(a, torch.Tensor):
                 a = a.contiguous()
@@ -237,8 +239,27 @@ class MoeFfn:
         bias = raw(exp_probs_b) if exp_probs_b is not None else (None, None, 0)
         self.handle = C.c_void_p()
         self.n_expert, self.n_used, self.hidden, self.ff = n_expert, n_used, hidden, ff
-        check(lib.cera_cuda_moe_create(n_expert, n_used, hidden, ff, ggml_type, keep[0][1], keep[1][1], keep[2][1], keep[0][2],
-                                       keep[2][2], keep[3][1], bias[1], max_tokens, C.byref(self.handle)))
+        self.tp = tuple(ep) if ep else (0, 1)
+        if self.tp[1] > 1:
+            check(lib.cera_cuda_moe_create_ep(n_expert, n_used, hidden, ff, ggml_type, keep[0][1], keep[1][1], keep[2][1],
+                                              keep[0][2], keep[2][2], keep[3][1], bias[1], max_tokens, self.tp[0], self.tp[1],
+                                              max_total_tokens or max_tokens * self.tp[1], C.byref(self.handle)))
+        else:
+            check(lib.cera_cuda_moe_create(n_expert, n_used, hidden, ff, ggml_type, keep[0][1], keep[1][1], keep[2][1],
+                                           keep[0][2], keep[2][2], keep[3][1], bias[1], max_tokens, C.byref(self.handle)))
+
+    def tp_handle(self):
+        buf = (C.c_uint8 * 64)()
+        check(lib.cera_cuda_moe_ep_handle(self.handle, buf, 64))
+        return bytes(buf)
+
+    def tp_connect(self, handles):
+        check(lib.cera_cuda_moe_ep_connect(self.handle, b"".join(handles), len(handles)))
+
+    def check_status(self):
+        """After synchronising: raises if a wait on a peer ran out during an earlier call."""
+        st = C.c_uint32()
+        check(lib.cera_cuda_moe_ep_status(self.handle, C.byref(st)))
 
     def __call__(self, x, softmax_gate=False, want_routing=False):
         """x: CUDA f32 [n, hidden] -> out [n, hidden] (and ids [n, n_used], weights [n, n_used])."""

@@ -318,6 +318,26 @@ CERA_API int32_t cera_cuda_moe_create(uint32_t n_expert, uint32_t n_used, uint32
 CERA_API int32_t cera_cuda_moe_ffn(cera_cuda_moe *moe, const float *x_dev, size_t n, int32_t softmax_gate,
                                    float *out_dev, uint32_t *ids_out_dev, float *weights_out_dev,
                                    void *stream);
+/* Expert parallelism, one process per GPU (no counterpart in the reference, which routes per token on
+ * one device): this layer becomes rank ep_rank of ep_size.  It is still handed the whole stacked
+ * tensors and keeps experts [ep_rank*n_expert/ep_size, (ep_rank+1)*n_expert/ep_size).  max_tokens
+ * bounds the tokens THIS rank passes per call, max_total_tokens the tokens of all ranks together.
+ * After creation exchange the 64-byte handles exactly as for a tensor-parallel model
+ * (cera_cuda_moe_ep_handle -> gather in rank order -> cera_cuda_moe_ep_connect).  Every
+ * cera_cuda_moe_ffn call is then collective: all ranks call it (n may differ per rank, 0 included);
+ * tokens are dispatched to the ranks that own their experts and the results combined back, all by
+ * peer stores from the kernels.  Outputs are bit-identical to the single-GPU layer.  A peer that does
+ * not arrive within CERA_CUDA_TP_TIMEOUT_MS leaves a status word that cera_cuda_moe_ep_status
+ * (call it after synchronising the stream) turns into CERA_CUDA_ERR_TIMEOUT. */
+CERA_API int32_t cera_cuda_moe_create_ep(uint32_t n_expert, uint32_t n_used, uint32_t hidden, uint32_t ff,
+                                         int32_t ggml_type, const void *gate_exps, const void *up_exps,
+                                         const void *down_exps, size_t gate_up_bytes, size_t down_bytes,
+                                         const float *router, const float *exp_probs_b, size_t max_tokens,
+                                         uint32_t ep_rank, uint32_t ep_size, size_t max_total_tokens,
+                                         cera_cuda_moe **out);
+CERA_API int32_t cera_cuda_moe_ep_handle(cera_cuda_moe *moe, void *handle_out, size_t handle_bytes);
+CERA_API int32_t cera_cuda_moe_ep_connect(cera_cuda_moe *moe, const void *handles, size_t n_handles);
+CERA_API int32_t cera_cuda_moe_ep_status(cera_cuda_moe *moe, uint32_t *status_out);
 CERA_API size_t cera_cuda_moe_memory_bytes(const cera_cuda_moe *moe);
 CERA_API void cera_cuda_moe_free(cera_cuda_moe *moe);
 

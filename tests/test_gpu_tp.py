@@ -74,3 +74,20 @@ def test_ranks_reproduce_single_gpu():
     for case in report["cases"]:
         assert case["stream_equal"], case
         assert case["bit_identical"], case  # a row's dot product is the same arithmetic on any number of ranks
+
+
+def test_expert_parallel_ffn_reproduces_single_gpu():
+    need_gpu()
+    import torch
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs two GPUs")
+    world = 4 if n >= 4 else 2
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", "29733", os.path.join(HERE, "ep_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    report = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    assert report["world"] == world and len(report["cases"]) == 3
+    for case in report["cases"]:
+        assert case["bit_identical"] and case["repeatable"], case
