@@ -327,6 +327,38 @@ def moe_microbench(torch, cb, iters, n_tokens=512, softmax_gate=False):
             "tokens_per_expert_min_max": [int(counts.min()), int(counts.max())]}
 
 
+def moe_ep_microbench(torch, cb, iters, rank, world, n_total=512):
+    """The same routed FFN expert-parallel over `world` GPUs (one process each): every rank owns 32/world experts
+    and n_total/world of the tokens; dispatch and combine are peer stores inside the call.  Device time, max over ranks."""
+    import torch.distributed as dist
+    from cera_b200 import tp
+    E, used, hs, ff = 32, 4, 2048, 1792
+    q = lambda n, seed: cb.quantize_weights(cb.Q4_0, cb.synth_normal(n, seed=seed, sigma=0.02))
+    gate, up, down = q(E * ff * hs, 1), q(E * ff * hs, 2), q(E * hs * ff, 3)
+    router = cb.synth_normal(E * hs, seed=4, sigma=0.05)
+    share = n_total // world
+    moe = cb.MoeFfn(E, used, hs, ff, cb.Q4_0, gate, up, down, router, max_tokens=share, ep=(rank, world), max_total_tokens=n_total)
+    tp.connect(moe, dist.new_group(backend="gloo"))
+    x = cb.synth_normal(n_total * hs, seed=5, sigma=1.0).view(n_total, hs)[rank * share:(rank + 1) * share].contiguous()
+    for _ in range(3):
+        moe(x)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        moe(x)
+    e1.record()
+    torch.cuda.synchronize()
+    moe.check_status()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    moe.close()
+    return {"tokens": n_total, "n_gpus": world, "experts_per_gpu": E // world, "ms": ms, "tok_s": n_total / ms * 1e3,
+            "tops": 2.0 * n_total * used * 3 * ff * hs / ms / 1e9, "parallelism": "expert-parallel, peer-store dispatch and combine"}
+
+
 def roofline_q4k_gemv(torch, cb, iters):
     """The dominant kernel of the decode step: the Q4_K GEMV at the gate/up shape."""
     return gemv_microbench(torch, cb, "q4_k", 14336, 4096, iters)
@@ -497,6 +529,17 @@ def main():
                 print(json.dumps({"kernel": "flash-decode attention 32/8 heads x 128", "ctx": ctx, "kv_dtype": "f16" if f16 else "f32",
                                   "algorithmic_bytes": algo, "us": round(us, 2), "achieved_gbs": round(gbs, 1),
                                   "frac": round(gbs / hbm, 3), "peak_source": which}), flush=True)
+    elif args.only == "moe" and world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+        import cera_b200 as cb
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))))
+        res = moe_ep_microbench(torch, cb, max(5, args.iters // 5), rank, world)
+        if rank == 0:
+            print(json.dumps(res), flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
     elif args.only == "moe":
         import torch
         import cera_b200 as cb
