@@ -63,6 +63,53 @@ __global__ void rope_kernel(float *q, float *k, const float *__restrict__ v, uin
     }
 }
 
+// Context shift of one layer's cache (cera/src/kv_cache.rs:1091-1320, shift_kv_with_rope): rows
+// [n_keep + shift, seq_len) move down by `shift`; every moved K head is rotated once more by R(-shift)
+// (cera/src/backend/cpu.rs:5056-5083 split halves, 5145-5180 adjacent pairs, same iterated theta with
+// theta_0 = -shift), V rows move unchanged.  The tail is read from a copy (`k_src` / `v_src` hold rows
+// [n_keep + shift, seq_len) as they were), so rows can be written in any order.  One thread per
+// rotation pair of a K row; the V row rides along.
+__global__ void kv_shift_kernel(const void *__restrict__ k_src, const void *__restrict__ v_src, void *k_cache, void *v_cache,
+                                uint32_t n_keep, uint32_t shift, uint32_t n_rows, uint32_t n_kv_heads, uint32_t hd, float ts,
+                                const float *__restrict__ ff, int neox, int kv_f16) {
+    const uint32_t half = hd / 2, row = blockIdx.y;
+    if (row >= n_rows) return;
+    const size_t kv_dim = (size_t)n_kv_heads * hd;
+    const size_t src = (size_t)row * kv_dim, dst = (size_t)(n_keep + row) * kv_dim;
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < n_kv_heads * half) {
+        const uint32_t h = idx / half, i = idx % half;
+        float theta = -(float)shift;
+        for (uint32_t s = 0; s < i; ++s) theta = __fmul_rn(theta, ts);
+        if (!neox && ff) theta = __fdiv_rn(theta, ff[i]);
+        float sn, cs;
+        sincosf(theta, &sn, &cs);
+        const uint32_t i0 = neox ? i : 2 * i, i1 = neox ? i + half : 2 * i + 1;
+        const size_t o = (size_t)h * hd;
+        float x0, x1;
+        if (kv_f16) {
+            x0 = __half2float(((const __half *)k_src)[src + o + i0]);
+            x1 = __half2float(((const __half *)k_src)[src + o + i1]);
+        } else {
+            x0 = ((const float *)k_src)[src + o + i0];
+            x1 = ((const float *)k_src)[src + o + i1];
+        }
+        const float r0 = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+        const float r1 = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
+        if (kv_f16) {
+            ((__half *)k_cache)[dst + o + i0] = __float2half_rn(r0);
+            ((__half *)k_cache)[dst + o + i1] = __float2half_rn(r1);
+        } else {
+            ((float *)k_cache)[dst + o + i0] = r0;
+            ((float *)k_cache)[dst + o + i1] = r1;
+        }
+    }
+    for (size_t e = idx; e < kv_dim; e += (size_t)gridDim.x * blockDim.x) {
+        if (kv_f16) ((__half *)v_cache)[dst + e] = ((const __half *)v_src)[src + e];
+        else ((float *)v_cache)[dst + e] = ((const float *)v_src)[src + e];
+    }
+}
+
 template <int T>
 __global__ void embed_kernel(WeightView w, uint32_t token_imm, const uint32_t *__restrict__ token_dev, float *out) {
     pdl_trigger();
@@ -201,6 +248,19 @@ int32_t launch_argmax(const float *x, size_t n, uint32_t *out, uint32_t *scratch
     CERA_CUDA_TRY(launch_k(argmax_stage1, dim3(ARGMAX_BLOCKS), dim3(ARGMAX_THREADS), 0, st, x, (uint32_t)n, scratch));
     return check_cuda(launch_k(argmax_stage2, dim3(1), dim3(32), 0, st, (const uint32_t *)scratch, (int)ARGMAX_BLOCKS, out),
                       "argmax launch");
+}
+
+int32_t launch_kv_shift(const void *k_src, const void *v_src, void *k_cache, void *v_cache, size_t n_keep, size_t shift,
+                        size_t n_rows, size_t n_kv_heads, size_t head_dim, float theta_scale, const float *freq_factors,
+                        int rope_type, int kv_f16, cudaStream_t st) {
+    if (n_rows == 0) return CERA_CUDA_OK;
+    const uint32_t pairs = (uint32_t)(n_kv_heads * head_dim / 2);
+    const dim3 grid((pairs + 127) / 128, (unsigned)n_rows);
+    kv_shift_kernel<<<grid, 128, 0, st>>>(k_src, v_src, k_cache, v_cache, (uint32_t)n_keep, (uint32_t)shift, (uint32_t)n_rows,
+                                         (uint32_t)n_kv_heads, (uint32_t)head_dim, theta_scale, freq_factors, rope_type != 0 ? 1 : 0,
+                                         kv_f16);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "kv shift launch");
 }
 
 }  // namespace cera

@@ -742,6 +742,103 @@ int32_t cera_cuda_truncate_kv(cera_cuda_model *m, size_t len) {
     return CERA_CUDA_OK;
 }
 
+// ---- KV cache management (trait Model: shift_kv, snapshot / restore) -----------------------------------
+
+int32_t cera_cuda_kv_shift(cera_cuda_model *m, size_t n_keep, size_t shift) {
+    if (!m) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_shift: null model");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    const auto &c = m->cfg;
+    if (!m->finalized) return fail(CERA_CUDA_ERR_STATE, "kv_shift: model_finalize has not been called");
+    if (shift == 0) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_shift: shift must be > 0");
+    if (n_keep + shift > m->seq_len)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "kv_shift: n_keep %zu + shift %zu exceed seq_len %zu", n_keep, shift, m->seq_len);
+    const size_t n_rows = m->seq_len - n_keep - shift, esz = c.kv_f16 ? 2 : 4, row_bytes = m->l_kvd * esz;
+    if (n_rows) {
+        void *tmp = nullptr;  // the tail as it was, K then V (a rare operation: allocated per call)
+        CERA_CUDA_TRY(cudaMalloc(&tmp, 2 * n_rows * row_bytes));
+        int32_t st = CERA_CUDA_OK;
+        for (auto &L : m->layers) {
+            char *kt = (char *)tmp, *vt = kt + n_rows * row_bytes;
+            st = check_cuda(cudaMemcpyAsync(kt, (char *)L.kc + (n_keep + shift) * row_bytes, n_rows * row_bytes, cudaMemcpyDeviceToDevice, m->stream), "kv_shift copy");
+            if (st == CERA_CUDA_OK)
+                st = check_cuda(cudaMemcpyAsync(vt, (char *)L.vc + (n_keep + shift) * row_bytes, n_rows * row_bytes, cudaMemcpyDeviceToDevice, m->stream), "kv_shift copy");
+            if (st == CERA_CUDA_OK)
+                st = launch_kv_shift(kt, vt, L.kc, L.vc, n_keep, shift, n_rows, m->l_kv_heads, c.head_dim, m->theta_scale, m->rope_freqs,
+                                     c.rope_type, c.kv_f16, m->stream);
+            if (st != CERA_CUDA_OK) break;
+        }
+        cudaError_t e = cudaStreamSynchronize(m->stream);
+        cudaFree(tmp);
+        CERA_TRY(st);
+        CERA_CUDA_TRY(e);
+    }
+    m->seq_len -= shift;
+    return CERA_CUDA_OK;
+}
+
+namespace {
+struct SnapshotHeader {
+    uint32_t magic, version, n_layers, kv_dim, elem_bytes, reserved;
+    uint64_t seq_len;
+};
+constexpr uint32_t SNAPSHOT_MAGIC = 0x564B4243u;  // "CBKV"
+}  // namespace
+
+size_t cera_cuda_kv_snapshot_bytes(const cera_cuda_model *m) {
+    if (!m || !m->finalized) return 0;
+    const size_t esz = m->cfg.kv_f16 ? 2 : 4;
+    return sizeof(SnapshotHeader) + 2 * (size_t)m->cfg.n_layers * m->seq_len * m->l_kvd * esz;
+}
+
+int32_t cera_cuda_kv_snapshot(cera_cuda_model *m, void *out, size_t out_bytes) {
+    if (!m || !out) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_snapshot: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    if (!m->finalized) return fail(CERA_CUDA_ERR_STATE, "kv_snapshot: model_finalize has not been called");
+    const size_t esz = m->cfg.kv_f16 ? 2 : 4, rows = m->seq_len * m->l_kvd * esz;
+    const size_t need = sizeof(SnapshotHeader) + 2 * (size_t)m->cfg.n_layers * rows;
+    if (out_bytes < need) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_snapshot: %zu bytes given, %zu needed", out_bytes, need);
+    CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    SnapshotHeader h{SNAPSHOT_MAGIC, 1, m->cfg.n_layers, (uint32_t)m->l_kvd, (uint32_t)esz, 0, (uint64_t)m->seq_len};
+    memcpy(out, &h, sizeof(h));
+    char *p = (char *)out + sizeof(h);
+    for (auto &L : m->layers) {
+        CERA_CUDA_TRY(cudaMemcpy(p, L.kc, rows, cudaMemcpyDeviceToHost));
+        CERA_CUDA_TRY(cudaMemcpy(p + rows, L.vc, rows, cudaMemcpyDeviceToHost));
+        p += 2 * rows;
+    }
+    return CERA_CUDA_OK;
+}
+
+int32_t cera_cuda_kv_restore(cera_cuda_model *m, const void *data, size_t bytes) {
+    if (!m || !data) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_restore: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    if (!m->finalized) return fail(CERA_CUDA_ERR_STATE, "kv_restore: model_finalize has not been called");
+    SnapshotHeader h;
+    if (bytes < sizeof(h)) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_restore: %zu bytes is shorter than the header", bytes);
+    memcpy(&h, data, sizeof(h));
+    const size_t esz = m->cfg.kv_f16 ? 2 : 4;
+    if (h.magic != SNAPSHOT_MAGIC || h.version != 1) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_restore: not a KV snapshot of this library");
+    if (h.n_layers != m->cfg.n_layers || h.kv_dim != m->l_kvd || h.elem_bytes != esz)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "kv_restore: snapshot of %u layers x %u x %u bytes does not fit this model (%u x %zu x %zu)",
+                    h.n_layers, h.kv_dim, h.elem_bytes, m->cfg.n_layers, m->l_kvd, esz);
+    if (h.seq_len > m->cfg.max_seq_len) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_restore: %llu positions exceed max_seq_len %u",
+                                                   (unsigned long long)h.seq_len, m->cfg.max_seq_len);
+    const size_t rows = (size_t)h.seq_len * m->l_kvd * esz;
+    if (bytes != sizeof(h) + 2 * (size_t)h.n_layers * rows) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_restore: truncated snapshot");
+    CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    const char *p = (const char *)data + sizeof(h);
+    for (auto &L : m->layers) {
+        CERA_CUDA_TRY(cudaMemcpy(L.kc, p, rows, cudaMemcpyHostToDevice));
+        CERA_CUDA_TRY(cudaMemcpy(L.vc, p + rows, rows, cudaMemcpyHostToDevice));
+        p += 2 * rows;
+    }
+    m->seq_len = (size_t)h.seq_len;
+    return CERA_CUDA_OK;
+}
+
 size_t cera_cuda_seq_len(const cera_cuda_model *m) { return m ? m->seq_len : 0; }
 size_t cera_cuda_memory_bytes(const cera_cuda_model *m) { return m ? m->mem_bytes : 0; }
 uint64_t cera_cuda_launch_count(const cera_cuda_model *m) { return m ? m->launches : 0; }

@@ -95,6 +95,11 @@ int32_t launch_rope_batch(float *q, float *k, const float *v, size_t start_pos, 
 int32_t launch_prefill_attention(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
                                  size_t n_kv_heads, size_t head_dim, size_t n, size_t start_pos, float scale, float *out,
                                  cudaStream_t st);
+// Rows [n_keep + shift, n_keep + shift + n_rows) of a cache, given as a copy in k_src / v_src, re-enter it at
+// [n_keep, n_keep + n_rows) with K rotated by R(-shift) (cera/src/kv_cache.rs:1091-1320).
+int32_t launch_kv_shift(const void *k_src, const void *v_src, void *k_cache, void *v_cache, size_t n_keep, size_t shift,
+                        size_t n_rows, size_t n_kv_heads, size_t head_dim, float theta_scale, const float *freq_factors,
+                        int rope_type, int kv_f16, cudaStream_t st);
 // First strict maximum (cera/src/sampler.rs:20-30).  scratch: 2*blocks words, see argmax_scratch_words().
 size_t argmax_scratch_words();
 int32_t launch_argmax(const float *x, size_t n, uint32_t *out, uint32_t *scratch, cudaStream_t st);

@@ -98,6 +98,21 @@ class CudaModel:
     def truncate_kv(self, n):
         check(lib.cera_cuda_truncate_kv(self.handle, n))
 
+    def shift_kv(self, n_keep, shift):
+        """Model::shift_kv: drop positions [n_keep, n_keep + shift) and re-rotate the keys that move down."""
+        check(lib.cera_cuda_kv_shift(self.handle, n_keep, shift))
+
+    def snapshot(self):
+        """The KV cache up to seq_len as bytes (restore() puts it back, seq_len included)."""
+        n = lib.cera_cuda_kv_snapshot_bytes(self.handle)
+        buf = np.empty(n, dtype=np.uint8)
+        check(lib.cera_cuda_kv_snapshot(self.handle, buf.ctypes.data_as(C.c_void_p), n))
+        return buf
+
+    def restore(self, snap):
+        snap = np.ascontiguousarray(snap, dtype=np.uint8)
+        check(lib.cera_cuda_kv_restore(self.handle, snap.ctypes.data_as(C.c_void_p), snap.size))
+
     @property
     def seq_len(self):
         return lib.cera_cuda_seq_len(self.handle)

@@ -283,6 +283,19 @@ CERA_API int32_t cera_cuda_forward_prefill(cera_cuda_model *m, const uint32_t *t
                                            size_t start_pos, float *logits_out);
 /* Model::truncate_kv (mod.rs:251-283). */
 CERA_API int32_t cera_cuda_truncate_kv(cera_cuda_model *m, size_t len);
+/* Model::shift_kv (cera/src/model/llama.rs:1728-1738 -> InferenceState::shift_kv_with_rope,
+ * cera/src/kv_cache.rs:1091-1320): drop cached positions [n_keep, n_keep + shift), move the rest down
+ * and rotate every moved K head by R(-shift) with the model's RoPE layout and frequency factors; V
+ * rows move unchanged; seq_len shrinks by shift.  shift == 0 or n_keep + shift > seq_len are errors
+ * (the reference asserts). */
+CERA_API int32_t cera_cuda_kv_shift(cera_cuda_model *m, size_t n_keep, size_t shift);
+/* Model::snapshot / restore (cera/src/model/mod.rs:230-283): the cached positions [0, seq_len) of every
+ * layer as host bytes, and back.  The layout is this library's own (a 32-byte header, then per layer the K
+ * rows and the V rows in the cache's element type), not the reference's StateSnapshot: device backends
+ * own their KV, and a snapshot is only ever restored into the model that made it or an identical one. */
+CERA_API size_t cera_cuda_kv_snapshot_bytes(const cera_cuda_model *m);
+CERA_API int32_t cera_cuda_kv_snapshot(cera_cuda_model *m, void *out, size_t out_bytes);
+CERA_API int32_t cera_cuda_kv_restore(cera_cuda_model *m, const void *data, size_t bytes);
 CERA_API size_t cera_cuda_seq_len(const cera_cuda_model *m);
 /* Model::gpu_memory_bytes (mod.rs:500). */
 CERA_API size_t cera_cuda_memory_bytes(const cera_cuda_model *m);

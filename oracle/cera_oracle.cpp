@@ -1079,6 +1079,37 @@ int cera_oracle_model_forward(cera_oracle_model *M, uint32_t token, size_t pos, 
 void cera_oracle_model_truncate_kv(cera_oracle_model *m, size_t len) {
     if (len < m->seq_len) m->seq_len = len;
 }
+// InferenceState::shift_kv_with_rope (cera/src/kv_cache.rs:1091-1320): drain rows [n_keep, n_keep+shift) of every
+// layer's K and V, then rotate each K head now at [n_keep, new_len) by R(-shift) with the forward pass's RoPE
+// helper (theta_0 = -shift; f16 caches are widened, rotated and narrowed again).
+int cera_oracle_model_shift_kv(cera_oracle_model *M, size_t n_keep, size_t shift) {
+    const auto &c = M->cfg;
+    if (shift == 0 || n_keep + shift > M->seq_len) return -1;
+    const size_t kvd = (size_t)c.n_kv_heads * c.head_dim, esz = c.kv_f16 ? 2 : 4, row = kvd * esz;
+    const size_t new_len = M->seq_len - shift;
+    const float *ffreq = M->rope_freqs.bytes ? (const float *)M->rope_freqs.bytes : nullptr;
+    std::vector<float> buf(c.head_dim);
+    for (uint32_t l = 0; l < c.n_layers; ++l) {
+        auto &kc = M->kcache[l];
+        auto &vc = M->vcache[l];
+        if (kc.size() < M->seq_len * row) return -1;
+        kc.erase(kc.begin() + n_keep * row, kc.begin() + (n_keep + shift) * row);
+        vc.erase(vc.begin() + n_keep * row, vc.begin() + (n_keep + shift) * row);
+        for (size_t t = n_keep; t < new_len; ++t)
+            for (size_t h = 0; h < c.n_kv_heads; ++h) {
+                if (c.kv_f16) {
+                    uint16_t *p = (uint16_t *)kc.data() + t * kvd + h * c.head_dim;
+                    for (size_t d = 0; d < c.head_dim; ++d) buf[d] = h2f(p[d]);
+                    rope_head(buf.data(), -(float)shift, c.head_dim, c.rope_theta, ffreq, c.rope_type);
+                    for (size_t d = 0; d < c.head_dim; ++d) p[d] = f2h(buf[d]);
+                } else {
+                    rope_head((float *)kc.data() + t * kvd + h * c.head_dim, -(float)shift, c.head_dim, c.rope_theta, ffreq, c.rope_type);
+                }
+            }
+    }
+    M->seq_len = new_len;
+    return 0;
+}
 size_t cera_oracle_model_seq_len(const cera_oracle_model *m) { return m->seq_len; }
 int cera_oracle_model_last_hidden(const cera_oracle_model *m, float *out) {
     if (m->last_hidden.empty()) return -1;

@@ -167,6 +167,8 @@ int cera_oracle_model_set_tensor(cera_oracle_model *m, int role, int layer, int 
 /* One decode token at position pos == current seq_len; logits may be NULL. */
 int cera_oracle_model_forward(cera_oracle_model *m, uint32_t token, size_t pos, float *logits);
 void cera_oracle_model_truncate_kv(cera_oracle_model *m, size_t len);
+/* cera/src/kv_cache.rs:1091-1320 (shift_kv_with_rope); -1 on the reference's assertion cases */
+int cera_oracle_model_shift_kv(cera_oracle_model *m, size_t n_keep, size_t shift);
 size_t cera_oracle_model_seq_len(const cera_oracle_model *m);
 /* Copies the last hidden-state snapshots recorded by forward (for drift
  * diagnosis): which = 0 final normed hidden. */

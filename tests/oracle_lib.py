@@ -70,6 +70,7 @@ _sig("cera_oracle_model_create", _p, C.POINTER(OracleConfig))
 _sig("cera_oracle_model_set_tensor", C.c_int, _p, C.c_int, C.c_int, C.c_int, _sz, _sz, _p)
 _sig("cera_oracle_model_forward", C.c_int, _p, C.c_uint32, _sz, _p)
 _sig("cera_oracle_model_truncate_kv", None, _p, _sz)
+_sig("cera_oracle_model_shift_kv", C.c_int, _p, _sz, _sz)
 _sig("cera_oracle_model_seq_len", _sz, _p)
 _sig("cera_oracle_model_last_hidden", C.c_int, _p, _p)
 _sig("cera_oracle_model_free", None, _p)
@@ -275,6 +276,9 @@ class OracleModel:
 
     def truncate_kv(self, n):
         _lib.cera_oracle_model_truncate_kv(self.h, n)
+
+    def shift_kv(self, n_keep, shift):
+        assert _lib.cera_oracle_model_shift_kv(self.h, n_keep, shift) == 0
 
     @property
     def seq_len(self):

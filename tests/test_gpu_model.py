@@ -183,3 +183,64 @@ def test_mixed_type_layers():
     prompt = synth.prompt_tokens(5, SMALL["vocab_size"], seed=4)
     for pos, t in enumerate(prompt):
         assert_model_logits(gpu.forward(int(t), pos), oracle.forward(int(t), pos), f"pos {pos}")
+
+
+@pytest.mark.parametrize("kv_f16", [0, 1])
+@pytest.mark.parametrize("rope_type", [0, 1])
+def test_kv_shift_matches_reference(kv_f16, rope_type):
+    """n_keep context shift (cera/src/kv_cache.rs:1091-1320): after dropping a middle range and re-rotating the keys
+    that moved, the next tokens' logits follow the oracle, which performs the same shift on its own cache."""
+    need_gpu()
+    import cera_b200 as cb
+    from cera_b200 import synth
+    cfg = dict(SMALL, rope_type=rope_type)
+    gpu, oracle = _pair(cfg, seed=13, kv_f16=kv_f16)
+    prompt = synth.prompt_tokens(26, cfg["vocab_size"], seed=2)
+    for pos, t in enumerate(prompt[:20]):
+        gpu.forward(int(t), pos)
+        oracle.forward(int(t), pos)
+    gpu.shift_kv(4, 6)
+    oracle.shift_kv(4, 6)
+    assert gpu.seq_len == oracle.seq_len == 14
+    for i, t in enumerate(prompt[20:]):
+        lg = gpu.forward(int(t), 14 + i)
+        lo = oracle.forward(int(t), 14 + i)
+        assert_model_logits(lg, lo, f"logits {i} tokens after the shift")
+    # shifting everything after n_keep away is a truncation
+    gpu.shift_kv(3, gpu.seq_len - 3)
+    oracle.shift_kv(3, oracle.seq_len - 3)
+    assert gpu.seq_len == 3
+    assert_model_logits(gpu.forward(5, 3), oracle.forward(5, 3), "after shifting the whole tail away")
+    with pytest.raises(cb.CeraCudaError, match="shift must be"):
+        gpu.shift_kv(1, 0)
+    with pytest.raises(cb.CeraCudaError, match="exceed seq_len"):
+        gpu.shift_kv(3, 2)
+
+
+def test_snapshot_restore_replays_the_same_tokens():
+    need_gpu()
+    import cera_b200 as cb
+    from cera_b200 import synth
+    gpu = synth.build_llama(WIDE, seed=21, max_seq_len=64)
+    prompt = synth.prompt_tokens(10, WIDE["vocab_size"], seed=4)
+    logits = gpu.forward_prefill(prompt, 0)
+    first = int(np.argmax(logits))
+    snap = gpu.snapshot()
+    assert snap.size == 32 + 2 * WIDE["n_layers"] * 10 * WIDE["n_kv_heads"] * WIDE["head_dim"] * 4
+    a, _ = gpu.generate_greedy(first, 10, 12)
+    gpu.restore(snap)
+    assert gpu.seq_len == 10
+    b, _ = gpu.generate_greedy(first, 10, 12)
+    assert list(a) == list(b)
+    # into a second model with the same weights
+    twin = synth.build_llama(WIDE, seed=21, max_seq_len=64)
+    twin.restore(snap)
+    c, _ = twin.generate_greedy(first, 10, 12)
+    assert list(a) == list(c)
+    other = synth.build_llama(SMALL, seed=21, max_seq_len=64)
+    with pytest.raises(cb.CeraCudaError, match="does not fit"):
+        other.restore(snap)
+    with pytest.raises(cb.CeraCudaError, match="truncated"):
+        twin.restore(snap[:-8])
+    with pytest.raises(cb.CeraCudaError, match="not a KV snapshot"):
+        twin.restore(np.zeros(64, dtype=np.uint8))
