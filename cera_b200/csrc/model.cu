@@ -89,6 +89,7 @@ struct cera_cuda_model {
     float *pf_hidden = nullptr, *pf_q = nullptr, *pf_k = nullptr, *pf_v = nullptr, *pf_attn = nullptr, *pf_g = nullptr,
           *pf_u = nullptr;
     ActBuf pf_act_hs, pf_act_q, pf_act_ff;
+    float *pf_logits = nullptr;  // [PREFILL_CHUNK][vocab], allocated by the first logits-for-every-position call
     uint32_t *tok_hist = nullptr;  // device ring of generated tokens (chained greedy decode)
     uint32_t tok_hist_cap = 0;
     // tensor parallelism (tp_size == 1: a single device, no exchange)
@@ -655,6 +656,46 @@ int32_t cera_cuda_forward_prefill(cera_cuda_model *m, const uint32_t *tokens, si
         CERA_CUDA_TRY(cudaMemcpyAsync(m->h_logits, m->logits, bytes, cudaMemcpyDeviceToHost, m->stream));
         CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
         memcpy(logits_out, m->h_logits, bytes);
+    }
+    return CERA_CUDA_OK;
+}
+
+// Model::forward_prefill_logits_all (cera/src/model/mod.rs:507-533, used by speculative decoding): the logits of
+// EVERY prompt position, logits_out[n][vocab] on the host, token-major.
+int32_t cera_cuda_forward_prefill_logits_all(cera_cuda_model *m, const uint32_t *tokens, size_t n, size_t start_pos,
+                                             float *logits_out) {
+    if (!m || !tokens || !logits_out) return fail(CERA_CUDA_ERR_BAD_ARG, "forward_prefill_logits_all: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    const auto &c = m->cfg;
+    if (!m->finalized) return fail(CERA_CUDA_ERR_STATE, "forward_prefill_logits_all: model_finalize has not been called");
+    if (start_pos != m->seq_len) return fail(CERA_CUDA_ERR_STATE, "forward_prefill_logits_all: start_pos %zu != seq_len %zu", start_pos, m->seq_len);
+    if (start_pos + n > c.max_seq_len)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "forward_prefill_logits_all: %zu tokens from %zu exceed max_seq_len %u", n, start_pos, c.max_seq_len);
+    for (size_t i = 0; i < n; ++i)
+        if (tokens[i] >= c.vocab_size) return fail(CERA_CUDA_ERR_BAD_ARG, "forward_prefill_logits_all: token %u out of range", tokens[i]);
+    const size_t vocab = c.vocab_size;
+    if (m->tp_size > 1) {
+        // tensor-parallel: the decode step per position, each with its logits exchange
+        if (!m->tp_connected) return fail(CERA_CUDA_ERR_STATE, "forward_prefill_logits_all: tensor-parallel model is not connected to its peers");
+        for (size_t i = 0; i < n; ++i) {
+            CERA_TRY(run_token(m, tokens[i], start_pos + i, G_LOGITS));
+            CERA_CUDA_TRY(cudaMemcpyAsync(logits_out + i * vocab, m->logits, vocab * 4, cudaMemcpyDeviceToHost, m->stream));
+            CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+        }
+        return tp_check(m);
+    }
+    if (!m->pf_logits) CERA_TRY(dev_alloc(m, (void **)&m->pf_logits, PREFILL_CHUNK * vocab * 4));
+    const cera_cuda_weight *ow = m->output ? m->output : m->embd;
+    for (size_t done = 0; done < n; done += PREFILL_CHUNK) {
+        const size_t cn = n - done < PREFILL_CHUNK ? n - done : PREFILL_CHUNK;
+        CERA_TRY(prefill_chunk(m, tokens + done, cn, start_pos + done));
+        CERA_TRY(launch_rmsnorm(m->pf_hidden, m->out_norm, c.hidden_size, cn, c.rms_norm_eps, nullptr, m->pf_act_hs.scales,
+                                m->pf_act_hs.quants, m->pf_act_hs.sums, m->stream));
+        CERA_TRY(launch_gemm_ex(ow->v, m->pf_act_hs.view(), cn, m->pf_logits, 1, vocab, EPI_STORE, m->stream));
+        CERA_CUDA_TRY(cudaMemcpyAsync(logits_out + done * vocab, m->pf_logits, cn * vocab * 4, cudaMemcpyDeviceToHost, m->stream));
+        CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+        m->seq_len = start_pos + done + cn;
     }
     return CERA_CUDA_OK;
 }

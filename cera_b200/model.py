@@ -95,6 +95,14 @@ class CudaModel:
                                             logits.ctypes.data_as(C.c_void_p) if want_logits else None))
         return logits
 
+    def forward_prefill_logits_all(self, tokens, start_pos):
+        """Logits of every prompt position -> float32 [n, vocab]."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.uint32)
+        out = np.empty((tokens.size, self.cfg.vocab_size), dtype=np.float32)
+        check(lib.cera_cuda_forward_prefill_logits_all(self.handle, tokens.ctypes.data_as(C.c_void_p), tokens.size, start_pos,
+                                                       out.ctypes.data_as(C.c_void_p)))
+        return out
+
     def truncate_kv(self, n):
         check(lib.cera_cuda_truncate_kv(self.handle, n))
 

@@ -283,6 +283,11 @@ CERA_API int32_t cera_cuda_forward_prefill(cera_cuda_model *m, const uint32_t *t
                                            size_t start_pos, float *logits_out);
 /* Model::truncate_kv (mod.rs:251-283). */
 CERA_API int32_t cera_cuda_truncate_kv(cera_cuda_model *m, size_t len);
+/* Model::forward_prefill_logits_all (cera/src/model/mod.rs:507-533; the verifier side of speculative
+ * decoding): like forward_prefill, but the logits of every position come back, logits_out[n][vocab]
+ * on the host, token-major. */
+CERA_API int32_t cera_cuda_forward_prefill_logits_all(cera_cuda_model *m, const uint32_t *tokens, size_t n,
+                                                      size_t start_pos, float *logits_out);
 /* Model::shift_kv (cera/src/model/llama.rs:1728-1738 -> InferenceState::shift_kv_with_rope,
  * cera/src/kv_cache.rs:1091-1320): drop cached positions [n_keep, n_keep + shift), move the rest down
  * and rotate every moved K head by R(-shift) with the model's RoPE layout and frequency factors; V

@@ -244,3 +244,21 @@ def test_snapshot_restore_replays_the_same_tokens():
         twin.restore(snap[:-8])
     with pytest.raises(cb.CeraCudaError, match="not a KV snapshot"):
         twin.restore(np.zeros(64, dtype=np.uint8))
+
+
+def test_prefill_logits_for_every_position():
+    """forward_prefill_logits_all: row j is what forward() returns at position j (batched kernels vs the decode
+    step: the reference's model-level bars), across a chunk boundary; the cache ends up the same."""
+    need_gpu()
+    from cera_b200 import synth
+    cfg = dict(SMALL, n_layers=1)
+    a = synth.build_llama(cfg, seed=17, max_seq_len=320)
+    b = synth.build_llama(cfg, seed=17, max_seq_len=320)
+    prompt = synth.prompt_tokens(270, cfg["vocab_size"], seed=8)
+    rows = a.forward_prefill_logits_all(prompt, 0)
+    assert rows.shape == (270, cfg["vocab_size"]) and a.seq_len == 270
+    want = [b.forward(int(t), pos) for pos, t in enumerate(prompt)]
+    for pos in (0, 1, 100, 255, 256, 269):
+        assert_model_logits(rows[pos], want[pos], f"position {pos}")
+    nxt = int(np.argmax(rows[-1]))
+    assert_model_logits(a.forward(nxt, 270), b.forward(nxt, 270), "next token after the two prefills")
