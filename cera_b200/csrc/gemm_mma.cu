@@ -1,10 +1,11 @@
-// Prefill GEMM on the integer tensor-core path: out[m x n] = W (Q4_K or Q6_K) x X (Q8_0 columns), n >= 16.
+// Prefill GEMM on the integer tensor-core path: out[m x n] = W (Q4_K, Q5_K or Q6_K) x X (Q8_0 columns), n >= 5.
 //
 // A CTA owns a 64-row x 128-column output tile and walks k one 256-element super-block at a time:
 // weights of the 64 rows and the Q8_0 quants of the 128 columns are staged in shared memory with
 // cp.async, the six-bit / int8 sub-block scales are expanded to f32 once per chunk, and every warp
 // (16 rows x 64 columns) issues mma.sync int8 instructions whose int32 results are EXACT per-block sums:
 //   Q4_K : m16n8k32 (u8 x s8) per 32-element sub-block,  out += (d*sc) * xs * U - (dmin*mn) * (xs*A32)
+//   Q5_K : the same with the fifth bit of every quant merged into the u8 operand
 //   Q6_K : m16n8k16 (u8 x s8) per 16-element scale group, out += (d*sc) * (xs*U - 32*xs*A16)
 // Each int32 tile is scaled and folded into f32 accumulators on the CUDA cores right after its mma:
 // with one scale pair per (row, block, column) that per-block rescale, not the tensor pipe, bounds the
@@ -12,19 +13,30 @@
 // This is the warp-level (mma.sync) form; the same tiling moved onto tcgen05 with TMEM accumulators
 // would free the issue slots the mma instructions take here, but keeps the same rescale bound.
 //
+// Small batches (few column tiles) would leave most SMs idle and each CTA with a long serial chain of
+// chunks, so the k range of one output tile is split over a thread-block CLUSTER of up to 8 CTAs: each
+// CTA accumulates its share of the super-blocks, parks its 64 x BN partial tile in its own shared memory,
+// and after a cluster barrier every CTA finishes 64/CL rows of the tile by adding the CL partials in rank
+// order through distributed shared memory (a fixed order: results do not depend on timing).  The column
+// width of the tile is a template parameter (16, 32, 64 or 128) picked from n.
+//
 // Arithmetic contract: cera/src/backend/simd.rs:5693-5878 (Q4_K) and 5988-6195 (Q6_K), per cell; the
 // f32 order is this kernel's own (blocks in k order per thread).
+#include <cooperative_groups.h>
+
 #include <cstdlib>
 #include <cstring>
 
 #include "act.cuh"
 #include "ops.h"
 
+namespace cg = cooperative_groups;
+
 namespace cera {
 
 namespace {
 
-constexpr int GM_BM = 64, GM_BN = 128, GM_THREADS = 256;
+constexpr int GM_BM = 64, GM_THREADS = 256;
 constexpr int GM_WQ_STRIDE = 144;   // 128 quant bytes per row, padded so 8 rows x 4 words hit 32 banks
 constexpr int GM_WH_STRIDE = 80;    // Q6_K high-bit plane: 64 bytes per row, padded likewise
 constexpr int GM_AQ_STRIDE = 272;   // 256 activation quants per column, padded likewise
@@ -61,8 +73,16 @@ __device__ __forceinline__ void mma_u8s8_k16(int (&c)[4], uint32_t a0, uint32_t 
         : "r"(a0), "r"(a1), "r"(b0), "r"(0), "r"(0), "r"(0), "r"(0));
 }
 
-template <int T>
+template <int BN>
+constexpr size_t gm_smem_bytes() {
+    return GM_BM * GM_WQ_STRIDE + GM_BM * GM_WH_STRIDE + GM_BM * 16 + GM_BM * 16 * 4 + GM_BM * 8 * 4 + BN * GM_AQ_STRIDE +
+           8 * BN * 4 + 16 * BN * 4;
+}
+
+template <int T, int GM_BN>
 __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p) {
+    constexpr int NT = GM_BN / 16;  // 8-column n-tiles per warp (the tile is 4 warps tall, 2 wide)
+    static_assert((size_t)GM_BM * GM_BN * 4 <= gm_smem_bytes<GM_BN>(), "the partial tile reuses the staging buffers");
     extern __shared__ __align__(16) uint8_t smem[];
     // shared-memory carve-up
     uint8_t *wq = smem;                                            // [64][144]
@@ -78,18 +98,22 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
     pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gid = lane >> 2, tig = lane & 3;
-    const int wrow = (warp & 3) * 16, wcol = (warp >> 2) * 64;  // this warp's 16 x 64 patch of the tile
-    const uint32_t row0 = blockIdx.x * GM_BM, col0 = blockIdx.y * GM_BN;
+    const int wrow = (warp & 3) * 16, wcol = (warp >> 2) * (GM_BN / 2);  // this warp's 16 x BN/2 patch of the tile
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t CL = cluster.num_blocks(), crank = cluster.block_rank();
+    const uint32_t row0 = (blockIdx.x / CL) * GM_BM, col0 = blockIdx.y * GM_BN;
     const uint32_t nb = p.w.nb, nb32 = p.k >> 5, nb16 = p.k >> 4;
     const TypeInfo ti = type_info(T);
 
-    float acc[8][4];
+    float acc[NT][4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
 
-    for (uint32_t bi = 0; bi < nb; ++bi) {
+    // this CTA's share of the super-blocks
+    const uint32_t per = (nb + CL - 1) / CL, bi_begin = min(nb, crank * per), bi_end = min(nb, bi_begin + per);
+    for (uint32_t bi = bi_begin; bi < bi_end; ++bi) {
         // ---- stage the chunk: weights of 64 rows, activations of 128 columns (rows / columns past the
         // edge are clamped to the last valid one; their results are never stored)
         for (int i = tid; i < GM_BM * 8; i += GM_THREADS) {
@@ -105,6 +129,13 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
                 cpa16(wqh + r * GM_WH_STRIDE + pc * 16, p.w.qh + ((size_t)row * nb + bi) * 64 + pc * 16);
             }
         }
+        if (T == CERA_TYPE_Q5_K) {  // fifth bits: 32 bytes per row, bit s of byte l belongs to element l of sub-block s
+            for (int i = tid; i < GM_BM * 2; i += GM_THREADS) {
+                const int r = i >> 1, pc = i & 1;
+                const uint32_t row = min(row0 + r, p.m - 1);
+                cpa16(wqh + r * GM_WH_STRIDE + pc * 16, p.w.qh + ((size_t)row * nb + bi) * 32 + pc * 16);
+            }
+        }
         for (int r = tid; r < GM_BM; r += GM_THREADS) {
             const uint32_t row = min(row0 + r, p.m - 1);
             cpa16(whd + r * 16, p.w.hdr + ((size_t)row * nb + bi) * 16);
@@ -115,12 +146,12 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
             cpa16(aq + c * GM_AQ_STRIDE + pc * 16, p.x.quants + (size_t)col * p.k + (size_t)bi * 256 + pc * 16);
         }
         for (int i = tid; i < GM_BN * 8; i += GM_THREADS) {
-            const int c = i & (GM_BN - 1), s = i >> 7;
+            const int c = i % GM_BN, s = i / GM_BN;
             const uint32_t col = min(col0 + c, p.n - 1);
             const float xs = p.x.scales[(size_t)col * nb32 + bi * 8 + s];
             const int16_t *sm = p.x.sums + (size_t)col * nb16 + (bi * 8 + s) * 2;
             axs[s * GM_BN + c] = xs;
-            if (T == CERA_TYPE_Q4_K) {
+            if (T != CERA_TYPE_Q6_K) {
                 axb[s * GM_BN + c] = xs * (float)((int)sm[0] + (int)sm[1]);
             } else {
                 axb[(2 * s) * GM_BN + c] = -32.0f * (xs * (float)sm[0]);
@@ -130,7 +161,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
         cpa_wait_all();
         __syncthreads();
         // ---- expand the sub-block scales of the 64 rows to f32
-        if (T == CERA_TYPE_Q4_K) {
+        if (T != CERA_TYPE_Q6_K) {
             for (int i = tid; i < GM_BM * 8; i += GM_THREADS) {
                 const int r = i >> 3, s = i & 7;
                 const uint8_t *h = whd + r * 16;
@@ -152,7 +183,15 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
 
         // ---- tensor-core work of this chunk
         const uint8_t *qa = wq + (wrow + gid) * GM_WQ_STRIDE, *qb = qa + 8 * GM_WQ_STRIDE;
-        if (T == CERA_TYPE_Q4_K) {
+        if (T != CERA_TYPE_Q6_K) {
+            const uint8_t *h5a = wqh + (wrow + gid) * GM_WH_STRIDE, *h5b = h5a + 8 * GM_WH_STRIDE;
+            uint32_t ha0 = 0, ha1 = 0, hb0 = 0, hb1 = 0;
+            if (T == CERA_TYPE_Q5_K) {
+                ha0 = *reinterpret_cast<const uint32_t *>(h5a + 4 * tig);
+                ha1 = *reinterpret_cast<const uint32_t *>(h5a + 16 + 4 * tig);
+                hb0 = *reinterpret_cast<const uint32_t *>(h5b + 4 * tig);
+                hb1 = *reinterpret_cast<const uint32_t *>(h5b + 16 + 4 * tig);
+            }
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
                 // 32-byte group g: low nibbles = sub-block 2g, high nibbles = sub-block 2g+1; byte l = element l
@@ -163,12 +202,18 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
 #pragma unroll
                 for (int hi = 0; hi < 2; ++hi) {
                     const int s = 2 * g + hi, sh = 4 * hi;
-                    const uint32_t a[4] = {(wa0 >> sh) & 0x0F0F0F0Fu, (wb0 >> sh) & 0x0F0F0F0Fu, (wa1 >> sh) & 0x0F0F0F0Fu,
-                                           (wb1 >> sh) & 0x0F0F0F0Fu};
+                    uint32_t a[4] = {(wa0 >> sh) & 0x0F0F0F0Fu, (wb0 >> sh) & 0x0F0F0F0Fu, (wa1 >> sh) & 0x0F0F0F0Fu,
+                                     (wb1 >> sh) & 0x0F0F0F0Fu};
+                    if (T == CERA_TYPE_Q5_K) {  // q = nibble + 16 * bit s of the high-bit byte (cera/src/quant.rs:846-866)
+                        a[0] |= ((ha0 >> s) & 0x01010101u) << 4;
+                        a[1] |= ((hb0 >> s) & 0x01010101u) << 4;
+                        a[2] |= ((ha1 >> s) & 0x01010101u) << 4;
+                        a[3] |= ((hb1 >> s) & 0x01010101u) << 4;
+                    }
                     const float sca = wsc[(wrow + gid) * 16 + s], scb = wsc[(wrow + gid + 8) * 16 + s];
                     const float mna = wmn[(wrow + gid) * 8 + s], mnb = wmn[(wrow + gid + 8) * 8 + s];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
+                    for (int j = 0; j < NT; ++j) {
                         const int cb = wcol + 8 * j;  // this n-tile's first column inside the CTA tile
                         const uint8_t *bp = aq + (cb + gid) * GM_AQ_STRIDE + 32 * s + 4 * tig;
                         const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp);
@@ -198,7 +243,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
                 const uint32_t a1 = ((lb >> nsh) & 0x0F0F0F0Fu) | (((hhb >> (2 * g)) & 0x03030303u) << 4);
                 const float sca = wsc[(wrow + gid) * 16 + e], scb = wsc[(wrow + gid + 8) * 16 + e];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < NT; ++j) {
                     const int cb = wcol + 8 * j;
                     const uint32_t b0 = *reinterpret_cast<const uint32_t *>(aq + (cb + gid) * GM_AQ_STRIDE + 16 * e + 4 * tig);
                     int c[4];
@@ -215,40 +260,91 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
         __syncthreads();  // the staging buffers are rewritten by the next chunk
     }
 
-    // ---- store: cell (row, col) at out[row*ldy + col*ldc]
+    // ---- combine the k shares of the cluster and store: cell (row, col) at out[row*ldy + col*ldc]
+    if (CL == 1) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < NT; ++j)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t row = row0 + wrow + gid + (i >= 2 ? 8 : 0);
-            const uint32_t col = col0 + wcol + 8 * j + 2 * tig + (i & 1);
-            if (row < p.m && col < p.n) {
-                float *y = p.out + (size_t)row * p.ldy + (size_t)col * p.ldc;
-                *y = p.epilogue == EPI_ADD ? __fadd_rn(*y, acc[j][i]) : acc[j][i];
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t row = row0 + wrow + gid + (i >= 2 ? 8 : 0);
+                const uint32_t col = col0 + wcol + 8 * j + 2 * tig + (i & 1);
+                if (row < p.m && col < p.n) {
+                    float *y = p.out + (size_t)row * p.ldy + (size_t)col * p.ldc;
+                    *y = p.epilogue == EPI_ADD ? __fadd_rn(*y, acc[j][i]) : acc[j][i];
+                }
             }
+        return;
+    }
+    float *tile = reinterpret_cast<float *>(smem);  // [64][BN]; the last chunk's trailing barrier freed the staging buffers
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            tile[(wrow + gid + (i >= 2 ? 8 : 0)) * GM_BN + wcol + 8 * j + 2 * tig + (i & 1)] = acc[j][i];
+    cluster.sync();
+    const uint32_t rows_each = GM_BM / CL;  // CL is 2, 4 or 8
+    for (uint32_t idx = tid; idx < rows_each * GM_BN; idx += GM_THREADS) {
+        const uint32_t r = crank * rows_each + idx / GM_BN, c = idx % GM_BN;
+        float v = 0.0f;
+        for (uint32_t q = 0; q < CL; ++q) v += cluster.map_shared_rank(tile, q)[r * GM_BN + c];
+        const uint32_t row = row0 + r, col = col0 + c;
+        if (row < p.m && col < p.n) {
+            float *y = p.out + (size_t)row * p.ldy + (size_t)col * p.ldc;
+            *y = p.epilogue == EPI_ADD ? __fadd_rn(*y, v) : v;
         }
+    }
+    cluster.sync();  // peers may still be reading this CTA's partial tile
 }
 
-constexpr size_t GM_SMEM = GM_BM * GM_WQ_STRIDE + GM_BM * GM_WH_STRIDE + GM_BM * 16 + GM_BM * 16 * 4 + GM_BM * 8 * 4 +
-                           GM_BN * GM_AQ_STRIDE + 8 * GM_BN * 4 + 16 * GM_BN * 4;
-
-template <int T>
-int32_t launch_mma_typed(const GemmParams &p, cudaStream_t st) {
+template <int T, int BN>
+int32_t launch_mma_bn(const GemmParams &p, uint32_t cl, cudaStream_t st) {
+    constexpr size_t smem = gm_smem_bytes<BN>();
     static thread_local int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_dev != dev) {
-        CERA_CUDA_TRY(cudaFuncSetAttribute(gemm_mma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM));
+        CERA_CUDA_TRY(cudaFuncSetAttribute(gemm_mma_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured_dev = dev;
     }
-    const dim3 grid((p.m + GM_BM - 1) / GM_BM, (p.n + GM_BN - 1) / GM_BN);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(((p.m + GM_BM - 1) / GM_BM) * cl, (p.n + BN - 1) / BN);
+    cfg.blockDim = dim3(GM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cl;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     count_launch();
-    return check_cuda(launch_k(gemm_mma_kernel<T>, grid, dim3(GM_THREADS), GM_SMEM, st, p), "gemm (mma) launch");
+    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_mma_kernel<T, BN>, p), "gemm (mma) launch");
+}
+
+template <int T>
+int32_t launch_mma_typed(const GemmParams &p, cudaStream_t st) {
+    const uint32_t bn = p.n > 64 ? 128 : p.n > 32 ? 64 : p.n > 16 ? 32 : 16;
+    // Split k over a cluster until the grid covers the machine once (wide tiles: a CTA's chunk is compute-heavy and a
+    // split only adds the reduction), twice (64 columns) or four times (narrow tiles: a chunk is mostly load latency),
+    // keeping at least two super-blocks per CTA.
+    const uint32_t tiles = ((p.m + GM_BM - 1) / GM_BM) * ((p.n + bn - 1) / bn);
+    const uint32_t want = (uint32_t)sm_count() * (bn >= 128 ? 1u : bn == 64 ? 2u : 4u);
+    uint32_t cl = 1;
+    while (cl < 8 && tiles * cl < want && p.w.nb / (cl * 2) >= 2) cl *= 2;
+    switch (bn) {
+        case 128: return launch_mma_bn<T, 128>(p, cl, st);
+        case 64: return launch_mma_bn<T, 64>(p, cl, st);
+        case 32: return launch_mma_bn<T, 32>(p, cl, st);
+        default: return launch_mma_bn<T, 16>(p, cl, st);
+    }
 }
 
 }  // namespace
 
-// Tensor-core GEMM for Q4_K / Q6_K weights and n >= 16 columns.  *taken = false: not this kernel's case.
+// Tensor-core GEMM for Q4_K / Q5_K / Q6_K weights and n >= 5 columns.  *taken = false: not this kernel's case.
 int32_t launch_gemm_mma(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
                         cudaStream_t st, bool *taken) {
     *taken = false;
@@ -256,7 +352,7 @@ int32_t launch_gemm_mma(const WeightView &w, const ActView &x, size_t n, float *
         const char *e = getenv("CERA_CUDA_GEMM");
         return e && strcmp(e, "columns") == 0;
     }();
-    if (off || n < 16 || (w.type != CERA_TYPE_Q4_K && w.type != CERA_TYPE_Q6_K) || w.k % 256) return CERA_CUDA_OK;
+    if (off || n < 5 || (w.type != CERA_TYPE_Q4_K && w.type != CERA_TYPE_Q5_K && w.type != CERA_TYPE_Q6_K) || w.k % 256) return CERA_CUDA_OK;
     if ((uintptr_t)x.quants % 16 || w.k % 16) return CERA_CUDA_OK;
     GemmParams p{};
     p.w = w;
@@ -270,6 +366,7 @@ int32_t launch_gemm_mma(const WeightView &w, const ActView &x, size_t n, float *
     p.epilogue = epilogue;
     *taken = true;
     if (w.type == CERA_TYPE_Q4_K) return launch_mma_typed<CERA_TYPE_Q4_K>(p, st);
+    if (w.type == CERA_TYPE_Q5_K) return launch_mma_typed<CERA_TYPE_Q5_K>(p, st);
     return launch_mma_typed<CERA_TYPE_Q6_K>(p, st);
 }
 

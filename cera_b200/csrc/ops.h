@@ -55,7 +55,7 @@ int32_t launch_gemv_fused(const GemvSeg *segs, int n_segs, const ActView &x, int
 int32_t launch_rope_table(const uint32_t *pos_dev, size_t head_dim, float theta_scale, const float *freq_factors,
                           float *table, cudaStream_t st);
 int32_t launch_gemm(const WeightView &w, const ActView &x, size_t n, float *out, cudaStream_t st);
-// Tensor-core (mma.sync int8) GEMM for Q4_K / Q6_K and n >= 16.  *taken = false: not its case.
+// Tensor-core (mma.sync int8) GEMM for Q4_K / Q5_K / Q6_K and n >= 5.  *taken = false: not its case.
 int32_t launch_gemm_mma(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
                         cudaStream_t st, bool *taken);
 int32_t launch_gemv_q5k_f32(const WeightView &w, const float *x, float *y, cudaStream_t st);

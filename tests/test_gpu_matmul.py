@@ -161,9 +161,11 @@ def test_gemm_preq_matches_oracle(t, n):
 
 
 @pytest.mark.parametrize("t", [O.Q4_K, O.Q6_K, O.Q5_K])
-@pytest.mark.parametrize("m,n,k", [(70, 130, 1024), (64, 128, 512), (200, 16, 768), (3, 64, 4096)])
+@pytest.mark.parametrize("m,n,k", [(70, 130, 1024), (64, 128, 512), (200, 16, 768), (3, 64, 4096), (130, 5, 2048),
+                                   (96, 8, 4096), (65, 33, 3072), (256, 100, 1024), (40, 17, 14336)])
 def test_gemm_tensor_core_shapes(t, m, n, k):
-    """n >= 16: Q4_K / Q6_K take the mma.sync int8 kernel (ragged tiles included), Q5_K the column-tile path."""
+    """n >= 5: the K-quants take the mma.sync int8 kernel (every column-tile width, ragged tiles, and the k range
+    split over clusters of 2, 4 and 8 CTAs)."""
     torch = need_gpu()
     import cera_b200 as cb
     raw = cb.quantize_weights(t, cb.synth_normal(m * k, seed=9 * t + m + n, sigma=0.02)).cpu().numpy()
