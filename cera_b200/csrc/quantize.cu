@@ -103,6 +103,88 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_kernel(const float *__rest
     }
 }
 
+// The same operation for columns whose length is a multiple of 32, laid out for latency: every thread owns FOUR
+// consecutive elements (one 128-bit load of x and of the weights), so a 32-element Q8_0 block is eight neighbouring
+// lanes: its amax takes three shuffle steps, its two 16-element sums two, and all blocks of the column are quantized
+// at the same time instead of four per warp one after another.  Up to 4096 elements stay in registers between the
+// sum of squares and the scaling; longer columns re-read x.
+__global__ void __launch_bounds__(RN_THREADS) rmsnorm_q8_kernel(const float *__restrict__ x, const float *__restrict__ weight,
+                                                                 size_t n_elem, double inv_n, float eps, float *out_f32,
+                                                                 float *scales, int8_t *quants, int16_t *sums, const TpHook tp) {
+    __shared__ double red[RN_WARPS];
+    __shared__ float inv_s;
+    pdl_trigger();
+    const size_t col = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t nvec = (uint32_t)(n_elem >> 2);
+    const bool single = nvec <= RN_THREADS;
+    float4 wv = make_float4(0.f, 0.f, 0.f, 0.f), xv = wv;
+    if (single && threadIdx.x < nvec) wv = reinterpret_cast<const float4 *>(weight)[threadIdx.x];  // independent of the previous kernel
+    pdl_wait();
+    tp_arrive_wait(tp.ctx, tp.wait_slot);
+    const float4 *xc = reinterpret_cast<const float4 *>(x + col * n_elem);
+    double ss = 0.0;
+    for (uint32_t v = threadIdx.x; v < nvec; v += RN_THREADS) {
+        xv = xc[v];
+        ss += (double)xv.x * (double)xv.x;
+        ss += (double)xv.y * (double)xv.y;
+        ss += (double)xv.z * (double)xv.z;
+        ss += (double)xv.w * (double)xv.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    if (warp == 0) {
+        double t = red[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (lane == 0) inv_s = (float)rsqrt(t * inv_n + (double)eps);
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    // whole warps iterate together: nvec is a multiple of 8, so a block's eight lanes are all in or all out
+    for (uint32_t v0 = 0; v0 < nvec; v0 += RN_THREADS) {
+        const uint32_t v = v0 + threadIdx.x;
+        const bool in = v < nvec;
+        if (!single) {
+            xv = in ? xc[v] : make_float4(0.f, 0.f, 0.f, 0.f);
+            wv = in ? reinterpret_cast<const float4 *>(weight)[v] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float e[4] = {__fmul_rn(__fmul_rn(xv.x, inv), wv.x), __fmul_rn(__fmul_rn(xv.y, inv), wv.y),
+                      __fmul_rn(__fmul_rn(xv.z, inv), wv.z), __fmul_rn(__fmul_rn(xv.w, inv), wv.w)};
+        if (out_f32 && in) reinterpret_cast<float4 *>(out_f32 + col * n_elem)[v] = make_float4(e[0], e[1], e[2], e[3]);
+        // Q8_0 of the block these eight lanes share (cera/src/backend/cpu.rs:942-958)
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float a = fabsf(e[i]);
+            amax = fmaxf(amax, a == a ? a : 0.0f);  // f32::max ignores NaN
+        }
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float d = __fdiv_rn(amax, 127.0f);
+        const float r = __fdiv_rn(1.0f, d);
+        const float id = (d != 0.0f && isfinite(r)) ? r : 0.0f;
+        int q[4], s4 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float pq = rintf(__fmul_rn(e[i], id));
+            q[i] = pq != pq ? 0 : (int)fminf(fmaxf(pq, -128.0f), 127.0f);
+            s4 += q[i];
+        }
+        s4 += __shfl_xor_sync(0xffffffffu, s4, 1);
+        s4 += __shfl_xor_sync(0xffffffffu, s4, 2);  // sum of the 16 elements of lanes 4j .. 4j+3
+        if (in) {
+            const uint32_t packed = (uint32_t)(uint8_t)q[0] | ((uint32_t)(uint8_t)q[1] << 8) | ((uint32_t)(uint8_t)q[2] << 16) |
+                                    ((uint32_t)(uint8_t)q[3] << 24);
+            reinterpret_cast<uint32_t *>(quants + col * n_elem)[v] = packed;
+            if ((lane & 7) == 0) scales[col * (n_elem / 32) + (v >> 3)] = __half2float(__float2half_rn(d));
+            if ((lane & 3) == 0) sums[col * (n_elem / 16) + (v >> 2)] = (int16_t)s4;
+        }
+    }
+}
+
 __global__ void silu_mul_kernel(float *gate, const float *__restrict__ up, size_t n_elem, size_t n_cols,
                                 float *scales, int8_t *quants, int16_t *sums, const TpHook tp) {
     pdl_trigger();
@@ -149,6 +231,13 @@ int32_t launch_rmsnorm(const float *x, const float *weight, size_t n_elem, size_
         return fail(CERA_CUDA_ERR_BAD_ARG, "rmsnorm+quantize: n=%zu must be a multiple of 32", n_elem);
     if (n_elem == 0 || n_cols == 0) return CERA_CUDA_OK;
     const int threads = RN_THREADS;
+    if (quants && ((uintptr_t)x % 16 == 0) && ((uintptr_t)weight % 16 == 0) && (!out_f32 || (uintptr_t)out_f32 % 16 == 0) &&
+        (uintptr_t)quants % 4 == 0) {
+        CERA_CUDA_TRY(launch_k(rmsnorm_q8_kernel, dim3((unsigned)n_cols), dim3(threads), 0, st, x, weight, n_elem, 1.0 / (double)n_elem, eps,
+                               out_f32, scales, quants, sums, tp ? *tp : TpHook{}));
+        count_launch();
+        return check_cuda(cudaGetLastError(), "rmsnorm launch");
+    }
     CERA_CUDA_TRY(launch_k(rmsnorm_kernel, dim3((unsigned)n_cols), dim3(threads), 0, st, x, weight, n_elem, 1.0 / (double)n_elem, eps, out_f32, scales,
                            quants, sums, tp ? *tp : TpHook{}));
     count_launch();
