@@ -31,6 +31,7 @@ namespace {
 constexpr int ATT_WARPS = 8;
 constexpr int MAX_SPLITS = 64;
 constexpr uint32_t ATT_CLUSTER_FLAG = 0x80;
+constexpr uint32_t ATT_STREAM_FLAG = 0x100;  // long contexts: the TMA-staged split kernel, low bits = splits
 constexpr size_t ATT_CLUSTER_MAX_SEQ = 4096;
 
 template <int VEC, bool F16>
@@ -475,6 +476,19 @@ uint32_t attn_pick_splits(size_t n_kv_heads, size_t seq_len_hint) {
         if (seq_len_hint > 1024) cl = 16;
         return ATT_CLUSTER_FLAG | cl;
     }
+    static const bool no_stream = [] {
+        const char *e = getenv("CERA_CUDA_ATTN");
+        return e && (strcmp(e, "split") == 0 || strcmp(e, "registers") == 0);
+    }();
+    if (!no_stream) {
+        // one CTA per SM, every split a whole number of 64-position tiles
+        size_t ns = (size_t)sm_count() / (n_kv_heads ? n_kv_heads : 1);
+        const size_t tiles = (seq_len_hint + 63) / 64;
+        if (ns > tiles) ns = tiles;
+        if (ns > 63) ns = 63;
+        if (ns < 1) ns = 1;
+        return ATT_STREAM_FLAG | (uint32_t)ns;
+    }
     // Fill the machine about twice over, but never give a split fewer than 64 positions.
     size_t want = (size_t)(2 * sm_count() + n_kv_heads - 1) / n_kv_heads;
     const size_t by_len = (seq_len_hint + 63) / 64;
@@ -496,6 +510,8 @@ int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *v
     if (seq_len == 0 && !seq_len_dev) return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: empty KV cache");
     if (workspace_bytes < attn_workspace_bytes(n_heads, head_dim, seq_len))
         return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: workspace of %zu bytes is too small", workspace_bytes);
+    const bool streamed = (n_splits & ATT_STREAM_FLAG) != 0;
+    if (streamed) n_splits &= ~ATT_STREAM_FLAG;
     const bool clustered = (n_splits & ATT_CLUSTER_FLAG) != 0;
     uint32_t cl = n_splits & ~ATT_CLUSTER_FLAG;
     if (clustered ? (cl != 1 && cl != 2 && cl != 4 && cl != 8 && cl != 16) : (n_splits < 1 || n_splits > MAX_SPLITS))
@@ -513,7 +529,13 @@ int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *v
                            : launch_split<VEC, GG>(f16, grid, st, q, kc, vc, sl, seq_len_dev, nkv, scale, ws)
     bool ok = true;
     int32_t att_status = CERA_CUDA_OK;
-    if (head_dim == 128) {
+    bool stream_taken = false;
+    if (streamed) {
+        CERA_TRY(launch_attention_stream(q, kc, vc, kv_f16, n_kv_heads, G, head_dim, sl, seq_len_dev, n_splits, scale, ws, st,
+                                         &stream_taken));
+    }
+    if (stream_taken) {
+    } else if (head_dim == 128) {
         switch (G) {
             case 4: CERA_ATT(4, 4); break;
             case 8: CERA_ATT(4, 8); break;

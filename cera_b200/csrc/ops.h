@@ -75,6 +75,12 @@ int32_t launch_decode_attention(const float *q, const void *kc, const void *vc, 
                                 cudaStream_t st);
 
 uint32_t attn_pick_splits(size_t n_kv_heads, size_t seq_len_hint);
+// Split pass of a long-context decode attention through the shared-memory-staged kernel (attention_stream.cu); writes the
+// same per-(head, split) records as the register-resident split kernel.  *taken = false: no instantiation.
+int32_t launch_attention_stream(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_kv_heads, size_t group,
+                                size_t head_dim, uint32_t seq_len, const uint32_t *seq_len_dev, uint32_t n_splits, float scale,
+                                float *ws, cudaStream_t st, bool *taken);
+
 // seq_len_dev != null: the kernel reads the length from device memory (graph replay).
 int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
                                    size_t n_kv_heads, size_t head_dim, size_t seq_len, const uint32_t *seq_len_dev,

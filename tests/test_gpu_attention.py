@@ -114,6 +114,20 @@ def test_decode_attention_long_context(seq, f16):
     _attn_case(torch, cb, 32, 8, 128, seq, f16, seed=5)
 
 
+@pytest.mark.parametrize("f16", [False, True])
+@pytest.mark.parametrize("nh,nkv,hd,seq", [(32, 8, 128, 4097), (32, 8, 128, 5000), (32, 8, 128, 8191), (16, 2, 128, 4500),
+                                           (8, 2, 64, 6000), (16, 2, 64, 4200)])
+def test_decode_attention_streamed_kernel(nh, nkv, hd, seq, f16):
+    """Beyond 4096 positions the split pass is the TMA-staged kernel: ragged last tiles, splits with no whole
+    tile, both KV widths, head_dim 64 / 128 and groups of 4 / 8; none of its bounded waits may run out."""
+    torch = need_gpu()
+    import cera_b200 as cb
+    from cera_b200._lib import kernel_status
+    _attn_case(torch, cb, nh, nkv, hd, seq, f16, seed=40 + seq % 7)
+    torch.cuda.synchronize()
+    assert kernel_status() == 0
+
+
 def test_decode_attention_rejects_unsupported_shapes():
     torch = need_gpu()
     import cera_b200 as cb
