@@ -283,3 +283,56 @@ def test_routing_ties_zero_gate_and_saturation():
     assert np.isfinite(w).all()
     ids, w = O.select_experts([0.5, 0.3], [0.0, 0.0], 8)
     assert list(ids) == [0, 1] and len(w) == 2
+
+
+def _cpu_llama(cfg, seed, kv_f16=0, max_seq_len=32):
+    """A small random-init llama on the oracle alone (CPU synthetic generator and weight quantizers)."""
+    m = O.OracleModel(**cfg, max_seq_len=max_seq_len, kv_f16=kv_f16, n_threads=1)
+    hs, ff = cfg["hidden_size"], cfg["intermediate_size"]
+    qd, kvd = cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"]
+    ones = np.ones(hs, dtype=np.float32)
+
+    def mat(role, layer, rows, cols, t=O.Q8_0):
+        raw = O.quantize_weights(t, O.synth_normal(rows * cols, seed * 131 + role * 17 + layer, 0.05))
+        m.set_tensor(role, layer, t, rows, cols, raw)
+
+    mat(0, 0, cfg["vocab_size"], hs)
+    mat(2, 0, cfg["vocab_size"], hs)
+    m.set_tensor(1, 0, O.F32, 1, hs, ones)
+    for l in range(cfg["n_layers"]):
+        m.set_tensor(3, l, O.F32, 1, hs, ones)
+        m.set_tensor(8, l, O.F32, 1, hs, ones)
+        mat(4, l, qd, hs)
+        mat(5, l, kvd, hs)
+        mat(6, l, kvd, hs)
+        mat(7, l, hs, qd)
+        mat(9, l, ff, hs)
+        mat(10, l, ff, hs)
+        mat(11, l, hs, ff)
+    return m
+
+
+@pytest.mark.parametrize("rope_type", [0, 1])
+@pytest.mark.parametrize("kv_f16", [0, 1])
+def test_kv_shift_of_a_one_layer_model_equals_the_shorter_sequence(rope_type, kv_f16):
+    """cera/src/kv_cache.rs:1091-1320.  In a one-layer model a cached K / V row depends only on (token, position),
+    so dropping positions [n_keep, n_keep+shift) and re-rotating the keys that moved must leave the cache of the
+    sequence that never had those tokens: R(-shift) R(p) k = R(p - shift) k up to f32 (f16) rounding."""
+    cfg = dict(n_layers=1, hidden_size=64, intermediate_size=128, n_heads=4, n_kv_heads=2, head_dim=32, vocab_size=96,
+               rope_theta=10000.0, rms_norm_eps=1e-5, rope_type=rope_type)
+    toks = [5, 17, 80, 3, 44, 9, 61, 23, 70]
+    a = _cpu_llama(cfg, 3, kv_f16)
+    for pos, t in enumerate(toks):
+        a.forward(t, pos)
+    a.shift_kv(2, 3)
+    assert a.seq_len == len(toks) - 3
+    b = _cpu_llama(cfg, 3, kv_f16)
+    short = toks[:2] + toks[5:]
+    for pos, t in enumerate(short):
+        b.forward(t, pos)
+    la, lb = a.forward(11, a.seq_len), b.forward(11, b.seq_len)
+    tol = 2e-2 if kv_f16 else 2e-4
+    assert np.abs(la - lb).max() <= tol * np.abs(lb).max()
+    # the reference's assertion cases
+    assert O._lib.cera_oracle_model_shift_kv(a.h, 1, 0) == -1
+    assert O._lib.cera_oracle_model_shift_kv(a.h, a.seq_len, 1) == -1
