@@ -70,7 +70,7 @@ __device__ __forceinline__ void load_row(const void *base, size_t elem_off, floa
 // The scan of one CTA over cached positions [t_begin, t_end) of KV head kvh for its G query heads: on return
 // acc / m_run / l_run hold this warp's unnormalised output, running maximum and running sum (the state of head
 // lane % G, replicated over its P lanes).
-template <int VEC, int G, bool F16>
+template <int VEC, int G, bool F16, int W>
 __device__ __forceinline__ void attn_scan(const float *__restrict__ q, const void *__restrict__ kc, const void *__restrict__ vc,
                                           uint32_t kvh, uint32_t t_begin, uint32_t t_end, size_t kv_dim, float scale,
                                           float (&acc)[G][VEC], float &m_run, float &l_run) {
@@ -92,7 +92,7 @@ __device__ __forceinline__ void attn_scan(const float *__restrict__ q, const voi
     l_run = 0.0f;
 
     const size_t head_off = (size_t)kvh * HD + lane * VEC;
-    for (uint32_t t0 = t_begin + warp * P; t0 < t_end; t0 += ATT_WARPS * P) {
+    for (uint32_t t0 = t_begin + warp * P; t0 < t_end; t0 += W * P) {
         float kr[P][VEC], vr[P][VEC];
 #pragma unroll
         for (int i = 0; i < P; ++i) {
@@ -177,7 +177,7 @@ attn_split_kernel(const float *__restrict__ q, const void *__restrict__ kc, cons
 
     float acc[G][VEC];
     float m_run, l_run;
-    attn_scan<VEC, G, F16>(q, kc, vc, kvh, t_begin, t_end, kv_dim, scale, acc, m_run, l_run);
+    attn_scan<VEC, G, F16, ATT_WARPS>(q, kc, vc, kvh, t_begin, t_end, kv_dim, scale, acc, m_run, l_run);
 
     // merge the warps of this CTA
     __shared__ float s_acc[ATT_WARPS][G][HD];
@@ -254,15 +254,15 @@ __global__ void attn_merge_kernel(const float *__restrict__ ws, uint32_t n_split
 // CL; CTA r of a cluster scans the r-th share of the positions, leaves its (out, max, sum) per query
 // head in its own shared memory, and after a cluster barrier combines G*HD/CL of the outputs from all
 // CL shares (same arithmetic as attn_merge_kernel), emitting f32 and Q8_0.
-template <int VEC, int G, bool F16>
-__global__ void __launch_bounds__(ATT_WARPS * 32)
+template <int VEC, int G, bool F16, int W>
+__global__ void __launch_bounds__(W * 32)
 attn_cluster_kernel(const float *__restrict__ q, const void *__restrict__ kc, const void *__restrict__ vc,
                     uint32_t seq_len_imm, const uint32_t *__restrict__ seq_len_dev, uint32_t n_kv_heads, float scale,
                     float *__restrict__ out, float *scales, int8_t *quants, int16_t *sums, const TpHook tp) {
     constexpr int HD = VEC * 32;
     constexpr int P = 32 / G;
-    __shared__ float s_acc[ATT_WARPS][G][HD];
-    __shared__ float s_m[ATT_WARPS][G], s_l[ATT_WARPS][G];
+    __shared__ float s_acc[W][G][HD];
+    __shared__ float s_m[W][G], s_l[W][G];
     __shared__ float part[G][HD];      // this CTA's share, read by the whole cluster
     __shared__ float part_m[G], part_l[G];
     cg::cluster_group cluster = cg::this_cluster();
@@ -279,7 +279,7 @@ attn_cluster_kernel(const float *__restrict__ q, const void *__restrict__ kc, co
 
     float acc[G][VEC];
     float m_run, l_run;
-    attn_scan<VEC, G, F16>(q, kc, vc, kvh, t_begin, t_end, kv_dim, scale, acc, m_run, l_run);
+    attn_scan<VEC, G, F16, W>(q, kc, vc, kvh, t_begin, t_end, kv_dim, scale, acc, m_run, l_run);
 
 #pragma unroll
     for (int g = 0; g < G; ++g)
@@ -294,10 +294,10 @@ attn_cluster_kernel(const float *__restrict__ q, const void *__restrict__ kc, co
         const int g = idx / HD, d = idx % HD;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, s_m[w][g]);
+        for (int w = 0; w < W; ++w) M = fmaxf(M, s_m[w][g]);
         float L = 0.0f, O = 0.0f;
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; ++w) {
+        for (int w = 0; w < W; ++w) {
             const float f = s_m[w][g] == -INFINITY ? 0.0f : ggml_expf(s_m[w][g] - M);
             L = fmaf(s_l[w][g], f, L);
             O = fmaf(s_acc[w][g][d], f, O);
@@ -314,15 +314,33 @@ attn_cluster_kernel(const float *__restrict__ q, const void *__restrict__ kc, co
     const int per = G * HD / (int)CL;
     for (int i = threadIdx.x; i < per; i += blockDim.x) {
         const int idx = (int)split * per + i, g = idx / HD, d = idx % HD;
+        // remote reads in batches of eight, issued together (they are independent: one round trip through the cluster
+        // network per batch, not one per share); pass 1 finds the maximum, pass 2 accumulates
         float M = -INFINITY;
-        for (uint32_t r = 0; r < CL; ++r) M = fmaxf(M, cluster.map_shared_rank(&part_m[0], r)[g]);
+        for (uint32_t r0 = 0; r0 < CL; r0 += 8) {
+            float mv[8];
+#pragma unroll
+            for (uint32_t r = 0; r < 8; ++r) mv[r] = r0 + r < CL ? cluster.map_shared_rank(&part_m[0], r0 + r)[g] : -INFINITY;
+#pragma unroll
+            for (uint32_t r = 0; r < 8; ++r) M = fmaxf(M, mv[r]);
+        }
         double L = 0.0;
         float O = 0.0f;
-        for (uint32_t r = 0; r < CL; ++r) {
-            const float m = cluster.map_shared_rank(&part_m[0], r)[g];
-            const float f = m == -INFINITY ? 0.0f : ggml_expf(m - M);
-            L += (double)(cluster.map_shared_rank(&part_l[0], r)[g] * f);
-            O = fmaf(cluster.map_shared_rank(&part[0][0], r)[g * HD + d], f, O);
+        for (uint32_t r0 = 0; r0 < CL; r0 += 8) {
+            float mv[8], lv[8], ov[8];
+#pragma unroll
+            for (uint32_t r = 0; r < 8; ++r) {
+                const bool in = r0 + r < CL;
+                mv[r] = in ? cluster.map_shared_rank(&part_m[0], r0 + r)[g] : -INFINITY;
+                lv[r] = in ? cluster.map_shared_rank(&part_l[0], r0 + r)[g] : 0.0f;
+                ov[r] = in ? cluster.map_shared_rank(&part[0][0], r0 + r)[g * HD + d] : 0.0f;
+            }
+#pragma unroll
+            for (uint32_t r = 0; r < 8; ++r) {
+                const float f = mv[r] == -INFINITY ? 0.0f : ggml_expf(mv[r] - M);
+                L += (double)(lv[r] * f);
+                O = fmaf(ov[r], f, O);
+            }
         }
         const float v = O * (float)(1.0 / L);
         const size_t o = (size_t)(kvh * G + g) * HD + d;
@@ -419,7 +437,7 @@ int32_t launch_split(bool f16, dim3 grid, cudaStream_t st, const float *q, const
                                seq_dev, n_kv, scale, ws), "attention launch");
 }
 
-template <int VEC, int G>
+template <int VEC, int G, int W>
 int32_t launch_cluster(bool f16, uint32_t cl, cudaStream_t st, const float *q, const void *kc, const void *vc, uint32_t seq_len,
                        const uint32_t *seq_dev, uint32_t n_kv, float scale, float *out, float *scales, int8_t *quants,
                        int16_t *sums, const TpHook &tp) {
@@ -428,14 +446,14 @@ int32_t launch_cluster(bool f16, uint32_t cl, cudaStream_t st, const float *q, c
         int dev = 0;
         cudaGetDevice(&dev);
         if (configured_dev != dev) {
-            CERA_CUDA_TRY(cudaFuncSetAttribute(attn_cluster_kernel<VEC, G, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-            CERA_CUDA_TRY(cudaFuncSetAttribute(attn_cluster_kernel<VEC, G, false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+            CERA_CUDA_TRY(cudaFuncSetAttribute(attn_cluster_kernel<VEC, G, true, W>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+            CERA_CUDA_TRY(cudaFuncSetAttribute(attn_cluster_kernel<VEC, G, false, W>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
             configured_dev = dev;
         }
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_kv * cl);
-    cfg.blockDim = dim3(ATT_WARPS * 32);
+    cfg.blockDim = dim3(W * 32);
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -447,9 +465,9 @@ int32_t launch_cluster(bool f16, uint32_t cl, cudaStream_t st, const float *q, c
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
     if (f16)
-        return check_cuda(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<VEC, G, true>, q, kc, vc, seq_len, seq_dev, n_kv, scale, out,
+        return check_cuda(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<VEC, G, true, W>, q, kc, vc, seq_len, seq_dev, n_kv, scale, out,
                                              scales, quants, sums, tp), "attention (cluster) launch");
-    return check_cuda(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<VEC, G, false>, q, kc, vc, seq_len, seq_dev, n_kv, scale, out,
+    return check_cuda(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<VEC, G, false, W>, q, kc, vc, seq_len, seq_dev, n_kv, scale, out,
                                          scales, quants, sums, tp), "attention (cluster) launch");
 }
 
@@ -469,10 +487,11 @@ uint32_t attn_pick_splits(size_t n_kv_heads, size_t seq_len_hint) {
         return e && strcmp(e, "split") == 0;
     }();
     if (!no_cluster && seq_len_hint <= ATT_CLUSTER_MAX_SEQ) {
-        // about 64 positions per CTA up to the portable cluster of 8 (measured faster than 16 up to 1024 positions);
-        // longer contexts take 16 CTAs per cluster, which the kernel opts into
+        // about 128 positions per CTA (one pass of its 16 warps at a group size of 4) up to the portable cluster of 8
+        // (measured faster than 16 up to 1024 positions); longer contexts take 16 CTAs per cluster, which the kernel
+        // opts into
         uint32_t cl = 1;
-        while (cl < 8 && (size_t)cl * 64 < seq_len_hint) cl <<= 1;
+        while (cl < 8 && (size_t)cl * 128 < seq_len_hint) cl <<= 1;
         if (seq_len_hint > 1024) cl = 16;
         return ATT_CLUSTER_FLAG | cl;
     }
@@ -523,10 +542,14 @@ int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *v
     const bool f16 = kv_f16 != 0;
     const uint32_t sl = (uint32_t)seq_len, nkv = (uint32_t)n_kv_heads;
     const TpHook hook = tp ? *tp : TpHook{};
+    // Cluster kernel: 16 warps per CTA for groups of 4 up to 1024 positions (128 positions per pass, 32 KB of merge
+    // buffers), 8 warps otherwise (measured faster in clusters of 16; groups of 8 would not fit static shared memory).
 #define CERA_ATT(VEC, GG)                                                                                                  \
-    att_status = clustered ? launch_cluster<VEC, GG>(f16, cl, st, q, kc, vc, sl, seq_len_dev, nkv, scale, out, scales, quants, \
-                                                     sums, hook)                                                            \
-                           : launch_split<VEC, GG>(f16, grid, st, q, kc, vc, sl, seq_len_dev, nkv, scale, ws)
+    att_status = !clustered ? launch_split<VEC, GG>(f16, grid, st, q, kc, vc, sl, seq_len_dev, nkv, scale, ws)               \
+                 : (GG == 4 && cl <= 8)                                                                                     \
+                     ? launch_cluster<VEC, GG, (GG == 4 ? 16 : 8)>(f16, cl, st, q, kc, vc, sl, seq_len_dev, nkv, scale, out, scales,   \
+                                                                  quants, sums, hook)                                       \
+                     : launch_cluster<VEC, GG, 8>(f16, cl, st, q, kc, vc, sl, seq_len_dev, nkv, scale, out, scales, quants, sums, hook)
     bool ok = true;
     int32_t att_status = CERA_CUDA_OK;
     bool stream_taken = false;
