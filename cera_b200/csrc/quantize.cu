@@ -209,6 +209,56 @@ __global__ void silu_mul_kernel(float *gate, const float *__restrict__ up, size_
     }
 }
 
+// SiLU*mul with the Q8_0 quantizer, four consecutive elements per thread (one 128-bit load of gate and of up): a
+// 32-element block is eight neighbouring lanes, so its amax takes three shuffle steps and its 16-element sums two.
+__global__ void __launch_bounds__(256) silu_mul_q8_kernel(float *gate, const float *__restrict__ up, size_t n_vec, float *scales,
+                                                          int8_t *quants, int16_t *sums, const TpHook tp) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool in = v < n_vec;  // n_vec is a multiple of 8: a block's eight lanes are all in or all out
+    const int lane = threadIdx.x & 31;
+    float4 g4 = make_float4(0.f, 0.f, 0.f, 0.f), u4 = g4;
+    if (in) {
+        g4 = reinterpret_cast<const float4 *>(gate)[v];
+        u4 = reinterpret_cast<const float4 *>(up)[v];
+    }
+    const float e[4] = {silu_mul(g4.x, u4.x), silu_mul(g4.y, u4.y), silu_mul(g4.z, u4.z), silu_mul(g4.w, u4.w)};
+    if (in) reinterpret_cast<float4 *>(gate)[v] = make_float4(e[0], e[1], e[2], e[3]);
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float a = fabsf(e[i]);
+        amax = fmaxf(amax, a == a ? a : 0.0f);
+    }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float r = __fdiv_rn(1.0f, d);
+    const float id = (d != 0.0f && isfinite(r)) ? r : 0.0f;
+    int q[4], s4 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float pq = rintf(__fmul_rn(e[i], id));
+        q[i] = pq != pq ? 0 : (int)fminf(fmaxf(pq, -128.0f), 127.0f);
+        s4 += q[i];
+    }
+    s4 += __shfl_xor_sync(0xffffffffu, s4, 1);
+    s4 += __shfl_xor_sync(0xffffffffu, s4, 2);
+    if (!in) return;
+    const uint32_t packed = (uint32_t)(uint8_t)q[0] | ((uint32_t)(uint8_t)q[1] << 8) | ((uint32_t)(uint8_t)q[2] << 16) |
+                            ((uint32_t)(uint8_t)q[3] << 24);
+    const float scale = __half2float(__float2half_rn(d));
+    reinterpret_cast<uint32_t *>(quants)[v] = packed;
+    if ((lane & 7) == 0) scales[v >> 3] = scale;
+    if ((lane & 3) == 0) sums[v >> 2] = (int16_t)s4;
+    if (tp.push) {
+        tp_push(tp.ctx, reinterpret_cast<uint32_t *>(quants) + v, packed);
+        if ((lane & 7) == 0) tp_push(tp.ctx, scales + (v >> 3), scale);
+        if ((lane & 3) == 0) tp_push(tp.ctx, sums + (v >> 2), (int16_t)s4);
+    }
+}
+
 }  // namespace
 
 int32_t launch_quantize(const float *x, size_t k, size_t n, bool strided, float *scales, int8_t *quants,
@@ -251,6 +301,13 @@ int32_t launch_silu_mul(float *gate, const float *up, size_t n_elem, size_t n_co
     const size_t total = n_elem * n_cols;
     if (total == 0) return CERA_CUDA_OK;
     const int threads = 256;
+    if (quants && (uintptr_t)gate % 16 == 0 && (uintptr_t)up % 16 == 0 && (uintptr_t)quants % 4 == 0) {
+        const size_t n_vec = total / 4;
+        CERA_CUDA_TRY(launch_k(silu_mul_q8_kernel, dim3((unsigned)((n_vec + threads - 1) / threads)), dim3(threads), 0, st, gate, up, n_vec,
+                               scales, quants, sums, tp ? *tp : TpHook{}));
+        count_launch();
+        return check_cuda(cudaGetLastError(), "silu_mul launch");
+    }
     CERA_CUDA_TRY(launch_k(silu_mul_kernel, dim3((unsigned)((total + threads - 1) / threads)), dim3(threads), 0, st, gate, up,
                            n_elem, n_cols, scales, quants, sums, tp ? *tp : TpHook{}));
     count_launch();

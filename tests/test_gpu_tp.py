@@ -14,6 +14,13 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+def _free_port():
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def test_exchange_wait_runs_out_and_reports():
     """A peer that never signals: the kernel gives up after its budget and leaves (slot, peer) behind."""
     need_gpu()
@@ -65,7 +72,7 @@ def test_ranks_reproduce_single_gpu():
         pytest.skip("needs two GPUs")
     world = 4 if n >= 4 else 2
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
-           "127.0.0.1", "--master-port", "29731", os.path.join(HERE, "tp_worker.py")]
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "tp_worker.py")]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
@@ -84,7 +91,7 @@ def test_expert_parallel_ffn_reproduces_single_gpu():
         pytest.skip("needs two GPUs")
     world = 4 if n >= 4 else 2
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
-           "127.0.0.1", "--master-port", "29733", os.path.join(HERE, "ep_worker.py")]
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "ep_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     report = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
