@@ -72,6 +72,8 @@ SIGNATURES = {
     "cera_cuda_launch_count": (_u64, [_p]),
     "cera_cuda_model_free": (None, [_p]),
     "cera_cuda_forward_prefill_logits_all": (_i32, [_p, _p, _sz, _sz, _p]),
+    "cera_cuda_model_attach_lora": (_i32, [_p, _i32, _i32, _sz, _sz, _sz, _p, _p, _f]),
+    "cera_cuda_model_detach_lora": (_i32, [_p]),
     "cera_cuda_kv_shift": (_i32, [_p, _sz, _sz]),
     "cera_cuda_kv_snapshot_bytes": (_sz, [_p]),
     "cera_cuda_kv_snapshot": (_i32, [_p, _p, _sz]),

@@ -63,6 +63,34 @@ __global__ void rope_kernel(float *q, float *k, const float *__restrict__ v, uin
     }
 }
 
+// LoRA delta of one projection for one token: y += B (scale * (A x))  (cera/src/lora.rs:794-821 apply_decode; A is
+// [rank x k], B is [d x rank], row-major, f32).  Every CTA recomputes the rank-sized vector (A is small and stays in
+// L2) and then finishes 256 outputs; each B-row dot product is summed from zero and added to y once, as the
+// reference requires for its decode and prefill forms to agree.
+constexpr int LORA_MAX_RANK = 256;
+__global__ void __launch_bounds__(256) lora_kernel(const float *__restrict__ x, const float *__restrict__ a,
+                                                   const float *__restrict__ b, uint32_t rank, uint32_t k, uint32_t d, float scale,
+                                                   float *y) {
+    __shared__ float tmp[LORA_MAX_RANK];
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t r = warp; r < rank; r += 8) {
+        const float *row = a + (size_t)r * k;
+        float acc = 0.0f;
+        for (uint32_t i = lane; i < k; i += 32) acc = fmaf(row[i], x[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) tmp[r] = __fmul_rn(acc, scale);
+    }
+    __syncthreads();
+    const uint32_t o = blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= d) return;
+    const float *row = b + (size_t)o * rank;
+    float acc = 0.0f;
+    for (uint32_t r = 0; r < rank; ++r) acc = __fadd_rn(acc, __fmul_rn(row[r], tmp[r]));
+    y[o] = __fadd_rn(y[o], acc);
+}
+
 // Context shift of one layer's cache (cera/src/kv_cache.rs:1091-1320, shift_kv_with_rope): rows
 // [n_keep + shift, seq_len) move down by `shift`; every moved K head is rotated once more by R(-shift)
 // (cera/src/backend/cpu.rs:5056-5083 split halves, 5145-5180 adjacent pairs, same iterated theta with
@@ -248,6 +276,15 @@ int32_t launch_argmax(const float *x, size_t n, uint32_t *out, uint32_t *scratch
     CERA_CUDA_TRY(launch_k(argmax_stage1, dim3(ARGMAX_BLOCKS), dim3(ARGMAX_THREADS), 0, st, x, (uint32_t)n, scratch));
     return check_cuda(launch_k(argmax_stage2, dim3(1), dim3(32), 0, st, (const uint32_t *)scratch, (int)ARGMAX_BLOCKS, out),
                       "argmax launch");
+}
+
+int32_t launch_lora(const float *x, const float *a, const float *b, size_t rank, size_t k, size_t d, float scale, float *y,
+                    cudaStream_t st) {
+    if (rank == 0 || rank > LORA_MAX_RANK) return fail(CERA_CUDA_ERR_BAD_ARG, "lora: rank %zu outside 1..%d", rank, LORA_MAX_RANK);
+    CERA_CUDA_TRY(launch_k(lora_kernel, dim3((unsigned)((d + 255) / 256)), dim3(256), 0, st, x, a, b, (uint32_t)rank, (uint32_t)k,
+                           (uint32_t)d, scale, y));
+    count_launch();
+    return CERA_CUDA_OK;
 }
 
 int32_t launch_kv_shift(const void *k_src, const void *v_src, void *k_cache, void *v_cache, size_t n_keep, size_t shift,

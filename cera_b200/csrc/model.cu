@@ -42,7 +42,15 @@ struct ActBuf {
     ActView view() const { return ActView{scales, quants, sums}; }
 };
 
+// One LoRA pair of a projection (device copies of A [rank x k] and B [d x rank]).
+struct Lora {
+    float *a = nullptr, *b = nullptr;
+    uint32_t rank = 0, k = 0, d = 0;
+    float scale = 0.0f;
+};
+
 struct Layer {
+    Lora lora[7];  // q, k, v, o, gate, up, down (the order of cera/src/lora.rs:63-70)
     float *attn_norm = nullptr, *ffn_norm = nullptr;
     cera_cuda_weight *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *gate = nullptr, *up = nullptr,
                      *down = nullptr;
@@ -90,6 +98,8 @@ struct cera_cuda_model {
           *pf_u = nullptr;
     ActBuf pf_act_hs, pf_act_q, pf_act_ff;
     float *pf_logits = nullptr;  // [PREFILL_CHUNK][vocab], allocated by the first logits-for-every-position call
+    bool has_lora = false;
+    float *normed = nullptr;       // f32 copy of the normed hidden state, written only while adapters are attached
     uint32_t *tok_hist = nullptr;  // device ring of generated tokens (chained greedy decode)
     uint32_t tok_hist_cap = 0;
     // tensor parallelism (tp_size == 1: a single device, no exchange)
@@ -172,10 +182,19 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
         const uint32_t s0 = 4 * li;
         const TpHook h_norm1 = hook(li ? s0 - 1 : TP_NO_SLOT, false), h_merge = hook(TP_NO_SLOT, true), h_wo = hook(s0, true),
                      h_norm2 = hook(s0 + 1, false), h_silu = hook(TP_NO_SLOT, true), h_down = hook(s0 + 2, true);
-        CERA_TRY(launch_rmsnorm(m->hidden, L.attn_norm, hs, 1, c.rms_norm_eps, nullptr, m->act_hs.scales,
+        // LoRA deltas read the f32 input of the projection they adapt (cera/src/model/transformer.rs:1383-1387,
+        // 1519-1528, 1588-1605, 1642-1651): the normed hidden, the attention output, the SwiGLU product
+        float *normed_f32 = m->has_lora ? m->normed : nullptr;
+        auto lora = [&](int target, const float *x, float *y) -> int32_t {
+            const Lora &t = L.lora[target];
+            if (!t.rank || t.scale == 0.0f) return CERA_CUDA_OK;
+            return launch_lora(x, t.a, t.b, t.rank, t.k, t.d, t.scale, y, st);
+        };
+        const bool lora_qkv = L.lora[0].rank || L.lora[1].rank || L.lora[2].rank;
+        CERA_TRY(launch_rmsnorm(m->hidden, L.attn_norm, hs, 1, c.rms_norm_eps, normed_f32, m->act_hs.scales,
                                 m->act_hs.quants, m->act_hs.sums, st, &h_norm1));
         bool fused_qkv = false;
-        if (norm_rope && L.wq->v.type == L.wk->v.type && L.wq->v.type == L.wv->v.type) {
+        if (!lora_qkv && norm_rope && L.wq->v.type == L.wk->v.type && L.wq->v.type == L.wv->v.type) {
             // q/k/v GEMV with RoPE and the KV-cache append as its epilogue
             GemvSeg segs[3] = {{L.wq->v, m->q}, {L.wk->v, m->k}, {L.wv->v, m->v}};
             GemvFusion f;
@@ -198,6 +217,11 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
             CERA_TRY(launch_gemv(&sk, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
             CERA_TRY(launch_gemv(&sv, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
         }
+        if (lora_qkv) {  // the deltas go in before RoPE, like the base projections
+            CERA_TRY(lora(0, m->normed, m->q));
+            CERA_TRY(lora(1, m->normed, m->k));
+            CERA_TRY(lora(2, m->normed, m->v));
+        }
         if (!fused_qkv)
             CERA_TRY(launch_rope(m->q, m->k, m->v, 0, m->dyn + 1, m->l_heads, m->l_kv_heads, c.head_dim, m->theta_scale,
                                  m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st));
@@ -207,7 +231,8 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
                                             aq.scales, aq.quants, aq.sums, st, &h_merge));
         GemvSeg so{L.wo->v, hidden_slice};
         CERA_TRY(launch_gemv(&so, 1, m->act_q.view(), 1, 1, EPI_ADD, st, 1, false, &h_wo));
-        CERA_TRY(launch_rmsnorm(m->hidden, L.ffn_norm, hs, 1, c.rms_norm_eps, nullptr, m->act_hs.scales,
+        CERA_TRY(lora(3, m->attn, m->hidden));  // o-proj output lives in the residual stream already
+        CERA_TRY(launch_rmsnorm(m->hidden, L.ffn_norm, hs, 1, c.rms_norm_eps, normed_f32, m->act_hs.scales,
                                 m->act_hs.quants, m->act_hs.sums, st, &h_norm2));
         if (L.gate->v.type == L.up->v.type) {
             GemvSeg segs[2] = {{L.gate->v, m->g}, {L.up->v, m->u}};
@@ -217,10 +242,13 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
             CERA_TRY(launch_gemv(&sg, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
             CERA_TRY(launch_gemv(&su, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
         }
+        CERA_TRY(lora(4, m->normed, m->g));
+        CERA_TRY(lora(5, m->normed, m->u));
         const ActBuf af = act_slice(m->act_ff, m->l_ff);
         CERA_TRY(launch_silu_mul(m->g, m->u, m->l_ff, 1, af.scales, af.quants, af.sums, st, &h_silu));
         GemvSeg sd{L.down->v, hidden_slice};
         CERA_TRY(launch_gemv(&sd, 1, m->act_ff.view(), 1, 1, EPI_ADD, st, 1, false, &h_down));
+        CERA_TRY(lora(6, m->g, m->hidden));  // input: the SwiGLU product, left in g by the kernel above
     }
     const uint32_t s_last = 4 * n_layers - 1, s_logits = 4 * n_layers, s_pick = 4 * n_layers + 1;
     if (kind == G_BODY) {
@@ -632,7 +660,7 @@ int32_t cera_cuda_forward_prefill(cera_cuda_model *m, const uint32_t *tokens, si
         return e && strcmp(e, "per_token") == 0;
     }();
     if (m->tp_size > 1 && !m->tp_connected) return fail(CERA_CUDA_ERR_STATE, "forward_prefill: tensor-parallel model is not connected to its peers");
-    if (per_token || n < 2 || m->tp_size > 1) {
+    if (per_token || n < 2 || m->tp_size > 1 || m->has_lora) {
         // Decode arithmetic for every prompt position (one graph launch per token).  h_dyn is rewritten per
         // token, so wait for the copy of the previous one before touching it again.
         for (size_t i = 0; i < n; ++i) {
@@ -675,9 +703,9 @@ int32_t cera_cuda_forward_prefill_logits_all(cera_cuda_model *m, const uint32_t 
     for (size_t i = 0; i < n; ++i)
         if (tokens[i] >= c.vocab_size) return fail(CERA_CUDA_ERR_BAD_ARG, "forward_prefill_logits_all: token %u out of range", tokens[i]);
     const size_t vocab = c.vocab_size;
-    if (m->tp_size > 1) {
-        // tensor-parallel: the decode step per position, each with its logits exchange
-        if (!m->tp_connected) return fail(CERA_CUDA_ERR_STATE, "forward_prefill_logits_all: tensor-parallel model is not connected to its peers");
+    if (m->tp_size > 1 || m->has_lora) {
+        // tensor-parallel (each position with its logits exchange) or adapters attached: the decode step per position
+        if (m->tp_size > 1 && !m->tp_connected) return fail(CERA_CUDA_ERR_STATE, "forward_prefill_logits_all: tensor-parallel model is not connected to its peers");
         for (size_t i = 0; i < n; ++i) {
             CERA_TRY(run_token(m, tokens[i], start_pos + i, G_LOGITS));
             CERA_CUDA_TRY(cudaMemcpyAsync(logits_out + i * vocab, m->logits, vocab * 4, cudaMemcpyDeviceToHost, m->stream));
@@ -780,6 +808,51 @@ int32_t cera_cuda_truncate_kv(cera_cuda_model *m, size_t len) {
     if (!m) return fail(CERA_CUDA_ERR_BAD_ARG, "truncate_kv: null model");
     std::lock_guard<std::mutex> lock(m->mu);
     if (len < m->seq_len) m->seq_len = len;  // rows beyond seq_len are simply overwritten later
+    return CERA_CUDA_OK;
+}
+
+// ---- LoRA (InferenceState::lora, cera/src/lora.rs) ---------------------------------------------------------
+
+int32_t cera_cuda_model_attach_lora(cera_cuda_model *m, int32_t target, int32_t layer, size_t rank, size_t k, size_t d,
+                                    const float *a, const float *b, float scale) {
+    if (!m || !a || !b) return fail(CERA_CUDA_ERR_BAD_ARG, "attach_lora: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    const auto &c = m->cfg;
+    if (!m->finalized) return fail(CERA_CUDA_ERR_STATE, "attach_lora: model_finalize has not been called");
+    if (m->tp_size > 1) return fail(CERA_CUDA_ERR_UNSUPPORTED, "attach_lora: adapters on a tensor-parallel model are not supported");
+    if (target < 0 || target > 6 || layer < 0 || (uint32_t)layer >= c.n_layers)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "attach_lora: target %d layer %d", target, layer);
+    const size_t hs = c.hidden_size, qd = (size_t)c.n_heads * c.head_dim, kvd = (size_t)c.n_kv_heads * c.head_dim, ff = c.intermediate_size;
+    const size_t want_k[7] = {hs, hs, hs, qd, hs, hs, ff}, want_d[7] = {qd, kvd, kvd, hs, ff, ff, hs};
+    if (k != want_k[target] || d != want_d[target] || rank == 0 || rank > 256)
+        return fail(CERA_CUDA_ERR_BAD_ARG, "attach_lora: target %d expects A [rank<=256 x %zu], B [%zu x rank]; got rank %zu, k %zu, d %zu", target,
+                    want_k[target], want_d[target], rank, k, d);
+    CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    Lora &t = m->layers[layer].lora[target];
+    float *da = nullptr, *db = nullptr;
+    CERA_TRY(dev_alloc(m, (void **)&da, rank * k * 4));
+    CERA_TRY(dev_alloc(m, (void **)&db, d * rank * 4));
+    CERA_CUDA_TRY(cudaMemcpy(da, a, rank * k * 4, cudaMemcpyDefault));
+    CERA_CUDA_TRY(cudaMemcpy(db, b, d * rank * 4, cudaMemcpyDefault));
+    if (!m->normed) CERA_TRY(dev_alloc(m, (void **)&m->normed, hs * 4));
+    t = Lora{da, db, (uint32_t)rank, (uint32_t)k, (uint32_t)d, scale};  // a replaced pair stays allocated until model_free
+    m->has_lora = true;
+    for (auto &kv : m->graphs) cudaGraphExecDestroy(kv.second);  // the recorded steps do not contain the new kernels
+    m->graphs.clear();
+    return CERA_CUDA_OK;
+}
+
+int32_t cera_cuda_model_detach_lora(cera_cuda_model *m) {
+    if (!m) return fail(CERA_CUDA_ERR_BAD_ARG, "detach_lora: null model");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    if (m->stream) CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    for (auto &L : m->layers)
+        for (auto &t : L.lora) t = Lora{};
+    m->has_lora = false;
+    for (auto &kv : m->graphs) cudaGraphExecDestroy(kv.second);
+    m->graphs.clear();
     return CERA_CUDA_OK;
 }
 

@@ -101,6 +101,9 @@ int32_t launch_rope_batch(float *q, float *k, const float *v, size_t start_pos, 
 int32_t launch_prefill_attention(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
                                  size_t n_kv_heads, size_t head_dim, size_t n, size_t start_pos, float scale, float *out,
                                  cudaStream_t st);
+// y[d] += B (scale * (A x)): one LoRA pair applied to one token (cera/src/lora.rs:794-821).
+int32_t launch_lora(const float *x, const float *a, const float *b, size_t rank, size_t k, size_t d, float scale, float *y,
+                    cudaStream_t st);
 // Rows [n_keep + shift, n_keep + shift + n_rows) of a cache, given as a copy in k_src / v_src, re-enter it at
 // [n_keep, n_keep + n_rows) with K rotated by R(-shift) (cera/src/kv_cache.rs:1091-1320).
 int32_t launch_kv_shift(const void *k_src, const void *v_src, void *k_cache, void *v_cache, size_t n_keep, size_t shift,

@@ -106,6 +106,21 @@ class CudaModel:
     def truncate_kv(self, n):
         check(lib.cera_cuda_truncate_kv(self.handle, n))
 
+    LORA_TARGETS = ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")
+
+    def attach_lora(self, target, layer, a, b, scale):
+        """y = W x + scale * B (A x) for one projection: a [rank, k], b [d, rank] float32 (numpy)."""
+        t = self.LORA_TARGETS.index(target) if isinstance(target, str) else int(target)
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        b = np.ascontiguousarray(b, dtype=np.float32)
+        if a.ndim != 2 or b.ndim != 2 or b.shape[1] != a.shape[0]:
+            raise ValueError("a must be [rank, k] and b [d, rank]")
+        check(lib.cera_cuda_model_attach_lora(self.handle, t, layer, a.shape[0], a.shape[1], b.shape[0],
+                                              a.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p), scale))
+
+    def detach_lora(self):
+        check(lib.cera_cuda_model_detach_lora(self.handle))
+
     def shift_kv(self, n_keep, shift):
         """Model::shift_kv: drop positions [n_keep, n_keep + shift) and re-rotate the keys that move down."""
         check(lib.cera_cuda_kv_shift(self.handle, n_keep, shift))

@@ -283,6 +283,18 @@ CERA_API int32_t cera_cuda_forward_prefill(cera_cuda_model *m, const uint32_t *t
                                            size_t start_pos, float *logits_out);
 /* Model::truncate_kv (mod.rs:251-283). */
 CERA_API int32_t cera_cuda_truncate_kv(cera_cuda_model *m, size_t len);
+/* LoRA adapters (cera/src/lora.rs; the reference carries them on InferenceState::lora and applies
+ * them in forward_attn_block / forward_ffn_block, cera/src/model/transformer.rs:1383-1387, 1519-1528,
+ * 1588-1605, 1642-1651): y = W x + scale * B (A x) on the f32 input of the projection, q/k/v before
+ * RoPE, gate/up before the SwiGLU product.  target: 0 q, 1 k, 2 v, 3 attn_output, 4 ffn_gate,
+ * 5 ffn_up, 6 ffn_down (the order of lora.rs:63-70); a is [rank x k], b is [d x rank], row-major F32,
+ * host or device, copied; scale = alpha / rank.  While any pair is attached prompts are processed
+ * with the decode step per token (the reference requires its batched form to equal the per-token form
+ * bit for bit, lora.rs:830-844).  MoE targets and tensor-parallel models: CERA_CUDA_ERR_UNSUPPORTED /
+ * not offered.  detach removes every pair. */
+CERA_API int32_t cera_cuda_model_attach_lora(cera_cuda_model *m, int32_t target, int32_t layer, size_t rank,
+                                             size_t k, size_t d, const float *a, const float *b, float scale);
+CERA_API int32_t cera_cuda_model_detach_lora(cera_cuda_model *m);
 /* Model::forward_prefill_logits_all (cera/src/model/mod.rs:507-533; the verifier side of speculative
  * decoding): like forward_prefill, but the logits of every position come back, logits_out[n][vocab]
  * on the host, token-major. */

@@ -961,8 +961,33 @@ struct TensorRef {
     const uint8_t *bytes = nullptr;
 };
 
+// One LoRA pair of a projection: y += B (scale * (A x))  (cera/src/lora.rs:794-821).
+struct LoraPair {
+    size_t rank = 0, k = 0, d = 0;
+    float scale = 0.0f;
+    std::vector<float> a, b;  // A [rank x k], B [d x rank], row-major
+};
+
+// lora.rs:799-821 apply_decode, operation for operation: each dot product is summed from zero in index order, the
+// scale is folded into the rank-sized vector, and the finished B row dot is added to y once.
+static void lora_apply(const LoraPair &t, const float *x, float *y) {
+    if (t.rank == 0 || t.scale == 0.0f) return;
+    std::vector<float> tmp(t.rank);
+    for (size_t r = 0; r < t.rank; ++r) {
+        float acc = 0.0f;
+        for (size_t i = 0; i < t.k; ++i) acc += t.a[r * t.k + i] * x[i];
+        tmp[r] = acc * t.scale;
+    }
+    for (size_t o = 0; o < t.d; ++o) {
+        float acc = 0.0f;
+        for (size_t r = 0; r < t.rank; ++r) acc += t.b[o * t.rank + r] * tmp[r];
+        y[o] += acc;
+    }
+}
+
 struct cera_oracle_model {
     cera_oracle_config cfg;
+    std::vector<LoraPair> lora;  // [layer * 7 + target], targets in the order of cera/src/lora.rs:63-70 (q, k, v, o, gate, up, down)
     TensorRef embd, out_norm, output, rope_freqs;
     std::vector<TensorRef> attn_norm, wq, wk, wv, wo, ffn_norm, gate, up, down;
     std::vector<std::vector<uint8_t>> kcache, vcache;  // f32 or f16 bytes, time-major
@@ -1037,6 +1062,11 @@ int cera_oracle_model_forward(cera_oracle_model *M, uint32_t token, size_t pos, 
         gemv(M->wq[l], normed.data(), q.data());
         gemv(M->wk[l], normed.data(), k.data());
         gemv(M->wv[l], normed.data(), v.data());
+        if (!M->lora.empty()) {  // before RoPE, input = the normed hidden (cera/src/model/transformer.rs:1383-1387)
+            lora_apply(M->lora[l * 7 + 0], normed.data(), q.data());
+            lora_apply(M->lora[l * 7 + 1], normed.data(), k.data());
+            lora_apply(M->lora[l * 7 + 2], normed.data(), v.data());
+        }
         cera_oracle_rope(q.data(), k.data(), pos, c.n_heads, c.n_kv_heads, hd, c.rope_theta, ffreq,
                          c.rope_type);
         auto &kc = M->kcache[l];
@@ -1057,13 +1087,19 @@ int cera_oracle_model_forward(cera_oracle_model *M, uint32_t token, size_t pos, 
                                      hd, pos + 1, 1.0f / std::sqrt((float)hd), attn.data(),
                                      scores.data());
         gemv(M->wo[l], attn.data(), out.data());
+        if (!M->lora.empty()) lora_apply(M->lora[l * 7 + 3], attn.data(), out.data());  // transformer.rs:1519-1528
         for (size_t i = 0; i < hs; ++i) hidden[i] += out[i];
         normed = hidden;
         cera_oracle_rmsnorm(normed.data(), (const float *)M->ffn_norm[l].bytes, hs, c.rms_norm_eps);
         gemv(M->gate[l], normed.data(), g.data());
         gemv(M->up[l], normed.data(), u.data());
+        if (!M->lora.empty()) {  // before the SwiGLU product (transformer.rs:1588-1605)
+            lora_apply(M->lora[l * 7 + 4], normed.data(), g.data());
+            lora_apply(M->lora[l * 7 + 5], normed.data(), u.data());
+        }
         cera_oracle_silu_mul(g.data(), u.data(), ff);
         gemv(M->down[l], g.data(), out.data());
+        if (!M->lora.empty()) lora_apply(M->lora[l * 7 + 6], g.data(), out.data());  // transformer.rs:1642-1651
         for (size_t i = 0; i < hs; ++i) hidden[i] += out[i];
     }
     cera_oracle_rmsnorm(hidden.data(), (const float *)M->out_norm.bytes, hs, c.rms_norm_eps);
@@ -1073,6 +1109,32 @@ int cera_oracle_model_forward(cera_oracle_model *M, uint32_t token, size_t pos, 
         const TensorRef &o = M->output.bytes ? M->output : M->embd;
         gemv(o, hidden.data(), logits);
     }
+    return 0;
+}
+
+void cera_oracle_lora_apply(size_t rank, size_t k, size_t d, float scale, const float *a, const float *b, const float *x,
+                            float *y) {
+    LoraPair t;
+    t.rank = rank;
+    t.k = k;
+    t.d = d;
+    t.scale = scale;
+    t.a.assign(a, a + rank * k);
+    t.b.assign(b, b + d * rank);
+    lora_apply(t, x, y);
+}
+
+int cera_oracle_model_set_lora(cera_oracle_model *M, int target, int layer, size_t rank, size_t k, size_t d, float scale,
+                               const float *a, const float *b) {
+    if (target < 0 || target > 6 || layer < 0 || (uint32_t)layer >= M->cfg.n_layers || !a || !b || rank == 0) return -1;
+    if (M->lora.empty()) M->lora.resize((size_t)M->cfg.n_layers * 7);
+    LoraPair &t = M->lora[(size_t)layer * 7 + target];
+    t.rank = rank;
+    t.k = k;
+    t.d = d;
+    t.scale = scale;
+    t.a.assign(a, a + rank * k);
+    t.b.assign(b, b + d * rank);
     return 0;
 }
 

@@ -166,6 +166,12 @@ int cera_oracle_model_set_tensor(cera_oracle_model *m, int role, int layer, int 
                                  size_t cols, const void *bytes);
 /* One decode token at position pos == current seq_len; logits may be NULL. */
 int cera_oracle_model_forward(cera_oracle_model *m, uint32_t token, size_t pos, float *logits);
+/* y += B (scale * (A x)), cera/src/lora.rs:799-821 apply_decode */
+void cera_oracle_lora_apply(size_t rank, size_t k, size_t d, float scale, const float *a, const float *b, const float *x,
+                            float *y);
+/* One LoRA pair (cera/src/lora.rs:794-821): target 0..6 = q, k, v, o, gate, up, down; A [rank x k], B [d x rank]. */
+int cera_oracle_model_set_lora(cera_oracle_model *m, int target, int layer, size_t rank, size_t k, size_t d, float scale,
+                               const float *a, const float *b);
 void cera_oracle_model_truncate_kv(cera_oracle_model *m, size_t len);
 /* cera/src/kv_cache.rs:1091-1320 (shift_kv_with_rope); -1 on the reference's assertion cases */
 int cera_oracle_model_shift_kv(cera_oracle_model *m, size_t n_keep, size_t shift);

@@ -71,6 +71,8 @@ _sig("cera_oracle_model_set_tensor", C.c_int, _p, C.c_int, C.c_int, C.c_int, _sz
 _sig("cera_oracle_model_forward", C.c_int, _p, C.c_uint32, _sz, _p)
 _sig("cera_oracle_model_truncate_kv", None, _p, _sz)
 _sig("cera_oracle_model_shift_kv", C.c_int, _p, _sz, _sz)
+_sig("cera_oracle_lora_apply", None, _sz, _sz, _sz, C.c_float, _p, _p, _p, _p)
+_sig("cera_oracle_model_set_lora", C.c_int, _p, C.c_int, C.c_int, _sz, _sz, _sz, C.c_float, _p, _p)
 _sig("cera_oracle_model_seq_len", _sz, _p)
 _sig("cera_oracle_model_last_hidden", C.c_int, _p, _p)
 _sig("cera_oracle_model_free", None, _p)
@@ -243,6 +245,14 @@ def select_experts(probs, bias, n_used):
     return ids, w
 
 
+def lora_apply(a, b, scale, x, y):
+    """y + B (scale * (A x)) with the reference's summation order; a [rank, k], b [d, rank]."""
+    a, b, x = c32(a), c32(b), c32(x)
+    y = c32(y).copy()
+    _lib.cera_oracle_lora_apply(a.shape[0], a.shape[1], b.shape[0], C.c_float(scale), _ptr(a), _ptr(b), _ptr(x), _ptr(y))
+    return y
+
+
 def synth_normal(n, seed, sigma, offset=0):
     out = np.empty(n, dtype=np.float32)
     _lib.cera_oracle_synth_normal(_ptr(out), n, seed, offset, C.c_float(sigma))
@@ -276,6 +286,12 @@ class OracleModel:
 
     def truncate_kv(self, n):
         _lib.cera_oracle_model_truncate_kv(self.h, n)
+
+    def set_lora(self, target, layer, a, b, scale):
+        """a: [rank, k], b: [d, rank] float32."""
+        a, b = c32(a), c32(b)
+        assert _lib.cera_oracle_model_set_lora(self.h, target, layer, a.shape[0], a.shape[1], b.shape[0], C.c_float(scale),
+                                               _ptr(a), _ptr(b)) == 0
 
     def shift_kv(self, n_keep, shift):
         assert _lib.cera_oracle_model_shift_kv(self.h, n_keep, shift) == 0

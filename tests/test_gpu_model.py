@@ -262,3 +262,57 @@ def test_prefill_logits_for_every_position():
         assert_model_logits(rows[pos], want[pos], f"position {pos}")
     nxt = int(np.argmax(rows[-1]))
     assert_model_logits(a.forward(nxt, 270), b.forward(nxt, 270), "next token after the two prefills")
+
+
+def test_lora_adapters_match_reference_and_detach_cleanly():
+    """Dense LoRA on every projection kind (cera/src/lora.rs:794-821, wired as in transformer.rs): logits follow the
+    oracle with the same pairs attached; a prompt gives the same logits as token-by-token decoding; B = 0 and a
+    detach both give back the base model bit for bit."""
+    need_gpu()
+    import cera_b200 as cb
+    from cera_b200 import synth
+    cfg = WIDE
+    gpu, oracle = _pair(cfg, seed=29)
+    hs, ff = cfg["hidden_size"], cfg["intermediate_size"]
+    qd, kvd = cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"]
+    shapes = {"attn_q": (hs, qd), "attn_k": (hs, kvd), "attn_v": (hs, kvd), "attn_output": (qd, hs), "ffn_gate": (hs, ff),
+              "ffn_up": (hs, ff), "ffn_down": (ff, hs)}
+    prompt = synth.prompt_tokens(6, cfg["vocab_size"], seed=3)
+    base = [gpu.forward(int(t), pos) for pos, t in enumerate(prompt)]
+    gpu.truncate_kv(0)
+    rng = np.random.default_rng(7)
+    pairs = []
+    for layer, targets in ((0, ("attn_q", "attn_v", "ffn_gate", "ffn_down")), (1, ("attn_k", "attn_output", "ffn_up"))):
+        for name in targets:
+            k, d = shapes[name]
+            rank = 8 if name != "ffn_down" else 5
+            a = (rng.standard_normal((rank, k)) * 0.05).astype(np.float32)
+            b = (rng.standard_normal((d, rank)) * 0.05).astype(np.float32)
+            pairs.append((name, layer, a, b))
+    # B = 0: attached but inert
+    for name, layer, a, b in pairs:
+        gpu.attach_lora(name, layer, a, np.zeros_like(b), 2.0)
+    inert = [gpu.forward(int(t), pos) for pos, t in enumerate(prompt)]
+    for x, y in zip(base, inert):
+        assert np.array_equal(x, y)
+    gpu.truncate_kv(0)
+    for name, layer, a, b in pairs:
+        gpu.attach_lora(name, layer, a, b, 2.0)
+        oracle.set_lora(cb.CudaModel.LORA_TARGETS.index(name), layer, a, b, 2.0)
+    moved = 0.0
+    for pos, t in enumerate(prompt):
+        lg, lo = gpu.forward(int(t), pos), oracle.forward(int(t), pos)
+        assert_model_logits(lg, lo, f"adapted logits at pos {pos}")
+        moved = max(moved, float(np.abs(lg - base[pos]).max()))
+    assert moved > 1e-3  # the adapters do change the model
+    last_step = lg
+    gpu.truncate_kv(0)
+    assert np.array_equal(gpu.forward_prefill(prompt, 0), last_step)  # prompts take the per-token path while adapted
+    gpu.detach_lora()
+    gpu.truncate_kv(0)
+    for pos, t in enumerate(prompt):
+        assert np.array_equal(gpu.forward(int(t), pos), base[pos])
+    with pytest.raises(cb.CeraCudaError, match="expects"):
+        gpu.attach_lora("attn_q", 0, np.zeros((4, hs + 1), np.float32), np.zeros((qd, 4), np.float32), 1.0)
+    with pytest.raises(cb.CeraCudaError, match="target"):
+        gpu.attach_lora(9, 0, np.zeros((4, hs), np.float32), np.zeros((qd, 4), np.float32), 1.0)

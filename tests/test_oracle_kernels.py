@@ -336,3 +336,36 @@ def test_kv_shift_of_a_one_layer_model_equals_the_shorter_sequence(rope_type, kv
     # the reference's assertion cases
     assert O._lib.cera_oracle_model_shift_kv(a.h, 1, 0) == -1
     assert O._lib.cera_oracle_model_shift_kv(a.h, a.seq_len, 1) == -1
+
+
+def test_lora_apply_known_answers():
+    """cera/src/lora.rs:1198-1215: B = 0 is a no-op whatever the scale; with A = B = 1 every output moves by
+    rank * scale * sum(x); a zero scale leaves y untouched bit for bit (no -0.0 -> +0.0 flip)."""
+    rank, k, d = 4, 16, 6
+    x = (np.arange(k, dtype=np.float32) - 3.0) * 0.25
+    y0 = np.array([0.5, -0.0, 1.0, -2.0, 3.5, 0.0], dtype=np.float32)
+    ones_a, ones_b = np.ones((rank, k), np.float32), np.ones((d, rank), np.float32)
+    assert np.array_equal(O.lora_apply(ones_a, np.zeros((d, rank), np.float32), 2.0, x, y0), y0)
+    got = O.lora_apply(ones_a, ones_b, 2.0, x, y0)
+    assert np.allclose(got, y0 + rank * 2.0 * x.sum(), rtol=1e-6)
+    assert np.array_equal(O.lora_apply(ones_a, ones_b, 0.0, x, y0).view(np.uint32), y0.view(np.uint32))
+    # against the plain formula on random factors
+    rng = np.random.default_rng(5)
+    a, b = rng.standard_normal((rank, k)).astype(np.float32), rng.standard_normal((d, rank)).astype(np.float32)
+    want = y0 + b.astype(np.float64) @ (0.5 * (a.astype(np.float64) @ x))
+    assert np.allclose(O.lora_apply(a, b, 0.5, x, y0), want, rtol=1e-5, atol=1e-6)
+
+
+def test_lora_changes_the_model_only_where_attached():
+    cfg = dict(n_layers=2, hidden_size=64, intermediate_size=128, n_heads=4, n_kv_heads=2, head_dim=32, vocab_size=96,
+               rope_theta=10000.0, rms_norm_eps=1e-5, rope_type=0)
+    base, tuned, zero = _cpu_llama(cfg, 4), _cpu_llama(cfg, 4), _cpu_llama(cfg, 4)
+    rng = np.random.default_rng(1)
+    a = rng.standard_normal((4, 64)).astype(np.float32) * 0.1
+    b = rng.standard_normal((64, 4)).astype(np.float32) * 0.1
+    tuned.set_lora(3, 1, a, b, 2.0)                                   # o-proj of layer 1: 64 -> 64
+    zero.set_lora(3, 1, a, np.zeros_like(b), 2.0)
+    for pos, t in enumerate([7, 50, 3]):
+        lb, lt, lz = base.forward(t, pos), tuned.forward(t, pos), zero.forward(t, pos)
+    assert np.array_equal(lb, lz)
+    assert np.abs(lb - lt).max() > 1e-4
