@@ -1,9 +1,11 @@
-// Prefill GEMM on the integer tensor-core path: out[m x n] = W (Q4_K, Q5_K or Q6_K) x X (Q8_0 columns), n >= 5.
+// Prefill GEMM on the integer tensor-core path: out[m x n] = W (Q4_0, Q4_K, Q5_K or Q6_K) x X (Q8_0 columns), n >= 5,
+// and its expert-grouped form for the routed FFN.
 //
 // A CTA owns a 64-row x 128-column output tile and walks k one 256-element super-block at a time:
 // weights of the 64 rows and the Q8_0 quants of the 128 columns are staged in shared memory with
 // cp.async, the six-bit / int8 sub-block scales are expanded to f32 once per chunk, and every warp
 // (16 rows x 64 columns) issues mma.sync int8 instructions whose int32 results are EXACT per-block sums:
+//   Q4_0 : m16n8k32 (u8 x s8) per 32-element block,      out += d * xs * U - (8*d) * (xs*A32)
 //   Q4_K : m16n8k32 (u8 x s8) per 32-element sub-block,  out += (d*sc) * xs * U - (dmin*mn) * (xs*A32)
 //   Q5_K : the same with the fifth bit of every quant merged into the u8 operand
 //   Q6_K : m16n8k16 (u8 x s8) per 16-element scale group, out += (d*sc) * (xs*U - 32*xs*A16)
@@ -48,6 +50,9 @@ struct GemmParams {
     uint32_t m, n, k;
     uint32_t ldy, ldc;
     int epilogue;
+    // expert-grouped form (tiles != null): blockIdx.y walks the device-side work list; m is the row count per expert
+    const MoeTile *tiles;
+    const uint32_t *n_tiles;
 };
 
 __device__ __forceinline__ void cpa16(void *smem, const void *gmem) {
@@ -101,7 +106,16 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
     const int wrow = (warp & 3) * 16, wcol = (warp >> 2) * (GM_BN / 2);  // this warp's 16 x BN/2 patch of the tile
     cg::cluster_group cluster = cg::this_cluster();
     const uint32_t CL = cluster.num_blocks(), crank = cluster.block_rank();
-    const uint32_t row0 = (blockIdx.x / CL) * GM_BM, col0 = blockIdx.y * GM_BN;
+    uint32_t row0 = (blockIdx.x / CL) * GM_BM, col0 = blockIdx.y * GM_BN;
+    uint32_t wrow0 = row0, n_cols = p.n;  // first weight row of the tile; one past the last valid activation column
+    if (p.tiles) {
+        if (blockIdx.y >= *p.n_tiles) return;  // uniform over the cluster (same blockIdx.y)
+        const MoeTile tile = p.tiles[blockIdx.y];
+        col0 = tile.first;
+        n_cols = tile.first + tile.count;
+        wrow0 = tile.expert * p.m + row0;
+    }
+    const uint32_t w_last = (p.tiles ? wrow0 - row0 : 0) + p.m - 1;  // last weight row this tile may touch
     const uint32_t nb = p.w.nb, nb32 = p.k >> 5, nb16 = p.k >> 4;
     const TypeInfo ti = type_info(T);
 
@@ -112,42 +126,44 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
 
     // this CTA's share of the super-blocks
-    const uint32_t per = (nb + CL - 1) / CL, bi_begin = min(nb, crank * per), bi_end = min(nb, bi_begin + per);
+    const uint32_t n_chunks = p.k >> 8;  // 256 weights per chunk: a K-quant super-block, or eight Q4_0 blocks
+    const uint32_t per = (n_chunks + CL - 1) / CL, bi_begin = min(n_chunks, crank * per), bi_end = min(n_chunks, bi_begin + per);
     for (uint32_t bi = bi_begin; bi < bi_end; ++bi) {
         // ---- stage the chunk: weights of 64 rows, activations of 128 columns (rows / columns past the
         // edge are clamped to the last valid one; their results are never stored)
         for (int i = tid; i < GM_BM * 8; i += GM_THREADS) {
             const int r = i >> 3, pc = i & 7;
-            const uint32_t row = min(row0 + r, p.m - 1);
+            const uint32_t row = min(wrow0 + r, w_last);
             const uint8_t *src = p.w.q + (size_t)row * nb * ti.q_b + q_piece_off(p.w.t128, 4, bi * 8 + pc);
             cpa16(wq + r * GM_WQ_STRIDE + pc * 16, src);
         }
         if (T == CERA_TYPE_Q6_K) {
             for (int i = tid; i < GM_BM * 4; i += GM_THREADS) {
                 const int r = i >> 2, pc = i & 3;
-                const uint32_t row = min(row0 + r, p.m - 1);
+                const uint32_t row = min(wrow0 + r, w_last);
                 cpa16(wqh + r * GM_WH_STRIDE + pc * 16, p.w.qh + ((size_t)row * nb + bi) * 64 + pc * 16);
             }
         }
         if (T == CERA_TYPE_Q5_K) {  // fifth bits: 32 bytes per row, bit s of byte l belongs to element l of sub-block s
             for (int i = tid; i < GM_BM * 2; i += GM_THREADS) {
                 const int r = i >> 1, pc = i & 1;
-                const uint32_t row = min(row0 + r, p.m - 1);
+                const uint32_t row = min(wrow0 + r, w_last);
                 cpa16(wqh + r * GM_WH_STRIDE + pc * 16, p.w.qh + ((size_t)row * nb + bi) * 32 + pc * 16);
             }
         }
         for (int r = tid; r < GM_BM; r += GM_THREADS) {
-            const uint32_t row = min(row0 + r, p.m - 1);
-            cpa16(whd + r * 16, p.w.hdr + ((size_t)row * nb + bi) * 16);
+            const uint32_t row = min(wrow0 + r, w_last);
+            if (T == CERA_TYPE_Q4_0) cpa16(whd + r * 16, p.w.hdr + ((size_t)row * nb + bi * 8) * 2);  // eight f16 block scales
+            else cpa16(whd + r * 16, p.w.hdr + ((size_t)row * nb + bi) * 16);
         }
         for (int i = tid; i < GM_BN * 16; i += GM_THREADS) {
             const int c = i >> 4, pc = i & 15;
-            const uint32_t col = min(col0 + c, p.n - 1);
+            const uint32_t col = min(col0 + c, n_cols - 1);
             cpa16(aq + c * GM_AQ_STRIDE + pc * 16, p.x.quants + (size_t)col * p.k + (size_t)bi * 256 + pc * 16);
         }
         for (int i = tid; i < GM_BN * 8; i += GM_THREADS) {
             const int c = i % GM_BN, s = i / GM_BN;
-            const uint32_t col = min(col0 + c, p.n - 1);
+            const uint32_t col = min(col0 + c, n_cols - 1);
             const float xs = p.x.scales[(size_t)col * nb32 + bi * 8 + s];
             const int16_t *sm = p.x.sums + (size_t)col * nb16 + (bi * 8 + s) * 2;
             axs[s * GM_BN + c] = xs;
@@ -161,7 +177,15 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
         cpa_wait_all();
         __syncthreads();
         // ---- expand the sub-block scales of the 64 rows to f32
-        if (T != CERA_TYPE_Q6_K) {
+        if (T == CERA_TYPE_Q4_0) {
+            // w = (q - 8) * d: the -8 is the "min" term with 8*d in the place of dmin*mn (cera/src/backend/simd.rs:5303-5314)
+            for (int i = tid; i < GM_BM * 8; i += GM_THREADS) {
+                const int r = i >> 3, s = i & 7;
+                const float d = h2f(reinterpret_cast<const uint16_t *>(whd + r * 16)[s]);
+                wsc[r * 16 + s] = d;
+                wmn[r * 8 + s] = 8.0f * d;
+            }
+        } else if (T != CERA_TYPE_Q6_K) {
             for (int i = tid; i < GM_BM * 8; i += GM_THREADS) {
                 const int r = i >> 3, s = i & 7;
                 const uint8_t *h = whd + r * 16;
@@ -174,7 +198,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
         } else {
             for (int i = tid; i < GM_BM * 16; i += GM_THREADS) {
                 const int r = i >> 4, e = i & 15;
-                const uint32_t row = min(row0 + r, p.m - 1);
+                const uint32_t row = min(wrow0 + r, w_last);
                 const float d = h2f(reinterpret_cast<const uint16_t *>(p.w.d)[(size_t)row * nb + bi]);
                 wsc[r * 16 + e] = d * (float)(int8_t)whd[r * 16 + e];
             }
@@ -183,7 +207,32 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
 
         // ---- tensor-core work of this chunk
         const uint8_t *qa = wq + (wrow + gid) * GM_WQ_STRIDE, *qb = qa + 8 * GM_WQ_STRIDE;
-        if (T != CERA_TYPE_Q6_K) {
+        if (T == CERA_TYPE_Q4_0) {
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                // block s = bytes [16s, 16s+16): low nibble of byte i = element i, high nibble = element i + 16
+                const uint32_t wa = *reinterpret_cast<const uint32_t *>(qa + 16 * s + 4 * tig);
+                const uint32_t wb = *reinterpret_cast<const uint32_t *>(qb + 16 * s + 4 * tig);
+                const uint32_t a[4] = {wa & 0x0F0F0F0Fu, wb & 0x0F0F0F0Fu, (wa >> 4) & 0x0F0F0F0Fu, (wb >> 4) & 0x0F0F0F0Fu};
+                const float sca = wsc[(wrow + gid) * 16 + s], scb = wsc[(wrow + gid + 8) * 16 + s];
+                const float mna = wmn[(wrow + gid) * 8 + s], mnb = wmn[(wrow + gid + 8) * 8 + s];
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const int cb = wcol + 8 * j;
+                    const uint8_t *bp = aq + (cb + gid) * GM_AQ_STRIDE + 32 * s + 4 * tig;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp);
+                    const uint32_t b1 = *reinterpret_cast<const uint32_t *>(bp + 16);
+                    int c[4];
+                    mma_u8s8_k32(c, a, b0, b1);
+                    const float2 xs = *reinterpret_cast<const float2 *>(axs + s * GM_BN + cb + 2 * tig);
+                    const float2 xb = *reinterpret_cast<const float2 *>(axb + s * GM_BN + cb + 2 * tig);
+                    acc[j][0] = fmaf(sca * xs.x, (float)c[0], fmaf(-mna, xb.x, acc[j][0]));
+                    acc[j][1] = fmaf(sca * xs.y, (float)c[1], fmaf(-mna, xb.y, acc[j][1]));
+                    acc[j][2] = fmaf(scb * xs.x, (float)c[2], fmaf(-mnb, xb.x, acc[j][2]));
+                    acc[j][3] = fmaf(scb * xs.y, (float)c[3], fmaf(-mnb, xb.y, acc[j][3]));
+                }
+            }
+        } else if (T != CERA_TYPE_Q6_K) {
             const uint8_t *h5a = wqh + (wrow + gid) * GM_WH_STRIDE, *h5b = h5a + 8 * GM_WH_STRIDE;
             uint32_t ha0 = 0, ha1 = 0, hb0 = 0, hb1 = 0;
             if (T == CERA_TYPE_Q5_K) {
@@ -268,7 +317,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
             for (int i = 0; i < 4; ++i) {
                 const uint32_t row = row0 + wrow + gid + (i >= 2 ? 8 : 0);
                 const uint32_t col = col0 + wcol + 8 * j + 2 * tig + (i & 1);
-                if (row < p.m && col < p.n) {
+                if (row < p.m && col < n_cols) {
                     float *y = p.out + (size_t)row * p.ldy + (size_t)col * p.ldc;
                     *y = p.epilogue == EPI_ADD ? __fadd_rn(*y, acc[j][i]) : acc[j][i];
                 }
@@ -288,7 +337,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
         float v = 0.0f;
         for (uint32_t q = 0; q < CL; ++q) v += cluster.map_shared_rank(tile, q)[r * GM_BN + c];
         const uint32_t row = row0 + r, col = col0 + c;
-        if (row < p.m && col < p.n) {
+        if (row < p.m && col < n_cols) {
             float *y = p.out + (size_t)row * p.ldy + (size_t)col * p.ldc;
             *y = p.epilogue == EPI_ADD ? __fadd_rn(*y, v) : v;
         }
@@ -296,8 +345,13 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
     cluster.sync();  // peers may still be reading this CTA's partial tile
 }
 
+inline bool mma_type(int t) {
+    return t == CERA_TYPE_Q4_0 || t == CERA_TYPE_Q4_K || t == CERA_TYPE_Q5_K || t == CERA_TYPE_Q6_K;
+}
+
+// grid_x / grid_y given: the expert-grouped form (row tiles of one expert x work items); else derived from m and n.
 template <int T, int BN>
-int32_t launch_mma_bn(const GemmParams &p, uint32_t cl, cudaStream_t st) {
+int32_t launch_mma_bn(const GemmParams &p, uint32_t cl, cudaStream_t st, uint32_t grid_x = 0, uint32_t grid_y = 0) {
     constexpr size_t smem = gm_smem_bytes<BN>();
     static thread_local int configured_dev = -1;
     int dev = 0;
@@ -307,7 +361,7 @@ int32_t launch_mma_bn(const GemmParams &p, uint32_t cl, cudaStream_t st) {
         configured_dev = dev;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(((p.m + GM_BM - 1) / GM_BM) * cl, (p.n + BN - 1) / BN);
+    cfg.gridDim = grid_x ? dim3(grid_x * cl, grid_y) : dim3(((p.m + GM_BM - 1) / GM_BM) * cl, (p.n + BN - 1) / BN);
     cfg.blockDim = dim3(GM_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -333,7 +387,7 @@ int32_t launch_mma_typed(const GemmParams &p, cudaStream_t st) {
     const uint32_t tiles = ((p.m + GM_BM - 1) / GM_BM) * ((p.n + bn - 1) / bn);
     const uint32_t want = (uint32_t)sm_count() * (bn >= 128 ? 1u : bn == 64 ? 2u : 4u);
     uint32_t cl = 1;
-    while (cl < 8 && tiles * cl < want && p.w.nb / (cl * 2) >= 2) cl *= 2;
+    while (cl < 8 && tiles * cl < want && (p.k >> 8) / (cl * 2) >= 2) cl *= 2;
     switch (bn) {
         case 128: return launch_mma_bn<T, 128>(p, cl, st);
         case 64: return launch_mma_bn<T, 64>(p, cl, st);
@@ -352,7 +406,7 @@ int32_t launch_gemm_mma(const WeightView &w, const ActView &x, size_t n, float *
         const char *e = getenv("CERA_CUDA_GEMM");
         return e && strcmp(e, "columns") == 0;
     }();
-    if (off || n < 5 || (w.type != CERA_TYPE_Q4_K && w.type != CERA_TYPE_Q5_K && w.type != CERA_TYPE_Q6_K) || w.k % 256) return CERA_CUDA_OK;
+    if (off || n < 5 || !mma_type(w.type) || w.k % 256) return CERA_CUDA_OK;
     if ((uintptr_t)x.quants % 16 || w.k % 16) return CERA_CUDA_OK;
     GemmParams p{};
     p.w = w;
@@ -365,9 +419,37 @@ int32_t launch_gemm_mma(const WeightView &w, const ActView &x, size_t n, float *
     p.ldc = (uint32_t)ldc;
     p.epilogue = epilogue;
     *taken = true;
+    if (w.type == CERA_TYPE_Q4_0) return launch_mma_typed<CERA_TYPE_Q4_0>(p, st);
     if (w.type == CERA_TYPE_Q4_K) return launch_mma_typed<CERA_TYPE_Q4_K>(p, st);
     if (w.type == CERA_TYPE_Q5_K) return launch_mma_typed<CERA_TYPE_Q5_K>(p, st);
     return launch_mma_typed<CERA_TYPE_Q6_K>(p, st);
+}
+
+bool gemm_mma_supports(int type, size_t k) { return mma_type(type) && k % 256 == 0; }
+
+// Expert-grouped form: one 64-column tile per work item of a device-side list (see ops.h).
+int32_t launch_gemm_mma_grouped(const WeightView &w, const ActView &x, const MoeTile *tiles, const uint32_t *n_tiles,
+                                uint32_t max_tiles, uint32_t rows_per_expert, float *out, size_t ldc, cudaStream_t st, bool *taken) {
+    *taken = false;
+    if (!mma_type(w.type) || w.k % 256 || (uintptr_t)x.quants % 16 || max_tiles == 0) return CERA_CUDA_OK;
+    GemmParams p{};
+    p.w = w;
+    p.x = x;
+    p.out = out;
+    p.m = rows_per_expert;
+    p.n = 0;
+    p.k = w.k;
+    p.ldy = 1;
+    p.ldc = (uint32_t)ldc;
+    p.epilogue = EPI_STORE;
+    p.tiles = tiles;
+    p.n_tiles = n_tiles;
+    *taken = true;
+    const uint32_t row_tiles = (rows_per_expert + GM_BM - 1) / GM_BM;
+    if (w.type == CERA_TYPE_Q4_0) return launch_mma_bn<CERA_TYPE_Q4_0, 64>(p, 1, st, row_tiles, max_tiles);
+    if (w.type == CERA_TYPE_Q4_K) return launch_mma_bn<CERA_TYPE_Q4_K, 64>(p, 1, st, row_tiles, max_tiles);
+    if (w.type == CERA_TYPE_Q5_K) return launch_mma_bn<CERA_TYPE_Q5_K, 64>(p, 1, st, row_tiles, max_tiles);
+    return launch_mma_bn<CERA_TYPE_Q6_K, 64>(p, 1, st, row_tiles, max_tiles);
 }
 
 }  // namespace cera

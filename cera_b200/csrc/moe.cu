@@ -11,7 +11,8 @@
 // Here the (token, pick) pairs of the whole batch are bucketed by expert (counting sort on the
 // device), the Q8_0 columns are gathered into bucket order, and one launch per projection walks a
 // device-built list of (expert, column tile) work items: each expert's weights are streamed once per
-// eight of its tokens instead of once per token.  The stacked expert tensors
+// eight of its tokens instead of once per token -- or, for batches, once per 64 of its tokens through the
+// tensor-core GEMM of gemm_mma.cu in its expert-grouped form.  The stacked expert tensors
 // (blk.N.ffn_{gate,up,down}_exps.weight, [n_expert][m][k] with expert stride m rows,
 // cera/src/model/gpu_weight_source.rs:179-257) are one weight matrix of n_expert*m rows here.
 //
@@ -43,9 +44,7 @@ constexpr int MOE_MAX_USED = 16;
 constexpr int MOE_NC = 8;             // token columns per work item
 constexpr int MOE_WARPS = 8;
 
-struct MoeTile {
-    uint32_t expert, first, count;  // entries [first, first + count) of the bucket order, count <= MOE_NC
-};
+constexpr int MOE_NC_MMA = 64;        // ... when the projections run on the tensor-core GEMM
 
 // ---- routing -------------------------------------------------------------------------------------
 // One CTA per token.  Warps take experts round-robin; lane-strided f32 dot, shuffle tree.
@@ -304,6 +303,29 @@ int32_t launch_moe_gemm(const MoeGemmParams &p, uint32_t max_tiles, bool single,
     return check_cuda(cudaGetLastError(), "moe grouped gemm launch");
 }
 
+// CERA_CUDA_MOE=dp4a keeps the grouped projections on the dp4a kernel (A/B runs); read once.
+bool moe_force_dp4a() {
+    static const bool v = [] {
+        const char *e = getenv("CERA_CUDA_MOE");
+        return e && strcmp(e, "dp4a") == 0;
+    }();
+    return v;
+}
+
+// One grouped projection over the work list: the tensor-core GEMM when the plan was made for it, else the dp4a kernel.
+int32_t grouped_projection(bool mma, const MoeGemmParams &p, uint32_t max_tiles, bool single, cudaStream_t st) {
+    if (mma) {
+        for (int s = 0; s < p.n_segs; ++s) {
+            bool taken = false;
+            CERA_TRY(launch_gemm_mma_grouped(p.w[s], p.x, p.tiles, p.n_tiles, max_tiles, p.m, p.y[s], p.ldc, st, &taken));
+            if (!taken) return fail(CERA_CUDA_ERR_STATE, "moe: tensor-core plan without a tensor-core kernel");
+        }
+        return CERA_CUDA_OK;
+    }
+    CERA_DISPATCH_BLOCK_TYPE(p.w[0].type, return (launch_moe_gemm<TT>(p, max_tiles, single, st)));
+    return CERA_CUDA_OK;
+}
+
 }  // namespace
 
 struct cera_cuda_moe {
@@ -466,7 +488,9 @@ int32_t moe_ffn_ep(cera_cuda_moe *h, const float *x_dev, size_t n, int32_t softm
     if (!h->connected) return fail(CERA_CUDA_ERR_STATE, "moe_ffn: expert-parallel layer is not connected to its peers");
     const uint32_t hs = h->hidden, ff = h->ff, ku = h->n_used, E = h->n_expert;
     const size_t entries = n * ku, rmax = h->max_total * ku;
-    const uint32_t max_tiles = (uint32_t)(rmax / MOE_NC + E / h->ep_size);
+    const bool mma = gemm_mma_supports(h->gate->v.type, hs) && gemm_mma_supports(h->down->v.type, ff) && !moe_force_dp4a();
+    const uint32_t nc = mma ? MOE_NC_MMA : MOE_NC;
+    const uint32_t max_tiles = (uint32_t)(rmax / nc + E / h->ep_size);
     uint32_t *counts_mine = (uint32_t *)(h->region + h->lay.counts) + (size_t)h->ep_rank * E;
     uint32_t *n_recv = h->ep_words + 32;
     CERA_TRY(launch_tp_tick(h->ep_words, st));
@@ -478,7 +502,7 @@ int32_t moe_ffn_ep(cera_cuda_moe *h, const float *x_dev, size_t n, int32_t softm
     // all ranks learn all counts
     const TpRange cr{(uint32_t)((char *)counts_mine - h->region), E * 4};
     CERA_TRY(launch_tp_exchange(h->ep, &cr, 1, 0, st));
-    moe_ep_plan_kernel<<<1, 32, 0, st>>>(h->ep, h->lay, E, MOE_NC, h->my_base, h->cursor, h->tiles, h->n_tiles, n_recv);
+    moe_ep_plan_kernel<<<1, 32, 0, st>>>(h->ep, h->lay, E, nc, h->my_base, h->cursor, h->tiles, h->n_tiles, n_recv);
     if (n)
         moe_ep_dispatch_kernel<<<(unsigned)entries, 128, 0, st>>>(h->ep, h->lay, h->ids, ku, hs, E, ActView{h->xs, h->xq, h->xsum},
                                                                    h->my_base, h->cursor);
@@ -498,7 +522,7 @@ int32_t moe_ffn_ep(cera_cuda_moe *h, const float *x_dev, size_t n, int32_t softm
     p.ldc = ff;
     p.tiles = h->tiles;
     p.n_tiles = h->n_tiles;
-    CERA_DISPATCH_BLOCK_TYPE(h->gate->v.type, CERA_TRY(launch_moe_gemm<TT>(p, max_tiles, false, st)));
+    CERA_TRY(grouped_projection(mma, p, max_tiles, false, st));
     const size_t worst = rmax * ff;
     moe_silu_q8_kernel<<<(unsigned)((worst + 255) / 256), 256, 0, st>>>(h->g, h->u, ff, n_recv, h->f_scales, h->f_quants, h->f_sums);
     count_launch();
@@ -512,7 +536,7 @@ int32_t moe_ffn_ep(cera_cuda_moe *h, const float *x_dev, size_t n, int32_t softm
     d.ldc = hs;
     d.tiles = h->tiles;
     d.n_tiles = h->n_tiles;
-    CERA_DISPATCH_BLOCK_TYPE(h->down->v.type, CERA_TRY(launch_moe_gemm<TT>(d, max_tiles, false, st)));
+    CERA_TRY(grouped_projection(mma, d, max_tiles, false, st));
     moe_ep_return_kernel<<<(unsigned)rmax, 128, 0, st>>>(h->ep, h->lay, h->expert_out, hs, n_recv);
     count_launch();
     CERA_CUDA_TRY(cudaGetLastError());
@@ -597,7 +621,9 @@ int32_t cera_cuda_moe_ffn(cera_cuda_moe *h, const float *x_dev, size_t n, int32_
     const uint32_t hs = h->hidden, ff = h->ff, ku = h->n_used;
     const size_t entries = n * ku;
     const bool single = n == 1;
-    const uint32_t nc = single ? 1 : MOE_NC;
+    // a handful of tokens: dp4a work items of 8 columns (1 for a single token); a batch: tensor-core items of 64
+    const bool mma = n >= 16 && gemm_mma_supports(h->gate->v.type, hs) && gemm_mma_supports(h->down->v.type, ff) && !moe_force_dp4a();
+    const uint32_t nc = single ? 1 : mma ? MOE_NC_MMA : MOE_NC;
     const uint32_t max_tiles = (uint32_t)(entries / nc + (single ? 0 : h->n_expert));
     CERA_TRY(launch_quantize(x_dev, hs, n, false, h->xs, h->xq, h->xsum, st));
     moe_route_kernel<<<(unsigned)n, 256, 0, st>>>(x_dev, h->router, h->bias, hs, h->n_expert, ku, softmax_gate, h->ids, h->weights,
@@ -619,7 +645,7 @@ int32_t cera_cuda_moe_ffn(cera_cuda_moe *h, const float *x_dev, size_t n, int32_
     p.ldc = ff;
     p.tiles = h->tiles;
     p.n_tiles = h->n_tiles;
-    CERA_DISPATCH_BLOCK_TYPE(h->gate->v.type, CERA_TRY(launch_moe_gemm<TT>(p, max_tiles, single, st)));
+    CERA_TRY(grouped_projection(mma, p, max_tiles, single, st));
     CERA_TRY(launch_silu_mul(h->g, h->u, ff, entries, h->f_scales, h->f_quants, h->f_sums, st));
     MoeGemmParams d{};
     d.w[0] = h->down->v;
@@ -631,7 +657,7 @@ int32_t cera_cuda_moe_ffn(cera_cuda_moe *h, const float *x_dev, size_t n, int32_
     d.ldc = hs;
     d.tiles = h->tiles;
     d.n_tiles = h->n_tiles;
-    CERA_DISPATCH_BLOCK_TYPE(h->down->v.type, CERA_TRY(launch_moe_gemm<TT>(d, max_tiles, single, st)));
+    CERA_TRY(grouped_projection(mma, d, max_tiles, single, st));
     const size_t total = n * hs;
     moe_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(h->expert_out, h->entry_of, h->weights, ku, hs, n, out_dev);
     count_launch();

@@ -160,11 +160,11 @@ def test_gemm_preq_matches_oracle(t, n):
     assert_close(got, want, f"{O.NAMES[t]} n={n}")
 
 
-@pytest.mark.parametrize("t", [O.Q4_K, O.Q6_K, O.Q5_K])
+@pytest.mark.parametrize("t", [O.Q4_K, O.Q6_K, O.Q5_K, O.Q4_0])
 @pytest.mark.parametrize("m,n,k", [(70, 130, 1024), (64, 128, 512), (200, 16, 768), (3, 64, 4096), (130, 5, 2048),
                                    (96, 8, 4096), (65, 33, 3072), (256, 100, 1024), (40, 17, 14336)])
 def test_gemm_tensor_core_shapes(t, m, n, k):
-    """n >= 5: the K-quants take the mma.sync int8 kernel (every column-tile width, ragged tiles, and the k range
+    """n >= 5 and k a multiple of 256: the K-quants and Q4_0 take the mma.sync int8 kernel (every column-tile width, ragged tiles, and the k range
     split over clusters of 2, 4 and 8 CTAs)."""
     torch = need_gpu()
     import cera_b200 as cb

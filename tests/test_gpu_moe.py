@@ -36,10 +36,11 @@ def _reference(t, layer, n_used, hidden, ff, x, bias, softmax_gate):
         margins.append(float(np.min(np.abs(np.diff(biased[:n_used + 1])))))
         acc = np.zeros(hidden, dtype=np.float32)
         for e, we in zip(sel, w):
-            g = O.gemv(t, gate[e * gb:(e + 1) * gb], xj, ff, hidden)
-            u = O.gemv(t, up[e * gb:(e + 1) * gb], xj, ff, hidden)
+            fast = O.has_avx2() and t != O.Q5_K  # bit-identical to the scalar restatement (tested), only faster
+            g = O.gemv(t, gate[e * gb:(e + 1) * gb], xj, ff, hidden, avx2=fast, threads=4)
+            u = O.gemv(t, up[e * gb:(e + 1) * gb], xj, ff, hidden, avx2=fast, threads=4)
             h = O.silu_mul(g, u)
-            y = O.gemv(t, down[e * db:(e + 1) * db], h, hidden, ff)
+            y = O.gemv(t, down[e * db:(e + 1) * db], h, hidden, ff, avx2=fast, threads=4)
             acc = (acc + (np.float32(we) * y).astype(np.float32)).astype(np.float32)
         out[j] = acc
         ids.append(list(sel))
@@ -89,6 +90,15 @@ def test_routed_ffn_k_quants(t_name):
     need_gpu()
     import cera_b200 as cb
     _run(getattr(cb, t_name), n_expert=6, n_used=3, hidden=512, ff=256, n=19, seed=33)
+
+
+@pytest.mark.parametrize("t_name,n", [("Q4_0", 96), ("Q4_K", 150), ("Q6_K", 70), ("Q5_K", 40)])
+def test_routed_ffn_batches_on_the_tensor_core_path(t_name, n):
+    """16 tokens and more with 256-aligned widths: 64-column work items through the expert-grouped tensor-core GEMM,
+    ragged per-expert counts included."""
+    need_gpu()
+    import cera_b200 as cb
+    _run(getattr(cb, t_name), n_expert=8, n_used=2, hidden=512, ff=256, n=n, seed=61)
 
 
 def test_selection_bias_steers_rank_not_weight():
