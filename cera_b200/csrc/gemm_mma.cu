@@ -380,7 +380,14 @@ int32_t launch_mma_bn(const GemmParams &p, uint32_t cl, cudaStream_t st, uint32_
 
 template <int T>
 int32_t launch_mma_typed(const GemmParams &p, cudaStream_t st) {
-    const uint32_t bn = p.n > 64 ? 128 : p.n > 32 ? 64 : p.n > 16 ? 32 : 16;
+    // CERA_CUDA_GEMM_BN=64 caps the column-tile width (A/B runs: narrower tiles trade operand reuse for occupancy)
+    static const uint32_t bn_cap = [] {
+        const char *e = getenv("CERA_CUDA_GEMM_BN");
+        const long v = e ? atol(e) : 0;
+        return (uint32_t)(v == 16 || v == 32 || v == 64 ? v : 128);
+    }();
+    uint32_t bn = p.n > 64 ? 128 : p.n > 32 ? 64 : p.n > 16 ? 32 : 16;
+    if (bn > bn_cap) bn = bn_cap;
     // Split k over a cluster until the grid covers the machine once (wide tiles: a CTA's chunk is compute-heavy and a
     // split only adds the reduction), twice (64 columns) or four times (narrow tiles: a chunk is mostly load latency),
     // keeping at least two super-blocks per CTA.
