@@ -183,10 +183,12 @@ def reference_arm(args, rank):
     sample = "per step: the 7 projection GEMVs of one layer + the LM-head GEMV, token = 32 layers + head"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": len(vals),
-        "warmup": args.warmup, "ms_per_step": 1000.0 / v, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": 1000.0 / v, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak",
         "vs_baseline": None, "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
-        "config": {"workload": "Llama-3-8B-shape decode token, Q4_K/Q6_K weights x Q8_0 activations, CPU int8 GEMV path",
-                   "prompt_len": PROMPT_LEN},
+        "config": {"workload": "Llama-3-8B-shape random-init model (32 layers, 4096/14336, 32/8 heads, vocab 128256; "
+                               "Q4_K attn/gate/up/embd, Q6_K down/output), 512-token prompt then greedy decode",
+                   "prompt_len": PROMPT_LEN, "parallelism": "host cores only: the CPU int8 GEMV path of the same decode token"},
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
