@@ -466,8 +466,8 @@ def cuda_arm(args, rank, world):
                          "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "peak_source": which,
                          "frac_of_nominal_8000": achieved / 8000.0, "us_per_launch": us, "algorithmic_bytes": algo,
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this shape, from
-                         # the ncu capture summarised in profiles/gemv_rows_q4k_14336x4096.md (not re-measured per run)
-                         "traffic": 33.05e6 + 0.06e6, "traffic_source": "ncu capture, profiles/gemv_rows_q4k_14336x4096.md"},
+                         # a separate ncu capture of this kernel at this shape (a profiler cannot run inside the timed bench)
+                         "traffic": 33.05e6 + 0.06e6, "traffic_source": "ncu capture of one launch of this kernel at this shape"},
             "step_roofline": {"bound": "hbm", "weight_bytes_per_token": TOKEN_WEIGHT_BYTES, "achieved": step_gbs,
                               "peak": hbm * world, "unit": "GB/s", "frac": step_gbs / (hbm * world),
                               "roofline_tok_s_at_peak": hbm * world * 1e9 / TOKEN_WEIGHT_BYTES},
