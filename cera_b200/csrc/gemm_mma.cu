@@ -436,7 +436,8 @@ bool gemm_mma_supports(int type, size_t k) { return mma_type(type) && k % 256 ==
 
 // Expert-grouped form: one 64-column tile per work item of a device-side list (see ops.h).
 int32_t launch_gemm_mma_grouped(const WeightView &w, const ActView &x, const MoeTile *tiles, const uint32_t *n_tiles,
-                                uint32_t max_tiles, uint32_t rows_per_expert, float *out, size_t ldc, cudaStream_t st, bool *taken) {
+                                uint32_t max_tiles, uint32_t rows_per_expert, float *out, size_t ldc, uint32_t bn, cudaStream_t st,
+                                bool *taken) {
     *taken = false;
     if (!mma_type(w.type) || w.k % 256 || (uintptr_t)x.quants % 16 || max_tiles == 0) return CERA_CUDA_OK;
     GemmParams p{};
@@ -453,10 +454,13 @@ int32_t launch_gemm_mma_grouped(const WeightView &w, const ActView &x, const Moe
     p.n_tiles = n_tiles;
     *taken = true;
     const uint32_t row_tiles = (rows_per_expert + GM_BM - 1) / GM_BM;
-    if (w.type == CERA_TYPE_Q4_0) return launch_mma_bn<CERA_TYPE_Q4_0, 64>(p, 1, st, row_tiles, max_tiles);
-    if (w.type == CERA_TYPE_Q4_K) return launch_mma_bn<CERA_TYPE_Q4_K, 64>(p, 1, st, row_tiles, max_tiles);
-    if (w.type == CERA_TYPE_Q5_K) return launch_mma_bn<CERA_TYPE_Q5_K, 64>(p, 1, st, row_tiles, max_tiles);
-    return launch_mma_bn<CERA_TYPE_Q6_K, 64>(p, 1, st, row_tiles, max_tiles);
+#define CERA_GROUPED(TT)                                                                     \
+    return bn == 32 ? launch_mma_bn<TT, 32>(p, 1, st, row_tiles, max_tiles) : launch_mma_bn<TT, 64>(p, 1, st, row_tiles, max_tiles)
+    if (w.type == CERA_TYPE_Q4_0) CERA_GROUPED(CERA_TYPE_Q4_0);
+    if (w.type == CERA_TYPE_Q4_K) CERA_GROUPED(CERA_TYPE_Q4_K);
+    if (w.type == CERA_TYPE_Q5_K) CERA_GROUPED(CERA_TYPE_Q5_K);
+    CERA_GROUPED(CERA_TYPE_Q6_K);
+#undef CERA_GROUPED
 }
 
 }  // namespace cera

@@ -106,19 +106,33 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict_
     }
 }
 
-// One CTA: bucket offsets, cursors, and the work list.  counts is zeroed again for the next call.
-__global__ void moe_plan_kernel(uint32_t *counts, uint32_t n_expert, uint32_t nc, uint32_t *cursor, MoeTile *tiles,
-                                uint32_t *n_tiles) {
+// Appends the work items of one expert's `c` entries starting at bucket offset `off`: items of `nc` columns go to
+// the main list; a last item of at most `small_nc` columns (0 = no such list) goes to the list of narrow items at
+// tiles[cap...], which a narrower kernel serves.
+__device__ __forceinline__ void moe_emit_items(MoeTile *tiles, uint32_t cap, uint32_t &t, uint32_t &ts, uint32_t e, uint32_t off,
+                                               uint32_t c, uint32_t nc, uint32_t small_nc) {
+    for (uint32_t f = 0; f < c; f += nc) {
+        const uint32_t n = c - f < nc ? c - f : nc;
+        if (small_nc && n <= small_nc) tiles[cap + ts++] = MoeTile{e, off + f, n};
+        else tiles[t++] = MoeTile{e, off + f, n};
+    }
+}
+
+// One CTA: bucket offsets, cursors, and the work lists (n_tiles[0] main, n_tiles[1] narrow).  counts is zeroed again
+// for the next call.
+__global__ void moe_plan_kernel(uint32_t *counts, uint32_t n_expert, uint32_t nc, uint32_t small_nc, uint32_t cap, uint32_t *cursor,
+                                MoeTile *tiles, uint32_t *n_tiles) {
     if (threadIdx.x != 0) return;
-    uint32_t off = 0, t = 0;
+    uint32_t off = 0, t = 0, ts = 0;
     for (uint32_t e = 0; e < n_expert; ++e) {
         const uint32_t c = counts[e];
         cursor[e] = off;
-        for (uint32_t f = 0; f < c; f += nc) tiles[t++] = MoeTile{e, off + f, c - f < nc ? c - f : nc};
+        moe_emit_items(tiles, cap, t, ts, e, off, c, nc, small_nc);
         off += c;
         counts[e] = 0;
     }
-    *n_tiles = t;
+    n_tiles[0] = t;
+    n_tiles[1] = ts;
 }
 
 // One CTA per (token, pick): take the next place in the expert's bucket and copy the token's Q8_0 column there.
@@ -213,12 +227,12 @@ struct EpLayout {  // byte offsets inside every rank's exchange region
 // One CTA.  counts_all[G][E] (every rank's per-expert entry counts) -> my_base[e] = first slot, in the
 // receive buffer of e's owner, of this rank's entries for expert e; the work list over what THIS rank
 // receives for its local experts; *n_recv.  Zeroes this rank's own count row for the next call.
-__global__ void moe_ep_plan_kernel(TpCtx c, EpLayout lay, uint32_t n_expert, uint32_t nc, uint32_t *my_base, uint32_t *cursor,
-                                   MoeTile *tiles, uint32_t *n_tiles, uint32_t *n_recv) {
+__global__ void moe_ep_plan_kernel(TpCtx c, EpLayout lay, uint32_t n_expert, uint32_t nc, uint32_t small_nc, uint32_t cap,
+                                   uint32_t *my_base, uint32_t *cursor, MoeTile *tiles, uint32_t *n_tiles, uint32_t *n_recv) {
     if (threadIdx.x != 0) return;
     uint32_t *counts = (uint32_t *)(c.peer[c.rank] + lay.counts);
     const uint32_t per = n_expert / c.size;
-    uint32_t t = 0;
+    uint32_t t = 0, ts = 0;
     for (uint32_t d = 0; d < c.size; ++d) {
         uint32_t off = 0;  // running slot in rank d's receive buffer
         for (uint32_t e = d * per; e < (d + 1) * per; ++e) {
@@ -230,13 +244,13 @@ __global__ void moe_ep_plan_kernel(TpCtx c, EpLayout lay, uint32_t n_expert, uin
             }
             my_base[e] = off + before_me;
             cursor[e] = 0;
-            if (d == c.rank)
-                for (uint32_t f = 0; f < tot; f += nc) tiles[t++] = MoeTile{e - d * per, off + f, tot - f < nc ? tot - f : nc};
+            if (d == c.rank) moe_emit_items(tiles, cap, t, ts, e - d * per, off, tot, nc, small_nc);
             off += tot;
         }
         if (d == c.rank) *n_recv = off;
     }
-    *n_tiles = t;
+    n_tiles[0] = t;
+    n_tiles[1] = ts;
     for (uint32_t e = 0; e < n_expert; ++e) counts[c.rank * n_expert + e] = 0;
 }
 
@@ -313,12 +327,17 @@ bool moe_force_dp4a() {
 }
 
 // One grouped projection over the work list: the tensor-core GEMM when the plan was made for it, else the dp4a kernel.
-int32_t grouped_projection(bool mma, const MoeGemmParams &p, uint32_t max_tiles, bool single, cudaStream_t st) {
+// cap / max_small: where the list of narrow items starts inside p.tiles and how many it can hold (tensor-core plan only).
+int32_t grouped_projection(bool mma, const MoeGemmParams &p, uint32_t max_tiles, uint32_t cap, uint32_t max_small, bool single,
+                           cudaStream_t st) {
     if (mma) {
         for (int s = 0; s < p.n_segs; ++s) {
             bool taken = false;
-            CERA_TRY(launch_gemm_mma_grouped(p.w[s], p.x, p.tiles, p.n_tiles, max_tiles, p.m, p.y[s], p.ldc, st, &taken));
+            CERA_TRY(launch_gemm_mma_grouped(p.w[s], p.x, p.tiles, p.n_tiles, max_tiles, p.m, p.y[s], p.ldc, MOE_NC_MMA, st, &taken));
             if (!taken) return fail(CERA_CUDA_ERR_STATE, "moe: tensor-core plan without a tensor-core kernel");
+            // an expert's last, at most half-filled item runs on the 32-column kernel
+            CERA_TRY(launch_gemm_mma_grouped(p.w[s], p.x, p.tiles + cap, p.n_tiles + 1, max_small, p.m, p.y[s], p.ldc, MOE_NC_MMA / 2, st,
+                                             &taken));
         }
         return CERA_CUDA_OK;
     }
@@ -410,7 +429,7 @@ int32_t moe_create_impl(uint32_t n_expert, uint32_t n_used, uint32_t hidden, uin
                  o_fq = take((entries + pad) * ff), o_fsum = take((entries + pad) * (ff / 16) * 2), o_w = take(entries * 4),
                  o_g = take(entries * ff * 4), o_u = take(entries * ff * 4), o_eo = take(entries * hidden * 4),
                  o_ids = take(entries * 4), o_counts = take((size_t)n_expert * 4), o_cursor = take((size_t)n_expert * 4),
-                 o_entry = take(entries * 4), o_nt = take(4), o_tiles = take((entries / 1 + n_expert) * sizeof(MoeTile)),
+                 o_entry = take(entries * 4), o_nt = take(8), o_tiles = take(2 * (entries + n_expert) * sizeof(MoeTile)),
                  o_words = take(64 * 4), o_base = take((size_t)n_expert * 4);
     h->bytes = off;
     if (st == CERA_CUDA_OK) st = check_cuda(cudaMalloc((void **)&h->base, off), "cudaMalloc(moe scratch)");
@@ -502,7 +521,9 @@ int32_t moe_ffn_ep(cera_cuda_moe *h, const float *x_dev, size_t n, int32_t softm
     // all ranks learn all counts
     const TpRange cr{(uint32_t)((char *)counts_mine - h->region), E * 4};
     CERA_TRY(launch_tp_exchange(h->ep, &cr, 1, 0, st));
-    moe_ep_plan_kernel<<<1, 32, 0, st>>>(h->ep, h->lay, E, nc, h->my_base, h->cursor, h->tiles, h->n_tiles, n_recv);
+    const uint32_t cap = (uint32_t)(rmax + E), max_small = E / h->ep_size;
+    moe_ep_plan_kernel<<<1, 32, 0, st>>>(h->ep, h->lay, E, nc, mma ? nc / 2 : 0, cap, h->my_base, h->cursor, h->tiles, h->n_tiles,
+                                         n_recv);
     if (n)
         moe_ep_dispatch_kernel<<<(unsigned)entries, 128, 0, st>>>(h->ep, h->lay, h->ids, ku, hs, E, ActView{h->xs, h->xq, h->xsum},
                                                                    h->my_base, h->cursor);
@@ -522,7 +543,7 @@ int32_t moe_ffn_ep(cera_cuda_moe *h, const float *x_dev, size_t n, int32_t softm
     p.ldc = ff;
     p.tiles = h->tiles;
     p.n_tiles = h->n_tiles;
-    CERA_TRY(grouped_projection(mma, p, max_tiles, false, st));
+    CERA_TRY(grouped_projection(mma, p, max_tiles, cap, max_small, false, st));
     const size_t worst = rmax * ff;
     moe_silu_q8_kernel<<<(unsigned)((worst + 255) / 256), 256, 0, st>>>(h->g, h->u, ff, n_recv, h->f_scales, h->f_quants, h->f_sums);
     count_launch();
@@ -536,7 +557,7 @@ int32_t moe_ffn_ep(cera_cuda_moe *h, const float *x_dev, size_t n, int32_t softm
     d.ldc = hs;
     d.tiles = h->tiles;
     d.n_tiles = h->n_tiles;
-    CERA_TRY(grouped_projection(mma, d, max_tiles, false, st));
+    CERA_TRY(grouped_projection(mma, d, max_tiles, cap, max_small, false, st));
     moe_ep_return_kernel<<<(unsigned)rmax, 128, 0, st>>>(h->ep, h->lay, h->expert_out, hs, n_recv);
     count_launch();
     CERA_CUDA_TRY(cudaGetLastError());
@@ -628,7 +649,8 @@ int32_t cera_cuda_moe_ffn(cera_cuda_moe *h, const float *x_dev, size_t n, int32_
     CERA_TRY(launch_quantize(x_dev, hs, n, false, h->xs, h->xq, h->xsum, st));
     moe_route_kernel<<<(unsigned)n, 256, 0, st>>>(x_dev, h->router, h->bias, hs, h->n_expert, ku, softmax_gate, h->ids, h->weights,
                                                   h->counts);
-    moe_plan_kernel<<<1, 32, 0, st>>>(h->counts, h->n_expert, nc, h->cursor, h->tiles, h->n_tiles);
+    const uint32_t cap = (uint32_t)(h->max_total * ku + h->n_expert), max_small = h->n_expert;
+    moe_plan_kernel<<<1, 32, 0, st>>>(h->counts, h->n_expert, nc, mma ? nc / 2 : 0, cap, h->cursor, h->tiles, h->n_tiles);
     moe_scatter_kernel<<<(unsigned)entries, 128, 0, st>>>(h->ids, ku, hs, ActView{h->xs, h->xq, h->xsum}, h->cursor, h->entry_of,
                                                           h->g_scales, h->g_quants, h->g_sums);
     count_launch(3);
@@ -645,7 +667,7 @@ int32_t cera_cuda_moe_ffn(cera_cuda_moe *h, const float *x_dev, size_t n, int32_
     p.ldc = ff;
     p.tiles = h->tiles;
     p.n_tiles = h->n_tiles;
-    CERA_TRY(grouped_projection(mma, p, max_tiles, single, st));
+    CERA_TRY(grouped_projection(mma, p, max_tiles, cap, max_small, single, st));
     CERA_TRY(launch_silu_mul(h->g, h->u, ff, entries, h->f_scales, h->f_quants, h->f_sums, st));
     MoeGemmParams d{};
     d.w[0] = h->down->v;
@@ -657,7 +679,7 @@ int32_t cera_cuda_moe_ffn(cera_cuda_moe *h, const float *x_dev, size_t n, int32_
     d.ldc = hs;
     d.tiles = h->tiles;
     d.n_tiles = h->n_tiles;
-    CERA_TRY(grouped_projection(mma, d, max_tiles, single, st));
+    CERA_TRY(grouped_projection(mma, d, max_tiles, cap, max_small, single, st));
     const size_t total = n * hs;
     moe_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(h->expert_out, h->entry_of, h->weights, ku, hs, n, out_dev);
     count_launch();

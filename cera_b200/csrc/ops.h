@@ -55,7 +55,7 @@ int32_t launch_gemv_fused(const GemvSeg *segs, int n_segs, const ActView &x, int
 int32_t launch_rope_table(const uint32_t *pos_dev, size_t head_dim, float theta_scale, const float *freq_factors,
                           float *table, cudaStream_t st);
 int32_t launch_gemm(const WeightView &w, const ActView &x, size_t n, float *out, cudaStream_t st);
-// Tensor-core (mma.sync int8) GEMM for Q4_K / Q5_K / Q6_K and n >= 5.  *taken = false: not its case.
+// Tensor-core (mma.sync int8) GEMM for Q4_0 / Q4_K / Q5_K / Q6_K (k a multiple of 256) and n >= 5.  *taken = false: not its case.
 int32_t launch_gemm_mma(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
                         cudaStream_t st, bool *taken);
 // One work item of an expert-grouped GEMM: `count` consecutive activation columns starting at `first` go through
@@ -63,12 +63,13 @@ int32_t launch_gemm_mma(const WeightView &w, const ActView &x, size_t n, float *
 struct MoeTile {
     uint32_t expert, first, count;
 };
-// The tensor-core GEMM over a device-side list of such items (one column tile of up to 64 columns per item):
+// The tensor-core GEMM over a device-side list of such items (one column tile of up to `bn` = 64 or 32 columns per item):
 // w stacks `rows_per_expert` rows per expert; cell (row i of the expert, column c) goes to out[c * ldc + i].
 // *taken = false: no tensor-core path for this weight type / shape.
 bool gemm_mma_supports(int type, size_t k);  // a tensor-core path exists for this weight type and row length
 int32_t launch_gemm_mma_grouped(const WeightView &w, const ActView &x, const MoeTile *tiles, const uint32_t *n_tiles,
-                                uint32_t max_tiles, uint32_t rows_per_expert, float *out, size_t ldc, cudaStream_t st, bool *taken);
+                                uint32_t max_tiles, uint32_t rows_per_expert, float *out, size_t ldc, uint32_t bn, cudaStream_t st,
+                                bool *taken);
 int32_t launch_gemv_q5k_f32(const WeightView &w, const float *x, float *y, cudaStream_t st);
 
 // Rotates q and k in place at position pos (or *pos_dev when non-null).  When k_cache is
