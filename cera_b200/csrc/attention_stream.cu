@@ -100,11 +100,15 @@ attn_stream_kernel(const float *__restrict__ q, const uint8_t *__restrict__ kc, 
             constexpr uint32_t CPR = RB / 16;  // 16-byte pieces per row
             const uint32_t t0 = t_begin + i * AS_TILE, rows = min((uint32_t)AS_TILE, t_end - t0);
             uint8_t *st = ring + (size_t)(i % S) * STAGE;
-            for (uint32_t idx = threadIdx.x; idx < rows * CPR; idx += AS_THREADS) {
-                const uint32_t r = idx / CPR, c = idx % CPR;
-                const size_t src = (size_t)(t0 + r) * row_pitch + (size_t)kvh * RB + c * 16;
-                tma::cp_async16(st + r * RS + c * 16, kc + src);
-                tma::cp_async16(st + (AS_TILE + r) * RS + c * 16, vc + src);
+            // thread t copies piece t % CPR of rows t / CPR, t / CPR + RSTEP, ...: pointers advance by constants
+            constexpr uint32_t RSTEP = AS_THREADS / CPR;
+            const uint32_t c16 = (threadIdx.x % CPR) * 16;
+            uint32_t r = threadIdx.x / CPR;
+            size_t src = (size_t)(t0 + r) * row_pitch + (size_t)kvh * RB + c16;
+            uint8_t *dk = st + r * RS + c16;
+            for (; r < rows; r += RSTEP, src += (size_t)RSTEP * row_pitch, dk += RSTEP * RS) {
+                tma::cp_async16(dk, kc + src);
+                tma::cp_async16(dk + AS_TILE * RS, vc + src);
             }
         }
         cp_async_commit();
