@@ -552,7 +552,7 @@ def main():
         import torch
         import cera_b200 as cb
         for tname, m, k in [("q4_k", 4096, 4096), ("q4_k", 14336, 4096), ("q6_k", 4096, 14336), ("q5_k", 4096, 4096)]:
-            for n in (8, 64, 512):
+            for n in (8, 64, 256, 512):
                 ops, us = gemm_microbench(torch, cb, tname, m, k, n, max(3, args.iters // (4 if n > 64 else 1)))
                 print(json.dumps({"type": tname, "m": m, "k": k, "n": n, "us": round(us, 2),
                                   "tops": round(ops / us / 1e6, 2), "frac_of_int8_nominal_4500": round(ops / us / 1e6 / 4500, 4)}),

@@ -395,6 +395,16 @@ int32_t launch_mma_typed(const GemmParams &p, cudaStream_t st) {
     const uint32_t want = (uint32_t)sm_count() * (bn >= 128 ? 1u : bn == 64 ? 2u : 4u);
     uint32_t cl = 1;
     while (cl < 8 && tiles * cl < want && (p.k >> 8) / (cl * 2) >= 2) cl *= 2;
+    // Wave quantization: with two CTAs resident per SM, a grid of 1.5 (or 3.03) times that many wide tiles leaves the
+    // machine nearly empty for its last round.  Splitting k over a cluster makes the rounds shorter, so the ragged last
+    // one costs less than the reduction adds (14336 x 4096 x 256 columns: 295 -> 265 us with clusters of 4).
+    if (cl == 1 && bn == 128) {
+        const uint32_t slots = (uint32_t)sm_count() * 2, rounds = tiles / slots, rest = tiles % slots;
+        if (rounds >= 1 && rounds <= 3 && rest != 0 && rest * 10 < slots * 6) {
+            const uint32_t split = rounds == 1 ? 4u : 2u;
+            if ((p.k >> 8) / (split * 2) >= 2) cl = split;
+        }
+    }
     switch (bn) {
         case 128: return launch_mma_bn<T, 128>(p, cl, st);
         case 64: return launch_mma_bn<T, 64>(p, cl, st);
