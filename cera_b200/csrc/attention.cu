@@ -593,6 +593,9 @@ int32_t launch_prefill_attention(const float *q, const void *kc, const void *vc,
     if (!q || !kc || !vc || !out) return fail(CERA_CUDA_ERR_BAD_ARG, "prefill_attention: null argument");
     if (n_kv_heads == 0 || n_heads % n_kv_heads) return fail(CERA_CUDA_ERR_BAD_ARG, "prefill_attention: bad head counts");
     if (n == 0) return CERA_CUDA_OK;
+    bool tiled = false;
+    CERA_TRY(launch_prefill_attention_tiled(q, kc, vc, kv_f16, n_heads, n_kv_heads, head_dim, n, start_pos, scale, out, st, &tiled));
+    if (tiled) return CERA_CUDA_OK;
     const dim3 grid((unsigned)n_heads, (unsigned)((n + ATT_WARPS - 1) / ATT_WARPS));
     const dim3 block(ATT_WARPS * 32);
     const uint32_t nh = (uint32_t)n_heads, nkv = (uint32_t)n_kv_heads, nn = (uint32_t)n, sp = (uint32_t)start_pos;

@@ -1,0 +1,222 @@
+// Causal attention of a chunk of prompt tokens (prefill), tiled through shared memory.
+//
+// A CTA owns one KV head and PA_BQ consecutive query tokens; warp w owns query w of the block with all G query heads of
+// the group, so every staged K / V row serves PA_BQ * G (query, head) pairs.  Keys go by in tiles of 32, double-buffered
+// with cp.async:
+//   scores : lane = key.  The lane keeps 32 dims of its K row in registers at a time and reads the queries as
+//            shared-memory broadcasts: no shuffle per key, four FMAs per broadcast load.
+//   softmax: one running maximum / sum per (query, head), updated once per tile (two warp reductions and ONE expf per
+//            key, against a reduction and two expf per key in the one-warp-per-row kernel).
+//   P.V    : lane = four output dims.  The tile's probabilities sit in shared memory, V rows are read as float4 and
+//            shared by the G heads.
+// Rows are padded to 132 floats, so the lane = key reads (stride one row) hit all 32 banks.
+//
+// Arithmetic contract: cera/src/backend/cpu.rs:4028-4241 (scaled dot, causal limit start_pos + j, online softmax);
+// the f32 summation order is this kernel's own.
+#include <cstdlib>
+#include <cstring>
+
+#include "act.cuh"
+#include "ops.h"
+#include "tma.cuh"
+
+namespace cera {
+
+namespace {
+
+constexpr int PA_WARPS = 8, PA_THREADS = PA_WARPS * 32, PA_BQ = PA_WARPS;
+constexpr int PA_TK = 32;        // keys per tile
+constexpr int PA_HD = 128;       // head dim
+constexpr int PA_STRIDE = 132;   // floats per staged row
+
+template <int G>
+constexpr size_t pa_smem_bytes() {
+    return (size_t)(2 * 2 * PA_TK * PA_STRIDE + PA_BQ * G * PA_HD + PA_WARPS * G * PA_TK) * sizeof(float);
+}
+
+__device__ __forceinline__ float pa_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+template <int G>
+__global__ void __launch_bounds__(PA_THREADS) attn_prefill_tiled_kernel(const float *__restrict__ q, const float *__restrict__ kc,
+                                                                        const float *__restrict__ vc, uint32_t n_heads,
+                                                                        uint32_t n_kv_heads, uint32_t n, uint32_t start_pos,
+                                                                        float scale, float *__restrict__ out) {
+    extern __shared__ __align__(16) float pa_smem[];
+    float *ks = pa_smem;                              // [2][32][132]
+    float *vs = ks + 2 * PA_TK * PA_STRIDE;           // [2][32][132]
+    float *qs = vs + 2 * PA_TK * PA_STRIDE;           // [PA_BQ * G][128]
+    float *ps = qs + PA_BQ * G * PA_HD;               // [warps][G][32]
+
+    pdl_trigger();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t kvh = blockIdx.x;
+    const uint32_t qb = gridDim.y - 1 - blockIdx.y;   // the longest rows start first
+    const uint32_t q0 = qb * PA_BQ, j = q0 + warp;
+    const size_t kv_dim = (size_t)n_kv_heads * PA_HD, q_dim = (size_t)n_heads * PA_HD;
+    const uint32_t q_last = min(q0 + PA_BQ, n) - 1;
+    const uint32_t cta_kv = start_pos + q_last + 1;   // keys the block's last query sees
+    const uint32_t n_tiles = (cta_kv + PA_TK - 1) / PA_TK;
+    const bool live = j < n;
+    const uint32_t my_kv = live ? start_pos + j + 1 : 0;
+
+    auto issue = [&](uint32_t t, int stage) {
+        float *kd = ks + stage * PA_TK * PA_STRIDE, *vd = vs + stage * PA_TK * PA_STRIDE;
+        for (int i = tid; i < PA_TK * 32; i += PA_THREADS) {
+            const int r = i >> 5, pc = i & 31;
+            const uint32_t key = min(t * PA_TK + r, cta_kv - 1);   // rows past the limit are masked; keep the read in range
+            const size_t src = (size_t)key * kv_dim + (size_t)kvh * PA_HD + pc * 4;
+            tma::cp_async16(kd + r * PA_STRIDE + pc * 4, kc + src);
+            tma::cp_async16(vd + r * PA_STRIDE + pc * 4, vc + src);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    issue(0, 0);
+    // queries of the block: pair (w, g) at qs[(w * G + g) * 128]
+    for (int i = tid; i < PA_BQ * G * 32; i += PA_THREADS) {
+        const int pair = i >> 5, pc = i & 31;
+        const uint32_t jq = q0 + pair / G;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (jq < n) v = *reinterpret_cast<const float4 *>(q + jq * q_dim + ((size_t)kvh * G + pair % G) * PA_HD + pc * 4);
+        *reinterpret_cast<float4 *>(qs + pair * PA_HD + pc * 4) = v;
+    }
+
+    float m_run[G], l_run[G];
+    float4 acc[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m_run[g] = -INFINITY;
+        l_run[g] = 0.0f;
+        acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const float *qw = qs + warp * G * PA_HD;
+    float *pw = ps + warp * G * PA_TK;
+
+    for (uint32_t t = 0; t < n_tiles; ++t) {
+        const int stage = t & 1;
+        if (t + 1 < n_tiles) {
+            issue(t + 1, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        if (t * PA_TK < my_kv) {
+            const float *kt = ks + stage * PA_TK * PA_STRIDE + lane * PA_STRIDE;
+            const float *vt = vs + stage * PA_TK * PA_STRIDE + lane * 4;
+            float s[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) s[g] = 0.0f;
+#pragma unroll
+            for (int dc = 0; dc < PA_HD / 32; ++dc) {
+                float4 kr[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) kr[i] = *reinterpret_cast<const float4 *>(kt + dc * 32 + 4 * i);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 qq = *reinterpret_cast<const float4 *>(qw + g * PA_HD + dc * 32 + 4 * i);
+                        s[g] = fmaf(qq.x, kr[i].x, s[g]);
+                        s[g] = fmaf(qq.y, kr[i].y, s[g]);
+                        s[g] = fmaf(qq.z, kr[i].z, s[g]);
+                        s[g] = fmaf(qq.w, kr[i].w, s[g]);
+                    }
+                }
+            }
+            const bool valid = t * PA_TK + lane < my_kv;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float sv = valid ? __fmul_rn(s[g], scale) : -INFINITY;
+                const float m_new = fmaxf(m_run[g], pa_warp_max(sv));   // finite: key t * 32 is valid for this query
+                const float corr = m_run[g] == -INFINITY ? 0.0f : ggml_expf(__fsub_rn(m_run[g], m_new));
+                const float p = valid ? ggml_expf(__fsub_rn(sv, m_new)) : 0.0f;
+                l_run[g] = fmaf(l_run[g], corr, warp_sum(p));
+                acc[g].x *= corr;
+                acc[g].y *= corr;
+                acc[g].z *= corr;
+                acc[g].w *= corr;
+                m_run[g] = m_new;
+                pw[g * PA_TK + lane] = p;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int k4 = 0; k4 < PA_TK / 4; ++k4) {
+                const float4 v0 = *reinterpret_cast<const float4 *>(vt + (4 * k4 + 0) * PA_STRIDE);
+                const float4 v1 = *reinterpret_cast<const float4 *>(vt + (4 * k4 + 1) * PA_STRIDE);
+                const float4 v2 = *reinterpret_cast<const float4 *>(vt + (4 * k4 + 2) * PA_STRIDE);
+                const float4 v3 = *reinterpret_cast<const float4 *>(vt + (4 * k4 + 3) * PA_STRIDE);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float4 pp = *reinterpret_cast<const float4 *>(pw + g * PA_TK + 4 * k4);
+                    acc[g].x = fmaf(pp.w, v3.x, fmaf(pp.z, v2.x, fmaf(pp.y, v1.x, fmaf(pp.x, v0.x, acc[g].x))));
+                    acc[g].y = fmaf(pp.w, v3.y, fmaf(pp.z, v2.y, fmaf(pp.y, v1.y, fmaf(pp.x, v0.y, acc[g].y))));
+                    acc[g].z = fmaf(pp.w, v3.z, fmaf(pp.z, v2.z, fmaf(pp.y, v1.z, fmaf(pp.x, v0.z, acc[g].z))));
+                    acc[g].w = fmaf(pp.w, v3.w, fmaf(pp.z, v2.w, fmaf(pp.y, v1.w, fmaf(pp.x, v0.w, acc[g].w))));
+                }
+            }
+            __syncwarp();   // the probabilities are rewritten by the next tile
+        }
+        __syncthreads();    // the stage is refilled by the copy issued in the next iteration
+    }
+
+    if (live) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float inv = 1.0f / l_run[g];
+            float4 o = make_float4(acc[g].x * inv, acc[g].y * inv, acc[g].z * inv, acc[g].w * inv);
+            *reinterpret_cast<float4 *>(out + j * q_dim + ((size_t)kvh * G + g) * PA_HD + 4 * lane) = o;
+        }
+    }
+}
+
+template <int G>
+int32_t launch_tiled(const float *q, const float *kc, const float *vc, uint32_t nh, uint32_t nkv, uint32_t n, uint32_t sp,
+                     float scale, float *out, cudaStream_t st) {
+    constexpr size_t smem = pa_smem_bytes<G>();
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        CERA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_tiled_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured_dev = dev;
+    }
+    const dim3 grid(nkv, (n + PA_BQ - 1) / PA_BQ);
+    count_launch();
+    return check_cuda(launch_k(attn_prefill_tiled_kernel<G>, grid, dim3(PA_THREADS), smem, st, q, kc, vc, nh, nkv, n, sp, scale, out),
+                      "prefill attention (tiled) launch");
+}
+
+}  // namespace
+
+// f32 cache, head_dim 128, group size 1, 2, 4 or 8, 16-byte aligned operands; anything else: *taken = false and the
+// caller runs the one-warp-per-row kernel.  CERA_CUDA_PREFILL_ATTN=rows turns this kernel off.
+int32_t launch_prefill_attention_tiled(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
+                                       size_t n_kv_heads, size_t head_dim, size_t n, size_t start_pos, float scale, float *out,
+                                       cudaStream_t st, bool *taken) {
+    *taken = false;
+    static const bool off = [] {
+        const char *e = getenv("CERA_CUDA_PREFILL_ATTN");
+        return e && strcmp(e, "rows") == 0;
+    }();
+    if (off || kv_f16 || head_dim != PA_HD || n == 0) return CERA_CUDA_OK;
+    if (((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out) % 16) return CERA_CUDA_OK;
+    const size_t g = n_heads / n_kv_heads;
+    const uint32_t nh = (uint32_t)n_heads, nkv = (uint32_t)n_kv_heads, nn = (uint32_t)n, sp = (uint32_t)start_pos;
+    const float *kf = (const float *)kc, *vf = (const float *)vc;
+    *taken = true;
+    switch (g) {
+        case 1: return launch_tiled<1>(q, kf, vf, nh, nkv, nn, sp, scale, out, st);
+        case 2: return launch_tiled<2>(q, kf, vf, nh, nkv, nn, sp, scale, out, st);
+        case 4: return launch_tiled<4>(q, kf, vf, nh, nkv, nn, sp, scale, out, st);
+        case 8: return launch_tiled<8>(q, kf, vf, nh, nkv, nn, sp, scale, out, st);
+        default: *taken = false; return CERA_CUDA_OK;
+    }
+}
+
+}  // namespace cera

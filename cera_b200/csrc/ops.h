@@ -113,6 +113,10 @@ int32_t launch_rope_batch(float *q, float *k, const float *v, size_t start_pos, 
 int32_t launch_prefill_attention(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
                                  size_t n_kv_heads, size_t head_dim, size_t n, size_t start_pos, float scale, float *out,
                                  cudaStream_t st);
+// The same through the shared-memory-tiled kernel (attention_prefill.cu).  *taken = false: not its case, nothing launched.
+int32_t launch_prefill_attention_tiled(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
+                                       size_t n_kv_heads, size_t head_dim, size_t n, size_t start_pos, float scale, float *out,
+                                       cudaStream_t st, bool *taken);
 // y[d] += B (scale * (A x)): one LoRA pair applied to one token (cera/src/lora.rs:794-821).
 int32_t launch_lora(const float *x, const float *a, const float *b, size_t rank, size_t k, size_t d, float scale, float *y,
                     cudaStream_t st);
