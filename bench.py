@@ -458,7 +458,7 @@ def cuda_arm(args, rank, world):
                        "stream_head": [int(t) for t in stream[:8]],
                        "l2": "each token streams 4.84 GB of weights (>> 126 MB L2); the kernel microbench rotates "
                              "16 weight copies (528 MB)",
-                       "build_s": round(t_build, 2), "prefill_s": round(t_pre, 2)},
+                       "build_s": round(t_build, 2), "prefill_s": round(t_pre, 4)},
             "e2e": {"value": K / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 4},
             "gpu_launches": int(model_launches + roof_launches),
             "clocks": clocks,
