@@ -9,10 +9,13 @@
 //            key, against a reduction and two expf per key in the one-warp-per-row kernel).
 //   P.V    : lane = four output dims.  The tile's probabilities sit in shared memory, V rows are read as float4 and
 //            shared by the G heads.
-// Rows are padded to 132 floats, so the lane = key reads (stride one row) hit all 32 banks.
+// Rows are padded to 132 floats (f16 caches: staged as stored, 272 bytes per row, widened on the way to the registers),
+// so the lane = key reads (stride one row) hit all 32 banks.
 //
 // Arithmetic contract: cera/src/backend/cpu.rs:4028-4241 (scaled dot, causal limit start_pos + j, online softmax);
 // the f32 summation order is this kernel's own.
+#include <cuda_fp16.h>
+
 #include <cstdlib>
 #include <cstring>
 
@@ -27,11 +30,38 @@ namespace {
 constexpr int PA_WARPS = 8, PA_THREADS = PA_WARPS * 32, PA_BQ = PA_WARPS;
 constexpr int PA_TK = 32;        // keys per tile
 constexpr int PA_HD = 128;       // head dim
-constexpr int PA_STRIDE = 132;   // floats per staged row
+constexpr int PA_ROW_F32 = 528, PA_ROW_F16 = 272;   // bytes per staged row (512 / 256 of data + padding)
 
-template <int G>
+template <int G, bool F16>
 constexpr size_t pa_smem_bytes() {
-    return (size_t)(2 * 2 * PA_TK * PA_STRIDE + PA_BQ * G * PA_HD + PA_WARPS * G * PA_TK) * sizeof(float);
+    return (size_t)2 * 2 * PA_TK * (F16 ? PA_ROW_F16 : PA_ROW_F32) + (size_t)(PA_BQ * G * PA_HD + PA_WARPS * G * PA_TK) * sizeof(float);
+}
+
+// Eight consecutive elements of a staged row as two float4.
+template <bool F16>
+__device__ __forceinline__ void pa_load8(const uint8_t *row, int first, float4 &a, float4 &b) {
+    if (F16) {
+        const uint4 r = *reinterpret_cast<const uint4 *>(row + first * 2);
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&r.x));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&r.y));
+        const float2 f2 = __half22float2(*reinterpret_cast<const __half2 *>(&r.z));
+        const float2 f3 = __half22float2(*reinterpret_cast<const __half2 *>(&r.w));
+        a = make_float4(f0.x, f0.y, f1.x, f1.y);
+        b = make_float4(f2.x, f2.y, f3.x, f3.y);
+    } else {
+        a = *reinterpret_cast<const float4 *>(row + first * 4);
+        b = *reinterpret_cast<const float4 *>(row + first * 4 + 16);
+    }
+}
+template <bool F16>
+__device__ __forceinline__ float4 pa_load4(const uint8_t *row, int first) {
+    if (F16) {
+        const uint2 r = *reinterpret_cast<const uint2 *>(row + first * 2);
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&r.x));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&r.y));
+        return make_float4(f0.x, f0.y, f1.x, f1.y);
+    }
+    return *reinterpret_cast<const float4 *>(row + first * 4);
 }
 
 __device__ __forceinline__ float pa_warp_max(float v) {
@@ -40,15 +70,17 @@ __device__ __forceinline__ float pa_warp_max(float v) {
     return v;
 }
 
-template <int G>
-__global__ void __launch_bounds__(PA_THREADS) attn_prefill_tiled_kernel(const float *__restrict__ q, const float *__restrict__ kc,
-                                                                        const float *__restrict__ vc, uint32_t n_heads,
+template <int G, bool F16>
+__global__ void __launch_bounds__(PA_THREADS) attn_prefill_tiled_kernel(const float *__restrict__ q, const uint8_t *__restrict__ kc,
+                                                                        const uint8_t *__restrict__ vc, uint32_t n_heads,
                                                                         uint32_t n_kv_heads, uint32_t n, uint32_t start_pos,
                                                                         float scale, float *__restrict__ out) {
-    extern __shared__ __align__(16) float pa_smem[];
-    float *ks = pa_smem;                              // [2][32][132]
-    float *vs = ks + 2 * PA_TK * PA_STRIDE;           // [2][32][132]
-    float *qs = vs + 2 * PA_TK * PA_STRIDE;           // [PA_BQ * G][128]
+    extern __shared__ __align__(16) uint8_t pa_smem[];
+    constexpr int ROWB = F16 ? PA_ROW_F16 : PA_ROW_F32, ESZ = F16 ? 2 : 4, STAGE = PA_TK * ROWB;
+    constexpr int PIECES = PA_HD * ESZ / 16;          // 16-byte pieces per cache row
+    uint8_t *ks = pa_smem;                            // [2][32][ROWB]
+    uint8_t *vs = ks + 2 * STAGE;                     // [2][32][ROWB]
+    float *qs = reinterpret_cast<float *>(vs + 2 * STAGE);   // [PA_BQ * G][128]
     float *ps = qs + PA_BQ * G * PA_HD;               // [warps][G][32]
 
     pdl_trigger();
@@ -65,13 +97,13 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_tiled_kernel(const fl
     const uint32_t my_kv = live ? start_pos + j + 1 : 0;
 
     auto issue = [&](uint32_t t, int stage) {
-        float *kd = ks + stage * PA_TK * PA_STRIDE, *vd = vs + stage * PA_TK * PA_STRIDE;
-        for (int i = tid; i < PA_TK * 32; i += PA_THREADS) {
-            const int r = i >> 5, pc = i & 31;
+        uint8_t *kd = ks + stage * STAGE, *vd = vs + stage * STAGE;
+        for (int i = tid; i < PA_TK * PIECES; i += PA_THREADS) {
+            const int r = i / PIECES, pc = i % PIECES;
             const uint32_t key = min(t * PA_TK + r, cta_kv - 1);   // rows past the limit are masked; keep the read in range
-            const size_t src = (size_t)key * kv_dim + (size_t)kvh * PA_HD + pc * 4;
-            tma::cp_async16(kd + r * PA_STRIDE + pc * 4, kc + src);
-            tma::cp_async16(vd + r * PA_STRIDE + pc * 4, vc + src);
+            const size_t src = ((size_t)key * kv_dim + (size_t)kvh * PA_HD) * ESZ + pc * 16;
+            tma::cp_async16(kd + r * ROWB + pc * 16, kc + src);
+            tma::cp_async16(vd + r * ROWB + pc * 16, vc + src);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -107,8 +139,8 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_tiled_kernel(const fl
         }
         __syncthreads();
         if (t * PA_TK < my_kv) {
-            const float *kt = ks + stage * PA_TK * PA_STRIDE + lane * PA_STRIDE;
-            const float *vt = vs + stage * PA_TK * PA_STRIDE + lane * 4;
+            const uint8_t *kt = ks + stage * STAGE + lane * ROWB;
+            const uint8_t *vt = vs + stage * STAGE;
             float s[G];
 #pragma unroll
             for (int g = 0; g < G; ++g) s[g] = 0.0f;
@@ -116,7 +148,7 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_tiled_kernel(const fl
             for (int dc = 0; dc < PA_HD / 32; ++dc) {
                 float4 kr[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) kr[i] = *reinterpret_cast<const float4 *>(kt + dc * 32 + 4 * i);
+                for (int i = 0; i < 4; ++i) pa_load8<F16>(kt, dc * 32 + 8 * i, kr[2 * i], kr[2 * i + 1]);
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
 #pragma unroll
@@ -147,10 +179,10 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_tiled_kernel(const fl
             __syncwarp();
 #pragma unroll
             for (int k4 = 0; k4 < PA_TK / 4; ++k4) {
-                const float4 v0 = *reinterpret_cast<const float4 *>(vt + (4 * k4 + 0) * PA_STRIDE);
-                const float4 v1 = *reinterpret_cast<const float4 *>(vt + (4 * k4 + 1) * PA_STRIDE);
-                const float4 v2 = *reinterpret_cast<const float4 *>(vt + (4 * k4 + 2) * PA_STRIDE);
-                const float4 v3 = *reinterpret_cast<const float4 *>(vt + (4 * k4 + 3) * PA_STRIDE);
+                const float4 v0 = pa_load4<F16>(vt + (4 * k4 + 0) * ROWB, 4 * lane);
+                const float4 v1 = pa_load4<F16>(vt + (4 * k4 + 1) * ROWB, 4 * lane);
+                const float4 v2 = pa_load4<F16>(vt + (4 * k4 + 2) * ROWB, 4 * lane);
+                const float4 v3 = pa_load4<F16>(vt + (4 * k4 + 3) * ROWB, 4 * lane);
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     const float4 pp = *reinterpret_cast<const float4 *>(pw + g * PA_TK + 4 * k4);
@@ -175,26 +207,26 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_tiled_kernel(const fl
     }
 }
 
-template <int G>
-int32_t launch_tiled(const float *q, const float *kc, const float *vc, uint32_t nh, uint32_t nkv, uint32_t n, uint32_t sp,
+template <int G, bool F16>
+int32_t launch_tiled(const float *q, const uint8_t *kc, const uint8_t *vc, uint32_t nh, uint32_t nkv, uint32_t n, uint32_t sp,
                      float scale, float *out, cudaStream_t st) {
-    constexpr size_t smem = pa_smem_bytes<G>();
+    constexpr size_t smem = pa_smem_bytes<G, F16>();
     static thread_local int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_dev != dev) {
-        CERA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_tiled_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        CERA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_tiled_kernel<G, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured_dev = dev;
     }
     const dim3 grid(nkv, (n + PA_BQ - 1) / PA_BQ);
     count_launch();
-    return check_cuda(launch_k(attn_prefill_tiled_kernel<G>, grid, dim3(PA_THREADS), smem, st, q, kc, vc, nh, nkv, n, sp, scale, out),
+    return check_cuda(launch_k(attn_prefill_tiled_kernel<G, F16>, grid, dim3(PA_THREADS), smem, st, q, kc, vc, nh, nkv, n, sp, scale, out),
                       "prefill attention (tiled) launch");
 }
 
 }  // namespace
 
-// f32 cache, head_dim 128, group size 1, 2, 4 or 8, 16-byte aligned operands; anything else: *taken = false and the
+// f32 or f16 cache, head_dim 128, group size 1, 2, 4 or 8, 16-byte aligned operands; anything else: *taken = false and the
 // caller runs the one-warp-per-row kernel.  CERA_CUDA_PREFILL_ATTN=rows turns this kernel off.
 int32_t launch_prefill_attention_tiled(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,
                                        size_t n_kv_heads, size_t head_dim, size_t n, size_t start_pos, float scale, float *out,
@@ -204,19 +236,24 @@ int32_t launch_prefill_attention_tiled(const float *q, const void *kc, const voi
         const char *e = getenv("CERA_CUDA_PREFILL_ATTN");
         return e && strcmp(e, "rows") == 0;
     }();
-    if (off || kv_f16 || head_dim != PA_HD || n == 0) return CERA_CUDA_OK;
+    if (off || head_dim != PA_HD || n == 0) return CERA_CUDA_OK;
     if (((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out) % 16) return CERA_CUDA_OK;
     const size_t g = n_heads / n_kv_heads;
     const uint32_t nh = (uint32_t)n_heads, nkv = (uint32_t)n_kv_heads, nn = (uint32_t)n, sp = (uint32_t)start_pos;
-    const float *kf = (const float *)kc, *vf = (const float *)vc;
+    const uint8_t *kf = (const uint8_t *)kc, *vf = (const uint8_t *)vc;
     *taken = true;
+#define CERA_PA_CASE(GG)                                                                              \
+    case GG:                                                                                          \
+        return kv_f16 ? launch_tiled<GG, true>(q, kf, vf, nh, nkv, nn, sp, scale, out, st)            \
+                      : launch_tiled<GG, false>(q, kf, vf, nh, nkv, nn, sp, scale, out, st)
     switch (g) {
-        case 1: return launch_tiled<1>(q, kf, vf, nh, nkv, nn, sp, scale, out, st);
-        case 2: return launch_tiled<2>(q, kf, vf, nh, nkv, nn, sp, scale, out, st);
-        case 4: return launch_tiled<4>(q, kf, vf, nh, nkv, nn, sp, scale, out, st);
-        case 8: return launch_tiled<8>(q, kf, vf, nh, nkv, nn, sp, scale, out, st);
+        CERA_PA_CASE(1);
+        CERA_PA_CASE(2);
+        CERA_PA_CASE(4);
+        CERA_PA_CASE(8);
         default: *taken = false; return CERA_CUDA_OK;
     }
+#undef CERA_PA_CASE
 }
 
 }  // namespace cera

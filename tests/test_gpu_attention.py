@@ -140,8 +140,9 @@ def test_decode_attention_rejects_unsupported_shapes():
 
 @pytest.mark.parametrize("nh,nkv,n,start", [(32, 8, 256, 256), (32, 8, 256, 0), (8, 8, 33, 5), (8, 4, 9, 0), (16, 2, 41, 90),
                                              (4, 1, 1, 0), (4, 1, 1, 63)])
-def test_prefill_attention_tiled_shapes(nh, nkv, n, start):
-    """The shared-memory-tiled kernel (f32 cache, head_dim 128, groups of 1 / 2 / 4 / 8): the 256-token chunk of the
+@pytest.mark.parametrize("f16", [False, True])
+def test_prefill_attention_tiled_shapes(nh, nkv, n, start, f16):
+    """The shared-memory-tiled kernel (f32 and f16 caches, head_dim 128, groups of 1 / 2 / 4 / 8): the 256-token chunk of the
     Llama-3-8B shape at both chunk positions, ragged query blocks, a single query, limits on and off tile boundaries."""
     torch = need_gpu()
     import cera_b200 as cb
@@ -151,11 +152,12 @@ def test_prefill_attention_tiled_shapes(nh, nkv, n, start):
     vc = cb.synth_normal(total * nkv * hd, seed=12, sigma=1.0).reshape(total, nkv * hd)
     q = cb.synth_normal(n * nh * hd, seed=13, sigma=1.0).reshape(n, nh * hd)
     scale = 1.0 / math.sqrt(hd)
-    got = cb.prefill_attention(q, kc, vc, nh, nkv, hd, n, start, scale).cpu().numpy()
+    kk, vv = (kc.half(), vc.half()) if f16 else (kc, vc)
+    got = cb.prefill_attention(q, kk, vv, nh, nkv, hd, n, start, scale).cpu().numpy()
     qm = np.ascontiguousarray(q.cpu().numpy().T)
-    want = O.flash_attention_gqa(qm, kc.cpu().numpy(), vc.cpu().numpy(), nh, nkv, hd, n, start, scale)
+    want = O.flash_attention_gqa(qm, kk.float().cpu().numpy(), vv.float().cpu().numpy(), nh, nkv, hd, n, start, scale)
     want = np.ascontiguousarray(want.transpose(1, 0, 2)).reshape(n, nh * hd)
-    assert_close(got, want, f"tiled prefill attention {nh}/{nkv} n={n} start={start}")
+    assert_close(got, want, f"tiled prefill attention {nh}/{nkv} n={n} start={start} f16={f16}")
 
 
 @pytest.mark.parametrize("f16", [False, True])
