@@ -78,6 +78,17 @@ __device__ __forceinline__ void mma_u8s8_k16(int (&c)[4], uint32_t a0, uint32_t 
         : "r"(a0), "r"(a1), "r"(b0), "r"(0), "r"(0), "r"(0), "r"(0));
 }
 
+// The per-block rescale on packed f32 pairs (sm_100 FFMA2 / FMUL2: one instruction per two cells, same rounding as the
+// scalar forms).  A thread's two cells of an accumulator row share the weight row and differ in the activation column.
+//   acc += (sc * xs) * sum - mn * xb       (Q4_0, Q4_K, Q5_K)
+__device__ __forceinline__ void rescale_pair(float2 &acc, float2 sc, float2 neg_mn, float2 xs, float2 xb, int c0, int c1) {
+    acc = __ffma2_rn(__fmul2_rn(sc, xs), make_float2((float)c0, (float)c1), __ffma2_rn(neg_mn, xb, acc));
+}
+//   acc += sc * (xs * sum + xb)            (Q6_K)
+__device__ __forceinline__ void rescale_pair_q6(float2 &acc, float2 sc, float2 xs, float2 xb, int c0, int c1) {
+    acc = __ffma2_rn(sc, __ffma2_rn(xs, make_float2((float)c0, (float)c1), xb), acc);
+}
+
 template <int BN>
 constexpr size_t gm_smem_bytes() {
     return GM_BM * GM_WQ_STRIDE + GM_BM * GM_WH_STRIDE + GM_BM * 16 + GM_BM * 16 * 4 + GM_BM * 8 * 4 + BN * GM_AQ_STRIDE +
@@ -119,11 +130,9 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
     const uint32_t nb = p.w.nb, nb32 = p.k >> 5, nb16 = p.k >> 4;
     const TypeInfo ti = type_info(T);
 
-    float acc[NT][4];
+    float2 acc[NT][2];  // [n-tile][row gid / row gid + 8] x (column 2*tig, 2*tig + 1)
 #pragma unroll
-    for (int j = 0; j < NT; ++j)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = make_float2(0.0f, 0.0f);
 
     // this CTA's share of the super-blocks
     const uint32_t n_chunks = p.k >> 8;  // 256 weights per chunk: a K-quant super-block, or eight Q4_0 blocks
@@ -216,6 +225,8 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
                 const uint32_t a[4] = {wa & 0x0F0F0F0Fu, wb & 0x0F0F0F0Fu, (wa >> 4) & 0x0F0F0F0Fu, (wb >> 4) & 0x0F0F0F0Fu};
                 const float sca = wsc[(wrow + gid) * 16 + s], scb = wsc[(wrow + gid + 8) * 16 + s];
                 const float mna = wmn[(wrow + gid) * 8 + s], mnb = wmn[(wrow + gid + 8) * 8 + s];
+                const float2 sca2 = make_float2(sca, sca), scb2 = make_float2(scb, scb);
+                const float2 mna2 = make_float2(-mna, -mna), mnb2 = make_float2(-mnb, -mnb);
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
                     const int cb = wcol + 8 * j;
@@ -226,10 +237,8 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
                     mma_u8s8_k32(c, a, b0, b1);
                     const float2 xs = *reinterpret_cast<const float2 *>(axs + s * GM_BN + cb + 2 * tig);
                     const float2 xb = *reinterpret_cast<const float2 *>(axb + s * GM_BN + cb + 2 * tig);
-                    acc[j][0] = fmaf(sca * xs.x, (float)c[0], fmaf(-mna, xb.x, acc[j][0]));
-                    acc[j][1] = fmaf(sca * xs.y, (float)c[1], fmaf(-mna, xb.y, acc[j][1]));
-                    acc[j][2] = fmaf(scb * xs.x, (float)c[2], fmaf(-mnb, xb.x, acc[j][2]));
-                    acc[j][3] = fmaf(scb * xs.y, (float)c[3], fmaf(-mnb, xb.y, acc[j][3]));
+                    rescale_pair(acc[j][0], sca2, mna2, xs, xb, c[0], c[1]);
+                    rescale_pair(acc[j][1], scb2, mnb2, xs, xb, c[2], c[3]);
                 }
             }
         } else if (T != CERA_TYPE_Q6_K) {
@@ -261,6 +270,8 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
                     }
                     const float sca = wsc[(wrow + gid) * 16 + s], scb = wsc[(wrow + gid + 8) * 16 + s];
                     const float mna = wmn[(wrow + gid) * 8 + s], mnb = wmn[(wrow + gid + 8) * 8 + s];
+                    const float2 sca2 = make_float2(sca, sca), scb2 = make_float2(scb, scb);
+                    const float2 mna2 = make_float2(-mna, -mna), mnb2 = make_float2(-mnb, -mnb);
 #pragma unroll
                     for (int j = 0; j < NT; ++j) {
                         const int cb = wcol + 8 * j;  // this n-tile's first column inside the CTA tile
@@ -271,10 +282,8 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
                         mma_u8s8_k32(c, a, b0, b1);
                         const float2 xs = *reinterpret_cast<const float2 *>(axs + s * GM_BN + cb + 2 * tig);
                         const float2 xb = *reinterpret_cast<const float2 *>(axb + s * GM_BN + cb + 2 * tig);
-                        acc[j][0] = fmaf(sca * xs.x, (float)c[0], fmaf(-mna, xb.x, acc[j][0]));
-                        acc[j][1] = fmaf(sca * xs.y, (float)c[1], fmaf(-mna, xb.y, acc[j][1]));
-                        acc[j][2] = fmaf(scb * xs.x, (float)c[2], fmaf(-mnb, xb.x, acc[j][2]));
-                        acc[j][3] = fmaf(scb * xs.y, (float)c[3], fmaf(-mnb, xb.y, acc[j][3]));
+                        rescale_pair(acc[j][0], sca2, mna2, xs, xb, c[0], c[1]);
+                        rescale_pair(acc[j][1], scb2, mnb2, xs, xb, c[2], c[3]);
                     }
                 }
             }
@@ -291,6 +300,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
                 const uint32_t a0 = ((la >> nsh) & 0x0F0F0F0Fu) | (((hha >> (2 * g)) & 0x03030303u) << 4);
                 const uint32_t a1 = ((lb >> nsh) & 0x0F0F0F0Fu) | (((hhb >> (2 * g)) & 0x03030303u) << 4);
                 const float sca = wsc[(wrow + gid) * 16 + e], scb = wsc[(wrow + gid + 8) * 16 + e];
+                const float2 sca2 = make_float2(sca, sca), scb2 = make_float2(scb, scb);
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
                     const int cb = wcol + 8 * j;
@@ -299,10 +309,8 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
                     mma_u8s8_k16(c, a0, a1, b0);
                     const float2 xs = *reinterpret_cast<const float2 *>(axs + (e >> 1) * GM_BN + cb + 2 * tig);
                     const float2 xb = *reinterpret_cast<const float2 *>(axb + e * GM_BN + cb + 2 * tig);
-                    acc[j][0] = fmaf(sca, fmaf(xs.x, (float)c[0], xb.x), acc[j][0]);
-                    acc[j][1] = fmaf(sca, fmaf(xs.y, (float)c[1], xb.y), acc[j][1]);
-                    acc[j][2] = fmaf(scb, fmaf(xs.x, (float)c[2], xb.x), acc[j][2]);
-                    acc[j][3] = fmaf(scb, fmaf(xs.y, (float)c[3], xb.y), acc[j][3]);
+                    rescale_pair_q6(acc[j][0], sca2, xs, xb, c[0], c[1]);
+                    rescale_pair_q6(acc[j][1], scb2, xs, xb, c[2], c[3]);
                 }
             }
         }
@@ -319,7 +327,8 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
                 const uint32_t col = col0 + wcol + 8 * j + 2 * tig + (i & 1);
                 if (row < p.m && col < n_cols) {
                     float *y = p.out + (size_t)row * p.ldy + (size_t)col * p.ldc;
-                    *y = p.epilogue == EPI_ADD ? __fadd_rn(*y, acc[j][i]) : acc[j][i];
+                    const float v = (i & 1) ? acc[j][i >> 1].y : acc[j][i >> 1].x;
+                    *y = p.epilogue == EPI_ADD ? __fadd_rn(*y, v) : v;
                 }
             }
         return;
@@ -329,7 +338,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
     for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-            tile[(wrow + gid + (i >= 2 ? 8 : 0)) * GM_BN + wcol + 8 * j + 2 * tig + (i & 1)] = acc[j][i];
+            tile[(wrow + gid + (i >= 2 ? 8 : 0)) * GM_BN + wcol + 8 * j + 2 * tig + (i & 1)] = (i & 1) ? acc[j][i >> 1].y : acc[j][i >> 1].x;
     cluster.sync();
     const uint32_t rows_each = GM_BM / CL;  // CL is 2, 4 or 8
     for (uint32_t idx = tid; idx < rows_each * GM_BN; idx += GM_THREADS) {
