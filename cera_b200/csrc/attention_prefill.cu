@@ -141,9 +141,9 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_tiled_kernel(const fl
         if (t * PA_TK < my_kv) {
             const uint8_t *kt = ks + stage * STAGE + lane * ROWB;
             const uint8_t *vt = vs + stage * STAGE;
-            float s[G];
+            float2 s[G];
 #pragma unroll
-            for (int g = 0; g < G; ++g) s[g] = 0.0f;
+            for (int g = 0; g < G; ++g) s[g] = make_float2(0.0f, 0.0f);
 #pragma unroll
             for (int dc = 0; dc < PA_HD / 32; ++dc) {
                 float4 kr[8];
@@ -154,17 +154,16 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_tiled_kernel(const fl
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const float4 qq = *reinterpret_cast<const float4 *>(qw + g * PA_HD + dc * 32 + 4 * i);
-                        s[g] = fmaf(qq.x, kr[i].x, s[g]);
-                        s[g] = fmaf(qq.y, kr[i].y, s[g]);
-                        s[g] = fmaf(qq.z, kr[i].z, s[g]);
-                        s[g] = fmaf(qq.w, kr[i].w, s[g]);
+                        // packed f32 pairs (FFMA2): even dims accumulate in .x, odd dims in .y
+                        s[g] = __ffma2_rn(make_float2(qq.x, qq.y), make_float2(kr[i].x, kr[i].y), s[g]);
+                        s[g] = __ffma2_rn(make_float2(qq.z, qq.w), make_float2(kr[i].z, kr[i].w), s[g]);
                     }
                 }
             }
             const bool valid = t * PA_TK + lane < my_kv;
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-                const float sv = valid ? __fmul_rn(s[g], scale) : -INFINITY;
+                const float sv = valid ? __fmul_rn(__fadd_rn(s[g].x, s[g].y), scale) : -INFINITY;
                 const float m_new = fmaxf(m_run[g], pa_warp_max(sv));   // finite: key t * 32 is valid for this query
                 const float corr = m_run[g] == -INFINITY ? 0.0f : ggml_expf(__fsub_rn(m_run[g], m_new));
                 const float p = valid ? ggml_expf(__fsub_rn(sv, m_new)) : 0.0f;
@@ -186,10 +185,14 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_tiled_kernel(const fl
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     const float4 pp = *reinterpret_cast<const float4 *>(pw + g * PA_TK + 4 * k4);
-                    acc[g].x = fmaf(pp.w, v3.x, fmaf(pp.z, v2.x, fmaf(pp.y, v1.x, fmaf(pp.x, v0.x, acc[g].x))));
-                    acc[g].y = fmaf(pp.w, v3.y, fmaf(pp.z, v2.y, fmaf(pp.y, v1.y, fmaf(pp.x, v0.y, acc[g].y))));
-                    acc[g].z = fmaf(pp.w, v3.z, fmaf(pp.z, v2.z, fmaf(pp.y, v1.z, fmaf(pp.x, v0.z, acc[g].z))));
-                    acc[g].w = fmaf(pp.w, v3.w, fmaf(pp.z, v2.w, fmaf(pp.y, v1.w, fmaf(pp.x, v0.w, acc[g].w))));
+                    const float2 p0 = make_float2(pp.x, pp.x), p1 = make_float2(pp.y, pp.y), p2 = make_float2(pp.z, pp.z),
+                                 p3 = make_float2(pp.w, pp.w);
+                    float2 lo = make_float2(acc[g].x, acc[g].y), hi = make_float2(acc[g].z, acc[g].w);
+                    lo = __ffma2_rn(p3, make_float2(v3.x, v3.y), __ffma2_rn(p2, make_float2(v2.x, v2.y),
+                         __ffma2_rn(p1, make_float2(v1.x, v1.y), __ffma2_rn(p0, make_float2(v0.x, v0.y), lo))));
+                    hi = __ffma2_rn(p3, make_float2(v3.z, v3.w), __ffma2_rn(p2, make_float2(v2.z, v2.w),
+                         __ffma2_rn(p1, make_float2(v1.z, v1.w), __ffma2_rn(p0, make_float2(v0.z, v0.w), hi))));
+                    acc[g] = make_float4(lo.x, lo.y, hi.x, hi.y);
                 }
             }
             __syncwarp();   // the probabilities are rewritten by the next tile
