@@ -224,16 +224,34 @@ struct EpLayout {  // byte offsets inside every rank's exchange region
     uint32_t counts, r_scales, r_quants, r_sums, r_meta, ret_out;
 };
 
+// Status word values of the expert-parallel call beyond the timeout codes of tp.cuh.
+constexpr uint32_t EP_STATUS_OVERFLOW = 0x40000000u;  // | destination rank << 24: more entries than a receive buffer holds
+
 // One CTA.  counts_all[G][E] (every rank's per-expert entry counts) -> my_base[e] = first slot, in the
 // receive buffer of e's owner, of this rank's entries for expert e; the work list over what THIS rank
 // receives for its local experts; *n_recv.  Zeroes this rank's own count row for the next call.
+// Every receive buffer holds `limit` entries.  If the counts of any destination add up to more (the
+// ranks' token counts exceed what the layer was created for), or an earlier exchange of this layer ran
+// out of time (the table may then mix rows of different calls), nothing may be stored into a peer:
+// *skip is set, the work list and *n_recv are emptied, and the status word names the cause.
 __global__ void moe_ep_plan_kernel(TpCtx c, EpLayout lay, uint32_t n_expert, uint32_t nc, uint32_t small_nc, uint32_t cap,
-                                   uint32_t *my_base, uint32_t *cursor, MoeTile *tiles, uint32_t *n_tiles, uint32_t *n_recv) {
+                                   uint32_t limit, uint32_t *my_base, uint32_t *cursor, MoeTile *tiles, uint32_t *n_tiles,
+                                   uint32_t *n_recv, uint32_t *skip) {
     if (threadIdx.x != 0) return;
     uint32_t *counts = (uint32_t *)(c.peer[c.rank] + lay.counts);
     const uint32_t per = n_expert / c.size;
     uint32_t t = 0, ts = 0;
-    for (uint32_t d = 0; d < c.size; ++d) {
+    bool bad = *(volatile uint32_t *)c.status != 0;
+    for (uint32_t d = 0; d < c.size && !bad; ++d) {
+        uint64_t tot_d = 0;
+        for (uint32_t e = d * per; e < (d + 1) * per; ++e)
+            for (uint32_t src = 0; src < c.size; ++src) tot_d += counts[src * n_expert + e];
+        if (tot_d > limit) {
+            atomicCAS(c.status, 0u, EP_STATUS_OVERFLOW | (d << 24));
+            bad = true;
+        }
+    }
+    for (uint32_t d = 0; d < c.size && !bad; ++d) {
         uint32_t off = 0;  // running slot in rank d's receive buffer
         for (uint32_t e = d * per; e < (d + 1) * per; ++e) {
             uint32_t tot = 0, before_me = 0;
@@ -249,6 +267,11 @@ __global__ void moe_ep_plan_kernel(TpCtx c, EpLayout lay, uint32_t n_expert, uin
         }
         if (d == c.rank) *n_recv = off;
     }
+    if (bad) {
+        t = ts = 0;
+        *n_recv = 0;
+    }
+    *skip = bad ? 1u : 0u;
     n_tiles[0] = t;
     n_tiles[1] = ts;
     for (uint32_t e = 0; e < n_expert; ++e) counts[c.rank * n_expert + e] = 0;
@@ -258,8 +281,10 @@ __global__ void moe_ep_plan_kernel(TpCtx c, EpLayout lay, uint32_t n_expert, uin
 // token's Q8_0 column and its return address into the owner's receive buffer.
 __global__ void __launch_bounds__(128) moe_ep_dispatch_kernel(TpCtx c, EpLayout lay, const uint32_t *__restrict__ ids,
                                                               uint32_t n_used, uint32_t hidden, uint32_t n_expert, ActView x,
-                                                              const uint32_t *__restrict__ my_base, uint32_t *cursor) {
+                                                              const uint32_t *__restrict__ my_base, uint32_t *cursor,
+                                                              const uint32_t *__restrict__ skip) {
     __shared__ uint32_t pos_s;
+    if (*skip) return;  // the plan found the receive buffers too small, or an earlier exchange timed out
     const uint32_t pair = blockIdx.x, j = pair / n_used, e = ids[pair];
     if (threadIdx.x == 0) pos_s = my_base[e] + atomicAdd(cursor + e, 1u);
     __syncthreads();
@@ -522,11 +547,12 @@ int32_t moe_ffn_ep(cera_cuda_moe *h, const float *x_dev, size_t n, int32_t softm
     const TpRange cr{(uint32_t)((char *)counts_mine - h->region), E * 4};
     CERA_TRY(launch_tp_exchange(h->ep, &cr, 1, 0, st));
     const uint32_t cap = (uint32_t)(rmax + E), max_small = E / h->ep_size;
-    moe_ep_plan_kernel<<<1, 32, 0, st>>>(h->ep, h->lay, E, nc, mma ? nc / 2 : 0, cap, h->my_base, h->cursor, h->tiles, h->n_tiles,
-                                         n_recv);
+    uint32_t *skip = h->ep_words + 33;
+    moe_ep_plan_kernel<<<1, 32, 0, st>>>(h->ep, h->lay, E, nc, mma ? nc / 2 : 0, cap, (uint32_t)rmax, h->my_base, h->cursor, h->tiles,
+                                         h->n_tiles, n_recv, skip);
     if (n)
         moe_ep_dispatch_kernel<<<(unsigned)entries, 128, 0, st>>>(h->ep, h->lay, h->ids, ku, hs, E, ActView{h->xs, h->xq, h->xsum},
-                                                                   h->my_base, h->cursor);
+                                                                   h->my_base, h->cursor, skip);
     count_launch(2);
     CERA_CUDA_TRY(cudaGetLastError());
     CERA_TRY(launch_tp_exchange(h->ep, nullptr, 0, 1, st));  // every rank's entries have landed
@@ -626,6 +652,11 @@ int32_t cera_cuda_moe_ep_status(cera_cuda_moe *h, uint32_t *status_out) {
     *status_out = 0;
     if (h->ep_size < 2) return CERA_CUDA_OK;
     CERA_CUDA_TRY(cudaMemcpy(status_out, h->ep_words + 16, 4, cudaMemcpyDeviceToHost));
+    if (*status_out & EP_STATUS_OVERFLOW && !(*status_out & 0x80000000u))
+        return fail(CERA_CUDA_ERR_BAD_ARG,
+                    "moe expert-parallel call: the ranks' tokens route more entries to rank %u than its receive buffer holds "
+                    "(the layer was created for %zu tokens in total); nothing was exchanged and the output is undefined",
+                    (*status_out >> 24) & 0x3Fu, h->max_total);
     if (*status_out)
         return fail(CERA_CUDA_ERR_TIMEOUT, "moe expert-parallel exchange %u: rank %u waited for rank %u too long", (*status_out & 0xFFFFFFu) - 1,
                     h->ep_rank, (*status_out >> 24) & 0x7Fu);

@@ -174,7 +174,9 @@ CERA_API int32_t cera_cuda_prefill_attention(const float *q_dev, const void *k_c
  * are rejected with CERA_CUDA_ERR_BAD_ARG.  The call allocates nothing.  The first call on each
  * device looks up the array's device address (cudaGetSymbolAddress, with that device current), so
  * make that first call before starting any stream capture.  All calls on a device share the array:
- * two calls that overlap on the GPU (different streams) race on it; calls on one stream do not. */
+ * two calls that overlap on the GPU (different streams) race on it; calls on one stream do not.
+ * The device that owns `stream` (and the buffers) must be the current device of the calling thread:
+ * the array's address is looked up for the current device. */
 CERA_API int32_t cera_cuda_decode_attention_noalloc(const float *q_dev, const void *k_cache_dev,
                                                     const void *v_cache_dev, int32_t kv_f16,
                                                     size_t n_heads, size_t n_kv_heads, size_t head_dim,
@@ -358,7 +360,9 @@ CERA_API int32_t cera_cuda_moe_ffn(cera_cuda_moe *moe, const float *x_dev, size_
  * tokens are dispatched to the ranks that own their experts and the results combined back, all by
  * peer stores from the kernels.  Outputs are bit-identical to the single-GPU layer.  A peer that does
  * not arrive within CERA_CUDA_TP_TIMEOUT_MS leaves a status word that cera_cuda_moe_ep_status
- * (call it after synchronising the stream) turns into CERA_CUDA_ERR_TIMEOUT. */
+ * (call it after synchronising the stream) turns into CERA_CUDA_ERR_TIMEOUT.  If the ranks together
+ * route more entries to one rank than max_total_tokens x n_used, the call stores nothing into any
+ * peer, its output is undefined and cera_cuda_moe_ep_status returns CERA_CUDA_ERR_BAD_ARG. */
 CERA_API int32_t cera_cuda_moe_create_ep(uint32_t n_expert, uint32_t n_used, uint32_t hidden, uint32_t ff,
                                          int32_t ggml_type, const void *gate_exps, const void *up_exps,
                                          const void *down_exps, size_t gate_up_bytes, size_t down_bytes,

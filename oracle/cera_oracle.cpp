@@ -827,28 +827,56 @@ void cera_oracle_rope(float *q, float *k, size_t pos, size_t nh, size_t nkv, siz
     for (size_t h = 0; h < nkv; ++h) rope_head(k + h * hd, (float)pos, hd, base, ff, rope_type);
 }
 
+// Decode attention of one token (cera/src/model/transformer.rs:1166-1305).  The score and value loops
+// follow what the reference runs on an x86 host with AVX2+FMA(+F16C) - the host class whose int8 tier the
+// GEMV restatement above follows - whenever head_dim is a multiple of 8 and at most 256
+// (cera/src/backend/cpu.rs:3264-3290, 3330-3352): scores are two 8-lane FMA accumulators over alternating
+// 8-wide slices of the head, added, then hsum256 (cpu.rs:3522-3585, 3489-3497); the value sum is one FMA per
+// output element per position, in position order (cpu.rs:3587-3625).  f16 caches widen each element first
+// (vcvtph2ps is exact; cpu.rs attn_scores_f16_avx2 / attn_values_f16_avx2).  Other head sizes take the
+// reference's scalar loops (cpu.rs:3292-3300, 3354-3362).
 void cera_oracle_decode_attention(const float *q, const void *kc, const void *vc, int kv_f16,
                                   size_t nh, size_t nkv, size_t hd, size_t seq, float scale,
                                   float *out, float *scores) {
     const size_t kv_dim = nkv * hd, group = nh / nkv;
     const float *kf = (const float *)kc, *vf = (const float *)vc;
     const uint16_t *kh = (const uint16_t *)kc, *vh = (const uint16_t *)vc;
+    const bool vec = hd % 8 == 0 && hd <= 256;
     for (size_t h = 0; h < nh; ++h) {
         const float *qh = q + h * hd;
         const size_t off = (h / group) * hd;
         for (size_t t = 0; t < seq; ++t) {
-            float dot = 0.0f;
-            for (size_t d = 0; d < hd; ++d)
-                dot += qh[d] * (kv_f16 ? h2f(kh[t * kv_dim + off + d]) : kf[t * kv_dim + off + d]);
-            scores[t] = dot * scale;
+            const size_t base = t * kv_dim + off;
+            auto kat = [&](size_t d) { return kv_f16 ? h2f(kh[base + d]) : kf[base + d]; };
+            if (vec) {
+                float s0[8] = {0, 0, 0, 0, 0, 0, 0, 0}, s1[8] = {0, 0, 0, 0, 0, 0, 0, 0}, s[8];
+                const size_t nv = hd / 8;
+                size_t i = 0;
+                for (; i + 2 <= nv; i += 2)
+                    for (int L = 0; L < 8; ++L) {
+                        s0[L] = std::fmaf(qh[8 * i + L], kat(8 * i + L), s0[L]);
+                        s1[L] = std::fmaf(qh[8 * (i + 1) + L], kat(8 * (i + 1) + L), s1[L]);
+                    }
+                if (i < nv)
+                    for (int L = 0; L < 8; ++L) s0[L] = std::fmaf(qh[8 * i + L], kat(8 * i + L), s0[L]);
+                for (int L = 0; L < 8; ++L) s[L] = s0[L] + s1[L];
+                scores[t] = hsum8(s) * scale;
+            } else {
+                float dot = 0.0f;
+                for (size_t d = 0; d < hd; ++d) dot += qh[d] * kat(d);
+                scores[t] = dot * scale;
+            }
         }
         cera_oracle_softmax(scores, seq);
         float *o = out + h * hd;
         for (size_t d = 0; d < hd; ++d) o[d] = 0.0f;
         for (size_t t = 0; t < seq; ++t) {
             const float s = scores[t];
-            for (size_t d = 0; d < hd; ++d)
-                o[d] += s * (kv_f16 ? h2f(vh[t * kv_dim + off + d]) : vf[t * kv_dim + off + d]);
+            const size_t base = t * kv_dim + off;
+            for (size_t d = 0; d < hd; ++d) {
+                const float v = kv_f16 ? h2f(vh[base + d]) : vf[base + d];
+                o[d] = vec ? std::fmaf(s, v, o[d]) : o[d] + s * v;
+            }
         }
     }
 }

@@ -57,6 +57,29 @@ def main():
             ok = ok and same and stable
         moe.close()
         dist.barrier()
+    # More tokens than the layer was created for (every rank passes its full max_tokens while max_total_tokens
+    # allows half of that in total): the plan must notice before anything is stored into a peer's receive
+    # buffer, every rank must report the named error, and the layer must not hang.
+    t, E, used, hs, ff = cb.Q4_0, 8, 2, 256, 128
+    q = lambda n, seed: cb.quantize_weights(t, cb.synth_normal(n, seed=seed, sigma=0.02))
+    per = 16
+    moe = cb.MoeFfn(E, used, hs, ff, t, q(E * ff * hs, 1), q(E * ff * hs, 2), q(E * hs * ff, 3), cb.synth_normal(E * hs, seed=4, sigma=0.05),
+                    max_tokens=per, ep=(rank, world), max_total_tokens=per * world // 2)
+    tp.connect(moe)
+    moe(cb.synth_normal(per * hs, seed=50 + rank, sigma=1.0).view(per, hs))
+    torch.cuda.synchronize()
+    try:
+        moe.check_status()
+        refused = False
+    except cb.CeraCudaError as e:
+        refused = e.code == 1 and "receive buffer" in str(e)
+    votes = [None] * world
+    dist.all_gather_object(votes, refused)
+    if rank == 0:
+        report["overflow_refused_on_every_rank"] = all(votes)
+        ok = ok and all(votes)
+    moe.close()
+    dist.barrier()
     flag = torch.tensor([1 if ok else 0])
     dist.broadcast(flag, 0)
     if rank == 0:

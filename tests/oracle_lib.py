@@ -307,3 +307,84 @@ class OracleModel:
 
     def __del__(self):
         self.close()
+
+
+# ---- seeded synthetic llama models, generated on the host --------------------------------------
+# The same tensors cera_b200.synth.build_llama generates on the device (same seeds, generator and
+# quantizer rules; a CPU test holds the two definitions together), built without touching the
+# CUDA library so that CPU-only legs can use them.
+LLAMA3_8B = dict(n_layers=32, hidden_size=4096, intermediate_size=14336, n_heads=32, n_kv_heads=8, head_dim=128,
+                 vocab_size=128256, rope_theta=500000.0, rms_norm_eps=1e-5, rope_type=0)
+ROLE = dict(TOKEN_EMBD=0, OUTPUT_NORM=1, OUTPUT=2, ATTN_NORM=3, ATTN_Q=4, ATTN_K=5, ATTN_V=6, ATTN_OUTPUT=7,
+            FFN_NORM=8, FFN_GATE=9, FFN_UP=10, FFN_DOWN=11, ROPE_FREQS=12)
+DEFAULT_TYPES = {"TOKEN_EMBD": Q4_K, "OUTPUT": Q6_K, "ATTN_Q": Q4_K, "ATTN_K": Q4_K, "ATTN_V": Q4_K,
+                 "ATTN_OUTPUT": Q4_K, "FFN_GATE": Q4_K, "FFN_UP": Q4_K, "FFN_DOWN": Q6_K}
+
+
+def tensor_seed(seed, role, layer):
+    return (seed * 1000003 + int(role) * 4099 + layer + 1) & 0xFFFFFFFFFFFFFFFF
+
+
+def prompt_tokens(n, vocab, seed):
+    mask = (1 << 64) - 1
+    out = np.empty(n, dtype=np.uint32)
+    for i in range(n):
+        x = (i + seed * 0x9E3779B97F4A7C15 + 0x9E3779B97F4A7C15) & mask
+        x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & mask
+        x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & mask
+        x ^= x >> 31
+        out[i] = x % vocab
+    return out
+
+
+def synth_quantized(t, rows, cols, seed, sigma=0.02, threads=1):
+    """rows x cols of sigma * IH12(seed, i), quantized to block type t; row ranges in parallel threads."""
+    e, b = BLOCK[t]
+    rb = cols // e * b
+    out = np.empty(rows * rb, dtype=np.uint8)
+
+    def part(lo, hi):
+        w = np.empty((hi - lo) * cols, dtype=np.float32)
+        _lib.cera_oracle_synth_normal(_ptr(w), w.size, seed, lo * cols, C.c_float(sigma))
+        dst = out[lo * rb:hi * rb]
+        assert _lib.cera_oracle_quantize_weights(t, _ptr(w), w.size, _ptr(dst)) == 0
+
+    if threads <= 1 or rows < 4 * threads:
+        part(0, rows)
+    else:
+        from concurrent.futures import ThreadPoolExecutor
+        per = -(-rows // (4 * threads))
+        with ThreadPoolExecutor(threads) as ex:
+            list(ex.map(lambda lo: part(lo, min(rows, lo + per)), range(0, rows, per)))
+    return out
+
+
+def build_oracle_llama(cfg, seed=0, sigma=0.02, types=None, max_seq_len=64, kv_f16=0, threads=1):
+    """OracleModel of cfg with the tensors of cera_b200.synth.build_llama(cfg, seed, sigma, types)."""
+    types = {**DEFAULT_TYPES, **(types or {})}
+    m = OracleModel(**cfg, max_seq_len=max_seq_len, kv_f16=kv_f16, n_threads=threads)
+    hs, ff = cfg["hidden_size"], cfg["intermediate_size"]
+    qd, kvd = cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"]
+
+    def matrix(role, layer, rows, cols):
+        t = types[role]
+        raw = synth_quantized(t, rows, cols, tensor_seed(seed, ROLE[role], layer), sigma, threads)
+        m.set_tensor(ROLE[role], layer, t, rows, cols, raw)
+
+    def ones(role, layer, n):
+        m.set_tensor(ROLE[role], layer, F32, 1, n, np.ones(n, dtype=np.float32))
+
+    matrix("TOKEN_EMBD", 0, cfg["vocab_size"], hs)
+    matrix("OUTPUT", 0, cfg["vocab_size"], hs)
+    ones("OUTPUT_NORM", 0, hs)
+    for l in range(cfg["n_layers"]):
+        ones("ATTN_NORM", l, hs)
+        ones("FFN_NORM", l, hs)
+        matrix("ATTN_Q", l, qd, hs)
+        matrix("ATTN_K", l, kvd, hs)
+        matrix("ATTN_V", l, kvd, hs)
+        matrix("ATTN_OUTPUT", l, hs, qd)
+        matrix("FFN_GATE", l, ff, hs)
+        matrix("FFN_UP", l, ff, hs)
+        matrix("FFN_DOWN", l, hs, ff)
+    return m

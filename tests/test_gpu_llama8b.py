@@ -1,0 +1,52 @@
+"""The benchmark's own model at full shape: 128 greedy tokens after a 512-token prompt must equal the CPU
+reference stream (tests/golden/llama8b_stream.json, written by tests/golden/make_llama8b_stream.py from the
+oracle).  A fork fails the test; the message classifies it with the reference's near-tie rule
+(cera/tests/gpu_transformer_parity.rs:168-238) so that the cause can be read off the report."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from gpu_util import TIE_FRACTION_TIGHT, need_gpu
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "llama8b_stream.json")
+N_DECODE = 128
+
+
+def _fork_report(i, got, gold):
+    want, top1, id2, top2, spread = (gold["stream"][i], gold["top1_logit"][i], gold["top2_id"][i], gold["top2_logit"][i],
+                                     gold["top8_spread"][i])
+    gap = top1 - top2
+    near = got == id2 and gap <= TIE_FRACTION_TIGHT * spread
+    return (f"stream forks at decoded token {i}: device picked {got}, reference picked {want} "
+            f"(reference top-1 {top1:.6f}, runner-up {id2} at {top2:.6f}, gap {gap:.3e}, top-8 spread {spread:.3e}; "
+            f"{'a near-tie by the reference rule' if near else 'NOT a near-tie'})")
+
+
+def test_llama8b_greedy_stream_equals_the_cpu_reference_stream():
+    need_gpu()
+    from cera_b200 import synth
+    with open(GOLDEN) as f:
+        gold = json.load(f)
+    cfg = dict(synth.LLAMA3_8B)
+    plen = gold["prompt_len"]
+    model = synth.build_llama(cfg, seed=gold["model_seed"], max_seq_len=plen + N_DECODE + 8)
+    try:
+        prompt = synth.prompt_tokens(plen, cfg["vocab_size"], seed=gold["prompt_seed"])
+        # the reference stream's prompt arithmetic: every prompt position through the decode kernels
+        for pos, t in enumerate(prompt[:-1]):
+            model.forward_prefill(np.array([t], dtype=np.uint32), pos, want_logits=False)
+        logits = model.forward(int(prompt[-1]), plen - 1)
+        first = int(np.argmax(logits))
+        assert first == gold["stream"][0], _fork_report(0, first, gold)
+        assert abs(float(logits[first]) - gold["top1_logit"][0]) <= 1e-3 * abs(gold["top1_logit"][0]) + 1e-4
+        toks, _ = model.generate_greedy(first, plen, N_DECODE - 1)
+        stream = [first] + [int(t) for t in toks]
+        for i, (g, w) in enumerate(zip(stream, gold["stream"][:N_DECODE])):
+            assert g == w, _fork_report(i, g, gold)
+        assert len(stream) == N_DECODE
+    finally:
+        model.close()

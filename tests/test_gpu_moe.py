@@ -122,6 +122,15 @@ def test_lfm2moe_layer_shape():
     _run(cb.Q4_0, n_expert=32, n_used=4, hidden=2048, ff=1792, n=24, seed=51)
 
 
+def test_lfm2moe_config5_512_tokens():
+    """The routed-FFN configuration at its full size: 512 tokens of N(0, 1) hidden states through 32 Q4_0
+    experts of 1792 x 2048, top-4 (the expert-grouped tensor-core path with ragged per-expert counts),
+    against the per-token composition of the reference."""
+    need_gpu()
+    import cera_b200 as cb
+    _run(cb.Q4_0, n_expert=32, n_used=4, hidden=2048, ff=1792, n=512, seed=71)
+
+
 def test_contract_errors():
     need_gpu()
     import torch

@@ -98,3 +98,4 @@ def test_expert_parallel_ffn_reproduces_single_gpu():
     assert report["world"] == world and len(report["cases"]) == 3
     for case in report["cases"]:
         assert case["bit_identical"] and case["repeatable"], case
+    assert report["overflow_refused_on_every_rank"]
