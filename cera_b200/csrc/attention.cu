@@ -473,8 +473,19 @@ int32_t launch_cluster(bool f16, uint32_t cl, cudaStream_t st, const float *q, c
 
 }  // namespace
 
-size_t attn_workspace_bytes(size_t n_heads, size_t head_dim, size_t) {
-    return n_heads * MAX_SPLITS * (head_dim + 2) * sizeof(float);
+constexpr uint32_t ATT_EXACT_FLAG = 0x200;  // plan word of the reference-order kernels (attention_exact.cu)
+
+// Enough for either decode path: per-split partial records (split kernels) or the score and probability rows of every
+// head (reference-order kernels).
+size_t attn_workspace_bytes(size_t n_heads, size_t head_dim, size_t seq_len) {
+    const size_t split = n_heads * MAX_SPLITS * (head_dim + 2) * sizeof(float);
+    const size_t exact = attn_exact_workspace_bytes(n_heads, seq_len);
+    return split > exact ? split : exact;
+}
+
+uint32_t attn_plan(size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t seq_len_hint) {
+    if (attn_exact_supports(n_heads, n_kv_heads, head_dim)) return attn_exact_plan(seq_len_hint);
+    return attn_pick_splits(n_kv_heads, seq_len_hint);
 }
 
 // Plan for a decode attention over seq_len_hint positions.  Up to ATT_CLUSTER_MAX_SEQ positions: the one-launch
@@ -527,7 +538,10 @@ int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *v
                     n_heads, n_kv_heads);
     const size_t G = n_heads / n_kv_heads;
     if (seq_len == 0 && !seq_len_dev) return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: empty KV cache");
-    if (workspace_bytes < attn_workspace_bytes(n_heads, head_dim, seq_len))
+    if (n_splits & ATT_EXACT_FLAG)
+        return launch_decode_attention_exact(q, kc, vc, kv_f16, n_heads, n_kv_heads, head_dim, seq_len, seq_len_dev, n_splits, scale,
+                                             out, workspace, workspace_bytes, scales, quants, sums, st, tp);
+    if (workspace_bytes < attn_workspace_bytes(n_heads, head_dim, 0))
         return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: workspace of %zu bytes is too small", workspace_bytes);
     const bool streamed = (n_splits & ATT_STREAM_FLAG) != 0;
     if (streamed) n_splits &= ~ATT_STREAM_FLAG;
@@ -616,7 +630,7 @@ int32_t launch_decode_attention(const float *q, const void *kc, const void *vc, 
                                 void *workspace, size_t workspace_bytes, float *scales, int8_t *quants, int16_t *sums,
                                 cudaStream_t st) {
     return launch_decode_attention_ex(q, kc, vc, kv_f16, n_heads, n_kv_heads, head_dim, seq_len, nullptr,
-                                      attn_pick_splits(n_kv_heads, seq_len), scale, out, workspace, workspace_bytes,
+                                      attn_plan(n_heads, n_kv_heads, head_dim, seq_len), scale, out, workspace, workspace_bytes,
                                       scales, quants, sums, st);
 }
 

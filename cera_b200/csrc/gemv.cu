@@ -173,6 +173,9 @@ int32_t launch_gemv(const GemvSeg *segs, int n_segs, const ActView &x, size_t n_
     if (n_segs < 1 || n_segs > MAX_SEGS) return fail(CERA_CUDA_ERR_BAD_ARG, "gemv: %d segments", n_segs);
     if (n_cols == 1 && ldy == 1 && !batch_tile && !force_direct()) {
         bool taken = false;
+        // K-quants: the kernel whose f32 order is the reference's (bit-identical results), else the streaming kernels
+        CERA_TRY(launch_gemv_exact(segs, n_segs, x, epilogue, nullptr, st, &taken, tp));
+        if (taken) return CERA_CUDA_OK;
         CERA_TRY(launch_gemv_fused(segs, n_segs, x, epilogue, nullptr, st, &taken, tp));
         if (taken) return CERA_CUDA_OK;
     }

@@ -151,11 +151,17 @@ __global__ void __launch_bounds__(RW_THREADS) gemv_rows_kernel(const RowsParams 
 }
 
 __global__ void rope_table_kernel(const uint32_t *__restrict__ pos_dev, uint32_t half, float ts, const float *__restrict__ ff,
-                                  float *__restrict__ table) {
+                                  float *__restrict__ table, const float *__restrict__ full) {
     pdl_trigger();
     pdl_wait();
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= half) return;
+    if (full) {  // host-computed cos / sin of every position: copy this position's row
+        const size_t at = ((size_t)*pos_dev * half + i) * 2;
+        table[2 * i] = full[at];
+        table[2 * i + 1] = full[at + 1];
+        return;
+    }
     float theta = (float)*pos_dev;
     for (uint32_t s = 0; s < i; ++s) theta = __fmul_rn(theta, ts);
     if (ff) theta = __fdiv_rn(theta, ff[i]);
@@ -220,11 +226,11 @@ int32_t launch_gemv_rows(const GemvSeg *segs, int n_segs, const ActView &x, int 
 }
 
 int32_t launch_rope_table(const uint32_t *pos_dev, size_t head_dim, float theta_scale, const float *freq_factors,
-                          float *table, cudaStream_t st) {
+                          float *table, cudaStream_t st, const float *full_table) {
     const uint32_t half = (uint32_t)(head_dim / 2);
     count_launch();
     return check_cuda(launch_k(rope_table_kernel, dim3((half + 63) / 64), dim3(64), 0, st, pos_dev, half, theta_scale,
-                               freq_factors, table),
+                               freq_factors, table, full_table),
                       "rope table launch");
 }
 

@@ -1,5 +1,7 @@
 // Small kernels around the matmuls on the decode path: RoPE (+KV append),
 // embedding row lookup, argmax.
+#include <cmath>
+
 #include "formats.cuh"
 #include "ops.h"
 
@@ -14,7 +16,8 @@ namespace {
 // the path's f32 tolerance).
 __global__ void rope_kernel(float *q, float *k, const float *__restrict__ v, uint32_t pos_imm,
                             const uint32_t *__restrict__ pos_dev, uint32_t n_heads, uint32_t n_kv_heads, uint32_t hd,
-                            float ts, const float *__restrict__ ff, int neox, void *k_cache, void *v_cache, int kv_f16) {
+                            float ts, const float *__restrict__ ff, int neox, void *k_cache, void *v_cache, int kv_f16,
+                            const float *__restrict__ table) {
     pdl_trigger();
     pdl_wait();
     const uint32_t half = hd / 2;
@@ -28,11 +31,16 @@ __global__ void rope_kernel(float *q, float *k, const float *__restrict__ v, uin
     if (v) v += (size_t)blockIdx.y * kv_dim;
     if (idx < total) {
         const uint32_t h = idx / half, i = idx % half;
-        float theta = (float)pos;
-        for (uint32_t s = 0; s < i; ++s) theta = __fmul_rn(theta, ts);
-        if (!neox && ff) theta = __fdiv_rn(theta, ff[i]);
         float sn, cs;
-        sincosf(theta, &sn, &cs);
+        if (table) {  // cos / sin of every (position, pair), computed on the host with the C library the reference's host uses
+            cs = table[((size_t)pos * half + i) * 2];
+            sn = table[((size_t)pos * half + i) * 2 + 1];
+        } else {
+            float theta = (float)pos;
+            for (uint32_t s = 0; s < i; ++s) theta = __fmul_rn(theta, ts);
+            if (!neox && ff) theta = __fdiv_rn(theta, ff[i]);
+            sincosf(theta, &sn, &cs);
+        }
         float *head = h < n_heads ? q + (size_t)h * hd : k + (size_t)(h - n_heads) * hd;
         const uint32_t i0 = neox ? i : 2 * i, i1 = neox ? i + half : 2 * i + 1;
         const float x0 = head[i0], x1 = head[i1];
@@ -223,7 +231,7 @@ __global__ void argmax_stage2(const uint32_t *__restrict__ scratch, int blocks, 
 
 int32_t launch_rope(float *q, float *k, const float *v, size_t pos, const uint32_t *pos_dev, size_t n_heads,
                     size_t n_kv_heads, size_t head_dim, float theta_scale, const float *freq_factors, int rope_type,
-                    void *k_cache, void *v_cache, int kv_f16, cudaStream_t st) {
+                    void *k_cache, void *v_cache, int kv_f16, cudaStream_t st, const float *table) {
     if (!q || !k) return fail(CERA_CUDA_ERR_BAD_ARG, "rope: null argument");
     if (head_dim == 0 || head_dim % 2) return fail(CERA_CUDA_ERR_BAD_ARG, "rope: head_dim %zu must be even", head_dim);
     if (v_cache && !v) return fail(CERA_CUDA_ERR_BAD_ARG, "rope: v_cache without v");
@@ -232,8 +240,28 @@ int32_t launch_rope(float *q, float *k, const float *v, size_t pos, const uint32
     count_launch();
     return check_cuda(launch_k(rope_kernel, dim3((total + threads - 1) / threads), dim3(threads), 0, st, q, k, v, (uint32_t)pos,
                                pos_dev, (uint32_t)n_heads, (uint32_t)n_kv_heads, (uint32_t)head_dim, theta_scale, freq_factors,
-                               rope_type == 1 ? 1 : 0, k_cache, v_cache, kv_f16),
+                               rope_type == 1 ? 1 : 0, k_cache, v_cache, kv_f16, table),
                       "rope launch");
+}
+
+// cos / sin of every (position, rotation pair) on the host, operation for operation as the reference's loop
+// (cera/src/backend/cpu.rs:5041-5054, 5161-5180): theta starts at the position and is multiplied by
+// base^(-2/head_dim) per pair in f32, NORM pairs divide by their frequency factor, and sin / cos come from the C
+// library - the one a CPU build of the reference on the same host calls, whereas the device's sincosf may differ
+// from it in the last bit.  out: [n_pos][head_dim/2][2] = {cos, sin}.
+void rope_table_host(size_t n_pos, size_t head_dim, float rope_theta, const float *freq_factors, int rope_type, float *out) {
+    const size_t half = head_dim / 2;
+    const float ts = std::pow(rope_theta, -2.0f / (float)head_dim);
+    const bool neox = rope_type == 1;
+    for (size_t pos = 0; pos < n_pos; ++pos) {
+        float theta = (float)pos;
+        for (size_t i = 0; i < half; ++i) {
+            const float t = neox ? theta : theta / (freq_factors ? freq_factors[i] : 1.0f);
+            out[(pos * half + i) * 2] = std::cos(t);
+            out[(pos * half + i) * 2 + 1] = std::sin(t);
+            theta *= ts;
+        }
+    }
 }
 
 int32_t launch_embed(const WeightView &w, uint32_t token, const uint32_t *token_dev, float *out, cudaStream_t st) {
@@ -246,7 +274,7 @@ int32_t launch_embed(const WeightView &w, uint32_t token, const uint32_t *token_
 
 int32_t launch_rope_batch(float *q, float *k, const float *v, size_t start_pos, size_t n, size_t n_heads, size_t n_kv_heads,
                           size_t head_dim, float theta_scale, const float *freq_factors, int rope_type, void *k_cache,
-                          void *v_cache, int kv_f16, cudaStream_t st) {
+                          void *v_cache, int kv_f16, cudaStream_t st, const float *table) {
     if (!q || !k) return fail(CERA_CUDA_ERR_BAD_ARG, "rope: null argument");
     if (head_dim == 0 || head_dim % 2) return fail(CERA_CUDA_ERR_BAD_ARG, "rope: head_dim %zu must be even", head_dim);
     if (n == 0) return CERA_CUDA_OK;
@@ -255,7 +283,7 @@ int32_t launch_rope_batch(float *q, float *k, const float *v, size_t start_pos, 
     count_launch();
     return check_cuda(launch_k(rope_kernel, dim3((total + threads - 1) / threads, (unsigned)n), dim3(threads), 0, st, q, k, v,
                                (uint32_t)start_pos, (const uint32_t *)nullptr, (uint32_t)n_heads, (uint32_t)n_kv_heads,
-                               (uint32_t)head_dim, theta_scale, freq_factors, rope_type == 1 ? 1 : 0, k_cache, v_cache, kv_f16),
+                               (uint32_t)head_dim, theta_scale, freq_factors, rope_type == 1 ? 1 : 0, k_cache, v_cache, kv_f16, table),
                       "rope launch");
 }
 
@@ -310,7 +338,7 @@ int32_t cera_cuda_rope(float *q_dev, float *k_dev, size_t pos, size_t n_heads, s
                        float freq_base, const float *freq_factors_dev, int32_t rope_type, void *stream) {
     const float ts = powf(freq_base, -2.0f / (float)head_dim);
     return launch_rope(q_dev, k_dev, nullptr, pos, nullptr, n_heads, n_kv_heads, head_dim, ts, freq_factors_dev,
-                       rope_type, nullptr, nullptr, 0, (cudaStream_t)stream);
+                       rope_type, nullptr, nullptr, 0, (cudaStream_t)stream, nullptr);
 }
 
 }  // extern "C"

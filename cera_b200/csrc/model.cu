@@ -87,6 +87,7 @@ struct cera_cuda_model {
     float *h_logits = nullptr;    // pinned host staging for logits
     float theta_scale = 0.0f;
     float *rope_cs = nullptr;  // [head_dim/2][2] cos/sin at the current position
+    float *rope_table = nullptr;  // [max_seq_len][head_dim/2][2] cos/sin of every position, computed on the host (null: too large)
     cudaStream_t stream = nullptr;
     std::map<uint32_t, cudaGraphExec_t> graphs;  // key = kind | n_splits << 8
     size_t seq_len = 0;
@@ -176,7 +177,7 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
     if (tp) CERA_TRY(launch_tp_tick(m->tp_words, st));
     CERA_TRY(launch_embed(m->embd->v, 0, m->dyn, m->hidden, st));
     const bool norm_rope = c.rope_type == 0;
-    if (norm_rope) CERA_TRY(launch_rope_table(m->dyn + 1, c.head_dim, m->theta_scale, m->rope_freqs, m->rope_cs, st));
+    if (norm_rope) CERA_TRY(launch_rope_table(m->dyn + 1, c.head_dim, m->theta_scale, m->rope_freqs, m->rope_cs, st, m->rope_table));
     for (uint32_t li = 0; li < n_layers; ++li) {
         Layer &L = m->layers[li];
         const uint32_t s0 = 4 * li;
@@ -205,7 +206,8 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
             f.kv_f16 = c.kv_f16;
             f.head_dim = c.head_dim;
             f.kv_dim = (uint32_t)m->l_kvd;
-            CERA_TRY(launch_gemv_fused(segs, 3, m->act_hs.view(), EPI_ROPE_KV, &f, st, &fused_qkv));
+            CERA_TRY(launch_gemv_exact(segs, 3, m->act_hs.view(), EPI_ROPE_KV, &f, st, &fused_qkv));
+            if (!fused_qkv) CERA_TRY(launch_gemv_fused(segs, 3, m->act_hs.view(), EPI_ROPE_KV, &f, st, &fused_qkv));
         }
         if (fused_qkv) {
         } else if (L.wq->v.type == L.wk->v.type && L.wq->v.type == L.wv->v.type) {
@@ -224,7 +226,7 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
         }
         if (!fused_qkv)
             CERA_TRY(launch_rope(m->q, m->k, m->v, 0, m->dyn + 1, m->l_heads, m->l_kv_heads, c.head_dim, m->theta_scale,
-                                 m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st));
+                                 m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st, m->rope_table));
         const ActBuf aq = act_slice(m->act_q, m->l_qd);
         CERA_TRY(launch_decode_attention_ex(m->q, L.kc, L.vc, c.kv_f16, m->l_heads, m->l_kv_heads, c.head_dim, 0,
                                             m->dyn + 2, n_splits, scale, m->attn, m->attn_ws, m->attn_ws_bytes,
@@ -319,7 +321,7 @@ int32_t run_token(cera_cuda_model *m, uint32_t token, size_t pos, int kind) {
     if (pos != m->seq_len) return fail(CERA_CUDA_ERR_STATE, "forward: pos %zu != seq_len %zu", pos, m->seq_len);
     if (pos >= c.max_seq_len) return fail(CERA_CUDA_ERR_BAD_ARG, "forward: pos %zu exceeds max_seq_len %u", pos, c.max_seq_len);
     if (m->tp_size > 1 && !m->tp_connected) return fail(CERA_CUDA_ERR_STATE, "forward: tensor-parallel model is not connected to its peers");
-    const uint32_t n_splits = attn_pick_splits(m->l_kv_heads, pos + 1);
+    const uint32_t n_splits = attn_plan(m->l_heads, m->l_kv_heads, m->cfg.head_dim, pos + 1);
     cudaGraphExec_t g = nullptr;
     CERA_TRY(get_graph(m, kind, n_splits, &g));
     m->h_dyn[0] = token;
@@ -352,7 +354,7 @@ int32_t prefill_chunk(cera_cuda_model *m, const uint32_t *tokens, size_t n, size
         CERA_TRY(launch_gemm_ex(L.wk->v, m->pf_act_hs.view(), n, m->pf_k, 1, kvd, EPI_STORE, st));
         CERA_TRY(launch_gemm_ex(L.wv->v, m->pf_act_hs.view(), n, m->pf_v, 1, kvd, EPI_STORE, st));
         CERA_TRY(launch_rope_batch(m->pf_q, m->pf_k, m->pf_v, start_pos, n, c.n_heads, c.n_kv_heads, c.head_dim,
-                                   m->theta_scale, m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st));
+                                   m->theta_scale, m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st, m->rope_table));
         CERA_TRY(launch_prefill_attention(m->pf_q, L.kc, L.vc, c.kv_f16, c.n_heads, c.n_kv_heads, c.head_dim, n, start_pos,
                                           scale, m->pf_attn, st));
         CERA_TRY(launch_quantize(m->pf_attn, qd, n, false, m->pf_act_q.scales, m->pf_act_q.quants, m->pf_act_q.sums, st));
@@ -606,6 +608,22 @@ int32_t cera_cuda_model_finalize(cera_cuda_model *m) {
     CERA_TRY(dev_alloc(m, (void **)&m->dyn, 4 * 4));
     CERA_TRY(dev_alloc(m, (void **)&m->tok_out, 4));
     CERA_TRY(dev_alloc(m, (void **)&m->rope_cs, (size_t)c.head_dim * 4));
+    {
+        // cos / sin of every position from the host's C library (see rope_table_host); skipped beyond 256 MB, where
+        // the kernels evaluate sincosf themselves
+        const size_t half = c.head_dim / 2, bytes = (size_t)c.max_seq_len * half * 2 * sizeof(float);
+        if (bytes <= ((size_t)256 << 20)) {
+            std::vector<float> ff;
+            if (m->rope_freqs) {
+                ff.resize(half);
+                CERA_CUDA_TRY(cudaMemcpy(ff.data(), m->rope_freqs, half * sizeof(float), cudaMemcpyDeviceToHost));
+            }
+            std::vector<float> table((size_t)c.max_seq_len * half * 2);
+            rope_table_host(c.max_seq_len, c.head_dim, c.rope_theta, ff.empty() ? nullptr : ff.data(), c.rope_type, table.data());
+            CERA_TRY(dev_alloc(m, (void **)&m->rope_table, bytes));
+            CERA_CUDA_TRY(cudaMemcpy(m->rope_table, table.data(), bytes, cudaMemcpyHostToDevice));
+        }
+    }
     m->tok_hist_cap = c.max_seq_len;
     CERA_TRY(dev_alloc(m, (void **)&m->tok_hist, (size_t)m->tok_hist_cap * 4));
     CERA_CUDA_TRY(cudaMallocHost((void **)&m->h_dyn, 8 * 4));
@@ -751,12 +769,12 @@ int32_t cera_cuda_generate_greedy(cera_cuda_model *m, uint32_t first_token, size
     // instantiate every graph the run needs before the timed region
     for (size_t i = 0; i < n; ++i) {
         cudaGraphExec_t g = nullptr;
-        CERA_TRY(get_graph(m, G_CHAIN, attn_pick_splits(m->l_kv_heads, start_pos + i + 1), &g));
+        CERA_TRY(get_graph(m, G_CHAIN, attn_plan(m->l_heads, m->l_kv_heads, m->cfg.head_dim, start_pos + i + 1), &g));
     }
     CERA_CUDA_TRY(cudaEventRecord(e0, m->stream));
     for (size_t i = 0; i < n; ++i) {
         cudaGraphExec_t g = nullptr;
-        CERA_TRY(get_graph(m, G_CHAIN, attn_pick_splits(m->l_kv_heads, start_pos + i + 1), &g));
+        CERA_TRY(get_graph(m, G_CHAIN, attn_plan(m->l_heads, m->l_kv_heads, m->cfg.head_dim, start_pos + i + 1), &g));
         CERA_CUDA_TRY(cudaGraphLaunch(g, m->stream));
     }
     CERA_CUDA_TRY(cudaEventRecord(e1, m->stream));

@@ -29,7 +29,9 @@ enum { EPI_STORE = 0, EPI_ADD = 1, EPI_ROPE_KV = 2 };
 
 // Work fused behind the single-column GEMV (EPI_ROPE_KV).
 struct GemvFusion {
-    const float *rope_cs = nullptr;       // [head_dim/2][2] cos, sin at the current position
+    const float *rope_cs = nullptr;       // [head_dim/2][2] cos, sin at the current position, or with rope_by_pos
+                                          // the table of every position [max_seq][head_dim/2][2]
+    int rope_by_pos = 0;
     const uint32_t *pos_dev = nullptr;
     void *k_cache = nullptr, *v_cache = nullptr;
     int kv_f16 = 0;
@@ -51,9 +53,13 @@ int32_t launch_gemv_tma(const GemvSeg *segs, int n_segs, const ActView &x, int e
 // Tries the TMA-staged kernel, then the register-streaming one.
 int32_t launch_gemv_fused(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
                           cudaStream_t st, bool *taken, const TpHook *tp = nullptr);
+// The same GEMV in the reference's f32 summation order (K-quants, k a multiple of 1024): results are bit-identical to
+// cera's x86 int8 kernels at one activation column.  *taken = false: not its case, nothing launched.
+int32_t launch_gemv_exact(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
+                          cudaStream_t st, bool *taken, const TpHook *tp = nullptr);
 // cos/sin of every rotation pair at position *pos_dev, same arithmetic as launch_rope.
 int32_t launch_rope_table(const uint32_t *pos_dev, size_t head_dim, float theta_scale, const float *freq_factors,
-                          float *table, cudaStream_t st);
+                          float *table, cudaStream_t st, const float *full_table = nullptr);
 int32_t launch_gemm(const WeightView &w, const ActView &x, size_t n, float *out, cudaStream_t st);
 // Tensor-core (mma.sync int8) GEMM for Q4_0 / Q4_K / Q5_K / Q6_K (k a multiple of 256) and n >= 5.  *taken = false: not its case.
 int32_t launch_gemm_mma(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
@@ -77,7 +83,10 @@ int32_t launch_gemv_q5k_f32(const WeightView &w, const float *x, float *y, cudaS
 // (f32, or f16 through the round-to-nearest-even narrow of cera/src/quant.rs:117-164).
 int32_t launch_rope(float *q, float *k, const float *v, size_t pos, const uint32_t *pos_dev, size_t n_heads,
                     size_t n_kv_heads, size_t head_dim, float theta_scale, const float *freq_factors, int rope_type,
-                    void *k_cache, void *v_cache, int kv_f16, cudaStream_t st);
+                    void *k_cache, void *v_cache, int kv_f16, cudaStream_t st, const float *table = nullptr);
+// table (optional, every rope launcher): cos / sin of every (position, rotation pair), [max_pos][head_dim/2][2], as
+// rope_table_host() computes them; the kernels then read the table instead of evaluating sincosf.
+void rope_table_host(size_t n_pos, size_t head_dim, float rope_theta, const float *freq_factors, int rope_type, float *out);
 
 size_t attn_workspace_bytes(size_t n_heads, size_t head_dim, size_t seq_len);
 // q8 outputs optional: the merge pass can emit the Q8_0 form of `out` for the next GEMV.
@@ -87,6 +96,16 @@ int32_t launch_decode_attention(const float *q, const void *kc, const void *vc, 
                                 cudaStream_t st);
 
 uint32_t attn_pick_splits(size_t n_kv_heads, size_t seq_len_hint);
+// The plan word launch_decode_attention_ex takes: the reference-order kernels (attention_exact.cu) whenever they cover
+// the head shape, else attn_pick_splits.
+uint32_t attn_plan(size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t seq_len_hint);
+bool attn_exact_supports(size_t n_heads, size_t n_kv_heads, size_t head_dim);
+uint32_t attn_exact_plan(size_t seq_len_hint);
+size_t attn_exact_workspace_bytes(size_t n_heads, size_t seq_len);
+int32_t launch_decode_attention_exact(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads, size_t n_kv_heads,
+                                      size_t head_dim, size_t seq_len, const uint32_t *seq_len_dev, uint32_t plan, float scale,
+                                      float *out, void *workspace, size_t workspace_bytes, float *scales, int8_t *quants,
+                                      int16_t *sums, cudaStream_t st, const TpHook *tp = nullptr);
 // Split pass of a long-context decode attention through the shared-memory-staged kernel (attention_stream.cu); writes the
 // same per-(head, split) records as the register-resident split kernel.  *taken = false: no instantiation.
 int32_t launch_attention_stream(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_kv_heads, size_t group,
@@ -107,7 +126,7 @@ int32_t launch_embed_batch(const WeightView &w, const uint32_t *tokens_dev, size
 // (token-major); rotated k and v rows are appended to the caches.
 int32_t launch_rope_batch(float *q, float *k, const float *v, size_t start_pos, size_t n, size_t n_heads, size_t n_kv_heads,
                           size_t head_dim, float theta_scale, const float *freq_factors, int rope_type, void *k_cache,
-                          void *v_cache, int kv_f16, cudaStream_t st);
+                          void *v_cache, int kv_f16, cudaStream_t st, const float *table = nullptr);
 // Causal attention of n query tokens (positions start_pos + j) over cache rows [0, start_pos + j]
 // (cera/src/backend/cpu.rs:4028-4241); q and out are token-major [n][n_heads*head_dim].
 int32_t launch_prefill_attention(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_heads,

@@ -74,9 +74,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_kernel(const float *__rest
         double t = red[lane];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-        // 1/sqrt(mean + eps) in f64, narrowed once: the reciprocal square root and the multiplication by 1/n are each
-        // within an f64 ulp of the reference's sqrt and divisions, far below the f32 rounding that follows
-        if (lane == 0) inv_s = (float)rsqrt(t * inv_n + (double)eps);
+        if (lane == 0) inv_s = (float)(1.0 / sqrt(t / (double)n_elem + (double)eps));  // the reference's f64 expression, IEEE division and square root
     }
     __syncthreads();
     const float inv = inv_s;
@@ -139,7 +137,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_q8_kernel(const float *__r
         double t = red[lane];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-        if (lane == 0) inv_s = (float)rsqrt(t * inv_n + (double)eps);
+        if (lane == 0) inv_s = (float)(1.0 / sqrt(t / (double)n_elem + (double)eps));  // the reference's f64 expression, IEEE division and square root
     }
     __syncthreads();
     const float inv = inv_s;

@@ -1,0 +1,105 @@
+"""Decode kernels that reproduce the reference's f32 ARITHMETIC ORDER: their outputs must equal the oracle's
+bit for bit, not merely within the path's tolerance.
+
+Covered: the K-quant GEMV at one activation column (four round-robin 8-lane FMA accumulators, sequential min
+term, hsum256 - cera/src/backend/simd.rs:5693-5878, 5988-6195), RMSNorm (cpu.rs:2479-2496), decode attention
+in the x86 lane order (cpu.rs:3522-3625, 2617-2633), and a whole model wired from them whose logits must be
+bit-identical to the oracle's at every position.
+"""
+import math
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+from gpu_util import assert_bits, need_gpu
+
+pytestmark = pytest.mark.gpu
+
+
+def _cuda(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("t", [O.Q4_K, O.Q5_K, O.Q6_K])
+@pytest.mark.parametrize("m,k", [(64, 4096), (40, 14336), (33, 1024), (1, 2048), (300, 3072)])
+def test_k_quant_gemv_bits(t, m, k):
+    torch = need_gpu()
+    import cera_b200 as cb
+    raw = cb.quantize_weights(t, cb.synth_normal(m * k, seed=77 * t + m, sigma=0.02)).cpu().numpy()
+    x = cb.synth_normal(k, seed=m + k, sigma=1.0)
+    got = cb.gemv(cb.QuantWeight(t, m, k, raw), x).cpu().numpy()
+    xh = x.cpu().numpy()
+    if t == O.Q5_K:  # the Q8_0-activation Q5_K product is this build's extension of the Q4_K kernel: oracle = its restated form
+        xs, xq = O.quantize_q8_0(xh)
+        want = O.gemm_preq(t, raw, xs, xq, m, 1, k).ravel()
+    else:
+        want = O.gemv(t, raw, xh, m, k)
+    assert np.abs(want).max() > 0
+    assert_bits(got, want, f"{O.NAMES[t]} {m}x{k}")
+
+
+@pytest.mark.parametrize("t,m,k", [(O.Q4_K, 4096, 4096), (O.Q4_K, 14336, 4096), (O.Q6_K, 4096, 14336)])
+def test_layer_shape_gemv_bits(t, m, k):
+    """The decode step's own shapes, all rows, against the AVX2 build of the oracle on every host thread."""
+    torch = need_gpu()
+    import os
+    import cera_b200 as cb
+    if not O.has_avx2():
+        pytest.skip("needs the AVX2 build of the oracle")
+    raw = cb.quantize_weights(t, cb.synth_normal(m * k, seed=5 + t, sigma=0.02))
+    x = cb.synth_normal(k, seed=9, sigma=1.0)
+    got = cb.gemv(cb.QuantWeight(t, m, k, raw), x).cpu().numpy()
+    want = O.gemv(t, raw.cpu().numpy(), x.cpu().numpy(), m, k, avx2=True, threads=os.cpu_count() or 4)
+    assert_bits(got, want, f"{O.NAMES[t]} {m}x{k}")
+
+
+@pytest.mark.parametrize("n", [32, 256, 4096, 14336])
+def test_rmsnorm_bits(n):
+    torch = need_gpu()
+    import cera_b200 as cb
+    x = O.synth_normal(n, 31 + n, 2.0)
+    w = O.synth_normal(n, 32, 1.0)
+    assert_bits(cb.rmsnorm(_cuda(torch, x), _cuda(torch, w), 1e-5).cpu().numpy(), O.rmsnorm(x, w, 1e-5), "rmsnorm")
+    out, _ = cb.rmsnorm_q8_0(_cuda(torch, x), _cuda(torch, w), 1e-5)
+    assert_bits(out.cpu().numpy(), O.rmsnorm(x, w, 1e-5), "rmsnorm + q8")
+
+
+@pytest.mark.parametrize("kv_f16", [0, 1])
+@pytest.mark.parametrize("nh,nkv,hd,seq", [(32, 8, 128, 1), (32, 8, 128, 37), (32, 8, 128, 640), (32, 8, 128, 4096),
+                                           (32, 8, 128, 5000), (16, 2, 64, 300), (8, 8, 128, 129), (8, 4, 96, 77)])
+def test_decode_attention_bits(nh, nkv, hd, seq, kv_f16):
+    torch = need_gpu()
+    import cera_b200 as cb
+    kv_dim = nkv * hd
+    kc = cb.synth_normal(seq * kv_dim, seed=seq, sigma=1.0).reshape(seq, kv_dim)
+    vc = cb.synth_normal(seq * kv_dim, seed=seq + 1, sigma=1.0).reshape(seq, kv_dim)
+    q = cb.synth_normal(nh * hd, seed=seq + 2, sigma=1.0)
+    if kv_f16:
+        kc, vc = kc.half(), vc.half()
+    scale = 1.0 / math.sqrt(hd)
+    got = cb.decode_attention(q, kc, vc, nh, nkv, hd, seq, scale).cpu().numpy()
+    kh = kc.cpu().numpy().view(np.uint16) if kv_f16 else kc.cpu().numpy()
+    vh = vc.cpu().numpy().view(np.uint16) if kv_f16 else vc.cpu().numpy()
+    want = O.decode_attention(q.cpu().numpy(), kh, vh, nh, nkv, hd, seq, scale)
+    assert_bits(got, want, f"attention {nh}/{nkv} x {hd}, {seq} positions, f16={kv_f16}")
+
+
+@pytest.mark.parametrize("kv_f16", [0, 1])
+def test_model_logits_bit_identical_to_the_oracle(kv_f16):
+    """A llama-architecture model whose matrices are K-quants with row lengths that are multiples of 1024 runs every
+    projection, norm, rotation and attention on reference-order kernels: logits equal the oracle's bits at every
+    position, so the greedy stream cannot differ."""
+    need_gpu()
+    from cera_b200 import synth
+    cfg = dict(n_layers=3, hidden_size=1024, intermediate_size=2048, n_heads=8, n_kv_heads=2, head_dim=128, vocab_size=2048,
+               rope_theta=500000.0, rms_norm_eps=1e-5, rope_type=0)
+    oracle = O.OracleModel(**cfg, max_seq_len=48, kv_f16=kv_f16, n_threads=4)
+    gpu = synth.build_llama(cfg, seed=17, max_seq_len=48, kv_f16=kv_f16,
+                            sink=lambda r, l, t, rows, cols, d: oracle.set_tensor(int(r), l, t, rows, cols, d))
+    tok = 5
+    for pos in range(40):
+        lg, lo = gpu.forward(tok, pos), oracle.forward(tok, pos)
+        assert_bits(lg, lo, f"logits at position {pos}")
+        tok = int(O.argmax(lo))
+    gpu.close()
