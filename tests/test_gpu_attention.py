@@ -131,11 +131,17 @@ def test_decode_attention_streamed_kernel(nh, nkv, hd, seq, f16):
 def test_decode_attention_rejects_unsupported_shapes():
     torch = need_gpu()
     import cera_b200 as cb
-    q = torch.zeros(6 * 64, device="cuda")
-    kc = torch.zeros(4, 2 * 64, device="cuda")
+    # 18 query heads on 2 KV heads (a group of 9) with head_dim 48: no decode kernel covers it, and the call says so
+    q = torch.zeros(18 * 48, device="cuda")
+    kc = torch.zeros(4, 2 * 48, device="cuda")
     with pytest.raises(cb.CeraCudaError) as e:
-        cb.decode_attention(q, kc, kc, 6, 2, 64, 4, 0.125)
+        cb.decode_attention(q, kc, kc, 18, 2, 48, 4, 0.125)
     assert e.value.code == 2
+    # a group of 3 is served (by the reference-order kernels): finite output of the right size
+    q = torch.ones(6 * 64, device="cuda")
+    kc = torch.ones(4, 2 * 64, device="cuda")
+    out = cb.decode_attention(q, kc, kc, 6, 2, 64, 4, 0.125)
+    assert out.shape[0] == 6 * 64 and bool(torch.isfinite(out).all())
 
 
 @pytest.mark.parametrize("nh,nkv,n,start", [(32, 8, 256, 256), (32, 8, 256, 0), (8, 8, 33, 5), (8, 4, 9, 0), (16, 2, 41, 90),
