@@ -12,11 +12,13 @@
 //
 //   scores kernel : one thread per (position, query head); the G heads of a KV head sit in adjacent
 //                   threads and share the K row.  Scores go to a workspace [n_heads][ld].
-//   values kernel : one CTA per (KV head, 32 output dims).  All threads first turn the scores of the
-//                   group's heads into probabilities (block maximum, ggml_expf, f64 sum by a fixed
-//                   tree, scaling); then 8 threads per head - four output dims each - walk the
-//                   positions in order with one FMA per dim per position, and finally emit the f32
-//                   outputs and their Q8_0 form (a 32-dim slice of a head is one Q8_0 block).
+//   values kernel : one CTA per (KV head, 32 output dims).  Its warps first turn the scores of the
+//                   group's heads into probabilities (maximum, ggml_expf, f64 sum by a fixed tree,
+//                   scaling; the heads side by side), while all threads stage the V slice through
+//                   shared memory with asynchronous copies, four 64-position tiles ahead; then 8
+//                   threads per head - four output dims each - walk the positions in order with one
+//                   FMA per dim per position, and finally emit the f32 outputs and their Q8_0 form
+//                   (a 32-dim slice of a head is one Q8_0 block).
 //
 // The f64 sum of the exponentials is a tree, the reference's a left-to-right loop: the two can differ
 // in the last bits of the f64 sum, which survive the narrowing to f32 only in about one softmax in
@@ -77,18 +79,32 @@ __global__ void attn_scores_exact_kernel(const float *__restrict__ q, const void
 #pragma unroll
         for (int L = 0; L < 8; ++L) s0[L] = s1[L] = 0.0f;
         uint32_t i = 0;
+        // 64 elements of the K row per batch: all of a batch's loads are issued before its FMAs
+        for (; i + 8 <= nv; i += 8) {
+            float kk[8][8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) load8(kc, row + 8 * (i + j), kv_f16, kk[j]);
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                const float4 qa = *reinterpret_cast<const float4 *>(qh + 8 * (i + j)), qb = *reinterpret_cast<const float4 *>(qh + 8 * (i + j) + 4);
+                const float4 qc = *reinterpret_cast<const float4 *>(qh + 8 * (i + j) + 8), qd = *reinterpret_cast<const float4 *>(qh + 8 * (i + j) + 12);
+                const float q0[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                const float q1[8] = {qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
+#pragma unroll
+                for (int L = 0; L < 8; ++L) {
+                    s0[L] = fmaf(q0[L], kk[j][L], s0[L]);
+                    s1[L] = fmaf(q1[L], kk[j + 1][L], s1[L]);
+                }
+            }
+        }
         for (; i + 2 <= nv; i += 2) {
             float k0[8], k1[8];
             load8(kc, row + 8 * i, kv_f16, k0);
             load8(kc, row + 8 * i + 8, kv_f16, k1);
-            const float4 qa = *reinterpret_cast<const float4 *>(qh + 8 * i), qb = *reinterpret_cast<const float4 *>(qh + 8 * i + 4);
-            const float4 qc = *reinterpret_cast<const float4 *>(qh + 8 * i + 8), qd = *reinterpret_cast<const float4 *>(qh + 8 * i + 12);
-            const float q0[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-            const float q1[8] = {qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
 #pragma unroll
             for (int L = 0; L < 8; ++L) {
-                s0[L] = fmaf(q0[L], k0[L], s0[L]);
-                s1[L] = fmaf(q1[L], k1[L], s1[L]);
+                s0[L] = fmaf(qh[8 * i + L], k0[L], s0[L]);
+                s1[L] = fmaf(qh[8 * i + 8 + L], k1[L], s1[L]);
             }
         }
         if (i < nv) {
@@ -107,102 +123,133 @@ __global__ void attn_scores_exact_kernel(const float *__restrict__ q, const void
     }
 }
 
+__device__ __forceinline__ void ax_cp16(void *smem, const void *gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void ax_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void ax_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int AX_VT = 64;      // positions per staged V tile
+constexpr int AX_VSTAGES = 4;  // tiles in flight
+
 // grid (hd / 32, n_kv), AX_VTHREADS threads.  ws: scores [n_heads][ld]; pw: probabilities [n_heads][ld] in global
 // memory, used when the positions do not fit shared memory (every CTA of a KV head writes the same values there).
-// Dynamic shared memory: min(seq bucket, AX_SMEM_POS) * G floats.
+// Dynamic shared memory: AX_VSTAGES V tiles of AX_VT x 32 floats, then smem_pos * G floats of probabilities.
 __global__ void __launch_bounds__(AX_VTHREADS)
 attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, uint32_t ld, const void *__restrict__ vc, int kv_f16,
                          uint32_t seq_len, const uint32_t *__restrict__ seq_dev, uint32_t n_kv, uint32_t G, uint32_t hd,
                          uint32_t smem_pos, float *__restrict__ out, float *scales, int8_t *quants, int16_t *sums, const TpHook tp) {
-    extern __shared__ __align__(16) float ax_p[];  // [position][G]
+    extern __shared__ __align__(16) float ax_dyn[];
+    float *vt = ax_dyn;                                  // [AX_VSTAGES][AX_VT][32] (f16 caches use half of each tile)
+    float *ax_p = ax_dyn + AX_VSTAGES * AX_VT * 32;      // [position][G]
     __shared__ double red_d[AX_VTHREADS / 32];
     __shared__ float red_f[AX_VTHREADS / 32];
-    __shared__ float bc_f;
     pdl_trigger();
-    pdl_wait();
-    const uint32_t seq = seq_dev ? *seq_dev : seq_len;
     const uint32_t kvh = blockIdx.y, d0 = blockIdx.x * 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t kv_dim = (size_t)n_kv * hd;
+    pdl_wait();
+    const uint32_t seq = seq_dev ? *seq_dev : seq_len;
     const bool in_smem = seq <= smem_pos;
-    for (uint32_t h = 0; h < G; ++h) {
-        const float *s = ws + (size_t)(kvh * G + h) * ld;
-        float *pg = pw + (size_t)(kvh * G + h) * ld;
-        // maximum (f32::max fold: NaN scores are ignored)
-        float mx = -INFINITY;
-        for (uint32_t t = tid; t < seq; t += AX_VTHREADS) mx = fmaxf(mx, s[t]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) red_f[warp] = mx;
-        __syncthreads();
-        if (tid == 0) {
-            float m = red_f[0];
-            for (int w = 1; w < AX_VTHREADS / 32; ++w) m = fmaxf(m, red_f[w]);
-            bc_f = m;
+    const uint32_t n_tiles = (seq + AX_VT - 1) / AX_VT;
+    // V tiles: a position's 32-dim slice is 128 contiguous bytes (64 for an f16 cache): 16-byte asynchronous copies,
+    // the first tiles are requested before the softmax below so that they land while it runs
+    const uint32_t per_pos = kv_f16 ? 4 : 8;  // 16-byte pieces per position
+    auto stage_tile = [&](uint32_t tile) {
+        if (tile < n_tiles) {
+            char *dst = reinterpret_cast<char *>(vt + (size_t)(tile % AX_VSTAGES) * AX_VT * 32);
+            const uint32_t t0 = tile * AX_VT, cnt = min((uint32_t)AX_VT, seq - t0) * per_pos;
+            for (uint32_t i = tid; i < cnt; i += AX_VTHREADS) {
+                const uint32_t pl = i / per_pos, pc = i % per_pos;
+                const char *src = reinterpret_cast<const char *>(vc) + ((size_t)(t0 + pl) * kv_dim + (size_t)kvh * hd + d0) * (kv_f16 ? 2 : 4) + pc * 16;
+                ax_cp16(dst + (size_t)pl * per_pos * 16 + pc * 16, src);
+            }
         }
-        __syncthreads();
-        mx = bc_f;
-        // exponentials and their f64 sum (fixed tree: thread-strided partials, xor shuffles, warps in index order)
-        double sum = 0.0;
-        for (uint32_t t = tid; t < seq; t += AX_VTHREADS) {
-            const float e = ggml_expf(__fsub_rn(s[t], mx));
-            if (in_smem) ax_p[(size_t)t * G + h] = e;
+        ax_commit();  // every thread commits one group per tile slot, empty or not, so the wait counts stay uniform
+    };
+#pragma unroll
+    for (int i = 0; i < AX_VSTAGES - 1; ++i) stage_tile(i);
+
+    // ---- probabilities of the group's heads.  Head h is handled by warps [h * nwh, (h + 1) * nwh).
+    const uint32_t nwh = (AX_VTHREADS / 32) / G, h_mine = warp / nwh, wl = warp % nwh;  // warps past G * nwh idle here
+    const bool has_head = h_mine < G;
+    const uint32_t hth = nwh * 32, hti = wl * 32 + lane;  // threads of my head, my index among them
+    const float *s_row = ws + (size_t)(kvh * G + (has_head ? h_mine : 0)) * ld;
+    float *p_row = pw + (size_t)(kvh * G + (has_head ? h_mine : 0)) * ld;
+    float mx = -INFINITY;
+    if (has_head) {
+        for (uint32_t t = hti; t < seq; t += hth) {
+            const float v = s_row[t];
+            if (in_smem) ax_p[(size_t)t * G + h_mine] = v;
+            mx = fmaxf(mx, v);  // f32::max fold: NaN scores are ignored
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red_f[warp] = mx;
+    __syncthreads();
+    if (has_head) {
+        mx = red_f[h_mine * nwh];
+        for (uint32_t w = 1; w < nwh; ++w) mx = fmaxf(mx, red_f[h_mine * nwh + w]);
+    }
+    // exponentials and their f64 sum (fixed tree: thread-strided partials, xor shuffles, the head's warps in index order)
+    double sum = 0.0;
+    if (has_head) {
+        for (uint32_t t = hti; t < seq; t += hth) {
+            const float e = ggml_expf(__fsub_rn(in_smem ? ax_p[(size_t)t * G + h_mine] : s_row[t], mx));
+            if (in_smem) ax_p[(size_t)t * G + h_mine] = e;
             sum += (double)e;
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if (lane == 0) red_d[warp] = sum;
-        __syncthreads();
-        if (tid == 0) {
-            double tot = red_d[0];
-            for (int w = 1; w < AX_VTHREADS / 32; ++w) tot += red_d[w];
-            bc_f = (float)(1.0 / tot);
-        }
-        __syncthreads();
-        const float inv = bc_f;
-        for (uint32_t t = tid; t < seq; t += AX_VTHREADS) {
-            if (in_smem) ax_p[(size_t)t * G + h] = __fmul_rn(ax_p[(size_t)t * G + h], inv);
-            else pg[t] = __fmul_rn(ggml_expf(__fsub_rn(s[t], mx)), inv);  // recomputed: the CTAs of a KV head all store the same final value
-        }
-        __syncthreads();
     }
-    // every CTA of the KV head wrote the same probabilities to pw; this CTA's own writes are visible to it after the barrier
-    if (tid >= (int)(G * 8)) return;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) red_d[warp] = sum;
+    __syncthreads();
+    if (has_head) {
+        double tot = red_d[h_mine * nwh];
+        for (uint32_t w = 1; w < nwh; ++w) tot += red_d[h_mine * nwh + w];
+        const float inv = (float)(1.0 / tot);
+        for (uint32_t t = hti; t < seq; t += hth) {
+            if (in_smem) ax_p[(size_t)t * G + h_mine] = __fmul_rn(ax_p[(size_t)t * G + h_mine], inv);
+            else p_row[t] = __fmul_rn(ggml_expf(__fsub_rn(s_row[t], mx)), inv);  // recomputed: the CTAs of a KV head all store the same value
+        }
+    }
+    // (the first barrier of the tile loop below also publishes the probabilities)
+
+    // ---- out[d] = fma(p[t], V[t][d], out[d]) in position order: eight threads per head, four dims each
+    const bool chain = tid < (int)(G * 8);
     const uint32_t h = tid >> 3, dq = tid & 7;
-    const size_t kv_dim = (size_t)n_kv * hd;
-    const size_t col = (size_t)kvh * hd + d0 + 4 * dq;
-    const float *pg = pw + (size_t)(kvh * G + h) * ld;
+    const float *pg = pw + (size_t)(kvh * G + (chain ? h : 0)) * ld;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    auto load_v = [&](uint32_t t, float (&v)[4]) {
-        if (kv_f16) {
-            const uint2 r = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(vc) + (size_t)t * kv_dim + col));
-            const __half2 *hh = reinterpret_cast<const __half2 *>(&r);
-            const float2 a = __half22float2(hh[0]), b = __half22float2(hh[1]);
-            v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-        } else {
-            const float4 r = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(vc) + (size_t)t * kv_dim + col));
-            v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+    for (uint32_t tile = 0; tile < n_tiles; ++tile) {
+        ax_wait<AX_VSTAGES - 2>();  // this thread's copies of tile `tile` have landed
+        __syncthreads();            // everyone's have; and every chain thread is done with the slot restaged below
+        stage_tile(tile + AX_VSTAGES - 1);
+        if (chain) {
+            const uint32_t t0 = tile * AX_VT, cnt = min((uint32_t)AX_VT, seq - t0);
+            const char *base = reinterpret_cast<const char *>(vt + (size_t)(tile % AX_VSTAGES) * AX_VT * 32);
+#pragma unroll 8
+            for (uint32_t i = 0; i < cnt; ++i) {
+                float v[4];
+                if (kv_f16) {
+                    const uint2 r = *reinterpret_cast<const uint2 *>(base + (size_t)i * 64 + dq * 8);
+                    const __half2 *hh = reinterpret_cast<const __half2 *>(&r);
+                    const float2 a = __half22float2(hh[0]), b = __half22float2(hh[1]);
+                    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+                } else {
+                    const float4 r = *reinterpret_cast<const float4 *>(base + (size_t)i * 128 + dq * 16);
+                    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+                }
+                const float p = in_smem ? ax_p[(size_t)(t0 + i) * G + h] : pg[t0 + i];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[j] = fmaf(p, v[j], acc[j]);
+            }
         }
-    };
-    uint32_t t0 = 0;
-    for (; t0 + 8 <= seq; t0 += 8) {
-        float v[8][4], p[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            load_v(t0 + i, v[i]);
-            p[i] = in_smem ? ax_p[(size_t)(t0 + i) * G + h] : pg[t0 + i];
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[j] = fmaf(p[i], v[i][j], acc[j]);
     }
-    for (; t0 < seq; ++t0) {
-        float v[4];
-        load_v(t0, v);
-        const float p = in_smem ? ax_p[(size_t)t0 * G + h] : pg[t0];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = fmaf(p, v[j], acc[j]);
-    }
+    ax_wait<0>();
+    if (!chain) return;
     const size_t o = (size_t)(kvh * G + h) * hd + d0 + 4 * dq;
     *reinterpret_cast<float4 *>(out + o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
     if (quants) {
@@ -215,7 +262,7 @@ attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, u
         }
         const unsigned grp = 0xFFu << (lane & 24);
 #pragma unroll
-        for (int s = 4; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(grp, amax, s));
+        for (int sft = 4; sft > 0; sft >>= 1) amax = fmaxf(amax, __shfl_xor_sync(grp, amax, sft));
         const float d = __fdiv_rn(amax, 127.0f);
         const float r = __fdiv_rn(1.0f, d);
         const float id = (d != 0.0f && isfinite(r)) ? r : 0.0f;
@@ -300,12 +347,12 @@ int32_t launch_decode_attention_exact(const float *q, const void *kc, const void
     CERA_CUDA_TRY(launch_k(attn_scores_exact_kernel, dim3(per_head, nkv), dim3(AX_TILE * G), (size_t)G * (hd + 4) * sizeof(float), st, q,
                            kc, kv_f16, (uint32_t)seq_len, seq_len_dev, nkv, G, hd, scale, ws, ld));
     const uint32_t smem_pos = b >= 5 ? 0u : (uint32_t)reach;
-    const size_t smem = (size_t)smem_pos * G * sizeof(float);
+    const size_t smem = ((size_t)AX_VSTAGES * AX_VT * 32 + (size_t)smem_pos * G) * sizeof(float);
     if (smem > 48 * 1024) {
         static bool raised = false;
         if (!raised) {
             CERA_CUDA_TRY(cudaFuncSetAttribute(attn_values_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)(AX_SMEM_POS * 8 * sizeof(float))));
+                                               (int)((AX_VSTAGES * AX_VT * 32 + AX_SMEM_POS * 8) * sizeof(float))));
             raised = true;
         }
     }

@@ -50,6 +50,7 @@ struct WeightView {
     int32_t type;
     uint32_t m, k, nb;
     uint32_t t128;       // lane tasks per row, 0 = pieces in GGUF order
+    uint32_t ilv;        // 8: K-quant planes interleave groups of eight rows (see below), 0: rows one after another
     const uint8_t *q;    // low quant plane
     const uint8_t *qh;   // high-bit plane (Q5_K, Q6_K)
     const uint8_t *hdr;  // scale plane (see table)
@@ -76,11 +77,31 @@ __host__ __device__ inline TypeInfo type_info(int t) {
     }
 }
 
+// K-quants with k a multiple of 128 are stored with groups of EIGHT ROWS INTERLEAVED (ilv = 8; the row count is
+// padded to a multiple of eight with zero rows): in the low-quant plane piece c of task t of row r sits at
+//   (r/8) * 8 * row_bytes + ((t*8 + r%8) * 4 + c) * 16,
+// so that the 32 lanes (row%8, c) of a warp that walk their strips in task order read 512 contiguous bytes per
+// load; the header, high-bit and super-scale planes are indexed by sb_index() = ((r/8)*nb + sb)*8 + r%8.
 // Byte offset inside a row's low-quant plane of its i-th 16-byte piece (GGUF order).
 __host__ __device__ inline size_t q_piece_off(uint32_t t128, uint32_t np, uint32_t i) {
     if (!t128) return (size_t)i * 16;
     const uint32_t t = i / np, c = i - t * np;
     return ((size_t)c * t128 + t) * 16;
+}
+
+// Index of (row, super-block) in the per-super-block planes (hdr, qh, d).
+__host__ __device__ inline size_t sb_index(const WeightView &w, size_t row, size_t sb) {
+    return w.ilv ? ((row >> 3) * w.nb + sb) * 8 + (row & 7) : row * w.nb + sb;
+}
+// Address of the i-th 16-byte piece (GGUF order) of a row's low-quant plane; np = pieces per lane task (4, Q8_0: 8).
+__host__ __device__ inline const uint8_t *q_piece_ptr(const WeightView &w, size_t row, uint32_t np, uint32_t i) {
+    const TypeInfo ti = type_info(w.type);
+    const size_t row_bytes = (size_t)w.nb * ti.q_b;
+    if (w.ilv) {
+        const uint32_t t = i >> 2, c = i & 3;
+        return w.q + (row >> 3) * 8 * row_bytes + (((size_t)t * 8 + (row & 7)) * 4 + c) * 16;
+    }
+    return w.q + row * row_bytes + q_piece_off(w.t128, np, i);
 }
 
 inline bool is_block_type(int t) {

@@ -161,9 +161,9 @@ struct Fmt<CERA_TYPE_Q4_K> {
         uint4 q, h;
     };
     __device__ static Raw load(const WeightView &w, size_t row, int item) {
-        const size_t sb = row * w.nb + (item >> 3);
+        const size_t sb = sb_index(w, row, item >> 3);
         Raw r;
-        r.q = ld_stream(w.q + row * ((size_t)w.nb * 128) + q_piece_off(w.t128, 4, (uint32_t)item));
+        r.q = ld_stream(q_piece_ptr(w, row, 4, (uint32_t)item));
         r.h = __ldg(reinterpret_cast<const uint4 *>(w.hdr) + sb);
         return r;
     }
@@ -198,9 +198,9 @@ struct Fmt<CERA_TYPE_Q5_K> {
         uint4 q, h, qh;
     };
     __device__ static Raw load(const WeightView &w, size_t row, int item) {
-        const size_t sb = row * w.nb + (item >> 3);
+        const size_t sb = sb_index(w, row, item >> 3);
         Raw r;
-        r.q = ld_stream(w.q + row * ((size_t)w.nb * 128) + q_piece_off(w.t128, 4, (uint32_t)item));
+        r.q = ld_stream(q_piece_ptr(w, row, 4, (uint32_t)item));
         r.qh = __ldg(reinterpret_cast<const uint4 *>(w.qh + sb * 32 + (item & 1) * 16));
         r.h = __ldg(reinterpret_cast<const uint4 *>(w.hdr) + sb);
         return r;
@@ -238,10 +238,10 @@ struct Fmt<CERA_TYPE_Q6_K> {
         uint16_t d;
     };
     __device__ static Raw load(const WeightView &w, size_t row, int item) {
-        const size_t sb = row * w.nb + (item >> 3);
+        const size_t sb = sb_index(w, row, item >> 3);
         const int c = item & 7;
         Raw r;
-        r.q = ld_stream(w.q + row * ((size_t)w.nb * 128) + q_piece_off(w.t128, 4, (uint32_t)item));
+        r.q = ld_stream(q_piece_ptr(w, row, 4, (uint32_t)item));
         r.qh = __ldg(reinterpret_cast<const uint4 *>(w.qh + sb * 64 + (c >> 2) * 32 + (c & 1) * 16));
         r.sc = __ldg(reinterpret_cast<const uint4 *>(w.hdr) + sb);
         r.d = __ldg(reinterpret_cast<const uint16_t *>(w.d) + sb);

@@ -143,27 +143,27 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
         for (int i = tid; i < GM_BM * 8; i += GM_THREADS) {
             const int r = i >> 3, pc = i & 7;
             const uint32_t row = min(wrow0 + r, w_last);
-            const uint8_t *src = p.w.q + (size_t)row * nb * ti.q_b + q_piece_off(p.w.t128, 4, bi * 8 + pc);
+            const uint8_t *src = q_piece_ptr(p.w, row, 4, bi * 8 + pc);
             cpa16(wq + r * GM_WQ_STRIDE + pc * 16, src);
         }
         if (T == CERA_TYPE_Q6_K) {
             for (int i = tid; i < GM_BM * 4; i += GM_THREADS) {
                 const int r = i >> 2, pc = i & 3;
                 const uint32_t row = min(wrow0 + r, w_last);
-                cpa16(wqh + r * GM_WH_STRIDE + pc * 16, p.w.qh + ((size_t)row * nb + bi) * 64 + pc * 16);
+                cpa16(wqh + r * GM_WH_STRIDE + pc * 16, p.w.qh + sb_index(p.w, row, bi) * 64 + pc * 16);
             }
         }
         if (T == CERA_TYPE_Q5_K) {  // fifth bits: 32 bytes per row, bit s of byte l belongs to element l of sub-block s
             for (int i = tid; i < GM_BM * 2; i += GM_THREADS) {
                 const int r = i >> 1, pc = i & 1;
                 const uint32_t row = min(wrow0 + r, w_last);
-                cpa16(wqh + r * GM_WH_STRIDE + pc * 16, p.w.qh + ((size_t)row * nb + bi) * 32 + pc * 16);
+                cpa16(wqh + r * GM_WH_STRIDE + pc * 16, p.w.qh + sb_index(p.w, row, bi) * 32 + pc * 16);
             }
         }
         for (int r = tid; r < GM_BM; r += GM_THREADS) {
             const uint32_t row = min(wrow0 + r, w_last);
             if (T == CERA_TYPE_Q4_0) cpa16(whd + r * 16, p.w.hdr + ((size_t)row * nb + bi * 8) * 2);  // eight f16 block scales
-            else cpa16(whd + r * 16, p.w.hdr + ((size_t)row * nb + bi) * 16);
+            else cpa16(whd + r * 16, p.w.hdr + sb_index(p.w, row, bi) * 16);
         }
         for (int i = tid; i < GM_BN * 16; i += GM_THREADS) {
             const int c = i >> 4, pc = i & 15;
@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_mma_kernel(const GemmParams p
             for (int i = tid; i < GM_BM * 16; i += GM_THREADS) {
                 const int r = i >> 4, e = i & 15;
                 const uint32_t row = min(wrow0 + r, w_last);
-                const float d = h2f(reinterpret_cast<const uint16_t *>(p.w.d)[(size_t)row * nb + bi]);
+                const float d = h2f(reinterpret_cast<const uint16_t *>(p.w.d)[sb_index(p.w, row, bi)]);
                 wsc[r * 16 + e] = d * (float)(int8_t)whd[r * 16 + e];
             }
         }

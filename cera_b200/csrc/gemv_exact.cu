@@ -10,12 +10,14 @@
 // `macc` that adds one min / offset term per block, in block order.  At the end the four accumulators
 // are tree-added, the eight lanes are added in the hsum256 order and macc is subtracted.
 //
-// Mapping.  The low-quant plane stores a row as four contiguous strips (see WeightView: piece c of
-// every 128-weight task t sits at 16*(c*t128 + t)).  Piece c = (pair, half) of task t holds, for
+// Mapping.  A row's low-quant plane is four STRIPS: strip c collects piece c (sixteen bytes) of every
+// 128-weight task t of the row, in task order.  Piece c = (pair, half) of task t holds, for
 // Q4_K / Q5_K, sixteen bytes whose low nibbles are elements [16*half, 16*half+16) of block
 // 4t + 2*pair and whose high nibbles are the same elements of block 4t + 2*pair + 1; for Q6_K the low
 // nibbles belong to block 4t + pair and the high nibbles to block 4t + pair + 2.  Either way the four
 // words of a piece feed eight chains - two accumulators x four lanes - that no other strip touches.
+// The planes interleave groups of eight rows (WeightView::ilv): the 8 x 4 strips of a group are stored
+// task by task, 32 pieces = 512 contiguous bytes per task, which is exactly one warp-wide 128-bit load.
 // So ONE LANE OWNS ONE STRIP of one row: it streams the strip with 128-bit loads in task order and
 // carries its eight chains in registers; four lanes cover a row, a warp eight rows, a CTA of four
 // such warps 32 rows per round.  Each product quad is one dp4a whose accumulator input is the bit
@@ -136,8 +138,10 @@ __global__ void __launch_bounds__(XG_THREADS) gemv_exact_kernel(const ExactParam
             while (sg + 1 < p.n_segs && row >= p.row_end[sg]) ++sg;
             const uint32_t local = row - (sg ? p.row_end[sg - 1] : 0);
             const WeightView &w = p.w[sg];
-            const uint8_t *strip = w.q + (size_t)local * ((size_t)nb * ti.q_b) + (size_t)c * t128 * 16;
-            const uint8_t *hdr = w.hdr + (size_t)local * nb * 16;
+            // interleaved planes: piece (t, c) of row `local` at group base + (t*32 + (local%8)*4 + c) * 16, so the 32 lanes
+            // of a warp (eight consecutive rows x four strips) read 512 contiguous bytes per load
+            const uint8_t *strip = w.q + (size_t)(local >> 3) * 8 * ((size_t)nb * ti.q_b) + ((size_t)(local & 7) * 4 + c) * 16;
+            const size_t sb0 = sb_index(w, local, 0);  // + 8 per super-block
             float *terms = s.terms + (size_t)rslot * (nb32 + 1);
             float acc_lo[4] = {0.0f, 0.0f, 0.0f, 0.0f}, acc_hi[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
@@ -147,18 +151,18 @@ __global__ void __launch_bounds__(XG_THREADS) gemv_exact_kernel(const ExactParam
                     // eight tasks = four super-blocks: all loads first
                     uint4 piece[8], head[4], hb[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) piece[i] = __ldg(reinterpret_cast<const uint4 *>(strip + (size_t)(t0 + i) * 16));
+                    for (int i = 0; i < 8; ++i) piece[i] = ld_stream(strip + (size_t)(t0 + i) * 512);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) head[i] = __ldg(reinterpret_cast<const uint4 *>(hdr + (size_t)((t0 >> 1) + i) * 16));
+                    for (int i = 0; i < 4; ++i) head[i] = __ldg(reinterpret_cast<const uint4 *>(w.hdr + (sb0 + (size_t)((t0 >> 1) + i) * 8) * 16));
                     if (T == CERA_TYPE_Q5_K) {
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) hb[i] = __ldg(reinterpret_cast<const uint4 *>(w.qh + ((size_t)local * nb + (t0 >> 1) + i) * 32 + half * 16));
+                        for (int i = 0; i < 4; ++i) hb[i] = __ldg(reinterpret_cast<const uint4 *>(w.qh + (sb0 + (size_t)((t0 >> 1) + i) * 8) * 32 + half * 16));
                     }
                     if (T == CERA_TYPE_Q6_K) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const uint32_t t = t0 + i;
-                            hb[i] = __ldg(reinterpret_cast<const uint4 *>(w.qh + ((size_t)local * nb + (t >> 1)) * 64 + (t & 1) * 32 + half * 16));
+                            hb[i] = __ldg(reinterpret_cast<const uint4 *>(w.qh + (sb0 + (size_t)(t >> 1) * 8) * 64 + (t & 1) * 32 + half * 16));
                         }
                     }
 #pragma unroll
@@ -201,7 +205,7 @@ __global__ void __launch_bounds__(XG_THREADS) gemv_exact_kernel(const ExactParam
                             const int4 ahi = *reinterpret_cast<const int4 *>(s.aq + 32 * xb_hi + 16 * half);
                             // h = the 16 int8 scales of the super-block; lanes 0-3 of a block use scales[8nh + 2g], lanes 4-7 the next
                             const uint32_t sw_lo = nh ? h.z : h.x, sw_hi = nh ? h.w : h.y;  // scales[8nh .. +3], [8nh+4 .. +7]
-                            const float d = h2f(__ldg(reinterpret_cast<const uint16_t *>(w.d) + (size_t)local * nb + (t >> 1)));
+                            const float d = h2f(__ldg(reinterpret_cast<const uint16_t *>(w.d) + sb0 + (size_t)(t >> 1) * 8));
                             const float sc_lo = (float)(int8_t)(sw_lo >> (8 * (2 * pair + half)));
                             const float sc_hi = (float)(int8_t)(sw_hi >> (8 * (2 * pair + half)));
                             const float scale_lo = __fmul_rn(__fmul_rn(sc_lo, d), s.xs[xb_lo]);
@@ -338,6 +342,8 @@ int32_t launch_gemv_exact(const GemvSeg *segs, int n_segs, const ActView &x, int
     if (type != CERA_TYPE_Q4_K && type != CERA_TYPE_Q5_K && type != CERA_TYPE_Q6_K) return CERA_CUDA_OK;
     const uint32_t k = segs[0].w.k, t128 = segs[0].w.t128;
     if (k % 1024 || t128 != k / 128 || (t128 + XG_SEG_TASKS - 1) / XG_SEG_TASKS > XG_MAX_HANDOVERS) return CERA_CUDA_OK;
+    for (int i = 0; i < n_segs; ++i)
+        if (segs[i].w.ilv != 8) return CERA_CUDA_OK;
     if (xg_smem_bytes(k) > 200 * 1024) return CERA_CUDA_OK;
     if ((uintptr_t)x.quants % 16) return CERA_CUDA_OK;
     ExactParams p{};
@@ -351,6 +357,8 @@ int32_t launch_gemv_exact(const GemvSeg *segs, int n_segs, const ActView &x, int
         rows += segs[i].w.m;
         p.row_end[i] = rows;
     }
+    for (int i = 0; i + 1 < n_segs; ++i)
+        if (segs[i].w.m % 8) return CERA_CUDA_OK;  // a warp's eight rows must be one interleave group of one matrix
     if (epilogue == EPI_ROPE_KV) {
         if (n_segs != 3 || !p.f.rope_cs || !p.f.pos_dev || !p.f.k_cache || !p.f.v_cache || p.f.head_dim % 2 || segs[0].w.m % 32 ||
             segs[1].w.m % 32 || segs[2].w.m % 32)

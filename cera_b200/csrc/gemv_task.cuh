@@ -91,23 +91,22 @@ template <int T, bool GLOBAL = true>
 __device__ __forceinline__ void load_raw(const WeightView &w, size_t row, uint32_t tau, Raw<T> &r) {
     constexpr int NP = T == CERA_TYPE_Q8_0 ? 8 : 4;
     const TypeInfo ti = type_info(T);
-    const uint8_t *q = w.q + row * ((size_t)w.nb * ti.q_b) + (size_t)tau * 16;
 #pragma unroll
-    for (int c = 0; c < NP; ++c) r.p[c] = ldw16<GLOBAL>(q + (size_t)c * w.t128 * 16);
+    for (int c = 0; c < NP; ++c) r.p[c] = ldw16<GLOBAL>(q_piece_ptr(w, row, NP, tau * NP + c));
     if (T == CERA_TYPE_Q4_0 || T == CERA_TYPE_Q8_0) {  // 4 half scales
         const uint2 d = ldh<GLOBAL, uint2>(w.hdr + (row * w.nb + 4 * (size_t)tau) * 2);
         r.hd = make_uint4(d.x, d.y, 0, 0);
     } else if (T == CERA_TYPE_Q4_1) {  // 4 x (d, m)
         r.hd = ldh<GLOBAL, uint4>(w.hdr + (row * w.nb + 4 * (size_t)tau) * 4);
     } else if (T == CERA_TYPE_Q4_K || T == CERA_TYPE_Q5_K) {  // d, dmin, scales[12] of super-block tau/2
-        const size_t sb = row * w.nb + (tau >> 1);
+        const size_t sb = sb_index(w, row, tau >> 1);
         r.hd = ldh<GLOBAL, uint4>(w.hdr + sb * 16);
         if (T == CERA_TYPE_Q5_K) {
             r.hi[0] = ldh<GLOBAL, uint4>(w.qh + sb * 32);
             r.hi[1] = ldh<GLOBAL, uint4>(w.qh + sb * 32 + 16);
         }
     } else {  // Q6_K: 8 int8 scales of half nh, d in .z
-        const size_t sb = row * w.nb + (tau >> 1);
+        const size_t sb = sb_index(w, row, tau >> 1);
         const uint32_t nh = tau & 1;
         const uint2 sc = ldh<GLOBAL, uint2>(w.hdr + sb * 16 + nh * 8);
         const uint16_t d = ldh<GLOBAL, uint16_t>(w.d + sb * 2);

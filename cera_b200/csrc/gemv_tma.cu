@@ -178,6 +178,7 @@ __global__ void __launch_bounds__(TM_THREADS, 1) gemv_tma_kernel(const TmaParams
         sv.k = p.k;
         sv.nb = p.w[0].nb;
         sv.t128 = p.t128;
+        sv.ilv = 0;
         sv.q = st;
         sv.qh = st + off_qh;
         sv.hdr = st + off_h;
@@ -285,6 +286,8 @@ int32_t launch_gemv_tma(const GemvSeg *segs, int n_segs, const ActView &x, int e
     const int type = segs[0].w.type;
     const uint32_t k = segs[0].w.k, t128 = segs[0].w.t128;
     if (!is_block_type(type) || t128 == 0 || t128 > 32 * TM_CONSUMER_WARPS) return CERA_CUDA_OK;
+    for (int i = 0; i < n_segs; ++i)
+        if (segs[i].w.ilv) return CERA_CUDA_OK;  // rows are copied whole: not for the interleaved K-quant planes
     if ((uintptr_t)x.quants % 16 || (uintptr_t)x.scales % 16 || (uintptr_t)x.sums % 16) return CERA_CUDA_OK;
     TmaParams p{};
     if (fusion) p.f = *fusion;

@@ -12,10 +12,12 @@ namespace {
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // One thread per GGUF block: scatter its fields into the planes.
-__global__ void repack_kernel(int type, const uint8_t *__restrict__ raw, size_t n_blocks, uint32_t nb, uint32_t t128,
-                              uint8_t *q, uint8_t *qh, uint8_t *hdr, uint8_t *d) {
+__global__ void repack_kernel(const WeightView w, const uint8_t *__restrict__ raw, size_t n_blocks) {
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n_blocks) return;
+    const int type = w.type;
+    const uint32_t nb = w.nb;
+    uint8_t *qh = const_cast<uint8_t *>(w.qh), *hdr = const_cast<uint8_t *>(w.hdr), *d = const_cast<uint8_t *>(w.d);
     const TypeInfo ti = type_info(type);
     const uint8_t *src = raw + b * ti.bytes;
     auto cp = [](uint8_t *dst, const uint8_t *s, int n) {
@@ -25,10 +27,10 @@ __global__ void repack_kernel(int type, const uint8_t *__restrict__ raw, size_t 
     const size_t row = b / nb;
     const uint32_t blk = (uint32_t)(b - row * nb);
     const uint32_t ppb = ti.q_b / 16, np = type == CERA_TYPE_Q8_0 ? 8u : 4u;
-    uint8_t *qrow = q + row * ((size_t)nb * ti.q_b);
     auto cpq = [&](const uint8_t *s) {
-        for (uint32_t j = 0; j < ppb; ++j) cp(qrow + q_piece_off(t128, np, blk * ppb + j), s + 16 * j, 16);
+        for (uint32_t j = 0; j < ppb; ++j) cp(const_cast<uint8_t *>(q_piece_ptr(w, row, np, blk * ppb + j)), s + 16 * j, 16);
     };
+    const size_t sbi = sb_index(w, row, blk);  // slot of this block in the per-block planes (== b unless rows are interleaved)
     switch (type) {
         case CERA_TYPE_Q4_0:  // d(2) qs(16)
             cp(hdr + b * 2, src, 2);
@@ -43,19 +45,19 @@ __global__ void repack_kernel(int type, const uint8_t *__restrict__ raw, size_t 
             cpq(src + 2);
             break;
         case CERA_TYPE_Q4_K:  // d(2) dmin(2) scales(12) qs(128)
-            cp(hdr + b * 16, src, 16);
+            cp(hdr + sbi * 16, src, 16);
             cpq(src + 16);
             break;
         case CERA_TYPE_Q5_K:  // d(2) dmin(2) scales(12) qh(32) qs(128)
-            cp(hdr + b * 16, src, 16);
-            cp(qh + b * 32, src + 16, 32);
+            cp(hdr + sbi * 16, src, 16);
+            cp(qh + sbi * 32, src + 16, 32);
             cpq(src + 48);
             break;
         case CERA_TYPE_Q6_K:  // ql(128) qh(64) scales(16) d(2)
             cpq(src);
-            cp(qh + b * 64, src + 128, 64);
-            cp(hdr + b * 16, src + 192, 16);
-            cp(d + b * 2, src + 208, 2);
+            cp(qh + sbi * 64, src + 128, 64);
+            cp(hdr + sbi * 16, src + 192, 16);
+            cp(d + sbi * 2, src + 208, 2);
             break;
     }
 }
@@ -125,8 +127,12 @@ int32_t weight_upload(int32_t type, size_t m, size_t k, const void *bytes, size_
     auto *w = new (std::nothrow) cera_cuda_weight();
     if (!w) return fail(CERA_CUDA_ERR_OOM, "weight_create: host allocation failed");
     cudaGetDevice(&w->device);
-    const size_t q_sz = align_up(n_blocks * ti.q_b, 256), qh_sz = align_up(n_blocks * ti.qh_b, 256),
-                 hdr_sz = align_up(n_blocks * ti.hdr_b, 256), d_sz = align_up(n_blocks * ti.d_b, 256);
+    // K-quants with whole 128-weight lane tasks: groups of eight rows interleaved (common.cuh), rows padded with zeros
+    const bool kq = type == CERA_TYPE_Q4_K || type == CERA_TYPE_Q5_K || type == CERA_TYPE_Q6_K;
+    const uint32_t ilv = (kq && k % 128 == 0) ? 8u : 0u;
+    const size_t plane_blocks = ilv ? (m + 7) / 8 * 8 * nb : n_blocks;
+    const size_t q_sz = align_up(plane_blocks * ti.q_b, 256), qh_sz = align_up(plane_blocks * ti.qh_b, 256),
+                 hdr_sz = align_up(plane_blocks * ti.hdr_b, 256), d_sz = align_up(plane_blocks * ti.d_b, 256);
     const size_t xs_sz = with_scratch ? align_up(k / 32 * 4, 256) : 0, xq_sz = with_scratch ? align_up(k, 256) : 0,
                  xsum_sz = with_scratch ? align_up(k / 16 * 2, 256) : 0;
     w->bytes = q_sz + qh_sz + hdr_sz + d_sz + xs_sz + xq_sz + xsum_sz;
@@ -146,8 +152,16 @@ int32_t weight_upload(int32_t type, size_t m, size_t k, const void *bytes, size_
         w->xsum = (int16_t *)((uint8_t *)w->xq + xq_sz);
     }
     const uint32_t t128 = k % 128 == 0 ? (uint32_t)(k / 128) : 0u;
-    w->v = WeightView{type, (uint32_t)m, (uint32_t)k, (uint32_t)nb, t128, q, ti.qh_b ? qh : nullptr, hdr,
+    w->v = WeightView{type, (uint32_t)m, (uint32_t)k, (uint32_t)nb, t128, ilv, q, ti.qh_b ? qh : nullptr, hdr,
                       ti.d_b ? d : nullptr};
+    if (ilv && plane_blocks != n_blocks) {  // the padding rows of the last group read as zero weights
+        st = check_cuda(cudaMemset(w->base, 0, q_sz + qh_sz + hdr_sz + d_sz), "cudaMemset(weight planes)");
+        if (st != CERA_CUDA_OK) {
+            cudaFree(w->base);
+            delete w;
+            return st;
+        }
+    }
 
     // Stage the raw blocks on the device, scatter, release the staging copy.
     void *raw = nullptr;
@@ -156,7 +170,7 @@ int32_t weight_upload(int32_t type, size_t m, size_t k, const void *bytes, size_
     if (st == CERA_CUDA_OK) {
         const int threads = 128;
         const size_t grid = (n_blocks + threads - 1) / threads;
-        repack_kernel<<<(unsigned)grid, threads>>>(type, (const uint8_t *)raw, n_blocks, (uint32_t)nb, t128, q, qh, hdr, d);
+        repack_kernel<<<(unsigned)grid, threads>>>(w->v, (const uint8_t *)raw, n_blocks);
         count_launch();
         st = check_cuda(cudaGetLastError(), "repack launch");
         if (st == CERA_CUDA_OK) st = check_cuda(cudaDeviceSynchronize(), "repack");
