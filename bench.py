@@ -121,78 +121,98 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU arm
-def cpu_decode_sample(reps, threads):
-    """Times the reference's x86 int8 GEMV path (AVX2 restatement) on one layer's seven
-    projections and the LM head, same shapes / types / generator as the device model;
-    a token is 32 layers + the head.  Attention and the O(k) glue are left out (< 1 %)."""
+WORKLOAD = ("Llama-3-8B-shape random-init model (32 layers, 4096/14336, 32/8 heads, vocab 128256; "
+            "Q4_K attn/gate/up/embd, Q6_K down/output), 512-token prompt then greedy decode")
+CPU_CONTEXT = 16  # prompt tokens the CPU arm feeds before its timed tokens (see cpu_token_bench)
+
+
+def cpu_token_bench(steps, warmup, threads):
+    """The reference's CPU decode token, whole: embedding row, 32 layers of RMSNorm, seven int8 GEMVs (activations
+    re-quantized to Q8_0 inside each, as cera does on x86), RoPE, KV append, attention, SiLU*mul, the final norm, the
+    LM-head GEMV and the argmax, on the full synthetic model, through the oracle's restatement of cera's x86 kernels.
+    The model is built once; `warmup` then `steps` greedy tokens are decoded after a CPU_CONTEXT-token prompt (a
+    bounded sample: at this depth attention is under 1 % of a token, as it is at 512 on the CPU, where the 4.84 GB
+    weight stream is the time).  Timed once per tier the host offers (AVX2; AVX-512 VNNI, the tier cera would pick
+    when present) and once on a single thread.  Nothing of the CUDA package is imported."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import numpy as np
     import oracle_lib as O
-    from cera_b200.types import Q4_K, Q6_K
-    shapes = [("attn_q", Q4_K, 4096, 4096), ("attn_k", Q4_K, 1024, 4096), ("attn_v", Q4_K, 1024, 4096),
-              ("attn_output", Q4_K, 4096, 4096), ("ffn_gate", Q4_K, 14336, 4096), ("ffn_up", Q4_K, 14336, 4096),
-              ("ffn_down", Q6_K, 4096, 14336)]
-    head = ("output", Q6_K, 128256, 4096)
-    rng = np.random.default_rng(0)
-
-    def make(t, m, k, seed):
-        # the quantizer is exact either way; host generation keeps this arm free of the GPU
-        w = O.synth_normal(m * k, seed=seed, sigma=0.02)
-        return O.quantize_weights(t, w)
-
-    layer = [(t, m, k, make(t, m, k, 100 + i)) for i, (_, t, m, k) in enumerate(shapes)]
-    hd = (head[1], head[2], head[3], make(head[1], head[2], head[3], 999))
-    xs = {4096: rng.standard_normal(4096).astype(np.float32), 14336: rng.standard_normal(14336).astype(np.float32)}
-
-    def run_layer():
-        for t, m, k, raw in layer:
-            O.gemv(t, raw, xs[k], m, k, avx2=True, threads=threads)
-
-    def run_head():
-        O.gemv(hd[0], hd[3], xs[4096], hd[1], hd[2], avx2=True, threads=threads)
-
-    run_layer()
-    run_head()  # warm the pool and the caches
     t0 = time.perf_counter()
-    for _ in range(reps):
-        run_layer()
-    t_layer = (time.perf_counter() - t0) / reps
-    t0 = time.perf_counter()
-    for _ in range(reps):
-        run_head()
-    t_head = (time.perf_counter() - t0) / reps
-    tok_s = 1.0 / (32 * t_layer + t_head)
-    return tok_s, t_layer, t_head
+    model = O.build_oracle_llama(dict(O.LLAMA3_8B), seed=0, max_seq_len=CPU_CONTEXT + 2 * (steps + warmup) + 8, threads=threads)
+    build_s = time.perf_counter() - t0
+    prompt = O.prompt_tokens(CPU_CONTEXT, O.LLAMA3_8B["vocab_size"], 7)
+    pos = 0
+    for t in prompt:
+        model.forward(int(t), pos, want_logits=False)
+        pos += 1
+    tok = int(prompt[-1])
+
+    def run(n):
+        nonlocal tok, pos
+        t1 = time.perf_counter()
+        for _ in range(n):
+            tok = int(O.argmax(model.forward(tok, pos)))
+            pos += 1
+        return time.perf_counter() - t1
+
+    tiers = {}
+    order = ["avx2"] + (["vnni"] if O.has_vnni() else [])
+    for tier in order:
+        O.set_cpu_tier(tier)
+        run(max(1, warmup if tier == order[0] else 1))
+        dt = run(steps)
+        tiers[tier] = steps / dt
+    best = max(tiers, key=tiers.get)
+    # one thread, two tokens, on the faster tier (a reported figure, not the baseline)
+    O.set_cpu_tier(best)
+    model.set_threads(1)
+    one_thread = 2 / run(2)
+    model.close()
+    return {"tok_s": tiers[best], "tier": best, "tiers": tiers, "build_s": build_s, "threads": threads, "one_thread_tok_s": one_thread}
 
 
 def reference_arm(args, rank):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    vals = []
-    for _ in range(max(1, args.warmup // 4)):
-        cpu_decode_sample(1, threads)
-    t_start = time.perf_counter()
-    for _ in range(args.steps):
-        v, _, _ = cpu_decode_sample(1, threads)
-        vals.append(v)
-        if time.perf_counter() - t_start > 150:
-            break
-    vals.sort()
-    v = vals[len(vals) // 2]
-    sample = "per step: the 7 projection GEMVs of one layer + the LM-head GEMV, token = 32 layers + head"
+    r = cpu_token_bench(args.steps, max(args.warmup, 1), threads)
+    v = r["tok_s"]
+    sample = (f"{args.steps} whole greedy decode tokens of the full 32-layer model (all seven GEMVs per layer, attention, norms, RoPE, "
+              f"SiLU*mul, LM head, argmax) after a {CPU_CONTEXT}-token prompt, oracle restatement of cera's x86 int8 tier "
+              f"'{r['tier']}', {threads} threads; other tiers: " + ", ".join(f"{k} {x:.2f} tok/s" for k, x in r["tiers"].items()))
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": len(vals),
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1000.0 / v, "higher_is_better": True,
         "scaling": "strong" if args.gpus > 1 else "weak",
-        "vs_baseline": None, "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
-        "config": {"workload": "Llama-3-8B-shape random-init model (32 layers, 4096/14336, 32/8 heads, vocab 128256; "
-                               "Q4_K attn/gate/up/embd, Q6_K down/output), 512-token prompt then greedy decode",
-                   "prompt_len": PROMPT_LEN, "parallelism": "host cores only: the CPU int8 GEMV path of the same decode token"},
-        "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": bench_config(args.prompt_len, args.gpus, None),
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample, "tiers": r["tiers"],
+                         "one_thread_tok_s": r["one_thread_tok_s"]},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
+
+
+DTYPE = "int8 x int8 -> int32 dot, f32 scales and accumulation"
+
+
+def bench_config(prompt_len, world, stream_head):
+    """The `config` object both arms print: same keys, same workload string."""
+    return {"workload": WORKLOAD, "prompt_len": prompt_len, "kv_dtype": "f32",
+            "parallelism": (f"tensor-parallel x{world}: rows of every matrix split over the GPUs, slices pushed into peer memory "
+                            "over NVLink inside the step") if world > 1 else "1 GPU",
+            "stream_head": stream_head,
+            "l2": "each token streams 4.84 GB of weights (>> 126 MB L2); the kernel microbench rotates 16 weight copies (528 MB)"}
+
+
+def reference_stream():
+    """The CPU reference's greedy stream for this workload (tests/golden/llama8b_stream.json), or None."""
+    p = os.path.join(ROOT, "tests", "golden", "llama8b_stream.json")
+    if not os.path.exists(p):
+        return None
+    with open(p) as f:
+        g = json.load(f)
+    return g
 
 
 # --------------------------------------------------------------------------- CUDA arm
@@ -361,6 +381,20 @@ def moe_ep_microbench(torch, cb, iters, rank, world, n_total=512):
             "tops": 2.0 * n_total * used * 3 * ff * hs / ms / 1e9, "parallelism": "expert-parallel, peer-store dispatch and combine"}
 
 
+ROOFLINE_KERNEL = "gemv_exact_kernel<Q4_K> 14336x4096 (reference-order decode GEMV, gate / up shape)"
+
+
+def roofline_traffic():
+    """DRAM bytes of one launch of the roofline kernel from the committed ncu summary (profiles/roofline_traffic.json)."""
+    p = os.path.join(ROOT, "profiles", "roofline_traffic.json")
+    try:
+        with open(p) as f:
+            t = json.load(f)
+        return {"bytes": t["dram_bytes_read"] + t["dram_bytes_write"], "source": t["source"]}
+    except (OSError, KeyError, ValueError):
+        return {"bytes": None, "source": "profiles/roofline_traffic.json missing"}
+
+
 def roofline_q4k_gemv(torch, cb, iters):
     """The dominant kernel of the decode step: the Q4_K GEMV at the gate/up shape."""
     return gemv_microbench(torch, cb, "q4_k", 14336, 4096, iters)
@@ -397,15 +431,26 @@ def cuda_arm(args, rank, world):
         tp.connect(model, dist.new_group(backend="gloo"))
     t_build = time.perf_counter() - t_build
     prompt = synth.prompt_tokens(prompt_len, cfg["vocab_size"], seed=7)
+    # batched prompt processing (tensor-core GEMMs, tiled attention), timed and reported on its own ...
     t_pre = time.perf_counter()
     logits = model.forward_prefill(prompt, 0)
     t_pre = time.perf_counter() - t_pre
+    # ... then the prompt again through the decode kernels, one position at a time: that is the arithmetic of the CPU
+    # reference stream (per-token processing; a tensor-parallel model always prefills this way), so the KV cache the
+    # timed decode starts from holds the reference's bits and the stream can be checked token for token
+    model.truncate_kv(0)
+    t_pt = time.perf_counter()
+    for i in range(prompt_len - 1):
+        model.forward_prefill(prompt[i:i + 1], i, want_logits=False)
+    logits = model.forward(int(prompt[-1]), prompt_len - 1)
+    t_pt = time.perf_counter() - t_pt
     tok = int(np.argmax(logits))
     pos = prompt_len
     launches0 = model.launch_count()
-
+    decoded = [tok]
     # ---- value: K chained steps on the device --------------------------------------------
     warm, _ = model.generate_greedy(tok, pos, W)
+    decoded += [int(t) for t in warm]
     tok, pos = int(warm[-1]), pos + W
     sampler = ClockSampler(local)
     if world > 1:
@@ -418,56 +463,70 @@ def cuda_arm(args, rank, world):
         t = torch.tensor([dev_ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_ms = float(t.item())
+    decoded += [int(t) for t in stream]
     tok, pos = int(stream[-1]), pos + K
 
     # ---- e2e: the same loop through the per-token host call -------------------------------
     for _ in range(W):
         tok = model.forward_greedy(tok, pos)
+        decoded.append(tok)
         pos += 1
     if world > 1:
         dist.barrier()
+    e2e_toks = []
     t0 = time.perf_counter()
     for _ in range(K):
         tok = model.forward_greedy(tok, pos)  # 16 bytes in (token, pos, len, step), 4 bytes out
+        e2e_toks.append(tok)
         pos += 1
     e2e_s = time.perf_counter() - t0
+    decoded += e2e_toks
     if world > 1:
         t = torch.tensor([e2e_s], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
-    clocks = sampler.stop()
     model_launches = model.launch_count() - launches0
+    # the stream against the CPU reference's (same model seed, same prompt): identical, or the run is not a valid number
+    gold = reference_stream() if (args.seed == 0 and prompt_len == PROMPT_LEN) else None
+    stream_check = None
+    if gold is not None:
+        want = gold["stream"][:len(decoded)]
+        n_same = next((i for i, (a, b) in enumerate(zip(decoded, want)) if a != b), min(len(decoded), len(want)))
+        stream_check = {"reference": "tests/golden/llama8b_stream.json (CPU oracle, per-token prompt)", "compared": min(len(decoded), len(want)),
+                        "matched": n_same, "identical": n_same == min(len(decoded), len(want))}
+        if not stream_check["identical"] and not args.no_stream_check:
+            raise SystemExit(f"bench.py: greedy stream differs from the CPU reference stream at decoded token {n_same} "
+                             f"(device {decoded[n_same]}, reference {want[n_same]})")
 
     out = None
+    if rank != 0:
+        sampler.stop()
     if rank == 0:
         hbm, which = measured_peaks()
         algo, us, roof_launches = roofline_q4k_gemv(torch, cb, iters=args.iters)
+        clocks = sampler.stop()  # the sampler covers the timed decode, the e2e loop and the kernel microbench
         achieved = algo / (us * 1e-6) / 1e9
+        traffic = roofline_traffic()
         step_gbs = TOKEN_WEIGHT_BYTES / (dev_ms / K * 1e-3) / 1e9
         value = K / (dev_ms * 1e-3)
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
             "vs_baseline": None,
-            "dtype": "int8 x int8 -> int32 dot, f32 scales and accumulation", "data": "synthetic",
-            "config": {"workload": "Llama-3-8B-shape random-init model (32 layers, 4096/14336, 32/8 heads, vocab 128256; "
-                                   "Q4_K attn/gate/up/embd, Q6_K down/output), 512-token prompt then greedy decode",
-                       "prompt_len": prompt_len, "kv_dtype": "f32", "parallelism": (f"tensor-parallel x{world}: rows of every matrix split over the GPUs, slices pushed "
-                                       "into peer memory over NVLink inside the step (4 exchanges per layer)")
-                       if world > 1 else "1 GPU",
-                       "stream_head": [int(t) for t in stream[:8]],
-                       "l2": "each token streams 4.84 GB of weights (>> 126 MB L2); the kernel microbench rotates "
-                             "16 weight copies (528 MB)",
-                       "build_s": round(t_build, 2), "prefill_s": round(t_pre, 4)},
+            "dtype": DTYPE, "data": "synthetic",
+            "config": bench_config(prompt_len, world, [int(t) for t in decoded[:8]]),
+            "prompt": {"batched_prefill_s": round(t_pre, 4), "batched_prefill_tok_s": round(prompt_len / t_pre, 1),
+                       "per_token_prefill_s": round(t_pt, 3), "build_s": round(t_build, 2)},
+            "stream_check": stream_check,
             "e2e": {"value": K / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 4},
             "gpu_launches": int(model_launches + roof_launches),
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "gemv_kernel<Q4_K, 1 column> 14336x4096", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": ROOFLINE_KERNEL, "achieved": achieved,
                          "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "peak_source": which,
                          "frac_of_nominal_8000": achieved / 8000.0, "us_per_launch": us, "algorithmic_bytes": algo,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this shape, from
-                         # a separate ncu capture of this kernel at this shape (a profiler cannot run inside the timed bench)
-                         "traffic": 33.05e6 + 0.06e6, "traffic_source": "ncu capture of one launch of this kernel at this shape"},
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this shape, read from
+                         # the summary of a separate ncu capture (a profiler cannot run inside the timed bench)
+                         "traffic": traffic["bytes"], "traffic_source": traffic["source"]},
             "step_roofline": {"bound": "hbm", "weight_bytes_per_token": TOKEN_WEIGHT_BYTES, "achieved": step_gbs,
                               "peak": hbm * world, "unit": "GB/s", "frac": step_gbs / (hbm * world),
                               "roofline_tok_s_at_peak": hbm * world * 1e9 / TOKEN_WEIGHT_BYTES},
@@ -476,11 +535,12 @@ def cuda_arm(args, rank, world):
     if rank == 0:
         if world == 1 and not args.no_cpu:
             threads = os.cpu_count() or 1
-            v, t_layer, t_head = cpu_decode_sample(3, threads)
-            out["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
-                                   "sample": "3 reps of one layer's 7 projection GEMVs + the LM-head GEMV (AVX2 int8 "
-                                             "tier, all host threads); token = 32 layers + head",
-                                   "ms_layer": t_layer * 1e3, "ms_head": t_head * 1e3}
+            r = cpu_token_bench(6, 2, threads)
+            out["cpu_baseline"] = {"value": r["tok_s"], "unit": UNIT, "cores": threads, "kind": "port",
+                                   "sample": f"6 whole greedy decode tokens of the full 32-layer model after a {CPU_CONTEXT}-token prompt "
+                                             f"(all GEMVs, attention, norms, RoPE, SiLU*mul, LM head, argmax), oracle restatement of cera's "
+                                             f"x86 int8 tier '{r['tier']}', all host threads",
+                                   "tiers": r["tiers"], "one_thread_tok_s": r["one_thread_tok_s"], "model_build_s": round(r["build_s"], 1)}
         print(json.dumps(out))
     if world > 1:
         dist.barrier()
@@ -497,6 +557,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
                     help="prompt tokens before the timed decode (512 is the benchmark; shorter only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-stream-check", action="store_true", help="report a stream that differs from the reference's instead of failing")
     ap.add_argument("--only", default=None, choices=["roofline", "gemv-sweep", "gemm-sweep", "moe", "attn-sweep"],
                     help="run just the dominant-kernel microbench (the case ncu captures are taken on)")
     ap.add_argument("--iters", type=int, default=200, help="timed launches of the kernel microbench")
@@ -508,7 +569,7 @@ def main():
         import cera_b200 as cb
         algo, us, n = roofline_q4k_gemv(torch, cb, args.iters)
         hbm, which = measured_peaks()
-        print(json.dumps({"kernel": "gemv_kernel<Q4_K, 1 column> 14336x4096", "us_per_launch": us,
+        print(json.dumps({"kernel": ROOFLINE_KERNEL, "us_per_launch": us,
                           "achieved_gbs": algo / us / 1e3, "frac": algo / us / 1e3 / hbm, "peak_source": which,
                           "launches": n}))
     elif args.only == "gemv-sweep":

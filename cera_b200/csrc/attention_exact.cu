@@ -10,8 +10,9 @@
 // position order.  The last step is a serial chain per output element that an online-softmax
 // (flash-decode) kernel cannot reproduce, so the work is split differently here:
 //
-//   scores kernel : one thread per (position, query head); the G heads of a KV head sit in adjacent
-//                   threads and share the K row.  Scores go to a workspace [n_heads][ld].
+//   scores kernel : one half-warp per (position, query head): its sixteen lanes are the sixteen chains, and
+//                   four shuffle steps add them in the reference's order.  Scores go to a workspace
+//                   [n_heads][ld].
 //   values kernel : one CTA per (KV head, 32 output dims).  Its warps first turn the scores of the
 //                   group's heads into probabilities (maximum, ggml_expf, f64 sum by a fixed tree,
 //                   scaling; the heads side by side), while all threads stage the V slice through
@@ -34,92 +35,59 @@ namespace cera {
 
 namespace {
 
-constexpr int AX_TILE = 32;        // positions per CTA pass of the scores kernel
 constexpr int AX_VTHREADS = 256;   // threads of the values kernel
 constexpr uint32_t AX_SMEM_POS = 4096;  // probabilities of up to this many positions stay in shared memory
 
-__device__ __forceinline__ void load8(const void *base, size_t elem, bool f16, float (&v)[8]) {
-    if (f16) {
-        const uint4 r = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(base) + elem));
-        const __half2 *h = reinterpret_cast<const __half2 *>(&r);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __half22float2(h[i]);
-            v[2 * i] = f.x;
-            v[2 * i + 1] = f.y;
-        }
-    } else {
-        const float4 a = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(base) + elem));
-        const float4 b = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(base) + elem + 4));
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    }
-}
-
-// blockDim.x = AX_TILE * G.  Dynamic shared memory: G * (hd + 4) floats.
-__global__ void attn_scores_exact_kernel(const float *__restrict__ q, const void *__restrict__ kc, int kv_f16, uint32_t seq_len,
-                                         const uint32_t *__restrict__ seq_dev, uint32_t n_kv, uint32_t G, uint32_t hd, float scale,
-                                         float *__restrict__ ws, uint32_t ld) {
+// One HALF-WARP per (position, query head): its sixteen lanes are the reference's sixteen FMA chains (accumulator a,
+// lane L) - lane c = 8a + L multiplies elements 16j + c of the head for j = 0, 1, ... - and four xor-shuffle steps add
+// them in the reference's order (the two accumulators, then hsum256: lanes L and L+4, then (0,2) and (1,3), then the
+// two).  The two half-warps of a warp take two heads of the same position, so they read the same K row; the heads of
+// a group iterate over the warp pairs.  blockDim.x = 256 (eight warps = eight positions per pass); dynamic shared
+// memory: G * hd floats of q.
+constexpr int AX_SWARPS = 8;
+template <int HD>  // head size known at compile time (0: read it from the argument)
+__global__ void __launch_bounds__(AX_SWARPS * 32)
+attn_scores_exact_kernel(const float *__restrict__ q, const void *__restrict__ kc, int kv_f16, uint32_t seq_len,
+                         const uint32_t *__restrict__ seq_dev, uint32_t n_kv, uint32_t G, uint32_t hd_arg, float scale,
+                         float *__restrict__ ws, uint32_t ld) {
     extern __shared__ __align__(16) float ax_q[];
+    const uint32_t hd = HD ? (uint32_t)HD : hd_arg;
     pdl_trigger();
     pdl_wait();
     const uint32_t seq = seq_dev ? *seq_dev : seq_len;
-    const uint32_t kvh = blockIdx.y, qstride = hd + 4;
-    for (uint32_t i = threadIdx.x; i < G * hd; i += blockDim.x) ax_q[(i / hd) * qstride + i % hd] = q[(size_t)kvh * G * hd + i];
+    const uint32_t kvh = blockIdx.y;
+    for (uint32_t i = threadIdx.x; i < G * hd; i += blockDim.x) ax_q[i] = q[(size_t)kvh * G * hd + i];
     __syncthreads();
-    const uint32_t h = threadIdx.x % G, pt = threadIdx.x / G;
-    const float *qh = ax_q + h * qstride;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, c = lane & 15, hsel = lane >> 4;
     const size_t kv_dim = (size_t)n_kv * hd;
-    const uint32_t nv = hd / 8;
-    for (uint32_t tile = blockIdx.x; tile * AX_TILE < seq; tile += gridDim.x) {
-        const uint32_t t = tile * AX_TILE + pt;
-        if (t >= seq) continue;
+    const uint32_t nv = hd / 8, a = c >> 3, steps = (nv + 1) / 2;
+    for (uint32_t t = blockIdx.x * AX_SWARPS + warp; t < seq; t += gridDim.x * AX_SWARPS) {
         const size_t row = (size_t)t * kv_dim + (size_t)kvh * hd;
-        float s0[8], s1[8];
+        // this lane's elements of the K row: 16j + c while chunk 2j + a exists (at most 16 of them: hd <= 256)
+        float kv[16];
 #pragma unroll
-        for (int L = 0; L < 8; ++L) s0[L] = s1[L] = 0.0f;
-        uint32_t i = 0;
-        // 64 elements of the K row per batch: all of a batch's loads are issued before its FMAs
-        for (; i + 8 <= nv; i += 8) {
-            float kk[8][8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) load8(kc, row + 8 * (i + j), kv_f16, kk[j]);
-#pragma unroll
-            for (int j = 0; j < 8; j += 2) {
-                const float4 qa = *reinterpret_cast<const float4 *>(qh + 8 * (i + j)), qb = *reinterpret_cast<const float4 *>(qh + 8 * (i + j) + 4);
-                const float4 qc = *reinterpret_cast<const float4 *>(qh + 8 * (i + j) + 8), qd = *reinterpret_cast<const float4 *>(qh + 8 * (i + j) + 12);
-                const float q0[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-                const float q1[8] = {qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
-#pragma unroll
-                for (int L = 0; L < 8; ++L) {
-                    s0[L] = fmaf(q0[L], kk[j][L], s0[L]);
-                    s1[L] = fmaf(q1[L], kk[j + 1][L], s1[L]);
-                }
+        for (uint32_t j = 0; j < 16; ++j) {
+            kv[j] = 0.0f;
+            if (j < steps && 2 * j + a < nv) {
+                const size_t e = row + 16 * j + c;
+                kv[j] = kv_f16 ? __half2float(__ldg(reinterpret_cast<const __half *>(kc) + e)) : __ldg(reinterpret_cast<const float *>(kc) + e);
             }
         }
-        for (; i + 2 <= nv; i += 2) {
-            float k0[8], k1[8];
-            load8(kc, row + 8 * i, kv_f16, k0);
-            load8(kc, row + 8 * i + 8, kv_f16, k1);
+        for (uint32_t h0 = 0; h0 < G; h0 += 2) {
+            const uint32_t h = h0 + hsel;
+            const bool live = h < G;
+            const float *qh = ax_q + (live ? h : 0) * hd;
+            float acc = 0.0f;
 #pragma unroll
-            for (int L = 0; L < 8; ++L) {
-                s0[L] = fmaf(qh[8 * i + L], k0[L], s0[L]);
-                s1[L] = fmaf(qh[8 * i + 8 + L], k1[L], s1[L]);
-            }
+            for (uint32_t j = 0; j < 16; ++j)
+                if (j < steps && 2 * j + a < nv) acc = fmaf(qh[16 * j + c], kv[j], acc);
+            // accumulators 0 and 1 of the same lane L, then hsum256
+            acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
+            acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+            acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+            acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+            if (live && c == 0) ws[(size_t)(kvh * G + h) * ld + t] = __fmul_rn(acc, scale);
         }
-        if (i < nv) {
-            float k0[8];
-            load8(kc, row + 8 * i, kv_f16, k0);
-#pragma unroll
-            for (int L = 0; L < 8; ++L) s0[L] = fmaf(qh[8 * i + L], k0[L], s0[L]);
-        }
-        float s[8];
-#pragma unroll
-        for (int L = 0; L < 8; ++L) s[L] = __fadd_rn(s0[L], s1[L]);
-        // hsum256: lanes i and i+4, then (0,2) and (1,3), then the two (cera/src/backend/cpu.rs:3489-3497)
-        const float a0 = __fadd_rn(s[0], s[4]), a1 = __fadd_rn(s[1], s[5]), a2 = __fadd_rn(s[2], s[6]), a3 = __fadd_rn(s[3], s[7]);
-        const float dot = __fadd_rn(__fadd_rn(a0, a2), __fadd_rn(a1, a3));
-        ws[(size_t)(kvh * G + h) * ld + t] = __fmul_rn(dot, scale);
     }
 }
 
@@ -133,6 +101,65 @@ __device__ __forceinline__ void ax_wait() { asm volatile("cp.async.wait_group %0
 
 constexpr int AX_VT = 64;      // positions per staged V tile
 constexpr int AX_VSTAGES = 4;  // tiles in flight
+constexpr int AX_VTHREADS_C = 256;
+
+__device__ __forceinline__ void ax_load_v(const char *base, uint32_t i, uint32_t dq, int kv_f16, float (&v)[4]) {
+    if (kv_f16) {
+        const uint2 r = *reinterpret_cast<const uint2 *>(base + (size_t)i * 64 + dq * 8);
+        const __half2 *hh = reinterpret_cast<const __half2 *>(&r);
+        const float2 a = __half22float2(hh[0]), b = __half22float2(hh[1]);
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    } else {
+        const float4 r = *reinterpret_cast<const float4 *>(base + (size_t)i * 128 + dq * 16);
+        v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+    }
+}
+
+// 64 positions (or fewer) of the chains of one thread: out[d] = fma(p[t], V[t][d], out[d]) for its four dims, in position
+// order.  pp: the head's probabilities from this tile's first position on, 16-byte aligned.
+__device__ __forceinline__ void ax_chain_tile(const char *base, const float *__restrict__ pp, uint32_t cnt, uint32_t dq, int kv_f16, float (&acc)[4]) {
+    uint32_t i = 0;
+#pragma unroll 4
+    for (; i + 4 <= cnt; i += 4) {  // four positions per step: one 128-bit load of probabilities, four of values
+        const float4 p4 = *reinterpret_cast<const float4 *>(pp + i);
+        float v0[4], v1[4], v2[4], v3[4];
+        ax_load_v(base, i, dq, kv_f16, v0);
+        ax_load_v(base, i + 1, dq, kv_f16, v1);
+        ax_load_v(base, i + 2, dq, kv_f16, v2);
+        ax_load_v(base, i + 3, dq, kv_f16, v3);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = fmaf(p4.x, v0[j], acc[j]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = fmaf(p4.y, v1[j], acc[j]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = fmaf(p4.z, v2[j], acc[j]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = fmaf(p4.w, v3[j], acc[j]);
+    }
+    for (; i < cnt; ++i) {
+        float v[4];
+        ax_load_v(base, i, dq, kv_f16, v);
+        const float pv = pp[i];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = fmaf(pv, v[j], acc[j]);
+    }
+}
+
+// Requests V tile `tile` (64 positions x 32 dims of one KV head) into its ring slot; every thread commits one group
+// per call, empty or not, so the wait counts stay uniform.
+__device__ __forceinline__ void ax_stage_tile(uint32_t tile, uint32_t n_tiles, uint32_t seq, uint32_t per_pos, float *vt, const void *vc,
+                                              size_t kv_dim, size_t col0, int kv_f16, int tid) {
+    if (tile < n_tiles) {
+        char *dst = reinterpret_cast<char *>(vt + (size_t)(tile % AX_VSTAGES) * AX_VT * 32);
+        const uint32_t t0 = tile * AX_VT, cnt = min((uint32_t)AX_VT, seq - t0) * per_pos;
+        for (uint32_t i = tid; i < cnt; i += AX_VTHREADS_C) {
+            const uint32_t pl = i / per_pos, pc = i % per_pos;
+            const char *src = reinterpret_cast<const char *>(vc) + ((size_t)(t0 + pl) * kv_dim + col0) * (kv_f16 ? 2 : 4) + pc * 16;
+            ax_cp16(dst + (size_t)pl * per_pos * 16 + pc * 16, src);
+        }
+    }
+    ax_commit();
+}
 
 // grid (hd / 32, n_kv), AX_VTHREADS threads.  ws: scores [n_heads][ld]; pw: probabilities [n_heads][ld] in global
 // memory, used when the positions do not fit shared memory (every CTA of a KV head writes the same values there).
@@ -143,7 +170,8 @@ attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, u
                          uint32_t smem_pos, float *__restrict__ out, float *scales, int8_t *quants, int16_t *sums, const TpHook tp) {
     extern __shared__ __align__(16) float ax_dyn[];
     float *vt = ax_dyn;                                  // [AX_VSTAGES][AX_VT][32] (f16 caches use half of each tile)
-    float *ax_p = ax_dyn + AX_VSTAGES * AX_VT * 32;      // [position][G]
+    float *ax_p = ax_dyn + AX_VSTAGES * AX_VT * 32;      // [G][smem_pos + 4]: a head's probabilities are contiguous, heads four banks apart
+    const uint32_t pstride = smem_pos + 4;
     __shared__ double red_d[AX_VTHREADS / 32];
     __shared__ float red_f[AX_VTHREADS / 32];
     pdl_trigger();
@@ -157,20 +185,9 @@ attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, u
     // V tiles: a position's 32-dim slice is 128 contiguous bytes (64 for an f16 cache): 16-byte asynchronous copies,
     // the first tiles are requested before the softmax below so that they land while it runs
     const uint32_t per_pos = kv_f16 ? 4 : 8;  // 16-byte pieces per position
-    auto stage_tile = [&](uint32_t tile) {
-        if (tile < n_tiles) {
-            char *dst = reinterpret_cast<char *>(vt + (size_t)(tile % AX_VSTAGES) * AX_VT * 32);
-            const uint32_t t0 = tile * AX_VT, cnt = min((uint32_t)AX_VT, seq - t0) * per_pos;
-            for (uint32_t i = tid; i < cnt; i += AX_VTHREADS) {
-                const uint32_t pl = i / per_pos, pc = i % per_pos;
-                const char *src = reinterpret_cast<const char *>(vc) + ((size_t)(t0 + pl) * kv_dim + (size_t)kvh * hd + d0) * (kv_f16 ? 2 : 4) + pc * 16;
-                ax_cp16(dst + (size_t)pl * per_pos * 16 + pc * 16, src);
-            }
-        }
-        ax_commit();  // every thread commits one group per tile slot, empty or not, so the wait counts stay uniform
-    };
 #pragma unroll
-    for (int i = 0; i < AX_VSTAGES - 1; ++i) stage_tile(i);
+#pragma unroll
+    for (int i = 0; i < AX_VSTAGES - 1; ++i) ax_stage_tile(i, n_tiles, seq, per_pos, vt, vc, kv_dim, (size_t)kvh * hd + d0, kv_f16, tid);
 
     // ---- probabilities of the group's heads.  Head h is handled by warps [h * nwh, (h + 1) * nwh).
     const uint32_t nwh = (AX_VTHREADS / 32) / G, h_mine = warp / nwh, wl = warp % nwh;  // warps past G * nwh idle here
@@ -182,7 +199,7 @@ attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, u
     if (has_head) {
         for (uint32_t t = hti; t < seq; t += hth) {
             const float v = s_row[t];
-            if (in_smem) ax_p[(size_t)t * G + h_mine] = v;
+            if (in_smem) ax_p[(size_t)h_mine * pstride + t] = v;
             mx = fmaxf(mx, v);  // f32::max fold: NaN scores are ignored
         }
     }
@@ -198,8 +215,8 @@ attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, u
     double sum = 0.0;
     if (has_head) {
         for (uint32_t t = hti; t < seq; t += hth) {
-            const float e = ggml_expf(__fsub_rn(in_smem ? ax_p[(size_t)t * G + h_mine] : s_row[t], mx));
-            if (in_smem) ax_p[(size_t)t * G + h_mine] = e;
+            const float e = ggml_expf(__fsub_rn(in_smem ? ax_p[(size_t)h_mine * pstride + t] : s_row[t], mx));
+            if (in_smem) ax_p[(size_t)h_mine * pstride + t] = e;
             sum += (double)e;
         }
     }
@@ -212,7 +229,7 @@ attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, u
         for (uint32_t w = 1; w < nwh; ++w) tot += red_d[h_mine * nwh + w];
         const float inv = (float)(1.0 / tot);
         for (uint32_t t = hti; t < seq; t += hth) {
-            if (in_smem) ax_p[(size_t)t * G + h_mine] = __fmul_rn(ax_p[(size_t)t * G + h_mine], inv);
+            if (in_smem) ax_p[(size_t)h_mine * pstride + t] = __fmul_rn(ax_p[(size_t)h_mine * pstride + t], inv);
             else p_row[t] = __fmul_rn(ggml_expf(__fsub_rn(s_row[t], mx)), inv);  // recomputed: the CTAs of a KV head all store the same value
         }
     }
@@ -226,26 +243,13 @@ attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, u
     for (uint32_t tile = 0; tile < n_tiles; ++tile) {
         ax_wait<AX_VSTAGES - 2>();  // this thread's copies of tile `tile` have landed
         __syncthreads();            // everyone's have; and every chain thread is done with the slot restaged below
-        stage_tile(tile + AX_VSTAGES - 1);
+        ax_stage_tile(tile + AX_VSTAGES - 1, n_tiles, seq, per_pos, vt, vc, kv_dim, (size_t)kvh * hd + d0, kv_f16, tid);
         if (chain) {
             const uint32_t t0 = tile * AX_VT, cnt = min((uint32_t)AX_VT, seq - t0);
             const char *base = reinterpret_cast<const char *>(vt + (size_t)(tile % AX_VSTAGES) * AX_VT * 32);
-#pragma unroll 8
-            for (uint32_t i = 0; i < cnt; ++i) {
-                float v[4];
-                if (kv_f16) {
-                    const uint2 r = *reinterpret_cast<const uint2 *>(base + (size_t)i * 64 + dq * 8);
-                    const __half2 *hh = reinterpret_cast<const __half2 *>(&r);
-                    const float2 a = __half22float2(hh[0]), b = __half22float2(hh[1]);
-                    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-                } else {
-                    const float4 r = *reinterpret_cast<const float4 *>(base + (size_t)i * 128 + dq * 16);
-                    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
-                }
-                const float p = in_smem ? ax_p[(size_t)(t0 + i) * G + h] : pg[t0 + i];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc[j] = fmaf(p, v[j], acc[j]);
-            }
+            // two copies of the loop so that shared-memory probabilities are read with shared loads, not generic ones
+            if (in_smem) ax_chain_tile(base, ax_p + (size_t)h * pstride + t0, cnt, dq, kv_f16, acc);
+            else ax_chain_tile(base, pg + t0, cnt, dq, kv_f16, acc);
         }
     }
     ax_wait<0>();
@@ -339,21 +343,28 @@ int32_t launch_decode_attention_exact(const float *q, const void *kc, const void
     if (seq_len > reach) return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: plan 0x%x does not cover %zu positions", plan, seq_len);
     float *ws = (float *)workspace, *pw = ws + n_heads * (size_t)ld;
     // scores: a fixed number of CTAs per KV head walks the position tiles, so one captured launch serves every length
-    const uint32_t tiles = (uint32_t)((reach + AX_TILE - 1) / AX_TILE);
-    uint32_t per_head = (uint32_t)(2 * sm_count() / (int)nkv);
+    const uint32_t tiles = (uint32_t)((reach + AX_SWARPS - 1) / AX_SWARPS);
+    uint32_t per_head = (uint32_t)(4 * sm_count() / (int)nkv);
     if (per_head < 1) per_head = 1;
     if (per_head > tiles) per_head = tiles;
     count_launch();
-    CERA_CUDA_TRY(launch_k(attn_scores_exact_kernel, dim3(per_head, nkv), dim3(AX_TILE * G), (size_t)G * (hd + 4) * sizeof(float), st, q,
-                           kc, kv_f16, (uint32_t)seq_len, seq_len_dev, nkv, G, hd, scale, ws, ld));
+    const dim3 sgrid(per_head, nkv), sblock(AX_SWARPS * 32);
+    const size_t sq = (size_t)G * hd * sizeof(float);
+    const uint32_t sl32 = (uint32_t)seq_len;
+    if (hd == 128) CERA_CUDA_TRY(launch_k(attn_scores_exact_kernel<128>, sgrid, sblock, sq, st, q, kc, kv_f16, sl32, seq_len_dev, nkv, G, hd, scale, ws, ld));
+    else if (hd == 64) CERA_CUDA_TRY(launch_k(attn_scores_exact_kernel<64>, sgrid, sblock, sq, st, q, kc, kv_f16, sl32, seq_len_dev, nkv, G, hd, scale, ws, ld));
+    else CERA_CUDA_TRY(launch_k(attn_scores_exact_kernel<0>, sgrid, sblock, sq, st, q, kc, kv_f16, sl32, seq_len_dev, nkv, G, hd, scale, ws, ld));
     const uint32_t smem_pos = b >= 5 ? 0u : (uint32_t)reach;
-    const size_t smem = ((size_t)AX_VSTAGES * AX_VT * 32 + (size_t)smem_pos * G) * sizeof(float);
-    if (smem > 48 * 1024) {
-        static bool raised = false;
-        if (!raised) {
+    const size_t smem = ((size_t)AX_VSTAGES * AX_VT * 32 + ((size_t)smem_pos + 4) * G) * sizeof(float);
+    {
+        // static + dynamic shared memory can pass the 48 KB default even at the shortest contexts: opt in once per device
+        static thread_local int raised_dev = -1;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (raised_dev != dev) {
             CERA_CUDA_TRY(cudaFuncSetAttribute(attn_values_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)((AX_VSTAGES * AX_VT * 32 + AX_SMEM_POS * 8) * sizeof(float))));
-            raised = true;
+                                               (int)((AX_VSTAGES * AX_VT * 32 + (AX_SMEM_POS + 4) * 8) * sizeof(float))));
+            raised_dev = dev;
         }
     }
     count_launch();

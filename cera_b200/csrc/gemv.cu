@@ -212,7 +212,9 @@ int32_t launch_gemm_ex(const WeightView &w, const ActView &x, size_t n, float *o
     const size_t k = w.k;
     {
         bool taken = false;
-        CERA_TRY(launch_gemm_mma(w, x, n, out, ldy, ldc, epilogue, st, &taken));
+        CERA_TRY(launch_gemm_tc(w, x, n, out, ldy, ldc, epilogue, st, &taken));  // tcgen05 / TMEM
+        if (taken) return CERA_CUDA_OK;
+        CERA_TRY(launch_gemm_mma(w, x, n, out, ldy, ldc, epilogue, st, &taken));  // warp-level mma.sync
         if (taken) return CERA_CUDA_OK;
     }
     size_t j = 0;

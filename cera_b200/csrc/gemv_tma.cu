@@ -344,6 +344,8 @@ int32_t cera_cuda_kernel_status(uint32_t *status_out) {
     if (!status_out) return fail(CERA_CUDA_ERR_BAD_ARG, "kernel_status: null argument");
     unsigned int v = 0;
     CERA_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_tma_status, sizeof(v)));
+    v |= gemm_tc_status() << 8;      // bits 8..12: roles of the tcgen05 GEMM
+    v |= gemv_exact_status() << 16;  // bit 16: a copy of the reference-order GEMV never arrived
     *status_out = v;
     if (v) return fail(CERA_CUDA_ERR_TIMEOUT, "a bounded device-side wait ran out (status word %u)", v);
     return CERA_CUDA_OK;

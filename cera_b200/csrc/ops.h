@@ -64,6 +64,11 @@ int32_t launch_gemm(const WeightView &w, const ActView &x, size_t n, float *out,
 // Tensor-core (mma.sync int8) GEMM for Q4_0 / Q4_K / Q5_K / Q6_K (k a multiple of 256) and n >= 5.  *taken = false: not its case.
 int32_t launch_gemm_mma(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
                         cudaStream_t st, bool *taken);
+// The same product on tcgen05 / TMEM (gemm_tc.cu): Q4_K / Q5_K, k a multiple of 256, more than 32 columns.
+int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
+                       cudaStream_t st, bool *taken);
+uint32_t gemm_tc_status();  // nonzero after a bounded wait of that kernel ran out
+uint32_t gemv_exact_status();
 // One work item of an expert-grouped GEMM: `count` consecutive activation columns starting at `first` go through
 // expert `expert`'s rows of a stacked weight matrix (built on the device by the routed-FFN kernels).
 struct MoeTile {

@@ -48,6 +48,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     atomicOr(status, who);
     return false;
 }
+// The same with mbarrier.try_wait, which suspends the thread in hardware for a bounded time instead of spinning on
+// test_wait: far fewer issued instructions while a copy is in flight.  Bounded like mbar_wait.
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_blocking(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag, unsigned int *status,
+                                                   unsigned int who) {
+    for (uint32_t i = 0; i < (SPIN_LIMIT >> 4); ++i) {  // each try may block for microseconds: keep the total bound comparable
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicOr(status, who);
+    return false;
+}
 // One contiguous global range (16-byte aligned, a multiple of 16 bytes) -> this CTA's shared memory; the bytes are
 // counted on `bar`.
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {

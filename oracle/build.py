@@ -10,7 +10,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "libcera_oracle.so")
-SRCS = ["cera_oracle.cpp", "cera_cpu_avx2.cpp"]
+SRCS = ["cera_oracle.cpp", "cera_cpu_avx2.cpp", "cera_cpu_vnni.cpp"]
 
 
 def build(force: bool = False) -> str:

@@ -110,7 +110,16 @@ class RowPool {
 };
 
 #if CERA_X86
+// One source, two tiers (as the reference instantiates one kernel macro twice, cera/src/backend/simd.rs:6306-6359 and
+// 7288-7345): the default build is the AVX2 tier; cera_cpu_vnni.cpp includes this file with CERA_TIER_VNNI defined,
+// which swaps the 4-way byte dot for vpdpbusd (256-bit, AVX-512 VNNI + VL) and suffixes the entry points with _vnni.
+#ifdef CERA_TIER_VNNI
+#define TGT __attribute__((target("avx2,fma,f16c,avx512f,avx512vl,avx512vnni")))
+#define CERA_CPU_FN(name) name##_vnni
+#else
 #define TGT __attribute__((target("avx2,fma,f16c")))
+#define CERA_CPU_FN(name) name
+#endif
 
 // Integer-only half widen, inlined here so the per-block scale load costs no call
 // (cera/src/quant.rs:48-73; tests compare it with cera_oracle_f16_to_f32).
@@ -133,7 +142,11 @@ inline float h2f_sw(uint16_t h) {
 inline uint16_t rd16(const uint8_t *p) { return (uint16_t)(p[0] | (p[1] << 8)); }
 
 TGT inline __m256i dot32u(__m256i w, __m256i a) {
+#ifdef CERA_TIER_VNNI
+    return _mm256_dpbusd_epi32(_mm256_setzero_si256(), w, a);  // simd.rs:7305-7313; equal to the AVX2 form while no i16 saturates
+#else
     return _mm256_madd_epi16(_mm256_maddubs_epi16(w, a), _mm256_set1_epi16(1));
+#endif
 }
 TGT inline __m256i dot32s(__m256i w, __m256i a) {
     return dot32u(_mm256_sign_epi8(w, w), _mm256_sign_epi8(a, w));
@@ -396,20 +409,25 @@ TGT void rows_q6_k(const uint8_t *w, const float *bs, const int8_t *bq, const in
 
 extern "C" {
 
-int cera_cpu_has_avx2(void) {
+int CERA_CPU_FN(cera_cpu_has_avx2)(void) {
 #if CERA_X86
+#ifdef CERA_TIER_VNNI
+    return __builtin_cpu_supports("avx2") && __builtin_cpu_supports("fma") && __builtin_cpu_supports("avx512vnni") &&
+           __builtin_cpu_supports("avx512vl");
+#else
     return __builtin_cpu_supports("avx2") && __builtin_cpu_supports("fma");
+#endif
 #else
     return 0;
 #endif
 }
 
-int cera_cpu_gemm_preq(int type, const uint8_t *w, const float *bs, const int8_t *bq, float *out,
-                       size_t m, size_t n, size_t k, int n_threads) {
+int CERA_CPU_FN(cera_cpu_gemm_preq)(int type, const uint8_t *w, const float *bs, const int8_t *bq, float *out,
+                                    size_t m, size_t n, size_t k, int n_threads) {
 #if CERA_X86
     const bool kq = type == CERA_T_Q4_K || type == CERA_T_Q6_K;
     const bool ok = type == CERA_T_Q4_0 || type == CERA_T_Q8_0 || type == CERA_T_Q4_1 || kq;
-    if (!cera_cpu_has_avx2() || !ok) return cera_oracle_gemm_preq(type, w, bs, bq, out, m, n, k);
+    if (!CERA_CPU_FN(cera_cpu_has_avx2)() || !ok) return cera_oracle_gemm_preq(type, w, bs, bq, out, m, n, k);
     if (k % (kq ? 256 : 32)) return -1;
     std::vector<int32_t> s32, s16;
     if (type == CERA_T_Q4_1 || kq) col_sums(bq, n, k, s32, s16, type == CERA_T_Q6_K);
@@ -430,13 +448,13 @@ int cera_cpu_gemm_preq(int type, const uint8_t *w, const float *bs, const int8_t
 #endif
 }
 
-int cera_cpu_gemv(int type, const uint8_t *w, const float *x, float *y, size_t m, size_t k,
-                  int n_threads) {
+int CERA_CPU_FN(cera_cpu_gemv)(int type, const uint8_t *w, const float *x, float *y, size_t m, size_t k,
+                               int n_threads) {
     if (k % 32) return -1;
     std::vector<float> xs(k / 32);
     std::vector<int8_t> xq(k);
     cera_oracle_quantize_q8_0(x, k, xs.data(), xq.data());
-    return cera_cpu_gemm_preq(type, w, xs.data(), xq.data(), y, m, 1, k, n_threads);
+    return CERA_CPU_FN(cera_cpu_gemm_preq)(type, w, xs.data(), xq.data(), y, m, 1, k, n_threads);
 }
 
 }  // extern "C"

@@ -1062,6 +1062,13 @@ int cera_oracle_model_set_tensor(cera_oracle_model *m, int role, int layer, int 
 }
 
 int cera_cpu_gemv(int type, const uint8_t *w, const float *x, float *y, size_t m, size_t k, int nt);
+int cera_cpu_gemv_vnni(int type, const uint8_t *w, const float *x, float *y, size_t m, size_t k, int nt);
+int cera_cpu_has_avx2_vnni(void);
+
+// Which build of the x86 int8 kernels the model forward uses: 0 = the scalar restatement, 1 = AVX2 (default when the host
+// has it), 2 = AVX-512 VNNI.  All three give identical bits (tests); the choice only changes the wall time.
+static int g_cpu_tier = 1;
+void cera_oracle_set_cpu_tier(int tier) { g_cpu_tier = tier; }
 
 int cera_oracle_model_forward(cera_oracle_model *M, uint32_t token, size_t pos, float *logits) {
     const auto &c = M->cfg;
@@ -1072,8 +1079,10 @@ int cera_oracle_model_forward(cera_oracle_model *M, uint32_t token, size_t pos, 
     auto gemv = [&](const TensorRef &t, const float *x, float *y) {
         // The AVX2 build is bit-identical to the scalar restatement (tested), so
         // use it when present; it only changes the wall time.
-        if (cera_cpu_has_avx2() && int8_type(t.type) && t.type != CERA_T_Q5_K)
-            return cera_cpu_gemv(t.type, t.bytes, x, y, t.rows, t.cols, nt);
+        if (int8_type(t.type) && t.type != CERA_T_Q5_K) {
+            if (g_cpu_tier == 2 && cera_cpu_has_avx2_vnni()) return cera_cpu_gemv_vnni(t.type, t.bytes, x, y, t.rows, t.cols, nt);
+            if (g_cpu_tier >= 1 && cera_cpu_has_avx2()) return cera_cpu_gemv(t.type, t.bytes, x, y, t.rows, t.cols, nt);
+        }
         return gemv_impl(t.type, t.bytes, x, y, t.rows, t.cols, nt);
     };
     std::vector<float> hidden(hs), normed(hs), q(qd), k(kvd), v(kvd), attn(qd), out(hs), g(ff), u(ff),
@@ -1201,6 +1210,7 @@ int cera_oracle_model_shift_kv(cera_oracle_model *M, size_t n_keep, size_t shift
     return 0;
 }
 size_t cera_oracle_model_seq_len(const cera_oracle_model *m) { return m->seq_len; }
+void cera_oracle_model_set_threads(cera_oracle_model *m, int n) { m->cfg.n_threads = n; }
 int cera_oracle_model_last_hidden(const cera_oracle_model *m, float *out) {
     if (m->last_hidden.empty()) return -1;
     std::memcpy(out, m->last_hidden.data(), m->last_hidden.size() * 4);

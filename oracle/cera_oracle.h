@@ -175,6 +175,7 @@ int cera_oracle_model_set_lora(cera_oracle_model *m, int target, int layer, size
 void cera_oracle_model_truncate_kv(cera_oracle_model *m, size_t len);
 /* cera/src/kv_cache.rs:1091-1320 (shift_kv_with_rope); -1 on the reference's assertion cases */
 int cera_oracle_model_shift_kv(cera_oracle_model *m, size_t n_keep, size_t shift);
+void cera_oracle_model_set_threads(cera_oracle_model *m, int n_threads);
 size_t cera_oracle_model_seq_len(const cera_oracle_model *m);
 /* Copies the last hidden-state snapshots recorded by forward (for drift
  * diagnosis): which = 0 final normed hidden. */
@@ -185,6 +186,12 @@ void cera_oracle_model_free(cera_oracle_model *m);
  * cera/src/backend/simd.rs:6306-6359 instantiation).  Bit-identical to
  * cera_oracle_gemm_preq by test. ---- */
 int cera_cpu_has_avx2(void);
+/* The AVX-512 VNNI tier (cera_cpu_vnni.cpp): same entry points with the _vnni suffix, bit-identical results. */
+int cera_cpu_has_avx2_vnni(void);
+void cera_oracle_set_cpu_tier(int tier); /* model forward: 0 scalar, 1 AVX2 (default), 2 AVX-512 VNNI */
+int cera_cpu_gemm_preq_vnni(int type, const uint8_t *w, const float *b_scales, const int8_t *b_quants, float *out,
+                            size_t m, size_t n, size_t k, int n_threads);
+int cera_cpu_gemv_vnni(int type, const uint8_t *w, const float *x, float *y, size_t m, size_t k, int n_threads);
 int cera_cpu_gemm_preq(int type, const uint8_t *w, const float *b_scales, const int8_t *b_quants,
                        float *out, size_t m, size_t n, size_t k, int n_threads);
 int cera_cpu_gemv(int type, const uint8_t *w, const float *x, float *y, size_t m, size_t k,

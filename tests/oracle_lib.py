@@ -57,6 +57,10 @@ _sig("cera_oracle_synth_normal", None, _p, _sz, C.c_uint64, C.c_uint64, C.c_floa
 _sig("cera_cpu_has_avx2", C.c_int)
 _sig("cera_cpu_gemm_preq", C.c_int, C.c_int, _p, _p, _p, _p, _sz, _sz, _sz, C.c_int)
 _sig("cera_cpu_gemv", C.c_int, C.c_int, _p, _p, _p, _sz, _sz, C.c_int)
+_sig("cera_cpu_has_avx2_vnni", C.c_int)
+_sig("cera_oracle_set_cpu_tier", None, C.c_int)
+_sig("cera_cpu_gemm_preq_vnni", C.c_int, C.c_int, _p, _p, _p, _p, _sz, _sz, _sz, C.c_int)
+_sig("cera_cpu_gemv_vnni", C.c_int, C.c_int, _p, _p, _p, _sz, _sz, C.c_int)
 
 
 class OracleConfig(C.Structure):
@@ -74,6 +78,7 @@ _sig("cera_oracle_model_shift_kv", C.c_int, _p, _sz, _sz)
 _sig("cera_oracle_lora_apply", None, _sz, _sz, _sz, C.c_float, _p, _p, _p, _p)
 _sig("cera_oracle_model_set_lora", C.c_int, _p, C.c_int, C.c_int, _sz, _sz, _sz, C.c_float, _p, _p)
 _sig("cera_oracle_model_seq_len", _sz, _p)
+_sig("cera_oracle_model_set_threads", None, _p, C.c_int)
 _sig("cera_oracle_model_last_hidden", C.c_int, _p, _p)
 _sig("cera_oracle_model_free", None, _p)
 
@@ -151,7 +156,9 @@ def gemm_preq(t, w, bs, bq, m, n, k, avx2=False, threads=1):
     bs = c32(bs)
     bq = np.ascontiguousarray(bq, dtype=np.int8)
     out = np.full(m * n, np.nan, dtype=np.float32)
-    if avx2:
+    if avx2 == "vnni":
+        rc = _lib.cera_cpu_gemm_preq_vnni(t, _ptr(w), _ptr(bs), _ptr(bq), _ptr(out), m, n, k, threads)
+    elif avx2:
         rc = _lib.cera_cpu_gemm_preq(t, _ptr(w), _ptr(bs), _ptr(bq), _ptr(out), m, n, k, threads)
     else:
         rc = _lib.cera_oracle_gemm_preq(t, _ptr(w), _ptr(bs), _ptr(bq), _ptr(out), m, n, k)
@@ -163,7 +170,9 @@ def gemv(t, w, x, m, k, avx2=False, threads=1):
     w = np.ascontiguousarray(w, dtype=np.uint8)
     x = c32(x)
     y = np.full(m, np.nan, dtype=np.float32)
-    if avx2:
+    if avx2 == "vnni":
+        rc = _lib.cera_cpu_gemv_vnni(t, _ptr(w), _ptr(x), _ptr(y), m, k, threads)
+    elif avx2:
         rc = _lib.cera_cpu_gemv(t, _ptr(w), _ptr(x), _ptr(y), m, k, threads)
     else:
         rc = _lib.cera_oracle_gemv(t, _ptr(w), _ptr(x), _ptr(y), m, k)
@@ -173,6 +182,15 @@ def gemv(t, w, x, m, k, avx2=False, threads=1):
 
 def has_avx2():
     return bool(_lib.cera_cpu_has_avx2())
+
+
+def has_vnni():
+    return bool(_lib.cera_cpu_has_avx2_vnni())
+
+
+def set_cpu_tier(tier):
+    """Which build of the x86 int8 kernels OracleModel.forward runs: "scalar", "avx2" (default) or "vnni"."""
+    _lib.cera_oracle_set_cpu_tier({"scalar": 0, "avx2": 1, "vnni": 2}[tier])
 
 
 def rmsnorm(x, w, eps):
@@ -286,6 +304,9 @@ class OracleModel:
 
     def truncate_kv(self, n):
         _lib.cera_oracle_model_truncate_kv(self.h, n)
+
+    def set_threads(self, n):
+        _lib.cera_oracle_model_set_threads(self.h, n)
 
     def set_lora(self, target, layer, a, b, scale):
         """a: [rank, k], b: [d, rank] float32."""

@@ -118,6 +118,28 @@ def test_avx2_build_is_bit_identical_to_scalar_restatement():
             assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), (t, m, n)
 
 
+def test_vnni_build_is_bit_identical_to_avx2_and_scalar():
+    """cera/src/backend/simd.rs:7216-7286 holds the AVX-512 VNNI tier bit-identical to the AVX2 one; so does this
+    restatement (vpdpbusd against maddubs + madd on the reference's fixtures, extreme bytes included)."""
+    if not O.has_vnni():
+        pytest.skip("host has no AVX-512 VNNI + VL")
+    import test_oracle_formats as F
+    rng = np.random.default_rng(12)
+    for t in (O.Q4_0, O.Q8_0, O.Q4_1, O.Q4_K, O.Q6_K):
+        for (m, n) in ((9, 7), (3, 1), (70, 5), (130, 1)):
+            k = 512
+            w = F._rand_block_bytes(t, m, k, rng)
+            if t == O.Q8_0:
+                w.reshape(-1, 34)[:, 2:4] = 0x80  # the -128 weight extreme
+            lcg = R.Lcg(0x13579B + t)
+            bs, bq = R.activations(n, k, lcg)
+            a = O.gemm_preq(t, w, bs, bq, m, n, k, avx2=False)
+            b = O.gemm_preq(t, w, bs, bq, m, n, k, avx2=True, threads=2)
+            c = O.gemm_preq(t, w, bs, bq, m, n, k, avx2="vnni", threads=2)
+            assert np.array_equal(a.view(np.uint32), c.view(np.uint32)), (t, m, n)
+            assert np.array_equal(b.view(np.uint32), c.view(np.uint32)), (t, m, n)
+
+
 # simd.rs:7017-7103: the GEMV entry is the GEMM at n == 1, bit for bit.
 def test_gemv_is_gemm_at_n1():
     import test_oracle_formats as F
