@@ -16,10 +16,11 @@
 //   values kernel : one CTA per (KV head, 32 output dims).  Its warps first turn the scores of the
 //                   group's heads into probabilities (maximum, ggml_expf, f64 sum by a fixed tree,
 //                   scaling; the heads side by side), while all threads stage the V slice through
-//                   shared memory with asynchronous copies, four 64-position tiles ahead; then 8
-//                   threads per head - four output dims each - walk the positions in order with one
-//                   FMA per dim per position, and finally emit the f32 outputs and their Q8_0 form
-//                   (a 32-dim slice of a head is one Q8_0 block).
+//                   shared memory with asynchronous copies, in tiles of 256 positions, two tiles
+//                   ahead (a context of up to 768 positions is requested whole before the softmax
+//                   starts); then one warp per head - a lane per output dim - walks the positions
+//                   in order with one FMA per position, and finally emits the f32 outputs and their
+//                   Q8_0 form (a 32-dim slice of a head is one Q8_0 block: one warp).
 //
 // The f64 sum of the exponentials is a tree, the reference's a left-to-right loop: the two can differ
 // in the last bits of the f64 sum, which survive the narrowing to f32 only in about one softmax in
@@ -99,63 +100,50 @@ __device__ __forceinline__ void ax_commit() { asm volatile("cp.async.commit_grou
 template <int N>
 __device__ __forceinline__ void ax_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-constexpr int AX_VT = 64;      // positions per staged V tile
-constexpr int AX_VSTAGES = 4;  // tiles in flight
+constexpr int AX_VT = 256;     // positions per staged V tile
+constexpr int AX_VSTAGES = 3;  // tiles in the ring (two in flight while one is walked)
 constexpr int AX_VTHREADS_C = 256;
 
-__device__ __forceinline__ void ax_load_v(const char *base, uint32_t i, uint32_t dq, int kv_f16, float (&v)[4]) {
-    if (kv_f16) {
-        const uint2 r = *reinterpret_cast<const uint2 *>(base + (size_t)i * 64 + dq * 8);
-        const __half2 *hh = reinterpret_cast<const __half2 *>(&r);
-        const float2 a = __half22float2(hh[0]), b = __half22float2(hh[1]);
-        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-    } else {
-        const float4 r = *reinterpret_cast<const float4 *>(base + (size_t)i * 128 + dq * 16);
-        v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
-    }
-}
-
-// 64 positions (or fewer) of the chains of one thread: out[d] = fma(p[t], V[t][d], out[d]) for its four dims, in position
-// order.  pp: the head's probabilities from this tile's first position on, 16-byte aligned.
-__device__ __forceinline__ void ax_chain_tile(const char *base, const float *__restrict__ pp, uint32_t cnt, uint32_t dq, int kv_f16, float (&acc)[4]) {
+// AX_VT positions (or fewer) of one lane's chain: out = fma(p[t], V[t][d], out) in position order.  `base`: the tile,
+// one row of 32 dims per position; pp: the head's probabilities from this tile's first position on, 16-byte aligned.
+template <bool F16>
+__device__ __forceinline__ float ax_chain_tile(const char *base, const float *__restrict__ pp, uint32_t cnt, uint32_t d, float acc) {
+    auto v_at = [&](uint32_t i) -> float {
+        if (F16) return __half2float(*reinterpret_cast<const __half *>(base + (size_t)i * 64 + d * 2));
+        return *reinterpret_cast<const float *>(base + (size_t)i * 128 + d * 4);
+    };
     uint32_t i = 0;
-#pragma unroll 4
-    for (; i + 4 <= cnt; i += 4) {  // four positions per step: one 128-bit load of probabilities, four of values
-        const float4 p4 = *reinterpret_cast<const float4 *>(pp + i);
-        float v0[4], v1[4], v2[4], v3[4];
-        ax_load_v(base, i, dq, kv_f16, v0);
-        ax_load_v(base, i + 1, dq, kv_f16, v1);
-        ax_load_v(base, i + 2, dq, kv_f16, v2);
-        ax_load_v(base, i + 3, dq, kv_f16, v3);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = fmaf(p4.x, v0[j], acc[j]);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = fmaf(p4.y, v1[j], acc[j]);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = fmaf(p4.z, v2[j], acc[j]);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = fmaf(p4.w, v3[j], acc[j]);
+#pragma unroll 2
+    for (; i + 8 <= cnt; i += 8) {  // eight positions per step: two 128-bit loads of probabilities, eight values
+        const float4 pa = *reinterpret_cast<const float4 *>(pp + i), pb = *reinterpret_cast<const float4 *>(pp + i + 4);
+        const float v0 = v_at(i), v1 = v_at(i + 1), v2 = v_at(i + 2), v3 = v_at(i + 3);
+        const float v4 = v_at(i + 4), v5 = v_at(i + 5), v6 = v_at(i + 6), v7 = v_at(i + 7);
+        acc = fmaf(pa.x, v0, acc);
+        acc = fmaf(pa.y, v1, acc);
+        acc = fmaf(pa.z, v2, acc);
+        acc = fmaf(pa.w, v3, acc);
+        acc = fmaf(pb.x, v4, acc);
+        acc = fmaf(pb.y, v5, acc);
+        acc = fmaf(pb.z, v6, acc);
+        acc = fmaf(pb.w, v7, acc);
     }
-    for (; i < cnt; ++i) {
-        float v[4];
-        ax_load_v(base, i, dq, kv_f16, v);
-        const float pv = pp[i];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = fmaf(pv, v[j], acc[j]);
-    }
+    for (; i < cnt; ++i) acc = fmaf(pp[i], v_at(i), acc);
+    return acc;
 }
 
-// Requests V tile `tile` (64 positions x 32 dims of one KV head) into its ring slot; every thread commits one group
+// Requests V tile `tile` (AX_VT positions x 32 dims of one KV head) into its ring slot; every thread commits one group
 // per call, empty or not, so the wait counts stay uniform.
 __device__ __forceinline__ void ax_stage_tile(uint32_t tile, uint32_t n_tiles, uint32_t seq, uint32_t per_pos, float *vt, const void *vc,
                                               size_t kv_dim, size_t col0, int kv_f16, int tid) {
     if (tile < n_tiles) {
         char *dst = reinterpret_cast<char *>(vt + (size_t)(tile % AX_VSTAGES) * AX_VT * 32);
         const uint32_t t0 = tile * AX_VT, cnt = min((uint32_t)AX_VT, seq - t0) * per_pos;
+        const uint32_t sh = kv_f16 ? 2 : 3;  // per_pos = 4 or 8 pieces of 16 bytes
+        const char *src0 = reinterpret_cast<const char *>(vc) + ((size_t)t0 * kv_dim + col0) * (kv_f16 ? 2 : 4);
+        const size_t row_bytes = kv_dim * (kv_f16 ? 2 : 4);
         for (uint32_t i = tid; i < cnt; i += AX_VTHREADS_C) {
-            const uint32_t pl = i / per_pos, pc = i % per_pos;
-            const char *src = reinterpret_cast<const char *>(vc) + ((size_t)(t0 + pl) * kv_dim + col0) * (kv_f16 ? 2 : 4) + pc * 16;
-            ax_cp16(dst + (size_t)pl * per_pos * 16 + pc * 16, src);
+            const uint32_t pl = i >> sh, pc = i & (per_pos - 1);
+            ax_cp16(dst + (size_t)i * 16, src0 + (size_t)pl * row_bytes + pc * 16);
         }
     }
     ax_commit();
@@ -186,8 +174,7 @@ attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, u
     // the first tiles are requested before the softmax below so that they land while it runs
     const uint32_t per_pos = kv_f16 ? 4 : 8;  // 16-byte pieces per position
 #pragma unroll
-#pragma unroll
-    for (int i = 0; i < AX_VSTAGES - 1; ++i) ax_stage_tile(i, n_tiles, seq, per_pos, vt, vc, kv_dim, (size_t)kvh * hd + d0, kv_f16, tid);
+    for (int i = 0; i < AX_VSTAGES; ++i) ax_stage_tile(i, n_tiles, seq, per_pos, vt, vc, kv_dim, (size_t)kvh * hd + d0, kv_f16, tid);
 
     // ---- probabilities of the group's heads.  Head h is handled by warps [h * nwh, (h + 1) * nwh).
     const uint32_t nwh = (AX_VTHREADS / 32) / G, h_mine = warp / nwh, wl = warp % nwh;  // warps past G * nwh idle here
@@ -235,61 +222,58 @@ attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, u
     }
     // (the first barrier of the tile loop below also publishes the probabilities)
 
-    // ---- out[d] = fma(p[t], V[t][d], out[d]) in position order: eight threads per head, four dims each
-    const bool chain = tid < (int)(G * 8);
-    const uint32_t h = tid >> 3, dq = tid & 7;
+    // ---- out[d] = fma(p[t], V[t][d], out[d]) in position order: warp h walks head h, a lane per output dim
+    const bool chain = (uint32_t)warp < G;
+    const uint32_t h = warp, d = lane;
     const float *pg = pw + (size_t)(kvh * G + (chain ? h : 0)) * ld;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float acc = 0.0f;
     for (uint32_t tile = 0; tile < n_tiles; ++tile) {
-        ax_wait<AX_VSTAGES - 2>();  // this thread's copies of tile `tile` have landed
-        __syncthreads();            // everyone's have; and every chain thread is done with the slot restaged below
-        ax_stage_tile(tile + AX_VSTAGES - 1, n_tiles, seq, per_pos, vt, vc, kv_dim, (size_t)kvh * hd + d0, kv_f16, tid);
+        // this thread's copies of tile `tile` have landed: tiles 0-2 were committed up front, tile j + 2 in iteration j,
+        // so at most two younger groups (iteration 0) or one (later) may still be in flight
+        if (tile == 0) ax_wait<2>();
+        else ax_wait<1>();
+        __syncthreads();  // everyone's have; and every chain warp is done with the slot restaged below
+        if (tile > 0) ax_stage_tile(tile - 1 + AX_VSTAGES, n_tiles, seq, per_pos, vt, vc, kv_dim, (size_t)kvh * hd + d0, kv_f16, tid);
         if (chain) {
             const uint32_t t0 = tile * AX_VT, cnt = min((uint32_t)AX_VT, seq - t0);
             const char *base = reinterpret_cast<const char *>(vt + (size_t)(tile % AX_VSTAGES) * AX_VT * 32);
-            // two copies of the loop so that shared-memory probabilities are read with shared loads, not generic ones
-            if (in_smem) ax_chain_tile(base, ax_p + (size_t)h * pstride + t0, cnt, dq, kv_f16, acc);
-            else ax_chain_tile(base, pg + t0, cnt, dq, kv_f16, acc);
+            // separate instantiations so that shared-memory probabilities are read with shared loads, not generic ones
+            if (in_smem) acc = kv_f16 ? ax_chain_tile<true>(base, ax_p + (size_t)h * pstride + t0, cnt, d, acc)
+                                      : ax_chain_tile<false>(base, ax_p + (size_t)h * pstride + t0, cnt, d, acc);
+            else acc = kv_f16 ? ax_chain_tile<true>(base, pg + t0, cnt, d, acc) : ax_chain_tile<false>(base, pg + t0, cnt, d, acc);
         }
     }
     ax_wait<0>();
     if (!chain) return;
-    const size_t o = (size_t)(kvh * G + h) * hd + d0 + 4 * dq;
-    *reinterpret_cast<float4 *>(out + o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    const size_t o = (size_t)(kvh * G + h) * hd + d0 + d;
+    out[o] = acc;
     if (quants) {
-        // Q8_0 of the 32-dim block the eight threads of this head hold (cera/src/backend/cpu.rs:942-958)
-        float amax = 0.0f;
+        // Q8_0 of the 32-dim block this warp holds (cera/src/backend/cpu.rs:942-958)
+        const float av = fabsf(acc);
+        float amax = av == av ? av : 0.0f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float a = fabsf(acc[j]);
-            amax = fmaxf(amax, a == a ? a : 0.0f);
-        }
-        const unsigned grp = 0xFFu << (lane & 24);
+        for (int sft = 16; sft > 0; sft >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sft));
+        const float dd = __fdiv_rn(amax, 127.0f);
+        const float r = __fdiv_rn(1.0f, dd);
+        const float id = (dd != 0.0f && isfinite(r)) ? r : 0.0f;
+        const float pq = rintf(__fmul_rn(acc, id));
+        const int qv = pq != pq ? 0 : (int)fminf(fmaxf(pq, -128.0f), 127.0f);
+        int s16 = qv;  // sums of the two 16-element halves
 #pragma unroll
-        for (int sft = 4; sft > 0; sft >>= 1) amax = fmaxf(amax, __shfl_xor_sync(grp, amax, sft));
-        const float d = __fdiv_rn(amax, 127.0f);
-        const float r = __fdiv_rn(1.0f, d);
-        const float id = (d != 0.0f && isfinite(r)) ? r : 0.0f;
-        int qv[4], s4 = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float pq = rintf(__fmul_rn(acc[j], id));
-            qv[j] = pq != pq ? 0 : (int)fminf(fmaxf(pq, -128.0f), 127.0f);
-            s4 += qv[j];
-        }
-        s4 += __shfl_xor_sync(grp, s4, 1);
-        s4 += __shfl_xor_sync(grp, s4, 2);
-        const uint32_t packed = (uint32_t)(uint8_t)qv[0] | ((uint32_t)(uint8_t)qv[1] << 8) | ((uint32_t)(uint8_t)qv[2] << 16) |
-                                ((uint32_t)(uint8_t)qv[3] << 24);
-        const float sc = __half2float(__float2half_rn(d));
-        uint32_t *qw = reinterpret_cast<uint32_t *>(quants + o);
-        *qw = packed;
-        if (dq == 0) scales[o / 32] = sc;
-        if ((dq & 3) == 0) sums[o / 16] = (int16_t)s4;
+        for (int sft = 8; sft > 0; sft >>= 1) s16 += __shfl_xor_sync(0xffffffffu, s16, sft);
+        const float sc = __half2float(__float2half_rn(dd));
+        quants[o] = (int8_t)qv;
+        if (d == 0) scales[o / 32] = sc;
+        if ((d & 15) == 0) sums[o / 16] = (int16_t)s16;
         if (tp.push) {
-            tp_push(tp.ctx, qw, packed);
-            if (dq == 0) tp_push(tp.ctx, scales + o / 32, sc);
-            if ((dq & 3) == 0) tp_push(tp.ctx, sums + o / 16, (int16_t)s4);
+            // peers receive whole 32-bit words: lanes 0, 4, 8, ... gather their four quants
+            uint32_t packed = (uint32_t)(uint8_t)qv;
+            packed |= (uint32_t)(uint8_t)__shfl_down_sync(0xffffffffu, qv, 1) << 8;
+            packed |= (uint32_t)(uint8_t)__shfl_down_sync(0xffffffffu, qv, 2) << 16;
+            packed |= (uint32_t)(uint8_t)__shfl_down_sync(0xffffffffu, qv, 3) << 24;
+            if ((d & 3) == 0) tp_push(tp.ctx, reinterpret_cast<uint32_t *>(quants + o), packed);
+            if (d == 0) tp_push(tp.ctx, scales + o / 32, sc);
+            if ((d & 15) == 0) tp_push(tp.ctx, sums + o / 16, (int16_t)s16);
         }
     }
 }
@@ -354,7 +338,9 @@ int32_t launch_decode_attention_exact(const float *q, const void *kc, const void
     if (hd == 128) CERA_CUDA_TRY(launch_k(attn_scores_exact_kernel<128>, sgrid, sblock, sq, st, q, kc, kv_f16, sl32, seq_len_dev, nkv, G, hd, scale, ws, ld));
     else if (hd == 64) CERA_CUDA_TRY(launch_k(attn_scores_exact_kernel<64>, sgrid, sblock, sq, st, q, kc, kv_f16, sl32, seq_len_dev, nkv, G, hd, scale, ws, ld));
     else CERA_CUDA_TRY(launch_k(attn_scores_exact_kernel<0>, sgrid, sblock, sq, st, q, kc, kv_f16, sl32, seq_len_dev, nkv, G, hd, scale, ws, ld));
-    const uint32_t smem_pos = b >= 5 ? 0u : (uint32_t)reach;
+    constexpr size_t AX_SMEM_MAX = 226 * 1024;  // dynamic shared memory the values kernel may ask for
+    uint32_t smem_pos = b >= 5 ? 0u : (uint32_t)reach;
+    if (((size_t)AX_VSTAGES * AX_VT * 32 + ((size_t)smem_pos + 4) * G) * sizeof(float) > AX_SMEM_MAX) smem_pos = 0;  // probabilities through global memory
     const size_t smem = ((size_t)AX_VSTAGES * AX_VT * 32 + ((size_t)smem_pos + 4) * G) * sizeof(float);
     {
         // static + dynamic shared memory can pass the 48 KB default even at the shortest contexts: opt in once per device
@@ -362,8 +348,7 @@ int32_t launch_decode_attention_exact(const float *q, const void *kc, const void
         int dev = 0;
         cudaGetDevice(&dev);
         if (raised_dev != dev) {
-            CERA_CUDA_TRY(cudaFuncSetAttribute(attn_values_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)((AX_VSTAGES * AX_VT * 32 + (AX_SMEM_POS + 4) * 8) * sizeof(float))));
+            CERA_CUDA_TRY(cudaFuncSetAttribute(attn_values_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AX_SMEM_MAX));
             raised_dev = dev;
         }
     }

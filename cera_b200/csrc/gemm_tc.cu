@@ -44,10 +44,11 @@ constexpr int TC_STAGES = 3;
 constexpr int TC_EPI_WARPS = 16;                // four warpgroups: each covers the 128 token lanes for 32 weight rows
 constexpr int TC_THREADS = (9 + TC_EPI_WARPS) * 32;
 constexpr uint32_t TC_OP_BYTES = TC_BM * TC_KS * 2;                      // one operand tile of a stage: 32 KB
-constexpr uint32_t TC_TAB_BYTES = 4 * TC_BN * 4 + TC_BN * 4;             // mneg[4][128] + dval[128]
-constexpr uint32_t TC_STAGE_BYTES = 2 * TC_OP_BYTES + TC_TAB_BYTES;      // 68 096
+constexpr uint32_t TC_TAB_BYTES = 4 * TC_BN * 4 + TC_BN * 4 + 2 * 4 * TC_BM * 4;  // mneg[4][128], dval[128]; xsv[4][128], xbv[4][128]
+constexpr uint32_t TC_STAGE_BYTES = 2 * TC_OP_BYTES + TC_TAB_BYTES;      // 72 192
 constexpr uint32_t TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 256;     // + barriers, TMEM address, abort flag
-constexpr uint32_t TC_TMEM_COLS = 512;                                   // D0 [0,128) D1 [128,256) OUT [256,384)
+constexpr uint32_t TC_TMEM_COLS = 512;                                   // D0 [0,128) D1 [128,256) D2 [256,384) OUT [384,512)
+constexpr uint32_t TC_DBUFS = 3;
 constexpr uint32_t TC_KC_STRIDE = TC_BM * 16;                            // bytes between 8-element k chunks: 2048
 
 struct TcParams {
@@ -109,7 +110,7 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr, uint32_t lbo, 
            (1ull << 46);
 }
 // Instruction descriptor: f16 x f16 -> f32, both operands K-major, M x N.
-constexpr uint32_t tc_idesc(uint32_t M, uint32_t N) { return (1u << 4) | ((N >> 3) << 17) | ((M >> 4) << 24); }
+__host__ __device__ constexpr uint32_t tc_idesc(uint32_t M, uint32_t N) { return (1u << 4) | ((N >> 3) << 17) | ((M >> 4) << 24); }
 
 // Eight f16 values of a k chunk for row `r`: offset of the 16-byte slot in an operand tile.
 __device__ __forceinline__ uint32_t op_off(uint32_t kc, uint32_t r) { return kc * TC_KC_STRIDE + r * 16; }
@@ -125,8 +126,8 @@ template <int T>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p) {
     extern __shared__ __align__(1024) uint8_t tc_smem[];
     uint64_t *bars = reinterpret_cast<uint64_t *>(tc_smem + TC_STAGES * TC_STAGE_BYTES);
-    uint64_t *full_ab = bars, *empty_ab = bars + TC_STAGES, *full_d = bars + 2 * TC_STAGES, *empty_d = full_d + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC_STAGES + 4);
+    uint64_t *full_ab = bars, *empty_ab = bars + TC_STAGES, *full_d = bars + 2 * TC_STAGES, *empty_d = full_d + TC_DBUFS;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC_STAGES + 2 * TC_DBUFS);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t col0 = blockIdx.x * TC_BM, row0 = blockIdx.y * TC_BN;
@@ -137,7 +138,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
             tma::mbar_init(full_ab + s, 256);                 // every producer thread
             tma::mbar_init(empty_ab + s, 1 + TC_EPI_WARPS);   // the MMAs' commit + each epilogue warp (it reads the stage's tables)
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < (int)TC_DBUFS; ++b) {
             tma::mbar_init(full_d + b, 1);
             tma::mbar_init(empty_d + b, TC_EPI_WARPS);
         }
@@ -162,12 +163,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
             bool ok = true;
             for (uint32_t it = 0; it < n_it && ok; ++it) {
                 const uint32_t s = it % TC_STAGES;
-                if (!tma::mbar_wait(full_ab + s, (it / TC_STAGES) & 1, abort_flag, &g_tc_status, 1u)) break;
+                if (!tma::mbar_wait_blocking(full_ab + s, (it / TC_STAGES) & 1, abort_flag, &g_tc_status, 1u)) break;
                 tc_fence_after();
                 const uint32_t a_base = tma::smem_u32(tc_smem + s * TC_STAGE_BYTES), b_base = a_base + TC_OP_BYTES;
                 for (uint32_t b = 0; b < 4; ++b) {
-                    const uint32_t gb = it * 4 + b, buf = gb & 1;
-                    if (!tma::mbar_wait(empty_d + buf, ((gb >> 1) & 1) ^ 1, abort_flag, &g_tc_status, 2u)) {
+                    const uint32_t gb = it * 4 + b, buf = gb % TC_DBUFS;
+                    if (!tma::mbar_wait_blocking(empty_d + buf, ((gb / TC_DBUFS) & 1) ^ 1, abort_flag, &g_tc_status, 2u)) {
                         ok = false;
                         break;
                     }
@@ -187,20 +188,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
         // ---------------------------------------------------------------- weight operand: thread = weight row
         const uint32_t r = tid - 32;
         const uint32_t row = min(row0 + r, p.m - 1);  // rows past the edge repeat the last one; their results are not stored
+        // the raw bytes of an iteration are fetched one iteration ahead of their conversion (global latency ~ one conversion)
+        struct RawW {
+            uint4 piece[4], h, hb0, hb1;
+        };
+        auto fetch = [&](uint32_t it) {
+            RawW r;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) r.piece[c] = ld_stream(q_piece_ptr(p.w, row, 4, it * 4 + c));
+            const size_t sbi = sb_index(p.w, row, it >> 1);
+            r.h = __ldg(reinterpret_cast<const uint4 *>(p.w.hdr) + sbi);
+            r.hb0 = make_uint4(0, 0, 0, 0);
+            r.hb1 = r.hb0;
+            if (T == CERA_TYPE_Q5_K) {
+                r.hb0 = __ldg(reinterpret_cast<const uint4 *>(p.w.qh + sbi * 32));
+                r.hb1 = __ldg(reinterpret_cast<const uint4 *>(p.w.qh + sbi * 32 + 16));
+            }
+            return r;
+        };
+        RawW nxt = fetch(0);
         for (uint32_t it = 0; it < n_it; ++it) {
             const uint32_t s = it % TC_STAGES;
-            // global loads first (they do not depend on the stage being free)
-            uint4 piece[4];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) piece[c] = ld_stream(q_piece_ptr(p.w, row, 4, it * 4 + c));
-            const size_t sbi = sb_index(p.w, row, it >> 1);
-            const uint4 h = __ldg(reinterpret_cast<const uint4 *>(p.w.hdr) + sbi);
-            uint4 hb0 = make_uint4(0, 0, 0, 0), hb1 = hb0;
-            if (T == CERA_TYPE_Q5_K) {
-                hb0 = __ldg(reinterpret_cast<const uint4 *>(p.w.qh + sbi * 32));
-                hb1 = __ldg(reinterpret_cast<const uint4 *>(p.w.qh + sbi * 32 + 16));
-            }
-            if (!tma::mbar_wait(empty_ab + s, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 4u)) break;
+            const RawW cur = nxt;
+            if (it + 1 < n_it) nxt = fetch(it + 1);
+            const uint4 (&piece)[4] = cur.piece;
+            const uint4 h = cur.h, hb0 = cur.hb0, hb1 = cur.hb1;
+            if (!tma::mbar_wait_blocking(empty_ab + s, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 4u)) break;
             uint8_t *stage = tc_smem + s * TC_STAGE_BYTES;
             uint8_t *opb = stage + TC_OP_BYTES;
             float *mneg = reinterpret_cast<float *>(stage + 2 * TC_OP_BYTES), *dval = mneg + 4 * TC_BN;
@@ -255,12 +268,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
         const uint32_t token = min(col0 + c, p.n - 1);
         const int8_t *src = p.x.quants + (size_t)token * p.k;
         const __half2 bias = __float2half2_rn(1152.0f);  // 1024 + 128
+        const uint32_t nb32 = p.k >> 5, nb16 = p.k >> 4;
+        struct RawX {
+            uint4 v[8];
+            float4 xs;  // the four block scales of the stage
+            uint4 sm;   // the eight 16-element sums
+        };
+        auto fetch = [&](uint32_t it) {
+            RawX r;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) r.v[j] = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)it * TC_KS) + j);
+            r.xs = __ldg(reinterpret_cast<const float4 *>(p.x.scales + (size_t)token * nb32 + it * 4));
+            r.sm = __ldg(reinterpret_cast<const uint4 *>(p.x.sums + (size_t)token * nb16 + it * 8));
+            return r;
+        };
+        RawX nxt = fetch(0);
         for (uint32_t it = 0; it < n_it; ++it) {
             const uint32_t s = it % TC_STAGES;
-            uint4 raw[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) raw[j] = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)it * TC_KS) + j);
-            if (!tma::mbar_wait(empty_ab + s, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) break;
+            const RawX cur = nxt;
+            if (it + 1 < n_it) nxt = fetch(it + 1);
+            const uint4 (&raw)[8] = cur.v;
+            if (!tma::mbar_wait_blocking(empty_ab + s, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) break;
             uint8_t *opa = tc_smem + s * TC_STAGE_BYTES;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {  // 16 quants -> k chunks 2j, 2j+1
@@ -276,6 +304,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
                 *reinterpret_cast<uint4 *>(opa + op_off(2 * j, c)) = *reinterpret_cast<const uint4 *>(&o[0]);
                 *reinterpret_cast<uint4 *>(opa + op_off(2 * j + 1, c)) = *reinterpret_cast<const uint4 *>(&o[4]);
             }
+            {
+                // per-token scalars of the stage's four blocks, for the epilogue: the block scale and scale x (sum of the quants)
+                float *xsv = reinterpret_cast<float *>(opa + 2 * TC_OP_BYTES) + 5 * TC_BN, *xbv = xsv + 4 * TC_BM;
+                const float xv[4] = {cur.xs.x, cur.xs.y, cur.xs.z, cur.xs.w};
+                const uint32_t sw[4] = {cur.sm.x, cur.sm.y, cur.sm.z, cur.sm.w};
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    xsv[b * TC_BM + c] = xv[b];
+                    xbv[b * TC_BM + c] = xv[b] * (float)((int)(int16_t)(sw[b] & 0xFFFF) + (int)(int16_t)(sw[b] >> 16));
+                }
+            }
             fence_async_smem();
             tma::mbar_arrive(full_ab + s);
         }
@@ -285,26 +324,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
         const uint32_t tl = quad * 32 + lane;                       // token lane
         const uint32_t token = min(col0 + tl, p.n - 1);
         const uint32_t lane_addr = tmem + ((quad * 32) << 16);
-        const uint32_t nb32 = p.k >> 5, nb16 = p.k >> 4;
         float pacc[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) pacc[i] = 0.0f;
         bool ok = true;
         for (uint32_t it = 0; it < n_it && ok; ++it) {
             const uint32_t s = it % TC_STAGES;
-            const float4 xs4 = __ldg(reinterpret_cast<const float4 *>(p.x.scales + (size_t)token * nb32 + it * 4));
-            const uint4 sm4 = __ldg(reinterpret_cast<const uint4 *>(p.x.sums + (size_t)token * nb16 + it * 8));
-            const float xsv[4] = {xs4.x, xs4.y, xs4.z, xs4.w};
-            const uint32_t smw[4] = {sm4.x, sm4.y, sm4.z, sm4.w};
             const float *mneg = reinterpret_cast<const float *>(tc_smem + s * TC_STAGE_BYTES + 2 * TC_OP_BYTES);
-            const float *dval = mneg + 4 * TC_BN;
+            const float *dval = mneg + 4 * TC_BN, *xsv = dval + TC_BN, *xbv = xsv + 4 * TC_BM;
             // the producers' release of this stage, observed directly: the row-side tables are read with plain loads
-            if (!tma::mbar_wait(full_ab + s, (it / TC_STAGES) & 1, abort_flag, &g_tc_status, 32u)) break;
+            if (!tma::mbar_wait_blocking(full_ab + s, (it / TC_STAGES) & 1, abort_flag, &g_tc_status, 32u)) break;
             for (uint32_t b = 0; b < 4; ++b) {
-                const uint32_t gb = it * 4 + b, buf = gb & 1;
-                const float xs = xsv[b];
-                const float xb = xs * (float)((int)(int16_t)(smw[b] & 0xFFFF) + (int)(int16_t)(smw[b] >> 16));
-                if (!tma::mbar_wait(full_d + buf, (gb >> 1) & 1, abort_flag, &g_tc_status, 16u)) {
+                const uint32_t gb = it * 4 + b, buf = gb % TC_DBUFS;
+                const float xs = xsv[b * TC_BM + tl], xb = xbv[b * TC_BM + tl];
+                if (!tma::mbar_wait_blocking(full_d + buf, (gb / TC_DBUFS) & 1, abort_flag, &g_tc_status, 16u)) {
                     ok = false;
                     break;
                 }
@@ -331,7 +364,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
 #pragma unroll
                 for (int c4 = 0; c4 < 2; ++c4) {
                     uint32_t oreg[16];
-                    const uint32_t addr = lane_addr + 2 * TC_BN + ch * 32 + c4 * 16;
+                    const uint32_t addr = lane_addr + TC_DBUFS * TC_BN + ch * 32 + c4 * 16;
                     if (it > 1) {
                         tmem_ld16(addr, oreg);
                         tmem_wait_ld();
@@ -360,7 +393,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
 #pragma unroll
             for (int c4 = 0; c4 < 2; ++c4) {
                 uint32_t oreg[16];
-                tmem_ld16(lane_addr + 2 * TC_BN + ch * 32 + c4 * 16, oreg);
+                tmem_ld16(lane_addr + TC_DBUFS * TC_BN + ch * 32 + c4 * 16, oreg);
                 tmem_wait_ld();
                 if (tok_ok) {
 #pragma unroll

@@ -177,6 +177,11 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
     if (tp) CERA_TRY(launch_tp_tick(m->tp_words, st));
     CERA_TRY(launch_embed(m->embd->v, 0, m->dyn, m->hidden, st));
     const bool norm_rope = c.rope_type == 0;
+    // CERA_CUDA_FUSE_NORM=1: RMSNorm runs as the prologue of the GEMV that consumes it (reference-order kernels, one GPU,
+    // no LoRA reading the normalised vector).  Off by default: it saves 65 launches per token but puts the norm on the
+    // critical path of every CTA of the GEMV, and measured 4 % slower per token than the stand-alone kernel.
+    static const bool fuse_norm_env = [] { const char *e = getenv("CERA_CUDA_FUSE_NORM"); return e && e[0] == '1'; }();
+    const bool fuse_norm = fuse_norm_env && !tp && !m->has_lora && hs % 1024 == 0;
     if (norm_rope) CERA_TRY(launch_rope_table(m->dyn + 1, c.head_dim, m->theta_scale, m->rope_freqs, m->rope_cs, st, m->rope_table));
     for (uint32_t li = 0; li < n_layers; ++li) {
         Layer &L = m->layers[li];
@@ -192,9 +197,14 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
             return launch_lora(x, t.a, t.b, t.rank, t.k, t.d, t.scale, y, st);
         };
         const bool lora_qkv = L.lora[0].rank || L.lora[1].rank || L.lora[2].rank;
-        CERA_TRY(launch_rmsnorm(m->hidden, L.attn_norm, hs, 1, c.rms_norm_eps, normed_f32, m->act_hs.scales,
-                                m->act_hs.quants, m->act_hs.sums, st, &h_norm1));
         bool fused_qkv = false;
+        bool normed = false;  // act_hs holds the normalised, quantized hidden state
+        auto norm1 = [&]() -> int32_t {
+            if (normed) return CERA_CUDA_OK;
+            normed = true;
+            return launch_rmsnorm(m->hidden, L.attn_norm, hs, 1, c.rms_norm_eps, normed_f32, m->act_hs.scales, m->act_hs.quants,
+                                  m->act_hs.sums, st, &h_norm1);
+        };
         if (!lora_qkv && norm_rope && L.wq->v.type == L.wk->v.type && L.wq->v.type == L.wv->v.type) {
             // q/k/v GEMV with RoPE and the KV-cache append as its epilogue
             GemvSeg segs[3] = {{L.wq->v, m->q}, {L.wk->v, m->k}, {L.wv->v, m->v}};
@@ -206,9 +216,20 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
             f.kv_f16 = c.kv_f16;
             f.head_dim = c.head_dim;
             f.kv_dim = (uint32_t)m->l_kvd;
-            CERA_TRY(launch_gemv_exact(segs, 3, m->act_hs.view(), EPI_ROPE_KV, &f, st, &fused_qkv));
+            if (fuse_norm) {  // RMSNorm as the GEMV's prologue
+                f.norm_x = m->hidden;
+                f.norm_w = L.attn_norm;
+                f.norm_eps = c.rms_norm_eps;
+                CERA_TRY(launch_gemv_exact(segs, 3, m->act_hs.view(), EPI_ROPE_KV, &f, st, &fused_qkv));
+                f.norm_x = nullptr;
+            }
+            if (!fused_qkv) {
+                CERA_TRY(norm1());
+                CERA_TRY(launch_gemv_exact(segs, 3, m->act_hs.view(), EPI_ROPE_KV, &f, st, &fused_qkv));
+            }
             if (!fused_qkv) CERA_TRY(launch_gemv_fused(segs, 3, m->act_hs.view(), EPI_ROPE_KV, &f, st, &fused_qkv));
         }
+        if (!fused_qkv) CERA_TRY(norm1());
         if (fused_qkv) {
         } else if (L.wq->v.type == L.wk->v.type && L.wq->v.type == L.wv->v.type) {
             GemvSeg segs[3] = {{L.wq->v, m->q}, {L.wk->v, m->k}, {L.wv->v, m->v}};
@@ -234,9 +255,20 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
         GemvSeg so{L.wo->v, hidden_slice};
         CERA_TRY(launch_gemv(&so, 1, m->act_q.view(), 1, 1, EPI_ADD, st, 1, false, &h_wo));
         CERA_TRY(lora(3, m->attn, m->hidden));  // o-proj output lives in the residual stream already
-        CERA_TRY(launch_rmsnorm(m->hidden, L.ffn_norm, hs, 1, c.rms_norm_eps, normed_f32, m->act_hs.scales,
-                                m->act_hs.quants, m->act_hs.sums, st, &h_norm2));
-        if (L.gate->v.type == L.up->v.type) {
+        bool fused_ffn = false;
+        if (fuse_norm && L.gate->v.type == L.up->v.type) {
+            GemvSeg segs[2] = {{L.gate->v, m->g}, {L.up->v, m->u}};
+            GemvFusion f;
+            f.norm_x = m->hidden;
+            f.norm_w = L.ffn_norm;
+            f.norm_eps = c.rms_norm_eps;
+            CERA_TRY(launch_gemv_exact(segs, 2, m->act_hs.view(), EPI_STORE, &f, st, &fused_ffn));
+        }
+        if (!fused_ffn)
+            CERA_TRY(launch_rmsnorm(m->hidden, L.ffn_norm, hs, 1, c.rms_norm_eps, normed_f32, m->act_hs.scales,
+                                    m->act_hs.quants, m->act_hs.sums, st, &h_norm2));
+        if (fused_ffn) {
+        } else if (L.gate->v.type == L.up->v.type) {
             GemvSeg segs[2] = {{L.gate->v, m->g}, {L.up->v, m->u}};
             CERA_TRY(launch_gemv(segs, 2, m->act_hs.view(), 1, 1, EPI_STORE, st));
         } else {
@@ -260,12 +292,23 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
         return CERA_CUDA_OK;
     }
     const TpHook h_final = hook(s_last, false);
-    CERA_TRY(launch_rmsnorm(m->hidden, m->out_norm, hs, 1, c.rms_norm_eps, m->final_hidden, m->act_hs.scales,
-                            m->act_hs.quants, m->act_hs.sums, st, &h_final));
     const cera_cuda_weight *ow = m->output ? m->output : m->embd_head;
     float *logits_slice = m->logits + r * m->l_vocab;
     GemvSeg sl{ow->v, logits_slice};
-    CERA_TRY(launch_gemv(&sl, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
+    bool fused_head = false;
+    if (fuse_norm) {
+        GemvFusion f;
+        f.norm_x = m->hidden;
+        f.norm_w = m->out_norm;
+        f.norm_eps = c.rms_norm_eps;
+        f.norm_out = m->final_hidden;
+        CERA_TRY(launch_gemv_exact(&sl, 1, m->act_hs.view(), EPI_STORE, &f, st, &fused_head));
+    }
+    if (!fused_head) {
+        CERA_TRY(launch_rmsnorm(m->hidden, m->out_norm, hs, 1, c.rms_norm_eps, m->final_hidden, m->act_hs.scales,
+                                m->act_hs.quants, m->act_hs.sums, st, &h_final));
+        CERA_TRY(launch_gemv(&sl, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
+    }
     if (kind == G_LOGITS && tp) {
         const TpRange rg{(uint32_t)((const char *)logits_slice - m->region), (uint32_t)(m->l_vocab * 4)};
         CERA_TRY(launch_tp_exchange(m->tp, &rg, 1, s_logits, st));

@@ -36,6 +36,12 @@ struct GemvFusion {
     void *k_cache = nullptr, *v_cache = nullptr;
     int kv_f16 = 0;
     uint32_t head_dim = 0, kv_dim = 0;
+    // RMSNorm prologue (reference-order GEMV only): the activation column is formed in the kernel from the f32 vector
+    // norm_x and the norm weights - normalise, scale, quantize to Q8_0 - instead of being read from `x`;
+    // norm_out (optional) receives the normalised f32 vector
+    const float *norm_x = nullptr, *norm_w = nullptr;
+    float norm_eps = 0.0f;
+    float *norm_out = nullptr;
 };
 // tp (optional): wait for the exchange that completes x before reading it and / or mirror the output stores
 // (EPI_STORE / EPI_ADD, single column) into the peers' regions.
