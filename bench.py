@@ -53,6 +53,14 @@ HEAD_WEIGHT_BYTES = 128256 * Q6K_ROW_4096
 TOKEN_WEIGHT_BYTES = 32 * LAYER_WEIGHT_BYTES + HEAD_WEIGHT_BYTES  # 4 841 250 816
 
 
+OUT = sys.stdout
+
+
+def emit(line):
+    OUT.write(line + "\n")
+    OUT.flush()
+
+
 def gemv_bytes(m, k, block, block_bytes, n=1):
     return m * (k // block) * block_bytes + n * (k // 32 * 4 + k) + 4 * m * n
 
@@ -180,7 +188,7 @@ def reference_arm(args, rank):
     sample = (f"{args.steps} whole greedy decode tokens of the full 32-layer model (all seven GEMVs per layer, attention, norms, RoPE, "
               f"SiLU*mul, LM head, argmax) after a {CPU_CONTEXT}-token prompt, oracle restatement of cera's x86 int8 tier "
               f"'{r['tier']}', {threads} threads; other tiers: " + ", ".join(f"{k} {x:.2f} tok/s" for k, x in r["tiers"].items()))
-    print(json.dumps({
+    emit(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1000.0 / v, "higher_is_better": True,
         "scaling": "strong" if args.gpus > 1 else "weak",
@@ -541,7 +549,7 @@ def cuda_arm(args, rank, world):
                                              f"(all GEMVs, attention, norms, RoPE, SiLU*mul, LM head, argmax), oracle restatement of cera's "
                                              f"x86 int8 tier '{r['tier']}', all host threads",
                                    "tiers": r["tiers"], "one_thread_tok_s": r["one_thread_tok_s"], "model_build_s": round(r["build_s"], 1)}
-        print(json.dumps(out))
+        emit(json.dumps(out))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -564,12 +572,18 @@ def main():
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
+    # Libraries may write to stdout (NCCL prints its version line there): file descriptor 1 is pointed at stderr for the
+    # whole run, and the JSON lines go to the real stdout through this handle.
+    global OUT
+    sys.stdout.flush()
+    OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if args.only == "roofline":
         import torch
         import cera_b200 as cb
         algo, us, n = roofline_q4k_gemv(torch, cb, args.iters)
         hbm, which = measured_peaks()
-        print(json.dumps({"kernel": ROOFLINE_KERNEL, "us_per_launch": us,
+        emit(json.dumps({"kernel": ROOFLINE_KERNEL, "us_per_launch": us,
                           "achieved_gbs": algo / us / 1e3, "frac": algo / us / 1e3 / hbm, "peak_source": which,
                           "launches": n}))
     elif args.only == "gemv-sweep":
@@ -578,9 +592,9 @@ def main():
         hbm, which = measured_peaks()
         for tname, m, k in DECODE_SHAPES:
             algo, us, _ = gemv_microbench(torch, cb, tname, m, k, args.iters if m < 100000 else max(8, args.iters // 8))
-            print(json.dumps({"type": tname, "m": m, "k": k, "us": round(us, 3), "algorithmic_bytes": algo,
+            emit(json.dumps({"type": tname, "m": m, "k": k, "us": round(us, 3), "algorithmic_bytes": algo,
                               "gbs": round(algo / us / 1e3, 1), "frac_of_measured": round(algo / us / 1e3 / hbm, 4),
-                              "frac_of_8000": round(algo / us / 1e3 / 8000.0, 4)}), flush=True)
+                              "frac_of_8000": round(algo / us / 1e3 / 8000.0, 4)}))
     elif args.only == "attn-sweep":
         import torch
         import cera_b200 as cb
@@ -589,9 +603,9 @@ def main():
             for ctx in (512, 4096, 16384, 32768):
                 algo, us = attention_microbench(torch, cb, ctx, f16, args.iters)
                 gbs = algo / us / 1e3
-                print(json.dumps({"kernel": "flash-decode attention 32/8 heads x 128", "ctx": ctx, "kv_dtype": "f16" if f16 else "f32",
+                emit(json.dumps({"kernel": "flash-decode attention 32/8 heads x 128", "ctx": ctx, "kv_dtype": "f16" if f16 else "f32",
                                   "algorithmic_bytes": algo, "us": round(us, 2), "achieved_gbs": round(gbs, 1),
-                                  "frac": round(gbs / hbm, 3), "peak_source": which}), flush=True)
+                                  "frac": round(gbs / hbm, 3), "peak_source": which}))
     elif args.only == "moe" and world > 1:
         import torch
         import torch.distributed as dist
@@ -600,22 +614,22 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))))
         res = moe_ep_microbench(torch, cb, max(5, args.iters // 5), rank, world)
         if rank == 0:
-            print(json.dumps(res), flush=True)
+            emit(json.dumps(res))
         dist.barrier()
         dist.destroy_process_group()
     elif args.only == "moe":
         import torch
         import cera_b200 as cb
         for n in (1, 64, 512):
-            print(json.dumps(moe_microbench(torch, cb, max(5, args.iters // 5), n_tokens=n)), flush=True)
-        print(json.dumps(moe_microbench(torch, cb, max(5, args.iters // 5), softmax_gate=True)), flush=True)
+            emit(json.dumps(moe_microbench(torch, cb, max(5, args.iters // 5), n_tokens=n)))
+        emit(json.dumps(moe_microbench(torch, cb, max(5, args.iters // 5), softmax_gate=True)))
     elif args.only == "gemm-sweep":
         import torch
         import cera_b200 as cb
         for tname, m, k in [("q4_k", 4096, 4096), ("q4_k", 14336, 4096), ("q6_k", 4096, 14336), ("q5_k", 4096, 4096)]:
             for n in (8, 64, 256, 512):
                 ops, us = gemm_microbench(torch, cb, tname, m, k, n, max(3, args.iters // (4 if n > 64 else 1)))
-                print(json.dumps({"type": tname, "m": m, "k": k, "n": n, "us": round(us, 2),
+                emit(json.dumps({"type": tname, "m": m, "k": k, "n": n, "us": round(us, 2),
                                   "tops": round(ops / us / 1e6, 2), "frac_of_int8_nominal_4500": round(ops / us / 1e6 / 4500, 4)}),
                       flush=True)
     elif args.impl == "reference":

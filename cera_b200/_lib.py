@@ -26,7 +26,8 @@ class Config(C.Structure):
     _fields_ = [("n_layers", _u32), ("hidden_size", _u32), ("intermediate_size", _u32), ("n_heads", _u32),
                 ("n_kv_heads", _u32), ("head_dim", _u32), ("vocab_size", _u32), ("max_seq_len", _u32),
                 ("rope_theta", _f), ("rms_norm_eps", _f), ("rope_type", _i32), ("kv_f16", _i32), ("device", _i32),
-                ("reserved", _i32)]
+                ("reserved", _i32), ("embedding_scale", _f), ("residual_scale", _f), ("attention_scale", _f),
+                ("logit_scale", _f)]
 
 
 # name -> (restype, argtypes); every symbol include/cera_cuda.h declares.
@@ -78,6 +79,9 @@ SIGNATURES = {
     "cera_cuda_kv_snapshot_bytes": (_sz, [_p]),
     "cera_cuda_kv_snapshot": (_i32, [_p, _p, _sz]),
     "cera_cuda_kv_restore": (_i32, [_p, _p, _sz]),
+    "cera_cuda_kv_layer_bytes": (_sz, [_p]),
+    "cera_cuda_kv_snapshot_layer": (_i32, [_p, _u32, _p, _p, _sz]),
+    "cera_cuda_kv_restore_layer": (_i32, [_p, _u32, _p, _p, _sz, _sz]),
     "cera_cuda_moe_create": (_i32, [_u32, _u32, _u32, _u32, _i32, _p, _p, _p, _sz, _sz, _p, _p, _sz, C.POINTER(_p)]),
     "cera_cuda_moe_create_ep": (_i32, [_u32, _u32, _u32, _u32, _i32, _p, _p, _p, _sz, _sz, _p, _p, _sz, _u32, _u32, _sz,
                                        C.POINTER(_p)]),

@@ -31,7 +31,7 @@ namespace {
 constexpr int ATT_WARPS = 8;
 constexpr int MAX_SPLITS = 64;
 constexpr uint32_t ATT_CLUSTER_FLAG = 0x80;
-constexpr uint32_t ATT_STREAM_FLAG = 0x100;  // long contexts: the TMA-staged split kernel, low bits = splits
+constexpr uint32_t ATT_STREAM_FLAG = 0x100;  // long contexts: the split kernel that stages K/V through shared memory with cp.async, low bits = splits
 constexpr size_t ATT_CLUSTER_MAX_SEQ = 4096;
 
 template <int VEC, bool F16>

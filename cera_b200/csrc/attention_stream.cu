@@ -275,7 +275,7 @@ int32_t launch_stream_typed(dim3 grid, cudaStream_t st, const float *q, const vo
 
 }  // namespace
 
-// The split pass of a long-context decode attention through the TMA-staged kernel; the caller runs the merge
+// The split pass of a long-context decode attention through the cp.async-staged kernel; the caller runs the merge
 // pass over the same workspace.  *taken = false: shape without an instantiation (head_dim 64 / 128, group 4 / 8).
 int32_t launch_attention_stream(const float *q, const void *kc, const void *vc, int kv_f16, size_t n_kv_heads, size_t group,
                                 size_t head_dim, uint32_t seq_len, const uint32_t *seq_len_dev, uint32_t n_splits, float scale,

@@ -298,6 +298,33 @@ int32_t launch_embed_batch(const WeightView &w, const uint32_t *tokens_dev, size
 
 size_t argmax_scratch_words() { return 2 * ARGMAX_BLOCKS; }
 
+namespace {
+__global__ void scale_kernel(float *__restrict__ x, size_t n, float s) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] = __fmul_rn(x[i], s);
+}
+__global__ void scaled_add_kernel(float *__restrict__ y, const float *__restrict__ x, size_t n, float s) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        y[i] = __fadd_rn(y[i], __fmul_rn(x[i], s));
+}
+}  // namespace
+
+int32_t launch_scale(float *x, size_t n, float s, cudaStream_t st) {
+    if (n == 0) return CERA_CUDA_OK;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
+    count_launch();
+    return check_cuda(launch_k(scale_kernel, dim3(grid), dim3(256), 0, st, x, n, s), "scale launch");
+}
+int32_t launch_scaled_add(float *y, const float *x, size_t n, float s, cudaStream_t st) {
+    if (n == 0) return CERA_CUDA_OK;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
+    count_launch();
+    return check_cuda(launch_k(scaled_add_kernel, dim3(grid), dim3(256), 0, st, y, x, n, s), "scaled add launch");
+}
+
 int32_t launch_argmax(const float *x, size_t n, uint32_t *out, uint32_t *scratch, cudaStream_t st) {
     if (!x || !out || !scratch) return fail(CERA_CUDA_ERR_BAD_ARG, "argmax: null argument");
     count_launch(2);

@@ -154,7 +154,8 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
     const size_t hs = c.hidden_size;
     const uint32_t r = m->tp_rank;
     const bool tp = m->tp_size > 1;
-    const float scale = 1.0f / sqrtf((float)c.head_dim);
+    const float scale = c.attention_scale != 0.0f ? c.attention_scale : 1.0f / sqrtf((float)c.head_dim);
+    const float res_scale = c.residual_scale != 0.0f ? c.residual_scale : 1.0f;  // Granite: block outputs are scaled before the residual add
     // Exchange slots of layer l: 4l = Q8_0 attention output, 4l+1 = residual after o-proj, 4l+2 = Q8_0 SwiGLU
     // activations, 4l+3 = residual after down-proj; then 4L = logits, 4L+1 = greedy pairs.  The producing kernel
     // mirrors its stores into the peers' regions; the consuming kernel signals and waits in its prologue.
@@ -176,6 +177,7 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
 
     if (tp) CERA_TRY(launch_tp_tick(m->tp_words, st));
     CERA_TRY(launch_embed(m->embd->v, 0, m->dyn, m->hidden, st));
+    if (c.embedding_scale != 0.0f && c.embedding_scale != 1.0f) CERA_TRY(launch_scale(m->hidden, hs, c.embedding_scale, st));
     const bool norm_rope = c.rope_type == 0;
     // CERA_CUDA_FUSE_NORM=1: RMSNorm runs as the prologue of the GEMV that consumes it (reference-order kernels, one GPU,
     // no LoRA reading the normalised vector).  Off by default: it saves 65 launches per token but puts the norm on the
@@ -252,9 +254,16 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
         CERA_TRY(launch_decode_attention_ex(m->q, L.kc, L.vc, c.kv_f16, m->l_heads, m->l_kv_heads, c.head_dim, 0,
                                             m->dyn + 2, n_splits, scale, m->attn, m->attn_ws, m->attn_ws_bytes,
                                             aq.scales, aq.quants, aq.sums, st, &h_merge));
-        GemvSeg so{L.wo->v, hidden_slice};
-        CERA_TRY(launch_gemv(&so, 1, m->act_q.view(), 1, 1, EPI_ADD, st, 1, false, &h_wo));
-        CERA_TRY(lora(3, m->attn, m->hidden));  // o-proj output lives in the residual stream already
+        if (res_scale != 1.0f) {  // the block output on its own (g is free here), its LoRA delta, then hidden += out * s
+            GemvSeg so{L.wo->v, m->g};
+            CERA_TRY(launch_gemv(&so, 1, m->act_q.view(), 1, 1, EPI_STORE, st));
+            CERA_TRY(lora(3, m->attn, m->g));
+            CERA_TRY(launch_scaled_add(m->hidden, m->g, hs, res_scale, st));
+        } else {
+            GemvSeg so{L.wo->v, hidden_slice};
+            CERA_TRY(launch_gemv(&so, 1, m->act_q.view(), 1, 1, EPI_ADD, st, 1, false, &h_wo));
+            CERA_TRY(lora(3, m->attn, m->hidden));  // o-proj output lives in the residual stream already
+        }
         bool fused_ffn = false;
         if (fuse_norm && L.gate->v.type == L.up->v.type) {
             GemvSeg segs[2] = {{L.gate->v, m->g}, {L.up->v, m->u}};
@@ -280,9 +289,16 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
         CERA_TRY(lora(5, m->normed, m->u));
         const ActBuf af = act_slice(m->act_ff, m->l_ff);
         CERA_TRY(launch_silu_mul(m->g, m->u, m->l_ff, 1, af.scales, af.quants, af.sums, st, &h_silu));
-        GemvSeg sd{L.down->v, hidden_slice};
-        CERA_TRY(launch_gemv(&sd, 1, m->act_ff.view(), 1, 1, EPI_ADD, st, 1, false, &h_down));
-        CERA_TRY(lora(6, m->g, m->hidden));  // input: the SwiGLU product, left in g by the kernel above
+        if (res_scale != 1.0f) {  // u is free once the SwiGLU product is in g
+            GemvSeg sd{L.down->v, m->u};
+            CERA_TRY(launch_gemv(&sd, 1, m->act_ff.view(), 1, 1, EPI_STORE, st));
+            CERA_TRY(lora(6, m->g, m->u));
+            CERA_TRY(launch_scaled_add(m->hidden, m->u, hs, res_scale, st));
+        } else {
+            GemvSeg sd{L.down->v, hidden_slice};
+            CERA_TRY(launch_gemv(&sd, 1, m->act_ff.view(), 1, 1, EPI_ADD, st, 1, false, &h_down));
+            CERA_TRY(lora(6, m->g, m->hidden));  // input: the SwiGLU product, left in g by the kernel above
+        }
     }
     const uint32_t s_last = 4 * n_layers - 1, s_logits = 4 * n_layers, s_pick = 4 * n_layers + 1;
     if (kind == G_BODY) {
@@ -309,6 +325,7 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
                                 m->act_hs.quants, m->act_hs.sums, st, &h_final));
         CERA_TRY(launch_gemv(&sl, 1, m->act_hs.view(), 1, 1, EPI_STORE, st));
     }
+    if (c.logit_scale != 0.0f && c.logit_scale != 1.0f) CERA_TRY(launch_scale(logits_slice, m->l_vocab, 1.0f / c.logit_scale, st));
     if (kind == G_LOGITS && tp) {
         const TpRange rg{(uint32_t)((const char *)logits_slice - m->region), (uint32_t)(m->l_vocab * 4)};
         CERA_TRY(launch_tp_exchange(m->tp, &rg, 1, s_logits, st));
@@ -386,9 +403,11 @@ int32_t prefill_chunk(cera_cuda_model *m, const uint32_t *tokens, size_t n, size
     cudaStream_t st = m->stream;
     const size_t hs = c.hidden_size, qd = (size_t)c.n_heads * c.head_dim, kvd = (size_t)c.n_kv_heads * c.head_dim,
                  ff = c.intermediate_size;
-    const float scale = 1.0f / sqrtf((float)c.head_dim);
+    const float scale = c.attention_scale != 0.0f ? c.attention_scale : 1.0f / sqrtf((float)c.head_dim);
+    const float res_scale = c.residual_scale != 0.0f ? c.residual_scale : 1.0f;
     CERA_CUDA_TRY(cudaMemcpyAsync(m->pf_tokens, tokens, n * 4, cudaMemcpyHostToDevice, st));
     CERA_TRY(launch_embed_batch(m->embd->v, m->pf_tokens, n, m->pf_hidden, st));
+    if (c.embedding_scale != 0.0f && c.embedding_scale != 1.0f) CERA_TRY(launch_scale(m->pf_hidden, n * hs, c.embedding_scale, st));
     const uint64_t before = launches_so_far();
     for (auto &L : m->layers) {
         CERA_TRY(launch_rmsnorm(m->pf_hidden, L.attn_norm, hs, n, c.rms_norm_eps, nullptr, m->pf_act_hs.scales,
@@ -401,13 +420,23 @@ int32_t prefill_chunk(cera_cuda_model *m, const uint32_t *tokens, size_t n, size
         CERA_TRY(launch_prefill_attention(m->pf_q, L.kc, L.vc, c.kv_f16, c.n_heads, c.n_kv_heads, c.head_dim, n, start_pos,
                                           scale, m->pf_attn, st));
         CERA_TRY(launch_quantize(m->pf_attn, qd, n, false, m->pf_act_q.scales, m->pf_act_q.quants, m->pf_act_q.sums, st));
-        CERA_TRY(launch_gemm_ex(L.wo->v, m->pf_act_q.view(), n, m->pf_hidden, 1, hs, EPI_ADD, st));
+        if (res_scale != 1.0f) {  // block output into pf_g (free until the gate projection), then hidden += out * s
+            CERA_TRY(launch_gemm_ex(L.wo->v, m->pf_act_q.view(), n, m->pf_g, 1, hs, EPI_STORE, st));
+            CERA_TRY(launch_scaled_add(m->pf_hidden, m->pf_g, n * hs, res_scale, st));
+        } else {
+            CERA_TRY(launch_gemm_ex(L.wo->v, m->pf_act_q.view(), n, m->pf_hidden, 1, hs, EPI_ADD, st));
+        }
         CERA_TRY(launch_rmsnorm(m->pf_hidden, L.ffn_norm, hs, n, c.rms_norm_eps, nullptr, m->pf_act_hs.scales,
                                 m->pf_act_hs.quants, m->pf_act_hs.sums, st));
         CERA_TRY(launch_gemm_ex(L.gate->v, m->pf_act_hs.view(), n, m->pf_g, 1, ff, EPI_STORE, st));
         CERA_TRY(launch_gemm_ex(L.up->v, m->pf_act_hs.view(), n, m->pf_u, 1, ff, EPI_STORE, st));
         CERA_TRY(launch_silu_mul(m->pf_g, m->pf_u, ff, n, m->pf_act_ff.scales, m->pf_act_ff.quants, m->pf_act_ff.sums, st));
-        CERA_TRY(launch_gemm_ex(L.down->v, m->pf_act_ff.view(), n, m->pf_hidden, 1, hs, EPI_ADD, st));
+        if (res_scale != 1.0f) {  // pf_u is free once the SwiGLU product is quantized
+            CERA_TRY(launch_gemm_ex(L.down->v, m->pf_act_ff.view(), n, m->pf_u, 1, hs, EPI_STORE, st));
+            CERA_TRY(launch_scaled_add(m->pf_hidden, m->pf_u, n * hs, res_scale, st));
+        } else {
+            CERA_TRY(launch_gemm_ex(L.down->v, m->pf_act_ff.view(), n, m->pf_hidden, 1, hs, EPI_ADD, st));
+        }
     }
     CERA_CUDA_TRY(cudaMemcpyAsync(m->hidden, m->pf_hidden + (n - 1) * hs, hs * 4, cudaMemcpyDeviceToDevice, st));
     m->launches += launches_so_far() - before + 1;
@@ -422,7 +451,12 @@ int32_t logits_from_hidden(cera_cuda_model *m) {
     const cera_cuda_weight *ow = m->output ? m->output : m->embd;
     GemvSeg sl{ow->v, m->logits};
     m->launches += 2;
-    return launch_gemv(&sl, 1, m->act_hs.view(), 1, 1, EPI_STORE, m->stream);
+    CERA_TRY(launch_gemv(&sl, 1, m->act_hs.view(), 1, 1, EPI_STORE, m->stream));
+    if (c.logit_scale != 0.0f && c.logit_scale != 1.0f) {
+        m->launches += 1;
+        CERA_TRY(launch_scale(m->logits, c.vocab_size, 1.0f / c.logit_scale, m->stream));
+    }
+    return CERA_CUDA_OK;
 }
 
 void set_extents(cera_cuda_model *m) {
@@ -494,6 +528,8 @@ int32_t cera_cuda_model_set_tp(cera_cuda_model *m, uint32_t rank, uint32_t size)
             return fail(CERA_CUDA_ERR_STATE, "set_tp: must precede the first add_tensor");
     if (size == 0 || size > TP_MAX_RANKS || rank >= size)
         return fail(CERA_CUDA_ERR_BAD_ARG, "set_tp: rank %u of %u (at most %u ranks)", rank, size, TP_MAX_RANKS);
+    if (size > 1 && c.residual_scale != 0.0f && c.residual_scale != 1.0f)
+        return fail(CERA_CUDA_ERR_UNSUPPORTED, "set_tp: a residual scale (Granite) on a tensor-parallel model is not supported");
     if (c.n_kv_heads % size) return fail(CERA_CUDA_ERR_BAD_ARG, "set_tp: %u KV heads do not split over %u ranks", c.n_kv_heads, size);
     if (c.intermediate_size % (32 * size))
         return fail(CERA_CUDA_ERR_BAD_ARG, "set_tp: intermediate size %u must be a multiple of 32 x %u ranks", c.intermediate_size, size);
@@ -782,6 +818,7 @@ int32_t cera_cuda_forward_prefill_logits_all(cera_cuda_model *m, const uint32_t 
         CERA_TRY(launch_rmsnorm(m->pf_hidden, m->out_norm, c.hidden_size, cn, c.rms_norm_eps, nullptr, m->pf_act_hs.scales,
                                 m->pf_act_hs.quants, m->pf_act_hs.sums, m->stream));
         CERA_TRY(launch_gemm_ex(ow->v, m->pf_act_hs.view(), cn, m->pf_logits, 1, vocab, EPI_STORE, m->stream));
+        if (c.logit_scale != 0.0f && c.logit_scale != 1.0f) CERA_TRY(launch_scale(m->pf_logits, cn * vocab, 1.0f / c.logit_scale, m->stream));
         CERA_CUDA_TRY(cudaMemcpyAsync(logits_out + done * vocab, m->pf_logits, cn * vocab * 4, cudaMemcpyDeviceToHost, m->stream));
         CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
         m->seq_len = start_pos + done + cn;
@@ -857,7 +894,11 @@ int32_t cera_cuda_model_tp_connect(cera_cuda_model *m, const void *handles, size
         cudaIpcMemHandle_t h;
         memcpy(&h, (const char *)handles + (size_t)p * sizeof(h), sizeof(h));
         void *ptr = nullptr;
-        CERA_CUDA_TRY(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        const cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return fail(CERA_CUDA_ERR_PEER, "tp_connect: rank %u's exchange region cannot be mapped: %s", p, cudaGetErrorString(e));
+        }
         m->tp_opened[p] = ptr;
         m->tp.peer[p] = (char *)ptr;
     }
@@ -1011,6 +1052,43 @@ int32_t cera_cuda_kv_restore(cera_cuda_model *m, const void *data, size_t bytes)
         p += 2 * rows;
     }
     m->seq_len = (size_t)h.seq_len;
+    return CERA_CUDA_OK;
+}
+
+size_t cera_cuda_kv_layer_bytes(const cera_cuda_model *m) {
+    return m ? m->seq_len * m->l_kvd * (m->cfg.kv_f16 ? 2 : 4) : 0;
+}
+
+int32_t cera_cuda_kv_snapshot_layer(cera_cuda_model *m, uint32_t layer, void *k_data, void *v_data, size_t bytes_each) {
+    if (!m || !k_data || !v_data) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_snapshot_layer: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    if (!m->finalized) return fail(CERA_CUDA_ERR_STATE, "kv_snapshot_layer: model not finalized");
+    if (layer >= m->cfg.n_layers) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_snapshot_layer: layer %u of %u", layer, m->cfg.n_layers);
+    const size_t rows = m->seq_len * m->l_kvd * (m->cfg.kv_f16 ? 2 : 4);
+    if (bytes_each != rows) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_snapshot_layer: %zu bytes given, a layer holds %zu", bytes_each, rows);
+    CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    CERA_CUDA_TRY(cudaMemcpy(k_data, m->layers[layer].kc, rows, cudaMemcpyDeviceToHost));
+    return check_cuda(cudaMemcpy(v_data, m->layers[layer].vc, rows, cudaMemcpyDeviceToHost), "cudaMemcpy(kv_snapshot_layer)");
+}
+
+int32_t cera_cuda_kv_restore_layer(cera_cuda_model *m, uint32_t layer, const void *k_data, const void *v_data, size_t bytes_each,
+                                   size_t seq_len) {
+    if (!m || (bytes_each && (!k_data || !v_data))) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_restore_layer: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard dg(m->cfg.device);
+    if (!m->finalized) return fail(CERA_CUDA_ERR_STATE, "kv_restore_layer: model not finalized");
+    if (layer >= m->cfg.n_layers) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_restore_layer: layer %u of %u", layer, m->cfg.n_layers);
+    if (seq_len > m->cfg.max_seq_len) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_restore_layer: %zu positions exceed max_seq_len %u", seq_len, m->cfg.max_seq_len);
+    const size_t rows = seq_len * m->l_kvd * (m->cfg.kv_f16 ? 2 : 4);
+    // a snapshot taken with the other element width has half / twice the bytes: the reference's cross-mode gate (kv_cache.rs:1411-1421)
+    if (bytes_each != rows) return fail(CERA_CUDA_ERR_BAD_ARG, "kv_restore_layer: %zu bytes given, %zu positions of this cache are %zu", bytes_each, seq_len, rows);
+    CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    if (rows) {
+        CERA_CUDA_TRY(cudaMemcpy(m->layers[layer].kc, k_data, rows, cudaMemcpyHostToDevice));
+        CERA_CUDA_TRY(cudaMemcpy(m->layers[layer].vc, v_data, rows, cudaMemcpyHostToDevice));
+    }
+    m->seq_len = seq_len;
     return CERA_CUDA_OK;
 }
 

@@ -639,7 +639,11 @@ int32_t cera_cuda_moe_ep_connect(cera_cuda_moe *h, const void *handles, size_t n
         cudaIpcMemHandle_t ih;
         memcpy(&ih, (const char *)handles + (size_t)p * sizeof(ih), sizeof(ih));
         void *ptr = nullptr;
-        CERA_CUDA_TRY(cudaIpcOpenMemHandle(&ptr, ih, cudaIpcMemLazyEnablePeerAccess));
+        const cudaError_t e = cudaIpcOpenMemHandle(&ptr, ih, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return fail(CERA_CUDA_ERR_PEER, "moe_ep_connect: rank %u's receive region cannot be mapped: %s", p, cudaGetErrorString(e));
+        }
         h->opened[p] = ptr;
         h->ep.peer[p] = (char *)ptr;
     }

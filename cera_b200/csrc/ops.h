@@ -132,6 +132,9 @@ int32_t launch_decode_attention_ex(const float *q, const void *kc, const void *v
 
 int32_t launch_embed(const WeightView &w, uint32_t token, const uint32_t *token_dev, float *out, cudaStream_t st);
 // n rows: out[j][k] = row tokens_dev[j] of the table.
+// x[i] *= s, and y[i] += x[i] * s (product rounded, then the sum: cera/src/backend/cpu.rs scale_inplace + add_inplace)
+int32_t launch_scale(float *x, size_t n, float s, cudaStream_t st);
+int32_t launch_scaled_add(float *y, const float *x, size_t n, float s, cudaStream_t st);
 int32_t launch_embed_batch(const WeightView &w, const uint32_t *tokens_dev, size_t n, float *out, cudaStream_t st);
 // n tokens at positions start_pos + j: q is [n][n_heads*head_dim], k and v are [n][n_kv_heads*head_dim]
 // (token-major); rotated k and v rows are appended to the caches.

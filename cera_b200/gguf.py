@@ -191,7 +191,12 @@ def llama_config(g):
                 vocab_size=int(g.metadata.get(f"{arch}.vocab_size", rows)),
                 rope_theta=float(g.metadata.get(f"{arch}.rope.freq_base", 10000.0)),
                 rms_norm_eps=float(need("attention.layer_norm_rms_epsilon")),
-                rope_type=1 if arch in ("qwen2", "qwen3") else 0), int(g.metadata.get(f"{arch}.context_length", 4096))
+                rope_type=1 if arch in ("qwen2", "qwen3") else 0,
+                # Granite's scalar multipliers (cera/src/model/mod.rs:84-111): absent keys are identity (0 here)
+                embedding_scale=float(g.metadata.get(f"{arch}.embedding_scale", 0.0)),
+                residual_scale=float(g.metadata.get(f"{arch}.residual_scale", 0.0)),
+                attention_scale=float(g.metadata.get(f"{arch}.attention.scale", 0.0)),
+                logit_scale=float(g.metadata.get(f"{arch}.logit_scale", 0.0))), int(g.metadata.get(f"{arch}.context_length", 4096))
 
 
 _LAYER_TENSORS = [("attn_norm", Role.ATTN_NORM), ("attn_q", Role.ATTN_Q), ("attn_k", Role.ATTN_K), ("attn_v", Role.ATTN_V),

@@ -136,6 +136,23 @@ class CudaModel:
         snap = np.ascontiguousarray(snap, dtype=np.uint8)
         check(lib.cera_cuda_kv_restore(self.handle, snap.ctypes.data_as(C.c_void_p), snap.size))
 
+    def state_snapshot(self):
+        """The reference's StateSnapshot shape (cera/src/kv_cache.rs:1379-1421): {"seq_len", "layers": [(k_data, v_data)]},
+        raw little-endian rows in the cache's element type."""
+        n = lib.cera_cuda_kv_layer_bytes(self.handle)
+        layers = []
+        for l in range(self.cfg.n_layers):
+            k, v = np.empty(n, dtype=np.uint8), np.empty(n, dtype=np.uint8)
+            check(lib.cera_cuda_kv_snapshot_layer(self.handle, l, k.ctypes.data_as(C.c_void_p), v.ctypes.data_as(C.c_void_p), n))
+            layers.append((k, v))
+        return {"seq_len": self.seq_len, "layers": layers}
+
+    def restore_state(self, snap):
+        for l, (k, v) in enumerate(snap["layers"]):
+            k, v = np.ascontiguousarray(k, dtype=np.uint8), np.ascontiguousarray(v, dtype=np.uint8)
+            check(lib.cera_cuda_kv_restore_layer(self.handle, l, k.ctypes.data_as(C.c_void_p), v.ctypes.data_as(C.c_void_p), k.size,
+                                                 snap["seq_len"]))
+
     @property
     def seq_len(self):
         return lib.cera_cuda_seq_len(self.handle)

@@ -40,7 +40,8 @@ enum {
                                       a silent fallback (cera/src/model/transformer.rs:607-633) */
     CERA_CUDA_ERR_OOM = 3,
     CERA_CUDA_ERR_CUDA = 4, /* driver / runtime error, text in last_error */
-    CERA_CUDA_ERR_NCCL = 5,
+    CERA_CUDA_ERR_PEER = 5, /* peer-memory set-up between tensor- / expert-parallel ranks failed
+                               (IPC handle, peer access); the library makes no NCCL call */
     CERA_CUDA_ERR_TIMEOUT = 6, /* a bounded device-side wait ran out */
     CERA_CUDA_ERR_STATE = 7    /* call order violated (e.g. pos != seq_len) */
 };
@@ -215,6 +216,15 @@ typedef struct {
     int32_t kv_f16;    /* 0: f32 KV (the CPU default), 1: f16 KV (KvCompression::F16) */
     int32_t device;    /* CUDA ordinal */
     int32_t reserved;
+    /* ScalarMultipliers (Granite 3.x; cera/src/model/mod.rs:49-112).  0 = absent = identity, so a zeroed tail
+     * is every other architecture.  embedding: hidden *= s after the token lookup (llama.rs:1544-1546);
+     * residual: each attention / FFN block output *= s before its residual add (llama.rs:515-521, 543-549);
+     * attention: softmax scale that REPLACES 1/sqrt(head_dim) (llama.rs:462); logit: logits *= 1/s
+     * (llama.rs:591-594).  residual != 1 on a tensor-parallel model: CERA_CUDA_ERR_UNSUPPORTED. */
+    float embedding_scale;
+    float residual_scale;
+    float attention_scale;
+    float logit_scale;
 } cera_cuda_config;
 
 /* Tensor roles: the GGUF names a llama-architecture loader resolves
@@ -315,6 +325,16 @@ CERA_API int32_t cera_cuda_kv_shift(cera_cuda_model *m, size_t n_keep, size_t sh
 CERA_API size_t cera_cuda_kv_snapshot_bytes(const cera_cuda_model *m);
 CERA_API int32_t cera_cuda_kv_snapshot(cera_cuda_model *m, void *out, size_t out_bytes);
 CERA_API int32_t cera_cuda_kv_restore(cera_cuda_model *m, const void *data, size_t bytes);
+/* The same state in the shape of the reference's StateSnapshot (cera/src/kv_cache.rs:1379-1421: `seq_len` plus, per
+ * attention layer, LayerSnapshot::Attention { k_data, v_data } - raw little-endian f32 rows - or ::AttentionF16 for an
+ * f16 cache): one call per layer fills k_data and v_data with the layer's rows [0, seq_len), kv_dim elements each,
+ * exactly the bytes InferenceState::snapshot takes from its key / value cache (kv_cache.rs:780-800).  bytes_each must
+ * be cera_cuda_kv_layer_bytes(m).  restore_layer writes the rows back and sets seq_len (give every layer the same
+ * value); the element width is the model's kv_f16 setting on both sides, as the reference's cross-mode gate demands. */
+CERA_API size_t cera_cuda_kv_layer_bytes(const cera_cuda_model *m);
+CERA_API int32_t cera_cuda_kv_snapshot_layer(cera_cuda_model *m, uint32_t layer, void *k_data, void *v_data, size_t bytes_each);
+CERA_API int32_t cera_cuda_kv_restore_layer(cera_cuda_model *m, uint32_t layer, const void *k_data, const void *v_data,
+                                            size_t bytes_each, size_t seq_len);
 CERA_API size_t cera_cuda_seq_len(const cera_cuda_model *m);
 /* Model::gpu_memory_bytes (mod.rs:500). */
 CERA_API size_t cera_cuda_memory_bytes(const cera_cuda_model *m);

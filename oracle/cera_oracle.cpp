@@ -1091,6 +1091,11 @@ int cera_oracle_model_forward(cera_oracle_model *M, uint32_t token, size_t pos, 
     cera_oracle_dequantize_row(M->embd.type,
                                M->embd.bytes + (size_t)token * cera_oracle_row_bytes(M->embd.type, hs),
                                hs, hidden.data());
+    // Granite scalar multipliers, applied where cera/src/model/llama.rs applies them (1544-1546, 515-521, 543-549, 591-594)
+    if (c.embedding_scale != 0.0f && c.embedding_scale != 1.0f)
+        for (size_t i = 0; i < hs; ++i) hidden[i] *= c.embedding_scale;
+    const float res_scale = c.residual_scale != 0.0f ? c.residual_scale : 1.0f;
+    const float att_scale = c.attention_scale != 0.0f ? c.attention_scale : 1.0f / std::sqrt((float)hd);
     const float *ffreq = M->rope_freqs.bytes ? (const float *)M->rope_freqs.bytes : nullptr;
     const size_t esz = c.kv_f16 ? 2 : 4;
     for (size_t l = 0; l < c.n_layers; ++l) {
@@ -1121,10 +1126,12 @@ int cera_oracle_model_forward(cera_oracle_model *M, uint32_t token, size_t pos, 
             std::memcpy(vc.data() + pos * kvd * 4, v.data(), kvd * 4);
         }
         cera_oracle_decode_attention(q.data(), kc.data(), vc.data(), c.kv_f16, c.n_heads, c.n_kv_heads,
-                                     hd, pos + 1, 1.0f / std::sqrt((float)hd), attn.data(),
+                                     hd, pos + 1, att_scale, attn.data(),
                                      scores.data());
         gemv(M->wo[l], attn.data(), out.data());
         if (!M->lora.empty()) lora_apply(M->lora[l * 7 + 3], attn.data(), out.data());  // transformer.rs:1519-1528
+        if (res_scale != 1.0f)
+            for (size_t i = 0; i < hs; ++i) out[i] *= res_scale;
         for (size_t i = 0; i < hs; ++i) hidden[i] += out[i];
         normed = hidden;
         cera_oracle_rmsnorm(normed.data(), (const float *)M->ffn_norm[l].bytes, hs, c.rms_norm_eps);
@@ -1137,6 +1144,8 @@ int cera_oracle_model_forward(cera_oracle_model *M, uint32_t token, size_t pos, 
         cera_oracle_silu_mul(g.data(), u.data(), ff);
         gemv(M->down[l], g.data(), out.data());
         if (!M->lora.empty()) lora_apply(M->lora[l * 7 + 6], g.data(), out.data());  // transformer.rs:1642-1651
+        if (res_scale != 1.0f)
+            for (size_t i = 0; i < hs; ++i) out[i] *= res_scale;
         for (size_t i = 0; i < hs; ++i) hidden[i] += out[i];
     }
     cera_oracle_rmsnorm(hidden.data(), (const float *)M->out_norm.bytes, hs, c.rms_norm_eps);
@@ -1145,6 +1154,11 @@ int cera_oracle_model_forward(cera_oracle_model *M, uint32_t token, size_t pos, 
     if (logits) {
         const TensorRef &o = M->output.bytes ? M->output : M->embd;
         gemv(o, hidden.data(), logits);
+        if (c.logit_scale != 0.0f && c.logit_scale != 1.0f) {
+            const float inv = 1.0f / c.logit_scale;
+            const size_t vocab = c.vocab_size;
+            for (size_t i = 0; i < vocab; ++i) logits[i] *= inv;
+        }
     }
     return 0;
 }
@@ -1215,6 +1229,14 @@ int cera_oracle_model_last_hidden(const cera_oracle_model *m, float *out) {
     if (m->last_hidden.empty()) return -1;
     std::memcpy(out, m->last_hidden.data(), m->last_hidden.size() * 4);
     return 0;
+}
+size_t cera_oracle_model_kv(const cera_oracle_model *m, size_t layer, int which, void *out, size_t cap) {
+    if (layer >= m->kcache.size()) return 0;
+    const auto &c = which ? m->vcache[layer] : m->kcache[layer];
+    const size_t kvd = (size_t)m->cfg.n_kv_heads * m->cfg.head_dim;
+    const size_t n = m->seq_len * kvd * (m->cfg.kv_f16 ? 2 : 4);
+    if (out) std::memcpy(out, c.data(), n < cap ? n : cap);
+    return n;
 }
 void cera_oracle_model_free(cera_oracle_model *m) { delete m; }
 

@@ -142,6 +142,9 @@ typedef struct {
     int32_t rope_type; /* 0 NORM, 1 NEOX */
     int32_t kv_f16;
     int32_t n_threads; /* rows of each GEMV are split over this many threads */
+    /* ScalarMultipliers (cera/src/model/mod.rs:49-112), 0 = absent = identity: hidden *= embedding after the lookup;
+     * block outputs *= residual before the residual add; attention replaces 1/sqrt(head_dim); logits *= 1/logit. */
+    float embedding_scale, residual_scale, attention_scale, logit_scale;
 } cera_oracle_config;
 
 enum {
@@ -177,6 +180,9 @@ void cera_oracle_model_truncate_kv(cera_oracle_model *m, size_t len);
 int cera_oracle_model_shift_kv(cera_oracle_model *m, size_t n_keep, size_t shift);
 void cera_oracle_model_set_threads(cera_oracle_model *m, int n_threads);
 size_t cera_oracle_model_seq_len(const cera_oracle_model *m);
+/* Bytes of one layer's key (which = 0) or value (1) cache, rows [0, seq_len): what InferenceState::snapshot copies
+ * (cera/src/kv_cache.rs:780-800).  Returns the byte count; copies at most cap bytes when out is not NULL. */
+size_t cera_oracle_model_kv(const cera_oracle_model *m, size_t layer, int which, void *out, size_t cap);
 /* Copies the last hidden-state snapshots recorded by forward (for drift
  * diagnosis): which = 0 final normed hidden. */
 int cera_oracle_model_last_hidden(const cera_oracle_model *m, float *out);

@@ -67,13 +67,15 @@ class OracleConfig(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("n_layers", "hidden_size", "intermediate_size", "n_heads",
                                           "n_kv_heads", "head_dim", "vocab_size", "max_seq_len")] + [
         ("rope_theta", C.c_float), ("rms_norm_eps", C.c_float), ("rope_type", C.c_int32),
-        ("kv_f16", C.c_int32), ("n_threads", C.c_int32)]
+        ("kv_f16", C.c_int32), ("n_threads", C.c_int32), ("embedding_scale", C.c_float), ("residual_scale", C.c_float),
+        ("attention_scale", C.c_float), ("logit_scale", C.c_float)]
 
 
 _sig("cera_oracle_model_create", _p, C.POINTER(OracleConfig))
 _sig("cera_oracle_model_set_tensor", C.c_int, _p, C.c_int, C.c_int, C.c_int, _sz, _sz, _p)
 _sig("cera_oracle_model_forward", C.c_int, _p, C.c_uint32, _sz, _p)
 _sig("cera_oracle_model_truncate_kv", None, _p, _sz)
+_sig("cera_oracle_model_kv", _sz, _p, _sz, C.c_int, _p, _sz)
 _sig("cera_oracle_model_shift_kv", C.c_int, _p, _sz, _sz)
 _sig("cera_oracle_lora_apply", None, _sz, _sz, _sz, C.c_float, _p, _p, _p, _p)
 _sig("cera_oracle_model_set_lora", C.c_int, _p, C.c_int, C.c_int, _sz, _sz, _sz, C.c_float, _p, _p)
@@ -304,6 +306,13 @@ class OracleModel:
 
     def truncate_kv(self, n):
         _lib.cera_oracle_model_truncate_kv(self.h, n)
+
+    def kv(self, layer, which):
+        """Bytes of the layer's key (0) / value (1) cache rows [0, seq_len)."""
+        n = _lib.cera_oracle_model_kv(self.h, layer, which, None, 0)
+        out = np.empty(n, dtype=np.uint8)
+        _lib.cera_oracle_model_kv(self.h, layer, which, _ptr(out), n)
+        return out
 
     def set_threads(self, n):
         _lib.cera_oracle_model_set_threads(self.h, n)

@@ -118,8 +118,9 @@ def test_decode_attention_long_context(seq, f16):
 @pytest.mark.parametrize("nh,nkv,hd,seq", [(32, 8, 128, 4097), (32, 8, 128, 5000), (32, 8, 128, 8191), (16, 2, 128, 4500),
                                            (8, 2, 64, 6000), (16, 2, 64, 4200)])
 def test_decode_attention_streamed_kernel(nh, nkv, hd, seq, f16):
-    """Beyond 4096 positions the split pass is the TMA-staged kernel: ragged last tiles, splits with no whole
-    tile, both KV widths, head_dim 64 / 128 and groups of 4 / 8; none of its bounded waits may run out."""
+    """The online-softmax split kernel that stages K/V through shared memory with cp.async (the path long
+    contexts take when the reference-order kernels are switched off): ragged last tiles, splits with no whole
+    tile, both KV widths, head_dim 64 / 128 and groups of 4 / 8; the kernel status word must stay clear."""
     torch = need_gpu()
     import cera_b200 as cb
     from cera_b200._lib import kernel_status

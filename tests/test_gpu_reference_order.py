@@ -102,4 +102,52 @@ def test_model_logits_bit_identical_to_the_oracle(kv_f16):
         lg, lo = gpu.forward(tok, pos), oracle.forward(tok, pos)
         assert_bits(lg, lo, f"logits at position {pos}")
         tok = int(O.argmax(lo))
+    # the per-layer snapshot is the reference's StateSnapshot content: the oracle's key / value cache bytes
+    snap = gpu.state_snapshot()
+    assert snap["seq_len"] == 40 and len(snap["layers"]) == cfg["n_layers"]
+    for l, (kd, vd) in enumerate(snap["layers"]):
+        assert np.array_equal(kd, oracle.kv(l, 0)), f"k_data of layer {l}"
+        assert np.array_equal(vd, oracle.kv(l, 1)), f"v_data of layer {l}"
+    # restoring it into a truncated cache brings the next token's logits back, bit for bit
+    want = gpu.forward(tok, 40)
+    gpu.truncate_kv(0)
+    gpu.restore_state(snap)
+    assert_bits(gpu.forward(tok, 40), want, "logits after restore_state")
+    with pytest.raises(Exception):  # half the bytes: a snapshot of the other element width
+        bad = {"seq_len": snap["seq_len"], "layers": [(k[: k.size // 2], v[: v.size // 2]) for k, v in snap["layers"]]}
+        gpu.restore_state(bad)
     gpu.close()
+
+
+@pytest.mark.gpu
+def test_granite_scalar_multipliers_bit_identical_to_the_oracle():
+    """Granite's four scalars (cera/src/model/mod.rs:49-112: embedding, residual, attention, logit) are applied where
+    cera/src/model/llama.rs applies them: decode logits equal the oracle's bits, the batched prompt path agrees within
+    the GEMM tolerance, and the per-layer KV snapshot holds the oracle's K/V bytes."""
+    need_gpu()
+    from cera_b200 import synth
+    cfg = dict(n_layers=2, hidden_size=1024, intermediate_size=2048, n_heads=8, n_kv_heads=2, head_dim=128, vocab_size=2048,
+               rope_theta=10000.0, rms_norm_eps=1e-5, rope_type=0,
+               embedding_scale=12.0, residual_scale=0.22, attention_scale=0.0078125, logit_scale=8.0)
+    oracle = O.OracleModel(**cfg, max_seq_len=48, kv_f16=0, n_threads=4)
+    gpu = synth.build_llama(cfg, seed=23, max_seq_len=48, kv_f16=0,
+                            sink=lambda r, l, t, rows, cols, d: oracle.set_tensor(int(r), l, t, rows, cols, d))
+    toks, tok = [], 9
+    for pos in range(12):
+        toks.append(tok)
+        lg, lo = gpu.forward(tok, pos), oracle.forward(tok, pos)
+        assert_bits(lg, lo, f"logits at position {pos}")
+        tok = int(O.argmax(lo))
+    # the same prompt through the batched kernels: same logits within the GEMM tolerance (1e-3 relative, 1e-4 absolute)
+    gpu.truncate_kv(0)
+    lb = gpu.forward_prefill(np.asarray(toks, dtype=np.uint32), 0)
+    scale = float(np.abs(lo).max())
+    assert float(np.abs(lb - lo).max()) <= 1e-3 * scale + 1e-4
+    # identity scalars are a no-op: a model created with 1.0 everywhere equals one created with the fields left at 0
+    gpu.close()
+    cfg1 = dict(cfg, embedding_scale=1.0, residual_scale=1.0, attention_scale=0.0, logit_scale=1.0)
+    cfg0 = {k: v for k, v in cfg.items() if not k.endswith("_scale")}
+    a, b = synth.build_llama(cfg1, seed=23, max_seq_len=8), synth.build_llama(cfg0, seed=23, max_seq_len=8)
+    assert_bits(a.forward(3, 0), b.forward(3, 0), "identity scalars")
+    a.close()
+    b.close()
