@@ -630,8 +630,7 @@ def main():
             for n in (8, 64, 256, 512):
                 ops, us = gemm_microbench(torch, cb, tname, m, k, n, max(3, args.iters // (4 if n > 64 else 1)))
                 emit(json.dumps({"type": tname, "m": m, "k": k, "n": n, "us": round(us, 2),
-                                  "tops": round(ops / us / 1e6, 2), "frac_of_int8_nominal_4500": round(ops / us / 1e6 / 4500, 4)}),
-                      flush=True)
+                                  "tops": round(ops / us / 1e6, 2), "frac_of_int8_nominal_4500": round(ops / us / 1e6 / 4500, 4)}))
     elif args.impl == "reference":
         reference_arm(args, rank)
     else:

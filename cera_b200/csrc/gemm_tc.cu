@@ -3,16 +3,20 @@
 //
 // The arithmetic contract (cera/src/backend/simd.rs:5248-5371, 5693-5878) scales every 32-element block's EXACT
 // integer sum by (weight block scale) x (activation block scale), so a tensor-core instruction may accumulate over
-// one block only and the rescale runs on the CUDA cores.  Three choices keep that rescale small:
+// one block only and the rescale runs on the CUDA cores.  Four choices keep that rescale small:
 //
 //  * f16 operands with exact small integers.  A weight operand element is sc * q (six-bit sub-block scale times
 //    the 4/5-bit quant, at most 63 * 31 = 1953 < 2048: exact in f16), an activation element is the int8 quant.
 //    kind::f16 MMAs accumulate the products exactly in f32 (|sum| < 2^24), so the accumulator already holds the
 //    float the rescale needs - no int-to-float conversion - and the sub-block scale is inside the product.
 //  * Tokens on the TMEM lanes.  D[token][weight row]: an epilogue thread owns one token, so the activation block
-//    scale is a register; it keeps p[row] += D * xs - (dmin*mn/d)[row] * (xs * sum of the block's quants) for its
-//    32 rows in registers, and once per 256-element super-block folds out[row] += d[row] * p[row] into a third
-//    TMEM region.  Two FMAs per cell per block, the row-side factors read as shared-memory broadcasts.
+//    scale is one value per thread; it keeps p[row] += D * xs for its 32 rows in registers - ONE FMA per cell
+//    per block - and once per 256-element super-block folds out[row] += d[row] * p[row] into a TMEM region.
+//  * The min term rides the tensor cores too.  sum_b dmin*mn_b * (xs_b * A_b) (A_b = the block's sum of quants)
+//    has one factor per (row, block) and one per (token, block): a 16-column MMA per super-block multiplies the
+//    eight six-bit mins (exact in f16, each twice) by the eight values g*xs_b*A_b split into an f16 high and low
+//    part (g = a power of two per token that brings them below 2^15; 22 significant bits survive), into a third
+//    accumulator; the fold subtracts dmin[row] * Dm / g.
 //  * Operand tiles are built in shared memory by producer warps straight from the quantized bytes (weights:
 //    nibble -> 0x6400|q -> one HFMA2 with the sub-block scale; activations: byte -> 0x6400|(b^0x80) -> HSUB2), in the
 //    canonical K-major no-swizzle layout (8-row x 16-byte core matrices), three stages of 128 k-elements deep.
@@ -44,11 +48,15 @@ constexpr int TC_STAGES = 3;
 constexpr int TC_EPI_WARPS = 16;                // four warpgroups: each covers the 128 token lanes for 32 weight rows
 constexpr int TC_THREADS = (9 + TC_EPI_WARPS) * 32;
 constexpr uint32_t TC_OP_BYTES = TC_BM * TC_KS * 2;                      // one operand tile of a stage: 32 KB
-constexpr uint32_t TC_TAB_BYTES = 4 * TC_BN * 4 + TC_BN * 4 + 2 * 4 * TC_BM * 4;  // mneg[4][128], dval[128]; xsv[4][128], xbv[4][128]
-constexpr uint32_t TC_STAGE_BYTES = 2 * TC_OP_BYTES + TC_TAB_BYTES;      // 72 192
-constexpr uint32_t TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 256;     // + barriers, TMEM address, abort flag
-constexpr uint32_t TC_TMEM_COLS = 512;                                   // D0 [0,128) D1 [128,256) D2 [256,384) OUT [384,512)
-constexpr uint32_t TC_DBUFS = 3;
+constexpr uint32_t TC_TAB_BYTES = 4 * TC_BM * 4;                         // xsv[4][128]: the stage's activation block scales per token
+constexpr uint32_t TC_STAGE_BYTES = 2 * TC_OP_BYTES + TC_TAB_BYTES;      // 67 584
+// per super-block (two stages), two slots: the min-term operands (16 k-columns each) and the row-side tables
+constexpr uint32_t TC_MINOP_BYTES = TC_BM * 16 * 2;                      // 4 KB: [2 k chunks][128 rows][8 f16]
+constexpr uint32_t TC_SLOT_BYTES = 2 * TC_MINOP_BYTES + 2 * TC_BN * 4;   // A, B, dval[128], dmin[128]
+constexpr uint32_t TC_TAIL_OFF = TC_STAGES * TC_STAGE_BYTES + 2 * TC_SLOT_BYTES;  // ginv[128], then barriers, TMEM address, abort flag
+constexpr uint32_t TC_SMEM_BYTES = TC_TAIL_OFF + TC_BM * 4 + 256;
+constexpr uint32_t TC_TMEM_COLS = 512;                                   // D0 [0,128) D1 [128,256) Dm [256,384) OUT [384,512)
+constexpr uint32_t TC_DBUFS = 2;
 constexpr uint32_t TC_KC_STRIDE = TC_BM * 16;                            // bytes between 8-element k chunks: 2048
 
 struct TcParams {
@@ -125,7 +133,9 @@ __device__ __forceinline__ void bytes_to_h1024(uint32_t v, __half2 &lo, __half2 
 template <int T>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p) {
     extern __shared__ __align__(1024) uint8_t tc_smem[];
-    uint64_t *bars = reinterpret_cast<uint64_t *>(tc_smem + TC_STAGES * TC_STAGE_BYTES);
+    uint8_t *slots = tc_smem + TC_STAGES * TC_STAGE_BYTES;
+    float *ginv_tab = reinterpret_cast<float *>(tc_smem + TC_TAIL_OFF);  // [128]: 1 / g of every token lane
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tc_smem + TC_TAIL_OFF + TC_BM * 4);
     uint64_t *full_ab = bars, *empty_ab = bars + TC_STAGES, *full_d = bars + 2 * TC_STAGES, *empty_d = full_d + TC_DBUFS;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC_STAGES + 2 * TC_DBUFS);
     volatile uint32_t *abort_flag = tmem_slot + 1;
@@ -179,6 +189,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
                         tc_mma_f16(tmem + buf * TC_BN, smem_desc(a_base + kc * TC_KC_STRIDE, TC_KC_STRIDE, 128),
                                    smem_desc(b_base + kc * TC_KC_STRIDE, TC_KC_STRIDE, 128), idesc, j);
                     }
+                    if ((it & 1) && b == 3) {
+                        // the super-block's min term: Dm[token][row] = sum_b mn_b * (hi_b + lo_b).  The epilogue has read the
+                        // previous Dm: it handed back a D buffer of THIS iteration, which it reaches only after that fold.
+                        const uint32_t slot = tma::smem_u32(slots + ((it >> 1) & 1) * TC_SLOT_BYTES);
+                        tc_mma_f16(tmem + 2 * TC_BN, smem_desc(slot, TC_KC_STRIDE, 128), smem_desc(slot + TC_MINOP_BYTES, TC_KC_STRIDE, 128),
+                                   idesc, 0);
+                    }
                     tc_commit(full_d + buf);
                 }
                 tc_commit(empty_ab + s);
@@ -193,18 +210,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
             uint4 piece[4], h, hb0, hb1;
         };
         auto fetch = [&](uint32_t it) {
-            RawW r;
+            RawW rw;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) r.piece[c] = ld_stream(q_piece_ptr(p.w, row, 4, it * 4 + c));
+            for (int c = 0; c < 4; ++c) rw.piece[c] = ld_stream(q_piece_ptr(p.w, row, 4, it * 4 + c));
             const size_t sbi = sb_index(p.w, row, it >> 1);
-            r.h = __ldg(reinterpret_cast<const uint4 *>(p.w.hdr) + sbi);
-            r.hb0 = make_uint4(0, 0, 0, 0);
-            r.hb1 = r.hb0;
+            rw.h = __ldg(reinterpret_cast<const uint4 *>(p.w.hdr) + sbi);
+            rw.hb0 = make_uint4(0, 0, 0, 0);
+            rw.hb1 = rw.hb0;
             if (T == CERA_TYPE_Q5_K) {
-                r.hb0 = __ldg(reinterpret_cast<const uint4 *>(p.w.qh + sbi * 32));
-                r.hb1 = __ldg(reinterpret_cast<const uint4 *>(p.w.qh + sbi * 32 + 16));
+                rw.hb0 = __ldg(reinterpret_cast<const uint4 *>(p.w.qh + sbi * 32));
+                rw.hb1 = __ldg(reinterpret_cast<const uint4 *>(p.w.qh + sbi * 32 + 16));
             }
-            return r;
+            return rw;
         };
         RawW nxt = fetch(0);
         for (uint32_t it = 0; it < n_it; ++it) {
@@ -216,17 +233,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
             if (!tma::mbar_wait_blocking(empty_ab + s, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 4u)) break;
             uint8_t *stage = tc_smem + s * TC_STAGE_BYTES;
             uint8_t *opb = stage + TC_OP_BYTES;
-            float *mneg = reinterpret_cast<float *>(stage + 2 * TC_OP_BYTES), *dval = mneg + 4 * TC_BN;
+            uint8_t *slot = slots + ((it >> 1) & 1) * TC_SLOT_BYTES;  // free: the stage it shares a phase with was released
             const uint32_t hf = it & 1;
             uint32_t scp, mnp;
             kq_quad(h, hf, scp, mnp);
             const float d = h2f((uint16_t)(h.x & 0xFFFF)), dmin = h2f((uint16_t)(h.x >> 16));
-            const bool live = d != 0.0f;  // d == 0: the quant part of the super-block is zero whatever q is
-            const float dv = live ? d : 1.0f, rd = 1.0f / dv;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int pair = c >> 1, half = c & 1;
-                const uint32_t sc_lo = live ? (scp >> (8 * (2 * pair))) & 0xFF : 0u, sc_hi = live ? (scp >> (8 * (2 * pair + 1))) & 0xFF : 0u;
+                const uint32_t sc_lo = (scp >> (8 * (2 * pair))) & 0xFF, sc_hi = (scp >> (8 * (2 * pair + 1))) & 0xFF;
                 const __half2 s_lo = __half2half2(__ushort2half_rn((unsigned short)sc_lo)), s_hi = __half2half2(__ushort2half_rn((unsigned short)sc_hi));
                 const __half2 nb_lo = __hmul2(s_lo, __float2half2_rn(-1024.0f)), nb_hi = __hmul2(s_hi, __float2half2_rn(-1024.0f));
                 const uint4 v4 = piece[c];
@@ -256,9 +271,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
                 *reinterpret_cast<uint4 *>(opb + op_off(kc_hi, r)) = *reinterpret_cast<const uint4 *>(&hi8[0]);
                 *reinterpret_cast<uint4 *>(opb + op_off(kc_hi + 1, r)) = *reinterpret_cast<const uint4 *>(&hi8[4]);
             }
+            {
+                // the four mins of this half super-block, each twice (for the high and the low part of the token side):
+                // k chunk `hf` of the min-term weight operand
+                __half2 mn2[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) mneg[j * TC_BN + r] = -(dmin * (float)((mnp >> (8 * j)) & 0xFF)) * rd;
-            dval[r] = live ? d : 1.0f;
+                for (int j = 0; j < 4; ++j) mn2[j] = __half2half2(__ushort2half_rn((unsigned short)((mnp >> (8 * j)) & 0xFF)));
+                *reinterpret_cast<uint4 *>(slot + TC_MINOP_BYTES + op_off(hf, r)) = *reinterpret_cast<const uint4 *>(&mn2[0]);
+                if (hf == 0) {
+                    float *dval = reinterpret_cast<float *>(slot + 2 * TC_MINOP_BYTES);
+                    dval[r] = d;
+                    dval[TC_BN + r] = dmin;
+                }
+            }
             fence_async_smem();
             tma::mbar_arrive(full_ab + s);
         }
@@ -275,14 +300,37 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
             uint4 sm;   // the eight 16-element sums
         };
         auto fetch = [&](uint32_t it) {
-            RawX r;
+            RawX rx;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) r.v[j] = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)it * TC_KS) + j);
-            r.xs = __ldg(reinterpret_cast<const float4 *>(p.x.scales + (size_t)token * nb32 + it * 4));
-            r.sm = __ldg(reinterpret_cast<const uint4 *>(p.x.sums + (size_t)token * nb16 + it * 8));
-            return r;
+            for (int j = 0; j < 8; ++j) rx.v[j] = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)it * TC_KS) + j);
+            rx.xs = __ldg(reinterpret_cast<const float4 *>(p.x.scales + (size_t)token * nb32 + it * 4));
+            rx.sm = __ldg(reinterpret_cast<const uint4 *>(p.x.sums + (size_t)token * nb16 + it * 8));
+            return rx;
         };
         RawX nxt = fetch(0);
+        // g: a power of two that brings every xs_b * A_b of the token below 2^15, so that its f16 high / low parts keep
+        // 22 significant bits whatever the magnitude of the activations
+        float g = 1.0f;
+        {
+            float mx = 0.0f;
+            for (uint32_t it = 0; it < n_it; ++it) {
+                const float4 x4 = __ldg(reinterpret_cast<const float4 *>(p.x.scales + (size_t)token * nb32 + it * 4));
+                const uint4 s4 = __ldg(reinterpret_cast<const uint4 *>(p.x.sums + (size_t)token * nb16 + it * 8));
+                const float xv[4] = {x4.x, x4.y, x4.z, x4.w};
+                const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const float v = fabsf(xv[b] * (float)((int)(int16_t)(sw[b] & 0xFFFF) + (int)(int16_t)(sw[b] >> 16)));
+                    mx = fmaxf(mx, v == v && v < 3.0e38f ? v : 0.0f);
+                }
+            }
+            if (mx > 0.0f) {
+                int e;
+                frexpf(mx, &e);  // mx < 2^e
+                g = ldexpf(1.0f, 15 - e);
+            }
+            ginv_tab[c] = 1.0f / g;  // published by the first full_ab arrival below
+        }
         for (uint32_t it = 0; it < n_it; ++it) {
             const uint32_t s = it % TC_STAGES;
             const RawX cur = nxt;
@@ -290,6 +338,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
             const uint4 (&raw)[8] = cur.v;
             if (!tma::mbar_wait_blocking(empty_ab + s, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) break;
             uint8_t *opa = tc_smem + s * TC_STAGE_BYTES;
+            uint8_t *slot = slots + ((it >> 1) & 1) * TC_SLOT_BYTES;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {  // 16 quants -> k chunks 2j, 2j+1
                 const uint32_t wv[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
@@ -305,15 +354,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
                 *reinterpret_cast<uint4 *>(opa + op_off(2 * j + 1, c)) = *reinterpret_cast<const uint4 *>(&o[4]);
             }
             {
-                // per-token scalars of the stage's four blocks, for the epilogue: the block scale and scale x (sum of the quants)
-                float *xsv = reinterpret_cast<float *>(opa + 2 * TC_OP_BYTES) + 5 * TC_BN, *xbv = xsv + 4 * TC_BM;
+                // per-token scalars of the stage's four blocks: the block scales for the epilogue, and g * xs_b * A_b as an f16
+                // high and low part = k chunk (it & 1) of the min-term token operand
+                float *xsv = reinterpret_cast<float *>(opa + 2 * TC_OP_BYTES);
                 const float xv[4] = {cur.xs.x, cur.xs.y, cur.xs.z, cur.xs.w};
                 const uint32_t sw[4] = {cur.sm.x, cur.sm.y, cur.sm.z, cur.sm.w};
+                __half2 hl[4];
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
                     xsv[b * TC_BM + c] = xv[b];
-                    xbv[b * TC_BM + c] = xv[b] * (float)((int)(int16_t)(sw[b] & 0xFFFF) + (int)(int16_t)(sw[b] >> 16));
+                    const float v = (xv[b] * (float)((int)(int16_t)(sw[b] & 0xFFFF) + (int)(int16_t)(sw[b] >> 16))) * g;
+                    const __half hi = __float2half_rn(v);
+                    const __half lo = __float2half_rn(v - __half2float(hi));
+                    hl[b] = __halves2half2(hi, lo);
                 }
+                *reinterpret_cast<uint4 *>(slot + op_off(it & 1, c)) = *reinterpret_cast<const uint4 *>(&hl[0]);
             }
             fence_async_smem();
             tma::mbar_arrive(full_ab + s);
@@ -322,70 +377,78 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
         // ---------------------------------------------------------------- epilogue: thread = (token lane, 32 rows)
         const uint32_t e = warp - 9, ch = e >> 2, quad = warp & 3;  // a warp reaches TMEM lanes [32 (warp % 4), +32)
         const uint32_t tl = quad * 32 + lane;                       // token lane
-        const uint32_t token = min(col0 + tl, p.n - 1);
         const uint32_t lane_addr = tmem + ((quad * 32) << 16);
         float pacc[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) pacc[i] = 0.0f;
+        float ginv = 1.0f;
         bool ok = true;
         for (uint32_t it = 0; it < n_it && ok; ++it) {
             const uint32_t s = it % TC_STAGES;
-            const float *mneg = reinterpret_cast<const float *>(tc_smem + s * TC_STAGE_BYTES + 2 * TC_OP_BYTES);
-            const float *dval = mneg + 4 * TC_BN, *xsv = dval + TC_BN, *xbv = xsv + 4 * TC_BM;
-            // the producers' release of this stage, observed directly: the row-side tables are read with plain loads
+            const float *xsv = reinterpret_cast<const float *>(tc_smem + s * TC_STAGE_BYTES + 2 * TC_OP_BYTES);
+            // the producers' release of this stage, observed directly: the tables are read with plain loads
             if (!tma::mbar_wait_blocking(full_ab + s, (it / TC_STAGES) & 1, abort_flag, &g_tc_status, 32u)) break;
+            if (it == 0) ginv = ginv_tab[tl];
             for (uint32_t b = 0; b < 4; ++b) {
                 const uint32_t gb = it * 4 + b, buf = gb % TC_DBUFS;
-                const float xs = xsv[b * TC_BM + tl], xb = xbv[b * TC_BM + tl];
+                const float xs = xsv[b * TC_BM + tl];
                 if (!tma::mbar_wait_blocking(full_d + buf, (gb / TC_DBUFS) & 1, abort_flag, &g_tc_status, 16u)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-#pragma unroll
-                for (int c4 = 0; c4 < 2; ++c4) {
+                {
                     uint32_t dreg[16];
-                    tmem_ld16(lane_addr + buf * TC_BN + ch * 32 + c4 * 16, dreg);
-                    const float4 *mq = reinterpret_cast<const float4 *>(mneg + b * TC_BN + ch * 32 + c4 * 16);
-                    const float4 m0 = mq[0], m1 = mq[1], m2 = mq[2], m3 = mq[3];
-                    const float mv[16] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w, m2.x, m2.y, m2.z, m2.w, m3.x, m3.y, m3.z, m3.w};
+                    tmem_ld16(lane_addr + buf * TC_BN + ch * 32, dreg);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        pacc[c4 * 16 + i] = fmaf(mv[i], xb, fmaf(__uint_as_float(dreg[i]), xs, pacc[c4 * 16 + i]));
+                    for (int i = 0; i < 16; ++i) pacc[i] = fmaf(__uint_as_float(dreg[i]), xs, pacc[i]);
+                    tmem_ld16(lane_addr + buf * TC_BN + ch * 32 + 16, dreg);
+                    tmem_wait_ld();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) tma::mbar_arrive(empty_d + buf);  // the values are in registers: the buffer may be overwritten
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) pacc[16 + i] = fmaf(__uint_as_float(dreg[i]), xs, pacc[16 + i]);
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) tma::mbar_arrive(empty_d + buf);
             }
             if (!ok) break;
             if (it & 1) {
-                // end of a 256-element super-block: out[row] += d[row] * p[row], the running sum lives in TMEM
+                // end of a 256-element super-block: out[row] += d[row] * p[row] - dmin[row] * Dm[row] / g; the running sum lives in TMEM
+                const float *dval = reinterpret_cast<const float *>(slots + ((it >> 1) & 1) * TC_SLOT_BYTES + 2 * TC_MINOP_BYTES);
 #pragma unroll
                 for (int c4 = 0; c4 < 2; ++c4) {
-                    uint32_t oreg[16];
-                    const uint32_t addr = lane_addr + TC_DBUFS * TC_BN + ch * 32 + c4 * 16;
+                    uint32_t oreg[16], mreg[16];
+                    const uint32_t addr = lane_addr + 3 * TC_BN + ch * 32 + c4 * 16;
+                    tmem_ld16(lane_addr + 2 * TC_BN + ch * 32 + c4 * 16, mreg);
                     if (it > 1) {
                         tmem_ld16(addr, oreg);
-                        tmem_wait_ld();
                     } else {
 #pragma unroll
                         for (int i = 0; i < 16; ++i) oreg[i] = 0u;
                     }
-                    const float4 *dq = reinterpret_cast<const float4 *>(dval + ch * 32 + c4 * 16);
-                    const float4 d0 = dq[0], d1 = dq[1], d2 = dq[2], d3 = dq[3];
-                    const float dvv[16] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w, d2.x, d2.y, d2.z, d2.w, d3.x, d3.y, d3.z, d3.w};
+                    tmem_wait_ld();
+                    const float4 *dq = reinterpret_cast<const float4 *>(dval + ch * 32 + c4 * 16), *mq = dq + TC_BN / 4;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        oreg[i] = __float_as_uint(fmaf(pacc[c4 * 16 + i], dvv[i], __uint_as_float(oreg[i])));
-                        pacc[c4 * 16 + i] = 0.0f;
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const float4 dv = dq[q4], mv = mq[q4];
+                        const float dvv[4] = {dv.x, dv.y, dv.z, dv.w}, mvv[4] = {mv.x, mv.y, mv.z, mv.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int j = q4 * 4 + i;
+                            float o = fmaf(pacc[c4 * 16 + j], dvv[i], __uint_as_float(oreg[j]));
+                            o = fmaf(-mvv[i], __uint_as_float(mreg[j]) * ginv, o);
+                            oreg[j] = __float_as_uint(o);
+                            pacc[c4 * 16 + j] = 0.0f;
+                        }
                     }
                     tmem_st16(addr, oreg);
                 }
                 tmem_wait_st();
             }
+            tc_fence_before();
             __syncwarp();
-            if (lane == 0) tma::mbar_arrive(empty_ab + s);  // this warp is done with the stage's tables
+            if (lane == 0) tma::mbar_arrive(empty_ab + s);  // this warp is done with the stage's tables (and the slot's)
         }
         if (ok) {
             // ---- the tile -> global memory: cell (row i, token j) at out[i * ldy + j * ldc]
@@ -393,7 +456,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
 #pragma unroll
             for (int c4 = 0; c4 < 2; ++c4) {
                 uint32_t oreg[16];
-                tmem_ld16(lane_addr + TC_DBUFS * TC_BN + ch * 32 + c4 * 16, oreg);
+                tmem_ld16(lane_addr + 3 * TC_BN + ch * 32 + c4 * 16, oreg);
                 tmem_wait_ld();
                 if (tok_ok) {
 #pragma unroll
