@@ -494,6 +494,12 @@ def cuda_arm(args, rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     model_launches = model.launch_count() - launches0
+    per_rank_launches = [int(model_launches)]
+    if world > 1:  # every rank runs its own copy of the step's kernels on its row slices
+        t = torch.zeros(world, device="cuda", dtype=torch.int64)
+        t[rank] = int(model_launches)
+        dist.all_reduce(t)
+        per_rank_launches = [int(v) for v in t.tolist()]
     # the stream against the CPU reference's (same model seed, same prompt): identical, or the run is not a valid number
     gold = reference_stream() if (args.seed == 0 and prompt_len == PROMPT_LEN) else None
     stream_check = None
@@ -528,6 +534,7 @@ def cuda_arm(args, rank, world):
             "stream_check": stream_check,
             "e2e": {"value": K / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 4},
             "gpu_launches": int(model_launches + roof_launches),
+            "gpu_launches_per_rank": per_rank_launches,  # the model's kernels in the timed regions, by rank (rank 0 also runs the kernel microbench)
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": ROOFLINE_KERNEL, "achieved": achieved,
                          "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "peak_source": which,

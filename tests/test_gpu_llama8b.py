@@ -50,3 +50,32 @@ def test_llama8b_greedy_stream_equals_the_cpu_reference_stream():
         assert len(stream) == N_DECODE
     finally:
         model.close()
+
+
+def test_llama8b_batched_prompt_agrees_with_the_per_token_prompt():
+    """The same prompt through the batched kernels (tcgen05 / mma GEMMs, tiled attention - toleranced by nature) must
+    lead to the same greedy stream as the per-token prompt of the reference stream: identical over 128 tokens, or
+    forking only where the reference's own rule calls the pick a near-tie (cera/tests/gpu_transformer_parity.rs:168-238,
+    cera/tests/llama_batched_prefill_parity.rs:74-147); and its first logits must agree within the GEMM tolerance."""
+    need_gpu()
+    from cera_b200 import synth
+    with open(GOLDEN) as f:
+        gold = json.load(f)
+    cfg = dict(synth.LLAMA3_8B)
+    plen = gold["prompt_len"]
+    model = synth.build_llama(cfg, seed=gold["model_seed"], max_seq_len=plen + N_DECODE + 8)
+    try:
+        prompt = synth.prompt_tokens(plen, cfg["vocab_size"], seed=gold["prompt_seed"])
+        logits = model.forward_prefill(prompt, 0)
+        first = int(np.argmax(logits))
+        # 512 positions of int8 re-quantization sit between the two prompt paths: the model-level bar, scaled to the logits
+        assert abs(float(logits[gold["stream"][0]]) - gold["top1_logit"][0]) <= 2e-2 * gold["top8_spread"][0] + 1e-3
+        toks, _ = model.generate_greedy(first, plen, N_DECODE - 1)
+        stream = [first] + [int(t) for t in toks]
+        fork = next((i for i, (g, w) in enumerate(zip(stream, gold["stream"][:N_DECODE])) if g != w), None)
+        if fork is not None:
+            gap = gold["top1_logit"][fork] - gold["top2_logit"][fork]
+            assert stream[fork] == gold["top2_id"][fork] and gap <= TIE_FRACTION_TIGHT * gold["top8_spread"][fork], _fork_report(fork, stream[fork], gold)
+            assert fork >= 4, _fork_report(fork, stream[fork], gold)
+    finally:
+        model.close()
