@@ -26,18 +26,21 @@
 // in the last bits of the f64 sum, which survive the narrowing to f32 only in about one softmax in
 // 10^7 (and not at all while every partial sum is exactly representable, which holds whenever the
 // probabilities span fewer than ~29 binary orders of magnitude).
+#include <cooperative_groups.h>
+
 #include <cstdlib>
 #include <cstring>
 
 #include "act.cuh"
 #include "ops.h"
 
+namespace cg = cooperative_groups;
+
 namespace cera {
 
 namespace {
 
 constexpr int AX_VTHREADS = 256;   // threads of the values kernel
-constexpr uint32_t AX_SMEM_POS = 4096;  // probabilities of up to this many positions stay in shared memory
 
 // One HALF-WARP per (position, query head): its sixteen lanes are the reference's sixteen FMA chains (accumulator a,
 // lane L) - lane c = 8a + L multiplies elements 16j + c of the head for j = 0, 1, ... - and four xor-shuffle steps add
@@ -152,29 +155,20 @@ __device__ __forceinline__ void ax_stage_tile(uint32_t tile, uint32_t n_tiles, u
 // grid (hd / 32, n_kv), AX_VTHREADS threads.  ws: scores [n_heads][ld]; pw: probabilities [n_heads][ld] in global
 // memory, used when the positions do not fit shared memory (every CTA of a KV head writes the same values there).
 // Dynamic shared memory: AX_VSTAGES V tiles of AX_VT x 32 floats, then smem_pos * G floats of probabilities.
-__global__ void __launch_bounds__(AX_VTHREADS)
-attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, uint32_t ld, const void *__restrict__ vc, int kv_f16,
-                         uint32_t seq_len, const uint32_t *__restrict__ seq_dev, uint32_t n_kv, uint32_t G, uint32_t hd,
-                         uint32_t smem_pos, float *__restrict__ out, float *scales, int8_t *quants, int16_t *sums, const TpHook tp) {
-    extern __shared__ __align__(16) float ax_dyn[];
-    float *vt = ax_dyn;                                  // [AX_VSTAGES][AX_VT][32] (f16 caches use half of each tile)
-    float *ax_p = ax_dyn + AX_VSTAGES * AX_VT * 32;      // [G][smem_pos + 4]: a head's probabilities are contiguous, heads four banks apart
+// Softmax of the group's heads, the position-ordered value chains of one 32-dim slice, and the outputs (f32 + Q8_0).
+// The first V tiles have been requested by the caller.  scores_in_smem: ax_p already holds the scores (the fused
+// kernel); otherwise they are read from ws.
+__device__ __forceinline__ void ax_softmax_chain_emit(const float *__restrict__ ws, float *__restrict__ pw, uint32_t ld, const void *__restrict__ vc,
+                                                      int kv_f16, uint32_t seq, uint32_t n_kv, uint32_t G, uint32_t hd, uint32_t smem_pos,
+                                                      uint32_t kvh, uint32_t d0, float *vt, float *ax_p, double *red_d, float *red_f,
+                                                      bool scores_in_smem, float *__restrict__ out, float *scales, int8_t *quants,
+                                                      int16_t *sums, const TpHook &tp) {
     const uint32_t pstride = smem_pos + 4;
-    __shared__ double red_d[AX_VTHREADS / 32];
-    __shared__ float red_f[AX_VTHREADS / 32];
-    pdl_trigger();
-    const uint32_t kvh = blockIdx.y, d0 = blockIdx.x * 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t kv_dim = (size_t)n_kv * hd;
-    pdl_wait();
-    const uint32_t seq = seq_dev ? *seq_dev : seq_len;
     const bool in_smem = seq <= smem_pos;
     const uint32_t n_tiles = (seq + AX_VT - 1) / AX_VT;
-    // V tiles: a position's 32-dim slice is 128 contiguous bytes (64 for an f16 cache): 16-byte asynchronous copies,
-    // the first tiles are requested before the softmax below so that they land while it runs
     const uint32_t per_pos = kv_f16 ? 4 : 8;  // 16-byte pieces per position
-#pragma unroll
-    for (int i = 0; i < AX_VSTAGES; ++i) ax_stage_tile(i, n_tiles, seq, per_pos, vt, vc, kv_dim, (size_t)kvh * hd + d0, kv_f16, tid);
 
     // ---- probabilities of the group's heads.  Head h is handled by warps [h * nwh, (h + 1) * nwh).
     const uint32_t nwh = (AX_VTHREADS / 32) / G, h_mine = warp / nwh, wl = warp % nwh;  // warps past G * nwh idle here
@@ -185,8 +179,8 @@ attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, u
     float mx = -INFINITY;
     if (has_head) {
         for (uint32_t t = hti; t < seq; t += hth) {
-            const float v = s_row[t];
-            if (in_smem) ax_p[(size_t)h_mine * pstride + t] = v;
+            const float v = scores_in_smem ? ax_p[(size_t)h_mine * pstride + t] : s_row[t];
+            if (in_smem && !scores_in_smem) ax_p[(size_t)h_mine * pstride + t] = v;
             mx = fmaxf(mx, v);  // f32::max fold: NaN scores are ignored
         }
     }
@@ -278,6 +272,147 @@ attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, u
     }
 }
 
+// grid (hd / 32, n_kv), AX_VTHREADS threads.  ws: scores [n_heads][ld]; pw: probabilities [n_heads][ld] in global
+// memory, used when the positions do not fit shared memory (every CTA of a KV head writes the same values there).
+// Dynamic shared memory: AX_VSTAGES V tiles of AX_VT x 32 floats, then smem_pos * G floats of probabilities.
+__global__ void __launch_bounds__(AX_VTHREADS)
+attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, uint32_t ld, const void *__restrict__ vc, int kv_f16,
+                         uint32_t seq_len, const uint32_t *__restrict__ seq_dev, uint32_t n_kv, uint32_t G, uint32_t hd,
+                         uint32_t smem_pos, float *__restrict__ out, float *scales, int8_t *quants, int16_t *sums, const TpHook tp) {
+    extern __shared__ __align__(16) float ax_dyn[];
+    float *vt = ax_dyn;                                  // [AX_VSTAGES][AX_VT][32] (f16 caches use half of each tile)
+    float *ax_p = ax_dyn + AX_VSTAGES * AX_VT * 32;      // [G][smem_pos + 4]: a head's probabilities are contiguous, heads four banks apart
+    __shared__ double red_d[AX_VTHREADS / 32];
+    __shared__ float red_f[AX_VTHREADS / 32];
+    pdl_trigger();
+    const uint32_t kvh = blockIdx.y, d0 = blockIdx.x * 32;
+    pdl_wait();
+    const uint32_t seq = seq_dev ? *seq_dev : seq_len;
+    const uint32_t n_tiles = (seq + AX_VT - 1) / AX_VT;
+    // V tiles: a position's 32-dim slice is 128 contiguous bytes (64 for an f16 cache): 16-byte asynchronous copies,
+    // the first tiles are requested before the softmax so that they land while it runs
+#pragma unroll
+    for (int i = 0; i < AX_VSTAGES; ++i)
+        ax_stage_tile(i, n_tiles, seq, kv_f16 ? 4 : 8, vt, vc, (size_t)n_kv * hd, (size_t)kvh * hd + d0, kv_f16, threadIdx.x);
+    ax_softmax_chain_emit(ws, pw, ld, vc, kv_f16, seq, n_kv, G, hd, smem_pos, kvh, d0, vt, ax_p, red_d, red_f, false, out, scales, quants,
+                          sums, tp);
+}
+
+// ONE launch for contexts whose scores fit shared memory: the hd / 32 CTAs of a KV head are a thread-block cluster.
+// CTA r computes the scores of the r-th share of the positions (a half-warp per (position, head) as above, four
+// positions in flight per warp) and stores each into the score table of EVERY CTA of the cluster (distributed shared
+// memory); after one cluster barrier each CTA runs the softmax on its own copy and the value chains of its 32 dims.
+// grid = n_kv * CL CTAs (CL = hd / 32), AX_VTHREADS threads; dynamic shared memory: V tiles, score table, G * hd floats of q.
+template <int HD>
+__global__ void __launch_bounds__(AX_VTHREADS)
+attn_fused_exact_kernel(const float *__restrict__ q, const void *__restrict__ kc, const void *__restrict__ vc, int kv_f16, uint32_t seq_len,
+                        const uint32_t *__restrict__ seq_dev, uint32_t n_kv, uint32_t G, float scale, uint32_t smem_pos,
+                        float *__restrict__ out, float *scales, int8_t *quants, int16_t *sums, const TpHook tp) {
+    extern __shared__ __align__(16) float ax_dyn[];
+    constexpr uint32_t CL = HD / 32, NK = HD / 16;       // cluster size; K elements per lane of a half-warp
+    float *vt = ax_dyn;
+    float *ax_p = ax_dyn + AX_VSTAGES * AX_VT * 32;      // [G][smem_pos + 4]
+    const uint32_t pstride = smem_pos + 4;
+    float *ax_q = ax_p + (size_t)G * pstride;            // [G][HD]
+    __shared__ double red_d[AX_VTHREADS / 32];
+    __shared__ float red_f[AX_VTHREADS / 32];
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t r = cluster.block_rank(), kvh = blockIdx.x / CL, d0 = r * 32;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // a CTA's shared memory may be written by its peers only once it runs: every CTA arrives here, and waits for the
+    // others just before its first remote store
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t seq = seq_dev ? *seq_dev : seq_len;
+    const uint32_t n_tiles = (seq + AX_VT - 1) / AX_VT;
+#pragma unroll
+    for (int i = 0; i < AX_VSTAGES; ++i)
+        ax_stage_tile(i, n_tiles, seq, kv_f16 ? 4 : 8, vt, vc, (size_t)n_kv * HD, (size_t)kvh * HD + d0, kv_f16, tid);
+    for (uint32_t i = tid; i < G * HD; i += AX_VTHREADS) ax_q[i] = q[(size_t)kvh * G * HD + i];
+    __syncthreads();
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    // ---- scores of this CTA's share of the positions, into every CTA's table
+    {
+        const uint32_t share = (seq + CL - 1) / CL, t_begin = r * share, t_end = min(seq, t_begin + share);
+        const uint32_t c16 = lane & 15, hsel = lane >> 4;
+        float *peer_p = cluster.map_shared_rank(ax_p, c16 < CL ? c16 : 0);  // lane c of a half-warp stores into CTA c's table
+        const size_t kv_dim = (size_t)n_kv * HD;
+        constexpr uint32_t UN = 4;  // positions in flight per warp
+        for (uint32_t t0 = t_begin + warp * UN; t0 < t_end; t0 += (AX_VTHREADS / 32) * UN) {
+            // lane c16 = 8a + L holds elements 16j + c16 of each K row (chunk 2j + a of the reference's alternating accumulators)
+            float kv[UN][NK];
+#pragma unroll
+            for (uint32_t u = 0; u < UN; ++u) {
+                const uint32_t t = min(t0 + u, t_end - 1);
+                const size_t row = (size_t)t * kv_dim + (size_t)kvh * HD;
+#pragma unroll
+                for (uint32_t j = 0; j < NK; ++j) {
+                    const size_t e = row + 16 * j + c16;
+                    kv[u][j] = kv_f16 ? __half2float(__ldg(reinterpret_cast<const __half *>(kc) + e)) : __ldg(reinterpret_cast<const float *>(kc) + e);
+                }
+            }
+            for (uint32_t h0 = 0; h0 < G; h0 += 2) {
+                const uint32_t h = h0 + hsel;
+                const bool live = h < G;
+                const float *qh = ax_q + (live ? h : 0) * HD;
+                float qv[NK];
+#pragma unroll
+                for (uint32_t j = 0; j < NK; ++j) qv[j] = qh[16 * j + c16];
+#pragma unroll
+                for (uint32_t u = 0; u < UN; ++u) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (uint32_t j = 0; j < NK; ++j) acc = fmaf(qv[j], kv[u][j], acc);
+                    // accumulators 0 and 1 of the same lane L, then hsum256
+                    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
+                    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+                    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+                    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+                    const float sc = __fmul_rn(acc, scale);
+                    if (live && c16 < CL && t0 + u < t_end) peer_p[(size_t)h * pstride + t0 + u] = sc;
+                }
+            }
+        }
+    }
+    cluster.sync();  // every CTA's table is complete; nothing remote is touched after this point
+    ax_softmax_chain_emit(nullptr, nullptr, 0, vc, kv_f16, seq, n_kv, G, HD, smem_pos, kvh, d0, vt, ax_p, red_d, red_f, true, out, scales,
+                          quants, sums, tp);
+}
+
+constexpr size_t AX_SMEM_MAX = 226 * 1024;  // dynamic shared memory the values / fused kernels may ask for
+
+template <int HD>
+int32_t launch_fused(uint32_t cl, size_t smem, cudaStream_t st, const float *q, const void *kc, const void *vc, int kv_f16, uint32_t seq_len,
+                     const uint32_t *seq_dev, uint32_t nkv, uint32_t G, float scale, uint32_t fpos, float *out, float *scales,
+                     int8_t *quants, int16_t *sums, const TpHook &tp) {
+    static thread_local int raised_dev = -1;  // per head size: opt in to more than 48 KB once per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (raised_dev != dev) {
+        CERA_CUDA_TRY(cudaFuncSetAttribute(attn_fused_exact_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AX_SMEM_MAX));
+        raised_dev = dev;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(nkv * cl);
+    cfg.blockDim = dim3(AX_VTHREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cl;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    count_launch();
+    return check_cuda(cudaLaunchKernelEx(&cfg, attn_fused_exact_kernel<HD>, q, kc, vc, kv_f16, seq_len, seq_dev, nkv, G, scale, fpos, out, scales,
+                                         quants, sums, tp),
+                      "attention (fused) launch");
+}
+
 // CERA_CUDA_ATTN=flash (or any of the split-kernel selectors) keeps decode attention on the online-softmax kernels.
 bool exact_off() {
     static const bool v = [] {
@@ -326,6 +461,21 @@ int32_t launch_decode_attention_exact(const float *q, const void *kc, const void
     if (reach > cap) reach = cap;
     if (seq_len > reach) return fail(CERA_CUDA_ERR_BAD_ARG, "decode_attention: plan 0x%x does not cover %zu positions", plan, seq_len);
     float *ws = (float *)workspace, *pw = ws + n_heads * (size_t)ld;
+    // ---- one launch when the scores fit shared memory (CERA_CUDA_ATTN_EXACT=split keeps the two-kernel form)
+    static const bool no_fused = [] { const char *e = getenv("CERA_CUDA_ATTN_EXACT"); return e && strcmp(e, "split") == 0; }();
+    if (!no_fused && b == 1 && (hd == 64 || hd == 128 || hd == 256)) {  // up to 1024 positions (measured: 12.7 against 14.3 us at 512, slower than the pair at 4096)
+        const uint32_t fpos = (uint32_t)reach;
+        const size_t fsmem = ((size_t)AX_VSTAGES * AX_VT * 32 + ((size_t)fpos + 4) * G + (size_t)G * hd) * sizeof(float);
+        if (fsmem <= AX_SMEM_MAX) {
+            const uint32_t cl = hd / 32;
+            const TpHook hook = tp ? *tp : TpHook{};
+            if (hd == 64)
+                return launch_fused<64>(cl, fsmem, st, q, kc, vc, kv_f16, (uint32_t)seq_len, seq_len_dev, nkv, G, scale, fpos, out, scales, quants, sums, hook);
+            if (hd == 128)
+                return launch_fused<128>(cl, fsmem, st, q, kc, vc, kv_f16, (uint32_t)seq_len, seq_len_dev, nkv, G, scale, fpos, out, scales, quants, sums, hook);
+            return launch_fused<256>(cl, fsmem, st, q, kc, vc, kv_f16, (uint32_t)seq_len, seq_len_dev, nkv, G, scale, fpos, out, scales, quants, sums, hook);
+        }
+    }
     // scores: a fixed number of CTAs per KV head walks the position tiles, so one captured launch serves every length
     const uint32_t tiles = (uint32_t)((reach + AX_SWARPS - 1) / AX_SWARPS);
     uint32_t per_head = (uint32_t)(4 * sm_count() / (int)nkv);
@@ -338,7 +488,6 @@ int32_t launch_decode_attention_exact(const float *q, const void *kc, const void
     if (hd == 128) CERA_CUDA_TRY(launch_k(attn_scores_exact_kernel<128>, sgrid, sblock, sq, st, q, kc, kv_f16, sl32, seq_len_dev, nkv, G, hd, scale, ws, ld));
     else if (hd == 64) CERA_CUDA_TRY(launch_k(attn_scores_exact_kernel<64>, sgrid, sblock, sq, st, q, kc, kv_f16, sl32, seq_len_dev, nkv, G, hd, scale, ws, ld));
     else CERA_CUDA_TRY(launch_k(attn_scores_exact_kernel<0>, sgrid, sblock, sq, st, q, kc, kv_f16, sl32, seq_len_dev, nkv, G, hd, scale, ws, ld));
-    constexpr size_t AX_SMEM_MAX = 226 * 1024;  // dynamic shared memory the values kernel may ask for
     uint32_t smem_pos = b >= 5 ? 0u : (uint32_t)reach;
     if (((size_t)AX_VSTAGES * AX_VT * 32 + ((size_t)smem_pos + 4) * G) * sizeof(float) > AX_SMEM_MAX) smem_pos = 0;  // probabilities through global memory
     const size_t smem = ((size_t)AX_VSTAGES * AX_VT * 32 + ((size_t)smem_pos + 4) * G) * sizeof(float);

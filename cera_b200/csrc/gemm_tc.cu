@@ -205,7 +205,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
         // ---------------------------------------------------------------- weight operand: thread = weight row
         const uint32_t r = tid - 32;
         const uint32_t row = min(row0 + r, p.m - 1);  // rows past the edge repeat the last one; their results are not stored
-        // the raw bytes of an iteration are fetched one iteration ahead of their conversion (global latency ~ one conversion)
         struct RawW {
             uint4 piece[4], h, hb0, hb1;
         };
@@ -223,11 +222,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
             }
             return rw;
         };
-        RawW nxt = fetch(0);
+        // (fetching an iteration ahead of the conversion was measured: no gain, and its 28 live registers spill)
         for (uint32_t it = 0; it < n_it; ++it) {
             const uint32_t s = it % TC_STAGES;
-            const RawW cur = nxt;
-            if (it + 1 < n_it) nxt = fetch(it + 1);
+            const RawW cur = fetch(it);
             const uint4 (&piece)[4] = cur.piece;
             const uint4 h = cur.h, hb0 = cur.hb0, hb1 = cur.hb1;
             if (!tma::mbar_wait_blocking(empty_ab + s, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 4u)) break;
@@ -307,7 +305,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
             rx.sm = __ldg(reinterpret_cast<const uint4 *>(p.x.sums + (size_t)token * nb16 + it * 8));
             return rx;
         };
-        RawX nxt = fetch(0);
         // g: a power of two that brings every xs_b * A_b of the token below 2^15, so that its f16 high / low parts keep
         // 22 significant bits whatever the magnitude of the activations
         float g = 1.0f;
@@ -333,8 +330,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
         }
         for (uint32_t it = 0; it < n_it; ++it) {
             const uint32_t s = it % TC_STAGES;
-            const RawX cur = nxt;
-            if (it + 1 < n_it) nxt = fetch(it + 1);
+            const RawX cur = fetch(it);  // (a register prefetch of the next stage spills at 72 registers: measured no faster)
             const uint4 (&raw)[8] = cur.v;
             if (!tma::mbar_wait_blocking(empty_ab + s, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) break;
             uint8_t *opa = tc_smem + s * TC_STAGE_BYTES;

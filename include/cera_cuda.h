@@ -152,6 +152,13 @@ CERA_API int32_t cera_cuda_rope(float *q_dev, float *k_dev, size_t pos, size_t n
 /* IEEE half bits (kv_f16 = 1), as cera/src/kv_cache.rs:201-221 keeps them.    */
 /* One query token attends to rows [0, seq_len).  workspace_dev must hold      */
 /* cera_cuda_decode_attention_workspace_bytes(...) bytes.                      */
+/* Shapes: n_heads a multiple of n_kv_heads with at most 8 query heads per KV   */
+/* head, head_dim a multiple of 32 up to 256: the result is then evaluated in   */
+/* the reference's own f32 order (scores, plain softmax over all positions,     */
+/* position-ordered value sums) and is bit-identical to it.  With the           */
+/* environment variable CERA_CUDA_ATTN set the online-softmax kernels run       */
+/* instead (groups of 4 or 8, head_dim 64 or 128; agreement within 1e-3         */
+/* relative).  Any other shape: CERA_CUDA_ERR_UNSUPPORTED.                      */
 CERA_API size_t cera_cuda_decode_attention_workspace_bytes(size_t n_heads, size_t head_dim,
                                                           size_t seq_len);
 CERA_API int32_t cera_cuda_decode_attention(const float *q_dev, const void *k_cache_dev,
