@@ -548,6 +548,8 @@ def cuda_arm(args, rank, world):
         }
     model.close()
     if rank == 0:
+        if world == 1 and not args.no_alt:
+            out["toleranced_kernels"] = toleranced_leg(args, decoded)
         if world == 1 and not args.no_cpu:
             threads = os.cpu_count() or 1
             r = cpu_token_bench(6, 2, threads)
@@ -562,6 +564,27 @@ def cuda_arm(args, rank, world):
         dist.destroy_process_group()
 
 
+def toleranced_leg(args, exact_stream):
+    """The same benchmark in a child process with the decode kernels that sum in their own order (the register-streaming
+    GEMV and the online-softmax attention; selected by environment variables the library reads once per process): what
+    the reference's bit pattern costs.  Reported beside the headline, never as it: that stream is allowed to leave the
+    reference's at a near-tie."""
+    env = dict(os.environ, CERA_CUDA_GEMV="rows", CERA_CUDA_ATTN="flash")
+    cmd = [sys.executable, os.path.abspath(__file__), "--steps", str(args.steps), "--warmup", str(args.warmup), "--seed", str(args.seed),
+           "--prompt-len", str(args.prompt_len), "--no-cpu", "--no-alt", "--no-stream-check", "--iters", "8"]
+    try:
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+        line = [l for l in r.stdout.splitlines() if l.startswith("{")][-1]
+        d = json.loads(line)
+        sc = d.get("stream_check") or {}
+        return {"value": d["value"], "unit": UNIT, "ms_per_step": d["ms_per_step"], "e2e": d["e2e"]["value"],
+                "env": "CERA_CUDA_GEMV=rows CERA_CUDA_ATTN=flash",
+                "stream_tokens_matching_reference": sc.get("matched"), "stream_tokens_compared": sc.get("compared"),
+                "note": "kernels with their own f32 summation order (1e-3 relative per operator); not the headline"}
+    except Exception as e:  # the leg is informational: never fail the run for it
+        return {"error": f"{type(e).__name__}: {e}"[:200]}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -572,6 +595,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
                     help="prompt tokens before the timed decode (512 is the benchmark; shorter only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-alt", action="store_true", help="skip the leg that re-runs the benchmark on the toleranced decode kernels")
     ap.add_argument("--no-stream-check", action="store_true", help="report a stream that differs from the reference's instead of failing")
     ap.add_argument("--only", default=None, choices=["roofline", "gemv-sweep", "gemm-sweep", "moe", "attn-sweep"],
                     help="run just the dominant-kernel microbench (the case ncu captures are taken on)")
