@@ -40,7 +40,7 @@ namespace cera {
 
 namespace {
 
-constexpr int AX_VTHREADS = 256;   // threads of the values kernel
+constexpr int AX_VTHREADS = 512;   // threads of the values and fused kernels
 
 // One HALF-WARP per (position, query head): its sixteen lanes are the reference's sixteen FMA chains (accumulator a,
 // lane L) - lane c = 8a + L multiplies elements 16j + c of the head for j = 0, 1, ... - and four xor-shuffle steps add
@@ -105,32 +105,53 @@ __device__ __forceinline__ void ax_wait() { asm volatile("cp.async.wait_group %0
 
 constexpr int AX_VT = 256;     // positions per staged V tile
 constexpr int AX_VSTAGES = 3;  // tiles in the ring (two in flight while one is walked)
-constexpr int AX_VTHREADS_C = 256;
+constexpr int AX_VTHREADS_C = AX_VTHREADS;
 
 // AX_VT positions (or fewer) of one lane's chain: out = fma(p[t], V[t][d], out) in position order.  `base`: the tile,
 // one row of 32 dims per position; pp: the head's probabilities from this tile's first position on, 16-byte aligned.
 template <bool F16>
-__device__ __forceinline__ float ax_chain_tile(const char *base, const float *__restrict__ pp, uint32_t cnt, uint32_t d, float acc) {
+__device__ __forceinline__ float ax_chain_tile(const char *base, const float *__restrict__ pp, uint32_t cnt, uint32_t d, float inv, float acc) {
     auto v_at = [&](uint32_t i) -> float {
         if (F16) return __half2float(*reinterpret_cast<const __half *>(base + (size_t)i * 64 + d * 2));
         return *reinterpret_cast<const float *>(base + (size_t)i * 128 + d * 4);
     };
     uint32_t i = 0;
-#pragma unroll 2
-    for (; i + 8 <= cnt; i += 8) {  // eight positions per step: two 128-bit loads of probabilities, eight values
-        const float4 pa = *reinterpret_cast<const float4 *>(pp + i), pb = *reinterpret_cast<const float4 *>(pp + i + 4);
-        const float v0 = v_at(i), v1 = v_at(i + 1), v2 = v_at(i + 2), v3 = v_at(i + 3);
-        const float v4 = v_at(i + 4), v5 = v_at(i + 5), v6 = v_at(i + 6), v7 = v_at(i + 7);
-        acc = fmaf(pa.x, v0, acc);
-        acc = fmaf(pa.y, v1, acc);
-        acc = fmaf(pa.z, v2, acc);
-        acc = fmaf(pa.w, v3, acc);
-        acc = fmaf(pb.x, v4, acc);
-        acc = fmaf(pb.y, v5, acc);
-        acc = fmaf(pb.z, v6, acc);
-        acc = fmaf(pb.w, v7, acc);
+    // eight positions per step (two 128-bit loads of probabilities, eight values), fetched one step ahead of their FMAs:
+    // the chain is a dependent FMA per position, the loads must never be what it waits for
+    if (cnt >= 8) {
+        float4 pa = *reinterpret_cast<const float4 *>(pp), pb = *reinterpret_cast<const float4 *>(pp + 4);
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = v_at(j);
+        for (; i + 16 <= cnt; i += 8) {
+            const float4 na = *reinterpret_cast<const float4 *>(pp + i + 8), nb = *reinterpret_cast<const float4 *>(pp + i + 12);
+            float nv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) nv[j] = v_at(i + 8 + j);
+            acc = fmaf(__fmul_rn(pa.x, inv), v[0], acc);
+            acc = fmaf(__fmul_rn(pa.y, inv), v[1], acc);
+            acc = fmaf(__fmul_rn(pa.z, inv), v[2], acc);
+            acc = fmaf(__fmul_rn(pa.w, inv), v[3], acc);
+            acc = fmaf(__fmul_rn(pb.x, inv), v[4], acc);
+            acc = fmaf(__fmul_rn(pb.y, inv), v[5], acc);
+            acc = fmaf(__fmul_rn(pb.z, inv), v[6], acc);
+            acc = fmaf(__fmul_rn(pb.w, inv), v[7], acc);
+            pa = na;
+            pb = nb;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = nv[j];
+        }
+        acc = fmaf(__fmul_rn(pa.x, inv), v[0], acc);
+        acc = fmaf(__fmul_rn(pa.y, inv), v[1], acc);
+        acc = fmaf(__fmul_rn(pa.z, inv), v[2], acc);
+        acc = fmaf(__fmul_rn(pa.w, inv), v[3], acc);
+        acc = fmaf(__fmul_rn(pb.x, inv), v[4], acc);
+        acc = fmaf(__fmul_rn(pb.y, inv), v[5], acc);
+        acc = fmaf(__fmul_rn(pb.z, inv), v[6], acc);
+        acc = fmaf(__fmul_rn(pb.w, inv), v[7], acc);
+        i += 8;
     }
-    for (; i < cnt; ++i) acc = fmaf(pp[i], v_at(i), acc);
+    for (; i < cnt; ++i) acc = fmaf(__fmul_rn(pp[i], inv), v_at(i), acc);
     return acc;
 }
 
@@ -160,7 +181,7 @@ __device__ __forceinline__ void ax_stage_tile(uint32_t tile, uint32_t n_tiles, u
 // kernel); otherwise they are read from ws.
 __device__ __forceinline__ void ax_softmax_chain_emit(const float *__restrict__ ws, float *__restrict__ pw, uint32_t ld, const void *__restrict__ vc,
                                                       int kv_f16, uint32_t seq, uint32_t n_kv, uint32_t G, uint32_t hd, uint32_t smem_pos,
-                                                      uint32_t kvh, uint32_t d0, float *vt, float *ax_p, double *red_d, float *red_f,
+                                                      uint32_t kvh, uint32_t d0, float *vt, float *ax_p, double *red_d, float *red_f, float *inv_h,
                                                       bool scores_in_smem, float *__restrict__ out, float *scales, int8_t *quants,
                                                       int16_t *sums, const TpHook &tp) {
     const uint32_t pstride = smem_pos + 4;
@@ -178,7 +199,8 @@ __device__ __forceinline__ void ax_softmax_chain_emit(const float *__restrict__ 
     float *p_row = pw + (size_t)(kvh * G + (has_head ? h_mine : 0)) * ld;
     float mx = -INFINITY;
     if (has_head) {
-        for (uint32_t t = hti; t < seq; t += hth) {
+#pragma unroll 4
+        for (uint32_t t = hti; t < seq; t += hth) {  // (unrolled: the loads of four steps are in flight together)
             const float v = scores_in_smem ? ax_p[(size_t)h_mine * pstride + t] : s_row[t];
             if (in_smem && !scores_in_smem) ax_p[(size_t)h_mine * pstride + t] = v;
             mx = fmaxf(mx, v);  // f32::max fold: NaN scores are ignored
@@ -195,9 +217,11 @@ __device__ __forceinline__ void ax_softmax_chain_emit(const float *__restrict__ 
     // exponentials and their f64 sum (fixed tree: thread-strided partials, xor shuffles, the head's warps in index order)
     double sum = 0.0;
     if (has_head) {
+#pragma unroll 4
         for (uint32_t t = hti; t < seq; t += hth) {
             const float e = ggml_expf(__fsub_rn(in_smem ? ax_p[(size_t)h_mine * pstride + t] : s_row[t], mx));
             if (in_smem) ax_p[(size_t)h_mine * pstride + t] = e;
+            else p_row[t] = e;  // every CTA of the KV head stores the same value; the chain multiplies by 1 / sum
             sum += (double)e;
         }
     }
@@ -209,17 +233,39 @@ __device__ __forceinline__ void ax_softmax_chain_emit(const float *__restrict__ 
         double tot = red_d[h_mine * nwh];
         for (uint32_t w = 1; w < nwh; ++w) tot += red_d[h_mine * nwh + w];
         const float inv = (float)(1.0 / tot);
-        for (uint32_t t = hti; t < seq; t += hth) {
-            if (in_smem) ax_p[(size_t)h_mine * pstride + t] = __fmul_rn(ax_p[(size_t)h_mine * pstride + t], inv);
-            else p_row[t] = __fmul_rn(ggml_expf(__fsub_rn(s_row[t], mx)), inv);  // recomputed: the CTAs of a KV head all store the same value
+        if (wl == 0 && lane == 0) inv_h[h_mine] = inv;
+        if (in_smem) {
+#pragma unroll 4
+            for (uint32_t t = hti; t < seq; t += hth) ax_p[(size_t)h_mine * pstride + t] = __fmul_rn(ax_p[(size_t)h_mine * pstride + t], inv);
         }
     }
     // (the first barrier of the tile loop below also publishes the probabilities)
+    // Probabilities that went through global memory come back tile by tile, by asynchronous copies into a ring beside
+    // the V tiles (a chain that read them with global loads spent its time on their latency): tiles 0-2 as groups of
+    // their own here, later ones in the group of the V tile they belong to.
+    float *pt = ax_p;  // [AX_VSTAGES][G][AX_VT], in place of the (unused) probability table
+    auto stage_p = [&](uint32_t tile) {
+        if (tile < n_tiles) {
+            const uint32_t t0 = tile * AX_VT, pieces = (min((uint32_t)AX_VT, seq - t0) + 3) / 4;
+            float *dst = pt + (size_t)(tile % AX_VSTAGES) * G * AX_VT;
+            for (uint32_t i = tid; i < G * (AX_VT / 4); i += AX_VTHREADS_C) {
+                const uint32_t hh = i / (AX_VT / 4), pc = i % (AX_VT / 4);
+                if (pc < pieces) ax_cp16(dst + (size_t)hh * AX_VT + pc * 4, pw + (size_t)(kvh * G + hh) * ld + t0 + pc * 4);
+            }
+        }
+    };
+    if (!in_smem) {
+        __syncthreads();  // every thread's probabilities are written
+#pragma unroll
+        for (int i = 0; i < AX_VSTAGES; ++i) {
+            stage_p(i);
+            ax_commit();
+        }
+    }
 
     // ---- out[d] = fma(p[t], V[t][d], out[d]) in position order: warp h walks head h, a lane per output dim
     const bool chain = (uint32_t)warp < G;
     const uint32_t h = warp, d = lane;
-    const float *pg = pw + (size_t)(kvh * G + (chain ? h : 0)) * ld;
     float acc = 0.0f;
     for (uint32_t tile = 0; tile < n_tiles; ++tile) {
         // this thread's copies of tile `tile` have landed: tiles 0-2 were committed up front, tile j + 2 in iteration j,
@@ -227,14 +273,21 @@ __device__ __forceinline__ void ax_softmax_chain_emit(const float *__restrict__ 
         if (tile == 0) ax_wait<2>();
         else ax_wait<1>();
         __syncthreads();  // everyone's have; and every chain warp is done with the slot restaged below
-        if (tile > 0) ax_stage_tile(tile - 1 + AX_VSTAGES, n_tiles, seq, per_pos, vt, vc, kv_dim, (size_t)kvh * hd + d0, kv_f16, tid);
+        if (tile > 0) {
+            if (!in_smem) stage_p(tile - 1 + AX_VSTAGES);  // joins the commit group of the V tile below
+            ax_stage_tile(tile - 1 + AX_VSTAGES, n_tiles, seq, per_pos, vt, vc, kv_dim, (size_t)kvh * hd + d0, kv_f16, tid);
+        }
         if (chain) {
             const uint32_t t0 = tile * AX_VT, cnt = min((uint32_t)AX_VT, seq - t0);
             const char *base = reinterpret_cast<const char *>(vt + (size_t)(tile % AX_VSTAGES) * AX_VT * 32);
             // separate instantiations so that shared-memory probabilities are read with shared loads, not generic ones
-            if (in_smem) acc = kv_f16 ? ax_chain_tile<true>(base, ax_p + (size_t)h * pstride + t0, cnt, d, acc)
-                                      : ax_chain_tile<false>(base, ax_p + (size_t)h * pstride + t0, cnt, d, acc);
-            else acc = kv_f16 ? ax_chain_tile<true>(base, pg + t0, cnt, d, acc) : ax_chain_tile<false>(base, pg + t0, cnt, d, acc);
+            if (in_smem) acc = kv_f16 ? ax_chain_tile<true>(base, ax_p + (size_t)h * pstride + t0, cnt, d, 1.0f, acc)
+                                      : ax_chain_tile<false>(base, ax_p + (size_t)h * pstride + t0, cnt, d, 1.0f, acc);
+            else {
+                const float *pp = pt + (size_t)(tile % AX_VSTAGES) * G * AX_VT + (size_t)h * AX_VT;
+                const float inv = inv_h[h];  // the staged values are the exponentials: p = e * (1 / sum), rounded, as the reference stores it
+                acc = kv_f16 ? ax_chain_tile<true>(base, pp, cnt, d, inv, acc) : ax_chain_tile<false>(base, pp, cnt, d, inv, acc);
+            }
         }
     }
     ax_wait<0>();
@@ -284,17 +337,21 @@ attn_values_exact_kernel(const float *__restrict__ ws, float *__restrict__ pw, u
     float *ax_p = ax_dyn + AX_VSTAGES * AX_VT * 32;      // [G][smem_pos + 4]: a head's probabilities are contiguous, heads four banks apart
     __shared__ double red_d[AX_VTHREADS / 32];
     __shared__ float red_f[AX_VTHREADS / 32];
+    __shared__ float inv_h[8];  // 1 / sum of every head of the group
     pdl_trigger();
     const uint32_t kvh = blockIdx.y, d0 = blockIdx.x * 32;
     pdl_wait();
-    const uint32_t seq = seq_dev ? *seq_dev : seq_len;
+    uint32_t seq = seq_dev ? *seq_dev : seq_len;
+    // a launch planned with a probability table serves lengths up to the table (the host checks this for lengths it knows
+    // and plans captured launches from the length they will meet); never index past it
+    if (smem_pos && seq > smem_pos) seq = smem_pos;
     const uint32_t n_tiles = (seq + AX_VT - 1) / AX_VT;
     // V tiles: a position's 32-dim slice is 128 contiguous bytes (64 for an f16 cache): 16-byte asynchronous copies,
     // the first tiles are requested before the softmax so that they land while it runs
 #pragma unroll
     for (int i = 0; i < AX_VSTAGES; ++i)
         ax_stage_tile(i, n_tiles, seq, kv_f16 ? 4 : 8, vt, vc, (size_t)n_kv * hd, (size_t)kvh * hd + d0, kv_f16, threadIdx.x);
-    ax_softmax_chain_emit(ws, pw, ld, vc, kv_f16, seq, n_kv, G, hd, smem_pos, kvh, d0, vt, ax_p, red_d, red_f, false, out, scales, quants,
+    ax_softmax_chain_emit(ws, pw, ld, vc, kv_f16, seq, n_kv, G, hd, smem_pos, kvh, d0, vt, ax_p, red_d, red_f, inv_h, false, out, scales, quants,
                           sums, tp);
 }
 
@@ -316,6 +373,7 @@ attn_fused_exact_kernel(const float *__restrict__ q, const void *__restrict__ kc
     float *ax_q = ax_p + (size_t)G * pstride;            // [G][HD]
     __shared__ double red_d[AX_VTHREADS / 32];
     __shared__ float red_f[AX_VTHREADS / 32];
+    __shared__ float inv_h[8];  // 1 / sum of every head of the group
     cg::cluster_group cluster = cg::this_cluster();
     const uint32_t r = cluster.block_rank(), kvh = blockIdx.x / CL, d0 = r * 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -324,7 +382,8 @@ attn_fused_exact_kernel(const float *__restrict__ q, const void *__restrict__ kc
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     pdl_trigger();
     pdl_wait();
-    const uint32_t seq = seq_dev ? *seq_dev : seq_len;
+    uint32_t seq = seq_dev ? *seq_dev : seq_len;
+    if (seq > smem_pos) seq = smem_pos;  // the score tables hold smem_pos positions (see the values kernel)
     const uint32_t n_tiles = (seq + AX_VT - 1) / AX_VT;
 #pragma unroll
     for (int i = 0; i < AX_VSTAGES; ++i)
@@ -376,7 +435,7 @@ attn_fused_exact_kernel(const float *__restrict__ q, const void *__restrict__ kc
         }
     }
     cluster.sync();  // every CTA's table is complete; nothing remote is touched after this point
-    ax_softmax_chain_emit(nullptr, nullptr, 0, vc, kv_f16, seq, n_kv, G, HD, smem_pos, kvh, d0, vt, ax_p, red_d, red_f, true, out, scales,
+    ax_softmax_chain_emit(nullptr, nullptr, 0, vc, kv_f16, seq, n_kv, G, HD, smem_pos, kvh, d0, vt, ax_p, red_d, red_f, inv_h, true, out, scales,
                           quants, sums, tp);
 }
 
@@ -490,7 +549,8 @@ int32_t launch_decode_attention_exact(const float *q, const void *kc, const void
     else CERA_CUDA_TRY(launch_k(attn_scores_exact_kernel<0>, sgrid, sblock, sq, st, q, kc, kv_f16, sl32, seq_len_dev, nkv, G, hd, scale, ws, ld));
     uint32_t smem_pos = b >= 5 ? 0u : (uint32_t)reach;
     if (((size_t)AX_VSTAGES * AX_VT * 32 + ((size_t)smem_pos + 4) * G) * sizeof(float) > AX_SMEM_MAX) smem_pos = 0;  // probabilities through global memory
-    const size_t smem = ((size_t)AX_VSTAGES * AX_VT * 32 + ((size_t)smem_pos + 4) * G) * sizeof(float);
+    // probability table [G][smem_pos + 4], or - probabilities through global memory - a ring of probability tiles [stages][G][AX_VT]
+    const size_t smem = ((size_t)AX_VSTAGES * AX_VT * 32 + (smem_pos ? ((size_t)smem_pos + 4) * G : (size_t)AX_VSTAGES * G * AX_VT)) * sizeof(float);
     {
         // static + dynamic shared memory can pass the 48 KB default even at the shortest contexts: opt in once per device
         static thread_local int raised_dev = -1;
