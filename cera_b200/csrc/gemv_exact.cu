@@ -518,7 +518,7 @@ static bool exact_off() {
 }
 
 // Single-column GEMV in the reference's f32 order over up to three same-typed K-quant matrices.
-// *taken = false: not a K-quant, k not a multiple of 1024, or a shape outside the kernel's rules;
+// *taken = false: not a K-quant, k not a multiple of 512, or a shape outside the kernel's rules;
 // nothing was launched.
 int32_t launch_gemv_exact(const GemvSeg *segs, int n_segs, const ActView &x, int epilogue, const GemvFusion *fusion,
                           cudaStream_t st, bool *taken, const TpHook *tp) {
@@ -527,7 +527,8 @@ int32_t launch_gemv_exact(const GemvSeg *segs, int n_segs, const ActView &x, int
     const int type = segs[0].w.type;
     if (type != CERA_TYPE_Q4_K && type != CERA_TYPE_Q5_K && type != CERA_TYPE_Q6_K) return CERA_CUDA_OK;
     const uint32_t k = segs[0].w.k;
-    if (k % 1024) return CERA_CUDA_OK;
+    if (k % (128 * XG_SEG_TASKS)) return CERA_CUDA_OK;  // whole segments (512 weights)
+    if (fusion && fusion->norm_x && k % 1024) return CERA_CUDA_OK;  // the norm prologue walks 1024 virtual threads of four elements
     for (int i = 0; i < n_segs; ++i)
         if (segs[i].w.ilv != 8) return CERA_CUDA_OK;
     if (xg_cta_smem(k) + xg_warp_smem(2, 4096) > XG_SMEM_LIMIT) return CERA_CUDA_OK;

@@ -22,7 +22,7 @@ def _cuda(torch, a):
 
 
 @pytest.mark.parametrize("t", [O.Q4_K, O.Q5_K, O.Q6_K])
-@pytest.mark.parametrize("m,k", [(64, 4096), (40, 14336), (33, 1024), (1, 2048), (300, 3072)])
+@pytest.mark.parametrize("m,k", [(64, 4096), (40, 14336), (33, 1024), (1, 2048), (300, 3072), (72, 512), (96, 3584), (16, 18944)])
 def test_k_quant_gemv_bits(t, m, k):
     torch = need_gpu()
     import cera_b200 as cb
@@ -87,7 +87,7 @@ def test_decode_attention_bits(nh, nkv, hd, seq, kv_f16):
 
 @pytest.mark.parametrize("kv_f16", [0, 1])
 def test_model_logits_bit_identical_to_the_oracle(kv_f16):
-    """A llama-architecture model whose matrices are K-quants with row lengths that are multiples of 1024 runs every
+    """A llama-architecture model whose matrices are K-quants with row lengths that are multiples of 512 runs every
     projection, norm, rotation and attention on reference-order kernels: logits equal the oracle's bits at every
     position, so the greedy stream cannot differ."""
     need_gpu()
@@ -151,3 +151,40 @@ def test_granite_scalar_multipliers_bit_identical_to_the_oracle():
     assert_bits(a.forward(3, 0), b.forward(3, 0), "identity scalars")
     a.close()
     b.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,cfg_over,types", [
+    ("neox rope (qwen layout)", dict(rope_type=1), None),
+    ("one query head per KV head", dict(n_heads=8, n_kv_heads=8), None),
+    ("eight query heads per KV head, head size 64", dict(n_heads=16, n_kv_heads=2, head_dim=64), None),
+    ("three query heads per KV head, rows of 1536", dict(n_heads=12, n_kv_heads=4), None),
+    ("every matrix Q6_K", dict(), "q6_k"),
+    ("mixed Q4_K / Q6_K attention, Q6_K feed-forward", dict(), "mixed"),
+])
+def test_model_variants_bit_identical_to_the_oracle(name, cfg_over, types):
+    """The whole-model bit identity of the test above across the shapes and tensor-type mixes a llama-architecture GGUF
+    brings: NEOX rotation (stand-alone rope kernel instead of the GEMV epilogue), group sizes 1 / 3 / 8, head size 64,
+    and K-quant mixes (different types for q/k/v go through separate GEMVs)."""
+    need_gpu()
+    import cera_b200 as cb
+    from cera_b200 import synth
+    from cera_b200.model import Role
+    cfg = dict(n_layers=2, hidden_size=1024, intermediate_size=2048, n_heads=8, n_kv_heads=2, head_dim=128, vocab_size=2048,
+               rope_theta=10000.0, rms_norm_eps=1e-6, rope_type=0)
+    cfg.update(cfg_over)
+    tmap = None
+    if types == "q6_k":
+        tmap = {r: cb.Q6_K for r in (Role.TOKEN_EMBD, Role.OUTPUT, Role.ATTN_Q, Role.ATTN_K, Role.ATTN_V, Role.ATTN_OUTPUT,
+                                     Role.FFN_GATE, Role.FFN_UP, Role.FFN_DOWN)}
+    elif types == "mixed":
+        tmap = {Role.ATTN_Q: cb.Q4_K, Role.ATTN_K: cb.Q6_K, Role.ATTN_V: cb.Q6_K, Role.FFN_GATE: cb.Q6_K, Role.FFN_UP: cb.Q6_K}
+    oracle = O.OracleModel(**cfg, max_seq_len=32, kv_f16=0, n_threads=4)
+    gpu = synth.build_llama(cfg, seed=31, max_seq_len=32, types=tmap,
+                            sink=lambda r, l, t, rows, cols, d: oracle.set_tensor(int(r), l, t, rows, cols, d))
+    tok = 11
+    for pos in range(20):
+        lg, lo = gpu.forward(tok, pos), oracle.forward(tok, pos)
+        assert_bits(lg, lo, f"{name}: logits at position {pos}")
+        tok = int(O.argmax(lo))
+    gpu.close()
