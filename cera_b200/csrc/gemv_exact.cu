@@ -87,13 +87,10 @@ struct SegLayout {  // bytes of one segment buffer
     static constexpr uint32_t TX = Q + HDR + QH + D;
 };
 
-// (float)(sum of four u8 x s8 products), exactly: the dp4a accumulates onto the bits of 1.5 * 2^23.
-__device__ __forceinline__ float quad_dot(uint32_t w, int a) { return __fsub_rn(__int_as_float(dp_us(w, a, XG_MAGIC_I)), XG_MAGIC_F); }
+// (float)(sum of four u8 x s8 products), exactly: a dp4a accumulates onto the bits of 1.5 * 2^23 and that constant is
+// subtracted again (in the main loop, as packed pairs).
 __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 __device__ __forceinline__ int word_of(const int4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
-// Small unsigned integer -> float without the convert pipe: 2^23 + v as bits, minus 2^23.
-__device__ __forceinline__ float small_uint_f(uint32_t v) { return __fsub_rn(__uint_as_float(0x4B000000u | v), 8388608.0f); }
-
 // Bulk copy / barrier forms on 32-bit shared addresses that are worked out once.
 __device__ __forceinline__ void expect_tx_u32(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -289,9 +286,12 @@ __global__ void __launch_bounds__(XG_MAX_WARPS * 32) gemv_exact_kernel(const Exa
 #pragma unroll
             for (int gq = 0; gq < 4; ++gq) {
                 const float s0 = (float)(int8_t)(sw[gq >> 1] >> (16 * (gq & 1))), s1 = (float)(int8_t)(sw[gq >> 1] >> (16 * (gq & 1) + 8));
-                e[2 * gq] = __fmul_rn(__fmul_rn(s0, d6), xv[gq]);
-                e[2 * gq + 1] = __fmul_rn(__fmul_rn(s1, d6), xv[gq]);
-                tm[gq] = __fmul_rn(__fmul_rn(xv[gq], d32), __fadd_rn(__fmul_rn(s0, am[2 * gq]), __fmul_rn(s1, am[2 * gq + 1])));
+                const float2 s2 = make_float2(s0, s1), x2 = make_float2(xv[gq], xv[gq]);
+                const float2 ee = __fmul2_rn(__fmul2_rn(s2, make_float2(d6, d6)), x2);                  // (s * d) * xs, both halves
+                const float2 pa = __fmul2_rn(s2, make_float2(am[2 * gq], am[2 * gq + 1]));              // s0 * A0, s1 * A1
+                e[2 * gq] = ee.x;
+                e[2 * gq + 1] = ee.y;
+                tm[gq] = __fmul_rn(__fmul_rn(xv[gq], d32), __fadd_rn(pa.x, pa.y));
             }
             // strip c = (pair, half) multiplies block `pair` (low nibbles) and block `pair + 2` (high), half `half`
             float4 *dst = reinterpret_cast<float4 *>(sct + (pi * 8 + pr) * 8);
@@ -303,11 +303,20 @@ __global__ void __launch_bounds__(XG_MAX_WARPS * 32) gemv_exact_kernel(const Exa
             const float d = h2f((uint16_t)(h.x & 0xFFFF)), dmin = h2f((uint16_t)(h.x >> 16));
             const float4 a4 = *reinterpret_cast<const float4 *>(a32 + 4 * t);
             const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+            // the same products as packed pairs (mul.f32x2 / add.f32x2: each half is the scalar IEEE operation)
             float e[4];
+            const float2 nb23 = make_float2(-8388608.0f, -8388608.0f), d2 = make_float2(d, d), dm2 = make_float2(dmin, dmin);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                e[j] = __fmul_rn(xv[j], __fmul_rn(d, small_uint_f((scp >> (8 * j)) & 0xFF)));
-                tm[j] = __fmul_rn(__fmul_rn(xv[j], __fmul_rn(dmin, small_uint_f((mnp >> (8 * j)) & 0xFF))), av[j]);
+            for (int jp = 0; jp < 2; ++jp) {
+                const float2 x2 = make_float2(xv[2 * jp], xv[2 * jp + 1]), a2 = make_float2(av[2 * jp], av[2 * jp + 1]);
+                const float2 scf = __fadd2_rn(make_float2(__uint_as_float(0x4B000000u | ((scp >> (16 * jp)) & 0xFF)),
+                                                          __uint_as_float(0x4B000000u | ((scp >> (16 * jp + 8)) & 0xFF))), nb23);
+                const float2 mnf = __fadd2_rn(make_float2(__uint_as_float(0x4B000000u | ((mnp >> (16 * jp)) & 0xFF)),
+                                                          __uint_as_float(0x4B000000u | ((mnp >> (16 * jp + 8)) & 0xFF))), nb23);
+                const float2 ee = __fmul2_rn(x2, __fmul2_rn(d2, scf));
+                const float2 tt = __fmul2_rn(__fmul2_rn(x2, __fmul2_rn(dm2, mnf)), a2);
+                e[2 * jp] = ee.x, e[2 * jp + 1] = ee.y;
+                tm[2 * jp] = tt.x, tm[2 * jp + 1] = tt.y;
             }
             *reinterpret_cast<float4 *>(sct + (pi * 8 + pr) * 4) = make_float4(e[0], e[1], e[2], e[3]);
         }
@@ -322,7 +331,7 @@ __global__ void __launch_bounds__(XG_MAX_WARPS * 32) gemv_exact_kernel(const Exa
     }
     uint32_t item = 0;
     for (uint32_t g = first; g < n_groups; g += step) {
-        float acc_lo[4] = {0.0f, 0.0f, 0.0f, 0.0f}, acc_hi[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float2 acc_lo2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)}, acc_hi2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
         float macc = 0.0f;  // every lane of a row carries the row's macc chain (the same adds in the same order)
         for (uint32_t seg = 0; seg < n_seg; ++seg, ++item) {
             const uint8_t *buf = ring + (size_t)(item & s_mask) * L::BYTES;
@@ -369,16 +378,17 @@ __global__ void __launch_bounds__(XG_MAX_WARPS * 32) gemv_exact_kernel(const Exa
                             hi[wd] |= ((hbw >> (2 * pair + 4)) & 0x03030303u) << 4;
                         }
                     }
-                    float ql[4], qh[4];
+                    // the subtraction of the bias and the FMA run as packed pairs (add.f32x2 / fma.f32x2: each half is the
+                    // IEEE operation of the scalar form, two chains per instruction)
+                    const float2 nbias = make_float2(-XG_MAGIC_F, -XG_MAGIC_F), s_lo = make_float2(sc2.x, sc2.x), s_hi = make_float2(sc2.y, sc2.y);
 #pragma unroll
-                    for (int wd = 0; wd < 4; ++wd) {
-                        ql[wd] = quad_dot(lo[wd], word_of(alo, wd));
-                        qh[wd] = quad_dot(hi[wd], word_of(ahi, wd));
-                    }
-#pragma unroll
-                    for (int wd = 0; wd < 4; ++wd) {
-                        acc_lo[wd] = fmaf(ql[wd], sc2.x, acc_lo[wd]);
-                        acc_hi[wd] = fmaf(qh[wd], sc2.y, acc_hi[wd]);
+                    for (int wp = 0; wp < 2; ++wp) {
+                        const float2 rl = make_float2(__int_as_float(dp_us(lo[2 * wp], word_of(alo, 2 * wp), XG_MAGIC_I)),
+                                                      __int_as_float(dp_us(lo[2 * wp + 1], word_of(alo, 2 * wp + 1), XG_MAGIC_I)));
+                        const float2 rh = make_float2(__int_as_float(dp_us(hi[2 * wp], word_of(ahi, 2 * wp), XG_MAGIC_I)),
+                                                      __int_as_float(dp_us(hi[2 * wp + 1], word_of(ahi, 2 * wp + 1), XG_MAGIC_I)));
+                        acc_lo2[wp] = __ffma2_rn(__fadd2_rn(rl, nbias), s_lo, acc_lo2[wp]);
+                        acc_hi2[wp] = __ffma2_rn(__fadd2_rn(rh, nbias), s_hi, acc_hi2[wp]);
                     }
                 }
                 // ---- the next segment's scale pass, one segment ahead of its use (it has its own table and term buffer)
@@ -395,6 +405,7 @@ __global__ void __launch_bounds__(XG_MAX_WARPS * 32) gemv_exact_kernel(const Exa
             }
         }
         // ---- the 32 chains of the row -> one value (tree over the accumulators, then the hsum256 order)
+        const float acc_lo[4] = {acc_lo2[0].x, acc_lo2[0].y, acc_lo2[1].x, acc_lo2[1].y}, acc_hi[4] = {acc_hi2[0].x, acc_hi2[0].y, acc_hi2[1].x, acc_hi2[1].y};
         float f[4];
         if (T == CERA_TYPE_Q6_K) {
             // lane (pair, half): acc_lo = accumulator `pair`, acc_hi = accumulator `pair + 2`
