@@ -18,8 +18,13 @@ token ids.  One JSON line goes to stdout.
   roofline : the dominant kernel (Q4_K GEMV at the 14336 x 4096 gate/up shape)
           timed alone with CUDA events, rotating over distinct weight copies
           larger than L2, against the measured HBM copy bandwidth.
-  cpu_baseline : the AVX2 restatement of the reference's int8 GEMV kernels on
-          this box's host cores, on a bounded sample of the same token.
+  stream_check : every decoded token against the committed CPU reference stream
+          (tests/golden/llama8b_stream.json); a difference fails the run.
+  toleranced_kernels : the same benchmark in a child process on the decode kernels
+          that sum in their own order, reported beside the headline.
+  cpu_baseline : whole greedy tokens of the full model on the CPU restatement of the
+          reference's x86 int8 tier (AVX2 and, where the host has it, AVX-512 VNNI),
+          all host threads, a bounded sample; plus a one-thread figure.
 
 With --impl reference only that CPU implementation is timed.  With N > 1
 (launched by torchrun, one rank per GPU) the ranks decode ONE sequence together:
@@ -657,11 +662,20 @@ def main():
     elif args.only == "gemm-sweep":
         import torch
         import cera_b200 as cb
+        dense, dense_src = 1590.0, "fallback"
+        mp = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(mp):
+            with open(mp) as f:
+                dense, dense_src = json.load(f).get("bf16_tflops", dense), "measured (cuBLAS bf16, burst)"
         for tname, m, k in [("q4_k", 4096, 4096), ("q4_k", 14336, 4096), ("q6_k", 4096, 14336), ("q5_k", 4096, 4096)]:
             for n in (8, 64, 256, 512):
                 ops, us = gemm_microbench(torch, cb, tname, m, k, n, max(3, args.iters // (4 if n > 64 else 1)))
+                # the tcgen05 kernel issues kind::f16 MMAs (exact small integers in f16): its tensor ceiling is the dense
+                # 16-bit rate, measured on this pool with cuBLAS bf16 (MEASURED_PEAKS.json); the nominal int8 figure beside it
                 emit(json.dumps({"type": tname, "m": m, "k": k, "n": n, "us": round(us, 2),
-                                  "tops": round(ops / us / 1e6, 2), "frac_of_int8_nominal_4500": round(ops / us / 1e6 / 4500, 4)}))
+                                  "tops": round(ops / us / 1e6, 2),
+                                  "frac_of_measured_dense_16bit": round(ops / us / 1e6 / dense, 4), "dense_16bit_tflops": dense,
+                                  "dense_source": dense_src, "frac_of_int8_nominal_4500": round(ops / us / 1e6 / 4500, 4)}))
     elif args.impl == "reference":
         reference_arm(args, rank)
     else:

@@ -12,7 +12,7 @@ from . import ops
 from .model import CudaModel, Role
 from .types import F32, Q4_K, Q6_K
 
-# BASELINE tensor mix: Q4_K attention / gate / up / token_embd, Q6_K ffn_down and output.
+# The benchmark model's tensor mix (a Q4_K_M-style GGUF): Q4_K attention / gate / up / token_embd, Q6_K ffn_down and output.
 LLAMA3_8B = dict(n_layers=32, hidden_size=4096, intermediate_size=14336, n_heads=32, n_kv_heads=8, head_dim=128,
                  vocab_size=128256, rope_theta=500000.0, rms_norm_eps=1e-5, rope_type=0)
 DEFAULT_TYPES = {Role.TOKEN_EMBD: Q4_K, Role.OUTPUT: Q6_K, Role.ATTN_Q: Q4_K, Role.ATTN_K: Q4_K, Role.ATTN_V: Q4_K,

@@ -130,7 +130,7 @@ def test_gemv_q5k_f32_matches_reference_semantics():
 
 
 def test_config1_q4_0_gemv_4096():
-    """BASELINE config 1: W 4096x4096 N(0,0.02) seed 0 -> Q4_0, x N(0,1) seed 1."""
+    """The reference's CPU-runnable benchmark case: W 4096x4096 N(0,0.02) seed 0 -> Q4_0, x N(0,1) seed 1."""
     torch = need_gpu()
     import cera_b200 as cb
     m = k = 4096
