@@ -1,32 +1,34 @@
 // Prefill GEMM on the fifth-generation tensor cores: out[m x n] = W (Q4_K / Q5_K) x X (Q8_0 columns) with
 // tcgen05.mma, accumulators in tensor memory (TMEM), for n >= 33 columns and k a multiple of 256.
 //
-// The arithmetic contract (cera/src/backend/simd.rs:5248-5371, 5693-5878) scales every 32-element block's EXACT
-// integer sum by (weight block scale) x (activation block scale), so a tensor-core instruction may accumulate over
-// one block only and the rescale runs on the CUDA cores.  Four choices keep that rescale small:
+// The arithmetic contract (cera/src/backend/simd.rs:5248-5371, 5693-5878) scales every 32-element block's integer sum
+// by (weight block scale) x (activation block scale).  A kernel that rescales each block's sum on the CUDA cores is
+// bound by that work, not by the tensor pipe (measured: 11 300 issued instructions per 128-k stage around 512 cycles
+// of MMA).  Here BOTH block scales ride inside the operands, so the tensor cores accumulate a whole 256-element
+// super-block and the CUDA cores touch the accumulators once per super-block:
 //
-//  * f16 operands with exact small integers.  A weight operand element is sc * q (six-bit sub-block scale times
-//    the 4/5-bit quant, at most 63 * 31 = 1953 < 2048: exact in f16), an activation element is the int8 quant.
-//    kind::f16 MMAs accumulate the products exactly in f32 (|sum| < 2^24), so the accumulator already holds the
-//    float the rescale needs - no int-to-float conversion - and the sub-block scale is inside the product.
-//  * Tokens on the TMEM lanes.  D[token][weight row]: an epilogue thread owns one token, so the activation block
-//    scale is one value per thread; it keeps p[row] += D * xs for its 32 rows in registers - ONE FMA per cell
-//    per block - and once per 256-element super-block folds out[row] += d[row] * p[row] into a TMEM region.
-//  * The min term rides the tensor cores too.  sum_b dmin*mn_b * (xs_b * A_b) (A_b = the block's sum of quants)
-//    has one factor per (row, block) and one per (token, block): a 16-column MMA per super-block multiplies the
-//    eight six-bit mins (exact in f16, each twice) by the eight values g*xs_b*A_b split into an f16 high and low
-//    part (g = a power of two per token that brings them below 2^15; 22 significant bits survive), into a third
-//    accumulator; the fold subtracts dmin[row] * Dm / g.
-//  * Operand tiles are built in shared memory by producer warps straight from the quantized bytes (weights:
-//    nibble -> 0x6400|q -> one HFMA2 with the sub-block scale; activations: byte -> 0x6400|(b^0x80) -> HSUB2), in the
-//    canonical K-major no-swizzle layout (8-row x 16-byte core matrices), three stages of 128 k-elements deep.
+//  * Weight operand: sc * q, the six-bit sub-block scale times the 4/5-bit quant (at most 63 * 31 = 1953 < 2048):
+//    an exact small integer in f16.
+//  * Activation operand: v = (g * xs_b) * a for the int8 quant a of block b - the activation block scale folded in, g a
+//    power of two per token that brings every v below 2^15 - as TWO f16 operands: the top 11 bits of v and the
+//    f16-rounded remainder.  Each MMA step runs twice (high and low part) into the same accumulator; 22 significant
+//    bits of every activation survive, the products are exact, the f32 accumulation is the tensor core's.
+//  * The min term sum_b dmin * mn_b * (xs_b * A_b) (A_b = the block's sum of quants) is one more 16-column MMA per
+//    super-block: the eight six-bit mins (each twice) times the high / low parts of g * xs_b * A_b, into a third
+//    accumulator.
+//  * Per super-block the epilogue folds out[row] += (d[row] * D - dmin[row] * Dm) / g into a TMEM region.
 //
-// Warp roles in a CTA of 25 warps (one 128-token x 128-row tile): warp 0 allocates TMEM and issues the MMAs from
-// one thread; warps 1-4 build the weight operand (thread = weight row) and the row-side tables; warps 5-8 build
-// the activation operand (thread = token); warps 9-24 are the epilogue (thread = token lane x 32 rows).  Stages
-// and the two D buffers are handed over through mbarriers (tcgen05.commit arrives on them when the MMAs have
-// finished).  Every wait is bounded: when a limit runs out the CTA raises an abort flag, its roles leave their
-// loops, TMEM is freed and a status word reports it (cera_cuda_kernel_status).
+// The results agree with the reference within its f32 tolerance (1e-3 relative; measured ~1e-6), not bit for bit: the
+// bit-exact block sums are the decode path's and cera_cuda_block_sums' business.
+//
+// Operand tiles are built in shared memory by producer warps straight from the quantized bytes, in the canonical
+// K-major no-swizzle layout (8-row x 16-byte core matrices), four stages of 64 k-elements.  Warp roles in a CTA of 21
+// warps (one 128-token x 128-row tile): warp 0 allocates TMEM and issues the MMAs from one thread; warps 1-4 build the
+// weight operand (thread = weight row); warps 5-12 build the two activation operands (thread = token x one 32-element
+// block of the stage); warps 13-20 are the epilogue (thread = token lane x 64 rows).  Stages and the two D buffers are
+// handed over through mbarriers (tcgen05.commit arrives on them when the MMAs have finished).  Every wait is bounded:
+// when a limit runs out the CTA raises an abort flag, its roles leave their loops, TMEM is freed and a status word
+// reports it (cera_cuda_kernel_status).
 #include <cuda_fp16.h>
 
 #include <cstdlib>
@@ -43,20 +45,18 @@ namespace {
 
 constexpr int TC_BM = 128;      // tokens per tile (TMEM lanes)
 constexpr int TC_BN = 128;      // weight rows per tile (TMEM columns)
-constexpr int TC_KS = 128;      // k elements per stage
-constexpr int TC_STAGES = 3;
-constexpr int TC_EPI_WARPS = 16;                // four warpgroups: each covers the 128 token lanes for 32 weight rows
-constexpr int TC_THREADS = (9 + TC_EPI_WARPS) * 32;
-constexpr uint32_t TC_OP_BYTES = TC_BM * TC_KS * 2;                      // one operand tile of a stage: 32 KB
-constexpr uint32_t TC_TAB_BYTES = 4 * TC_BM * 4;                         // xsv[4][128]: the stage's activation block scales per token
-constexpr uint32_t TC_STAGE_BYTES = 2 * TC_OP_BYTES + TC_TAB_BYTES;      // 67 584
-// per super-block (two stages), two slots: the min-term operands (16 k-columns each) and the row-side tables
+constexpr int TC_KS = 64;       // k elements per stage: two 32-element blocks, half a 128-weight task
+constexpr int TC_STAGES = 4;    // = stages per 256-element super-block
+constexpr int TC_W_WARPS = 4, TC_T_WARPS = 8, TC_EPI_WARPS = 8;
+constexpr int TC_THREADS = (1 + TC_W_WARPS + TC_T_WARPS + TC_EPI_WARPS) * 32;  // 672
+constexpr uint32_t TC_OP_BYTES = TC_BM * TC_KS * 2;                      // one operand tile of a stage: 16 KB
+constexpr uint32_t TC_STAGE_BYTES = 3 * TC_OP_BYTES;                     // activations high, activations low, weights
+// per super-block, two slots: the min-term operands (16 k-columns each) and the row-side tables
 constexpr uint32_t TC_MINOP_BYTES = TC_BM * 16 * 2;                      // 4 KB: [2 k chunks][128 rows][8 f16]
 constexpr uint32_t TC_SLOT_BYTES = 2 * TC_MINOP_BYTES + 2 * TC_BN * 4;   // A, B, dval[128], dmin[128]
 constexpr uint32_t TC_TAIL_OFF = TC_STAGES * TC_STAGE_BYTES + 2 * TC_SLOT_BYTES;  // ginv[128], then barriers, TMEM address, abort flag
 constexpr uint32_t TC_SMEM_BYTES = TC_TAIL_OFF + TC_BM * 4 + 256;
 constexpr uint32_t TC_TMEM_COLS = 512;                                   // D0 [0,128) D1 [128,256) Dm [256,384) OUT [384,512)
-constexpr uint32_t TC_DBUFS = 2;
 constexpr uint32_t TC_KC_STRIDE = TC_BM * 16;                            // bytes between 8-element k chunks: 2048
 
 struct TcParams {
@@ -136,21 +136,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
     uint8_t *slots = tc_smem + TC_STAGES * TC_STAGE_BYTES;
     float *ginv_tab = reinterpret_cast<float *>(tc_smem + TC_TAIL_OFF);  // [128]: 1 / g of every token lane
     uint64_t *bars = reinterpret_cast<uint64_t *>(tc_smem + TC_TAIL_OFF + TC_BM * 4);
-    uint64_t *full_ab = bars, *empty_ab = bars + TC_STAGES, *full_d = bars + 2 * TC_STAGES, *empty_d = full_d + TC_DBUFS;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC_STAGES + 2 * TC_DBUFS);
+    uint64_t *full_ab = bars, *empty_ab = bars + TC_STAGES, *full_d = bars + 2 * TC_STAGES, *empty_d = full_d + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC_STAGES + 4);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t col0 = blockIdx.x * TC_BM, row0 = blockIdx.y * TC_BN;
-    const uint32_t n_it = p.k / TC_KS;
+    const uint32_t n_sb = p.k / 256, n_it = n_sb * TC_STAGES;
+    const uint32_t nb32 = p.k >> 5, nb16 = p.k >> 4;
 
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
-            tma::mbar_init(full_ab + s, 256);                 // every producer thread
-            tma::mbar_init(empty_ab + s, 1 + TC_EPI_WARPS);   // the MMAs' commit + each epilogue warp (it reads the stage's tables)
+            tma::mbar_init(full_ab + s, (TC_W_WARPS + TC_T_WARPS) * 32);  // every producer thread
+            tma::mbar_init(empty_ab + s, 1);                              // the commit of the stage's MMAs
         }
-        for (int b = 0; b < (int)TC_DBUFS; ++b) {
-            tma::mbar_init(full_d + b, 1);
-            tma::mbar_init(empty_d + b, TC_EPI_WARPS);
+        for (int b = 0; b < 2; ++b) {
+            tma::mbar_init(full_d + b, 1);              // the commit after a super-block's last MMA
+            tma::mbar_init(empty_d + b, TC_EPI_WARPS);  // every epilogue warp is done with the buffer, Dm and the slot
         }
         *abort_flag = 0;
         tma::mbar_init_fence();
@@ -171,48 +172,56 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
         if (lane == 0) {
             const uint32_t idesc = tc_idesc(TC_BM, TC_BN);
             bool ok = true;
-            for (uint32_t it = 0; it < n_it && ok; ++it) {
-                const uint32_t s = it % TC_STAGES;
-                if (!tma::mbar_wait_blocking(full_ab + s, (it / TC_STAGES) & 1, abort_flag, &g_tc_status, 1u)) break;
+            for (uint32_t sb = 0; sb < n_sb && ok; ++sb) {
+                const uint32_t buf = sb & 1;
+                // the epilogue has left this D buffer (super-block sb - 2)
+                if (!tma::mbar_wait_blocking(empty_d + buf, ((sb >> 1) & 1) ^ 1, abort_flag, &g_tc_status, 2u)) break;
                 tc_fence_after();
-                const uint32_t a_base = tma::smem_u32(tc_smem + s * TC_STAGE_BYTES), b_base = a_base + TC_OP_BYTES;
-                for (uint32_t b = 0; b < 4; ++b) {
-                    const uint32_t gb = it * 4 + b, buf = gb % TC_DBUFS;
-                    if (!tma::mbar_wait_blocking(empty_d + buf, ((gb / TC_DBUFS) & 1) ^ 1, abort_flag, &g_tc_status, 2u)) {
+                for (uint32_t st = 0; st < (uint32_t)TC_STAGES; ++st) {
+                    const uint32_t it = sb * TC_STAGES + st;
+                    if (!tma::mbar_wait_blocking(full_ab + st, (it / TC_STAGES) & 1, abort_flag, &g_tc_status, 1u)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
+                    const uint32_t a_hi = tma::smem_u32(tc_smem + st * TC_STAGE_BYTES), a_lo = a_hi + TC_OP_BYTES, b_base = a_lo + TC_OP_BYTES;
 #pragma unroll
-                    for (uint32_t j = 0; j < 2; ++j) {
-                        const uint32_t kc = 4 * b + 2 * j;
-                        tc_mma_f16(tmem + buf * TC_BN, smem_desc(a_base + kc * TC_KC_STRIDE, TC_KC_STRIDE, 128),
-                                   smem_desc(b_base + kc * TC_KC_STRIDE, TC_KC_STRIDE, 128), idesc, j);
+                    for (uint32_t ks = 0; ks < TC_KS / 16; ++ks) {
+                        const uint64_t bd = smem_desc(b_base + 2 * ks * TC_KC_STRIDE, TC_KC_STRIDE, 128);
+                        tc_mma_f16(tmem + buf * TC_BN, smem_desc(a_hi + 2 * ks * TC_KC_STRIDE, TC_KC_STRIDE, 128), bd, idesc, (st | ks) != 0);
+                        tc_mma_f16(tmem + buf * TC_BN, smem_desc(a_lo + 2 * ks * TC_KC_STRIDE, TC_KC_STRIDE, 128), bd, idesc, 1);
                     }
-                    if ((it & 1) && b == 3) {
-                        // the super-block's min term: Dm[token][row] = sum_b mn_b * (hi_b + lo_b).  The epilogue has read the
-                        // previous Dm: it handed back a D buffer of THIS iteration, which it reaches only after that fold.
-                        const uint32_t slot = tma::smem_u32(slots + ((it >> 1) & 1) * TC_SLOT_BYTES);
-                        tc_mma_f16(tmem + 2 * TC_BN, smem_desc(slot, TC_KC_STRIDE, 128), smem_desc(slot + TC_MINOP_BYTES, TC_KC_STRIDE, 128),
-                                   idesc, 0);
+                    if (st + 1 == (uint32_t)TC_STAGES) {
+                        // the super-block's min term.  Dm has one buffer: the epilogue must have read super-block sb - 1's
+                        if (sb && !tma::mbar_wait_blocking(empty_d + (buf ^ 1), ((sb - 1) >> 1) & 1, abort_flag, &g_tc_status, 2u)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t slot = tma::smem_u32(slots + buf * TC_SLOT_BYTES);
+                        tc_mma_f16(tmem + 2 * TC_BN, smem_desc(slot, TC_KC_STRIDE, 128), smem_desc(slot + TC_MINOP_BYTES, TC_KC_STRIDE, 128), idesc, 0);
                     }
-                    tc_commit(full_d + buf);
+                    tc_commit(empty_ab + st);
                 }
-                tc_commit(empty_ab + s);
+                if (ok) tc_commit(full_d + buf);
             }
         }
-    } else if (warp <= 4) {
+    } else if (warp <= TC_W_WARPS) {
         // ---------------------------------------------------------------- weight operand: thread = weight row
         const uint32_t r = tid - 32;
         const uint32_t row = min(row0 + r, p.m - 1);  // rows past the edge repeat the last one; their results are not stored
+        // the raw bytes of a stage are fetched one stage ahead of their conversion (a thread converts every stage itself:
+        // a global round trip per stage would bound the pipeline)
         struct RawW {
-            uint4 piece[4], h, hb0, hb1;
+            uint4 p0, p1, h, hb0, hb1;
         };
         auto fetch = [&](uint32_t it) {
             RawW rw;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) rw.piece[c] = ld_stream(q_piece_ptr(p.w, row, 4, it * 4 + c));
-            const size_t sbi = sb_index(p.w, row, it >> 1);
+            const uint32_t st = it % TC_STAGES, sb = it / TC_STAGES, pair = st & 1, hf = st >> 1;
+            // the stage's 32 bytes: pieces 2 pair, 2 pair + 1 of the task (low nibbles = sub-block 2 pair, high = 2 pair + 1)
+            rw.p0 = ld_stream(q_piece_ptr(p.w, row, 4, (2 * sb + hf) * 4 + 2 * pair));
+            rw.p1 = ld_stream(q_piece_ptr(p.w, row, 4, (2 * sb + hf) * 4 + 2 * pair + 1));
+            const size_t sbi = sb_index(p.w, row, sb);
             rw.h = __ldg(reinterpret_cast<const uint4 *>(p.w.hdr) + sbi);
             rw.hb0 = make_uint4(0, 0, 0, 0);
             rw.hb1 = rw.hb0;
@@ -222,27 +231,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
             }
             return rw;
         };
-        // (fetching an iteration ahead of the conversion was measured: no gain, and its 28 live registers spill)
+        RawW nxt = fetch(0);
         for (uint32_t it = 0; it < n_it; ++it) {
-            const uint32_t s = it % TC_STAGES;
-            const RawW cur = fetch(it);
-            const uint4 (&piece)[4] = cur.piece;
-            const uint4 h = cur.h, hb0 = cur.hb0, hb1 = cur.hb1;
-            if (!tma::mbar_wait_blocking(empty_ab + s, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 4u)) break;
-            uint8_t *stage = tc_smem + s * TC_STAGE_BYTES;
-            uint8_t *opb = stage + TC_OP_BYTES;
-            uint8_t *slot = slots + ((it >> 1) & 1) * TC_SLOT_BYTES;  // free: the stage it shares a phase with was released
-            const uint32_t hf = it & 1;
+            const uint32_t st = it % TC_STAGES, sb = it / TC_STAGES, pair = st & 1, hf = st >> 1;  // task 2 sb + hf, byte pair `pair`
+            const RawW cur = nxt;
+            if (it + 1 < n_it) nxt = fetch(it + 1);
+            const uint4 p0 = cur.p0, p1 = cur.p1, h = cur.h, hb0 = cur.hb0, hb1 = cur.hb1;
+            if (!tma::mbar_wait_blocking(empty_ab + st, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 4u)) break;
+            // the slot of this super-block (tables, min operand) was last used by super-block sb - 2
+            if (st == 0 && sb >= 2 && !tma::mbar_wait_blocking(empty_d + (sb & 1), ((sb - 2) >> 1) & 1, abort_flag, &g_tc_status, 4u)) break;
+            uint8_t *opb = tc_smem + st * TC_STAGE_BYTES + 2 * TC_OP_BYTES;
+            uint8_t *slot = slots + (sb & 1) * TC_SLOT_BYTES;
             uint32_t scp, mnp;
             kq_quad(h, hf, scp, mnp);
-            const float d = h2f((uint16_t)(h.x & 0xFFFF)), dmin = h2f((uint16_t)(h.x >> 16));
+            const uint32_t sc_lo = (scp >> (16 * pair)) & 0xFF, sc_hi = (scp >> (16 * pair + 8)) & 0xFF;
+            const __half2 s_lo = __half2half2(__ushort2half_rn((unsigned short)sc_lo)), s_hi = __half2half2(__ushort2half_rn((unsigned short)sc_hi));
+            const __half2 nb_lo = __hmul2(s_lo, __float2half2_rn(-1024.0f)), nb_hi = __hmul2(s_hi, __float2half2_rn(-1024.0f));
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int pair = c >> 1, half = c & 1;
-                const uint32_t sc_lo = (scp >> (8 * (2 * pair))) & 0xFF, sc_hi = (scp >> (8 * (2 * pair + 1))) & 0xFF;
-                const __half2 s_lo = __half2half2(__ushort2half_rn((unsigned short)sc_lo)), s_hi = __half2half2(__ushort2half_rn((unsigned short)sc_hi));
-                const __half2 nb_lo = __hmul2(s_lo, __float2half2_rn(-1024.0f)), nb_hi = __hmul2(s_hi, __float2half2_rn(-1024.0f));
-                const uint4 v4 = piece[c];
+            for (int half = 0; half < 2; ++half) {
+                const uint4 v4 = half ? p1 : p0;
                 const uint4 hbv = half ? hb1 : hb0;
                 const uint32_t wv[4] = {v4.x, v4.y, v4.z, v4.w}, hw[4] = {hbv.x, hbv.y, hbv.z, hbv.w};
                 __half2 lo8[8], hi8[8];  // 16 low-nibble and 16 high-nibble elements, two per half2
@@ -262,202 +269,168 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
                     hi8[2 * i] = __hfma2(a, s_hi, nb_hi);
                     hi8[2 * i + 1] = __hfma2(b, s_hi, nb_hi);
                 }
-                // low nibbles: elements [16 half, +16) of sub-block 2 pair; high nibbles: the same of sub-block 2 pair + 1
-                const uint32_t kc_lo = 8 * pair + 2 * half, kc_hi = kc_lo + 4;
+                // low nibbles: elements [16 half, +16) of the stage's first block; high nibbles: the same of its second block
+                const uint32_t kc_lo = 2 * half, kc_hi = kc_lo + 4;
                 *reinterpret_cast<uint4 *>(opb + op_off(kc_lo, r)) = *reinterpret_cast<const uint4 *>(&lo8[0]);
                 *reinterpret_cast<uint4 *>(opb + op_off(kc_lo + 1, r)) = *reinterpret_cast<const uint4 *>(&lo8[4]);
                 *reinterpret_cast<uint4 *>(opb + op_off(kc_hi, r)) = *reinterpret_cast<const uint4 *>(&hi8[0]);
                 *reinterpret_cast<uint4 *>(opb + op_off(kc_hi + 1, r)) = *reinterpret_cast<const uint4 *>(&hi8[4]);
             }
             {
-                // the four mins of this half super-block, each twice (for the high and the low part of the token side):
-                // k chunk `hf` of the min-term weight operand
-                __half2 mn2[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) mn2[j] = __half2half2(__ushort2half_rn((unsigned short)((mnp >> (8 * j)) & 0xFF)));
-                *reinterpret_cast<uint4 *>(slot + TC_MINOP_BYTES + op_off(hf, r)) = *reinterpret_cast<const uint4 *>(&mn2[0]);
-                if (hf == 0) {
+                // the mins of the stage's two blocks, each twice (for the high and the low part of the token side): four
+                // f16 = blocks 2 st, 2 st + 1 of the super-block's 16-column min operand
+                const uint32_t mn0 = (mnp >> (16 * pair)) & 0xFF, mn1 = (mnp >> (16 * pair + 8)) & 0xFF;
+                __half2 m2[2] = {__half2half2(__ushort2half_rn((unsigned short)mn0)), __half2half2(__ushort2half_rn((unsigned short)mn1))};
+                *reinterpret_cast<uint2 *>(slot + TC_MINOP_BYTES + op_off(st >> 1, r) + (st & 1) * 8) = *reinterpret_cast<const uint2 *>(&m2[0]);
+                if (st == 0) {
                     float *dval = reinterpret_cast<float *>(slot + 2 * TC_MINOP_BYTES);
-                    dval[r] = d;
-                    dval[TC_BN + r] = dmin;
+                    dval[r] = h2f((uint16_t)(h.x & 0xFFFF));
+                    dval[TC_BN + r] = h2f((uint16_t)(h.x >> 16));
                 }
             }
             fence_async_smem();
-            tma::mbar_arrive(full_ab + s);
+            tma::mbar_arrive(full_ab + st);
         }
-    } else if (warp <= 8) {
-        // ---------------------------------------------------------------- activation operand: thread = token
-        const uint32_t c = tid - 160;
+    } else if (warp <= TC_W_WARPS + TC_T_WARPS) {
+        // ---------------------------------------------------------------- activation operands: thread = (token, block of the stage)
+        const uint32_t tt = tid - (1 + TC_W_WARPS) * 32, c = tt >> 1, blk = tt & 1;
         const uint32_t token = min(col0 + c, p.n - 1);
         const int8_t *src = p.x.quants + (size_t)token * p.k;
-        const __half2 bias = __float2half2_rn(1152.0f);  // 1024 + 128
-        const uint32_t nb32 = p.k >> 5, nb16 = p.k >> 4;
-        struct RawX {
-            uint4 v[8];
-            float4 xs;  // the four block scales of the stage
-            uint4 sm;   // the eight 16-element sums
-        };
-        auto fetch = [&](uint32_t it) {
-            RawX rx;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) rx.v[j] = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)it * TC_KS) + j);
-            rx.xs = __ldg(reinterpret_cast<const float4 *>(p.x.scales + (size_t)token * nb32 + it * 4));
-            rx.sm = __ldg(reinterpret_cast<const uint4 *>(p.x.sums + (size_t)token * nb16 + it * 8));
-            return rx;
-        };
-        // g: a power of two that brings every xs_b * A_b of the token below 2^15, so that its f16 high / low parts keep
-        // 22 significant bits whatever the magnitude of the activations
+        const float *xs_row = p.x.scales + (size_t)token * nb32;
+        const int16_t *sm_row = reinterpret_cast<const int16_t *>(p.x.sums) + (size_t)token * nb16;
+        // g: a power of two that brings every |xs_b * a| of the token below 2^15 (|a| <= 127, and |A_b| <= 4064 for the
+        // min operand: 2^15 / 32 keeps both in range); the token's two threads scan half of the blocks each
         float g = 1.0f;
         {
             float mx = 0.0f;
-            for (uint32_t it = 0; it < n_it; ++it) {
-                const float4 x4 = __ldg(reinterpret_cast<const float4 *>(p.x.scales + (size_t)token * nb32 + it * 4));
-                const uint4 s4 = __ldg(reinterpret_cast<const uint4 *>(p.x.sums + (size_t)token * nb16 + it * 8));
-                const float xv[4] = {x4.x, x4.y, x4.z, x4.w};
-                const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    const float v = fabsf(xv[b] * (float)((int)(int16_t)(sw[b] & 0xFFFF) + (int)(int16_t)(sw[b] >> 16)));
-                    mx = fmaxf(mx, v == v && v < 3.0e38f ? v : 0.0f);
-                }
+            for (uint32_t b = blk; b < nb32; b += 2) {
+                const float v = fabsf(__ldg(xs_row + b));
+                mx = fmaxf(mx, v == v && v < 1.0e30f ? v : 0.0f);  // (scales beyond 1e30 are not activations: left out of the range search)
             }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             if (mx > 0.0f) {
                 int e;
-                frexpf(mx, &e);  // mx < 2^e
+                frexpf(mx * 4064.0f, &e);  // |xs_b * A_b| <= mx * 4064 < 2^e
                 g = ldexpf(1.0f, 15 - e);
             }
-            ginv_tab[c] = 1.0f / g;  // published by the first full_ab arrival below
+            if (blk == 0) ginv_tab[c] = 1.0f / g;  // published by the first full_ab arrival below
         }
+        struct RawX {
+            uint4 r0, r1;
+            float xs;
+            int asum;
+        };
+        auto fetch = [&](uint32_t it) {
+            RawX rx;
+            const uint32_t xb = it * 2 + blk;  // this thread's 32-element activation block
+            rx.r0 = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)xb * 32));
+            rx.r1 = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)xb * 32) + 1);
+            rx.xs = __ldg(xs_row + xb);
+            rx.asum = (int)__ldg(sm_row + 2 * xb) + (int)__ldg(sm_row + 2 * xb + 1);
+            return rx;
+        };
+        RawX nxt = fetch(0);
         for (uint32_t it = 0; it < n_it; ++it) {
-            const uint32_t s = it % TC_STAGES;
-            const RawX cur = fetch(it);  // (a register prefetch of the next stage spills at 72 registers: measured no faster)
-            const uint4 (&raw)[8] = cur.v;
-            if (!tma::mbar_wait_blocking(empty_ab + s, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) break;
-            uint8_t *opa = tc_smem + s * TC_STAGE_BYTES;
-            uint8_t *slot = slots + ((it >> 1) & 1) * TC_SLOT_BYTES;
+            const uint32_t st = it % TC_STAGES, sb = it / TC_STAGES;
+            const RawX cur = nxt;
+            if (it + 1 < n_it) nxt = fetch(it + 1);
+            const uint4 r0 = cur.r0, r1 = cur.r1;
+            const float sg = cur.xs * g;
+            const float asum = (float)cur.asum;
+            if (!tma::mbar_wait_blocking(empty_ab + st, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) break;
+            if (st == 0 && sb >= 2 && !tma::mbar_wait_blocking(empty_d + (sb & 1), ((sb - 2) >> 1) & 1, abort_flag, &g_tc_status, 8u)) break;
+            uint8_t *op_hi = tc_smem + st * TC_STAGE_BYTES, *op_lo = op_hi + TC_OP_BYTES;
+            uint8_t *slot = slots + (sb & 1) * TC_SLOT_BYTES;
+            const uint32_t words[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+            const float2 sg2 = make_float2(sg, sg);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {  // 16 quants -> k chunks 2j, 2j+1
-                const uint32_t wv[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
-                __half2 o[8];
+            for (int ch = 0; ch < 4; ++ch) {  // eight elements = one 16-byte k chunk of each operand
+                __half2 hi2[4], lo2[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    __half2 a, b;
-                    bytes_to_h1024(wv[i] ^ 0x80808080u, a, b);  // signed byte + 128 -> unsigned
-                    o[2 * i] = __hsub2(a, bias);
-                    o[2 * i + 1] = __hsub2(b, bias);
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t w = words[2 * ch + (q >> 1)];
+                    const int e0 = (int)(int8_t)(w >> (16 * (q & 1))), e1 = (int)(int8_t)(w >> (16 * (q & 1) + 8));
+                    const float2 v = __fmul2_rn(make_float2((float)e0, (float)e1), sg2);
+                    // high part: the top 11 significant bits (exactly an f16 while v is in the normal range); low: the rest, rounded
+                    const float2 vh = make_float2(__uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u), __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u));
+                    const float2 vl = __fadd2_rn(v, make_float2(-vh.x, -vh.y));
+                    hi2[q] = __float22half2_rn(vh);
+                    lo2[q] = __float22half2_rn(vl);
                 }
-                *reinterpret_cast<uint4 *>(opa + op_off(2 * j, c)) = *reinterpret_cast<const uint4 *>(&o[0]);
-                *reinterpret_cast<uint4 *>(opa + op_off(2 * j + 1, c)) = *reinterpret_cast<const uint4 *>(&o[4]);
+                *reinterpret_cast<uint4 *>(op_hi + op_off(4 * blk + ch, c)) = *reinterpret_cast<const uint4 *>(&hi2[0]);
+                *reinterpret_cast<uint4 *>(op_lo + op_off(4 * blk + ch, c)) = *reinterpret_cast<const uint4 *>(&lo2[0]);
             }
             {
-                // per-token scalars of the stage's four blocks: the block scales for the epilogue, and g * xs_b * A_b as an f16
-                // high and low part = k chunk (it & 1) of the min-term token operand
-                float *xsv = reinterpret_cast<float *>(opa + 2 * TC_OP_BYTES);
-                const float xv[4] = {cur.xs.x, cur.xs.y, cur.xs.z, cur.xs.w};
-                const uint32_t sw[4] = {cur.sm.x, cur.sm.y, cur.sm.z, cur.sm.w};
-                __half2 hl[4];
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    xsv[b * TC_BM + c] = xv[b];
-                    const float v = (xv[b] * (float)((int)(int16_t)(sw[b] & 0xFFFF) + (int)(int16_t)(sw[b] >> 16))) * g;
-                    const __half hi = __float2half_rn(v);
-                    const __half lo = __float2half_rn(v - __half2float(hi));
-                    hl[b] = __halves2half2(hi, lo);
-                }
-                *reinterpret_cast<uint4 *>(slot + op_off(it & 1, c)) = *reinterpret_cast<const uint4 *>(&hl[0]);
+                // g * xs_b * A_b as a high and a low f16: block 2 st + blk of the super-block's min operand
+                const float v = sg * asum;
+                const float vh = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+                const __half2 hl = __floats2half2_rn(vh, v - vh);
+                *reinterpret_cast<uint32_t *>(slot + op_off(st >> 1, c) + ((st & 1) * 2 + blk) * 4) = *reinterpret_cast<const uint32_t *>(&hl);
             }
             fence_async_smem();
-            tma::mbar_arrive(full_ab + s);
+            tma::mbar_arrive(full_ab + st);
         }
     } else {
-        // ---------------------------------------------------------------- epilogue: thread = (token lane, 32 rows)
-        const uint32_t e = warp - 9, ch = e >> 2, quad = warp & 3;  // a warp reaches TMEM lanes [32 (warp % 4), +32)
-        const uint32_t tl = quad * 32 + lane;                       // token lane
+        // ---------------------------------------------------------------- epilogue: thread = (token lane, 64 rows)
+        const uint32_t e = warp - (1 + TC_W_WARPS + TC_T_WARPS), quad = warp & 3, ch = e >> 2;  // a warp reaches TMEM lanes [32 (warp % 4), +32)
+        const uint32_t tl = quad * 32 + lane;                                                    // token lane
         const uint32_t lane_addr = tmem + ((quad * 32) << 16);
-        float pacc[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) pacc[i] = 0.0f;
         float ginv = 1.0f;
         bool ok = true;
-        for (uint32_t it = 0; it < n_it && ok; ++it) {
-            const uint32_t s = it % TC_STAGES;
-            const float *xsv = reinterpret_cast<const float *>(tc_smem + s * TC_STAGE_BYTES + 2 * TC_OP_BYTES);
-            // the producers' release of this stage, observed directly: the tables are read with plain loads
-            if (!tma::mbar_wait_blocking(full_ab + s, (it / TC_STAGES) & 1, abort_flag, &g_tc_status, 32u)) break;
-            if (it == 0) ginv = ginv_tab[tl];
-            for (uint32_t b = 0; b < 4; ++b) {
-                const uint32_t gb = it * 4 + b, buf = gb % TC_DBUFS;
-                const float xs = xsv[b * TC_BM + tl];
-                if (!tma::mbar_wait_blocking(full_d + buf, (gb / TC_DBUFS) & 1, abort_flag, &g_tc_status, 16u)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                {
-                    uint32_t dreg[16];
-                    tmem_ld16(lane_addr + buf * TC_BN + ch * 32, dreg);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) pacc[i] = fmaf(__uint_as_float(dreg[i]), xs, pacc[i]);
-                    tmem_ld16(lane_addr + buf * TC_BN + ch * 32 + 16, dreg);
-                    tmem_wait_ld();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) tma::mbar_arrive(empty_d + buf);  // the values are in registers: the buffer may be overwritten
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) pacc[16 + i] = fmaf(__uint_as_float(dreg[i]), xs, pacc[16 + i]);
-                }
+        for (uint32_t sb = 0; sb < n_sb && ok; ++sb) {
+            const uint32_t buf = sb & 1;
+            if (!tma::mbar_wait_blocking(full_d + buf, (sb >> 1) & 1, abort_flag, &g_tc_status, 16u)) {
+                ok = false;
+                break;
             }
-            if (!ok) break;
-            if (it & 1) {
-                // end of a 256-element super-block: out[row] += d[row] * p[row] - dmin[row] * Dm[row] / g; the running sum lives in TMEM
-                const float *dval = reinterpret_cast<const float *>(slots + ((it >> 1) & 1) * TC_SLOT_BYTES + 2 * TC_MINOP_BYTES);
+            tc_fence_after();
+            if (sb == 0) ginv = ginv_tab[tl];  // written before the first producer arrival, which the MMAs of this super-block followed
+            const float *dval = reinterpret_cast<const float *>(slots + buf * TC_SLOT_BYTES + 2 * TC_MINOP_BYTES);
+            // out[row] += (d[row] * D - dmin[row] * Dm) / g, the running sum in TMEM
+#pragma unroll 1
+            for (uint32_t c4 = 0; c4 < 4; ++c4) {
+                const uint32_t col = ch * 64 + c4 * 16;
+                uint32_t dreg[16], mreg[16], oreg[16];
+                tmem_ld16(lane_addr + buf * TC_BN + col, dreg);
+                tmem_ld16(lane_addr + 2 * TC_BN + col, mreg);
+                if (sb) {
+                    tmem_ld16(lane_addr + 3 * TC_BN + col, oreg);
+                } else {
 #pragma unroll
-                for (int c4 = 0; c4 < 2; ++c4) {
-                    uint32_t oreg[16], mreg[16];
-                    const uint32_t addr = lane_addr + 3 * TC_BN + ch * 32 + c4 * 16;
-                    tmem_ld16(lane_addr + 2 * TC_BN + ch * 32 + c4 * 16, mreg);
-                    if (it > 1) {
-                        tmem_ld16(addr, oreg);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) oreg[i] = 0u;
-                    }
-                    tmem_wait_ld();
-                    const float4 *dq = reinterpret_cast<const float4 *>(dval + ch * 32 + c4 * 16), *mq = dq + TC_BN / 4;
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const float4 dv = dq[q4], mv = mq[q4];
-                        const float dvv[4] = {dv.x, dv.y, dv.z, dv.w}, mvv[4] = {mv.x, mv.y, mv.z, mv.w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int j = q4 * 4 + i;
-                            float o = fmaf(pacc[c4 * 16 + j], dvv[i], __uint_as_float(oreg[j]));
-                            o = fmaf(-mvv[i], __uint_as_float(mreg[j]) * ginv, o);
-                            oreg[j] = __float_as_uint(o);
-                            pacc[c4 * 16 + j] = 0.0f;
-                        }
-                    }
-                    tmem_st16(addr, oreg);
+                    for (int i = 0; i < 16; ++i) oreg[i] = 0u;
                 }
-                tmem_wait_st();
+                tmem_wait_ld();
+                const float4 *dq = reinterpret_cast<const float4 *>(dval + col), *mq = dq + TC_BN / 4;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const float4 dv = dq[q4], mv = mq[q4];
+                    const float dvv[4] = {dv.x, dv.y, dv.z, dv.w}, mvv[4] = {mv.x, mv.y, mv.z, mv.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int j = q4 * 4 + i;
+                        const float t = fmaf(dvv[i], __uint_as_float(dreg[j]), -(mvv[i] * __uint_as_float(mreg[j])));
+                        oreg[j] = __float_as_uint(fmaf(t, ginv, __uint_as_float(oreg[j])));
+                    }
+                }
+                tmem_st16(lane_addr + 3 * TC_BN + col, oreg);
             }
+            tmem_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) tma::mbar_arrive(empty_ab + s);  // this warp is done with the stage's tables (and the slot's)
+            if (lane == 0) tma::mbar_arrive(empty_d + buf);  // D buffer, Dm and the slot's tables are free again
         }
         if (ok) {
             // ---- the tile -> global memory: cell (row i, token j) at out[i * ldy + j * ldc]
             const bool tok_ok = col0 + tl < p.n;
-#pragma unroll
-            for (int c4 = 0; c4 < 2; ++c4) {
+#pragma unroll 1
+            for (uint32_t c4 = 0; c4 < 4; ++c4) {
                 uint32_t oreg[16];
-                tmem_ld16(lane_addr + 3 * TC_BN + ch * 32 + c4 * 16, oreg);
+                tmem_ld16(lane_addr + 3 * TC_BN + ch * 64 + c4 * 16, oreg);
                 tmem_wait_ld();
                 if (tok_ok) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const uint32_t row = row0 + ch * 32 + c4 * 16 + i;
+                        const uint32_t row = row0 + ch * 64 + c4 * 16 + i;
                         if (row < p.m) {
                             float *o = p.out + (size_t)row * p.ldy + (size_t)(col0 + tl) * p.ldc;
                             const float v = __uint_as_float(oreg[i]);
