@@ -21,11 +21,14 @@
 // The results agree with the reference within its f32 tolerance (1e-3 relative; measured ~1e-6), not bit for bit: the
 // bit-exact block sums are the decode path's and cera_cuda_block_sums' business.
 //
-// Operand tiles are built in shared memory by producer warps straight from the quantized bytes, in the canonical
-// K-major no-swizzle layout (8-row x 16-byte core matrices), four stages of 64 k-elements.  Warp roles in a CTA of 21
-// warps (one 128-token x 128-row tile): warp 0 allocates TMEM and issues the MMAs from one thread; warps 1-4 build the
-// weight operand (thread = weight row); warps 5-12 build the two activation operands (thread = token x one 32-element
-// block of the stage); warps 13-20 are the epilogue (thread = token lane x 64 rows).  Stages and the two D buffers are
+// The activation operands are converted ONCE per GEMM by two small kernels (a per-token range search for g, then the
+// high / low operand tiles written to a stream-ordered scratch buffer in the shared-memory layout of the GEMM kernel,
+// so that a stage's 32 KB arrive by one bulk asynchronous copy); the weight operand is built in shared memory by
+// producer warps straight from the quantized bytes (nibble -> 0x6400|q -> one HFMA2 with the sub-block scale).  Tiles use
+// the canonical K-major no-swizzle layout (8-row x 16-byte core matrices), four stages of 64 k-elements.  Warp roles
+// in a CTA of 18 warps (one 128-token x 128-row tile): warp 0 allocates TMEM and issues the MMAs from one thread; warps
+// 1-8 build the weight operand (thread = weight row x half of the stage's bytes); one thread of warp 9 requests the
+// activation operands; warps 10-17 are the epilogue (thread = token lane x 64 rows).  Stages and the two D buffers are
 // handed over through mbarriers (tcgen05.commit arrives on them when the MMAs have finished).  Every wait is bounded:
 // when a limit runs out the CTA raises an abort flag, its roles leave their loops, TMEM is freed and a status word
 // reports it (cera_cuda_kernel_status).
@@ -47,25 +50,29 @@ constexpr int TC_BM = 128;      // tokens per tile (TMEM lanes)
 constexpr int TC_BN = 128;      // weight rows per tile (TMEM columns)
 constexpr int TC_KS = 64;       // k elements per stage: two 32-element blocks, half a 128-weight task
 constexpr int TC_STAGES = 4;    // = stages per 256-element super-block
-constexpr int TC_W_WARPS = 4, TC_T_WARPS = 8, TC_EPI_WARPS = 8;
-constexpr int TC_THREADS = (1 + TC_W_WARPS + TC_T_WARPS + TC_EPI_WARPS) * 32;  // 672
+constexpr int TC_W_WARPS = 8, TC_EPI_WARPS = 8;
+constexpr int TC_THREADS = (2 + TC_W_WARPS + TC_EPI_WARPS) * 32;  // 576: MMA issue, weight producers, operand loader, epilogue
+constexpr int TC_IMG_THREADS = 256;                                   // the activation-image kernel: (token, block of the stage)
 constexpr uint32_t TC_OP_BYTES = TC_BM * TC_KS * 2;                      // one operand tile of a stage: 16 KB
 constexpr uint32_t TC_STAGE_BYTES = 3 * TC_OP_BYTES;                     // activations high, activations low, weights
 // per super-block, two slots: the min-term operands (16 k-columns each) and the row-side tables
 constexpr uint32_t TC_MINOP_BYTES = TC_BM * 16 * 2;                      // 4 KB: [2 k chunks][128 rows][8 f16]
 constexpr uint32_t TC_SLOT_BYTES = 2 * TC_MINOP_BYTES + 2 * TC_BN * 4;   // A, B, dval[128], dmin[128]
-constexpr uint32_t TC_TAIL_OFF = TC_STAGES * TC_STAGE_BYTES + 2 * TC_SLOT_BYTES;  // ginv[128], then barriers, TMEM address, abort flag
-constexpr uint32_t TC_SMEM_BYTES = TC_TAIL_OFF + TC_BM * 4 + 256;
+constexpr uint32_t TC_TAIL_OFF = TC_STAGES * TC_STAGE_BYTES + 2 * TC_SLOT_BYTES;  // barriers, TMEM address, abort flag
+constexpr uint32_t TC_SMEM_BYTES = TC_TAIL_OFF + 256;
 constexpr uint32_t TC_TMEM_COLS = 512;                                   // D0 [0,128) D1 [128,256) Dm [256,384) OUT [384,512)
 constexpr uint32_t TC_KC_STRIDE = TC_BM * 16;                            // bytes between 8-element k chunks: 2048
 
 struct TcParams {
     WeightView w;
-    ActView x;
     float *out;
     uint32_t m, n, k;
     uint32_t ldy, ldc;
     int epilogue;
+    // the activation operands of this GEMM, converted once (tc_token_image_kernel): per (token tile, stage) the high and
+    // the low operand tile, per (token tile, super-block) the token side of the min operand, per token 1 / g
+    const uint8_t *img, *img_min;
+    const float *ginv;
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------------
@@ -130,23 +137,96 @@ __device__ __forceinline__ void bytes_to_h1024(uint32_t v, __half2 &lo, __half2 
     hi = *reinterpret_cast<const __half2 *>(&b);
 }
 
+// g[token]: a power of two that brings every |xs_b * a| of the token below 2^15 (|a| <= 127, and |A_b| <= 4064 for the
+// min operand: 2^15 / 32 keeps both in range).  One warp per token (tokens past n repeat the last one).
+__global__ void tc_token_range_kernel(const ActView x, uint32_t n, uint32_t k, uint32_t n_pad, float *__restrict__ g_out, float *__restrict__ ginv_out) {
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= n_pad) return;
+    const uint32_t token = min(t, n - 1), nb32 = k >> 5;
+    float mx = 0.0f;
+    for (uint32_t b = lane; b < nb32; b += 32) {
+        const float v = fabsf(__ldg(x.scales + (size_t)token * nb32 + b));
+        mx = fmaxf(mx, v == v && v < 1.0e30f ? v : 0.0f);  // (scales beyond 1e30 are not activations: left out of the range search)
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float g = 1.0f;
+    if (mx > 0.0f) {
+        int e;
+        frexpf(mx * 4064.0f, &e);  // |xs_b * A_b| <= mx * 4064 < 2^e
+        g = ldexpf(1.0f, 15 - e);
+    }
+    if (lane == 0) {
+        g_out[t] = g;
+        ginv_out[t] = 1.0f / g;
+    }
+}
+
+// The activation operands of one (token tile, stage): v = (g * xs_b) * a for the 64 quants of the stage, as the top 11
+// significant bits of v (high operand) and the f16-rounded remainder (low operand), written in the shared-memory
+// layout of the GEMM kernel (chunk kc of token c at kc * 2048 + c * 16) so that a stage is one contiguous 32 KB copy;
+// and g * xs_b * A_b, high and low, into the token side of the super-block's min operand.  grid (token tiles, stages),
+// 256 threads: thread = (token, block of the stage).
+__global__ void __launch_bounds__(TC_IMG_THREADS) tc_token_image_kernel(const ActView x, uint32_t n, uint32_t k, const float *__restrict__ g_tab,
+                                                                         uint8_t *__restrict__ img, uint8_t *__restrict__ img_min) {
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t c = threadIdx.x >> 1, blk = threadIdx.x & 1, it = blockIdx.y, st = it % TC_STAGES, sb = it / TC_STAGES;
+    const uint32_t n_it = k / TC_KS, n_sb = k / 256, nb32 = k >> 5, nb16 = k >> 4;
+    const uint32_t token = min(blockIdx.x * TC_BM + c, n - 1);
+    const float g = g_tab[blockIdx.x * TC_BM + c];
+    const uint32_t xb = it * 2 + blk;  // this thread's 32-element activation block
+    const int8_t *src = x.quants + (size_t)token * k + (size_t)xb * 32;
+    const uint4 r0 = __ldg(reinterpret_cast<const uint4 *>(src)), r1 = __ldg(reinterpret_cast<const uint4 *>(src) + 1);
+    const float sg = __ldg(x.scales + (size_t)token * nb32 + xb) * g;
+    const int16_t *sm = reinterpret_cast<const int16_t *>(x.sums) + (size_t)token * nb16 + 2 * xb;
+    const float asum = (float)((int)__ldg(sm) + (int)__ldg(sm + 1));
+    uint8_t *op_hi = img + ((size_t)blockIdx.x * n_it + it) * (2 * TC_OP_BYTES), *op_lo = op_hi + TC_OP_BYTES;
+    const uint32_t words[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+    const float2 sg2 = make_float2(sg, sg);
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) {  // eight elements = one 16-byte k chunk of each operand
+        __half2 hi2[4], lo2[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t w = words[2 * ch + (q >> 1)];
+            const int e0 = (int)(int8_t)(w >> (16 * (q & 1))), e1 = (int)(int8_t)(w >> (16 * (q & 1) + 8));
+            const float2 v = __fmul2_rn(make_float2((float)e0, (float)e1), sg2);
+            // high part: the top 11 significant bits (exactly an f16 while v is in the normal range); low: the rest, rounded
+            const float2 vh = make_float2(__uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u), __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u));
+            const float2 vl = __fadd2_rn(v, make_float2(-vh.x, -vh.y));
+            hi2[q] = __float22half2_rn(vh);
+            lo2[q] = __float22half2_rn(vl);
+        }
+        *reinterpret_cast<uint4 *>(op_hi + op_off(4 * blk + ch, c)) = *reinterpret_cast<const uint4 *>(&hi2[0]);
+        *reinterpret_cast<uint4 *>(op_lo + op_off(4 * blk + ch, c)) = *reinterpret_cast<const uint4 *>(&lo2[0]);
+    }
+    {
+        // g * xs_b * A_b as a high and a low f16: block 2 st + blk of the super-block's min operand
+        const float v = sg * asum;
+        const float vh = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+        const __half2 hl = __floats2half2_rn(vh, v - vh);
+        uint8_t *slot = img_min + ((size_t)blockIdx.x * n_sb + sb) * TC_MINOP_BYTES;
+        *reinterpret_cast<uint32_t *>(slot + op_off(st >> 1, c) + ((st & 1) * 2 + blk) * 4) = *reinterpret_cast<const uint32_t *>(&hl);
+    }
+}
+
 template <int T>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p) {
     extern __shared__ __align__(1024) uint8_t tc_smem[];
     uint8_t *slots = tc_smem + TC_STAGES * TC_STAGE_BYTES;
-    float *ginv_tab = reinterpret_cast<float *>(tc_smem + TC_TAIL_OFF);  // [128]: 1 / g of every token lane
-    uint64_t *bars = reinterpret_cast<uint64_t *>(tc_smem + TC_TAIL_OFF + TC_BM * 4);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tc_smem + TC_TAIL_OFF);
     uint64_t *full_ab = bars, *empty_ab = bars + TC_STAGES, *full_d = bars + 2 * TC_STAGES, *empty_d = full_d + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC_STAGES + 4);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t col0 = blockIdx.x * TC_BM, row0 = blockIdx.y * TC_BN;
     const uint32_t n_sb = p.k / 256, n_it = n_sb * TC_STAGES;
-    const uint32_t nb32 = p.k >> 5, nb16 = p.k >> 4;
-
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
-            tma::mbar_init(full_ab + s, (TC_W_WARPS + TC_T_WARPS) * 32);  // every producer thread
+            tma::mbar_init(full_ab + s, TC_W_WARPS * 32 + 1);           // every weight-producer thread + the loader's expect_tx
             tma::mbar_init(empty_ab + s, 1);                              // the commit of the stage's MMAs
         }
         for (int b = 0; b < 2; ++b) {
@@ -207,28 +287,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
             }
         }
     } else if (warp <= TC_W_WARPS) {
-        // ---------------------------------------------------------------- weight operand: thread = weight row
-        const uint32_t r = tid - 32;
+        // ---------------------------------------------------------------- weight operand: thread = (weight row, half of the stage's bytes)
+        const uint32_t r = (tid - 32) >> 1, half = (tid - 32) & 1;
         const uint32_t row = min(row0 + r, p.m - 1);  // rows past the edge repeat the last one; their results are not stored
         // the raw bytes of a stage are fetched one stage ahead of their conversion (a thread converts every stage itself:
         // a global round trip per stage would bound the pipeline)
         struct RawW {
-            uint4 p0, p1, h, hb0, hb1;
+            uint4 pc, h, hb;
         };
         auto fetch = [&](uint32_t it) {
             RawW rw;
             const uint32_t st = it % TC_STAGES, sb = it / TC_STAGES, pair = st & 1, hf = st >> 1;
-            // the stage's 32 bytes: pieces 2 pair, 2 pair + 1 of the task (low nibbles = sub-block 2 pair, high = 2 pair + 1)
-            rw.p0 = ld_stream(q_piece_ptr(p.w, row, 4, (2 * sb + hf) * 4 + 2 * pair));
-            rw.p1 = ld_stream(q_piece_ptr(p.w, row, 4, (2 * sb + hf) * 4 + 2 * pair + 1));
+            // the stage's 32 bytes are pieces 2 pair, 2 pair + 1 of the task (low nibbles = sub-block 2 pair, high = 2 pair + 1);
+            // this thread takes piece 2 pair + half: elements [16 half, +16) of both sub-blocks
+            rw.pc = ld_stream(q_piece_ptr(p.w, row, 4, (2 * sb + hf) * 4 + 2 * pair + half));
             const size_t sbi = sb_index(p.w, row, sb);
             rw.h = __ldg(reinterpret_cast<const uint4 *>(p.w.hdr) + sbi);
-            rw.hb0 = make_uint4(0, 0, 0, 0);
-            rw.hb1 = rw.hb0;
-            if (T == CERA_TYPE_Q5_K) {
-                rw.hb0 = __ldg(reinterpret_cast<const uint4 *>(p.w.qh + sbi * 32));
-                rw.hb1 = __ldg(reinterpret_cast<const uint4 *>(p.w.qh + sbi * 32 + 16));
-            }
+            rw.hb = make_uint4(0, 0, 0, 0);
+            if (T == CERA_TYPE_Q5_K) rw.hb = __ldg(reinterpret_cast<const uint4 *>(p.w.qh + sbi * 32 + half * 16));
             return rw;
         };
         RawW nxt = fetch(0);
@@ -236,7 +312,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
             const uint32_t st = it % TC_STAGES, sb = it / TC_STAGES, pair = st & 1, hf = st >> 1;  // task 2 sb + hf, byte pair `pair`
             const RawW cur = nxt;
             if (it + 1 < n_it) nxt = fetch(it + 1);
-            const uint4 p0 = cur.p0, p1 = cur.p1, h = cur.h, hb0 = cur.hb0, hb1 = cur.hb1;
+            const uint4 v4 = cur.pc, h = cur.h, hbv = cur.hb;
             if (!tma::mbar_wait_blocking(empty_ab + st, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 4u)) break;
             // the slot of this super-block (tables, min operand) was last used by super-block sb - 2
             if (st == 0 && sb >= 2 && !tma::mbar_wait_blocking(empty_d + (sb & 1), ((sb - 2) >> 1) & 1, abort_flag, &g_tc_status, 4u)) break;
@@ -247,10 +323,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
             const uint32_t sc_lo = (scp >> (16 * pair)) & 0xFF, sc_hi = (scp >> (16 * pair + 8)) & 0xFF;
             const __half2 s_lo = __half2half2(__ushort2half_rn((unsigned short)sc_lo)), s_hi = __half2half2(__ushort2half_rn((unsigned short)sc_hi));
             const __half2 nb_lo = __hmul2(s_lo, __float2half2_rn(-1024.0f)), nb_hi = __hmul2(s_hi, __float2half2_rn(-1024.0f));
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const uint4 v4 = half ? p1 : p0;
-                const uint4 hbv = half ? hb1 : hb0;
+            {
                 const uint32_t wv[4] = {v4.x, v4.y, v4.z, v4.w}, hw[4] = {hbv.x, hbv.y, hbv.z, hbv.w};
                 __half2 lo8[8], hi8[8];  // 16 low-nibble and 16 high-nibble elements, two per half2
 #pragma unroll
@@ -276,7 +349,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
                 *reinterpret_cast<uint4 *>(opb + op_off(kc_hi, r)) = *reinterpret_cast<const uint4 *>(&hi8[0]);
                 *reinterpret_cast<uint4 *>(opb + op_off(kc_hi + 1, r)) = *reinterpret_cast<const uint4 *>(&hi8[4]);
             }
-            {
+            if (half == 0) {
                 // the mins of the stage's two blocks, each twice (for the high and the low part of the token side): four
                 // f16 = blocks 2 st, 2 st + 1 of the super-block's 16-column min operand
                 const uint32_t mn0 = (mnp >> (16 * pair)) & 0xFF, mn1 = (mnp >> (16 * pair + 8)) & 0xFF;
@@ -291,88 +364,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
             fence_async_smem();
             tma::mbar_arrive(full_ab + st);
         }
-    } else if (warp <= TC_W_WARPS + TC_T_WARPS) {
-        // ---------------------------------------------------------------- activation operands: thread = (token, block of the stage)
-        const uint32_t tt = tid - (1 + TC_W_WARPS) * 32, c = tt >> 1, blk = tt & 1;
-        const uint32_t token = min(col0 + c, p.n - 1);
-        const int8_t *src = p.x.quants + (size_t)token * p.k;
-        const float *xs_row = p.x.scales + (size_t)token * nb32;
-        const int16_t *sm_row = reinterpret_cast<const int16_t *>(p.x.sums) + (size_t)token * nb16;
-        // g: a power of two that brings every |xs_b * a| of the token below 2^15 (|a| <= 127, and |A_b| <= 4064 for the
-        // min operand: 2^15 / 32 keeps both in range); the token's two threads scan half of the blocks each
-        float g = 1.0f;
-        {
-            float mx = 0.0f;
-            for (uint32_t b = blk; b < nb32; b += 2) {
-                const float v = fabsf(__ldg(xs_row + b));
-                mx = fmaxf(mx, v == v && v < 1.0e30f ? v : 0.0f);  // (scales beyond 1e30 are not activations: left out of the range search)
+    } else if (warp == TC_W_WARPS + 1) {
+        // ---------------------------------------------------------------- activation operands: one thread asks for them
+        // (bulk asynchronous copies of the tiles tc_token_image_kernel wrote in this layout; 32 KB per stage, and the token
+        // side of the min operand with a super-block's first stage)
+        if (lane == 0) {
+            const uint8_t *img = p.img + (size_t)blockIdx.x * n_it * (2 * TC_OP_BYTES);
+            const uint8_t *img_min = p.img_min + (size_t)blockIdx.x * n_sb * TC_MINOP_BYTES;
+            for (uint32_t it = 0; it < n_it; ++it) {
+                const uint32_t st = it % TC_STAGES, sb = it / TC_STAGES;
+                if (!tma::mbar_wait_blocking(empty_ab + st, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) break;
+                if (st == 0 && sb >= 2 && !tma::mbar_wait_blocking(empty_d + (sb & 1), ((sb - 2) >> 1) & 1, abort_flag, &g_tc_status, 8u)) break;
+                tma::mbar_expect_tx(full_ab + st, 2 * TC_OP_BYTES + (st == 0 ? TC_MINOP_BYTES : 0));
+                tma::bulk_g2s(tc_smem + st * TC_STAGE_BYTES, img + (size_t)it * (2 * TC_OP_BYTES), 2 * TC_OP_BYTES, full_ab + st);
+                if (st == 0) tma::bulk_g2s(slots + (sb & 1) * TC_SLOT_BYTES, img_min + (size_t)sb * TC_MINOP_BYTES, TC_MINOP_BYTES, full_ab + st);
             }
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            if (mx > 0.0f) {
-                int e;
-                frexpf(mx * 4064.0f, &e);  // |xs_b * A_b| <= mx * 4064 < 2^e
-                g = ldexpf(1.0f, 15 - e);
-            }
-            if (blk == 0) ginv_tab[c] = 1.0f / g;  // published by the first full_ab arrival below
-        }
-        struct RawX {
-            uint4 r0, r1;
-            float xs;
-            int asum;
-        };
-        auto fetch = [&](uint32_t it) {
-            RawX rx;
-            const uint32_t xb = it * 2 + blk;  // this thread's 32-element activation block
-            rx.r0 = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)xb * 32));
-            rx.r1 = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)xb * 32) + 1);
-            rx.xs = __ldg(xs_row + xb);
-            rx.asum = (int)__ldg(sm_row + 2 * xb) + (int)__ldg(sm_row + 2 * xb + 1);
-            return rx;
-        };
-        RawX nxt = fetch(0);
-        for (uint32_t it = 0; it < n_it; ++it) {
-            const uint32_t st = it % TC_STAGES, sb = it / TC_STAGES;
-            const RawX cur = nxt;
-            if (it + 1 < n_it) nxt = fetch(it + 1);
-            const uint4 r0 = cur.r0, r1 = cur.r1;
-            const float sg = cur.xs * g;
-            const float asum = (float)cur.asum;
-            if (!tma::mbar_wait_blocking(empty_ab + st, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) break;
-            if (st == 0 && sb >= 2 && !tma::mbar_wait_blocking(empty_d + (sb & 1), ((sb - 2) >> 1) & 1, abort_flag, &g_tc_status, 8u)) break;
-            uint8_t *op_hi = tc_smem + st * TC_STAGE_BYTES, *op_lo = op_hi + TC_OP_BYTES;
-            uint8_t *slot = slots + (sb & 1) * TC_SLOT_BYTES;
-            const uint32_t words[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-            const float2 sg2 = make_float2(sg, sg);
-#pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {  // eight elements = one 16-byte k chunk of each operand
-                __half2 hi2[4], lo2[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint32_t w = words[2 * ch + (q >> 1)];
-                    const int e0 = (int)(int8_t)(w >> (16 * (q & 1))), e1 = (int)(int8_t)(w >> (16 * (q & 1) + 8));
-                    const float2 v = __fmul2_rn(make_float2((float)e0, (float)e1), sg2);
-                    // high part: the top 11 significant bits (exactly an f16 while v is in the normal range); low: the rest, rounded
-                    const float2 vh = make_float2(__uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u), __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u));
-                    const float2 vl = __fadd2_rn(v, make_float2(-vh.x, -vh.y));
-                    hi2[q] = __float22half2_rn(vh);
-                    lo2[q] = __float22half2_rn(vl);
-                }
-                *reinterpret_cast<uint4 *>(op_hi + op_off(4 * blk + ch, c)) = *reinterpret_cast<const uint4 *>(&hi2[0]);
-                *reinterpret_cast<uint4 *>(op_lo + op_off(4 * blk + ch, c)) = *reinterpret_cast<const uint4 *>(&lo2[0]);
-            }
-            {
-                // g * xs_b * A_b as a high and a low f16: block 2 st + blk of the super-block's min operand
-                const float v = sg * asum;
-                const float vh = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
-                const __half2 hl = __floats2half2_rn(vh, v - vh);
-                *reinterpret_cast<uint32_t *>(slot + op_off(st >> 1, c) + ((st & 1) * 2 + blk) * 4) = *reinterpret_cast<const uint32_t *>(&hl);
-            }
-            fence_async_smem();
-            tma::mbar_arrive(full_ab + st);
         }
     } else {
         // ---------------------------------------------------------------- epilogue: thread = (token lane, 64 rows)
-        const uint32_t e = warp - (1 + TC_W_WARPS + TC_T_WARPS), quad = warp & 3, ch = e >> 2;  // a warp reaches TMEM lanes [32 (warp % 4), +32)
+        const uint32_t e = warp - (2 + TC_W_WARPS), quad = warp & 3, ch = e >> 2;  // a warp reaches TMEM lanes [32 (warp % 4), +32)
         const uint32_t tl = quad * 32 + lane;                                                    // token lane
         const uint32_t lane_addr = tmem + ((quad * 32) << 16);
         float ginv = 1.0f;
@@ -384,7 +394,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
                 break;
             }
             tc_fence_after();
-            if (sb == 0) ginv = ginv_tab[tl];  // written before the first producer arrival, which the MMAs of this super-block followed
+            if (sb == 0) ginv = __ldg(p.ginv + col0 + tl);
             const float *dval = reinterpret_cast<const float *>(slots + buf * TC_SLOT_BYTES + 2 * TC_MINOP_BYTES);
             // out[row] += (d[row] * D - dmin[row] * Dm) / g, the running sum in TMEM
 #pragma unroll 1
@@ -483,9 +493,26 @@ int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *o
     }();
     if (off || n <= 32 || w.k % 256 || (w.type != CERA_TYPE_Q4_K && w.type != CERA_TYPE_Q5_K)) return CERA_CUDA_OK;
     if ((uintptr_t)x.quants % 16 || (uintptr_t)x.scales % 16 || (uintptr_t)x.sums % 16) return CERA_CUDA_OK;
+    // the activation operands, converted once for all row tiles: a stream-ordered scratch allocation that lives for this
+    // call (token tiles x stages x 32 KB, the min operand's token side, g and 1 / g)
+    const uint32_t tiles = (uint32_t)((n + TC_BM - 1) / TC_BM), n_pad = tiles * TC_BM, n_it = w.k / TC_KS, n_sb = w.k / 256;
+    const size_t img_bytes = (size_t)tiles * n_it * (2 * TC_OP_BYTES), min_bytes = (size_t)tiles * n_sb * TC_MINOP_BYTES;
+    uint8_t *scratch = nullptr;
+    CERA_CUDA_TRY(cudaMallocAsync((void **)&scratch, img_bytes + min_bytes + (size_t)n_pad * 8, st));
+    float *g_tab = reinterpret_cast<float *>(scratch + img_bytes + min_bytes), *ginv_tab = g_tab + n_pad;
+    int32_t rc = check_cuda(launch_k(tc_token_range_kernel, dim3((n_pad + 7) / 8), dim3(256), 0, st, x, (uint32_t)n, (uint32_t)w.k, n_pad, g_tab, ginv_tab),
+                            "gemm (tcgen05) token range launch");
+    if (rc == CERA_CUDA_OK)
+        rc = check_cuda(launch_k(tc_token_image_kernel, dim3(tiles, n_it), dim3(TC_IMG_THREADS), 0, st, x, (uint32_t)n, (uint32_t)w.k, (const float *)g_tab,
+                                 scratch, scratch + img_bytes),
+                        "gemm (tcgen05) token image launch");
+    count_launch();
+    count_launch();
     TcParams p{};
     p.w = w;
-    p.x = x;
+    p.img = scratch;
+    p.img_min = scratch + img_bytes;
+    p.ginv = ginv_tab;
     p.out = out;
     p.m = w.m;
     p.n = (uint32_t)n;
@@ -494,8 +521,9 @@ int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *o
     p.ldc = (uint32_t)ldc;
     p.epilogue = epilogue;
     *taken = true;
-    if (w.type == CERA_TYPE_Q4_K) return launch_tc_typed<CERA_TYPE_Q4_K>(p, st);
-    return launch_tc_typed<CERA_TYPE_Q5_K>(p, st);
+    if (rc == CERA_CUDA_OK) rc = w.type == CERA_TYPE_Q4_K ? launch_tc_typed<CERA_TYPE_Q4_K>(p, st) : launch_tc_typed<CERA_TYPE_Q5_K>(p, st);
+    cudaFreeAsync(scratch, st);  // after the kernels above, in stream order
+    return rc;
 }
 
 }  // namespace cera
