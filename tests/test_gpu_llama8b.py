@@ -8,7 +8,7 @@ import os
 import numpy as np
 import pytest
 
-from gpu_util import TIE_FRACTION_TIGHT, need_gpu
+from gpu_util import TIE_FRACTION_LOOSE, TIE_FRACTION_TIGHT, need_gpu
 
 pytestmark = pytest.mark.gpu
 
@@ -55,13 +55,15 @@ def test_llama8b_greedy_stream_equals_the_cpu_reference_stream():
 def test_llama8b_batched_prompt_agrees_with_the_per_token_prompt():
     """The same prompt through the batched kernels (tcgen05 / mma GEMMs, tiled attention - toleranced by nature, as the
     reference's own batched prompt is against its per-token path, cera/tests/llama_batched_prefill_parity.rs:74-147)
-    against the per-token prompt of the reference stream: the top logit agrees within 1 %, and where the greedy streams
-    part, the two picks are a near-tie by the reference's gap rule (relative logit gap below 2 %,
-    cera/tests/gpu_transformer_parity.rs:208-232) and the device picked the reference's runner-up.  The reference also
-    asks for four matching tokens before a flip; that part is not asserted here: it tells a wrong rope / scalar (which
-    perturbs every step) from noise on TRAINED checkpoints, whose logits are peaked, while this random-init model's
-    top two logits are within 0.5 % of each other at every other step, so the place of the first flip carries no
-    information (measured: the streams part at token 2, at a pair 0.45 % apart)."""
+    against the per-token prompt: whole-vector cosine of the logits at least 0.99 (the reference's floor for paths whose
+    reduction is tiled differently, same file), the batched pick inside the reference's loose tie window (6 % of the
+    per-token top-8 spread), and where the greedy streams part, the two picks are a near-tie by the reference's gap rule
+    (relative logit gap below 2 %, cera/tests/gpu_transformer_parity.rs:208-232) and the device picked the reference's
+    runner-up.  The per-token logits come from the device's reference-order kernels, which the test above (and the
+    top-logit check here) pins to the CPU reference stream.  512 positions x 32 layers of int8 re-quantization sit
+    between the two prompt paths: on this random-init model two toleranced GEMM kernels that agree to 1e-6 per
+    operator end 0.997 apart in cosine, and its top two logits are within 0.5 % of each other at every other step, so
+    neither a tight logit bar nor the place of the first flip carries information."""
     need_gpu()
     from cera_b200 import synth
     with open(GOLDEN) as f:
@@ -71,12 +73,18 @@ def test_llama8b_batched_prompt_agrees_with_the_per_token_prompt():
     model = synth.build_llama(cfg, seed=gold["model_seed"], max_seq_len=plen + N_DECODE + 8)
     try:
         prompt = synth.prompt_tokens(plen, cfg["vocab_size"], seed=gold["prompt_seed"])
+        for pos, t in enumerate(prompt[:-1]):
+            model.forward_prefill(np.array([t], dtype=np.uint32), pos, want_logits=False)
+        ref = model.forward(int(prompt[-1]), plen - 1).copy()
+        assert int(np.argmax(ref)) == gold["stream"][0]
+        assert abs(float(ref.max()) - gold["top1_logit"][0]) <= 1e-3 * abs(gold["top1_logit"][0]) + 1e-4
+        model.truncate_kv(0)
         logits = model.forward_prefill(prompt, 0)
+        cos = float(np.dot(ref, logits) / (np.linalg.norm(ref) * np.linalg.norm(logits)))
+        assert cos >= 0.99, f"batched prompt logits: cosine {cos:.5f} against the per-token prompt"
         first = int(np.argmax(logits))
-        # 512 positions x 32 layers of int8 re-quantization sit between the two prompt paths (measured: 0.55 % of the
-        # top logit); the whole-vector cosine bar of the reference's test needs the reference logits, which the golden
-        # file does not carry, so the top logit stands in at 1 %
-        assert abs(float(logits[gold["stream"][0]]) - gold["top1_logit"][0]) <= 1e-2 * abs(gold["top1_logit"][0])
+        top8 = np.sort(ref)[-8:]
+        assert float(ref.max() - ref[first]) <= TIE_FRACTION_LOOSE * float(top8[-1] - top8[0]), (first, int(np.argmax(ref)))
         toks, _ = model.generate_greedy(first, plen, N_DECODE - 1)
         stream = [first] + [int(t) for t in toks]
         fork = next((i for i, (g, w) in enumerate(zip(stream, gold["stream"][:N_DECODE])) if g != w), None)
