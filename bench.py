@@ -308,10 +308,15 @@ def attention_microbench(torch, cb, ctx, f16, iters):
     return kv_bytes + 2 * nh * hd * 4, us
 
 
-def gemm_microbench(torch, cb, tname, m, k, n, iters):
-    """Prefill GEMM out[m x n] = W x X for pre-quantized columns: CUDA events over a graph of `iters` launches."""
+def gemm_microbench(torch, cb, tname, m, k, n, iters, image=False):
+    """Prefill GEMM out[m x n] = W x X for pre-quantized columns: CUDA events over a graph of `iters` launches.
+    image: the weight holds its resident f16 operand image (what a model's layer weights hold after the first batched
+    prompt); None is returned when the weight takes none."""
     t, blk, bb = BLOCKS[tname]
     w = cb.QuantWeight(t, m, k, cb.quantize_weights(t, cb.synth_normal(m * k, seed=3, sigma=0.02)))
+    if image and not w.prepare_gemm():
+        w.close()
+        return None
     acts = cb.quantize_q8_0(cb.synth_normal(n * k, seed=5, sigma=1.0), k=k, n=n)
     out = torch.empty(m, n, device="cuda")
     cb.gemm_preq(w, acts, out)
@@ -673,11 +678,14 @@ def main():
             with open(mp) as f:
                 dense, dense_src = json.load(f).get("bf16_tflops", dense), "measured (cuBLAS bf16, burst)"
         for tname, m, k in [("q4_k", 4096, 4096), ("q4_k", 14336, 4096), ("q6_k", 4096, 14336), ("q5_k", 4096, 4096)]:
-            for n in (8, 64, 256, 512):
-                ops, us = gemm_microbench(torch, cb, tname, m, k, n, max(3, args.iters // (4 if n > 64 else 1)))
+            for n, image in [(8, False), (64, False), (256, False), (512, False), (64, True), (256, True), (512, True), (2048, True)]:
+                r = gemm_microbench(torch, cb, tname, m, k, n, max(3, args.iters // (4 if n > 64 else 1)), image=image)
+                if r is None:
+                    continue
+                ops, us = r
                 # the tcgen05 kernel issues kind::f16 MMAs (exact small integers in f16): its tensor ceiling is the dense
                 # 16-bit rate, measured on this pool with cuBLAS bf16 (MEASURED_PEAKS.json); the nominal int8 figure beside it
-                emit(json.dumps({"type": tname, "m": m, "k": k, "n": n, "us": round(us, 2),
+                emit(json.dumps({"type": tname, "m": m, "k": k, "n": n, "weight_image": image, "us": round(us, 2),
                                   "tops": round(ops / us / 1e6, 2),
                                   "frac_of_measured_dense_16bit": round(ops / us / 1e6 / dense, 4), "dense_16bit_tflops": dense,
                                   "dense_source": dense_src, "frac_of_int8_nominal_4500": round(ops / us / 1e6 / 4500, 4)}))

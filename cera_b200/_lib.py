@@ -37,6 +37,7 @@ SIGNATURES = {
     "cera_cuda_device_count": (_i32, [C.POINTER(_i32)]),
     "cera_cuda_weight_create": (_i32, [_i32, _sz, _sz, _p, _sz, C.POINTER(_p)]),
     "cera_cuda_weight_free": (None, [_p]),
+    "cera_cuda_weight_prepare_gemm": (_i32, [_p, C.POINTER(_i32)]),
     "cera_cuda_weight_info": (_i32, [_p, C.POINTER(_i32), C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz)]),
     "cera_cuda_dequantize_rows": (_i32, [_p, _sz, _sz, _p, _p]),
     "cera_cuda_quantize_q8_0": (_i32, [_p, _sz, _sz, _p, _p, _p, _p]),

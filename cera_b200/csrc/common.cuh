@@ -55,6 +55,7 @@ struct WeightView {
     const uint8_t *qh;   // high-bit plane (Q5_K, Q6_K)
     const uint8_t *hdr;  // scale plane (see table)
     const uint8_t *d;    // Q6_K super-scale plane
+    const uint8_t *tc;   // optional: f16 operand image for the tcgen05 GEMM (Q4_K / Q5_K), null without one
 };
 
 struct TypeInfo {

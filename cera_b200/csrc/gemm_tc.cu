@@ -39,6 +39,7 @@
 
 #include "gemv_task.cuh"
 #include "tma.cuh"
+#include "weight.h"
 
 namespace cera {
 
@@ -52,15 +53,19 @@ constexpr int TC_KS = 64;       // k elements per stage: two 32-element blocks, 
 constexpr int TC_STAGES = 4;    // = stages per 256-element super-block
 constexpr int TC_W_WARPS = 8, TC_EPI_WARPS = 8;
 constexpr int TC_THREADS = (2 + TC_W_WARPS + TC_EPI_WARPS) * 32;  // 576: MMA issue, weight producers, operand loader, epilogue
+constexpr int TC_THREADS_IMG = (2 + TC_EPI_WARPS) * 32;            // 320: with a resident weight image there are no weight producers
 constexpr int TC_IMG_THREADS = 256;                                   // the activation-image kernel: (token, block of the stage)
 constexpr uint32_t TC_OP_BYTES = TC_BM * TC_KS * 2;                      // one operand tile of a stage: 16 KB
 constexpr uint32_t TC_STAGE_BYTES = 3 * TC_OP_BYTES;                     // activations high, activations low, weights
 // per super-block, two slots: the min-term operands (16 k-columns each) and the row-side tables
 constexpr uint32_t TC_MINOP_BYTES = TC_BM * 16 * 2;                      // 4 KB: [2 k chunks][128 rows][8 f16]
 constexpr uint32_t TC_SLOT_BYTES = 2 * TC_MINOP_BYTES + 2 * TC_BN * 4;   // A, B, dval[128], dmin[128]
+// resident weight image (tc_weight_image_kernel): per (row tile, stage) one operand tile; per (row tile, super-block) the
+// row side of the min operand followed by dval[128], dmin[128] - the tail of a slot, one copy
+constexpr uint32_t TC_SIDE_BYTES = TC_MINOP_BYTES + 2 * TC_BN * 4;        // 5 KB
 constexpr uint32_t TC_TAIL_OFF = TC_STAGES * TC_STAGE_BYTES + 2 * TC_SLOT_BYTES;  // barriers, TMEM address, abort flag
 constexpr uint32_t TC_SMEM_BYTES = TC_TAIL_OFF + 256;
-constexpr uint32_t TC_TMEM_COLS = 512;                                   // D0 [0,128) D1 [128,256) Dm [256,384) OUT [384,512)
+constexpr uint32_t TC_TMEM_COLS = 512;  // D0 [0,128) D1 [128,256), then Dm [256,384) OUT [384,512) or, with the weight image, Dm0 Dm1
 constexpr uint32_t TC_KC_STRIDE = TC_BM * 16;                            // bytes between 8-element k chunks: 2048
 
 struct TcParams {
@@ -213,8 +218,89 @@ __global__ void __launch_bounds__(TC_IMG_THREADS) tc_token_image_kernel(const Ac
     }
 }
 
+// ---- the weight operand of one stage: thread = (weight row r of the tile, half of the stage's bytes) -------------------
+struct TcRawW {
+    uint4 pc, h, hb;
+};
+// The stage's 32 quant bytes of a row are pieces 2 pair, 2 pair + 1 of the task (low nibbles = sub-block 2 pair, high =
+// 2 pair + 1); the thread takes piece 2 pair + half: elements [16 half, +16) of both sub-blocks.
 template <int T>
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p) {
+__device__ __forceinline__ TcRawW tc_fetch_w(const WeightView &w, uint32_t row, uint32_t half, uint32_t it) {
+    TcRawW rw;
+    const uint32_t st = it % TC_STAGES, sb = it / TC_STAGES, pair = st & 1, hf = st >> 1;
+    rw.pc = ld_stream(q_piece_ptr(w, row, 4, (2 * sb + hf) * 4 + 2 * pair + half));
+    const size_t sbi = sb_index(w, row, sb);
+    rw.h = __ldg(reinterpret_cast<const uint4 *>(w.hdr) + sbi);
+    rw.hb = make_uint4(0, 0, 0, 0);
+    if (T == CERA_TYPE_Q5_K) rw.hb = __ldg(reinterpret_cast<const uint4 *>(w.qh + sbi * 32 + half * 16));
+    return rw;
+}
+// sc * q as f16 into the operand tile `opb`; with half == 0 also the stage's two mins into the row side of the min
+// operand `bmin` and, with the super-block's first stage, d and dmin into `dval`.  The destinations are shared memory in
+// the GEMM kernel and global memory when the resident image is built.
+template <int T>
+__device__ __forceinline__ void tc_convert_w(const TcRawW &cur, uint32_t r, uint32_t half, uint32_t st, uint8_t *opb, uint8_t *bmin, float *dval) {
+    const uint32_t pair = st & 1, hf = st >> 1;  // task 2 sb + hf, byte pair `pair`
+    const uint4 v4 = cur.pc, h = cur.h, hbv = cur.hb;
+    uint32_t scp, mnp;
+    kq_quad(h, hf, scp, mnp);
+    const uint32_t sc_lo = (scp >> (16 * pair)) & 0xFF, sc_hi = (scp >> (16 * pair + 8)) & 0xFF;
+    const __half2 s_lo = __half2half2(__ushort2half_rn((unsigned short)sc_lo)), s_hi = __half2half2(__ushort2half_rn((unsigned short)sc_hi));
+    const __half2 nb_lo = __hmul2(s_lo, __float2half2_rn(-1024.0f)), nb_hi = __hmul2(s_hi, __float2half2_rn(-1024.0f));
+    {
+        const uint32_t wv[4] = {v4.x, v4.y, v4.z, v4.w}, hw[4] = {hbv.x, hbv.y, hbv.z, hbv.w};
+        __half2 lo8[8], hi8[8];  // 16 low-nibble and 16 high-nibble elements, two per half2
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t lo = wv[i] & 0x0F0F0F0Fu, hi = (wv[i] >> 4) & 0x0F0F0F0Fu;
+            if (T == CERA_TYPE_Q5_K) {
+                const int sh = 4 * hf + 2 * pair;
+                lo |= ((hw[i] >> sh) & 0x01010101u) << 4;
+                hi |= ((hw[i] >> (sh + 1)) & 0x01010101u) << 4;
+            }
+            __half2 a, b;
+            bytes_to_h1024(lo, a, b);
+            lo8[2 * i] = __hfma2(a, s_lo, nb_lo);  // (1024 + q) * sc - 1024 * sc = q * sc, one rounding of an exact value
+            lo8[2 * i + 1] = __hfma2(b, s_lo, nb_lo);
+            bytes_to_h1024(hi, a, b);
+            hi8[2 * i] = __hfma2(a, s_hi, nb_hi);
+            hi8[2 * i + 1] = __hfma2(b, s_hi, nb_hi);
+        }
+        // low nibbles: elements [16 half, +16) of the stage's first block; high nibbles: the same of its second block
+        const uint32_t kc_lo = 2 * half, kc_hi = kc_lo + 4;
+        *reinterpret_cast<uint4 *>(opb + op_off(kc_lo, r)) = *reinterpret_cast<const uint4 *>(&lo8[0]);
+        *reinterpret_cast<uint4 *>(opb + op_off(kc_lo + 1, r)) = *reinterpret_cast<const uint4 *>(&lo8[4]);
+        *reinterpret_cast<uint4 *>(opb + op_off(kc_hi, r)) = *reinterpret_cast<const uint4 *>(&hi8[0]);
+        *reinterpret_cast<uint4 *>(opb + op_off(kc_hi + 1, r)) = *reinterpret_cast<const uint4 *>(&hi8[4]);
+    }
+    if (half == 0) {
+        // the mins of the stage's two blocks, each twice (for the high and the low part of the token side): four
+        // f16 = blocks 2 st, 2 st + 1 of the super-block's 16-column min operand
+        const uint32_t mn0 = (mnp >> (16 * pair)) & 0xFF, mn1 = (mnp >> (16 * pair + 8)) & 0xFF;
+        __half2 m2[2] = {__half2half2(__ushort2half_rn((unsigned short)mn0)), __half2half2(__ushort2half_rn((unsigned short)mn1))};
+        *reinterpret_cast<uint2 *>(bmin + op_off(st >> 1, r) + (st & 1) * 8) = *reinterpret_cast<const uint2 *>(&m2[0]);
+        if (st == 0) {
+            dval[r] = h2f((uint16_t)(h.x & 0xFFFF));
+            dval[TC_BN + r] = h2f((uint16_t)(h.x >> 16));
+        }
+    }
+}
+
+// The resident weight image: every stage's weight operand tile and every super-block's row-side tables, converted once
+// (when the weight is prepared) into the shared-memory layout of the GEMM kernel.  grid (stages, row tiles), 256
+// threads = (row, half) as the producer warps of the GEMM kernel.
+template <int T>
+__global__ void __launch_bounds__(TC_W_WARPS * 32) tc_weight_image_kernel(const WeightView w, uint8_t *__restrict__ img, uint8_t *__restrict__ side) {
+    const uint32_t r = threadIdx.x >> 1, half = threadIdx.x & 1, it = blockIdx.x, tile = blockIdx.y;
+    const uint32_t n_it = w.k / TC_KS, n_sb = w.k / 256, st = it % TC_STAGES, sb = it / TC_STAGES;
+    const uint32_t row = min(tile * TC_BN + r, w.m - 1);  // rows past the edge repeat the last one; their results are not stored
+    uint8_t *sd = side + ((size_t)tile * n_sb + sb) * TC_SIDE_BYTES;
+    tc_convert_w<T>(tc_fetch_w<T>(w, row, half, it), r, half, st, img + ((size_t)tile * n_it + it) * TC_OP_BYTES, sd,
+                    reinterpret_cast<float *>(sd + TC_MINOP_BYTES));
+}
+
+template <int T, bool IMG>
+__global__ void __launch_bounds__(IMG ? TC_THREADS_IMG : TC_THREADS, 1) gemm_tc_kernel(const TcParams p) {
     extern __shared__ __align__(1024) uint8_t tc_smem[];
     uint8_t *slots = tc_smem + TC_STAGES * TC_STAGE_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(tc_smem + TC_TAIL_OFF);
@@ -224,9 +310,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t col0 = blockIdx.x * TC_BM, row0 = blockIdx.y * TC_BN;
     const uint32_t n_sb = p.k / 256, n_it = n_sb * TC_STAGES;
+    constexpr int TC_LOADER_WARP = IMG ? 1 : TC_W_WARPS + 1;  // the epilogue warps follow it
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
-            tma::mbar_init(full_ab + s, TC_W_WARPS * 32 + 1);           // every weight-producer thread + the loader's expect_tx
+            tma::mbar_init(full_ab + s, IMG ? 1 : TC_W_WARPS * 32 + 1);  // (every weight-producer thread +) the loader's expect_tx
             tma::mbar_init(empty_ab + s, 1);                              // the commit of the stage's MMAs
         }
         for (int b = 0; b < 2; ++b) {
@@ -272,121 +359,142 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
                         tc_mma_f16(tmem + buf * TC_BN, smem_desc(a_lo + 2 * ks * TC_KC_STRIDE, TC_KC_STRIDE, 128), bd, idesc, 1);
                     }
                     if (st + 1 == (uint32_t)TC_STAGES) {
-                        // the super-block's min term.  Dm has one buffer: the epilogue must have read super-block sb - 1's
-                        if (sb && !tma::mbar_wait_blocking(empty_d + (buf ^ 1), ((sb - 1) >> 1) & 1, abort_flag, &g_tc_status, 2u)) {
+                        // the super-block's min term.  Without the weight image Dm has one buffer (the fourth TMEM region holds
+                        // the running output): the epilogue must have read super-block sb - 1's
+                        if (!IMG && sb && !tma::mbar_wait_blocking(empty_d + (buf ^ 1), ((sb - 1) >> 1) & 1, abort_flag, &g_tc_status, 2u)) {
                             ok = false;
                             break;
                         }
                         tc_fence_after();
                         const uint32_t slot = tma::smem_u32(slots + buf * TC_SLOT_BYTES);
-                        tc_mma_f16(tmem + 2 * TC_BN, smem_desc(slot, TC_KC_STRIDE, 128), smem_desc(slot + TC_MINOP_BYTES, TC_KC_STRIDE, 128), idesc, 0);
+                        tc_mma_f16(tmem + (IMG ? 2 + buf : 2) * TC_BN, smem_desc(slot, TC_KC_STRIDE, 128), smem_desc(slot + TC_MINOP_BYTES, TC_KC_STRIDE, 128),
+                                   idesc, 0);
                     }
                     tc_commit(empty_ab + st);
                 }
                 if (ok) tc_commit(full_d + buf);
             }
         }
-    } else if (warp <= TC_W_WARPS) {
+    } else if (!IMG && warp <= TC_W_WARPS) {
         // ---------------------------------------------------------------- weight operand: thread = (weight row, half of the stage's bytes)
         const uint32_t r = (tid - 32) >> 1, half = (tid - 32) & 1;
         const uint32_t row = min(row0 + r, p.m - 1);  // rows past the edge repeat the last one; their results are not stored
         // the raw bytes of a stage are fetched one stage ahead of their conversion (a thread converts every stage itself:
         // a global round trip per stage would bound the pipeline)
-        struct RawW {
-            uint4 pc, h, hb;
-        };
-        auto fetch = [&](uint32_t it) {
-            RawW rw;
-            const uint32_t st = it % TC_STAGES, sb = it / TC_STAGES, pair = st & 1, hf = st >> 1;
-            // the stage's 32 bytes are pieces 2 pair, 2 pair + 1 of the task (low nibbles = sub-block 2 pair, high = 2 pair + 1);
-            // this thread takes piece 2 pair + half: elements [16 half, +16) of both sub-blocks
-            rw.pc = ld_stream(q_piece_ptr(p.w, row, 4, (2 * sb + hf) * 4 + 2 * pair + half));
-            const size_t sbi = sb_index(p.w, row, sb);
-            rw.h = __ldg(reinterpret_cast<const uint4 *>(p.w.hdr) + sbi);
-            rw.hb = make_uint4(0, 0, 0, 0);
-            if (T == CERA_TYPE_Q5_K) rw.hb = __ldg(reinterpret_cast<const uint4 *>(p.w.qh + sbi * 32 + half * 16));
-            return rw;
-        };
-        RawW nxt = fetch(0);
+        TcRawW nxt = tc_fetch_w<T>(p.w, row, half, 0);
         for (uint32_t it = 0; it < n_it; ++it) {
-            const uint32_t st = it % TC_STAGES, sb = it / TC_STAGES, pair = st & 1, hf = st >> 1;  // task 2 sb + hf, byte pair `pair`
-            const RawW cur = nxt;
-            if (it + 1 < n_it) nxt = fetch(it + 1);
-            const uint4 v4 = cur.pc, h = cur.h, hbv = cur.hb;
+            const uint32_t st = it % TC_STAGES, sb = it / TC_STAGES;
+            const TcRawW cur = nxt;
+            if (it + 1 < n_it) nxt = tc_fetch_w<T>(p.w, row, half, it + 1);
             if (!tma::mbar_wait_blocking(empty_ab + st, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 4u)) break;
             // the slot of this super-block (tables, min operand) was last used by super-block sb - 2
             if (st == 0 && sb >= 2 && !tma::mbar_wait_blocking(empty_d + (sb & 1), ((sb - 2) >> 1) & 1, abort_flag, &g_tc_status, 4u)) break;
-            uint8_t *opb = tc_smem + st * TC_STAGE_BYTES + 2 * TC_OP_BYTES;
             uint8_t *slot = slots + (sb & 1) * TC_SLOT_BYTES;
-            uint32_t scp, mnp;
-            kq_quad(h, hf, scp, mnp);
-            const uint32_t sc_lo = (scp >> (16 * pair)) & 0xFF, sc_hi = (scp >> (16 * pair + 8)) & 0xFF;
-            const __half2 s_lo = __half2half2(__ushort2half_rn((unsigned short)sc_lo)), s_hi = __half2half2(__ushort2half_rn((unsigned short)sc_hi));
-            const __half2 nb_lo = __hmul2(s_lo, __float2half2_rn(-1024.0f)), nb_hi = __hmul2(s_hi, __float2half2_rn(-1024.0f));
-            {
-                const uint32_t wv[4] = {v4.x, v4.y, v4.z, v4.w}, hw[4] = {hbv.x, hbv.y, hbv.z, hbv.w};
-                __half2 lo8[8], hi8[8];  // 16 low-nibble and 16 high-nibble elements, two per half2
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint32_t lo = wv[i] & 0x0F0F0F0Fu, hi = (wv[i] >> 4) & 0x0F0F0F0Fu;
-                    if (T == CERA_TYPE_Q5_K) {
-                        const int sh = 4 * hf + 2 * pair;
-                        lo |= ((hw[i] >> sh) & 0x01010101u) << 4;
-                        hi |= ((hw[i] >> (sh + 1)) & 0x01010101u) << 4;
-                    }
-                    __half2 a, b;
-                    bytes_to_h1024(lo, a, b);
-                    lo8[2 * i] = __hfma2(a, s_lo, nb_lo);  // (1024 + q) * sc - 1024 * sc = q * sc, one rounding of an exact value
-                    lo8[2 * i + 1] = __hfma2(b, s_lo, nb_lo);
-                    bytes_to_h1024(hi, a, b);
-                    hi8[2 * i] = __hfma2(a, s_hi, nb_hi);
-                    hi8[2 * i + 1] = __hfma2(b, s_hi, nb_hi);
-                }
-                // low nibbles: elements [16 half, +16) of the stage's first block; high nibbles: the same of its second block
-                const uint32_t kc_lo = 2 * half, kc_hi = kc_lo + 4;
-                *reinterpret_cast<uint4 *>(opb + op_off(kc_lo, r)) = *reinterpret_cast<const uint4 *>(&lo8[0]);
-                *reinterpret_cast<uint4 *>(opb + op_off(kc_lo + 1, r)) = *reinterpret_cast<const uint4 *>(&lo8[4]);
-                *reinterpret_cast<uint4 *>(opb + op_off(kc_hi, r)) = *reinterpret_cast<const uint4 *>(&hi8[0]);
-                *reinterpret_cast<uint4 *>(opb + op_off(kc_hi + 1, r)) = *reinterpret_cast<const uint4 *>(&hi8[4]);
-            }
-            if (half == 0) {
-                // the mins of the stage's two blocks, each twice (for the high and the low part of the token side): four
-                // f16 = blocks 2 st, 2 st + 1 of the super-block's 16-column min operand
-                const uint32_t mn0 = (mnp >> (16 * pair)) & 0xFF, mn1 = (mnp >> (16 * pair + 8)) & 0xFF;
-                __half2 m2[2] = {__half2half2(__ushort2half_rn((unsigned short)mn0)), __half2half2(__ushort2half_rn((unsigned short)mn1))};
-                *reinterpret_cast<uint2 *>(slot + TC_MINOP_BYTES + op_off(st >> 1, r) + (st & 1) * 8) = *reinterpret_cast<const uint2 *>(&m2[0]);
-                if (st == 0) {
-                    float *dval = reinterpret_cast<float *>(slot + 2 * TC_MINOP_BYTES);
-                    dval[r] = h2f((uint16_t)(h.x & 0xFFFF));
-                    dval[TC_BN + r] = h2f((uint16_t)(h.x >> 16));
-                }
-            }
+            tc_convert_w<T>(cur, r, half, st, tc_smem + st * TC_STAGE_BYTES + 2 * TC_OP_BYTES, slot + TC_MINOP_BYTES,
+                            reinterpret_cast<float *>(slot + 2 * TC_MINOP_BYTES));
             fence_async_smem();
             tma::mbar_arrive(full_ab + st);
         }
-    } else if (warp == TC_W_WARPS + 1) {
+    } else if (warp == TC_LOADER_WARP) {
         // ---------------------------------------------------------------- activation operands: one thread asks for them
         // (bulk asynchronous copies of the tiles tc_token_image_kernel wrote in this layout; 32 KB per stage, and the token
         // side of the min operand with a super-block's first stage)
         if (lane == 0) {
             const uint8_t *img = p.img + (size_t)blockIdx.x * n_it * (2 * TC_OP_BYTES);
             const uint8_t *img_min = p.img_min + (size_t)blockIdx.x * n_sb * TC_MINOP_BYTES;
+            // the resident weight image of this row tile (null without one): operand tiles, then the per-super-block sides
+            const uint32_t tiles_m = (p.m + TC_BN - 1) / TC_BN;
+            const uint8_t *wimg = IMG ? p.w.tc + (size_t)blockIdx.y * n_it * TC_OP_BYTES : nullptr;
+            const uint8_t *wside = IMG ? p.w.tc + (size_t)tiles_m * n_it * TC_OP_BYTES + (size_t)blockIdx.y * n_sb * TC_SIDE_BYTES : nullptr;
             for (uint32_t it = 0; it < n_it; ++it) {
                 const uint32_t st = it % TC_STAGES, sb = it / TC_STAGES;
                 if (!tma::mbar_wait_blocking(empty_ab + st, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) break;
                 if (st == 0 && sb >= 2 && !tma::mbar_wait_blocking(empty_d + (sb & 1), ((sb - 2) >> 1) & 1, abort_flag, &g_tc_status, 8u)) break;
-                tma::mbar_expect_tx(full_ab + st, 2 * TC_OP_BYTES + (st == 0 ? TC_MINOP_BYTES : 0));
+                tma::mbar_expect_tx(full_ab + st, (IMG ? 3 : 2) * TC_OP_BYTES + (st == 0 ? TC_MINOP_BYTES + (IMG ? TC_SIDE_BYTES : 0) : 0));
                 tma::bulk_g2s(tc_smem + st * TC_STAGE_BYTES, img + (size_t)it * (2 * TC_OP_BYTES), 2 * TC_OP_BYTES, full_ab + st);
-                if (st == 0) tma::bulk_g2s(slots + (sb & 1) * TC_SLOT_BYTES, img_min + (size_t)sb * TC_MINOP_BYTES, TC_MINOP_BYTES, full_ab + st);
+                if (IMG) tma::bulk_g2s(tc_smem + st * TC_STAGE_BYTES + 2 * TC_OP_BYTES, wimg + (size_t)it * TC_OP_BYTES, TC_OP_BYTES, full_ab + st);
+                if (st == 0) {
+                    uint8_t *slot = slots + (sb & 1) * TC_SLOT_BYTES;
+                    tma::bulk_g2s(slot, img_min + (size_t)sb * TC_MINOP_BYTES, TC_MINOP_BYTES, full_ab + st);
+                    if (IMG) tma::bulk_g2s(slot + TC_MINOP_BYTES, wside + (size_t)sb * TC_SIDE_BYTES, TC_SIDE_BYTES, full_ab + st);
+                }
             }
         }
     } else {
         // ---------------------------------------------------------------- epilogue: thread = (token lane, 64 rows)
-        const uint32_t e = warp - (2 + TC_W_WARPS), quad = warp & 3, ch = e >> 2;  // a warp reaches TMEM lanes [32 (warp % 4), +32)
+        const uint32_t e = warp - (TC_LOADER_WARP + 1), quad = warp & 3, ch = e >> 2;  // a warp reaches TMEM lanes [32 (warp % 4), +32)
         const uint32_t tl = quad * 32 + lane;                                                    // token lane
         const uint32_t lane_addr = tmem + ((quad * 32) << 16);
         float ginv = 1.0f;
         bool ok = true;
+        if constexpr (IMG) {
+            // The running output of the thread's 64 rows stays in registers (this variant has no producer warps, so the
+            // register file has the room), D and Dm are both double-buffered in TMEM: a super-block costs two TMEM reads
+            // per cell and the MMAs of the next super-block never wait for this one's epilogue.
+            float acc[64];
+#pragma unroll
+            for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+            for (uint32_t sb = 0; sb < n_sb && ok; ++sb) {
+                const uint32_t buf = sb & 1;
+                if (!tma::mbar_wait_blocking(full_d + buf, (sb >> 1) & 1, abort_flag, &g_tc_status, 16u)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                if (sb == 0) ginv = __ldg(p.ginv + col0 + tl);
+                const float *dval = reinterpret_cast<const float *>(slots + buf * TC_SLOT_BYTES + 2 * TC_MINOP_BYTES);
+#pragma unroll
+                for (uint32_t c2 = 0; c2 < 2; ++c2) {  // 32 rows per round: four loads in flight
+                    const uint32_t col = ch * 64 + c2 * 32;
+                    uint32_t d0[16], m0[16], d1[16], m1[16];
+                    tmem_ld16(lane_addr + buf * TC_BN + col, d0);
+                    tmem_ld16(lane_addr + (2 + buf) * TC_BN + col, m0);
+                    tmem_ld16(lane_addr + buf * TC_BN + col + 16, d1);
+                    tmem_ld16(lane_addr + (2 + buf) * TC_BN + col + 16, m1);
+                    tmem_wait_ld();
+                    const float4 *dq = reinterpret_cast<const float4 *>(dval + col), *mq = dq + TC_BN / 4;
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; ++q4) {
+                        const float4 dv = dq[q4], mv = mq[q4];
+                        const float dvv[4] = {dv.x, dv.y, dv.z, dv.w}, mvv[4] = {mv.x, mv.y, mv.z, mv.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int j = q4 * 4 + i;
+                            const float dd = __uint_as_float(j < 16 ? d0[j & 15] : d1[j & 15]), mm = __uint_as_float(j < 16 ? m0[j & 15] : m1[j & 15]);
+                            const float t = fmaf(dvv[i], dd, -(mvv[i] * mm));
+                            acc[c2 * 32 + j] = fmaf(t, ginv, acc[c2 * 32 + j]);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) tma::mbar_arrive(empty_d + buf);  // D and Dm of this parity and the slot's tables are free again
+            }
+            if (ok && col0 + tl < p.n) {
+                // ---- the thread's 64 cells -> global memory: cell (row i, token j) at out[i * ldy + j * ldc]
+                float *o = p.out + (size_t)(row0 + ch * 64) * p.ldy + (size_t)(col0 + tl) * p.ldc;
+                if (p.ldy == 1 && row0 + ch * 64 + 64 <= p.m && ((uintptr_t)o & 15) == 0) {  // token-major output: 256 contiguous bytes
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float4 v = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+                        float4 *o4 = reinterpret_cast<float4 *>(o) + i;
+                        if (p.epilogue == EPI_ADD) {
+                            const float4 c = *o4;
+                            v = make_float4(__fadd_rn(c.x, v.x), __fadd_rn(c.y, v.y), __fadd_rn(c.z, v.z), __fadd_rn(c.w, v.w));
+                        }
+                        *o4 = v;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i)
+                        if (row0 + ch * 64 + i < p.m) {
+                            float *oi = o + (size_t)i * p.ldy;
+                            *oi = p.epilogue == EPI_ADD ? __fadd_rn(*oi, acc[i]) : acc[i];
+                        }
+                }
+            }
+            ok = false;  // (stored already: skip the TMEM-resident path below)
+        }
         for (uint32_t sb = 0; sb < n_sb && ok; ++sb) {
             const uint32_t buf = sb & 1;
             if (!tma::mbar_wait_blocking(full_d + buf, (sb >> 1) & 1, abort_flag, &g_tc_status, 16u)) {
@@ -460,21 +568,74 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
     }
 }
 
-template <int T>
+template <int T, bool IMG>
 int32_t launch_tc_typed(const TcParams &p, cudaStream_t st) {
-    static thread_local int configured_dev = -1;
+    static thread_local int configured_dev = -1;  // (one per instantiation)
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_dev != dev) {
-        CERA_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
+        CERA_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<T, IMG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
         configured_dev = dev;
     }
     const dim3 grid((p.n + TC_BM - 1) / TC_BM, (p.m + TC_BN - 1) / TC_BN);
     count_launch();
-    return check_cuda(launch_k(gemm_tc_kernel<T>, grid, dim3(TC_THREADS), (size_t)TC_SMEM_BYTES, st, p), "gemm (tcgen05) launch");
+    return check_cuda(launch_k(gemm_tc_kernel<T, IMG>, grid, dim3(IMG ? TC_THREADS_IMG : TC_THREADS), (size_t)TC_SMEM_BYTES, st, p),
+                      "gemm (tcgen05) launch");
 }
 
 }  // namespace
+
+// The resident tensor-core image of a Q4_K / Q5_K weight: sc * q as f16 in the GEMM kernel's shared-memory tile layout
+// (2 bytes per weight) plus 40 bytes per (row, super-block) of min operand and super-scales.  With it the prefill GEMM
+// has no conversion work left: every stage is three bulk copies and eight MMAs.  Built once; a weight that is not this
+// kernel's case, CERA_CUDA_TC_IMAGE=0, or a device without room leave the weight as it is (the GEMM then converts on
+// the fly).  *built (optional) reports whether the weight now has an image.
+int32_t weight_prepare_tc(cera_cuda_weight *w, bool *built) {
+    if (built) *built = false;
+    if (!w) return fail(CERA_CUDA_ERR_BAD_ARG, "weight_prepare_gemm: null weight");
+    if (w->v.tc) {
+        if (built) *built = true;
+        return CERA_CUDA_OK;
+    }
+    static const bool off = [] {
+        const char *e = getenv("CERA_CUDA_TC_IMAGE");
+        return e && strcmp(e, "0") == 0;
+    }();
+    const WeightView &v = w->v;
+    if (off || v.k % 256 || v.ilv != 8 || (v.type != CERA_TYPE_Q4_K && v.type != CERA_TYPE_Q5_K)) return CERA_CUDA_OK;
+    const uint32_t tiles = (v.m + TC_BN - 1) / TC_BN, n_it = v.k / TC_KS, n_sb = v.k / 256;
+    const size_t img_bytes = (size_t)tiles * n_it * TC_OP_BYTES, side_bytes = (size_t)tiles * n_sb * TC_SIDE_BYTES;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    if (prev != w->device) cudaSetDevice(w->device);
+    size_t free_b = 0, total_b = 0;
+    int32_t rc = CERA_CUDA_OK;
+    void *img = nullptr;
+    // keep a margin for KV caches and prefill scratch: the image is an accelerator, not a requirement
+    if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess && free_b > img_bytes + side_bytes + (4ull << 30) &&
+        cudaMalloc(&img, img_bytes + side_bytes) == cudaSuccess) {
+        const dim3 grid(n_it, tiles);
+        if (v.type == CERA_TYPE_Q4_K)
+            tc_weight_image_kernel<CERA_TYPE_Q4_K><<<grid, TC_W_WARPS * 32>>>(v, (uint8_t *)img, (uint8_t *)img + img_bytes);
+        else
+            tc_weight_image_kernel<CERA_TYPE_Q5_K><<<grid, TC_W_WARPS * 32>>>(v, (uint8_t *)img, (uint8_t *)img + img_bytes);
+        count_launch();
+        rc = check_cuda(cudaGetLastError(), "weight image launch");
+        if (rc == CERA_CUDA_OK) rc = check_cuda(cudaDeviceSynchronize(), "weight image");
+        if (rc == CERA_CUDA_OK) {
+            w->tc_image = img;
+            w->tc_bytes = img_bytes + side_bytes;
+            w->v.tc = (const uint8_t *)img;
+            if (built) *built = true;
+        } else {
+            cudaFree(img);
+        }
+    } else {
+        cudaGetLastError();  // no room: not an error
+    }
+    if (prev != w->device) cudaSetDevice(prev);
+    return rc;
+}
 
 uint32_t gemm_tc_status() {
     unsigned int v = 0;
@@ -521,7 +682,12 @@ int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *o
     p.ldc = (uint32_t)ldc;
     p.epilogue = epilogue;
     *taken = true;
-    if (rc == CERA_CUDA_OK) rc = w.type == CERA_TYPE_Q4_K ? launch_tc_typed<CERA_TYPE_Q4_K>(p, st) : launch_tc_typed<CERA_TYPE_Q5_K>(p, st);
+    if (rc == CERA_CUDA_OK) {
+        if (w.tc)
+            rc = w.type == CERA_TYPE_Q4_K ? launch_tc_typed<CERA_TYPE_Q4_K, true>(p, st) : launch_tc_typed<CERA_TYPE_Q5_K, true>(p, st);
+        else
+            rc = w.type == CERA_TYPE_Q4_K ? launch_tc_typed<CERA_TYPE_Q4_K, false>(p, st) : launch_tc_typed<CERA_TYPE_Q5_K, false>(p, st);
+    }
     cudaFreeAsync(scratch, st);  // after the kernels above, in stream order
     return rc;
 }

@@ -67,6 +67,7 @@ struct cera_cuda_model {
     cera_cuda_config cfg{};
     std::mutex mu;
     bool finalized = false;
+    bool tc_prepared = false;  // the prefill GEMM's weight images have been asked for
     cera_cuda_weight *embd = nullptr, *output = nullptr;
     cera_cuda_weight *embd_rows = nullptr;  // tensor parallel: this rank's rows of a tied embedding, as LM head
     cera_cuda_weight *embd_head = nullptr;  // LM head when output.weight is absent (embd or embd_rows)
@@ -405,6 +406,17 @@ int32_t prefill_chunk(cera_cuda_model *m, const uint32_t *tokens, size_t n, size
                  ff = c.intermediate_size;
     const float scale = c.attention_scale != 0.0f ? c.attention_scale : 1.0f / sqrtf((float)c.head_dim);
     const float res_scale = c.residual_scale != 0.0f ? c.residual_scale : 1.0f;
+    if (n > 32 && !m->tc_prepared) {
+        // the first batched prompt builds the f16 operand images of the tensor-core GEMM's weights (a decode-only model
+        // never pays their 2.2 bytes per weight; a weight that gets none is converted on the fly)
+        m->tc_prepared = true;
+        for (auto &L : m->layers)
+            for (cera_cuda_weight *w : {L.wq, L.wk, L.wv, L.wo, L.gate, L.up, L.down}) {
+                bool built = false;
+                CERA_TRY(weight_prepare_tc(w, &built));
+                if (built) m->mem_bytes += w->tc_bytes;
+            }
+    }
     CERA_CUDA_TRY(cudaMemcpyAsync(m->pf_tokens, tokens, n * 4, cudaMemcpyHostToDevice, st));
     CERA_TRY(launch_embed_batch(m->embd->v, m->pf_tokens, n, m->pf_hidden, st));
     if (c.embedding_scale != 0.0f && c.embedding_scale != 1.0f) CERA_TRY(launch_scale(m->pf_hidden, n * hs, c.embedding_scale, st));

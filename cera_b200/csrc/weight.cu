@@ -153,7 +153,7 @@ int32_t weight_upload(int32_t type, size_t m, size_t k, const void *bytes, size_
     }
     const uint32_t t128 = k % 128 == 0 ? (uint32_t)(k / 128) : 0u;
     w->v = WeightView{type, (uint32_t)m, (uint32_t)k, (uint32_t)nb, t128, ilv, q, ti.qh_b ? qh : nullptr, hdr,
-                      ti.d_b ? d : nullptr};
+                      ti.d_b ? d : nullptr, nullptr};
     if (ilv && plane_blocks != n_blocks) {  // the padding rows of the last group read as zero weights
         st = check_cuda(cudaMemset(w->base, 0, q_sz + qh_sz + hdr_sz + d_sz), "cudaMemset(weight planes)");
         if (st != CERA_CUDA_OK) {
@@ -199,7 +199,15 @@ int32_t cera_cuda_weight_create(int32_t type, size_t m, size_t k, const void *by
 void cera_cuda_weight_free(cera_cuda_weight *w) {
     if (!w) return;
     if (w->base) cudaFree(w->base);
+    if (w->tc_image) cudaFree(w->tc_image);
     delete w;
+}
+
+int32_t cera_cuda_weight_prepare_gemm(cera_cuda_weight *w, int32_t *has_image) {
+    bool built = false;
+    const int32_t rc = weight_prepare_tc(w, &built);
+    if (has_image) *has_image = built ? 1 : 0;
+    return rc;
 }
 
 int32_t cera_cuda_weight_info(const cera_cuda_weight *w, int32_t *type, size_t *m, size_t *k, size_t *device_bytes) {

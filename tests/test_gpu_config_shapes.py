@@ -49,7 +49,11 @@ def _check(cb, torch, t, m, k, n):
         got = got[rows]
     else:
         want = O.gemm_preq(t, raw, bs, bq, m, n, k, avx2=True, threads=THREADS)
+        rows = None
     assert_close(got, want, f"{O.NAMES[t]} {m}x{k} n={n}")
+    if n == 512 and w.prepare_gemm():  # once more through the resident f16 operand image of the tcgen05 kernel
+        got = cb.gemm_preq(w, acts, torch.full((m, n), float("nan"), device="cuda")).cpu().numpy()
+        assert_close(got if rows is None else got[rows], want, f"{O.NAMES[t]} {m}x{k} n={n} (weight image)")
 
 
 @pytest.mark.parametrize("n", [1, 8, 64, 512])

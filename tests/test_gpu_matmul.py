@@ -162,7 +162,7 @@ def test_gemm_preq_matches_oracle(t, n):
 
 @pytest.mark.parametrize("t", [O.Q4_K, O.Q6_K, O.Q5_K, O.Q4_0])
 @pytest.mark.parametrize("m,n,k", [(70, 130, 1024), (64, 128, 512), (200, 16, 768), (3, 64, 4096), (130, 5, 2048),
-                                   (96, 8, 4096), (65, 33, 3072), (256, 100, 1024), (40, 17, 14336)])
+                                   (96, 8, 4096), (65, 33, 3072), (256, 100, 1024), (40, 17, 14336), (300, 390, 2048)])
 def test_gemm_tensor_core_shapes(t, m, n, k):
     """n >= 5 and k a multiple of 256: the K-quants and Q4_0 take the mma.sync int8 kernel (every column-tile width, ragged tiles, and the k range
     split over clusters of 2, 4 and 8 CTAs)."""
@@ -176,6 +176,12 @@ def test_gemm_tensor_core_shapes(t, m, n, k):
     got = cb.gemm_preq(w, acts, out).cpu().numpy()
     want = O.gemm_preq(t, raw, acts.scales.cpu().numpy(), acts.quants.cpu().numpy(), m, n, k, avx2=t != O.Q5_K, threads=4)
     assert_close(got, want, f"{O.NAMES[t]} {m}x{n}x{k}")
+    # the same through the resident f16 operand image of the tcgen05 kernel (Q4_K / Q5_K, k a multiple of 256)
+    has = w.prepare_gemm()
+    assert has == (t in (O.Q4_K, O.Q5_K) and k % 256 == 0)
+    if has:
+        out2 = torch.full((m, n), float("nan"), device="cuda")
+        assert_close(cb.gemm_preq(w, acts, out2).cpu().numpy(), want, f"{O.NAMES[t]} {m}x{n}x{k} (weight image)")
 
 
 def test_gemm_on_reference_fixtures():
