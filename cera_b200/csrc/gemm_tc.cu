@@ -68,6 +68,39 @@ constexpr uint32_t TC_SMEM_BYTES = TC_TAIL_OFF + 256;
 constexpr uint32_t TC_TMEM_COLS = 512;  // D0 [0,128) D1 [128,256), then Dm [256,384) OUT [384,512) or, with the weight image, Dm0 Dm1
 constexpr uint32_t TC_KC_STRIDE = TC_BM * 16;                            // bytes between 8-element k chunks: 2048
 
+// The wide variant (a CTA owns 128 tokens x 256 weight rows, weight image only): stages of the two activation operand
+// tiles and the operand tiles of two 128-row image tiles; the min term is one more GEMM at the end of the k loop (see
+// gemm_tcw_kernel), whose stages of 32 activation blocks reuse the ring.
+constexpr int TCW_STAGES = 3;
+constexpr uint32_t TCW_STAGE_BYTES = 4 * TC_OP_BYTES;                     // A high, A low, B rows [0,128), B rows [128,256): 64 KB
+constexpr uint32_t TCW_MIN_J = 32;                                        // activation blocks (k / 32 columns) per min stage
+constexpr uint32_t TCW_MINT_BYTES = TC_BM * TCW_MIN_J * 2;                // one min-GEMM operand tile: 8 KB
+constexpr uint32_t TCW_DVAL_OFF = TCW_STAGES * TCW_STAGE_BYTES;           // two slots of d[256]
+constexpr uint32_t TCW_RS_OFF = TCW_DVAL_OFF + 2 * 2 * TC_BN * 4;         // 2^-s[256] of the min GEMM's weight rows
+constexpr uint32_t TCW_TAIL_OFF = TCW_RS_OFF + 2 * TC_BN * 4;
+constexpr uint32_t TCW_SMEM_BYTES = TCW_TAIL_OFF + 256;
+constexpr int TCW_THREADS = (2 + TC_EPI_WARPS) * 32;
+
+// Regions of a weight's resident image (byte offsets): the operand tile of every (128-row tile, stage); per (tile,
+// super-block) the row side of the min operand, d[128] and dmin[128]; per (tile, min stage) the high and the low part of
+// dmin * min * 2^s; per tile 2^-s[128].
+struct TcImage {
+    uint32_t tiles, n_it, n_sb, n_mit;
+    size_t side, wmin, rscale, total;
+};
+__host__ __device__ inline TcImage tc_image_layout(uint32_t m, uint32_t k) {
+    TcImage L;
+    L.tiles = (m + TC_BN - 1) / TC_BN;
+    L.n_it = k / TC_KS;
+    L.n_sb = k / 256;
+    L.n_mit = (k / 32 + TCW_MIN_J - 1) / TCW_MIN_J;
+    L.side = (size_t)L.tiles * L.n_it * TC_OP_BYTES;
+    L.wmin = L.side + (size_t)L.tiles * L.n_sb * TC_SIDE_BYTES;
+    L.rscale = L.wmin + (size_t)L.tiles * L.n_mit * 2 * TCW_MINT_BYTES;
+    L.total = L.rscale + (size_t)L.tiles * TC_BN * 4;
+    return L;
+}
+
 struct TcParams {
     WeightView w;
     float *out;
@@ -78,6 +111,7 @@ struct TcParams {
     // the low operand tile, per (token tile, super-block) the token side of the min operand, per token 1 / g
     const uint8_t *img, *img_min;
     const float *ginv;
+    const uint8_t *xm;  // per (token tile, min stage) the high and the low part of g * xs_b * A_b (the wide variant's min GEMM)
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------------
@@ -175,7 +209,7 @@ __global__ void tc_token_range_kernel(const ActView x, uint32_t n, uint32_t k, u
 // and g * xs_b * A_b, high and low, into the token side of the super-block's min operand.  grid (token tiles, stages),
 // 256 threads: thread = (token, block of the stage).
 __global__ void __launch_bounds__(TC_IMG_THREADS) tc_token_image_kernel(const ActView x, uint32_t n, uint32_t k, const float *__restrict__ g_tab,
-                                                                         uint8_t *__restrict__ img, uint8_t *__restrict__ img_min) {
+                                                                         uint8_t *__restrict__ img, uint8_t *__restrict__ img_min, uint8_t *__restrict__ xm) {
     pdl_trigger();
     pdl_wait();
     const uint32_t c = threadIdx.x >> 1, blk = threadIdx.x & 1, it = blockIdx.y, st = it % TC_STAGES, sb = it / TC_STAGES;
@@ -215,6 +249,11 @@ __global__ void __launch_bounds__(TC_IMG_THREADS) tc_token_image_kernel(const Ac
         const __half2 hl = __floats2half2_rn(vh, v - vh);
         uint8_t *slot = img_min + ((size_t)blockIdx.x * n_sb + sb) * TC_MINOP_BYTES;
         *reinterpret_cast<uint32_t *>(slot + op_off(st >> 1, c) + ((st & 1) * 2 + blk) * 4) = *reinterpret_cast<const uint32_t *>(&hl);
+        // the same pair as column xb of the wide variant's min GEMM: a high tile and a low tile per 32 blocks
+        const uint32_t n_mit = (nb32 + TCW_MIN_J - 1) / TCW_MIN_J, mi = xb / TCW_MIN_J, jj = xb % TCW_MIN_J;
+        uint8_t *xt = xm + ((size_t)blockIdx.x * n_mit + mi) * (2 * TCW_MINT_BYTES) + op_off(jj >> 3, c) + (jj & 7) * 2;
+        *reinterpret_cast<__half *>(xt) = __low2half(hl);
+        *reinterpret_cast<__half *>(xt + TCW_MINT_BYTES) = __high2half(hl);
     }
 }
 
@@ -297,6 +336,290 @@ __global__ void __launch_bounds__(TC_W_WARPS * 32) tc_weight_image_kernel(const 
     uint8_t *sd = side + ((size_t)tile * n_sb + sb) * TC_SIDE_BYTES;
     tc_convert_w<T>(tc_fetch_w<T>(w, row, half, it), r, half, st, img + ((size_t)tile * n_it + it) * TC_OP_BYTES, sd,
                     reinterpret_cast<float *>(sd + TC_MINOP_BYTES));
+}
+
+// The weight side of the wide variant's min GEMM: w[row][j] = dmin[row, j / 8] * min[row, j] * 2^s[row] for the k / 32
+// blocks j of a row, as a high part (top 11 significant bits) and the remainder - both exact in f16, since the product
+// of an f16 and a six-bit integer has 17 significant bits and 2^s[row] brings the row's largest entry to [2^14, 2^15).
+// Tiles of 32 blocks in the operand layout, zero beyond k / 32; 2^-s[row] beside them.  grid = 128-row tiles, thread = row.
+__global__ void __launch_bounds__(TC_BN) tc_weight_min_kernel(const WeightView w, uint8_t *__restrict__ wmin, float *__restrict__ rscale) {
+    const uint32_t r = threadIdx.x, tile = blockIdx.x, n_sb = w.k / 256, n_mit = (w.k / 32 + TCW_MIN_J - 1) / TCW_MIN_J;
+    const uint32_t row = min(tile * TC_BN + r, w.m - 1);
+    float mx = 0.0f;
+    for (uint32_t sb = 0; sb < n_sb; ++sb) {
+        const uint4 h = __ldg(reinterpret_cast<const uint4 *>(w.hdr) + sb_index(w, row, sb));
+        const float dmin = fabsf(h2f((uint16_t)(h.x >> 16)));
+        uint32_t sc, m0, m1;
+        kq_quad(h, 0, sc, m0);
+        kq_quad(h, 1, sc, m1);
+        uint32_t mm = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mm = max(mm, max((m0 >> (8 * i)) & 0xFF, (m1 >> (8 * i)) & 0xFF));
+        const float v = dmin * (float)mm;
+        mx = fmaxf(mx, v == v && v < 3.0e38f ? v : 0.0f);
+    }
+    int e = 0;
+    if (mx > 0.0f) frexpf(mx, &e);  // mx < 2^e
+    const float up = mx > 0.0f ? ldexpf(1.0f, 15 - e) : 1.0f;
+    rscale[tile * TC_BN + r] = 1.0f / up;
+    for (uint32_t mi = 0; mi < n_mit; ++mi) {
+        uint8_t *hi_t = wmin + ((size_t)tile * n_mit + mi) * (2 * TCW_MINT_BYTES), *lo_t = hi_t + TCW_MINT_BYTES;
+#pragma unroll 1
+        for (uint32_t kc = 0; kc < TCW_MIN_J / 8; ++kc) {  // eight blocks = one super-block = one 16-byte k chunk
+            const uint32_t sb = mi * (TCW_MIN_J / 8) + kc;
+            __half2 hi2[4], lo2[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) hi2[q] = lo2[q] = __float2half2_rn(0.0f);
+            if (sb < n_sb) {
+                const uint4 h = __ldg(reinterpret_cast<const uint4 *>(w.hdr) + sb_index(w, row, sb));
+                const float dm = h2f((uint16_t)(h.x >> 16)) * up;
+                uint32_t sc, mp[2];
+                kq_quad(h, 0, sc, mp[0]);
+                kq_quad(h, 1, sc, mp[1]);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float v[2], vh[2];
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        const int b = 2 * q + t;
+                        v[t] = dm * (float)((mp[b >> 2] >> (8 * (b & 3))) & 0xFF);
+                        vh[t] = __uint_as_float(__float_as_uint(v[t]) & 0xFFFFE000u);
+                    }
+                    hi2[q] = __floats2half2_rn(vh[0], vh[1]);
+                    lo2[q] = __floats2half2_rn(v[0] - vh[0], v[1] - vh[1]);
+                }
+            }
+            *reinterpret_cast<uint4 *>(hi_t + op_off(kc, r)) = *reinterpret_cast<const uint4 *>(&hi2[0]);
+            *reinterpret_cast<uint4 *>(lo_t + op_off(kc, r)) = *reinterpret_cast<const uint4 *>(&lo2[0]);
+        }
+    }
+}
+
+// The wide variant: one CTA = 128 tokens x 256 weight rows (two 128-row tiles of the weight image), for GEMMs with enough
+// tiles to fill the device.  Against the 128 x 128 kernel the activation operands are fetched once for twice the MMAs
+// (64 KB per 1024 tensor-pipe cycles instead of 48 KB per 512) and a stage hand-over pays for sixteen MMAs, which is what
+// the 128-wide kernel is short of: its MMA thread waits a third of the time for operands.  TMEM then holds nothing but the
+// two double-buffered accumulators (2 x 256 columns), so
+//  * the running output lives in the epilogue threads' registers (thread = token lane x 128 rows), and
+//  * the min term sum_b dmin * mn_b * (xs_b * A_b) is not accumulated per super-block but as ONE more GEMM over the k / 32
+//    blocks of the whole row after the k loop - weights dmin * mn * 2^s[row] (tc_weight_min_kernel) and activations
+//    g * xs_b * A_b, each as high and low f16 parts, three MMAs per step (the low x low product is below 2^-22) - into
+//    the accumulator buffer of a virtual last super-block.
+// Warps: 0 MMA issue (one thread), 1 operand loader (one thread), 2-9 epilogue.
+__global__ void __launch_bounds__(TCW_THREADS, 1) gemm_tcw_kernel(const TcParams p) {
+    extern __shared__ __align__(1024) uint8_t tc_smem[];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tc_smem + TCW_TAIL_OFF);
+    uint64_t *full_ab = bars, *empty_ab = bars + TCW_STAGES, *full_d = bars + 2 * TCW_STAGES, *empty_d = full_d + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TCW_STAGES + 4);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t col0 = blockIdx.x * TC_BM, row0 = blockIdx.y * 2 * TC_BN;
+    const TcImage L = tc_image_layout(p.m, p.k);
+    const uint32_t n_sb = L.n_sb, n_it = L.n_it, n_mit = L.n_mit;
+    if (tid == 0) {
+        for (int s = 0; s < TCW_STAGES; ++s) {
+            tma::mbar_init(full_ab + s, 1);   // the loader's expect_tx
+            tma::mbar_init(empty_ab + s, 1);  // the commit of the stage's MMAs
+        }
+        for (int b = 0; b < 2; ++b) {
+            tma::mbar_init(full_d + b, 1);              // the commit after a super-block's last MMA
+            tma::mbar_init(empty_d + b, TC_EPI_WARPS);  // every epilogue warp is done with the buffer and the slot
+        }
+        *abort_flag = 0;
+        tma::mbar_init_fence();
+    }
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, TC_TMEM_COLS);
+        tmem_relinquish();
+    }
+    pdl_trigger();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    pdl_wait();
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- MMA issue (one thread)
+        if (lane == 0) {
+            const uint32_t idesc = tc_idesc(TC_BM, TC_BN);
+            bool ok = true;
+            uint32_t it = 0;
+            for (uint32_t sb = 0; sb <= n_sb && ok; ++sb) {  // super-block n_sb is the min GEMM
+                const uint32_t buf = sb & 1, d0 = tmem + buf * 2 * TC_BN;
+                if (!tma::mbar_wait_blocking(empty_d + buf, ((sb >> 1) & 1) ^ 1, abort_flag, &g_tc_status, 2u)) break;
+                tc_fence_after();
+                const uint32_t n_st = sb < n_sb ? 4u : n_mit;
+                for (uint32_t st = 0; st < n_st; ++st, ++it) {
+                    const uint32_t s = it % TCW_STAGES;
+                    if (!tma::mbar_wait_blocking(full_ab + s, (it / TCW_STAGES) & 1, abort_flag, &g_tc_status, 1u)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t base = tma::smem_u32(tc_smem + s * TCW_STAGE_BYTES);
+                    if (sb < n_sb) {
+                        const uint32_t a_hi = base, a_lo = base + TC_OP_BYTES, b0 = a_lo + TC_OP_BYTES, b1 = b0 + TC_OP_BYTES;
+#pragma unroll
+                        for (uint32_t ks = 0; ks < TC_KS / 16; ++ks) {
+                            const uint32_t o = 2 * ks * TC_KC_STRIDE;
+                            const uint64_t ah = smem_desc(a_hi + o, TC_KC_STRIDE, 128), al = smem_desc(a_lo + o, TC_KC_STRIDE, 128);
+                            const uint64_t bd0 = smem_desc(b0 + o, TC_KC_STRIDE, 128), bd1 = smem_desc(b1 + o, TC_KC_STRIDE, 128);
+                            const uint32_t acc = (st | ks) != 0;
+                            tc_mma_f16(d0, ah, bd0, idesc, acc);
+                            tc_mma_f16(d0 + TC_BN, ah, bd1, idesc, acc);
+                            tc_mma_f16(d0, al, bd0, idesc, 1);
+                            tc_mma_f16(d0 + TC_BN, al, bd1, idesc, 1);
+                        }
+                    } else {
+                        // min GEMM: [x high | x low | w high, w low of rows [0,128) | the same of rows [128,256)], 32 blocks = two steps
+                        const uint32_t x_hi = base, x_lo = base + TCW_MINT_BYTES;
+#pragma unroll
+                        for (uint32_t ks = 0; ks < TCW_MIN_J / 16; ++ks) {
+                            const uint32_t o = 2 * ks * TC_KC_STRIDE;
+                            const uint64_t xh = smem_desc(x_hi + o, TC_KC_STRIDE, 128), xl = smem_desc(x_lo + o, TC_KC_STRIDE, 128);
+#pragma unroll
+                            for (uint32_t h = 0; h < 2; ++h) {
+                                const uint32_t w_hi = base + (2 + 2 * h) * TCW_MINT_BYTES, w_lo = w_hi + TCW_MINT_BYTES;
+                                const uint64_t wh = smem_desc(w_hi + o, TC_KC_STRIDE, 128), wl = smem_desc(w_lo + o, TC_KC_STRIDE, 128);
+                                tc_mma_f16(d0 + h * TC_BN, xh, wh, idesc, (st | ks) != 0);
+                                tc_mma_f16(d0 + h * TC_BN, xl, wh, idesc, 1);
+                                tc_mma_f16(d0 + h * TC_BN, xh, wl, idesc, 1);
+                            }
+                        }
+                    }
+                    tc_commit(empty_ab + s);
+                }
+                if (ok) tc_commit(full_d + buf);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- operands: one thread asks for them (bulk asynchronous copies)
+        if (lane == 0) {
+            const uint32_t t0 = min(2 * blockIdx.y, L.tiles - 1), t1 = min(2 * blockIdx.y + 1, L.tiles - 1);  // (an odd last tile is read twice)
+            const uint8_t *img = p.img + (size_t)blockIdx.x * n_it * (2 * TC_OP_BYTES);
+            const uint8_t *w0 = p.w.tc + (size_t)t0 * n_it * TC_OP_BYTES, *w1 = p.w.tc + (size_t)t1 * n_it * TC_OP_BYTES;
+            const uint8_t *sd0 = p.w.tc + L.side + (size_t)t0 * n_sb * TC_SIDE_BYTES + TC_MINOP_BYTES;  // d[128] of a super-block
+            const uint8_t *sd1 = p.w.tc + L.side + (size_t)t1 * n_sb * TC_SIDE_BYTES + TC_MINOP_BYTES;
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t sb = 0; sb < n_sb && ok; ++sb) {
+                for (uint32_t st = 0; st < 4; ++st, ++it) {
+                    const uint32_t s = it % TCW_STAGES;
+                    if (!tma::mbar_wait_blocking(empty_ab + s, ((it / TCW_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) {
+                        ok = false;
+                        break;
+                    }
+                    // the d slot of this super-block was last read by the epilogue of super-block sb - 2
+                    if (st == 0 && sb >= 2 && !tma::mbar_wait_blocking(empty_d + (sb & 1), ((sb - 2) >> 1) & 1, abort_flag, &g_tc_status, 8u)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *dst = tc_smem + s * TCW_STAGE_BYTES;
+                    tma::mbar_expect_tx(full_ab + s, TCW_STAGE_BYTES + (st == 0 ? 2 * TC_BN * 4 : 0));
+                    tma::bulk_g2s(dst, img + (size_t)it * (2 * TC_OP_BYTES), 2 * TC_OP_BYTES, full_ab + s);
+                    tma::bulk_g2s(dst + 2 * TC_OP_BYTES, w0 + (size_t)it * TC_OP_BYTES, TC_OP_BYTES, full_ab + s);
+                    tma::bulk_g2s(dst + 3 * TC_OP_BYTES, w1 + (size_t)it * TC_OP_BYTES, TC_OP_BYTES, full_ab + s);
+                    if (st == 0) {
+                        uint8_t *dv = tc_smem + TCW_DVAL_OFF + (sb & 1) * (2 * TC_BN * 4);
+                        tma::bulk_g2s(dv, sd0 + (size_t)sb * TC_SIDE_BYTES, TC_BN * 4, full_ab + s);
+                        tma::bulk_g2s(dv + TC_BN * 4, sd1 + (size_t)sb * TC_SIDE_BYTES, TC_BN * 4, full_ab + s);
+                    }
+                }
+            }
+            const uint8_t *xm = p.xm + (size_t)blockIdx.x * n_mit * (2 * TCW_MINT_BYTES);
+            const uint8_t *m0 = p.w.tc + L.wmin + (size_t)t0 * n_mit * (2 * TCW_MINT_BYTES), *m1 = p.w.tc + L.wmin + (size_t)t1 * n_mit * (2 * TCW_MINT_BYTES);
+            for (uint32_t mi = 0; mi < n_mit && ok; ++mi, ++it) {
+                const uint32_t s = it % TCW_STAGES;
+                if (!tma::mbar_wait_blocking(empty_ab + s, ((it / TCW_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) break;
+                uint8_t *dst = tc_smem + s * TCW_STAGE_BYTES;
+                tma::mbar_expect_tx(full_ab + s, 6 * TCW_MINT_BYTES + (mi == 0 ? 2 * TC_BN * 4 : 0));
+                tma::bulk_g2s(dst, xm + (size_t)mi * (2 * TCW_MINT_BYTES), 2 * TCW_MINT_BYTES, full_ab + s);
+                tma::bulk_g2s(dst + 2 * TCW_MINT_BYTES, m0 + (size_t)mi * (2 * TCW_MINT_BYTES), 2 * TCW_MINT_BYTES, full_ab + s);
+                tma::bulk_g2s(dst + 4 * TCW_MINT_BYTES, m1 + (size_t)mi * (2 * TCW_MINT_BYTES), 2 * TCW_MINT_BYTES, full_ab + s);
+                if (mi == 0) {  // 2^-s of the CTA's rows (read by the epilogue after the min GEMM)
+                    tma::bulk_g2s(tc_smem + TCW_RS_OFF, p.w.tc + L.rscale + (size_t)t0 * TC_BN * 4, TC_BN * 4, full_ab + s);
+                    tma::bulk_g2s(tc_smem + TCW_RS_OFF + TC_BN * 4, p.w.tc + L.rscale + (size_t)t1 * TC_BN * 4, TC_BN * 4, full_ab + s);
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue: thread = (token lane, 128 rows of one image tile)
+        const uint32_t e = warp - 2, quad = warp & 3, hh = e >> 2;  // a warp reaches TMEM lanes [32 (warp % 4), +32)
+        const uint32_t tl = quad * 32 + lane;
+        const uint32_t lane_addr = tmem + ((quad * 32) << 16) + hh * TC_BN;
+        float acc[TC_BN];
+#pragma unroll
+        for (int i = 0; i < TC_BN; ++i) acc[i] = 0.0f;
+        float ginv = 1.0f;
+        bool ok = true;
+        for (uint32_t sb = 0; sb <= n_sb && ok; ++sb) {
+            const uint32_t buf = sb & 1;
+            if (!tma::mbar_wait_blocking(full_d + buf, (sb >> 1) & 1, abort_flag, &g_tc_status, 16u)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            if (sb == 0) ginv = __ldg(p.ginv + col0 + tl);
+            // per super-block: out += d[row] * D / g; after the min GEMM: out -= 2^-s[row] * Dmin / g
+            const float *fac = sb < n_sb ? reinterpret_cast<const float *>(tc_smem + TCW_DVAL_OFF + buf * (2 * TC_BN * 4)) + hh * TC_BN
+                                         : reinterpret_cast<const float *>(tc_smem + TCW_RS_OFF) + hh * TC_BN;
+            const float gs = sb < n_sb ? ginv : -ginv;
+#pragma unroll
+            for (uint32_t c = 0; c < TC_BN / 32; ++c) {
+                uint32_t v0[16], v1[16];
+                tmem_ld16(lane_addr + buf * 2 * TC_BN + c * 32, v0);
+                tmem_ld16(lane_addr + buf * 2 * TC_BN + c * 32 + 16, v1);
+                tmem_wait_ld();
+                const float4 *fq = reinterpret_cast<const float4 *>(fac + c * 32);
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4) {
+                    const float4 f = fq[q4];
+                    const float fv[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int j = q4 * 4 + i;
+                        const float dd = __uint_as_float(j < 16 ? v0[j & 15] : v1[j & 15]);
+                        acc[c * 32 + j] = fmaf(fv[i] * dd, gs, acc[c * 32 + j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tma::mbar_arrive(empty_d + buf);  // the accumulator buffer and the d slot are free again
+        }
+        if (ok && col0 + tl < p.n) {
+            // ---- the thread's 128 cells -> global memory: cell (row i, token j) at out[i * ldy + j * ldc]
+            const uint32_t r0 = row0 + hh * TC_BN;
+            float *o = p.out + (size_t)r0 * p.ldy + (size_t)(col0 + tl) * p.ldc;
+            if (p.ldy == 1 && r0 + TC_BN <= p.m && ((uintptr_t)o & 15) == 0) {  // token-major output: 512 contiguous bytes
+#pragma unroll
+                for (int i = 0; i < TC_BN / 4; ++i) {
+                    float4 v = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+                    float4 *o4 = reinterpret_cast<float4 *>(o) + i;
+                    if (p.epilogue == EPI_ADD) {
+                        const float4 c = *o4;
+                        v = make_float4(__fadd_rn(c.x, v.x), __fadd_rn(c.y, v.y), __fadd_rn(c.z, v.z), __fadd_rn(c.w, v.w));
+                    }
+                    *o4 = v;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < TC_BN; ++i)
+                    if (r0 + i < p.m) {
+                        float *oi = o + (size_t)i * p.ldy;
+                        *oi = p.epilogue == EPI_ADD ? __fadd_rn(*oi, acc[i]) : acc[i];
+                    }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem, TC_TMEM_COLS);
+    }
 }
 
 template <int T, bool IMG>
@@ -583,6 +906,19 @@ int32_t launch_tc_typed(const TcParams &p, cudaStream_t st) {
                       "gemm (tcgen05) launch");
 }
 
+int32_t launch_tc_wide(const TcParams &p, cudaStream_t st) {
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        CERA_CUDA_TRY(cudaFuncSetAttribute(gemm_tcw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TCW_SMEM_BYTES));
+        configured_dev = dev;
+    }
+    const dim3 grid((p.n + TC_BM - 1) / TC_BM, (p.m + 2 * TC_BN - 1) / (2 * TC_BN));
+    count_launch();
+    return check_cuda(launch_k(gemm_tcw_kernel, grid, dim3(TCW_THREADS), (size_t)TCW_SMEM_BYTES, st, p), "gemm (tcgen05, wide) launch");
+}
+
 }  // namespace
 
 // The resident tensor-core image of a Q4_K / Q5_K weight: sc * q as f16 in the GEMM kernel's shared-memory tile layout
@@ -603,8 +939,7 @@ int32_t weight_prepare_tc(cera_cuda_weight *w, bool *built) {
     }();
     const WeightView &v = w->v;
     if (off || v.k % 256 || v.ilv != 8 || (v.type != CERA_TYPE_Q4_K && v.type != CERA_TYPE_Q5_K)) return CERA_CUDA_OK;
-    const uint32_t tiles = (v.m + TC_BN - 1) / TC_BN, n_it = v.k / TC_KS, n_sb = v.k / 256;
-    const size_t img_bytes = (size_t)tiles * n_it * TC_OP_BYTES, side_bytes = (size_t)tiles * n_sb * TC_SIDE_BYTES;
+    const TcImage L = tc_image_layout(v.m, v.k);
     int prev = 0;
     cudaGetDevice(&prev);
     if (prev != w->device) cudaSetDevice(w->device);
@@ -612,19 +947,21 @@ int32_t weight_prepare_tc(cera_cuda_weight *w, bool *built) {
     int32_t rc = CERA_CUDA_OK;
     void *img = nullptr;
     // keep a margin for KV caches and prefill scratch: the image is an accelerator, not a requirement
-    if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess && free_b > img_bytes + side_bytes + (4ull << 30) &&
-        cudaMalloc(&img, img_bytes + side_bytes) == cudaSuccess) {
-        const dim3 grid(n_it, tiles);
+    if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess && free_b > L.total + (4ull << 30) && cudaMalloc(&img, L.total) == cudaSuccess) {
+        const dim3 grid(L.n_it, L.tiles);
+        uint8_t *b = (uint8_t *)img;
         if (v.type == CERA_TYPE_Q4_K)
-            tc_weight_image_kernel<CERA_TYPE_Q4_K><<<grid, TC_W_WARPS * 32>>>(v, (uint8_t *)img, (uint8_t *)img + img_bytes);
+            tc_weight_image_kernel<CERA_TYPE_Q4_K><<<grid, TC_W_WARPS * 32>>>(v, b, b + L.side);
         else
-            tc_weight_image_kernel<CERA_TYPE_Q5_K><<<grid, TC_W_WARPS * 32>>>(v, (uint8_t *)img, (uint8_t *)img + img_bytes);
+            tc_weight_image_kernel<CERA_TYPE_Q5_K><<<grid, TC_W_WARPS * 32>>>(v, b, b + L.side);
+        tc_weight_min_kernel<<<L.tiles, TC_BN>>>(v, b + L.wmin, reinterpret_cast<float *>(b + L.rscale));  // (the header layout is the same for both types)
+        count_launch();
         count_launch();
         rc = check_cuda(cudaGetLastError(), "weight image launch");
         if (rc == CERA_CUDA_OK) rc = check_cuda(cudaDeviceSynchronize(), "weight image");
         if (rc == CERA_CUDA_OK) {
             w->tc_image = img;
-            w->tc_bytes = img_bytes + side_bytes;
+            w->tc_bytes = L.total;
             w->v.tc = (const uint8_t *)img;
             if (built) *built = true;
         } else {
@@ -657,15 +994,20 @@ int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *o
     // the activation operands, converted once for all row tiles: a stream-ordered scratch allocation that lives for this
     // call (token tiles x stages x 32 KB, the min operand's token side, g and 1 / g)
     const uint32_t tiles = (uint32_t)((n + TC_BM - 1) / TC_BM), n_pad = tiles * TC_BM, n_it = w.k / TC_KS, n_sb = w.k / 256;
-    const size_t img_bytes = (size_t)tiles * n_it * (2 * TC_OP_BYTES), min_bytes = (size_t)tiles * n_sb * TC_MINOP_BYTES;
+    const uint32_t nb32 = w.k / 32, n_mit = (nb32 + TCW_MIN_J - 1) / TCW_MIN_J;
+    const size_t img_bytes = (size_t)tiles * n_it * (2 * TC_OP_BYTES), min_bytes = (size_t)tiles * n_sb * TC_MINOP_BYTES,
+                 xm_bytes = (size_t)tiles * n_mit * (2 * TCW_MINT_BYTES);
     uint8_t *scratch = nullptr;
-    CERA_CUDA_TRY(cudaMallocAsync((void **)&scratch, img_bytes + min_bytes + (size_t)n_pad * 8, st));
-    float *g_tab = reinterpret_cast<float *>(scratch + img_bytes + min_bytes), *ginv_tab = g_tab + n_pad;
+    CERA_CUDA_TRY(cudaMallocAsync((void **)&scratch, img_bytes + min_bytes + xm_bytes + (size_t)n_pad * 8, st));
+    uint8_t *xm = scratch + img_bytes + min_bytes;
+    float *g_tab = reinterpret_cast<float *>(xm + xm_bytes), *ginv_tab = g_tab + n_pad;
+    // the last min stage's columns beyond k / 32 are zero (never written by the image kernel)
+    if (nb32 % TCW_MIN_J) CERA_CUDA_TRY(cudaMemsetAsync(xm, 0, xm_bytes, st));
     int32_t rc = check_cuda(launch_k(tc_token_range_kernel, dim3((n_pad + 7) / 8), dim3(256), 0, st, x, (uint32_t)n, (uint32_t)w.k, n_pad, g_tab, ginv_tab),
                             "gemm (tcgen05) token range launch");
     if (rc == CERA_CUDA_OK)
         rc = check_cuda(launch_k(tc_token_image_kernel, dim3(tiles, n_it), dim3(TC_IMG_THREADS), 0, st, x, (uint32_t)n, (uint32_t)w.k, (const float *)g_tab,
-                                 scratch, scratch + img_bytes),
+                                 scratch, scratch + img_bytes, xm),
                         "gemm (tcgen05) token image launch");
     count_launch();
     count_launch();
@@ -674,6 +1016,7 @@ int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *o
     p.img = scratch;
     p.img_min = scratch + img_bytes;
     p.ginv = ginv_tab;
+    p.xm = xm;
     p.out = out;
     p.m = w.m;
     p.n = (uint32_t)n;
@@ -682,7 +1025,16 @@ int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *o
     p.ldc = (uint32_t)ldc;
     p.epilogue = epilogue;
     *taken = true;
-    if (rc == CERA_CUDA_OK) {
+    // with a weight image: the wide kernel when its 128 x 256 tiles alone fill the device, else the 128 x 128 one
+    static const int tile_pref = [] {
+        const char *e = getenv("CERA_CUDA_GEMM_TILE");
+        return e ? atoi(e) : 0;
+    }();
+    const uint32_t wide_ctas = tiles * ((w.m + 2 * TC_BN - 1) / (2 * TC_BN));
+    const bool wide = w.tc && (tile_pref == 256 || (tile_pref != 128 && wide_ctas >= 120));
+    if (rc == CERA_CUDA_OK && wide) {
+        rc = launch_tc_wide(p, st);
+    } else if (rc == CERA_CUDA_OK) {
         if (w.tc)
             rc = w.type == CERA_TYPE_Q4_K ? launch_tc_typed<CERA_TYPE_Q4_K, true>(p, st) : launch_tc_typed<CERA_TYPE_Q5_K, true>(p, st);
         else
