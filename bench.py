@@ -612,6 +612,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-alt", action="store_true", help="skip the leg that re-runs the benchmark on the toleranced decode kernels")
     ap.add_argument("--no-stream-check", action="store_true", help="report a stream that differs from the reference's instead of failing")
+    ap.add_argument("--gemm-case", default=None, help="with --only gemm-sweep: a single case type:m:k:n:image (e.g. q4_k:14336:4096:512:1)")
     ap.add_argument("--only", default=None, choices=["roofline", "gemv-sweep", "gemm-sweep", "moe", "attn-sweep"],
                     help="run just the dominant-kernel microbench (the case ncu captures are taken on)")
     ap.add_argument("--iters", type=int, default=200, help="timed launches of the kernel microbench")
@@ -677,8 +678,13 @@ def main():
         if os.path.exists(mp):
             with open(mp) as f:
                 dense, dense_src = json.load(f).get("bf16_tflops", dense), "measured (cuBLAS bf16, burst)"
-        for tname, m, k in [("q4_k", 4096, 4096), ("q4_k", 14336, 4096), ("q6_k", 4096, 14336), ("q5_k", 4096, 4096)]:
-            for n, image in [(8, False), (64, False), (256, False), (512, False), (64, True), (256, True), (512, True), (2048, True)]:
+        shapes = [("q4_k", 4096, 4096), ("q4_k", 14336, 4096), ("q6_k", 4096, 14336), ("q5_k", 4096, 4096)]
+        cols = [(8, False), (64, False), (256, False), (512, False), (64, True), (256, True), (512, True), (2048, True)]
+        if args.gemm_case:  # one case only, e.g. for a profiler capture: type:m:k:n:image
+            tn, cm, ck, cn, ci = args.gemm_case.split(":")
+            shapes, cols = [(tn, int(cm), int(ck))], [(int(cn), ci not in ("0", ""))]
+        for tname, m, k in shapes:
+            for n, image in cols:
                 r = gemm_microbench(torch, cb, tname, m, k, n, max(3, args.iters // (4 if n > 64 else 1)), image=image)
                 if r is None:
                     continue
