@@ -71,6 +71,7 @@ struct ExactParams {
     uint32_t k;
     int epilogue;
     int stages;  // log2 of the ring depth
+    int team;    // log2 of the warps that share one row group's walk over k
     GemvFusion f;
     TpHook tp;
 };
@@ -104,13 +105,19 @@ __device__ __forceinline__ void bulk_g2s_u32(uint32_t dst, const void *src, uint
 __host__ __device__ inline size_t xg_cta_smem(uint32_t k) {  // what the CTA shares: barriers, activation column
     return XG_HEAD_BYTES + (size_t)k + (size_t)(k / 32) * 4 * 2 + (size_t)(k / 16) * 4;
 }
+// A team's mailbox: the chain state of a row group (eight chains and the macc sum of every lane) handed from the warp
+// that finished one segment to the warp that holds the next.  Hand-overs are numbered along the team's walk (group by
+// group, segment by segment) and use 2 W slots in turn, each with its own barrier: a warp that starts to wait for
+// hand-over h has seen h - 2 W complete (at most 2 W - 2 are pending then), which is what a parity wait needs.
+constexpr uint32_t XG_MAIL_SLOT = 9 * 32 * 4;
+__host__ __device__ inline uint32_t xg_mail_bytes(uint32_t team_log) { return (2u << team_log) * (XG_MAIL_SLOT + 8); }
 constexpr uint32_t XG_TERM_STRIDE = 20;              // floats per row of a term buffer (16 terms + padding: conflict-free stores)
 constexpr uint32_t XG_TERM_BYTES = 8 * XG_TERM_STRIDE * 4;
 __host__ __device__ inline size_t xg_warp_smem(uint32_t stages, uint32_t seg_bytes) {  // ring; two scale tables and two term buffers
     return (size_t)stages * seg_bytes + 2 * XG_SCT_BYTES + 2 * XG_TERM_BYTES;
 }
 
-template <int T>
+template <int T, bool TEAM>
 __global__ void __launch_bounds__(XG_MAX_WARPS * 32) gemv_exact_kernel(const ExactParams p) {
     using L = SegLayout<T>;
     extern __shared__ __align__(128) uint8_t xg_smem[];
@@ -133,15 +140,23 @@ __global__ void __launch_bounds__(XG_MAX_WARPS * 32) gemv_exact_kernel(const Exa
     uint8_t *ring = rings + (size_t)warp * S * L::BYTES;
     uint64_t *wbars = bars + warp * XG_MAX_STAGES;
 
-    // this warp's row groups: CTAs take groups round-robin, the warps of a CTA take the CTA's groups round-robin
+    // this warp's row groups: CTAs take groups round-robin, the TEAMS of a CTA take the CTA's groups round-robin, and the
+    // W warps of a team take a group's segments round-robin (W = 1: a warp walks its groups alone)
     const uint32_t n_groups = (p.total_rows + 7) >> 3;
-    const uint32_t first = blockIdx.x + gridDim.x * warp, step = gridDim.x * P;
+    const uint32_t W = 1u << p.team, team = warp >> p.team, wj = warp & (W - 1);
+    const uint32_t first = blockIdx.x + gridDim.x * team, step = gridDim.x * (P >> p.team);
     const uint32_t my_groups = first < n_groups ? (n_groups - first + step - 1) / step : 0;
-    const uint32_t n_items = my_groups * n_seg;  // segments this warp walks, over all its groups
+    const uint32_t n_my_seg = wj < n_seg ? (n_seg - wj + W - 1) >> p.team : 0;  // this warp's segments of a group: wj, wj + W, ...
+    const uint32_t n_items = my_groups * n_my_seg;  // segments this warp walks, over all its groups
+    const uint32_t m_slots = 2 * W, m_log = p.team + 1;
+    uint8_t *mail = reinterpret_cast<uint8_t *>(a16 + 2 * nb32) + (size_t)P * (2 * XG_SCT_BYTES + 2 * XG_TERM_BYTES) + (size_t)team * xg_mail_bytes(p.team);
+    uint64_t *mbars = reinterpret_cast<uint64_t *>(mail + m_slots * XG_MAIL_SLOT);
 
     if (tid == 0) *abort_flag = 0;
     if (lane == 0) {
         for (uint32_t s = 0; s < S; ++s) tma::mbar_init(wbars + s, 1);
+        if (W > 1 && wj == 0)
+            for (uint32_t s = 0; s < m_slots; ++s) tma::mbar_init(mbars + s, 1);
         tma::mbar_init_fence();
     }
 
@@ -165,16 +180,17 @@ __global__ void __launch_bounds__(XG_MAX_WARPS * 32) gemv_exact_kernel(const Exa
                    : lane == 1 ? w.hdr + sb0 * 16
                    : lane == 2 ? w.qh + sb0 * (L::QH / (L::SB * 8))
                                : w.d + sb0 * 2;
+            is_src += (size_t)wj * my_bytes;  // the warp's first segment of the group
         }
         const uint32_t st = is_j & s_mask, bar = bar_u32 + st * 8;
         if (lane == 0) expect_tx_u32(bar, L::TX);
         __syncwarp();
         if (my_bytes) {
             bulk_g2s_u32(ring_u32 + st * L::BYTES + my_off, is_src, my_bytes, bar);
-            is_src += my_bytes;
+            is_src += (size_t)my_bytes << p.team;
         }
         ++is_j;
-        if (++is_seg == n_seg) {
+        if (++is_seg == n_my_seg) {
             is_seg = 0;
             is_group += step;
         }
@@ -326,18 +342,24 @@ __global__ void __launch_bounds__(XG_MAX_WARPS * 32) gemv_exact_kernel(const Exa
     bool ok = true;  // false once a wait on a copy gave up: nothing more is stored
     if (n_items) {
         if (!tma::mbar_wait_blocking(wbars, 0, abort_flag, &g_xg_status, 1u)) ok = false;
-        if (ok) scale_pass(ring, 0, 0);
+        if (ok) scale_pass(ring, wj, 0);
         __syncwarp();
     }
-    uint32_t item = 0;
-    for (uint32_t g = first; g < n_groups; g += step) {
+    uint32_t item = 0, gi = 0;  // gi counts the team's groups (the mailbox slots alternate with it)
+    for (uint32_t g = first; g < n_groups; g += step, ++gi) {
         float2 acc_lo2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)}, acc_hi2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
         float macc = 0.0f;  // every lane of a row carries the row's macc chain (the same adds in the same order)
-        for (uint32_t seg = 0; seg < n_seg; ++seg, ++item) {
+        bool last_mine = !TEAM;  // this warp holds the group's final chain state
+        for (uint32_t sl = 0; sl < n_my_seg; ++sl, ++item) {
+            const uint32_t seg = TEAM ? wj + (sl << p.team) : sl;
             const uint8_t *buf = ring + (size_t)(item & s_mask) * L::BYTES;
             const uint32_t b = item & 1;
             if (ok) {
                 const float *sct = sct0 + b * (XG_SCT_BYTES / 4);
+                // In a team the exact float sums of the segment are formed first (they do not depend on the chain state),
+                // the state arrives from the warp that held the previous segment, and only the FMAs and the macc adds
+                // run on the serial path; a lone warp feeds each sum straight into its FMA.
+                float2 pl[XG_SEG_TASKS][2], ph[XG_SEG_TASKS][2], scs[XG_SEG_TASKS];
                 // ---- the segment's tasks, this lane's strip: per 4 weights one mask, one dp4a, one subtraction, one FMA
 #pragma unroll
                 for (int i = 0; i < XG_SEG_TASKS; ++i) {
@@ -360,8 +382,10 @@ __global__ void __launch_bounds__(XG_MAX_WARPS * 32) gemv_exact_kernel(const Exa
                     }
                     const int4 alo = *reinterpret_cast<const int4 *>(aq + 32 * xb_lo + 16 * half);
                     const int4 ahi = *reinterpret_cast<const int4 *>(aq + 32 * xb_hi + 16 * half);
-                    const float4 tm = *reinterpret_cast<const float4 *>(terms0 + b * (8 * XG_TERM_STRIDE) + rr * XG_TERM_STRIDE + 4 * i);
-                    macc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(macc, tm.x), tm.y), tm.z), tm.w);
+                    if (!TEAM) {
+                        const float4 tm = *reinterpret_cast<const float4 *>(terms0 + b * (8 * XG_TERM_STRIDE) + rr * XG_TERM_STRIDE + 4 * i);
+                        macc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(macc, tm.x), tm.y), tm.z), tm.w);
+                    }
                     uint32_t lo[4], hi[4];
 #pragma unroll
                     for (int wd = 0; wd < 4; ++wd) {
@@ -381,21 +405,63 @@ __global__ void __launch_bounds__(XG_MAX_WARPS * 32) gemv_exact_kernel(const Exa
                     // the subtraction of the bias and the FMA run as packed pairs (add.f32x2 / fma.f32x2: each half is the
                     // IEEE operation of the scalar form, two chains per instruction)
                     const float2 nbias = make_float2(-XG_MAGIC_F, -XG_MAGIC_F), s_lo = make_float2(sc2.x, sc2.x), s_hi = make_float2(sc2.y, sc2.y);
+                    scs[i] = sc2;
 #pragma unroll
                     for (int wp = 0; wp < 2; ++wp) {
                         const float2 rl = make_float2(__int_as_float(dp_us(lo[2 * wp], word_of(alo, 2 * wp), XG_MAGIC_I)),
                                                       __int_as_float(dp_us(lo[2 * wp + 1], word_of(alo, 2 * wp + 1), XG_MAGIC_I)));
                         const float2 rh = make_float2(__int_as_float(dp_us(hi[2 * wp], word_of(ahi, 2 * wp), XG_MAGIC_I)),
                                                       __int_as_float(dp_us(hi[2 * wp + 1], word_of(ahi, 2 * wp + 1), XG_MAGIC_I)));
-                        acc_lo2[wp] = __ffma2_rn(__fadd2_rn(rl, nbias), s_lo, acc_lo2[wp]);
-                        acc_hi2[wp] = __ffma2_rn(__fadd2_rn(rh, nbias), s_hi, acc_hi2[wp]);
+                        if (TEAM) {
+                            pl[i][wp] = __fadd2_rn(rl, nbias);
+                            ph[i][wp] = __fadd2_rn(rh, nbias);
+                        } else {
+                            acc_lo2[wp] = __ffma2_rn(__fadd2_rn(rl, nbias), s_lo, acc_lo2[wp]);
+                            acc_hi2[wp] = __ffma2_rn(__fadd2_rn(rh, nbias), s_hi, acc_hi2[wp]);
+                        }
                     }
                 }
                 // ---- the next segment's scale pass, one segment ahead of its use (it has its own table and term buffer)
                 if (item + 1 < n_items) {
                     const uint32_t nx = item + 1;
                     if (!tma::mbar_wait_blocking(wbars + (nx & s_mask), (nx >> s_shift) & 1, abort_flag, &g_xg_status, 1u)) ok = false;
-                    if (ok) scale_pass(ring + (size_t)(nx & s_mask) * L::BYTES, seg + 1 == n_seg ? 0 : seg + 1, b ^ 1);
+                    const uint32_t nseg = TEAM ? (sl + 1 == n_my_seg ? wj : seg + W) : (seg + 1 == n_seg ? 0 : seg + 1);
+                    if (ok) scale_pass(ring + (size_t)(nx & s_mask) * L::BYTES, nseg, b ^ 1);
+                }
+                if (TEAM) {
+                    // ---- the serial path: chain state in, the segment's FMAs and macc adds in task order, chain state out
+                    if (seg > 0) {
+                        const uint32_t h = gi * (n_seg - 1) + seg - 1, slot = h & (m_slots - 1);  // the hand-over after segment seg - 1
+                        if (!tma::mbar_wait_blocking(mbars + slot, (h >> m_log) & 1, abort_flag, &g_xg_status, 2u)) ok = false;
+                        const float *ms = reinterpret_cast<const float *>(mail + slot * XG_MAIL_SLOT) + lane;
+                        acc_lo2[0] = make_float2(ms[0], ms[32]);
+                        acc_lo2[1] = make_float2(ms[64], ms[96]);
+                        acc_hi2[0] = make_float2(ms[128], ms[160]);
+                        acc_hi2[1] = make_float2(ms[192], ms[224]);
+                        macc = ms[256];
+                    }
+#pragma unroll
+                    for (int i = 0; i < XG_SEG_TASKS; ++i) {
+                        const float4 tm = *reinterpret_cast<const float4 *>(terms0 + b * (8 * XG_TERM_STRIDE) + rr * XG_TERM_STRIDE + 4 * i);
+                        macc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(macc, tm.x), tm.y), tm.z), tm.w);
+                        const float2 s_lo = make_float2(scs[i].x, scs[i].x), s_hi = make_float2(scs[i].y, scs[i].y);
+#pragma unroll
+                        for (int wp = 0; wp < 2; ++wp) {
+                            acc_lo2[wp] = __ffma2_rn(pl[i][wp], s_lo, acc_lo2[wp]);
+                            acc_hi2[wp] = __ffma2_rn(ph[i][wp], s_hi, acc_hi2[wp]);
+                        }
+                    }
+                    if (seg + 1 < n_seg) {
+                        const uint32_t slot = (gi * (n_seg - 1) + seg) & (m_slots - 1);
+                        float *ms = reinterpret_cast<float *>(mail + slot * XG_MAIL_SLOT) + lane;
+                        ms[0] = acc_lo2[0].x, ms[32] = acc_lo2[0].y, ms[64] = acc_lo2[1].x, ms[96] = acc_lo2[1].y;
+                        ms[128] = acc_hi2[0].x, ms[160] = acc_hi2[0].y, ms[192] = acc_hi2[1].x, ms[224] = acc_hi2[1].y;
+                        ms[256] = macc;
+                        __syncwarp();
+                        if (lane == 0 && ok) tma::mbar_arrive(mbars + slot);
+                    } else {
+                        last_mine = true;
+                    }
                 }
             }
             __syncwarp();  // every lane is done with this segment's buffer, table and terms; the next ones are written
@@ -404,6 +470,7 @@ __global__ void __launch_bounds__(XG_MAX_WARPS * 32) gemv_exact_kernel(const Exa
                 issue_next();
             }
         }
+        if (!last_mine) continue;  // another warp of the team finishes this group
         // ---- the 32 chains of the row -> one value (tree over the accumulators, then the hsum256 order)
         const float acc_lo[4] = {acc_lo2[0].x, acc_lo2[0].y, acc_lo2[1].x, acc_lo2[1].y}, acc_hi[4] = {acc_hi2[0].x, acc_hi2[0].y, acc_hi2[1].x, acc_hi2[1].y};
         float f[4];
@@ -498,17 +565,44 @@ int32_t launch_exact_typed(const ExactParams &p0, cudaStream_t st) {
     if (env_p >= 1) P = (uint32_t)env_p < share ? (uint32_t)env_p : share;
     if (P > max_warps(1u << s_log)) P = max_warps(1u << s_log);
     if (P == 0) return fail(CERA_CUDA_ERR_BAD_ARG, "gemv (reference order): k too large for shared memory");
+    // Few row groups per SM (o-proj, down-proj): the warps that would idle join TEAMS of W = 2 or 4 that share one
+    // group's walk over k - each forms the exact sums of its segments on its own, only the FMA chains pass from warp to
+    // warp in segment order.  CERA_CUDA_XG_TEAM (log2 W) overrides.
+    static const int env_t = [] { const char *e = getenv("CERA_CUDA_XG_TEAM"); return e ? atoi(e) : -1; }();
+    const uint32_t n_seg = p.k / (128 * XG_SEG_TASKS);
+    uint32_t t_log = 0;
+    if (env_p < 1) {
+        while (t_log < 2 && (share << (t_log + 1)) <= (uint32_t)XG_MAX_WARPS && (2u << t_log) <= n_seg) ++t_log;
+        if (env_t >= 0 && env_t <= 2) t_log = (uint32_t)env_t;
+        while (t_log && ((2u << (t_log - 1)) > n_seg)) --t_log;
+        if (t_log) {
+            // teams x W warps, each warp with its ring, plus a mailbox per team; shrink the ring, then the team, to fit
+            for (;;) {
+                const uint32_t Pt = share << t_log;
+                const size_t need = cta + (size_t)Pt * xg_warp_smem(1u << s_log, L::BYTES) + (size_t)share * xg_mail_bytes(t_log);
+                if (Pt <= (uint32_t)XG_MAX_WARPS && need <= XG_SMEM_LIMIT) {
+                    P = Pt;
+                    break;
+                }
+                if (s_log > 1 && Pt <= (uint32_t)XG_MAX_WARPS) --s_log;
+                else if (--t_log == 0) break;
+            }
+        }
+    }
     p.stages = (int)s_log;
-    const size_t smem = cta + (size_t)P * xg_warp_smem(1u << s_log, L::BYTES);
+    p.team = (int)t_log;
+    const size_t smem = cta + (size_t)P * xg_warp_smem(1u << s_log, L::BYTES) + (t_log ? (size_t)(P >> t_log) * xg_mail_bytes(t_log) : 0);
     static thread_local int raised_dev = -1;  // per instantiation: opt in to more than 48 KB once per device
     int dev = 0;
     cudaGetDevice(&dev);
     if (raised_dev != dev) {
-        CERA_CUDA_TRY(cudaFuncSetAttribute(gemv_exact_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)XG_SMEM_LIMIT));
+        CERA_CUDA_TRY(cudaFuncSetAttribute(gemv_exact_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)XG_SMEM_LIMIT));
+        CERA_CUDA_TRY(cudaFuncSetAttribute(gemv_exact_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)XG_SMEM_LIMIT));
         raised_dev = dev;
     }
     count_launch();
-    return check_cuda(launch_k(gemv_exact_kernel<T>, dim3(grid), dim3(P * 32), smem, st, p), "gemv (reference order) launch");
+    if (t_log) return check_cuda(launch_k(gemv_exact_kernel<T, true>, dim3(grid), dim3(P * 32), smem, st, p), "gemv (reference order, teams) launch");
+    return check_cuda(launch_k(gemv_exact_kernel<T, false>, dim3(grid), dim3(P * 32), smem, st, p), "gemv (reference order) launch");
 }
 
 }  // namespace
