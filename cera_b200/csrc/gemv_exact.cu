@@ -565,28 +565,29 @@ int32_t launch_exact_typed(const ExactParams &p0, cudaStream_t st) {
     if (env_p >= 1) P = (uint32_t)env_p < share ? (uint32_t)env_p : share;
     if (P > max_warps(1u << s_log)) P = max_warps(1u << s_log);
     if (P == 0) return fail(CERA_CUDA_ERR_BAD_ARG, "gemv (reference order): k too large for shared memory");
-    // Few row groups per SM (o-proj, down-proj): the warps that would idle join TEAMS of W = 2 or 4 that share one
+    // Few row groups per SM (o-proj, down-proj, a tensor-parallel rank's slices): the warps that would idle join TEAMS of
+    // W = 2 .. 16 that share one
     // group's walk over k - each forms the exact sums of its segments on its own, only the FMA chains pass from warp to
     // warp in segment order.  CERA_CUDA_XG_TEAM (log2 W) overrides.
     static const int env_t = [] { const char *e = getenv("CERA_CUDA_XG_TEAM"); return e ? atoi(e) : -1; }();
     const uint32_t n_seg = p.k / (128 * XG_SEG_TASKS);
     uint32_t t_log = 0;
     if (env_p < 1) {
-        while (t_log < 2 && (share << (t_log + 1)) <= (uint32_t)XG_MAX_WARPS && (2u << t_log) <= n_seg) ++t_log;
-        if (env_t >= 0 && env_t <= 2) t_log = (uint32_t)env_t;
-        while (t_log && ((2u << (t_log - 1)) > n_seg)) --t_log;
-        if (t_log) {
-            // teams x W warps, each warp with its ring, plus a mailbox per team; shrink the ring, then the team, to fit
-            for (;;) {
-                const uint32_t Pt = share << t_log;
-                const size_t need = cta + (size_t)Pt * xg_warp_smem(1u << s_log, L::BYTES) + (size_t)share * xg_mail_bytes(t_log);
-                if (Pt <= (uint32_t)XG_MAX_WARPS && need <= XG_SMEM_LIMIT) {
-                    P = Pt;
-                    break;
-                }
-                if (s_log > 1 && Pt <= (uint32_t)XG_MAX_WARPS) --s_log;
-                else if (--t_log == 0) break;
+        while (t_log < 4 && (share << (t_log + 1)) <= (uint32_t)XG_MAX_WARPS && (2u << t_log) <= n_seg) ++t_log;
+        if (env_t >= 0 && env_t <= 4) t_log = (uint32_t)env_t;
+        while (t_log && ((1u << t_log) > n_seg)) --t_log;
+        while (t_log) {
+            // whole teams, at most sixteen warps, each warp with its ring, plus a mailbox per team; shrink the ring, then
+            // the team, to fit
+            uint32_t Pt = share << t_log;
+            if (Pt > (uint32_t)XG_MAX_WARPS) Pt = (uint32_t)XG_MAX_WARPS;
+            const size_t need = cta + (size_t)Pt * xg_warp_smem(1u << s_log, L::BYTES) + (size_t)(Pt >> t_log) * xg_mail_bytes(t_log);
+            if (need <= XG_SMEM_LIMIT) {
+                P = Pt;
+                break;
             }
+            if (s_log > 1) --s_log;
+            else --t_log;
         }
     }
     p.stages = (int)s_log;
