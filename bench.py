@@ -15,7 +15,7 @@ token ids.  One JSON line goes to stdout.
           on the model's stream), all inputs resident in HBM.
   e2e   : the same K steps through cera_cuda_forward_greedy, one call per token
           with the token id going in from, and coming back to, host memory.
-  roofline : the dominant kernel (Q4_K GEMV at the 14336 x 4096 gate/up shape)
+  roofline : the dominant kernel launch of the step (Q4_K GEMV over gate and up together: 28672 rows x 4096)
           timed alone with CUDA events, rotating over distinct weight copies
           larger than L2, against the measured HBM copy bandwidth.
   stream_check : every decoded token against the committed CPU reference stream
@@ -215,7 +215,7 @@ def bench_config(prompt_len, world, stream_head):
             "parallelism": (f"tensor-parallel x{world}: rows of every matrix split over the GPUs, slices pushed into peer memory "
                             "over NVLink inside the step") if world > 1 else "1 GPU",
             "stream_head": stream_head,
-            "l2": "each token streams 4.84 GB of weights (>> 126 MB L2); the kernel microbench rotates 16 weight copies (528 MB)"}
+            "l2": "each token streams 4.84 GB of weights (>> 126 MB L2); the kernel microbench rotates distinct weight copies (528 MB)"}
 
 
 def reference_stream():
@@ -399,7 +399,7 @@ def moe_ep_microbench(torch, cb, iters, rank, world, n_total=512):
             "tops": 2.0 * n_total * used * 3 * ff * hs / ms / 1e9, "parallelism": "expert-parallel, peer-store dispatch and combine"}
 
 
-ROOFLINE_KERNEL = "gemv_exact_kernel<Q4_K> 14336x4096 (reference-order decode GEMV, gate / up shape)"
+ROOFLINE_KERNEL = "gemv_exact_kernel<Q4_K> 28672x4096 (reference-order decode GEMV, gate and up in one launch as the step issues them)"
 
 
 def roofline_traffic():
@@ -414,13 +414,14 @@ def roofline_traffic():
 
 
 def roofline_q4k_gemv(torch, cb, iters):
-    """The dominant kernel of the decode step: the Q4_K GEMV at the gate/up shape."""
-    return gemv_microbench(torch, cb, "q4_k", 14336, 4096, iters)
+    """The dominant kernel launch of the decode step: the Q4_K GEMV over the gate and up matrices together (the step
+    issues them as one launch of 2 x 14336 rows that share the activation column; here one matrix of 28672 rows)."""
+    return gemv_microbench(torch, cb, "q4_k", 28672, 4096, iters)
 
 
 DECODE_SHAPES = [("q4_k", 4096, 4096), ("q4_k", 14336, 4096), ("q6_k", 4096, 14336), ("q6_k", 128256, 4096),
                  ("q5_k", 4096, 4096), ("q6_k", 4096, 4096), ("q4_0", 4096, 4096), ("q8_0", 4096, 4096),
-                 ("q4_1", 4096, 4096), ("q4_k", 4096, 14336)]
+                 ("q4_1", 4096, 4096), ("q4_k", 4096, 14336), ("q4_k", 28672, 4096)]  # the last: gate and up in one launch
 
 
 def cuda_arm(args, rank, world):

@@ -51,11 +51,12 @@ __device__ unsigned int g_xg_status = 0;
 
 namespace {
 
-constexpr int XG_MAX_WARPS = 16;                     // warps per CTA (picked per launch)
+constexpr int XG_MAX_WARPS = 16;                     // warps per CTA when they form teams (picked per launch)
+constexpr int XG_LONE_MAX_WARPS = 32;                // ... when every warp walks its groups alone (64 registers per thread)
 constexpr int XG_MAX_SEGS = 3;
 constexpr int XG_SEG_TASKS = 4;                      // tasks (of 128 weights) per segment: two super-blocks
 constexpr int XG_MAX_STAGES = 8;
-constexpr int XG_HEAD_BYTES = 1088;                  // barriers [16][8], then the abort flag
+constexpr int XG_HEAD_BYTES = 2112;                  // barriers [32][8], then the abort flag
 constexpr int XG_MAGIC_I = 0x4B400000;               // bits of 12582912.0f = 1.5 * 2^23
 constexpr float XG_MAGIC_F = 12582912.0f;
 constexpr size_t XG_SMEM_LIMIT = 224 * 1024;
@@ -118,7 +119,7 @@ __host__ __device__ inline size_t xg_warp_smem(uint32_t stages, uint32_t seg_byt
 }
 
 template <int T, bool TEAM>
-__global__ void __launch_bounds__(XG_MAX_WARPS * 32) gemv_exact_kernel(const ExactParams p) {
+__global__ void __launch_bounds__((TEAM ? XG_MAX_WARPS : XG_LONE_MAX_WARPS) * 32) gemv_exact_kernel(const ExactParams p) {
     using L = SegLayout<T>;
     extern __shared__ __align__(128) uint8_t xg_smem[];
     const uint32_t k = p.k, nb32 = k >> 5, nb = k >> 8, n_seg = k / (128 * XG_SEG_TASKS);
@@ -544,17 +545,21 @@ int32_t launch_exact_typed(const ExactParams &p0, cudaStream_t st) {
     const uint32_t grid = groups < sms ? groups : sms;
     const uint32_t share = (groups + grid - 1) / grid;
     const size_t cta = xg_cta_smem(p.k);
+    static const int env_cap = [] { const char *e = getenv("CERA_CUDA_XG_CAP"); return e ? atoi(e) : 0; }();
+    // lone warps: up to 32 per CTA (28 672 gate / up rows give an SM 24 groups: one round of 25 warps instead of two of 16;
+    // CERA_CUDA_XG_CAP lowers the cap for A/B runs)
+    const uint32_t warp_cap = env_cap >= 1 && env_cap <= XG_LONE_MAX_WARPS ? (uint32_t)env_cap : (uint32_t)XG_LONE_MAX_WARPS;
     auto max_warps = [&](uint32_t stages) -> uint32_t {
         const size_t per_warp = xg_warp_smem(stages, L::BYTES);
         if (cta + per_warp > XG_SMEM_LIMIT) return 0;
         const size_t n = (XG_SMEM_LIMIT - cta) / per_warp;
-        return n > (size_t)XG_MAX_WARPS ? (uint32_t)XG_MAX_WARPS : (uint32_t)n;
+        return n > (size_t)warp_cap ? warp_cap : (uint32_t)n;
     };
     uint32_t s_log = 3, P = share;
     if (P > max_warps(8)) s_log = 2;
     if (s_log == 2 && P > max_warps(4)) {
         // more groups than warps fit: keep the deeper ring unless that costs more than a quarter of the warps
-        if (max_warps(4) * 4 >= (P < (uint32_t)XG_MAX_WARPS ? P : (uint32_t)XG_MAX_WARPS) * 3) P = max_warps(4);
+        if (max_warps(4) * 4 >= (P < warp_cap ? P : warp_cap) * 3) P = max_warps(4);
         else s_log = 1;
     }
     if (s_log == 1 && P > max_warps(2)) P = max_warps(2);
