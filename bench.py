@@ -614,7 +614,7 @@ def main():
     ap.add_argument("--no-alt", action="store_true", help="skip the leg that re-runs the benchmark on the toleranced decode kernels")
     ap.add_argument("--no-stream-check", action="store_true", help="report a stream that differs from the reference's instead of failing")
     ap.add_argument("--gemm-case", default=None, help="with --only gemm-sweep: a single case type:m:k:n:image (e.g. q4_k:14336:4096:512:1)")
-    ap.add_argument("--only", default=None, choices=["roofline", "gemv-sweep", "gemm-sweep", "moe", "attn-sweep"],
+    ap.add_argument("--only", default=None, choices=["roofline", "gemv-sweep", "gemm-sweep", "moe", "attn-sweep", "prefill"],
                     help="run just the dominant-kernel microbench (the case ncu captures are taken on)")
     ap.add_argument("--iters", type=int, default=200, help="timed launches of the kernel microbench")
     args = ap.parse_args()
@@ -665,6 +665,22 @@ def main():
             emit(json.dumps(res))
         dist.barrier()
         dist.destroy_process_group()
+    elif args.only == "prefill":
+        # the batched prompt alone (tensor-core GEMMs, tiled attention): one warm pass, one timed pass
+        import torch
+        from cera_b200 import synth
+        cfg = dict(synth.LLAMA3_8B)
+        model = synth.build_llama(cfg, seed=args.seed, max_seq_len=args.prompt_len + 16)
+        prompt = synth.prompt_tokens(args.prompt_len, cfg["vocab_size"], seed=7)
+        model.forward_prefill(prompt, 0, want_logits=False)
+        model.truncate_kv(0)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        model.forward_prefill(prompt, 0)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        emit(json.dumps({"prompt_len": args.prompt_len, "batched_prefill_s": round(dt, 4), "tok_s": round(args.prompt_len / dt, 1)}))
+        model.close()
     elif args.only == "moe":
         import torch
         import cera_b200 as cb

@@ -57,7 +57,7 @@ struct Layer {
     void *kc = nullptr, *vc = nullptr;
 };
 
-constexpr size_t PREFILL_CHUNK = 256;
+constexpr size_t PREFILL_CHUNK = 512;
 
 enum GraphKind { G_BODY = 0, G_LOGITS = 1, G_GREEDY = 2, G_CHAIN = 3 };
 

@@ -109,18 +109,18 @@ def test_wide_llama_matches_oracle(kv_f16):
 
 
 def test_batched_prefill_matches_oracle_and_crosses_a_chunk_boundary():
-    """300 prompt tokens = one full 256-token chunk + a ragged one, through the batched kernels; the last-token logits
+    """600 prompt tokens = one full 512-token chunk + a ragged one, through the batched kernels; the last-token logits
     against the oracle's per-token forward, then decode continues from the batched KV cache."""
     need_gpu()
     from cera_b200 import synth
-    gpu, oracle = _pair(SMALL, seed=13, max_seq_len=320, threads=4)
-    prompt = synth.prompt_tokens(300, SMALL["vocab_size"], seed=6)
+    gpu, oracle = _pair(SMALL, seed=13, max_seq_len=620, threads=4)
+    prompt = synth.prompt_tokens(600, SMALL["vocab_size"], seed=6)
     lp = gpu.forward_prefill(prompt, 0)
     for pos, t in enumerate(prompt):
         lo = oracle.forward(int(t), pos)
-    assert_model_logits(lp, lo, "batched prefill, 300 tokens")
+    assert_model_logits(lp, lo, "batched prefill, 600 tokens")
     tok = int(O.argmax(lo))
-    assert_model_logits(gpu.forward(tok, 300), oracle.forward(tok, 300), "decode after batched prefill")
+    assert_model_logits(gpu.forward(tok, 600), oracle.forward(tok, 600), "decode after batched prefill")
 
 
 def test_batched_prefill_wide_model_and_f16_kv():
@@ -252,16 +252,16 @@ def test_prefill_logits_for_every_position():
     need_gpu()
     from cera_b200 import synth
     cfg = dict(SMALL, n_layers=1)
-    a = synth.build_llama(cfg, seed=17, max_seq_len=320)
-    b = synth.build_llama(cfg, seed=17, max_seq_len=320)
-    prompt = synth.prompt_tokens(270, cfg["vocab_size"], seed=8)
+    a = synth.build_llama(cfg, seed=17, max_seq_len=560)
+    b = synth.build_llama(cfg, seed=17, max_seq_len=560)
+    prompt = synth.prompt_tokens(530, cfg["vocab_size"], seed=8)
     rows = a.forward_prefill_logits_all(prompt, 0)
-    assert rows.shape == (270, cfg["vocab_size"]) and a.seq_len == 270
+    assert rows.shape == (530, cfg["vocab_size"]) and a.seq_len == 530
     want = [b.forward(int(t), pos) for pos, t in enumerate(prompt)]
-    for pos in (0, 1, 100, 255, 256, 269):
+    for pos in (0, 1, 100, 255, 256, 511, 512, 529):
         assert_model_logits(rows[pos], want[pos], f"position {pos}")
     nxt = int(np.argmax(rows[-1]))
-    assert_model_logits(a.forward(nxt, 270), b.forward(nxt, 270), "next token after the two prefills")
+    assert_model_logits(a.forward(nxt, 530), b.forward(nxt, 530), "next token after the two prefills")
 
 
 def test_lora_adapters_match_reference_and_detach_cleanly():
