@@ -157,7 +157,7 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
     const bool tp = m->tp_size > 1;
     const float scale = c.attention_scale != 0.0f ? c.attention_scale : 1.0f / sqrtf((float)c.head_dim);
     const float res_scale = c.residual_scale != 0.0f ? c.residual_scale : 1.0f;  // Granite: block outputs are scaled before the residual add
-    // Exchange slots of layer l: 4l = Q8_0 attention output, 4l+1 = residual after o-proj, 4l+2 = Q8_0 SwiGLU
+    // Exchange slots of layer l: 4l = Q8_0 attention output, 4l+1 = (unused), 4l+2 = Q8_0 SwiGLU
     // activations, 4l+3 = residual after down-proj; then 4L = logits, 4L+1 = greedy pairs.  The producing kernel
     // mirrors its stores into the peers' regions; the consuming kernel signals and waits in its prologue.
     const uint32_t n_layers = (uint32_t)m->layers.size();
@@ -189,8 +189,9 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
     for (uint32_t li = 0; li < n_layers; ++li) {
         Layer &L = m->layers[li];
         const uint32_t s0 = 4 * li;
-        const TpHook h_norm1 = hook(li ? s0 - 1 : TP_NO_SLOT, false), h_merge = hook(TP_NO_SLOT, true), h_wo = hook(s0, true),
-                     h_norm2 = hook(s0 + 1, false), h_silu = hook(TP_NO_SLOT, true), h_down = hook(s0 + 2, true);
+        // (slot s0 + 1 is unused: every rank holds the whole o-proj, so the residual after it needs no exchange)
+        const TpHook h_norm1 = hook(li ? s0 - 1 : TP_NO_SLOT, false), h_merge = hook(TP_NO_SLOT, true), h_wo = hook(s0, false),
+                     h_norm2 = hook(TP_NO_SLOT, false), h_silu = hook(TP_NO_SLOT, true), h_down = hook(s0 + 2, true);
         // LoRA deltas read the f32 input of the projection they adapt (cera/src/model/transformer.rs:1383-1387,
         // 1519-1528, 1588-1605, 1642-1651): the normed hidden, the attention output, the SwiGLU product
         float *normed_f32 = m->has_lora ? m->normed : nullptr;
@@ -261,7 +262,7 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
             CERA_TRY(lora(3, m->attn, m->g));
             CERA_TRY(launch_scaled_add(m->hidden, m->g, hs, res_scale, st));
         } else {
-            GemvSeg so{L.wo->v, hidden_slice};
+            GemvSeg so{L.wo->v, m->hidden};  // all rows on every rank
             CERA_TRY(launch_gemv(&so, 1, m->act_q.view(), 1, 1, EPI_ADD, st, 1, false, &h_wo));
             CERA_TRY(lora(3, m->attn, m->hidden));  // o-proj output lives in the residual stream already
         }
@@ -602,7 +603,10 @@ int32_t cera_cuda_model_add_tensor(cera_cuda_model *m, int32_t role, int32_t lay
         case CERA_ROLE_ATTN_Q: return matrix(&L->wq, qd, c.hidden_size);
         case CERA_ROLE_ATTN_K: return matrix(&L->wk, kvd, c.hidden_size);
         case CERA_ROLE_ATTN_V: return matrix(&L->wv, kvd, c.hidden_size);
-        case CERA_ROLE_ATTN_OUTPUT: return matrix(&L->wo, c.hidden_size, qd);
+        // the o-proj is kept whole on every rank of a tensor-parallel model: its launch is latency-bound either way
+        // (4096 x 4096: 6 us whole or halved), and a rank that computes all of its rows needs no exchange of the
+        // residual stream after it - one NVLink round trip less per layer
+        case CERA_ROLE_ATTN_OUTPUT: return matrix(&L->wo, c.hidden_size, qd, false);
         case CERA_ROLE_FFN_GATE: return matrix(&L->gate, c.intermediate_size, c.hidden_size);
         case CERA_ROLE_FFN_UP: return matrix(&L->up, c.intermediate_size, c.hidden_size);
         case CERA_ROLE_FFN_DOWN: return matrix(&L->down, c.hidden_size, c.intermediate_size);
