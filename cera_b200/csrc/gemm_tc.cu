@@ -906,6 +906,227 @@ int32_t launch_tc_typed(const TcParams &p, cudaStream_t st) {
                       "gemm (tcgen05) launch");
 }
 
+// ---- Q6_K ---------------------------------------------------------------------------------------------------------
+// w = d * sc * (q - 32) with an int8 scale per 16 elements: B = sc * (q - 32) reaches 4096 in magnitude, one bit more than
+// f16 holds exactly.  The image therefore keeps B as TWO exact f16 operands, B with its lowest bit cleared (an even
+// integer up to 4096) and that bit (0 or 1); per k-step the kernel issues three MMAs into one accumulator - even part x
+// activations high, even part x activations low, low bit x activations high (low bit x activations low is below 2^-22
+// of the sum) - and the epilogue is out += d * D / g per super-block (Q6_K has no min term).  128 tokens x 128 rows per
+// CTA, stages of 32 k (activations 2 x 8 KB out of the 64-k tiles of tc_token_image_kernel, weights 16 KB), six stages.
+constexpr int TC6_KS = 32, TC6_STAGES = 6;
+constexpr uint32_t TC6_HALF = TC_OP_BYTES / 2;                 // one operand tile of a 32-k stage: 8 KB
+constexpr uint32_t TC6_STAGE_BYTES = 4 * TC6_HALF;             // A high, A low, B even, B low bit
+constexpr uint32_t TC6_DVAL_OFF = TC6_STAGES * TC6_STAGE_BYTES;
+constexpr uint32_t TC6_TAIL_OFF = TC6_DVAL_OFF + 2 * TC_BN * 4;
+constexpr uint32_t TC6_SMEM_BYTES = TC6_TAIL_OFF + 256;
+constexpr uint32_t TC6_TMEM_COLS = 256;
+
+// Image of a Q6_K weight: per (128-row tile, 32-k stage) [even part 8 KB | low bit 8 KB], then per (tile, super-block)
+// d[128].  grid (k / 32, tiles), thread = row.
+__global__ void __launch_bounds__(TC_BN) tc_weight_image6_kernel(const WeightView w, uint8_t *__restrict__ img, float *__restrict__ dvals) {
+    const uint32_t r = threadIdx.x, xb = blockIdx.x, tile = blockIdx.y, n_it = w.k / TC6_KS, n_sb = w.k / 256;
+    const uint32_t row = min(tile * TC_BN + r, w.m - 1);
+    const uint32_t t = xb >> 2, g = xb & 3, sb = xb >> 3;  // 128-weight task, 32-element group of the task, super-block
+    const size_t sbi = sb_index(w, row, sb);
+    const uint4 sc16 = __ldg(reinterpret_cast<const uint4 *>(w.hdr) + sbi);
+    const uint32_t scw[4] = {sc16.x, sc16.y, sc16.z, sc16.w};
+    uint8_t *even_t = img + ((size_t)tile * n_it + xb) * (2 * TC6_HALF), *low_t = even_t + TC6_HALF;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        // elements [16 half, +16) of the group: low (groups 0, 1) or high (groups 2, 3) nibbles of piece 2 (g % 2) + half,
+        // bits 2 g, 2 g + 1 of the task's high-bit piece `half`, scale 8 (t % 2) + 2 g + half of the super-block
+        const uint4 pc = __ldg(reinterpret_cast<const uint4 *>(q_piece_ptr(w, row, 4, t * 4 + 2 * (g & 1) + half)));
+        const uint4 hb = __ldg(reinterpret_cast<const uint4 *>(w.qh + sbi * 64 + (t & 1) * 32 + half * 16));
+        const uint32_t si = (t & 1) * 8 + 2 * g + half;
+        const int sc = (int)(int8_t)(scw[si >> 2] >> (8 * (si & 3)));
+        const uint32_t pw[4] = {pc.x, pc.y, pc.z, pc.w}, hw[4] = {hb.x, hb.y, hb.z, hb.w};
+        __align__(16) __half ev[16], lw[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t byte = (pw[j >> 2] >> (8 * (j & 3))) & 0xFF, hbyte = (hw[j >> 2] >> (8 * (j & 3))) & 0xFF;
+            const int q = (int)((g < 2 ? byte & 0xF : byte >> 4) | (((hbyte >> (2 * g)) & 3) << 4)) - 32;
+            const int b = sc * q, b0 = b & 1;
+            ev[j] = __int2half_rn(b - b0);
+            lw[j] = __int2half_rn(b0);
+        }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            *reinterpret_cast<uint4 *>(even_t + op_off(2 * half + c, r)) = *reinterpret_cast<const uint4 *>(&ev[8 * c]);
+            *reinterpret_cast<uint4 *>(low_t + op_off(2 * half + c, r)) = *reinterpret_cast<const uint4 *>(&lw[8 * c]);
+        }
+    }
+    if ((xb & 7) == 0) dvals[((size_t)tile * n_sb + sb) * TC_BN + r] = h2f(__ldg(reinterpret_cast<const uint16_t *>(w.d) + sbi));
+}
+
+__global__ void __launch_bounds__(TC_THREADS_IMG, 1) gemm_tc6_kernel(const TcParams p) {
+    extern __shared__ __align__(1024) uint8_t tc_smem[];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tc_smem + TC6_TAIL_OFF);
+    uint64_t *full_ab = bars, *empty_ab = bars + TC6_STAGES, *full_d = bars + 2 * TC6_STAGES, *empty_d = full_d + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC6_STAGES + 4);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t col0 = blockIdx.x * TC_BM, row0 = blockIdx.y * TC_BN;
+    const uint32_t n_sb = p.k / 256, n_it = p.k / TC6_KS, tiles_m = (p.m + TC_BN - 1) / TC_BN;
+    if (tid == 0) {
+        for (int s = 0; s < TC6_STAGES; ++s) {
+            tma::mbar_init(full_ab + s, 1);
+            tma::mbar_init(empty_ab + s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            tma::mbar_init(full_d + b, 1);
+            tma::mbar_init(empty_d + b, TC_EPI_WARPS);
+        }
+        *abort_flag = 0;
+        tma::mbar_init_fence();
+    }
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, TC6_TMEM_COLS);
+        tmem_relinquish();
+    }
+    pdl_trigger();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {  // ---- MMA issue
+            const uint32_t idesc = tc_idesc(TC_BM, TC_BN);
+            bool ok = true;
+            uint32_t it = 0;
+            for (uint32_t sb = 0; sb < n_sb && ok; ++sb) {
+                const uint32_t buf = sb & 1, d0 = tmem + buf * TC_BN;
+                if (!tma::mbar_wait_blocking(empty_d + buf, ((sb >> 1) & 1) ^ 1, abort_flag, &g_tc_status, 2u)) break;
+                tc_fence_after();
+                for (uint32_t st = 0; st < 8; ++st, ++it) {
+                    const uint32_t s = it % TC6_STAGES;
+                    if (!tma::mbar_wait_blocking(full_ab + s, (it / TC6_STAGES) & 1, abort_flag, &g_tc_status, 1u)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_hi = tma::smem_u32(tc_smem + s * TC6_STAGE_BYTES), a_lo = a_hi + TC6_HALF, b_ev = a_lo + TC6_HALF, b_lo = b_ev + TC6_HALF;
+#pragma unroll
+                    for (uint32_t ks = 0; ks < TC6_KS / 16; ++ks) {
+                        const uint32_t o = 2 * ks * TC_KC_STRIDE;
+                        const uint64_t ah = smem_desc(a_hi + o, TC_KC_STRIDE, 128), be = smem_desc(b_ev + o, TC_KC_STRIDE, 128);
+                        tc_mma_f16(d0, ah, be, idesc, (st | ks) != 0);
+                        tc_mma_f16(d0, smem_desc(a_lo + o, TC_KC_STRIDE, 128), be, idesc, 1);
+                        tc_mma_f16(d0, ah, smem_desc(b_lo + o, TC_KC_STRIDE, 128), idesc, 1);
+                    }
+                    tc_commit(empty_ab + s);
+                }
+                if (ok) tc_commit(full_d + buf);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {  // ---- operands (bulk asynchronous copies)
+            const uint8_t *img = p.img + (size_t)blockIdx.x * (p.k / TC_KS) * (2 * TC_OP_BYTES);
+            const uint8_t *wimg = p.w.tc + (size_t)blockIdx.y * n_it * (2 * TC6_HALF);
+            const uint8_t *dv = p.w.tc + (size_t)tiles_m * n_it * (2 * TC6_HALF) + (size_t)blockIdx.y * n_sb * (TC_BN * 4);
+            for (uint32_t it = 0; it < n_it; ++it) {
+                const uint32_t s = it % TC6_STAGES, sb = it >> 3, st = it & 7;
+                if (!tma::mbar_wait_blocking(empty_ab + s, ((it / TC6_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) break;
+                if (st == 0 && sb >= 2 && !tma::mbar_wait_blocking(empty_d + (sb & 1), ((sb - 2) >> 1) & 1, abort_flag, &g_tc_status, 8u)) break;
+                uint8_t *dst = tc_smem + s * TC6_STAGE_BYTES;
+                // the 64-k activation stage it / 2 holds [high 16 KB | low 16 KB]; its k half it % 2 is 8 contiguous KB of each
+                const uint8_t *a = img + (size_t)(it >> 1) * (2 * TC_OP_BYTES) + (it & 1) * TC6_HALF;
+                tma::mbar_expect_tx(full_ab + s, TC6_STAGE_BYTES + (st == 0 ? TC_BN * 4 : 0));
+                tma::bulk_g2s(dst, a, TC6_HALF, full_ab + s);
+                tma::bulk_g2s(dst + TC6_HALF, a + TC_OP_BYTES, TC6_HALF, full_ab + s);
+                tma::bulk_g2s(dst + 2 * TC6_HALF, wimg + (size_t)it * (2 * TC6_HALF), 2 * TC6_HALF, full_ab + s);
+                if (st == 0) tma::bulk_g2s(tc_smem + TC6_DVAL_OFF + (sb & 1) * (TC_BN * 4), dv + (size_t)sb * (TC_BN * 4), TC_BN * 4, full_ab + s);
+            }
+        }
+    } else {
+        // ---- epilogue: thread = (token lane, 64 rows), the running output in registers
+        const uint32_t e = warp - 2, quad = warp & 3, ch = e >> 2;
+        const uint32_t tl = quad * 32 + lane;
+        const uint32_t lane_addr = tmem + ((quad * 32) << 16);
+        float acc[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+        float ginv = 1.0f;
+        bool ok = true;
+        for (uint32_t sb = 0; sb < n_sb && ok; ++sb) {
+            const uint32_t buf = sb & 1;
+            if (!tma::mbar_wait_blocking(full_d + buf, (sb >> 1) & 1, abort_flag, &g_tc_status, 16u)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            if (sb == 0) ginv = __ldg(p.ginv + col0 + tl);
+            const float *dval = reinterpret_cast<const float *>(tc_smem + TC6_DVAL_OFF + buf * (TC_BN * 4));
+#pragma unroll
+            for (uint32_t c2 = 0; c2 < 2; ++c2) {
+                const uint32_t col = ch * 64 + c2 * 32;
+                uint32_t v0[16], v1[16];
+                tmem_ld16(lane_addr + buf * TC_BN + col, v0);
+                tmem_ld16(lane_addr + buf * TC_BN + col + 16, v1);
+                tmem_wait_ld();
+                const float4 *dq = reinterpret_cast<const float4 *>(dval + col);
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4) {
+                    const float4 dv = dq[q4];
+                    const float dvv[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int j = q4 * 4 + i;
+                        const float dd = __uint_as_float(j < 16 ? v0[j & 15] : v1[j & 15]);
+                        acc[c2 * 32 + j] = fmaf(dvv[i] * dd, ginv, acc[c2 * 32 + j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tma::mbar_arrive(empty_d + buf);
+        }
+        if (ok && col0 + tl < p.n) {
+            float *o = p.out + (size_t)(row0 + ch * 64) * p.ldy + (size_t)(col0 + tl) * p.ldc;
+            if (p.ldy == 1 && row0 + ch * 64 + 64 <= p.m && ((uintptr_t)o & 15) == 0) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float4 v = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+                    float4 *o4 = reinterpret_cast<float4 *>(o) + i;
+                    if (p.epilogue == EPI_ADD) {
+                        const float4 c = *o4;
+                        v = make_float4(__fadd_rn(c.x, v.x), __fadd_rn(c.y, v.y), __fadd_rn(c.z, v.z), __fadd_rn(c.w, v.w));
+                    }
+                    *o4 = v;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 64; ++i)
+                    if (row0 + ch * 64 + i < p.m) {
+                        float *oi = o + (size_t)i * p.ldy;
+                        *oi = p.epilogue == EPI_ADD ? __fadd_rn(*oi, acc[i]) : acc[i];
+                    }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem, TC6_TMEM_COLS);
+    }
+}
+
+int32_t launch_tc6(const TcParams &p, cudaStream_t st) {
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        CERA_CUDA_TRY(cudaFuncSetAttribute(gemm_tc6_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC6_SMEM_BYTES));
+        configured_dev = dev;
+    }
+    const dim3 grid((p.n + TC_BM - 1) / TC_BM, (p.m + TC_BN - 1) / TC_BN);
+    count_launch();
+    return check_cuda(launch_k(gemm_tc6_kernel, grid, dim3(TC_THREADS_IMG), (size_t)TC6_SMEM_BYTES, st, p), "gemm (tcgen05, Q6_K) launch");
+}
+
 int32_t launch_tc_wide(const TcParams &p, cudaStream_t st) {
     static thread_local int configured_dev = -1;
     int dev = 0;
@@ -938,8 +1159,10 @@ int32_t weight_prepare_tc(cera_cuda_weight *w, bool *built) {
         return e && strcmp(e, "0") == 0;
     }();
     const WeightView &v = w->v;
-    if (off || v.k % 256 || v.ilv != 8 || (v.type != CERA_TYPE_Q4_K && v.type != CERA_TYPE_Q5_K)) return CERA_CUDA_OK;
-    const TcImage L = tc_image_layout(v.m, v.k);
+    if (off || v.k % 256 || v.ilv != 8 || (v.type != CERA_TYPE_Q4_K && v.type != CERA_TYPE_Q5_K && v.type != CERA_TYPE_Q6_K)) return CERA_CUDA_OK;
+    TcImage L = tc_image_layout(v.m, v.k);
+    const bool q6 = v.type == CERA_TYPE_Q6_K;
+    if (q6) L.total = (size_t)L.tiles * (v.k / TC6_KS) * (2 * TC6_HALF) + (size_t)L.tiles * L.n_sb * (TC_BN * 4);  // 4 bytes per weight + d
     int prev = 0;
     cudaGetDevice(&prev);
     if (prev != w->device) cudaSetDevice(w->device);
@@ -950,11 +1173,14 @@ int32_t weight_prepare_tc(cera_cuda_weight *w, bool *built) {
     if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess && free_b > L.total + (4ull << 30) && cudaMalloc(&img, L.total) == cudaSuccess) {
         const dim3 grid(L.n_it, L.tiles);
         uint8_t *b = (uint8_t *)img;
-        if (v.type == CERA_TYPE_Q4_K)
+        if (q6) {
+            tc_weight_image6_kernel<<<dim3(v.k / TC6_KS, L.tiles), TC_BN>>>(
+                v, b, reinterpret_cast<float *>(b + (size_t)L.tiles * (v.k / TC6_KS) * (2 * TC6_HALF)));
+        } else if (v.type == CERA_TYPE_Q4_K)
             tc_weight_image_kernel<CERA_TYPE_Q4_K><<<grid, TC_W_WARPS * 32>>>(v, b, b + L.side);
         else
             tc_weight_image_kernel<CERA_TYPE_Q5_K><<<grid, TC_W_WARPS * 32>>>(v, b, b + L.side);
-        tc_weight_min_kernel<<<L.tiles, TC_BN>>>(v, b + L.wmin, reinterpret_cast<float *>(b + L.rscale));  // (the header layout is the same for both types)
+        if (!q6) tc_weight_min_kernel<<<L.tiles, TC_BN>>>(v, b + L.wmin, reinterpret_cast<float *>(b + L.rscale));  // (the header layout is the same for both types)
         count_launch();
         count_launch();
         rc = check_cuda(cudaGetLastError(), "weight image launch");
@@ -989,7 +1215,10 @@ int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *o
         const char *e = getenv("CERA_CUDA_GEMM");
         return e && (strcmp(e, "mma") == 0 || strcmp(e, "columns") == 0);
     }();
-    if (off || n <= 32 || w.k % 256 || (w.type != CERA_TYPE_Q4_K && w.type != CERA_TYPE_Q5_K)) return CERA_CUDA_OK;
+    if (off || n <= 32 || w.k % 256 || (w.type != CERA_TYPE_Q4_K && w.type != CERA_TYPE_Q5_K && w.type != CERA_TYPE_Q6_K)) return CERA_CUDA_OK;
+    // Q6_K: only over its image, and only with at least two token tiles (a single tile of a long-k matrix leaves each of
+    // the few CTAs a serial walk that the warp-level kernel's split-k clusters beat: 189 against 111 us at 4096 x 14336 x 64)
+    if (w.type == CERA_TYPE_Q6_K && (!w.tc || n <= 128)) return CERA_CUDA_OK;
     if ((uintptr_t)x.quants % 16 || (uintptr_t)x.scales % 16 || (uintptr_t)x.sums % 16) return CERA_CUDA_OK;
     // the activation operands, converted once for all row tiles: a stream-ordered scratch allocation that lives for this
     // call (token tiles x stages x 32 KB, the min operand's token side, g and 1 / g)
@@ -998,7 +1227,10 @@ int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *o
     const size_t img_bytes = (size_t)tiles * n_it * (2 * TC_OP_BYTES), min_bytes = (size_t)tiles * n_sb * TC_MINOP_BYTES,
                  xm_bytes = (size_t)tiles * n_mit * (2 * TCW_MINT_BYTES);
     uint8_t *scratch = nullptr;
-    CERA_CUDA_TRY(cudaMallocAsync((void **)&scratch, img_bytes + min_bytes + xm_bytes + (size_t)n_pad * 8, st));
+    if (cudaMallocAsync((void **)&scratch, img_bytes + min_bytes + xm_bytes + (size_t)n_pad * 8, st) != cudaSuccess) {
+        cudaGetLastError();  // no room for the operand scratch: leave the GEMM to the kernels that need none
+        return CERA_CUDA_OK;
+    }
     uint8_t *xm = scratch + img_bytes + min_bytes;
     float *g_tab = reinterpret_cast<float *>(xm + xm_bytes), *ginv_tab = g_tab + n_pad;
     // the last min stage's columns beyond k / 32 are zero (never written by the image kernel)
@@ -1032,7 +1264,9 @@ int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *o
     }();
     const uint32_t wide_ctas = tiles * ((w.m + 2 * TC_BN - 1) / (2 * TC_BN));
     const bool wide = w.tc && (tile_pref == 256 || (tile_pref != 128 && wide_ctas >= 120));
-    if (rc == CERA_CUDA_OK && wide) {
+    if (rc == CERA_CUDA_OK && w.type == CERA_TYPE_Q6_K) {
+        rc = launch_tc6(p, st);
+    } else if (rc == CERA_CUDA_OK && wide) {
         rc = launch_tc_wide(p, st);
     } else if (rc == CERA_CUDA_OK) {
         if (w.tc)

@@ -215,7 +215,7 @@ int32_t cera_cuda_weight_info(const cera_cuda_weight *w, int32_t *type, size_t *
     if (type) *type = w->v.type;
     if (m) *m = w->v.m;
     if (k) *k = w->v.k;
-    if (device_bytes) *device_bytes = w->bytes;
+    if (device_bytes) *device_bytes = w->bytes + w->tc_bytes;
     return CERA_CUDA_OK;
 }
 

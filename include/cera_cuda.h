@@ -80,11 +80,12 @@ CERA_API int32_t cera_cuda_weight_create(int32_t ggml_type, size_t m, size_t k, 
 CERA_API void cera_cuda_weight_free(cera_cuda_weight *w);
 /* Optional, for weights that will see many-column GEMMs (cera_cuda_gemm_preq with more than 32 columns; the reference
  * reaches that path through quantized_matmul_preq, cera/src/model/transformer.rs:790-820): builds a device-resident f16
- * operand image of a Q4_K / Q5_K weight (k a multiple of 256) for the tensor-core kernel, about 2.2 extra bytes per
- * weight.  *has_image (optional) = 1 when the weight now holds one; 0 when the type or shape is not that kernel's, the
- * device has no room, or CERA_CUDA_TC_IMAGE=0 - the GEMM then converts the quantized bytes on the fly, same results.
- * A model (cera_cuda_model_*) prepares its own layer weights at its first batched prompt.  Not thread-safe against
- * concurrent calls on the same weight. */
+ * operand image of a K-quant weight (k a multiple of 256) for the tensor-core kernels: about 2.2 extra bytes per weight
+ * for Q4_K / Q5_K, 4 for Q6_K (whose products of scale and quant need two f16 operands).  *has_image (optional) = 1
+ * when the weight now holds one; 0 when the type or shape is not those kernels', the device has no room, or
+ * CERA_CUDA_TC_IMAGE=0 - Q4_K / Q5_K GEMMs then convert the quantized bytes on the fly and Q6_K runs the warp-level
+ * kernel, same results within the path's tolerance.  A model (cera_cuda_model_*) prepares its own layer weights at its
+ * first batched prompt.  Not thread-safe against concurrent calls on the same weight. */
 CERA_API int32_t cera_cuda_weight_prepare_gemm(cera_cuda_weight *w, int32_t *has_image);
 CERA_API int32_t cera_cuda_weight_info(const cera_cuda_weight *w, int32_t *ggml_type, size_t *m,
                                        size_t *k, size_t *device_bytes);

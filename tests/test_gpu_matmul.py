@@ -176,9 +176,10 @@ def test_gemm_tensor_core_shapes(t, m, n, k):
     got = cb.gemm_preq(w, acts, out).cpu().numpy()
     want = O.gemm_preq(t, raw, acts.scales.cpu().numpy(), acts.quants.cpu().numpy(), m, n, k, avx2=t != O.Q5_K, threads=4)
     assert_close(got, want, f"{O.NAMES[t]} {m}x{n}x{k}")
-    # the same through the resident f16 operand image of the tcgen05 kernel (Q4_K / Q5_K, k a multiple of 256)
+    # the same through the resident f16 operand image of the tcgen05 kernels (the K-quants, k a multiple of 256; Q6_K
+    # reaches the tensor-core kernel only through its image)
     has = w.prepare_gemm()
-    assert has == (t in (O.Q4_K, O.Q5_K) and k % 256 == 0)
+    assert has == (t in (O.Q4_K, O.Q5_K, O.Q6_K) and k % 256 == 0)
     if has:
         out2 = torch.full((m, n), float("nan"), device="cuda")
         assert_close(cb.gemm_preq(w, acts, out2).cpu().numpy(), want, f"{O.NAMES[t]} {m}x{n}x{k} (weight image)")
