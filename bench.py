@@ -460,7 +460,7 @@ def cuda_arm(args, rank, world):
     torch.cuda.synchronize()
     t_pre = time.perf_counter() - t_pre
     # ... then the prompt again through the decode kernels, one position at a time: that is the arithmetic of the CPU
-    # reference stream (per-token processing; a tensor-parallel model always prefills this way), so the KV cache the
+    # reference stream (per-token processing), so the KV cache the
     # timed decode starts from holds the reference's bits and the stream can be checked token for token
     model.truncate_kv(0)
     t_pt = time.perf_counter()

@@ -98,6 +98,7 @@ struct cera_cuda_model {
     uint32_t *pf_tokens = nullptr;
     float *pf_hidden = nullptr, *pf_q = nullptr, *pf_k = nullptr, *pf_v = nullptr, *pf_attn = nullptr, *pf_g = nullptr,
           *pf_u = nullptr;
+    float *pf_attn_local = nullptr;  // tensor parallel: this rank's heads [chunk][l_qd] before they are gathered into pf_attn
     ActBuf pf_act_hs, pf_act_q, pf_act_ff;
     float *pf_logits = nullptr;  // [PREFILL_CHUNK][vocab], allocated by the first logits-for-every-position call
     bool has_lora = false;
@@ -418,37 +419,69 @@ int32_t prefill_chunk(cera_cuda_model *m, const uint32_t *tokens, size_t n, size
                 if (built) m->mem_bytes += w->tc_bytes;
             }
     }
+    // Tensor parallel: every rank runs the chunk on its rows of q / k / v, gate / up and down (its heads, its slice of
+    // the SwiGLU product and of the residual), keeps the o-proj whole, and after each row-split product copies its column
+    // slice of the chunk-wide buffer into every peer's copy (strided device-to-device copies into the peers' exchange
+    // regions), then signals and waits on the layer's exchange slot as the decode step does (bounded waits, tp.cu).
+    const bool tp = m->tp_size > 1;
+    const uint32_t r = m->tp_rank;
+    const size_t l_qd = m->l_qd, l_kvd = m->l_kvd, l_ff = m->l_ff, l_hs = m->l_hs;
+    auto gather = [&](float *full, size_t cols, size_t l_cols, const float *src, size_t src_pitch_elems, uint32_t slot) -> int32_t {
+        // column slice [r * l_cols, +l_cols) of the [n x cols] buffer `full`: into this rank's copy (when it was formed
+        // elsewhere) and into every peer's
+        const size_t col_off = (size_t)r * l_cols;
+        if (src != full + col_off)
+            CERA_CUDA_TRY(cudaMemcpy2DAsync(full + col_off, cols * 4, src, src_pitch_elems * 4, l_cols * 4, n, cudaMemcpyDeviceToDevice, st));
+        const size_t off = (size_t)((char *)(full + col_off) - m->region);
+        for (uint32_t p = 0; p < m->tp_size; ++p)
+            if (p != r)
+                CERA_CUDA_TRY(cudaMemcpy2DAsync(m->tp.peer[p] + off, cols * 4, src, src_pitch_elems * 4, l_cols * 4, n, cudaMemcpyDeviceToDevice, st));
+        return launch_tp_exchange(m->tp, nullptr, 0, slot, st);
+    };
+    if (tp) CERA_TRY(launch_tp_tick(m->tp_words, st));
     CERA_CUDA_TRY(cudaMemcpyAsync(m->pf_tokens, tokens, n * 4, cudaMemcpyHostToDevice, st));
     CERA_TRY(launch_embed_batch(m->embd->v, m->pf_tokens, n, m->pf_hidden, st));
     if (c.embedding_scale != 0.0f && c.embedding_scale != 1.0f) CERA_TRY(launch_scale(m->pf_hidden, n * hs, c.embedding_scale, st));
     const uint64_t before = launches_so_far();
+    uint32_t li = 0;
     for (auto &L : m->layers) {
+        const uint32_t s0 = 4 * li++;
         CERA_TRY(launch_rmsnorm(m->pf_hidden, L.attn_norm, hs, n, c.rms_norm_eps, nullptr, m->pf_act_hs.scales,
                                 m->pf_act_hs.quants, m->pf_act_hs.sums, st));
-        CERA_TRY(launch_gemm_ex(L.wq->v, m->pf_act_hs.view(), n, m->pf_q, 1, qd, EPI_STORE, st));
-        CERA_TRY(launch_gemm_ex(L.wk->v, m->pf_act_hs.view(), n, m->pf_k, 1, kvd, EPI_STORE, st));
-        CERA_TRY(launch_gemm_ex(L.wv->v, m->pf_act_hs.view(), n, m->pf_v, 1, kvd, EPI_STORE, st));
-        CERA_TRY(launch_rope_batch(m->pf_q, m->pf_k, m->pf_v, start_pos, n, c.n_heads, c.n_kv_heads, c.head_dim,
+        CERA_TRY(launch_gemm_ex(L.wq->v, m->pf_act_hs.view(), n, m->pf_q, 1, l_qd, EPI_STORE, st));
+        CERA_TRY(launch_gemm_ex(L.wk->v, m->pf_act_hs.view(), n, m->pf_k, 1, l_kvd, EPI_STORE, st));
+        CERA_TRY(launch_gemm_ex(L.wv->v, m->pf_act_hs.view(), n, m->pf_v, 1, l_kvd, EPI_STORE, st));
+        CERA_TRY(launch_rope_batch(m->pf_q, m->pf_k, m->pf_v, start_pos, n, m->l_heads, m->l_kv_heads, c.head_dim,
                                    m->theta_scale, m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st, m->rope_table));
-        CERA_TRY(launch_prefill_attention(m->pf_q, L.kc, L.vc, c.kv_f16, c.n_heads, c.n_kv_heads, c.head_dim, n, start_pos,
-                                          scale, m->pf_attn, st));
+        CERA_TRY(launch_prefill_attention(m->pf_q, L.kc, L.vc, c.kv_f16, m->l_heads, m->l_kv_heads, c.head_dim, n, start_pos,
+                                          scale, m->pf_attn_local, st));
+        if (tp) CERA_TRY(gather(m->pf_attn, qd, l_qd, m->pf_attn_local, l_qd, s0));
         CERA_TRY(launch_quantize(m->pf_attn, qd, n, false, m->pf_act_q.scales, m->pf_act_q.quants, m->pf_act_q.sums, st));
         if (res_scale != 1.0f) {  // block output into pf_g (free until the gate projection), then hidden += out * s
             CERA_TRY(launch_gemm_ex(L.wo->v, m->pf_act_q.view(), n, m->pf_g, 1, hs, EPI_STORE, st));
             CERA_TRY(launch_scaled_add(m->pf_hidden, m->pf_g, n * hs, res_scale, st));
         } else {
-            CERA_TRY(launch_gemm_ex(L.wo->v, m->pf_act_q.view(), n, m->pf_hidden, 1, hs, EPI_ADD, st));
+            CERA_TRY(launch_gemm_ex(L.wo->v, m->pf_act_q.view(), n, m->pf_hidden, 1, hs, EPI_ADD, st));  // whole on every rank
         }
         CERA_TRY(launch_rmsnorm(m->pf_hidden, L.ffn_norm, hs, n, c.rms_norm_eps, nullptr, m->pf_act_hs.scales,
                                 m->pf_act_hs.quants, m->pf_act_hs.sums, st));
-        CERA_TRY(launch_gemm_ex(L.gate->v, m->pf_act_hs.view(), n, m->pf_g, 1, ff, EPI_STORE, st));
-        CERA_TRY(launch_gemm_ex(L.up->v, m->pf_act_hs.view(), n, m->pf_u, 1, ff, EPI_STORE, st));
+        CERA_TRY(launch_gemm_ex(L.gate->v, m->pf_act_hs.view(), n, m->pf_g + (size_t)r * l_ff, 1, ff, EPI_STORE, st));
+        CERA_TRY(launch_gemm_ex(L.up->v, m->pf_act_hs.view(), n, m->pf_u + (size_t)r * l_ff, 1, ff, EPI_STORE, st));
+        if (tp) {
+            // (two copies, one signal: the second gather carries the slot)
+            const size_t col_off = (size_t)r * l_ff, off = (size_t)((char *)(m->pf_g + col_off) - m->region);
+            for (uint32_t p = 0; p < m->tp_size; ++p)
+                if (p != r)
+                    CERA_CUDA_TRY(cudaMemcpy2DAsync(m->tp.peer[p] + off, ff * 4, m->pf_g + col_off, ff * 4, l_ff * 4, n, cudaMemcpyDeviceToDevice, st));
+            CERA_TRY(gather(m->pf_u, ff, l_ff, m->pf_u + col_off, ff, s0 + 2));
+        }
         CERA_TRY(launch_silu_mul(m->pf_g, m->pf_u, ff, n, m->pf_act_ff.scales, m->pf_act_ff.quants, m->pf_act_ff.sums, st));
         if (res_scale != 1.0f) {  // pf_u is free once the SwiGLU product is quantized
             CERA_TRY(launch_gemm_ex(L.down->v, m->pf_act_ff.view(), n, m->pf_u, 1, hs, EPI_STORE, st));
             CERA_TRY(launch_scaled_add(m->pf_hidden, m->pf_u, n * hs, res_scale, st));
         } else {
-            CERA_TRY(launch_gemm_ex(L.down->v, m->pf_act_ff.view(), n, m->pf_hidden, 1, hs, EPI_ADD, st));
+            CERA_TRY(launch_gemm_ex(L.down->v, m->pf_act_ff.view(), n, m->pf_hidden + (size_t)r * l_hs, 1, hs, EPI_ADD, st));
+            if (tp) CERA_TRY(gather(m->pf_hidden, hs, l_hs, m->pf_hidden + (size_t)r * l_hs, hs, s0 + 3));
         }
     }
     CERA_CUDA_TRY(cudaMemcpyAsync(m->hidden, m->pf_hidden + (n - 1) * hs, hs * 4, cudaMemcpyDeviceToDevice, st));
@@ -646,6 +679,11 @@ int32_t cera_cuda_model_finalize(cera_cuda_model *m) {
                      o_logits = take((size_t)c.vocab_size * 4), o_pairs = take(TP_MAX_RANKS * 8);
         m->tp_slots = 4 * c.n_layers + 2;
         const size_t o_flags = take((size_t)m->tp_slots * TP_MAX_RANKS * 4);
+        // tensor-parallel batched prompt: the chunk-wide buffers whose column slices the peers fill
+        const bool tp_pf = m->tp_size > 1;
+        const size_t C = PREFILL_CHUNK;
+        const size_t o_pf_hidden = tp_pf ? take(C * hs * 4) : 0, o_pf_attn = tp_pf ? take(C * qd * 4) : 0,
+                     o_pf_g = tp_pf ? take(C * ff * 4) : 0, o_pf_u = tp_pf ? take(C * ff * 4) : 0;
         m->region_bytes = (off + ((size_t)2 << 20) - 1) & ~(((size_t)2 << 20) - 1);  // an allocation of its own to export
         if (m->region_bytes > 0xFFFFFFFFull) return fail(CERA_CUDA_ERR_UNSUPPORTED, "finalize: exchange region of %zu bytes", m->region_bytes);
         CERA_TRY(dev_alloc(m, (void **)&m->region, m->region_bytes));
@@ -655,6 +693,12 @@ int32_t cera_cuda_model_finalize(cera_cuda_model *m) {
         m->act_q = ActBuf{(float *)(b + o_qs), (int8_t *)(b + o_qq), (int16_t *)(b + o_qsum)};
         m->act_ff = ActBuf{(float *)(b + o_fs), (int8_t *)(b + o_fq), (int16_t *)(b + o_fsum)};
         m->logits = (float *)(b + o_logits);
+        if (tp_pf) {
+            m->pf_hidden = (float *)(b + o_pf_hidden);
+            m->pf_attn = (float *)(b + o_pf_attn);
+            m->pf_g = (float *)(b + o_pf_g);
+            m->pf_u = (float *)(b + o_pf_u);
+        }
         CERA_TRY(dev_alloc(m, (void **)&m->tp_words, 64 * 4));
         CERA_CUDA_TRY(cudaMemset(m->tp_words, 0, 64 * 4));
         m->tp.rank = m->tp_rank;
@@ -683,16 +727,21 @@ int32_t cera_cuda_model_finalize(cera_cuda_model *m) {
     CERA_TRY(dev_alloc(m, (void **)&m->g, m->l_ff * 4));
     CERA_TRY(dev_alloc(m, (void **)&m->u, m->l_ff * 4));
     CERA_TRY(alloc_act(m, m->act_hs, hs));
-    if (m->tp_size == 1) {
+    {
         const size_t C = PREFILL_CHUNK;
         CERA_TRY(dev_alloc(m, (void **)&m->pf_tokens, C * 4));
-        CERA_TRY(dev_alloc(m, (void **)&m->pf_hidden, C * hs * 4));
-        CERA_TRY(dev_alloc(m, (void **)&m->pf_q, C * qd * 4));
-        CERA_TRY(dev_alloc(m, (void **)&m->pf_k, C * kvd * 4));
-        CERA_TRY(dev_alloc(m, (void **)&m->pf_v, C * kvd * 4));
-        CERA_TRY(dev_alloc(m, (void **)&m->pf_attn, C * qd * 4));
-        CERA_TRY(dev_alloc(m, (void **)&m->pf_g, C * ff * 4));
-        CERA_TRY(dev_alloc(m, (void **)&m->pf_u, C * ff * 4));
+        CERA_TRY(dev_alloc(m, (void **)&m->pf_q, C * m->l_qd * 4));
+        CERA_TRY(dev_alloc(m, (void **)&m->pf_k, C * m->l_kvd * 4));
+        CERA_TRY(dev_alloc(m, (void **)&m->pf_v, C * m->l_kvd * 4));
+        if (m->tp_size == 1) {
+            CERA_TRY(dev_alloc(m, (void **)&m->pf_hidden, C * hs * 4));
+            CERA_TRY(dev_alloc(m, (void **)&m->pf_attn, C * qd * 4));
+            CERA_TRY(dev_alloc(m, (void **)&m->pf_g, C * ff * 4));
+            CERA_TRY(dev_alloc(m, (void **)&m->pf_u, C * ff * 4));
+            m->pf_attn_local = m->pf_attn;
+        } else {
+            CERA_TRY(dev_alloc(m, (void **)&m->pf_attn_local, C * m->l_qd * 4));  // (the chunk-wide ones sit in the exchange region)
+        }
         CERA_TRY(alloc_act(m, m->pf_act_hs, C * hs));
         CERA_TRY(alloc_act(m, m->pf_act_q, C * qd));
         CERA_TRY(alloc_act(m, m->pf_act_ff, C * ff));
@@ -773,7 +822,22 @@ int32_t cera_cuda_forward_prefill(cera_cuda_model *m, const uint32_t *tokens, si
         return e && strcmp(e, "per_token") == 0;
     }();
     if (m->tp_size > 1 && !m->tp_connected) return fail(CERA_CUDA_ERR_STATE, "forward_prefill: tensor-parallel model is not connected to its peers");
-    if (per_token || n < 2 || m->tp_size > 1 || m->has_lora) {
+    // a tensor-parallel model takes the batched kernels for prompts of at least 64 tokens: all but the last token in
+    // chunks, the last one through the decode step (which carries the logits exchange)
+    const bool tp_batched = m->tp_size > 1 && !per_token && !m->has_lora && n >= 65;
+    if (tp_batched) {
+        const size_t nb = n - 1;
+        for (size_t done = 0; done < nb; done += PREFILL_CHUNK) {
+            const size_t cn = nb - done < PREFILL_CHUNK ? nb - done : PREFILL_CHUNK;
+            CERA_TRY(prefill_chunk(m, tokens + done, cn, start_pos + done));
+            CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+            CERA_TRY(tp_check(m));
+        }
+        m->seq_len = start_pos + nb;
+        CERA_TRY(run_token(m, tokens[nb], start_pos + nb, logits_out ? G_LOGITS : G_BODY));
+        CERA_CUDA_TRY(cudaStreamSynchronize(m->stream));
+        CERA_TRY(tp_check(m));
+    } else if (per_token || n < 2 || m->tp_size > 1 || m->has_lora) {
         // Decode arithmetic for every prompt position (one graph launch per token).  h_dyn is rewritten per
         // token, so wait for the copy of the previous one before touching it again.
         for (size_t i = 0; i < n; ++i) {

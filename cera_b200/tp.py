@@ -7,9 +7,10 @@ ranks, so a tensor-parallel model reproduces the single-GPU logits.  The device 
 exchange is csrc/tp.cu."""
 from .model import Role
 
-#: roles whose rows are split; everything else (norm vectors, embedding table, rope factors) is replicated
-SPLIT_ROLES = (Role.ATTN_Q, Role.ATTN_K, Role.ATTN_V, Role.ATTN_OUTPUT, Role.FFN_GATE, Role.FFN_UP, Role.FFN_DOWN,
-               Role.OUTPUT)
+#: roles whose rows are split; everything else is replicated: norm vectors, embedding table, rope factors, and the
+#: o-proj (its launch is latency-bound whole or split, and a rank that holds all of its rows needs no exchange of the
+#: residual stream after it)
+SPLIT_ROLES = (Role.ATTN_Q, Role.ATTN_K, Role.ATTN_V, Role.FFN_GATE, Role.FFN_UP, Role.FFN_DOWN, Role.OUTPUT)
 
 
 def check_divisible(cfg, size):
@@ -35,8 +36,8 @@ def row_range(role, rows, rank, size):
 
 
 def exchange_slots(n_layers):
-    """Exchanges of one decode step: attention output, residual, SwiGLU activations, residual per
-    layer, then the logits slice or the greedy pair."""
+    """Exchange slots of one decode step: four per layer (attention output, one unused since the o-proj is whole on
+    every rank, SwiGLU activations, residual after the down-proj), then the logits slice or the greedy pair."""
     return 4 * n_layers + 1
 
 

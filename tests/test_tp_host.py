@@ -31,7 +31,7 @@ def test_llama3_8b_splits_over_1_2_4_8():
 
 
 def test_row_ranges_partition_every_split_tensor():
-    rows = {Role.ATTN_Q: 4096, Role.ATTN_K: 1024, Role.ATTN_V: 1024, Role.ATTN_OUTPUT: 4096, Role.FFN_GATE: 14336,
+    rows = {Role.ATTN_Q: 4096, Role.ATTN_K: 1024, Role.ATTN_V: 1024, Role.FFN_GATE: 14336,
             Role.FFN_UP: 14336, Role.FFN_DOWN: 4096, Role.OUTPUT: 128256}
     for size in (1, 2, 4, 8):
         for role, m in rows.items():
@@ -43,6 +43,7 @@ def test_row_ranges_partition_every_split_tensor():
             == 1024 // size  # whole heads of 128 rows at every size
     assert tp.row_range(Role.TOKEN_EMBD, 128256, 3, 8) == (0, 128256)
     assert tp.row_range(Role.ATTN_NORM, 1, 1, 2) == (0, 1)
+    assert tp.row_range(Role.ATTN_OUTPUT, 4096, 1, 2) == (0, 4096)  # the o-proj is whole on every rank
     with pytest.raises(ValueError):
         tp.row_range(Role.FFN_GATE, 100, 0, 8)
     assert tp.exchange_slots(32) == 129

@@ -33,6 +33,12 @@ def main():
             first = int(np.argmax(last))
             steps = [m.forward_greedy(first, 12)]
             stream, ms = m.generate_greedy(steps[0], 13, 40)
+            # a prompt long enough for the batched tensor-parallel path (row-split GEMMs, column slices gathered into
+            # the peers' chunk buffers), continuing from position 53
+            long_prompt = synth.prompt_tokens(80, cfg["vocab_size"], seed=9)
+            m.truncate_kv(0)
+            batched = m.forward_prefill(long_prompt, 0)
+            after = m.forward(int(np.argmax(batched)), 80)
             m.close()
             dist.barrier()
             if rank == 0:
@@ -43,11 +49,24 @@ def main():
                     last_1 = s.forward(int(t), 4 + i)
                 steps_1 = [s.forward_greedy(int(np.argmax(last_1)), 12)]
                 stream_1, _ = s.generate_greedy(steps_1[0], 13, 40)
+                s.truncate_kv(0)
+                for i, t in enumerate(long_prompt):
+                    per_token = s.forward(int(t), i)
+                after_1 = s.forward(int(np.argmax(batched)), 80)
                 s.close()
+
+                def cosine(a, b):
+                    return float(np.dot(a, b) / (np.linalg.norm(a) * np.linalg.norm(b)))
+
+                # batched against per-token arithmetic: the reference's batched-prompt test holds tiled-attention paths to a
+                # cosine floor of 0.99 (cera/tests/llama_batched_prefill_parity.rs); measured here 0.9999 (f16 KV 0.99989)
+                cos_b, cos_a = cosine(batched, per_token), cosine(after, after_1)
                 diff = max(float(np.abs(a - b).max()) for a, b in zip(logits + [last], logits_1 + [last_1]))
                 scale = max(float(np.abs(b).max()) for b in logits_1)
-                case_ok = (diff <= 1e-3 * scale and steps == steps_1 and list(stream) == list(stream_1))
+                case_ok = (diff <= 1e-3 * scale and steps == steps_1 and list(stream) == list(stream_1) and cos_b >= 0.999 and
+                           cos_a >= 0.999)
                 report["cases"].append({"model": name, "kv_f16": kv_f16, "max_logit_diff": diff, "logit_scale": scale,
+                                        "batched_prompt_cosine": cos_b, "decode_after_batched_prompt_cosine": cos_a,
                                         "bit_identical": diff == 0.0, "stream_equal": list(stream) == list(stream_1),
                                         "ms_per_step": ms / 40})
                 ok = ok and case_ok
