@@ -1,5 +1,5 @@
-// Prefill GEMM on the fifth-generation tensor cores: out[m x n] = W (Q4_K / Q5_K) x X (Q8_0 columns) with
-// tcgen05.mma, accumulators in tensor memory (TMEM), for n >= 33 columns and k a multiple of 256.
+// Prefill GEMM on the fifth-generation tensor cores: out[m x n] = W (Q4_K / Q5_K / Q6_K) x X (Q8_0 columns) with
+// tcgen05.mma, accumulators in tensor memory (TMEM), for n >= 33 columns (Q6_K: n >= 129) and k a multiple of 256.
 //
 // The arithmetic contract (cera/src/backend/simd.rs:5248-5371, 5693-5878) scales every 32-element block's integer sum
 // by (weight block scale) x (activation block scale).  A kernel that rescales each block's sum on the CUDA cores is
@@ -22,16 +22,28 @@
 // bit-exact block sums are the decode path's and cera_cuda_block_sums' business.
 //
 // The activation operands are converted ONCE per GEMM by two small kernels (a per-token range search for g, then the
-// high / low operand tiles written to a stream-ordered scratch buffer in the shared-memory layout of the GEMM kernel,
-// so that a stage's 32 KB arrive by one bulk asynchronous copy); the weight operand is built in shared memory by
-// producer warps straight from the quantized bytes (nibble -> 0x6400|q -> one HFMA2 with the sub-block scale).  Tiles use
-// the canonical K-major no-swizzle layout (8-row x 16-byte core matrices), four stages of 64 k-elements.  Warp roles
-// in a CTA of 18 warps (one 128-token x 128-row tile): warp 0 allocates TMEM and issues the MMAs from one thread; warps
-// 1-8 build the weight operand (thread = weight row x half of the stage's bytes); one thread of warp 9 requests the
-// activation operands; warps 10-17 are the epilogue (thread = token lane x 64 rows).  Stages and the two D buffers are
-// handed over through mbarriers (tcgen05.commit arrives on them when the MMAs have finished).  Every wait is bounded:
-// when a limit runs out the CTA raises an abort flag, its roles leave their loops, TMEM is freed and a status word
-// reports it (cera_cuda_kernel_status).
+// high / low operand tiles written to a stream-ordered scratch buffer in the shared-memory layout of the GEMM kernels,
+// so that a stage's 32 KB arrive by one bulk asynchronous copy).  The weight operand comes from a RESIDENT IMAGE of the
+// weight (weight_prepare_tc: sc * q as f16 in the same tile layout, about 2.2 bytes per weight, built when a model sees
+// its first batched prompt or a caller asks for it), so a stage is a few bulk copies and 8-16 MMAs; a weight without an
+// image has its operand built in shared memory by producer warps straight from the quantized bytes (nibble -> 0x6400|q
+// -> one HFMA2 with the sub-block scale), same results.  Tiles use the canonical K-major no-swizzle layout (8-row x
+// 16-byte core matrices), 64 k-elements per stage.
+//
+// Three kernels:
+//  * gemm_tcw_kernel ("wide", image only): 128 tokens x 256 rows per CTA when those tiles alone fill the device.  TMEM
+//    holds two double-buffered 256-column accumulators; the running output lives in the epilogue threads' registers;
+//    the min term is one more GEMM over the k / 32 blocks after the k loop.
+//  * gemm_tc_kernel<T, IMG>: 128 x 128 per CTA.  IMG: the loader thread fetches all three operands, the min term is the
+//    16-column MMA above into its own double-buffered accumulator, output in registers.  !IMG: 18 warps - warp 0
+//    issues the MMAs from one thread, warps 1-8 build the weight operand (thread = weight row x half of the stage's
+//    bytes), one thread of warp 9 requests the activation operands, warps 10-17 are the epilogue (thread = token lane x
+//    64 rows) with the running output in a fourth TMEM region.
+//  * gemm_tc6_kernel (Q6_K, image only): sc * (q - 32) needs 13 bits, so the image holds it as two exact f16 operands
+//    and a k-step is three MMAs; no min term.
+// Stages and accumulator buffers are handed over through mbarriers (tcgen05.commit arrives on them when the MMAs have
+// finished).  Every wait is bounded: when a limit runs out the CTA raises an abort flag, its roles leave their loops,
+// TMEM is freed and a status word reports it (cera_cuda_kernel_status).
 #include <cuda_fp16.h>
 
 #include <cstdlib>

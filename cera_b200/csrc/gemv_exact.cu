@@ -28,7 +28,15 @@
 // own, with no CTA-wide barrier after the activation column has been staged.  The first segments are
 // requested before the kernel waits for its predecessor (weights never change), and the ring keeps
 // several segments per warp in flight across the warp's groups.  A launch puts one CTA on every SM
-// with as many warps as the SM's share of the row groups (up to sixteen).
+// with as many warps as the SM's share of the row groups (up to 32).
+//
+// Teams.  A matrix with few rows leaves an SM three or four groups, each a long serial walk over k
+// for one warp.  There the launch forms TEAMS of W = 2 .. 16 warps per group: the team's warps take
+// the group's segments round-robin, each forms the exact float sums of its segment on its own (that
+// work does not depend on the chain state), then receives the group's chain state - eight
+// accumulators and the macc sum per lane - from the warp that held the previous segment through a
+// shared-memory mailbox, runs the segment's FMAs and macc adds (the same operations in the same
+// order as a lone warp) and hands the state on; the warp with the last segment reduces and stores.
 //
 // Arithmetic.  Per segment, a SCALE PASS (one lane per (task, row)) forms the f32 block scales
 // xs*(d*sc) and the macc terms exactly as the reference forms them.  Then, per 4 weights: one mask,
