@@ -57,14 +57,15 @@ def main():
             ok = ok and same and stable
         moe.close()
         dist.barrier()
-    # More tokens than the layer was created for (every rank passes its full max_tokens while max_total_tokens
-    # allows half of that in total): the plan must notice before anything is stored into a peer's receive
-    # buffer, every rank must report the named error, and the layer must not hang.
+    # More tokens than the layer was created for: every rank passes its full max_tokens while max_total_tokens is
+    # the smallest value the constructor takes, so a rank's receive buffer holds exactly the average share and
+    # the seeded routing's imbalance overflows at least one of them.  The plan must notice before anything is stored
+    # into a peer's receive buffer, every rank must report the named error, and the layer must not hang.
     t, E, used, hs, ff = cb.Q4_0, 8, 2, 256, 128
     q = lambda n, seed: cb.quantize_weights(t, cb.synth_normal(n, seed=seed, sigma=0.02))
     per = 16
     moe = cb.MoeFfn(E, used, hs, ff, t, q(E * ff * hs, 1), q(E * ff * hs, 2), q(E * hs * ff, 3), cb.synth_normal(E * hs, seed=4, sigma=0.05),
-                    max_tokens=per, ep=(rank, world), max_total_tokens=per * world // 2)
+                    max_tokens=per, ep=(rank, world), max_total_tokens=per)
     tp.connect(moe)
     moe(cb.synth_normal(per * hs, seed=50 + rank, sigma=1.0).view(per, hs))
     torch.cuda.synchronize()
