@@ -98,7 +98,7 @@ struct cera_cuda_model {
     uint32_t *pf_tokens = nullptr;
     float *pf_hidden = nullptr, *pf_q = nullptr, *pf_k = nullptr, *pf_v = nullptr, *pf_attn = nullptr, *pf_g = nullptr,
           *pf_u = nullptr;
-    float *pf_attn_local = nullptr;  // tensor parallel: this rank's heads [chunk][l_qd] before they are gathered into pf_attn
+    float *pf_attn_local = nullptr;  // = pf_attn (every rank computes all heads)
     ActBuf pf_act_hs, pf_act_q, pf_act_ff;
     float *pf_logits = nullptr;  // [PREFILL_CHUNK][vocab], allocated by the first logits-for-every-position call
     bool has_lora = false;
@@ -158,7 +158,7 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
     const bool tp = m->tp_size > 1;
     const float scale = c.attention_scale != 0.0f ? c.attention_scale : 1.0f / sqrtf((float)c.head_dim);
     const float res_scale = c.residual_scale != 0.0f ? c.residual_scale : 1.0f;  // Granite: block outputs are scaled before the residual add
-    // Exchange slots of layer l: 4l = Q8_0 attention output, 4l+1 = (unused), 4l+2 = Q8_0 SwiGLU
+    // Exchange slots of layer l: 4l, 4l+1 = (unused), 4l+2 = Q8_0 SwiGLU
     // activations, 4l+3 = residual after down-proj; then 4L = logits, 4L+1 = greedy pairs.  The producing kernel
     // mirrors its stores into the peers' regions; the consuming kernel signals and waits in its prologue.
     const uint32_t n_layers = (uint32_t)m->layers.size();
@@ -190,8 +190,9 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
     for (uint32_t li = 0; li < n_layers; ++li) {
         Layer &L = m->layers[li];
         const uint32_t s0 = 4 * li;
-        // (slot s0 + 1 is unused: every rank holds the whole o-proj, so the residual after it needs no exchange)
-        const TpHook h_norm1 = hook(li ? s0 - 1 : TP_NO_SLOT, false), h_merge = hook(TP_NO_SLOT, true), h_wo = hook(s0, false),
+        // (slots s0 and s0 + 1 are unused: every rank holds the whole attention block, so neither the attention output
+        // nor the residual after the o-proj needs an exchange)
+        const TpHook h_norm1 = hook(li ? s0 - 1 : TP_NO_SLOT, false), h_merge = hook(TP_NO_SLOT, false), h_wo = hook(TP_NO_SLOT, false),
                      h_norm2 = hook(TP_NO_SLOT, false), h_silu = hook(TP_NO_SLOT, true), h_down = hook(s0 + 2, true);
         // LoRA deltas read the f32 input of the projection they adapt (cera/src/model/transformer.rs:1383-1387,
         // 1519-1528, 1588-1605, 1642-1651): the normed hidden, the attention output, the SwiGLU product
@@ -253,7 +254,7 @@ int32_t enqueue_step(cera_cuda_model *m, int kind, uint32_t n_splits) {
         if (!fused_qkv)
             CERA_TRY(launch_rope(m->q, m->k, m->v, 0, m->dyn + 1, m->l_heads, m->l_kv_heads, c.head_dim, m->theta_scale,
                                  m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st, m->rope_table));
-        const ActBuf aq = act_slice(m->act_q, m->l_qd);
+        const ActBuf aq = m->act_q;  // all heads on every rank
         CERA_TRY(launch_decode_attention_ex(m->q, L.kc, L.vc, c.kv_f16, m->l_heads, m->l_kv_heads, c.head_dim, 0,
                                             m->dyn + 2, n_splits, scale, m->attn, m->attn_ws, m->attn_ws_bytes,
                                             aq.scales, aq.quants, aq.sums, st, &h_merge));
@@ -419,8 +420,8 @@ int32_t prefill_chunk(cera_cuda_model *m, const uint32_t *tokens, size_t n, size
                 if (built) m->mem_bytes += w->tc_bytes;
             }
     }
-    // Tensor parallel: every rank runs the chunk on its rows of q / k / v, gate / up and down (its heads, its slice of
-    // the SwiGLU product and of the residual), keeps the o-proj whole, and after each row-split product copies its column
+    // Tensor parallel: every rank runs the whole attention block and its rows of gate / up and down (its slice of the
+    // SwiGLU product and of the residual), and after each row-split product copies its column
     // slice of the chunk-wide buffer into every peer's copy (strided device-to-device copies into the peers' exchange
     // regions), then signals and waits on the layer's exchange slot as the decode step does (bounded waits, tp.cu).
     const bool tp = m->tp_size > 1;
@@ -455,7 +456,6 @@ int32_t prefill_chunk(cera_cuda_model *m, const uint32_t *tokens, size_t n, size
                                    m->theta_scale, m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st, m->rope_table));
         CERA_TRY(launch_prefill_attention(m->pf_q, L.kc, L.vc, c.kv_f16, m->l_heads, m->l_kv_heads, c.head_dim, n, start_pos,
                                           scale, m->pf_attn_local, st));
-        if (tp) CERA_TRY(gather(m->pf_attn, qd, l_qd, m->pf_attn_local, l_qd, s0));
         CERA_TRY(launch_quantize(m->pf_attn, qd, n, false, m->pf_act_q.scales, m->pf_act_q.quants, m->pf_act_q.sums, st));
         if (res_scale != 1.0f) {  // block output into pf_g (free until the gate projection), then hidden += out * s
             CERA_TRY(launch_gemm_ex(L.wo->v, m->pf_act_q.view(), n, m->pf_g, 1, hs, EPI_STORE, st));
@@ -508,8 +508,11 @@ int32_t logits_from_hidden(cera_cuda_model *m) {
 void set_extents(cera_cuda_model *m) {
     const auto &c = m->cfg;
     const uint32_t G = m->tp_size;
-    m->l_heads = c.n_heads / G;
-    m->l_kv_heads = c.n_kv_heads / G;
+    // the attention block (q / k / v, the KV cache, attention, o-proj) is whole on every rank: its launches are
+    // latency-bound whole or split, and a rank that holds all heads needs no exchange around the attention - only the
+    // feed-forward matrices (four fifths of a layer's bytes) and the LM head are split by rows
+    m->l_heads = c.n_heads;
+    m->l_kv_heads = c.n_kv_heads;
     m->l_qd = (size_t)m->l_heads * c.head_dim;
     m->l_kvd = (size_t)m->l_kv_heads * c.head_dim;
     m->l_ff = c.intermediate_size / G;
@@ -633,12 +636,10 @@ int32_t cera_cuda_model_add_tensor(cera_cuda_model *m, int32_t role, int32_t lay
         case CERA_ROLE_ROPE_FREQS: return f32_vector(&m->rope_freqs, c.head_dim / 2);
         case CERA_ROLE_ATTN_NORM: return f32_vector(&L->attn_norm, c.hidden_size);
         case CERA_ROLE_FFN_NORM: return f32_vector(&L->ffn_norm, c.hidden_size);
-        case CERA_ROLE_ATTN_Q: return matrix(&L->wq, qd, c.hidden_size);
-        case CERA_ROLE_ATTN_K: return matrix(&L->wk, kvd, c.hidden_size);
-        case CERA_ROLE_ATTN_V: return matrix(&L->wv, kvd, c.hidden_size);
-        // the o-proj is kept whole on every rank of a tensor-parallel model: its launch is latency-bound either way
-        // (4096 x 4096: 6 us whole or halved), and a rank that computes all of its rows needs no exchange of the
-        // residual stream after it - one NVLink round trip less per layer
+        case CERA_ROLE_ATTN_Q: return matrix(&L->wq, qd, c.hidden_size, false);
+        case CERA_ROLE_ATTN_K: return matrix(&L->wk, kvd, c.hidden_size, false);
+        case CERA_ROLE_ATTN_V: return matrix(&L->wv, kvd, c.hidden_size, false);
+        // q / k / v and the o-proj are kept whole on every rank of a tensor-parallel model (see set_extents)
         case CERA_ROLE_ATTN_OUTPUT: return matrix(&L->wo, c.hidden_size, qd, false);
         case CERA_ROLE_FFN_GATE: return matrix(&L->gate, c.intermediate_size, c.hidden_size);
         case CERA_ROLE_FFN_UP: return matrix(&L->up, c.intermediate_size, c.hidden_size);
@@ -740,7 +741,7 @@ int32_t cera_cuda_model_finalize(cera_cuda_model *m) {
             CERA_TRY(dev_alloc(m, (void **)&m->pf_u, C * ff * 4));
             m->pf_attn_local = m->pf_attn;
         } else {
-            CERA_TRY(dev_alloc(m, (void **)&m->pf_attn_local, C * m->l_qd * 4));  // (the chunk-wide ones sit in the exchange region)
+            m->pf_attn_local = m->pf_attn;  // (the chunk-wide buffers sit in the exchange region)
         }
         CERA_TRY(alloc_act(m, m->pf_act_hs, C * hs));
         CERA_TRY(alloc_act(m, m->pf_act_q, C * qd));

@@ -1,16 +1,16 @@
 """Tensor-parallel plumbing above the C ABI: which rows of which tensor a rank keeps, and the
 exchange of the ranks' region handles through torch.distributed (one process per GPU).
 
-The split is by output rows of every matrix, the one axis cera parallelises on the CPU
+The split is by output rows of the feed-forward matrices and the LM head, the one axis cera parallelises on the CPU
 (cera/src/backend/cpu.rs:380-391): a row's dot product is the same arithmetic on any number of
 ranks, so a tensor-parallel model reproduces the single-GPU logits.  The device side of the
 exchange is csrc/tp.cu."""
 from .model import Role
 
-#: roles whose rows are split; everything else is replicated: norm vectors, embedding table, rope factors, and the
-#: o-proj (its launch is latency-bound whole or split, and a rank that holds all of its rows needs no exchange of the
-#: residual stream after it)
-SPLIT_ROLES = (Role.ATTN_Q, Role.ATTN_K, Role.ATTN_V, Role.FFN_GATE, Role.FFN_UP, Role.FFN_DOWN, Role.OUTPUT)
+#: roles whose rows are split: the feed-forward matrices (four fifths of a layer's bytes) and the LM head.  Everything else
+#: is replicated - norm vectors, embedding table, rope factors, and the whole attention block (q / k / v, KV cache, o-proj):
+#: its launches are latency-bound whole or split, and a rank that holds all heads needs no exchange around the attention
+SPLIT_ROLES = (Role.FFN_GATE, Role.FFN_UP, Role.FFN_DOWN, Role.OUTPUT)
 
 
 def check_divisible(cfg, size):
@@ -36,8 +36,8 @@ def row_range(role, rows, rank, size):
 
 
 def exchange_slots(n_layers):
-    """Exchange slots of one decode step: four per layer (attention output, one unused since the o-proj is whole on
-    every rank, SwiGLU activations, residual after the down-proj), then the logits slice or the greedy pair."""
+    """Exchange slots of one decode step: four per layer (two unused since the attention block is whole on every rank,
+    SwiGLU activations, residual after the down-proj), then the logits slice or the greedy pair."""
     return 4 * n_layers + 1
 
 
