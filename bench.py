@@ -28,9 +28,9 @@ token ids.  One JSON line goes to stdout.
 
 With --impl reference only that CPU implementation is timed.  With N > 1
 (launched by torchrun, one rank per GPU) the ranks decode ONE sequence together:
-every matrix is split by output rows over the N GPUs (whole heads for q/k/v, so
-each head's KV cache lives on one GPU) and the ranks push their slices of the
-gathered vectors into each other's memory over NVLink inside the decode step.
+the feed-forward matrices and the LM head are split by output rows over the N GPUs
+(the attention block stays whole on every rank) and the ranks push their slices of
+the gathered vectors into each other's memory over NVLink inside the decode step.
 Total work is fixed as N grows ("scaling": "strong"); the token stream is the
 single-GPU one by construction.
 """
@@ -212,7 +212,7 @@ DTYPE = "int8 x int8 -> int32 dot, f32 scales and accumulation"
 def bench_config(prompt_len, world, stream_head):
     """The `config` object both arms print: same keys, same workload string."""
     return {"workload": WORKLOAD, "prompt_len": prompt_len, "kv_dtype": "f32",
-            "parallelism": (f"tensor-parallel x{world}: rows of every matrix split over the GPUs, slices pushed into peer memory "
+            "parallelism": (f"tensor-parallel x{world}: rows of the feed-forward matrices and the LM head split over the GPUs, slices pushed into peer memory "
                             "over NVLink inside the step") if world > 1 else "1 GPU",
             "stream_head": stream_head,
             "l2": "each token streams 4.84 GB of weights (>> 126 MB L2); the kernel microbench rotates distinct weight copies (528 MB)"}

@@ -262,13 +262,16 @@ enum {
 };
 
 CERA_API int32_t cera_cuda_model_create(const cera_cuda_config *cfg, cera_cuda_model **out);
-/* Tensor parallelism over the output rows of every matrix, the axis the reference itself
- * parallelises (cera/src/backend/cpu.rs:380-391, RowPool): this model becomes rank `rank` of
- * `size` (<= 8) cooperating models, one process and one GPU each.  Call before the first
- * add_tensor; add_tensor still receives every tensor in full (each rank's loader has the same
- * mmap, cera/src/model/gpu_weight_source.rs:40-118) and keeps rows [rank*m/size, (rank+1)*m/size).
- * Needs n_kv_heads, hidden_size, vocab_size divisible by size and intermediate_size by 32*size.
- * Per-row arithmetic is unchanged, so logits and greedy streams do not depend on size. */
+/* Tensor parallelism over output rows, the axis the reference itself parallelises
+ * (cera/src/backend/cpu.rs:380-391, RowPool): this model becomes rank `rank` of `size` (<= 8)
+ * cooperating models, one process and one GPU each.  Call before the first add_tensor; add_tensor
+ * still receives every tensor in full (each rank's loader has the same mmap,
+ * cera/src/model/gpu_weight_source.rs:40-118).  The feed-forward matrices (gate, up, down) and the
+ * LM head keep rows [rank*m/size, (rank+1)*m/size); the attention block (q / k / v, KV cache,
+ * o-proj) stays whole on every rank, since splitting its latency-bound launches costs more in
+ * exchanges than it saves.  Needs n_kv_heads, hidden_size, vocab_size divisible by size and
+ * intermediate_size by 32*size.  Per-row arithmetic is unchanged, so logits and greedy streams do
+ * not depend on size. */
 CERA_API int32_t cera_cuda_model_set_tp(cera_cuda_model *m, uint32_t rank, uint32_t size);
 /* GpuWeightSource::weight_bytes (cera/src/model/gpu_weight_source.rs:40-118):
  * bytes are borrowed for the call only (host or device memory). */
