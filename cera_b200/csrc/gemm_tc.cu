@@ -124,7 +124,33 @@ struct TcParams {
     const uint8_t *img, *img_min;
     const float *ginv;
     const uint8_t *xm;  // per (token tile, min stage) the high and the low part of g * xs_b * A_b (the wide variant's min GEMM)
+    // Up to two more weights that take the same activations (q / k / v, gate / up), with images, in the same launch: the
+    // grid's y tiles [y_end[i - 1], y_end[i]) belong to weight i (0 = the fields above).
+    uint32_t n_w;
+    uint32_t y_end[3];
+    const uint8_t *tc_x[2];
+    float *out_x[2];
+    uint32_t m_x[2], ldc_x[2];
 };
+
+// The weight a CTA works for and its y tile inside that weight.
+struct TcSub {
+    const uint8_t *tc;
+    float *out;
+    uint32_t m, ldc, by;
+};
+__device__ __forceinline__ TcSub tc_select(const TcParams &p) {
+    TcSub s{p.w.tc, p.out, p.m, p.ldc, blockIdx.y};
+    if (p.n_w > 1 && blockIdx.y >= p.y_end[0]) {
+        const int i = (p.n_w > 2 && blockIdx.y >= p.y_end[1]) ? 1 : 0;
+        s.tc = p.tc_x[i];
+        s.out = p.out_x[i];
+        s.m = p.m_x[i];
+        s.ldc = p.ldc_x[i];
+        s.by = blockIdx.y - p.y_end[i];
+    }
+    return s;
+}
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_dst, uint32_t cols) {
@@ -425,8 +451,9 @@ __global__ void __launch_bounds__(TCW_THREADS, 1) gemm_tcw_kernel(const TcParams
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TCW_STAGES + 4);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t col0 = blockIdx.x * TC_BM, row0 = blockIdx.y * 2 * TC_BN;
-    const TcImage L = tc_image_layout(p.m, p.k);
+    const TcSub sub = tc_select(p);
+    const uint32_t col0 = blockIdx.x * TC_BM, row0 = sub.by * 2 * TC_BN;
+    const TcImage L = tc_image_layout(sub.m, p.k);
     const uint32_t n_sb = L.n_sb, n_it = L.n_it, n_mit = L.n_mit;
     if (tid == 0) {
         for (int s = 0; s < TCW_STAGES; ++s) {
@@ -508,11 +535,11 @@ __global__ void __launch_bounds__(TCW_THREADS, 1) gemm_tcw_kernel(const TcParams
     } else if (warp == 1) {
         // ---------------------------------------------------------------- operands: one thread asks for them (bulk asynchronous copies)
         if (lane == 0) {
-            const uint32_t t0 = min(2 * blockIdx.y, L.tiles - 1), t1 = min(2 * blockIdx.y + 1, L.tiles - 1);  // (an odd last tile is read twice)
+            const uint32_t t0 = min(2 * sub.by, L.tiles - 1), t1 = min(2 * sub.by + 1, L.tiles - 1);  // (an odd last tile is read twice)
             const uint8_t *img = p.img + (size_t)blockIdx.x * n_it * (2 * TC_OP_BYTES);
-            const uint8_t *w0 = p.w.tc + (size_t)t0 * n_it * TC_OP_BYTES, *w1 = p.w.tc + (size_t)t1 * n_it * TC_OP_BYTES;
-            const uint8_t *sd0 = p.w.tc + L.side + (size_t)t0 * n_sb * TC_SIDE_BYTES + TC_MINOP_BYTES;  // d[128] of a super-block
-            const uint8_t *sd1 = p.w.tc + L.side + (size_t)t1 * n_sb * TC_SIDE_BYTES + TC_MINOP_BYTES;
+            const uint8_t *w0 = sub.tc + (size_t)t0 * n_it * TC_OP_BYTES, *w1 = sub.tc + (size_t)t1 * n_it * TC_OP_BYTES;
+            const uint8_t *sd0 = sub.tc + L.side + (size_t)t0 * n_sb * TC_SIDE_BYTES + TC_MINOP_BYTES;  // d[128] of a super-block
+            const uint8_t *sd1 = sub.tc + L.side + (size_t)t1 * n_sb * TC_SIDE_BYTES + TC_MINOP_BYTES;
             uint32_t it = 0;
             bool ok = true;
             for (uint32_t sb = 0; sb < n_sb && ok; ++sb) {
@@ -540,7 +567,7 @@ __global__ void __launch_bounds__(TCW_THREADS, 1) gemm_tcw_kernel(const TcParams
                 }
             }
             const uint8_t *xm = p.xm + (size_t)blockIdx.x * n_mit * (2 * TCW_MINT_BYTES);
-            const uint8_t *m0 = p.w.tc + L.wmin + (size_t)t0 * n_mit * (2 * TCW_MINT_BYTES), *m1 = p.w.tc + L.wmin + (size_t)t1 * n_mit * (2 * TCW_MINT_BYTES);
+            const uint8_t *m0 = sub.tc + L.wmin + (size_t)t0 * n_mit * (2 * TCW_MINT_BYTES), *m1 = sub.tc + L.wmin + (size_t)t1 * n_mit * (2 * TCW_MINT_BYTES);
             for (uint32_t mi = 0; mi < n_mit && ok; ++mi, ++it) {
                 const uint32_t s = it % TCW_STAGES;
                 if (!tma::mbar_wait_blocking(empty_ab + s, ((it / TCW_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) break;
@@ -550,8 +577,8 @@ __global__ void __launch_bounds__(TCW_THREADS, 1) gemm_tcw_kernel(const TcParams
                 tma::bulk_g2s(dst + 2 * TCW_MINT_BYTES, m0 + (size_t)mi * (2 * TCW_MINT_BYTES), 2 * TCW_MINT_BYTES, full_ab + s);
                 tma::bulk_g2s(dst + 4 * TCW_MINT_BYTES, m1 + (size_t)mi * (2 * TCW_MINT_BYTES), 2 * TCW_MINT_BYTES, full_ab + s);
                 if (mi == 0) {  // 2^-s of the CTA's rows (read by the epilogue after the min GEMM)
-                    tma::bulk_g2s(tc_smem + TCW_RS_OFF, p.w.tc + L.rscale + (size_t)t0 * TC_BN * 4, TC_BN * 4, full_ab + s);
-                    tma::bulk_g2s(tc_smem + TCW_RS_OFF + TC_BN * 4, p.w.tc + L.rscale + (size_t)t1 * TC_BN * 4, TC_BN * 4, full_ab + s);
+                    tma::bulk_g2s(tc_smem + TCW_RS_OFF, sub.tc + L.rscale + (size_t)t0 * TC_BN * 4, TC_BN * 4, full_ab + s);
+                    tma::bulk_g2s(tc_smem + TCW_RS_OFF + TC_BN * 4, sub.tc + L.rscale + (size_t)t1 * TC_BN * 4, TC_BN * 4, full_ab + s);
                 }
             }
         }
@@ -603,8 +630,8 @@ __global__ void __launch_bounds__(TCW_THREADS, 1) gemm_tcw_kernel(const TcParams
         if (ok && col0 + tl < p.n) {
             // ---- the thread's 128 cells -> global memory: cell (row i, token j) at out[i * ldy + j * ldc]
             const uint32_t r0 = row0 + hh * TC_BN;
-            float *o = p.out + (size_t)r0 * p.ldy + (size_t)(col0 + tl) * p.ldc;
-            if (p.ldy == 1 && r0 + TC_BN <= p.m && ((uintptr_t)o & 15) == 0) {  // token-major output: 512 contiguous bytes
+            float *o = sub.out + (size_t)r0 * p.ldy + (size_t)(col0 + tl) * sub.ldc;
+            if (p.ldy == 1 && r0 + TC_BN <= sub.m && ((uintptr_t)o & 15) == 0) {  // token-major output: 512 contiguous bytes
 #pragma unroll
                 for (int i = 0; i < TC_BN / 4; ++i) {
                     float4 v = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
@@ -618,7 +645,7 @@ __global__ void __launch_bounds__(TCW_THREADS, 1) gemm_tcw_kernel(const TcParams
             } else {
 #pragma unroll
                 for (int i = 0; i < TC_BN; ++i)
-                    if (r0 + i < p.m) {
+                    if (r0 + i < sub.m) {
                         float *oi = o + (size_t)i * p.ldy;
                         *oi = p.epilogue == EPI_ADD ? __fadd_rn(*oi, acc[i]) : acc[i];
                     }
@@ -643,7 +670,8 @@ __global__ void __launch_bounds__(IMG ? TC_THREADS_IMG : TC_THREADS, 1) gemm_tc_
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC_STAGES + 4);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t col0 = blockIdx.x * TC_BM, row0 = blockIdx.y * TC_BN;
+    const TcSub sub = tc_select(p);
+    const uint32_t col0 = blockIdx.x * TC_BM, row0 = sub.by * TC_BN;
     const uint32_t n_sb = p.k / 256, n_it = n_sb * TC_STAGES;
     constexpr int TC_LOADER_WARP = IMG ? 1 : TC_W_WARPS + 1;  // the epilogue warps follow it
     if (tid == 0) {
@@ -713,7 +741,7 @@ __global__ void __launch_bounds__(IMG ? TC_THREADS_IMG : TC_THREADS, 1) gemm_tc_
     } else if (!IMG && warp <= TC_W_WARPS) {
         // ---------------------------------------------------------------- weight operand: thread = (weight row, half of the stage's bytes)
         const uint32_t r = (tid - 32) >> 1, half = (tid - 32) & 1;
-        const uint32_t row = min(row0 + r, p.m - 1);  // rows past the edge repeat the last one; their results are not stored
+        const uint32_t row = min(row0 + r, sub.m - 1);  // rows past the edge repeat the last one; their results are not stored
         // the raw bytes of a stage are fetched one stage ahead of their conversion (a thread converts every stage itself:
         // a global round trip per stage would bound the pipeline)
         TcRawW nxt = tc_fetch_w<T>(p.w, row, half, 0);
@@ -738,9 +766,9 @@ __global__ void __launch_bounds__(IMG ? TC_THREADS_IMG : TC_THREADS, 1) gemm_tc_
             const uint8_t *img = p.img + (size_t)blockIdx.x * n_it * (2 * TC_OP_BYTES);
             const uint8_t *img_min = p.img_min + (size_t)blockIdx.x * n_sb * TC_MINOP_BYTES;
             // the resident weight image of this row tile (null without one): operand tiles, then the per-super-block sides
-            const uint32_t tiles_m = (p.m + TC_BN - 1) / TC_BN;
-            const uint8_t *wimg = IMG ? p.w.tc + (size_t)blockIdx.y * n_it * TC_OP_BYTES : nullptr;
-            const uint8_t *wside = IMG ? p.w.tc + (size_t)tiles_m * n_it * TC_OP_BYTES + (size_t)blockIdx.y * n_sb * TC_SIDE_BYTES : nullptr;
+            const uint32_t tiles_m = (sub.m + TC_BN - 1) / TC_BN;
+            const uint8_t *wimg = IMG ? sub.tc + (size_t)sub.by * n_it * TC_OP_BYTES : nullptr;
+            const uint8_t *wside = IMG ? sub.tc + (size_t)tiles_m * n_it * TC_OP_BYTES + (size_t)sub.by * n_sb * TC_SIDE_BYTES : nullptr;
             for (uint32_t it = 0; it < n_it; ++it) {
                 const uint32_t st = it % TC_STAGES, sb = it / TC_STAGES;
                 if (!tma::mbar_wait_blocking(empty_ab + st, ((it / TC_STAGES) & 1) ^ 1, abort_flag, &g_tc_status, 8u)) break;
@@ -807,8 +835,8 @@ __global__ void __launch_bounds__(IMG ? TC_THREADS_IMG : TC_THREADS, 1) gemm_tc_
             }
             if (ok && col0 + tl < p.n) {
                 // ---- the thread's 64 cells -> global memory: cell (row i, token j) at out[i * ldy + j * ldc]
-                float *o = p.out + (size_t)(row0 + ch * 64) * p.ldy + (size_t)(col0 + tl) * p.ldc;
-                if (p.ldy == 1 && row0 + ch * 64 + 64 <= p.m && ((uintptr_t)o & 15) == 0) {  // token-major output: 256 contiguous bytes
+                float *o = sub.out + (size_t)(row0 + ch * 64) * p.ldy + (size_t)(col0 + tl) * sub.ldc;
+                if (p.ldy == 1 && row0 + ch * 64 + 64 <= sub.m && ((uintptr_t)o & 15) == 0) {  // token-major output: 256 contiguous bytes
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         float4 v = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
@@ -822,7 +850,7 @@ __global__ void __launch_bounds__(IMG ? TC_THREADS_IMG : TC_THREADS, 1) gemm_tc_
                 } else {
 #pragma unroll
                     for (int i = 0; i < 64; ++i)
-                        if (row0 + ch * 64 + i < p.m) {
+                        if (row0 + ch * 64 + i < sub.m) {
                             float *oi = o + (size_t)i * p.ldy;
                             *oi = p.epilogue == EPI_ADD ? __fadd_rn(*oi, acc[i]) : acc[i];
                         }
@@ -884,8 +912,8 @@ __global__ void __launch_bounds__(IMG ? TC_THREADS_IMG : TC_THREADS, 1) gemm_tc_
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const uint32_t row = row0 + ch * 64 + c4 * 16 + i;
-                        if (row < p.m) {
-                            float *o = p.out + (size_t)row * p.ldy + (size_t)(col0 + tl) * p.ldc;
+                        if (row < sub.m) {
+                            float *o = sub.out + (size_t)row * p.ldy + (size_t)(col0 + tl) * sub.ldc;
                             const float v = __uint_as_float(oreg[i]);
                             *o = p.epilogue == EPI_ADD ? __fadd_rn(*o, v) : v;
                         }
@@ -904,7 +932,7 @@ __global__ void __launch_bounds__(IMG ? TC_THREADS_IMG : TC_THREADS, 1) gemm_tc_
 }
 
 template <int T, bool IMG>
-int32_t launch_tc_typed(const TcParams &p, cudaStream_t st) {
+int32_t launch_tc_typed(const TcParams &p, uint32_t y_tiles, cudaStream_t st) {
     static thread_local int configured_dev = -1;  // (one per instantiation)
     int dev = 0;
     cudaGetDevice(&dev);
@@ -912,7 +940,7 @@ int32_t launch_tc_typed(const TcParams &p, cudaStream_t st) {
         CERA_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<T, IMG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
         configured_dev = dev;
     }
-    const dim3 grid((p.n + TC_BM - 1) / TC_BM, (p.m + TC_BN - 1) / TC_BN);
+    const dim3 grid((p.n + TC_BM - 1) / TC_BM, y_tiles);
     count_launch();
     return check_cuda(launch_k(gemm_tc_kernel<T, IMG>, grid, dim3(IMG ? TC_THREADS_IMG : TC_THREADS), (size_t)TC_SMEM_BYTES, st, p),
                       "gemm (tcgen05) launch");
@@ -1139,7 +1167,7 @@ int32_t launch_tc6(const TcParams &p, cudaStream_t st) {
     return check_cuda(launch_k(gemm_tc6_kernel, grid, dim3(TC_THREADS_IMG), (size_t)TC6_SMEM_BYTES, st, p), "gemm (tcgen05, Q6_K) launch");
 }
 
-int32_t launch_tc_wide(const TcParams &p, cudaStream_t st) {
+int32_t launch_tc_wide(const TcParams &p, uint32_t y_tiles, cudaStream_t st) {
     static thread_local int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1147,7 +1175,7 @@ int32_t launch_tc_wide(const TcParams &p, cudaStream_t st) {
         CERA_CUDA_TRY(cudaFuncSetAttribute(gemm_tcw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TCW_SMEM_BYTES));
         configured_dev = dev;
     }
-    const dim3 grid((p.n + TC_BM - 1) / TC_BM, (p.m + 2 * TC_BN - 1) / (2 * TC_BN));
+    const dim3 grid((p.n + TC_BM - 1) / TC_BM, y_tiles);
     count_launch();
     return check_cuda(launch_k(gemm_tcw_kernel, grid, dim3(TCW_THREADS), (size_t)TCW_SMEM_BYTES, st, p), "gemm (tcgen05, wide) launch");
 }
@@ -1218,19 +1246,24 @@ uint32_t gemm_tc_status() {
     return v;
 }
 
-// tcgen05 GEMM for Q4_K / Q5_K weights stored with interleaved row groups, k a multiple of 256, n > 32 columns.
-// *taken = false: not this kernel's case, nothing launched.  CERA_CUDA_GEMM=mma keeps the warp-level kernel.
-int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
-                       cudaStream_t st, bool *taken) {
+// One activation matrix against up to three weights (q / k / v, gate / up): the activation operands are converted once
+// and, when every weight has its image, ONE kernel launch covers all of them (the small matrices' CTAs run beside the
+// large one's instead of after them).  *taken = false: not these kernels' case, nothing launched.
+int32_t launch_gemm_tc_multi(const GemmTarget *t, int count, const ActView &x, size_t n, size_t ldy, int epilogue, cudaStream_t st,
+                             bool *taken) {
     *taken = false;
     static const bool off = [] {
         const char *e = getenv("CERA_CUDA_GEMM");
         return e && (strcmp(e, "mma") == 0 || strcmp(e, "columns") == 0);
     }();
-    if (off || n <= 32 || w.k % 256 || (w.type != CERA_TYPE_Q4_K && w.type != CERA_TYPE_Q5_K && w.type != CERA_TYPE_Q6_K)) return CERA_CUDA_OK;
+    if (off || count < 1 || count > 3 || n <= 32) return CERA_CUDA_OK;
+    const WeightView &w = t[0].w;
+    if (w.k % 256 || (w.type != CERA_TYPE_Q4_K && w.type != CERA_TYPE_Q5_K && w.type != CERA_TYPE_Q6_K)) return CERA_CUDA_OK;
     // Q6_K: only over its image, and only with at least two token tiles (a single tile of a long-k matrix leaves each of
     // the few CTAs a serial walk that the warp-level kernel's split-k clusters beat: 189 against 111 us at 4096 x 14336 x 64)
-    if (w.type == CERA_TYPE_Q6_K && (!w.tc || n <= 128)) return CERA_CUDA_OK;
+    if (w.type == CERA_TYPE_Q6_K && (!w.tc || n <= 128 || count > 1)) return CERA_CUDA_OK;
+    for (int i = 1; i < count; ++i)  // several weights: the same k, Q4_K / Q5_K, every one with its image
+        if (t[i].w.k != w.k || !t[i].w.tc || !w.tc || (t[i].w.type != CERA_TYPE_Q4_K && t[i].w.type != CERA_TYPE_Q5_K)) return CERA_CUDA_OK;
     if ((uintptr_t)x.quants % 16 || (uintptr_t)x.scales % 16 || (uintptr_t)x.sums % 16) return CERA_CUDA_OK;
     // the activation operands, converted once for all row tiles: a stream-ordered scratch allocation that lives for this
     // call (token tiles x stages x 32 KB, the min operand's token side, g and 1 / g)
@@ -1238,6 +1271,22 @@ int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *o
     const uint32_t nb32 = w.k / 32, n_mit = (nb32 + TCW_MIN_J - 1) / TCW_MIN_J;
     const size_t img_bytes = (size_t)tiles * n_it * (2 * TC_OP_BYTES), min_bytes = (size_t)tiles * n_sb * TC_MINOP_BYTES,
                  xm_bytes = (size_t)tiles * n_mit * (2 * TCW_MINT_BYTES);
+    {
+        // keep the stream-ordered pool's memory across synchronisations (by default a pool hands everything back to the
+        // driver at every synchronise, and the next prompt's first allocations pay for mapping it again); once per device
+        static thread_local int pooled_dev = -1;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (pooled_dev != dev) {
+            cudaMemPool_t pool = nullptr;
+            if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+                uint64_t keep = 1ull << 30;  // up to 1 GB of scratch stays cached
+                cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+            }
+            cudaGetLastError();
+            pooled_dev = dev;
+        }
+    }
     uint8_t *scratch = nullptr;
     if (cudaMallocAsync((void **)&scratch, img_bytes + min_bytes + xm_bytes + (size_t)n_pad * 8, st) != cudaSuccess) {
         cudaGetLastError();  // no room for the operand scratch: leave the GEMM to the kernels that need none
@@ -1261,33 +1310,54 @@ int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *o
     p.img_min = scratch + img_bytes;
     p.ginv = ginv_tab;
     p.xm = xm;
-    p.out = out;
+    p.out = t[0].out;
     p.m = w.m;
     p.n = (uint32_t)n;
     p.k = w.k;
     p.ldy = (uint32_t)ldy;
-    p.ldc = (uint32_t)ldc;
+    p.ldc = (uint32_t)t[0].ldc;
     p.epilogue = epilogue;
+    p.n_w = (uint32_t)count;
     *taken = true;
-    // with a weight image: the wide kernel when its 128 x 256 tiles alone fill the device, else the 128 x 128 one
+    // with weight images: the wide kernel when its 128 x 256 tiles alone fill the device, else the 128 x 128 one
     static const int tile_pref = [] {
         const char *e = getenv("CERA_CUDA_GEMM_TILE");
         return e ? atoi(e) : 0;
     }();
-    const uint32_t wide_ctas = tiles * ((w.m + 2 * TC_BN - 1) / (2 * TC_BN));
-    const bool wide = w.tc && (tile_pref == 256 || (tile_pref != 128 && wide_ctas >= 120));
+    uint32_t wide_y = 0;
+    for (int i = 0; i < count; ++i) wide_y += (t[i].w.m + 2 * TC_BN - 1) / (2 * TC_BN);
+    const bool wide = w.tc && (tile_pref == 256 || (tile_pref != 128 && tiles * wide_y >= 120));
+    uint32_t y = 0;
+    for (int i = 0; i < count; ++i) {
+        y += wide ? (t[i].w.m + 2 * TC_BN - 1) / (2 * TC_BN) : (t[i].w.m + TC_BN - 1) / TC_BN;
+        p.y_end[i] = y;
+        if (i) {
+            p.tc_x[i - 1] = t[i].w.tc;
+            p.out_x[i - 1] = t[i].out;
+            p.m_x[i - 1] = t[i].w.m;
+            p.ldc_x[i - 1] = (uint32_t)t[i].ldc;
+        }
+    }
     if (rc == CERA_CUDA_OK && w.type == CERA_TYPE_Q6_K) {
         rc = launch_tc6(p, st);
     } else if (rc == CERA_CUDA_OK && wide) {
-        rc = launch_tc_wide(p, st);
+        rc = launch_tc_wide(p, y, st);
     } else if (rc == CERA_CUDA_OK) {
         if (w.tc)
-            rc = w.type == CERA_TYPE_Q4_K ? launch_tc_typed<CERA_TYPE_Q4_K, true>(p, st) : launch_tc_typed<CERA_TYPE_Q5_K, true>(p, st);
+            rc = w.type == CERA_TYPE_Q4_K ? launch_tc_typed<CERA_TYPE_Q4_K, true>(p, y, st) : launch_tc_typed<CERA_TYPE_Q5_K, true>(p, y, st);
         else
-            rc = w.type == CERA_TYPE_Q4_K ? launch_tc_typed<CERA_TYPE_Q4_K, false>(p, st) : launch_tc_typed<CERA_TYPE_Q5_K, false>(p, st);
+            rc = w.type == CERA_TYPE_Q4_K ? launch_tc_typed<CERA_TYPE_Q4_K, false>(p, y, st) : launch_tc_typed<CERA_TYPE_Q5_K, false>(p, y, st);
     }
     cudaFreeAsync(scratch, st);  // after the kernels above, in stream order
     return rc;
+}
+
+// tcgen05 GEMM for K-quant weights stored with interleaved row groups, k a multiple of 256, n > 32 columns.
+// *taken = false: not this kernel's case, nothing launched.  CERA_CUDA_GEMM=mma keeps the warp-level kernel.
+int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
+                       cudaStream_t st, bool *taken) {
+    const GemmTarget t{w, out, ldc};
+    return launch_gemm_tc_multi(&t, 1, x, n, ldy, epilogue, st, taken);
 }
 
 }  // namespace cera

@@ -24,6 +24,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <initializer_list>
 #include <mutex>
 #include <new>
 #include <vector>
@@ -439,6 +440,15 @@ int32_t prefill_chunk(cera_cuda_model *m, const uint32_t *tokens, size_t n, size
                 CERA_CUDA_TRY(cudaMemcpy2DAsync(m->tp.peer[p] + off, cols * 4, src, src_pitch_elems * 4, l_cols * 4, n, cudaMemcpyDeviceToDevice, st));
         return launch_tp_exchange(m->tp, nullptr, 0, slot, st);
     };
+    // projections that share their activations (q / k / v, gate / up): one tensor-core launch when every weight has its
+    // operand image, else one GEMM each
+    auto gemm_group = [&](std::initializer_list<GemmTarget> ts, const ActView &x) -> int32_t {
+        bool taken = false;
+        CERA_TRY(launch_gemm_tc_multi(ts.begin(), (int)ts.size(), x, n, 1, EPI_STORE, st, &taken));
+        if (taken) return CERA_CUDA_OK;
+        for (const GemmTarget &t : ts) CERA_TRY(launch_gemm_ex(t.w, x, n, t.out, 1, t.ldc, EPI_STORE, st));
+        return CERA_CUDA_OK;
+    };
     if (tp) CERA_TRY(launch_tp_tick(m->tp_words, st));
     CERA_CUDA_TRY(cudaMemcpyAsync(m->pf_tokens, tokens, n * 4, cudaMemcpyHostToDevice, st));
     CERA_TRY(launch_embed_batch(m->embd->v, m->pf_tokens, n, m->pf_hidden, st));
@@ -449,9 +459,7 @@ int32_t prefill_chunk(cera_cuda_model *m, const uint32_t *tokens, size_t n, size
         const uint32_t s0 = 4 * li++;
         CERA_TRY(launch_rmsnorm(m->pf_hidden, L.attn_norm, hs, n, c.rms_norm_eps, nullptr, m->pf_act_hs.scales,
                                 m->pf_act_hs.quants, m->pf_act_hs.sums, st));
-        CERA_TRY(launch_gemm_ex(L.wq->v, m->pf_act_hs.view(), n, m->pf_q, 1, l_qd, EPI_STORE, st));
-        CERA_TRY(launch_gemm_ex(L.wk->v, m->pf_act_hs.view(), n, m->pf_k, 1, l_kvd, EPI_STORE, st));
-        CERA_TRY(launch_gemm_ex(L.wv->v, m->pf_act_hs.view(), n, m->pf_v, 1, l_kvd, EPI_STORE, st));
+        CERA_TRY(gemm_group({{L.wq->v, m->pf_q, l_qd}, {L.wk->v, m->pf_k, l_kvd}, {L.wv->v, m->pf_v, l_kvd}}, m->pf_act_hs.view()));
         CERA_TRY(launch_rope_batch(m->pf_q, m->pf_k, m->pf_v, start_pos, n, m->l_heads, m->l_kv_heads, c.head_dim,
                                    m->theta_scale, m->rope_freqs, c.rope_type, L.kc, L.vc, c.kv_f16, st, m->rope_table));
         CERA_TRY(launch_prefill_attention(m->pf_q, L.kc, L.vc, c.kv_f16, m->l_heads, m->l_kv_heads, c.head_dim, n, start_pos,
@@ -465,8 +473,7 @@ int32_t prefill_chunk(cera_cuda_model *m, const uint32_t *tokens, size_t n, size
         }
         CERA_TRY(launch_rmsnorm(m->pf_hidden, L.ffn_norm, hs, n, c.rms_norm_eps, nullptr, m->pf_act_hs.scales,
                                 m->pf_act_hs.quants, m->pf_act_hs.sums, st));
-        CERA_TRY(launch_gemm_ex(L.gate->v, m->pf_act_hs.view(), n, m->pf_g + (size_t)r * l_ff, 1, ff, EPI_STORE, st));
-        CERA_TRY(launch_gemm_ex(L.up->v, m->pf_act_hs.view(), n, m->pf_u + (size_t)r * l_ff, 1, ff, EPI_STORE, st));
+        CERA_TRY(gemm_group({{L.gate->v, m->pf_g + (size_t)r * l_ff, ff}, {L.up->v, m->pf_u + (size_t)r * l_ff, ff}}, m->pf_act_hs.view()));
         if (tp) {
             // (two copies, one signal: the second gather carries the slot)
             const size_t col_off = (size_t)r * l_ff, off = (size_t)((char *)(m->pf_g + col_off) - m->region);

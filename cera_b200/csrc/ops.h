@@ -73,6 +73,14 @@ int32_t launch_gemm_mma(const WeightView &w, const ActView &x, size_t n, float *
 // The same product on tcgen05 / TMEM (gemm_tc.cu): Q4_K / Q5_K, k a multiple of 256, more than 32 columns.
 int32_t launch_gemm_tc(const WeightView &w, const ActView &x, size_t n, float *out, size_t ldy, size_t ldc, int epilogue,
                        cudaStream_t st, bool *taken);
+// The same for up to three weights that take the same activations, in one launch when every weight has its image.
+struct GemmTarget {
+    WeightView w;
+    float *out;
+    size_t ldc;
+};
+int32_t launch_gemm_tc_multi(const GemmTarget *t, int count, const ActView &x, size_t n, size_t ldy, int epilogue, cudaStream_t st,
+                             bool *taken);
 uint32_t gemm_tc_status();  // nonzero after a bounded wait of that kernel ran out
 uint32_t gemv_exact_status();
 // One work item of an expert-grouped GEMM: `count` consecutive activation columns starting at `first` go through
