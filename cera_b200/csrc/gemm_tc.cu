@@ -24,7 +24,7 @@
 // The activation operands are converted ONCE per GEMM by two small kernels (a per-token range search for g, then the
 // high / low operand tiles written to a stream-ordered scratch buffer in the shared-memory layout of the GEMM kernels,
 // so that a stage's 32 KB arrive by one bulk asynchronous copy).  The weight operand comes from a RESIDENT IMAGE of the
-// weight (weight_prepare_tc: sc * q as f16 in the same tile layout, about 2.2 bytes per weight, built when a model sees
+// weight (weight_prepare_tc: sc * q as f16 in the same tile layout, about 2.3 bytes per weight, built when a model sees
 // its first batched prompt or a caller asks for it), so a stage is a few bulk copies and 8-16 MMAs; a weight without an
 // image has its operand built in shared memory by producer warps straight from the quantized bytes (nibble -> 0x6400|q
 // -> one HFMA2 with the sub-block scale), same results.  Tiles use the canonical K-major no-swizzle layout (8-row x

@@ -412,7 +412,7 @@ int32_t prefill_chunk(cera_cuda_model *m, const uint32_t *tokens, size_t n, size
     const float res_scale = c.residual_scale != 0.0f ? c.residual_scale : 1.0f;
     if (n > 32 && !m->tc_prepared) {
         // the first batched prompt builds the f16 operand images of the tensor-core GEMM's weights (a decode-only model
-        // never pays their 2.2 bytes per weight; a weight that gets none is converted on the fly)
+        // never pays their 2.3 bytes per weight; a weight that gets none is converted on the fly)
         m->tc_prepared = true;
         for (auto &L : m->layers)
             for (cera_cuda_weight *w : {L.wq, L.wk, L.wv, L.wo, L.gate, L.up, L.down}) {

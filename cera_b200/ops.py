@@ -52,12 +52,18 @@ class QuantWeight:
         self.handle, self.type, self.m, self.k = h, ggml_type, m, k
 
     def prepare_gemm(self):
-        """Build the resident f16 operand image for many-column GEMMs (K-quants, k a multiple of 256; about 2.2 extra
+        """Build the resident f16 operand image for many-column GEMMs (K-quants, k a multiple of 256; about 2.3 extra
         bytes per weight, 4 for Q6_K).  True when the weight now holds one; without it the GEMM converts on the fly
         (Q6_K: runs the warp-level kernel), same results within tolerance."""
         has = C.c_int32(0)
         check(lib.cera_cuda_weight_prepare_gemm(self.handle, C.byref(has)))
         return bool(has.value)
+
+    def device_bytes(self):
+        """Device memory the weight holds: its planes, the one-column scratch and, once built, the operand image."""
+        n = C.c_size_t(0)
+        check(lib.cera_cuda_weight_info(self.handle, None, None, None, C.byref(n)))
+        return int(n.value)
 
     def close(self):
         if getattr(self, "handle", None):

@@ -80,7 +80,7 @@ CERA_API int32_t cera_cuda_weight_create(int32_t ggml_type, size_t m, size_t k, 
 CERA_API void cera_cuda_weight_free(cera_cuda_weight *w);
 /* Optional, for weights that will see many-column GEMMs (cera_cuda_gemm_preq with more than 32 columns; the reference
  * reaches that path through quantized_matmul_preq, cera/src/model/transformer.rs:790-820): builds a device-resident f16
- * operand image of a K-quant weight (k a multiple of 256) for the tensor-core kernels: about 2.2 extra bytes per weight
+ * operand image of a K-quant weight (k a multiple of 256) for the tensor-core kernels: about 2.3 extra bytes per weight
  * for Q4_K / Q5_K, 4 for Q6_K (whose products of scale and quant need two f16 operands).  *has_image (optional) = 1
  * when the weight now holds one; 0 when the type or shape is not those kernels', the device has no room, or
  * CERA_CUDA_TC_IMAGE=0 - Q4_K / Q5_K GEMMs then convert the quantized bytes on the fly and Q6_K runs the warp-level

@@ -205,6 +205,27 @@ def test_gemm_on_reference_fixtures():
             assert np.all(np.abs(got - want) <= 1e-5 * np.maximum(np.abs(want), 1.0)), (t, m, n)
 
 
+def test_operand_image_is_built_once_and_accounted():
+    """cera_cuda_weight_prepare_gemm: about 2.3 bytes per weight for Q4_K / Q5_K, 4 for Q6_K, reported by weight_info;
+    a second call changes nothing; types and shapes outside the tensor-core kernels get none."""
+    need_gpu()
+    import cera_b200 as cb
+    m, k = 256, 2048
+    for t, per_weight in ((O.Q4_K, 2.0), (O.Q5_K, 2.0), (O.Q6_K, 4.0)):
+        w = cb.QuantWeight(t, m, k, cb.quantize_weights(t, cb.synth_normal(m * k, seed=3, sigma=0.02)))
+        before = w.device_bytes()
+        assert w.prepare_gemm()
+        grown = w.device_bytes() - before
+        assert per_weight * m * k <= grown <= (per_weight + 0.35) * m * k, (t, grown)
+        assert w.prepare_gemm() and w.device_bytes() - before == grown
+        w.close()
+    for t, kk in ((O.Q4_0, 2048), (O.Q8_0, 2048), (O.Q4_1, 1024)):
+        w = cb.QuantWeight(t, 64, kk, cb.quantize_weights(t, cb.synth_normal(64 * kk, seed=4, sigma=0.02)))
+        before = w.device_bytes()
+        assert not w.prepare_gemm() and w.device_bytes() == before
+        w.close()
+
+
 def test_gemm_preq_declines_loudly():
     torch = need_gpu()
     import cera_b200 as cb
