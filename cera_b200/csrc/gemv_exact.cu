@@ -407,8 +407,11 @@ __global__ void __launch_bounds__((TEAM ? XG_MAX_WARPS : XG_LONE_MAX_WARPS) * 32
                             hi[wd] |= ((hbw >> (sh_lo + 1)) & 0x01010101u) << 4;
                         }
                         if (T == CERA_TYPE_Q6_K) {
-                            lo[wd] |= ((hbw >> (2 * pair)) & 0x03030303u) << 4;
-                            hi[wd] |= ((hbw >> (2 * pair + 4)) & 0x03030303u) << 4;
+                            // bits 2 pair, 2 pair + 1 of each high-bit byte belong to the low-nibble element, bits 2 pair + 4,
+                            // 2 pair + 5 to the high-nibble one: one shift brings the first pair to bits 0-1 and the second to 4-5
+                            const uint32_t hs = hbw >> (2 * pair);
+                            lo[wd] |= (hs << 4) & 0x30303030u;
+                            hi[wd] |= hs & 0x30303030u;
                         }
                     }
                     // the subtraction of the bias and the FMA run as packed pairs (add.f32x2 / fma.f32x2: each half is the
