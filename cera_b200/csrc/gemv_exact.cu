@@ -67,6 +67,10 @@ constexpr int XG_MAX_STAGES = 8;
 constexpr int XG_HEAD_BYTES = 2112;                  // barriers [32][8], then the abort flag
 constexpr int XG_MAGIC_I = 0x4B400000;               // bits of 12582912.0f = 1.5 * 2^23
 constexpr float XG_MAGIC_F = 12582912.0f;
+// The same trick for high nibbles left in place (16 x the quant in each byte, Q4_K): on the bits of 1.5 * 2^19, whose unit in
+// the last place is 1/16, the accumulated 16 * sum moves the value by exactly sum - no shift of the nibbles needed.
+constexpr int XG_MAGIC16_I = 0x49400000;
+constexpr float XG_MAGIC16_F = 786432.0f;
 constexpr size_t XG_SMEM_LIMIT = 224 * 1024;
 constexpr uint32_t XG_SCT_BYTES = 1024;              // per warp: the segment's block scales, [task][row][...]
 
@@ -400,7 +404,7 @@ __global__ void __launch_bounds__((TEAM ? XG_MAX_WARPS : XG_LONE_MAX_WARPS) * 32
                     for (int wd = 0; wd < 4; ++wd) {
                         const uint32_t v = word_of(piece, wd), hbw = word_of(hb, wd);
                         lo[wd] = v & 0x0F0F0F0Fu;
-                        hi[wd] = (v >> 4) & 0x0F0F0F0Fu;
+                        hi[wd] = T == CERA_TYPE_Q4_K ? v & 0xF0F0F0F0u : (v >> 4) & 0x0F0F0F0Fu;
                         if (T == CERA_TYPE_Q5_K) {
                             const int sh_lo = 4 * hf + 2 * pair;  // fifth-bit position of the low-nibble sub-block
                             lo[wd] |= ((hbw >> sh_lo) & 0x01010101u) << 4;
@@ -417,19 +421,21 @@ __global__ void __launch_bounds__((TEAM ? XG_MAX_WARPS : XG_LONE_MAX_WARPS) * 32
                     // the subtraction of the bias and the FMA run as packed pairs (add.f32x2 / fma.f32x2: each half is the
                     // IEEE operation of the scalar form, two chains per instruction)
                     const float2 nbias = make_float2(-XG_MAGIC_F, -XG_MAGIC_F), s_lo = make_float2(sc2.x, sc2.x), s_hi = make_float2(sc2.y, sc2.y);
+                    constexpr int MAGIC_HI = T == CERA_TYPE_Q4_K ? XG_MAGIC16_I : XG_MAGIC_I;
+                    const float2 nbias_hi = T == CERA_TYPE_Q4_K ? make_float2(-XG_MAGIC16_F, -XG_MAGIC16_F) : nbias;
                     scs[i] = sc2;
 #pragma unroll
                     for (int wp = 0; wp < 2; ++wp) {
                         const float2 rl = make_float2(__int_as_float(dp_us(lo[2 * wp], word_of(alo, 2 * wp), XG_MAGIC_I)),
                                                       __int_as_float(dp_us(lo[2 * wp + 1], word_of(alo, 2 * wp + 1), XG_MAGIC_I)));
-                        const float2 rh = make_float2(__int_as_float(dp_us(hi[2 * wp], word_of(ahi, 2 * wp), XG_MAGIC_I)),
-                                                      __int_as_float(dp_us(hi[2 * wp + 1], word_of(ahi, 2 * wp + 1), XG_MAGIC_I)));
+                        const float2 rh = make_float2(__int_as_float(dp_us(hi[2 * wp], word_of(ahi, 2 * wp), MAGIC_HI)),
+                                                      __int_as_float(dp_us(hi[2 * wp + 1], word_of(ahi, 2 * wp + 1), MAGIC_HI)));
                         if (TEAM) {
                             pl[i][wp] = __fadd2_rn(rl, nbias);
-                            ph[i][wp] = __fadd2_rn(rh, nbias);
+                            ph[i][wp] = __fadd2_rn(rh, nbias_hi);
                         } else {
                             acc_lo2[wp] = __ffma2_rn(__fadd2_rn(rl, nbias), s_lo, acc_lo2[wp]);
-                            acc_hi2[wp] = __ffma2_rn(__fadd2_rn(rh, nbias), s_hi, acc_hi2[wp]);
+                            acc_hi2[wp] = __ffma2_rn(__fadd2_rn(rh, nbias_hi), s_hi, acc_hi2[wp]);
                         }
                     }
                 }
